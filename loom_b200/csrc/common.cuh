@@ -1,0 +1,201 @@
+// common.cuh -- shared declarations of the loom_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/loom_b200.h"
+
+// ---- device layout of a packed ternary matrix -------------------------------------------------
+//
+// The reference keeps a matrix row-major, 16 two-bit codes per u32 (code = weight + 1).  On upload
+// it is re-tiled into 512-byte tiles of 16 rows x 128 columns.  Inside a tile, lane L = g*4 + t
+// (g = 0..7, t = 0..3) owns 16 contiguous bytes holding four of the reference's words:
+//     [ word(row g, t), word(row g+8, t), word(row g, 4+t), word(row g+8, 4+t) ]
+// where word(r, i) is the i-th u32 (columns 16i..16i+15) of row r inside the tile's 128-column block.
+// A warp therefore reads a tile with one fully coalesced 16-byte access per lane, and the four words a
+// lane holds are exactly the rows/columns that lane feeds to an m16n8k32 integer MMA (or four dp4a
+// pairs).  Tiles are stored strip-major: tile index = strip * kblocks + kblock, strip = row / 16.
+// Rows are padded to a multiple of 16 and columns to a multiple of 128 with code 1 (weight 0), so the
+// hot loop never masks a tail.
+constexpr int kTileRows = 16;
+constexpr int kTileCols = 128;
+constexpr int kTileBytes = 512;
+constexpr int kTileWords = 128;
+
+struct loom_b200_weight {
+    int rows = 0, cols = 0, row_words = 0;
+    int strips = 0, kblocks = 0;  // padded rows / 16, padded cols / 128
+    float scale = 1.0f;
+    uint32_t* tiles = nullptr;  // strips * kblocks * 128 u32
+    int device = 0;
+    size_t tile_bytes() const { return (size_t)strips * kblocks * kTileBytes; }
+};
+
+struct loom_b200_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 148;
+    std::string last_error;
+    uint64_t launches = 0;
+    // scratch of the stream-K fix-up: int32 partial sums and arrival counters.  Both are zero
+    // whenever no kernel is in flight (the last arriver of every group clears what it used).
+    int32_t* fix_acc = nullptr;
+    unsigned int* fix_cnt = nullptr;
+    size_t fix_acc_elems = 0, fix_cnt_elems = 0;
+    // small device scratch reused by the layer-level calls
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    // device status word written by kernels with bounded waits (0 = ok)
+    int* status_dev = nullptr;
+    unsigned func_attr_mask = 0;  // kernels whose shared-memory limit was raised on this device
+    // tuning knobs (loom_b200_ctx_set_option; initial values from LOOM_B200_* environment variables)
+    int opt_gemv_variant = 0;      // 0 = integer-MMA inner loop, 1 = dp4a inner loop (batch 1 only)
+    int opt_gemv_ctas_per_sm = 2;  // grid = SMs * this
+    int opt_pdl = 1;               // programmatic dependent launch on/off
+};
+
+int lb_fail(loom_b200_ctx* ctx, int code, const char* fmt, ...);
+const char* lb_global_error();
+int lb_ensure_fixup(loom_b200_ctx* ctx, size_t acc_elems, size_t cnt_elems);
+int lb_ensure_scratch(loom_b200_ctx* ctx, size_t bytes);
+
+#define LB_CUDA(ctx, expr)                                                                          \
+    do {                                                                                            \
+        cudaError_t _e = (expr);                                                                    \
+        if (_e != cudaSuccess)                                                                      \
+            return lb_fail((ctx), LOOM_B200_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,             \
+                           cudaGetErrorString(_e), __FILE__, __LINE__);                             \
+    } while (0)
+
+#define LB_CHECK_LAUNCH(ctx, name)                                                                  \
+    do {                                                                                            \
+        cudaError_t _e = cudaGetLastError();                                                        \
+        if (_e != cudaSuccess)                                                                      \
+            return lb_fail((ctx), LOOM_B200_ERR_CUDA, "launch of %s failed: %s", (name),          \
+                           cudaGetErrorString(_e));                                                 \
+        (ctx)->launches++;                                                                          \
+    } while (0)
+
+#define LB_REQUIRE(ctx, cond, ...)                                                                  \
+    do {                                                                                            \
+        if (!(cond)) return lb_fail((ctx), LOOM_B200_ERR_INVALID, __VA_ARGS__);                     \
+    } while (0)
+
+static inline int lb_set_device(loom_b200_ctx* ctx) {
+    cudaError_t e = cudaSetDevice(ctx->device);
+    if (e != cudaSuccess) return lb_fail(ctx, LOOM_B200_ERR_CUDA, "cudaSetDevice(%d): %s", ctx->device, cudaGetErrorString(e));
+    return 0;
+}
+
+// ---- arithmetic helpers (device) ----------------------------------------------------------------
+// The CPU contract is IEEE double without fused multiply-add; the intrinsics below pin the rounding
+// of every step so that the compiler cannot contract them.
+
+__device__ __forceinline__ float lb_abs_to_f32(float v) { return fabsf(v); }
+
+// bitNetQuantizedActivation: int8(clamp(Round(float64(v) * (127/float64(amax))), -128, 127))
+__device__ __forceinline__ int lb_quant_i8(double v, double s) {
+    double r = round(__dmul_rn(v, s));  // round(): half away from zero, like Go's math.Round
+    r = fmin(fmax(r, -128.0), 127.0);
+    return (int)r;
+}
+
+// outputScale = float64(scale) * float64(amax) / 127, zero -> 1
+__device__ __forceinline__ double lb_output_scale(float scale, float amax) {
+    double os = __ddiv_rn(__dmul_rn((double)scale, (double)amax), 127.0);
+    return os == 0.0 ? 1.0 : os;
+}
+
+__device__ __forceinline__ double lb_gate_product(double g, double u, int act) {
+    if (act == LOOM_B200_ACT_RELU2) {
+        if (g < 0) g = 0;
+        return __dmul_rn(__dmul_rn(g, g), u);
+    }
+    double sig = __ddiv_rn(1.0, __dadd_rn(1.0, exp(-g)));
+    return __dmul_rn(__dmul_rn(g, sig), u);
+}
+
+// Activate[float32], poly/poly.go:167-200
+__device__ __forceinline__ float lb_activate(float v, int act) {
+    switch (act) {
+        case LOOM_B200_ACT_RELU: return v < 0.f ? 0.f : v;
+        case LOOM_B200_ACT_SILU: return __fmul_rn(v, (float)__ddiv_rn(1.0, __dadd_rn(1.0, exp(-(double)v))));
+        case LOOM_B200_ACT_GELU: {
+            double x = (double)v;
+            double inner = __dmul_rn(sqrt(2.0 / 3.14159265358979323846),
+                                     __dadd_rn(x, __dmul_rn(0.044715, pow(x, 3.0))));
+            return (float)__dmul_rn(__dmul_rn(0.5, x), __dadd_rn(1.0, tanh(inner)));
+        }
+        case LOOM_B200_ACT_TANH: return (float)tanh((double)v);
+        case LOOM_B200_ACT_SIGMOID: return (float)__ddiv_rn(1.0, __dadd_rn(1.0, exp(-(double)v)));
+        case LOOM_B200_ACT_LEAKY_RELU: return v < 0.f ? (float)__dmul_rn((double)v, 0.01) : v;
+        case LOOM_B200_ACT_RELU2: return v < 0.f ? 0.f : __fmul_rn(v, v);
+        default: return v;
+    }
+}
+
+__device__ __forceinline__ float lb_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ double lb_warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ int lb_warp_sum_i(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ---- sm_100a plumbing: mbarrier, bulk async copy (TMA engine), programmatic dependent launch ------
+
+__device__ __forceinline__ uint32_t lb_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void lb_mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(lb_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void lb_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(lb_smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool lb_mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(lb_smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls and returns false (callers set an error flag and leave).
+__device__ __forceinline__ bool lb_mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = 4000000u) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (lb_mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void lb_fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+// 1-D bulk copy global -> shared through the TMA engine; dst/src 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void lb_bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     lb_smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(lb_smem_u32(bar))
+                 : "memory");
+}
+// Programmatic dependent launch: wait for the kernels this one depends on / release dependents.
+__device__ __forceinline__ void lb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void lb_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
