@@ -49,6 +49,7 @@ extern "C" {
 #define LOOM_B200_ACT_LINEAR (-1)
 
 typedef struct loom_b200_ctx loom_b200_ctx;       /* stands in for *poly.WGPUContext */
+typedef struct loom_b200_graph loom_b200_graph;   /* a recorded command buffer (one frame) */
 typedef struct loom_b200_weight loom_b200_weight; /* a packed ternary matrix resident in HBM:
                                                      WeightStore.GPUWeights[key] + GPUScaleValues[key],
                                                      poly/weights.go:14-24 */
@@ -69,6 +70,15 @@ int loom_b200_ctx_create(int device, void* stream, loom_b200_ctx** out);
 void loom_b200_ctx_destroy(loom_b200_ctx* ctx);
 /* FlushFrame + wait, poly/wgpu_context_native.go:276 */
 int loom_b200_sync(loom_b200_ctx* ctx);
+/* BeginFrame ... FlushFrame (poly/wgpu_context_native.go:263-276, used once per forward by
+ * ForwardTokenIDsWGPU, poly/wgpu_forward.go:99,564): the dispatches issued between begin and end are
+ * recorded into a CUDA graph instead of running; graph_launch replays them with one submission.
+ * Run the same dispatches once before graph_begin so that every scratch buffer already has its size;
+ * allocation, upload, download and sync are refused while recording. */
+int loom_b200_graph_begin(loom_b200_ctx* ctx);
+int loom_b200_graph_end(loom_b200_ctx* ctx, loom_b200_graph** out);
+int loom_b200_graph_launch(loom_b200_ctx* ctx, loom_b200_graph* graph);
+void loom_b200_graph_free(loom_b200_ctx* ctx, loom_b200_graph* graph);
 /* the cudaStream_t the context launches on */
 void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
 /* Tuning knobs, the counterpart of the tileSize argument the WGSL dispatchers take

@@ -42,6 +42,10 @@ SIGNATURES = {
     "loom_b200_ctx_destroy": (None, [_vp]),
     "loom_b200_sync": (_i, [_vp]),
     "loom_b200_ctx_stream": (_vp, [_vp]),
+    "loom_b200_graph_begin": (_i, [_vp]),
+    "loom_b200_graph_end": (_i, [_vp, C.POINTER(_vp)]),
+    "loom_b200_graph_launch": (_i, [_vp, _vp]),
+    "loom_b200_graph_free": (None, [_vp, _vp]),
     "loom_b200_launch_count": (C.c_uint64, [_vp]),
     "loom_b200_ctx_set_option": (_i, [_vp, C.c_char_p, _i]),
     "loom_b200_buffer_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
@@ -160,6 +164,20 @@ class Context:
 
     def sync(self):
         self._check(lib().loom_b200_sync(self.h))
+
+    def graph_begin(self):
+        self._check(lib().loom_b200_graph_begin(self.h))
+
+    def graph_end(self):
+        g = _vp()
+        self._check(lib().loom_b200_graph_end(self.h, C.byref(g)))
+        return g
+
+    def graph_launch(self, g):
+        self._check(lib().loom_b200_graph_launch(self.h, g))
+
+    def graph_free(self, g):
+        lib().loom_b200_graph_free(self.h, g)
 
     def set_option(self, key: str, value: int):
         self._check(lib().loom_b200_ctx_set_option(self.h, key.encode(), int(value)))

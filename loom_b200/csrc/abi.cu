@@ -29,7 +29,20 @@ int lb_fail(loom_b200_ctx* ctx, int code, const char* fmt, ...) {
 
 const char* lb_global_error() { return g_global_error.c_str(); }
 
+struct loom_b200_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
+#define LB_NO_CAPTURE(ctx, what)                                                                               \
+    do {                                                                                                       \
+        if ((ctx)->capturing)                                                                                  \
+            return lb_fail((ctx), LOOM_B200_ERR_INVALID, "%s is not allowed between graph_begin and graph_end", what); \
+    } while (0)
+
 int lb_ensure_fixup(loom_b200_ctx* ctx, size_t acc_elems, size_t cnt_elems) {
+    if ((acc_elems > ctx->fix_acc_elems || cnt_elems > ctx->fix_cnt_elems) && ctx->capturing)
+        return lb_fail(ctx, LOOM_B200_ERR_INVALID, "scratch would grow while recording a graph: run the same calls once before graph_begin");
     if (acc_elems > ctx->fix_acc_elems) {
         // growing happens between launches on this stream; wait for users of the old buffer first
         LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -54,6 +67,7 @@ int lb_ensure_fixup(loom_b200_ctx* ctx, size_t acc_elems, size_t cnt_elems) {
 
 int lb_ensure_scratch(loom_b200_ctx* ctx, size_t bytes) {
     if (bytes <= ctx->scratch_bytes) return 0;
+    LB_NO_CAPTURE(ctx, "growing the scratch buffer");
     LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ctx->scratch) cudaFree(ctx->scratch);
     ctx->scratch = nullptr;
@@ -298,6 +312,8 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
     } else if (!strcmp(key, "gemv_ctas_per_sm")) {
         LB_REQUIRE(ctx, value >= 1 && value <= 8, "ctx_set_option: gemv_ctas_per_sm must be in [1,8]");
         ctx->opt_gemv_ctas_per_sm = value;
+    } else if (!strcmp(key, "debug")) {
+        ctx->opt_debug = value;
     } else if (!strcmp(key, "pdl")) {
         ctx->opt_pdl = value != 0;
     } else {
@@ -320,9 +336,63 @@ void loom_b200_ctx_destroy(loom_b200_ctx* ctx) {
 
 int loom_b200_sync(loom_b200_ctx* ctx) {
     if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "sync: ctx is NULL");
+    LB_NO_CAPTURE(ctx, "sync");
     if (int rc = lb_set_device(ctx)) return rc;
     LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return 0;
+}
+
+int loom_b200_graph_begin(loom_b200_ctx* ctx) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "graph_begin: ctx is NULL");
+    LB_NO_CAPTURE(ctx, "graph_begin");
+    if (int rc = lb_set_device(ctx)) return rc;
+    LB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    return 0;
+}
+
+int loom_b200_graph_end(loom_b200_ctx* ctx, loom_b200_graph** out) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "graph_end: ctx is NULL");
+    LB_REQUIRE(ctx, out != nullptr, "graph_end: out is NULL");
+    LB_REQUIRE(ctx, ctx->capturing, "graph_end without graph_begin");
+    *out = nullptr;
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+    if (e != cudaSuccess || !g) {
+        cudaGetLastError();
+        return lb_fail(ctx, LOOM_B200_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    }
+    auto* gr = new loom_b200_graph();
+    gr->graph = g;
+    e = cudaGraphInstantiate(&gr->exec, g, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(g);
+        delete gr;
+        return lb_fail(ctx, LOOM_B200_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    }
+    *out = gr;
+    return 0;
+}
+
+int loom_b200_graph_launch(loom_b200_ctx* ctx, loom_b200_graph* graph) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "graph_launch: ctx is NULL");
+    LB_REQUIRE(ctx, graph && graph->exec, "graph_launch: graph is NULL");
+    LB_NO_CAPTURE(ctx, "graph_launch");
+    if (int rc = lb_set_device(ctx)) return rc;
+    LB_CUDA(ctx, cudaGraphLaunch(graph->exec, ctx->stream));
+    return 0;
+}
+
+void loom_b200_graph_free(loom_b200_ctx* ctx, loom_b200_graph* graph) {
+    if (!graph) return;
+    if (ctx) {
+        cudaSetDevice(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+    }
+    if (graph->exec) cudaGraphExecDestroy(graph->exec);
+    if (graph->graph) cudaGraphDestroy(graph->graph);
+    delete graph;
 }
 
 void* loom_b200_ctx_stream(loom_b200_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
@@ -331,6 +401,7 @@ uint64_t loom_b200_launch_count(const loom_b200_ctx* ctx) { return ctx ? ctx->la
 int loom_b200_buffer_alloc(loom_b200_ctx* ctx, size_t bytes, void** dptr) {
     if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "buffer_alloc: ctx is NULL");
     LB_REQUIRE(ctx, dptr != nullptr, "buffer_alloc: dptr is NULL");
+    LB_NO_CAPTURE(ctx, "buffer_alloc");
     if (int rc = lb_set_device(ctx)) return rc;
     *dptr = nullptr;
     LB_CUDA(ctx, cudaMalloc(dptr, bytes ? bytes : 1));
@@ -340,6 +411,7 @@ int loom_b200_buffer_alloc(loom_b200_ctx* ctx, size_t bytes, void** dptr) {
 int loom_b200_buffer_free(loom_b200_ctx* ctx, void* dptr) {
     if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "buffer_free: ctx is NULL");
     if (!dptr) return 0;
+    LB_NO_CAPTURE(ctx, "buffer_free");
     if (int rc = lb_set_device(ctx)) return rc;
     LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     LB_CUDA(ctx, cudaFree(dptr));
@@ -350,6 +422,7 @@ int loom_b200_buffer_upload(loom_b200_ctx* ctx, void* dst, const void* src, size
     if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "buffer_upload: ctx is NULL");
     LB_REQUIRE(ctx, (dst && src) || bytes == 0, "buffer_upload: NULL pointer");
     if (bytes == 0) return 0;
+    LB_NO_CAPTURE(ctx, "buffer_upload");
     if (int rc = lb_set_device(ctx)) return rc;
     // The caller's memory may be pageable and may be reused after return: finish the copy here.
     LB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -361,6 +434,7 @@ int loom_b200_buffer_download(loom_b200_ctx* ctx, void* dst, const void* src, si
     if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "buffer_download: ctx is NULL");
     LB_REQUIRE(ctx, (dst && src) || bytes == 0, "buffer_download: NULL pointer");
     if (bytes == 0) return 0;
+    LB_NO_CAPTURE(ctx, "buffer_download");
     if (int rc = lb_set_device(ctx)) return rc;
     LB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

@@ -60,6 +60,8 @@ struct loom_b200_ctx {
     int opt_gemv_variant = 0;      // 0 = integer-MMA inner loop, 1 = dp4a inner loop (batch 1 only)
     int opt_gemv_ctas_per_sm = 2;  // grid = SMs * this
     int opt_pdl = 1;               // programmatic dependent launch on/off
+    int opt_debug = 0;             // timing experiments (results are wrong when non-zero)
+    bool capturing = false;        // between graph_begin and graph_end
 };
 
 int lb_fail(loom_b200_ctx* ctx, int code, const char* fmt, ...);

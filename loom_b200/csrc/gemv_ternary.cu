@@ -28,9 +28,9 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kStageTiles = 4;                          // tiles per ring stage (2 KB)
-constexpr int kStages = 6;                              // stages per warp
-constexpr int kStageBytes = kStageTiles * kTileBytes;   // 2048
+constexpr int kStageTiles = 8;                          // tiles per ring stage (4 KB)
+constexpr int kStages = 3;                              // stages per warp
+constexpr int kStageBytes = kStageTiles * kTileBytes;   // 4096
 constexpr int kRingBytes = kWarps * kStages * kStageBytes;  // 98304
 constexpr int kMaxM = 8;
 
@@ -259,7 +259,7 @@ __device__ __forceinline__ void finish_row(const LbGemvParams& p, const Smem& sm
 }
 
 template <bool MMA>
-__global__ void __launch_bounds__(kThreads) lb_gemv_ternary_kernel(const LbGemvParams p) {
+__global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const LbGemvParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int KB = p.kblocks, M = p.M;
@@ -304,26 +304,42 @@ __global__ void __launch_bounds__(kThreads) lb_gemv_ternary_kernel(const LbGemvP
     uint8_t* my_ring = sm.ring + (size_t)warp * kStages * kStageBytes;
     uint64_t* my_bars = sm.bars + warp * kStages;
 
-    auto chunk_len = [&](int pos) {
-        int kb = pos % KB;
-        int len = KB - kb;
+    // Cursors walk the warp's tile range chunk by chunk; a chunk never crosses a strip, so (strip, kblock)
+    // advance without any division.
+    struct Cursor {
+        int pos, v, kb;
+    };
+    auto chunk_len = [&](const Cursor& c) {
+        int len = KB - c.kb;
         if (len > kStageTiles) len = kStageTiles;
-        if (len > w1 - pos) len = w1 - pos;
+        if (len > w1 - c.pos) len = w1 - c.pos;
         return len;
     };
-    auto issue = [&](int stage, int pos, int len) {  // lane 0 only
-        int v = pos / KB, kb = pos - v * KB;
+    auto advance = [&](Cursor& c, int len) {
+        c.pos += len;
+        c.kb += len;
+        if (c.kb >= KB) {
+            c.kb = 0;
+            c.v++;
+        }
+    };
+    auto issue = [&](int stage, const Cursor& c, int len) {  // lane 0 only
+        if (p.debug == 2) return;
         lb_mbar_expect_tx(&my_bars[stage], (uint32_t)len * kTileBytes);
-        lb_bulk_g2s(my_ring + (size_t)stage * kStageBytes, tile_ptr(p, v, kb), (uint32_t)len * kTileBytes,
+        lb_bulk_g2s(my_ring + (size_t)stage * kStageBytes, tile_ptr(p, c.v, c.kb), (uint32_t)len * kTileBytes,
                     &my_bars[stage]);
     };
 
     // first ring fill: weights do not depend on the producer of the activations
-    int ipos = w0;
-    for (int s = 0; s < kStages && ipos < w1; ++s) {
-        int len = chunk_len(ipos);
-        if (lane == 0) issue(s, ipos, len);
-        ipos += len;
+    Cursor ic;
+    ic.pos = w0;
+    ic.v = w0 / KB;
+    ic.kb = w0 - ic.v * KB;
+    Cursor cc = ic;
+    for (int s = 0; s < kStages && ic.pos < w1; ++s) {
+        int len = chunk_len(ic);
+        if (lane == 0) issue(s, ic, len);
+        advance(ic, len);
     }
 
     lb_pdl_wait();  // everything below may read what earlier launches wrote
@@ -375,8 +391,10 @@ __global__ void __launch_bounds__(kThreads) lb_gemv_ternary_kernel(const LbGemvP
             }
         } else {
             // acc[j][0]: row g, acc[j][1]: row g+8 (this lane's k subset); reduce over t
-            int v0 = acc[0][0] + (acc[1][0] >> 2) + (acc[2][0] >> 4) + (acc[3][0] >> 6);
-            int v1 = acc[0][1] + (acc[1][1] >> 2) + (acc[2][1] >> 4) + (acc[3][1] >> 6);
+            int v0 = (acc[0][0] + acc[0][2]) + ((acc[1][0] + acc[1][2]) >> 2) + ((acc[2][0] + acc[2][2]) >> 4) +
+                     ((acc[3][0] + acc[3][2]) >> 6);
+            int v1 = (acc[0][1] + acc[0][3]) + ((acc[1][1] + acc[1][3]) >> 2) + ((acc[2][1] + acc[2][3]) >> 4) +
+                     ((acc[3][1] + acc[3][3]) >> 6);
             v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
             v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
             v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
@@ -392,62 +410,61 @@ __global__ void __launch_bounds__(kThreads) lb_gemv_ternary_kernel(const LbGemvP
             for (int k = 0; k < 4; ++k) acc[j][k] = 0;
     };
 
-    int cpos = w0, cstage = 0;
+    auto tile_step = [&](const uint8_t* tile, const uint32_t* ab) {
+        const uint4 w = *reinterpret_cast<const uint4*>(tile);
+        const uint4 b01 = *reinterpret_cast<const uint4*>(ab);
+        const uint4 b23 = *reinterpret_cast<const uint4*>(ab + 4);
+        if (MMA) {
+            mma_u8s8(acc[0], w.x & 0x03030303u, w.y & 0x03030303u, w.z & 0x03030303u, w.w & 0x03030303u, b01.x, b01.y);
+            mma_u8s8(acc[1], w.x & 0x0c0c0c0cu, w.y & 0x0c0c0c0cu, w.z & 0x0c0c0c0cu, w.w & 0x0c0c0c0cu, b01.z, b01.w);
+            mma_u8s8(acc[2], w.x & 0x30303030u, w.y & 0x30303030u, w.z & 0x30303030u, w.w & 0x30303030u, b23.x, b23.y);
+            mma_u8s8(acc[3], w.x & 0xc0c0c0c0u, w.y & 0xc0c0c0c0u, w.z & 0xc0c0c0c0u, w.w & 0xc0c0c0c0u, b23.z, b23.w);
+        } else {
+            const uint32_t bh0[4] = {b01.x, b01.z, b23.x, b23.z};
+            const uint32_t bh1[4] = {b01.y, b01.w, b23.y, b23.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t mk = 0x03030303u << (2 * j);
+                acc[j][0] = dp4a_u8s8(w.x & mk, bh0[j], acc[j][0]);
+                acc[j][2] = dp4a_u8s8(w.z & mk, bh1[j], acc[j][2]);
+                acc[j][1] = dp4a_u8s8(w.y & mk, bh0[j], acc[j][1]);
+                acc[j][3] = dp4a_u8s8(w.w & mk, bh1[j], acc[j][3]);
+            }
+        }
+    };
+
+    int cstage = 0;
     uint32_t cphase = 0;
-    while (cpos < w1) {
-        const int len = chunk_len(cpos);
-        if (!failed && !lb_mbar_wait_bounded(&my_bars[cstage], cphase)) {
+    while (cc.pos < w1) {
+        const int len = chunk_len(cc);
+        if (p.debug != 2 && !failed && !lb_mbar_wait_bounded(&my_bars[cstage], cphase)) {
             failed = true;
             if (lane == 0) atomicExch(p.status, 1);
         }
-        const int v = cpos / KB, kb0 = cpos - v * KB;
-        if (v != cur_v) {
+        if (cc.v != cur_v) {
             flush();
-            cur_v = v;
+            cur_v = cc.v;
         }
-        const uint8_t* stage = my_ring + (size_t)cstage * kStageBytes;
-        if (!failed) {
+        const uint8_t* tile = my_ring + (size_t)cstage * kStageBytes + lane * 16;
+        const uint32_t* ab = act_base + cc.kb * act_kb_mul;
+        if (!failed && p.debug != 1) {
+            if (len == kStageTiles) {
 #pragma unroll
-            for (int i = 0; i < kStageTiles; ++i) {
-                if (i < len) {
-                    const uint4 w = *reinterpret_cast<const uint4*>(stage + i * kTileBytes + lane * 16);
-                    const uint32_t* ab = act_base + (kb0 + i) * act_kb_mul;
-                    const uint4 b01 = *reinterpret_cast<const uint4*>(ab);
-                    const uint4 b23 = *reinterpret_cast<const uint4*>(ab + 4);
-                    if (MMA) {
-                        mma_u8s8(acc[0], w.x & 0x03030303u, w.y & 0x03030303u, w.z & 0x03030303u, w.w & 0x03030303u,
-                                 b01.x, b01.y);
-                        mma_u8s8(acc[1], w.x & 0x0c0c0c0cu, w.y & 0x0c0c0c0cu, w.z & 0x0c0c0c0cu, w.w & 0x0c0c0c0cu,
-                                 b01.z, b01.w);
-                        mma_u8s8(acc[2], w.x & 0x30303030u, w.y & 0x30303030u, w.z & 0x30303030u, w.w & 0x30303030u,
-                                 b23.x, b23.y);
-                        mma_u8s8(acc[3], w.x & 0xc0c0c0c0u, w.y & 0xc0c0c0c0u, w.z & 0xc0c0c0c0u, w.w & 0xc0c0c0c0u,
-                                 b23.z, b23.w);
-                    } else {
-                        const uint32_t bh0[4] = {b01.x, b01.z, b23.x, b23.z};
-                        const uint32_t bh1[4] = {b01.y, b01.w, b23.y, b23.w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t mk = 0x03030303u << (2 * j);
-                            acc[j][0] = dp4a_u8s8(w.x & mk, bh0[j], acc[j][0]);
-                            acc[j][0] = dp4a_u8s8(w.z & mk, bh1[j], acc[j][0]);
-                            acc[j][1] = dp4a_u8s8(w.y & mk, bh0[j], acc[j][1]);
-                            acc[j][1] = dp4a_u8s8(w.w & mk, bh1[j], acc[j][1]);
-                        }
-                    }
-                }
+                for (int i = 0; i < kStageTiles; ++i) tile_step(tile + i * kTileBytes, ab + i * act_kb_mul);
+            } else {
+                for (int i = 0; i < len; ++i) tile_step(tile + i * kTileBytes, ab + i * act_kb_mul);
             }
         }
+        advance(cc, len);
         __syncwarp();
-        if (ipos < w1) {
-            int len2 = chunk_len(ipos);
+        if (ic.pos < w1) {
+            const int len2 = chunk_len(ic);
             if (lane == 0) {
                 fence_proxy_async();
-                issue(cstage, ipos, len2);
+                issue(cstage, ic, len2);
             }
-            ipos += len2;
+            advance(ic, len2);
         }
-        cpos += len;
         if (++cstage == kStages) {
             cstage = 0;
             cphase ^= 1u;
@@ -544,6 +561,7 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     p.fix_acc = ctx->fix_acc;
     p.fix_cnt = ctx->fix_cnt;
     p.status = ctx->status_dev;
+    p.debug = ctx->opt_debug;
     size_t smem = gemv_smem_bytes(p, p.max_local_strips);
     if (smem > 227 * 1024)
         return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: K=%d with %d tokens needs %zu B of shared memory", p.K, p.M, smem);

@@ -57,6 +57,7 @@ struct LbGemvParams {
     int32_t* fix_acc;
     unsigned int* fix_cnt;
     int* status;
+    int debug;  // timing experiments only: 1 = skip the arithmetic, 2 = skip the weight copies
 };
 
 // Launches the GEMV on ctx->stream (programmatic dependent launch unless disabled).
