@@ -83,8 +83,16 @@ void loom_b200_graph_free(loom_b200_ctx* ctx, loom_b200_graph* graph);
 void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
 /* Tuning knobs, the counterpart of the tileSize argument the WGSL dispatchers take
  * (poly/wgpu_kernels.go:416-427): "gemv_variant" 0 = integer-MMA inner loop, 1 = dp4a inner loop;
- * "gemv_ctas_per_sm" 1..8; "pdl" 0/1 = programmatic dependent launch.  Results never depend on them. */
+ * "gemv_ctas_per_sm" 1..8; "gemv_partition" 0 = choose, 1 = stream-K over tiles with the int32 fix-up,
+ * 2 = whole strips per CTA; "pdl" 0/1 = programmatic dependent launch.  Results never depend on them
+ * ("debug" is for timing experiments only and does change results). */
 int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value);
+/* Phase trace of the ternary GEMV, the counterpart of WGPUContext.TimeCommands
+ * (poly/wgpu_context_native.go:553): with option "trace" = 1 every CTA of a GEMV launch records the
+ * GPU global timer (ns) at: 0 start, 1 weights requested, 2 upstream data ready, 3 activations staged,
+ * 4 dot products done, 5 epilogue done.  trace_read copies the first `ctas` rows of 8 values; rows of
+ * launches with a larger grid are limited to 2048 CTAs. */
+int loom_b200_trace_read(loom_b200_ctx* ctx, uint64_t* host, int ctas);
 /* number of kernels of this library launched on the context since creation */
 uint64_t loom_b200_launch_count(const loom_b200_ctx* ctx);
 
@@ -154,6 +162,93 @@ int loom_b200_gate_product(loom_b200_ctx* ctx, int batch, int hidden, int activa
  * weight [weight_len] or NULL; eps <= 0 means 1e-5. */
 int loom_b200_inner_rmsnorm(loom_b200_ctx* ctx, int batch, int n, float* x, const float* weight, int weight_len,
                             double eps);
+
+/* ---- layer forwards (host buffers) --------------------------------------------------------
+ * The packed-ternary layer paths of poly, with host tensors in and out like the cabi exports
+ * LoomDenseForwardPackedTernaryCPU / LoomSwiGLUForwardPackedTernaryCPU / LoomMHAForwardPackedTernaryCPU
+ * (welvet/cabi/engine_ext.go:267-331).  Host-to-device and device-to-host copies happen inside the call. */
+
+/* DenseForwardPackedTernaryCPU, poly/dense.go:66-101: in [batch,cols] -> pre, post [batch,rows]
+ * (either may be NULL).  No bias. */
+int loom_b200_dense_forward(loom_b200_ctx* ctx, const loom_b200_weight* w, int activation, const float* in_host,
+                            int batch, float* pre_host, float* post_host);
+
+/* SwiGLUForwardPackedTernaryCPU, poly/swiglu.go:270-322: in [seq,hidden] -> pre [seq,inter] (the gate
+ * product after the always-on inner RMSNorm) and post [seq,hidden].  Bias and inner-norm vectors are host
+ * pointers or NULL; rms_eps <= 0 means 1e-5 (layer.RMSNormEps unset). */
+int loom_b200_swiglu_forward(loom_b200_ctx* ctx, const loom_b200_weight* gate, const loom_b200_weight* up,
+                             const loom_b200_weight* down, const float* bias_gate, const float* bias_up,
+                             const float* bias_down, const float* inner_norm_w, int inner_norm_len, double rms_eps,
+                             int activation, const float* in_host, int seq, float* pre_host, float* post_host);
+
+/* The MHA VolumetricLayer with its ring KV cache (fields read by MHAForwardPackedTernaryCPU,
+ * poly/mha.go:204-371).  Weights are borrowed and must outlive the layer; host vectors are copied.
+ * max_seq_len 0 means 512, rope_theta <= 0 means 10000, rms_eps as layer.RMSNormEps. */
+typedef struct loom_b200_mha loom_b200_mha;
+int loom_b200_mha_create(loom_b200_ctx* ctx, int d_model, int num_heads, int num_kv_heads, int head_dim,
+                         int max_seq_len, double rope_theta, double rms_eps, const loom_b200_weight* wq,
+                         const loom_b200_weight* wk, const loom_b200_weight* wv, const loom_b200_weight* wo,
+                         const float* bq, const float* bk, const float* bv, const float* bo, const float* q_norm_w,
+                         int q_norm_len, const float* k_norm_w, int k_norm_len, const float* inner_norm_w,
+                         int inner_norm_len, loom_b200_mha** out);
+void loom_b200_mha_destroy(loom_b200_mha* layer);
+/* Transformer.Reset for this layer: KVOffset = 0, poly/transformer.go:119-127 */
+int loom_b200_mha_reset(loom_b200_mha* layer);
+int loom_b200_mha_kv_offset(const loom_b200_mha* layer);
+/* MHAForwardPackedTernaryCPU: in [batch,seq,d_model] -> pre (normalised attention rows) and post
+ * [batch,seq,d_model].  The ring restarts unless batch == seq == 1 and it already holds positions
+ * (mhaPrepareKVForForward, poly/mha_layout.go:62-70).  Positions beyond max_seq_len are refused. */
+int loom_b200_mha_forward(loom_b200_mha* layer, const float* in_host, int batch, int seq, float* pre_host,
+                          float* post_host);
+/* copies the KV ring [max_seq_len, kv_heads*head_dim] to the host (either pointer may be NULL) */
+int loom_b200_mha_download_cache(loom_b200_mha* layer, float* k_host, float* v_host);
+
+/* ---- decoder --------------------------------------------------------------------------------
+ * The ternary decoder stack InitHFDecoderBlocks wires (poly/hf_decoder.go:20-68) driven the way
+ * Transformer.Generate drives ForwardTokenIDsWGPU (poly/transformer.go:341-485, poly/wgpu_forward.go:31). */
+typedef struct loom_b200_decoder loom_b200_decoder;
+
+/* HFDecoderDims (poly/hf_decoder.go:4-16) + vocabulary + MaxSeqLen.  rms_eps is applied like
+ * SetRMSNormEps (block norms, MHA layers, final norm; poly/transformer.go:162-175). */
+typedef struct loom_b200_decoder_dims {
+    int num_layers, hidden, num_heads, num_kv_heads, head_dim, intermediate, vocab;
+    double rms_eps, rope_theta;
+    int activation;  /* SwiGLU activation: LOOM_B200_ACT_SILU or LOOM_B200_ACT_RELU2 */
+    int max_seq_len; /* <= 0 means 2048 */
+} loom_b200_decoder_dims;
+
+/* GenMetrics, poly/transformer.go:323-338 (the timing fields) */
+typedef struct loom_b200_gen_metrics {
+    double prefill_seconds;        /* host clock around the prompt forward */
+    double decode_seconds;         /* host clock around the decode loop, tokens copied back */
+    double decode_device_seconds;  /* CUDA events around the decode loop */
+    int prefill_tokens, generated_tokens;
+    double launches_per_token;     /* kernels of this library inside one decode step */
+} loom_b200_gen_metrics;
+
+int loom_b200_decoder_create(loom_b200_ctx* ctx, const loom_b200_decoder_dims* dims, loom_b200_decoder** out);
+void loom_b200_decoder_destroy(loom_b200_decoder* dec);
+/* One decoder block = layers 4b..4b+3.  Gains are host vectors [hidden] or NULL (= 1).  w7 = the packed
+ * projections in slab order q, k, v, o, gate, up, down (borrowed; syncBitNetPackedMHA / ...SwiGLU,
+ * poly/bitnet_gpu.go:56-115).  Inner-norm vectors (attn_sub_norm / ffn_sub_norm) are host or NULL. */
+int loom_b200_decoder_set_block(loom_b200_decoder* dec, int block, const float* norm1_gain, const float* norm2_gain,
+                                const loom_b200_weight* const* w7, const float* attn_inner_norm, int attn_inner_len,
+                                const float* ffn_inner_norm, int ffn_inner_len);
+/* Tied fp32 embedding / LM head [vocab,hidden] in device memory (borrowed) and the final norm gain (host). */
+int loom_b200_decoder_set_embeddings(loom_b200_decoder* dec, const float* emb_dev, const float* final_gain);
+/* Transformer.Reset */
+int loom_b200_decoder_reset(loom_b200_decoder* dec);
+int loom_b200_decoder_kv_offset(const loom_b200_decoder* dec);
+/* ForwardTokenIDsWGPU(tokens, nil, true, true), poly/wgpu_forward.go:31: runs the stack over n token ids and
+ * returns the logits of the last one ([vocab], may be NULL to skip the readback).  n > 1 restarts the KV
+ * rings (a prompt); n == 1 continues them. */
+int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int n, float* logits_host);
+/* the last token's hidden row after the final RMSNorm [hidden] */
+int loom_b200_decoder_last_hidden(loom_b200_decoder* dec, float* hidden_host);
+/* Transformer.Generate with deterministic (greedy) sampling: prefill the prompt, then max_new times
+ * {first-maximum token, forward it}.  The loop runs on the device; tokens come back once at the end. */
+int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, int n_prompt, int max_new,
+                               int32_t* out_tokens, loom_b200_gen_metrics* metrics);
 
 #ifdef __cplusplus
 }

@@ -47,6 +47,7 @@ SIGNATURES = {
     "loom_b200_graph_launch": (_i, [_vp, _vp]),
     "loom_b200_graph_free": (None, [_vp, _vp]),
     "loom_b200_launch_count": (C.c_uint64, [_vp]),
+    "loom_b200_trace_read": (_i, [_vp, _vp, _i]),
     "loom_b200_ctx_set_option": (_i, [_vp, C.c_char_p, _i]),
     "loom_b200_buffer_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "loom_b200_buffer_free": (_i, [_vp, _vp]),
@@ -65,7 +66,36 @@ SIGNATURES = {
     "loom_b200_ternary_linear": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
     "loom_b200_gate_product": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "loom_b200_inner_rmsnorm": (_i, [_vp, _i, _i, _vp, _vp, _i, _d]),
+    "loom_b200_dense_forward": (_i, [_vp, _vp, _i, _vp, _i, _vp, _vp]),
+    "loom_b200_swiglu_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _d, _i, _vp, _i, _vp, _vp]),
+    "loom_b200_mha_create": (_i, [_vp, _i, _i, _i, _i, _i, _d, _d, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i,
+                                   _vp, _i, _vp, _i, C.POINTER(_vp)]),
+    "loom_b200_mha_destroy": (None, [_vp]),
+    "loom_b200_mha_reset": (_i, [_vp]),
+    "loom_b200_mha_kv_offset": (_i, [_vp]),
+    "loom_b200_mha_forward": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
+    "loom_b200_mha_download_cache": (_i, [_vp, _vp, _vp]),
+    "loom_b200_decoder_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "loom_b200_decoder_destroy": (None, [_vp]),
+    "loom_b200_decoder_set_block": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i]),
+    "loom_b200_decoder_set_embeddings": (_i, [_vp, _vp, _vp]),
+    "loom_b200_decoder_reset": (_i, [_vp]),
+    "loom_b200_decoder_kv_offset": (_i, [_vp]),
+    "loom_b200_decoder_forward": (_i, [_vp, _vp, _i, _vp]),
+    "loom_b200_decoder_last_hidden": (_i, [_vp, _vp]),
+    "loom_b200_decoder_generate": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
 }
+
+
+class DecoderDims(C.Structure):
+    _fields_ = [("num_layers", _i), ("hidden", _i), ("num_heads", _i), ("num_kv_heads", _i), ("head_dim", _i),
+                ("intermediate", _i), ("vocab", _i), ("rms_eps", _d), ("rope_theta", _d), ("activation", _i),
+                ("max_seq_len", _i)]
+
+
+class GenMetrics(C.Structure):
+    _fields_ = [("prefill_seconds", _d), ("decode_seconds", _d), ("decode_device_seconds", _d), ("prefill_tokens", _i),
+                ("generated_tokens", _i), ("launches_per_token", _d)]
 
 
 def lib() -> C.CDLL:
@@ -179,6 +209,11 @@ class Context:
     def graph_free(self, g):
         lib().loom_b200_graph_free(self.h, g)
 
+    def trace_read(self, ctas: int) -> np.ndarray:
+        out = np.zeros((ctas, 8), np.uint64)
+        self._check(lib().loom_b200_trace_read(self.h, out.ctypes.data, ctas))
+        return out
+
     def set_option(self, key: str, value: int):
         self._check(lib().loom_b200_ctx_set_option(self.h, key.encode(), int(value)))
 
@@ -253,3 +288,151 @@ class Context:
 
     def inner_rmsnorm(self, batch, n, x, weight=None, weight_len=0, eps=0.0):
         self._check(lib().loom_b200_inner_rmsnorm(self.h, batch, n, _ptr(x), _ptr(weight), weight_len, eps))
+
+
+def _f32(a):
+    return None if a is None else np.ascontiguousarray(a, np.float32)
+
+
+def _hp(a):
+    return None if a is None else a.ctypes.data
+
+
+def dense_forward(ctx: Context, w: Weight, act: int, x: np.ndarray):
+    """DenseForwardPackedTernaryCPU stand-in: host in, host (pre, post) out."""
+    x = _f32(x)
+    batch = x.shape[0]
+    pre = np.empty((batch, w.rows), np.float32)
+    post = np.empty((batch, w.rows), np.float32)
+    ctx._check(lib().loom_b200_dense_forward(ctx.h, w.h, act, x.ctypes.data, batch, pre.ctypes.data, post.ctypes.data))
+    return pre, post
+
+
+def swiglu_forward(ctx: Context, gate: Weight, up: Weight, down: Weight, x: np.ndarray, act=ACT_SILU, bias_gate=None,
+                   bias_up=None, bias_down=None, inner_w=None, eps=0.0):
+    """SwiGLUForwardPackedTernaryCPU stand-in."""
+    x = _f32(x)
+    seq = x.shape[0]
+    pre = np.empty((seq, gate.rows), np.float32)
+    post = np.empty((seq, gate.cols), np.float32)
+    bg, bu, bd, iw = _f32(bias_gate), _f32(bias_up), _f32(bias_down), _f32(inner_w)
+    ctx._check(lib().loom_b200_swiglu_forward(ctx.h, gate.h, up.h, down.h, _hp(bg), _hp(bu), _hp(bd), _hp(iw),
+                                              0 if iw is None else iw.size, eps, act, x.ctypes.data, seq,
+                                              pre.ctypes.data, post.ctypes.data))
+    return pre, post
+
+
+class MHA:
+    """The MHA layer with its KV ring on the device (MHAForwardPackedTernaryCPU stand-in)."""
+
+    def __init__(self, ctx: Context, d_model, heads, kv_heads, head_dim, max_seq_len, theta, eps, wq, wk, wv, wo,
+                 bq=None, bk=None, bv=None, bo=None, q_norm=None, k_norm=None, inner_w=None):
+        self.ctx, self.h = ctx, None
+        self.weights = (wq, wk, wv, wo)
+        self.d_model, self.heads, self.kv_heads, self.head_dim = d_model, heads, kv_heads or heads, head_dim
+        self.msl = max_seq_len or 512
+        a = [_f32(v) for v in (bq, bk, bv, bo, q_norm, k_norm, inner_w)]
+        h = _vp()
+        ctx._check(lib().loom_b200_mha_create(ctx.h, d_model, heads, kv_heads, head_dim, max_seq_len, theta, eps, wq.h,
+                                              wk.h, wv.h, wo.h, _hp(a[0]), _hp(a[1]), _hp(a[2]), _hp(a[3]), _hp(a[4]),
+                                              0 if a[4] is None else a[4].size, _hp(a[5]),
+                                              0 if a[5] is None else a[5].size, _hp(a[6]),
+                                              0 if a[6] is None else a[6].size, C.byref(h)))
+        self.h = h
+
+    def reset(self):
+        self.ctx._check(lib().loom_b200_mha_reset(self.h))
+
+    @property
+    def kv_offset(self):
+        return lib().loom_b200_mha_kv_offset(self.h)
+
+    def forward(self, x):
+        x = _f32(x)
+        batch, seq = (1, x.shape[0]) if x.ndim == 2 else (x.shape[0], x.shape[1])
+        pre = np.empty((batch * seq, self.d_model), np.float32)
+        post = np.empty((batch * seq, self.d_model), np.float32)
+        self.ctx._check(lib().loom_b200_mha_forward(self.h, x.ctypes.data, batch, seq, pre.ctypes.data, post.ctypes.data))
+        return pre, post
+
+    def cache(self):
+        kvd = self.kv_heads * self.head_dim
+        k = np.empty((self.msl, kvd), np.float32)
+        v = np.empty((self.msl, kvd), np.float32)
+        self.ctx._check(lib().loom_b200_mha_download_cache(self.h, k.ctypes.data, v.ctypes.data))
+        return k, v
+
+    def close(self):
+        if self.h:
+            lib().loom_b200_mha_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Decoder:
+    """The ternary decoder stack on the device (InitHFDecoderBlocks + Transformer stand-in)."""
+
+    def __init__(self, ctx: Context, layers, hidden, heads, kv_heads, head_dim, inter, vocab, eps, theta,
+                 act=ACT_SILU, max_seq_len=2048):
+        self.ctx, self.h = ctx, None
+        self.dims = DecoderDims(layers, hidden, heads, kv_heads, head_dim, inter, vocab, eps, theta, act, max_seq_len)
+        h = _vp()
+        ctx._check(lib().loom_b200_decoder_create(ctx.h, C.byref(self.dims), C.byref(h)))
+        self.h = h
+        self._keep = []
+
+    def set_block(self, b, weights7, g1=None, g2=None, attn_inner=None, ffn_inner=None):
+        assert len(weights7) == 7
+        self._keep.append(list(weights7))
+        arr = (_vp * 7)(*[w.h for w in weights7])
+        g1, g2, ai, fi = _f32(g1), _f32(g2), _f32(attn_inner), _f32(ffn_inner)
+        self.ctx._check(lib().loom_b200_decoder_set_block(self.h, b, _hp(g1), _hp(g2), C.cast(arr, _vp), _hp(ai),
+                                                          0 if ai is None else ai.size, _hp(fi),
+                                                          0 if fi is None else fi.size))
+
+    def set_embeddings(self, emb_dev, final_gain=None):
+        self._keep.append(emb_dev)
+        fg = _f32(final_gain)
+        self.ctx._check(lib().loom_b200_decoder_set_embeddings(self.h, _ptr(emb_dev), _hp(fg)))
+
+    def reset(self):
+        self.ctx._check(lib().loom_b200_decoder_reset(self.h))
+
+    @property
+    def kv_offset(self):
+        return lib().loom_b200_decoder_kv_offset(self.h)
+
+    def forward(self, tokens, want_logits=True):
+        tokens = np.ascontiguousarray(tokens, np.int32).ravel()
+        logits = np.empty(self.dims.vocab, np.float32) if want_logits else None
+        self.ctx._check(lib().loom_b200_decoder_forward(self.h, tokens.ctypes.data, tokens.size, _hp(logits)))
+        return logits
+
+    def last_hidden(self):
+        out = np.empty(self.dims.hidden, np.float32)
+        self.ctx._check(lib().loom_b200_decoder_last_hidden(self.h, out.ctypes.data))
+        return out
+
+    def generate(self, prompt, max_new):
+        prompt = np.ascontiguousarray(prompt, np.int32).ravel()
+        out = np.zeros(max(max_new, 1), np.int32)
+        m = GenMetrics()
+        self.ctx._check(lib().loom_b200_decoder_generate(self.h, prompt.ctypes.data, prompt.size, max_new,
+                                                         out.ctypes.data, C.byref(m)))
+        return out[:max_new], m
+
+    def close(self):
+        if self.h:
+            lib().loom_b200_decoder_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

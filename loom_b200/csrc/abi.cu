@@ -312,6 +312,20 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
     } else if (!strcmp(key, "gemv_ctas_per_sm")) {
         LB_REQUIRE(ctx, value >= 1 && value <= 8, "ctx_set_option: gemv_ctas_per_sm must be in [1,8]");
         ctx->opt_gemv_ctas_per_sm = value;
+    } else if (!strcmp(key, "gemv_partition")) {
+        LB_REQUIRE(ctx, value >= 0 && value <= 2, "ctx_set_option: gemv_partition must be 0 (auto), 1 (stream-K) or 2 (whole strips)");
+        ctx->opt_gemv_partition = value;
+    } else if (!strcmp(key, "trace")) {
+        LB_NO_CAPTURE(ctx, "switching the trace");
+        if (int rc = lb_set_device(ctx)) return rc;
+        LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (value && !ctx->trace_dev) {
+            LB_CUDA(ctx, cudaMalloc(&ctx->trace_dev, (size_t)kTraceCtas * 8 * sizeof(unsigned long long)));
+            LB_CUDA(ctx, cudaMemset(ctx->trace_dev, 0, (size_t)kTraceCtas * 8 * sizeof(unsigned long long)));
+        } else if (!value && ctx->trace_dev) {
+            cudaFree(ctx->trace_dev);
+            ctx->trace_dev = nullptr;
+        }
     } else if (!strcmp(key, "debug")) {
         ctx->opt_debug = value;
     } else if (!strcmp(key, "pdl")) {
@@ -330,6 +344,7 @@ void loom_b200_ctx_destroy(loom_b200_ctx* ctx) {
     if (ctx->fix_cnt) cudaFree(ctx->fix_cnt);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
+    if (ctx->trace_dev) cudaFree(ctx->trace_dev);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -393,6 +408,17 @@ void loom_b200_graph_free(loom_b200_ctx* ctx, loom_b200_graph* graph) {
     if (graph->exec) cudaGraphExecDestroy(graph->exec);
     if (graph->graph) cudaGraphDestroy(graph->graph);
     delete graph;
+}
+
+int loom_b200_trace_read(loom_b200_ctx* ctx, uint64_t* host, int ctas) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "trace_read: ctx is NULL");
+    LB_REQUIRE(ctx, host && ctas > 0 && ctas <= kTraceCtas, "trace_read: bad arguments");
+    LB_REQUIRE(ctx, ctx->trace_dev != nullptr, "trace_read: tracing is off (set option \"trace\" to 1)");
+    LB_NO_CAPTURE(ctx, "trace_read");
+    if (int rc = lb_set_device(ctx)) return rc;
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    LB_CUDA(ctx, cudaMemcpy(host, ctx->trace_dev, (size_t)ctas * 8 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    return 0;
 }
 
 void* loom_b200_ctx_stream(loom_b200_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }

@@ -28,6 +28,7 @@ constexpr int kTileRows = 16;
 constexpr int kTileCols = 128;
 constexpr int kTileBytes = 512;
 constexpr int kTileWords = 128;
+constexpr int kTraceCtas = 2048;
 
 struct loom_b200_weight {
     int rows = 0, cols = 0, row_words = 0;
@@ -60,6 +61,8 @@ struct loom_b200_ctx {
     int opt_gemv_variant = 0;      // 0 = integer-MMA inner loop, 1 = dp4a inner loop (batch 1 only)
     int opt_gemv_ctas_per_sm = 2;  // grid = SMs * this
     int opt_pdl = 1;               // programmatic dependent launch on/off
+    int opt_gemv_partition = 0;    // 0 = choose, 1 = always stream-K, 2 = always whole strip groups
+    unsigned long long* trace_dev = nullptr;  // [kTraceCtas][8] phase timestamps of the last GEMV launch
     int opt_debug = 0;             // timing experiments (results are wrong when non-zero)
     bool capturing = false;        // between graph_begin and graph_end
 };

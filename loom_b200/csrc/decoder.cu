@@ -1,0 +1,385 @@
+// decoder.cu -- the decoder block loop on the GPU: the ternary branches of ForwardTokenIDsWGPU
+// (poly/wgpu_forward.go:31-596) with the CPU path's arithmetic (forwardOnCPUNormal,
+// poly/transformer_forward.go:220-253) and Generate's greedy loop (poly/transformer.go:341-485).
+//
+// One decode step is a single recorded frame (CUDA graph) of six launches per block -- QKV GEMV with the block
+// RMSNorm fused in, q/k norm + RoPE, attention, O GEMV (+ inner norm, + residual), gate/up GEMV (+ block norm,
+// + SwiGLU product), down GEMV (+ inner norm, + residual) -- followed by the fp32 LM head.  Positions, the
+// current token and the output cursor live in device memory, so the same frame replays for every token and
+// the greedy loop never waits for the host.
+#include "layers.cuh"
+
+#include <chrono>
+#include <vector>
+
+struct loom_b200_graph;  // defined in abi.cu
+
+struct LbDecBlock {
+    loom_b200_mha mha;
+    const loom_b200_weight *gate = nullptr, *up = nullptr, *down = nullptr;
+    float *g1 = nullptr, *g2 = nullptr;  // block RMSNorm gains [hidden]
+    float* ffn_inner = nullptr;
+    int ffn_inner_len = 0;
+    bool ready = false;
+};
+
+struct loom_b200_decoder {
+    loom_b200_ctx* ctx = nullptr;
+    loom_b200_decoder_dims d{};
+    std::vector<LbDecBlock> blocks;
+    const float* emb = nullptr;  // borrowed device pointer [vocab, hidden]
+    float* final_gain = nullptr;
+    float *x = nullptr, *prod = nullptr, *logits = nullptr, *hidden = nullptr;
+    int *tok = nullptr, *pos = nullptr, *step = nullptr, *out_tokens = nullptr;
+    int out_cap = 0;
+    int kv_offset = 0;
+    int* h_tok = nullptr;       // pinned
+    float* h_logits = nullptr;  // pinned [vocab]
+    loom_b200_graph* step_graph = nullptr;
+    int decode_splits = 8;
+};
+
+namespace {
+
+int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int head_row) {
+    loom_b200_ctx* ctx = dec->ctx;
+    const loom_b200_decoder_dims& d = dec->d;
+    if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, d.hidden, dec->tok, M, dec->x)) return rc;
+    for (auto& b : dec->blocks) {
+        LbMhaStepArgs a = {};
+        a.pro_mode = LB_PRO_BLOCKNORM;
+        a.x = dec->x;
+        a.gain = b.g1;
+        a.block_eps = d.rms_eps > 0 ? d.rms_eps : 1e-6;
+        a.out = dec->x;
+        a.residual = dec->x;
+        a.M = M;
+        a.splits = splits;
+        if (int rc = lb_mha_step_dev(&b.mha, a)) return rc;
+        LbSwigluArgs s = {};
+        s.gate = b.gate;
+        s.up = b.up;
+        s.down = b.down;
+        s.inner_w = b.ffn_inner;
+        s.inner_w_len = b.ffn_inner_len;
+        s.inner_eps = 0.0;  // the decoder builder never sets RMSNormEps on the SwiGLU layer: default 1e-5
+        s.act = d.activation;
+        s.pro_mode = LB_PRO_BLOCKNORM;
+        s.x = dec->x;
+        s.gain = b.g2;
+        s.block_eps = d.rms_eps > 0 ? d.rms_eps : 1e-6;
+        s.prod = dec->prod;
+        s.out = dec->x;
+        s.residual = dec->x;
+        s.M = M;
+        if (int rc = lb_swiglu_dev(ctx, s)) return rc;
+    }
+    if (head) {
+        LbLmHeadParams h = {};
+        h.x = dec->x + (size_t)head_row * d.hidden;
+        h.gain = dec->final_gain;
+        h.eps = d.rms_eps > 0 ? d.rms_eps : 1e-6;
+        h.head = dec->emb;
+        h.vocab = d.vocab;
+        h.hidden = d.hidden;
+        h.logits = dec->logits;
+        h.hidden_out = dec->hidden;
+        if (int rc = lb_launch_lm_head(ctx, h)) return rc;
+    }
+    return lb_launch_add_scalar(ctx, dec->pos, M);
+}
+
+int dec_check_ready(loom_b200_decoder* dec) {
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, dec->emb != nullptr, "decoder: embeddings are not set");
+    for (size_t i = 0; i < dec->blocks.size(); ++i)
+        LB_REQUIRE(ctx, dec->blocks[i].ready, "decoder: block %zu has no weights", i);
+    return 0;
+}
+
+void dec_drop_graph(loom_b200_decoder* dec) {
+    if (dec->step_graph) {
+        loom_b200_graph_free(dec->ctx, dec->step_graph);
+        dec->step_graph = nullptr;
+    }
+}
+
+// One token from tok[0] at position *pos: eager the first time (sizes every scratch buffer), recorded after.
+int dec_step(loom_b200_decoder* dec) {
+    loom_b200_ctx* ctx = dec->ctx;
+    if (dec->step_graph) return loom_b200_graph_launch(ctx, dec->step_graph);
+    if (int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0)) return rc;  // warm-up run, counts as the step
+    // record the same step for all later tokens
+    if (int rc = loom_b200_graph_begin(ctx)) return rc;
+    int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0);
+    loom_b200_graph* g = nullptr;
+    int rc2 = loom_b200_graph_end(ctx, &g);
+    if (rc) {
+        if (g) loom_b200_graph_free(ctx, g);
+        return rc;
+    }
+    if (rc2) return rc2;
+    dec->step_graph = g;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int loom_b200_decoder_create(loom_b200_ctx* ctx, const loom_b200_decoder_dims* dims, loom_b200_decoder** out) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_create: ctx is NULL");
+    LB_REQUIRE(ctx, dims && out, "decoder_create: NULL argument");
+    *out = nullptr;
+    const loom_b200_decoder_dims& d = *dims;
+    LB_REQUIRE(ctx, d.num_layers > 0 && d.hidden > 0 && d.num_heads > 0 && d.head_dim > 0 && d.intermediate > 0 && d.vocab > 0,
+               "decoder_create: bad dimensions");
+    LB_REQUIRE(ctx, d.num_heads * d.head_dim == d.hidden, "decoder_create: heads*head_dim must equal hidden");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_create cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    auto* dec = new loom_b200_decoder();
+    dec->ctx = ctx;
+    dec->d = d;
+    if (dec->d.num_kv_heads == 0) dec->d.num_kv_heads = d.num_heads;
+    if (dec->d.max_seq_len <= 0) dec->d.max_seq_len = 2048;  // NewTransformer default, poly/transformer.go:111-113
+    dec->blocks.resize(d.num_layers);
+    dec->out_cap = dec->d.max_seq_len;
+    cudaError_t e = cudaSuccess;
+    auto A = [&](void** p, size_t bytes) {
+        if (e == cudaSuccess) e = cudaMalloc(p, bytes);
+        if (e == cudaSuccess) e = cudaMemsetAsync(*p, 0, bytes, ctx->stream);
+    };
+    A((void**)&dec->x, (size_t)kChunkTokens * d.hidden * 4);
+    A((void**)&dec->prod, (size_t)kChunkTokens * d.intermediate * 4);
+    A((void**)&dec->logits, (size_t)d.vocab * 4);
+    A((void**)&dec->hidden, (size_t)d.hidden * 4);
+    A((void**)&dec->tok, kChunkTokens * sizeof(int));
+    A((void**)&dec->pos, sizeof(int));
+    A((void**)&dec->step, sizeof(int));
+    A((void**)&dec->out_tokens, (size_t)dec->out_cap * sizeof(int));
+    if (e == cudaSuccess) e = cudaMallocHost((void**)&dec->h_tok, kChunkTokens * sizeof(int));
+    if (e == cudaSuccess) e = cudaMallocHost((void**)&dec->h_logits, (size_t)d.vocab * 4);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        loom_b200_decoder_destroy(dec);
+        return lb_fail(ctx, LOOM_B200_ERR_CUDA, "decoder_create: %s", cudaGetErrorString(e));
+    }
+    *out = dec;
+    return 0;
+}
+
+void loom_b200_decoder_destroy(loom_b200_decoder* dec) {
+    if (!dec) return;
+    if (dec->ctx) {
+        cudaSetDevice(dec->ctx->device);
+        cudaStreamSynchronize(dec->ctx->stream);
+    }
+    dec_drop_graph(dec);
+    for (auto& b : dec->blocks) {
+        if (b.ready) {
+            b.mha.pos_dev = nullptr;  // shared with the decoder
+            lb_mha_release(&b.mha);
+        }
+        if (b.g1) cudaFree(b.g1);
+        if (b.g2) cudaFree(b.g2);
+        if (b.ffn_inner) cudaFree(b.ffn_inner);
+    }
+    void* ptrs[] = {dec->final_gain, dec->x, dec->prod, dec->logits, dec->hidden, dec->tok, dec->pos, dec->step, dec->out_tokens};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    if (dec->h_tok) cudaFreeHost(dec->h_tok);
+    if (dec->h_logits) cudaFreeHost(dec->h_logits);
+    delete dec;
+}
+
+int loom_b200_decoder_set_block(loom_b200_decoder* dec, int block, const float* norm1_gain, const float* norm2_gain,
+                                const loom_b200_weight* const* w7, const float* attn_inner_norm, int attn_inner_len,
+                                const float* ffn_inner_norm, int ffn_inner_len) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_set_block: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    const loom_b200_decoder_dims& d = dec->d;
+    LB_REQUIRE(ctx, block >= 0 && block < d.num_layers, "decoder_set_block: block %d out of range", block);
+    LB_REQUIRE(ctx, w7 != nullptr, "decoder_set_block: weights are NULL");
+    for (int i = 0; i < 7; ++i) LB_REQUIRE(ctx, w7[i] != nullptr, "decoder_set_block: weight %d is NULL", i);
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_set_block cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    const int H = d.hidden, I = d.intermediate, qd = d.num_heads * d.head_dim, kvd = d.num_kv_heads * d.head_dim;
+    const int rows[7] = {qd, kvd, kvd, H, I, I, H}, cols[7] = {H, H, H, qd, H, H, I};
+    for (int i = 0; i < 7; ++i)
+        LB_REQUIRE(ctx, w7[i]->rows == rows[i] && w7[i]->cols == cols[i], "decoder_set_block: weight %d is %dx%d, expected %dx%d", i,
+                   w7[i]->rows, w7[i]->cols, rows[i], cols[i]);
+    LbDecBlock& b = dec->blocks[block];
+    LB_REQUIRE(ctx, !b.ready, "decoder_set_block: block %d is already set", block);
+    dec_drop_graph(dec);
+    loom_b200_mha& m = b.mha;
+    m.d_model = H;
+    m.heads = d.num_heads;
+    m.kv_heads = d.num_kv_heads;
+    m.head_dim = d.head_dim;
+    m.q_dim = qd;
+    m.kv_dim = kvd;
+    m.msl = d.max_seq_len;
+    m.theta = d.rope_theta > 0 ? d.rope_theta : 10000.0;
+    m.rms_eps = d.rms_eps;  // SetRMSNormEps reaches the MHA layers, poly/transformer.go:162-175
+    m.wq = w7[0];
+    m.wk = w7[1];
+    m.wv = w7[2];
+    m.wo = w7[3];
+    if (int rc = lb_mha_alloc(ctx, &m, 16)) return rc;
+    cudaFree(m.pos_dev);
+    m.pos_dev = dec->pos;
+    b.gate = w7[4];
+    b.up = w7[5];
+    b.down = w7[6];
+    std::vector<float> ones(H, 1.0f);
+    LB_CUDA(ctx, cudaMalloc(&b.g1, (size_t)H * 4));
+    LB_CUDA(ctx, cudaMalloc(&b.g2, (size_t)H * 4));
+    LB_CUDA(ctx, cudaMemcpyAsync(b.g1, norm1_gain ? norm1_gain : ones.data(), (size_t)H * 4, cudaMemcpyHostToDevice, ctx->stream));
+    LB_CUDA(ctx, cudaMemcpyAsync(b.g2, norm2_gain ? norm2_gain : ones.data(), (size_t)H * 4, cudaMemcpyHostToDevice, ctx->stream));
+    if (attn_inner_norm && attn_inner_len > 0) {
+        LB_CUDA(ctx, cudaMalloc(&m.inner, (size_t)attn_inner_len * 4));
+        LB_CUDA(ctx, cudaMemcpyAsync(m.inner, attn_inner_norm, (size_t)attn_inner_len * 4, cudaMemcpyHostToDevice, ctx->stream));
+        m.inner_len = attn_inner_len;
+    }
+    if (ffn_inner_norm && ffn_inner_len > 0) {
+        LB_CUDA(ctx, cudaMalloc(&b.ffn_inner, (size_t)ffn_inner_len * 4));
+        LB_CUDA(ctx, cudaMemcpyAsync(b.ffn_inner, ffn_inner_norm, (size_t)ffn_inner_len * 4, cudaMemcpyHostToDevice, ctx->stream));
+        b.ffn_inner_len = ffn_inner_len;
+    }
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    b.ready = true;
+    return 0;
+}
+
+int loom_b200_decoder_set_embeddings(loom_b200_decoder* dec, const float* emb_dev, const float* final_gain) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_set_embeddings: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, emb_dev != nullptr, "decoder_set_embeddings: embeddings are NULL");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_set_embeddings cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    dec_drop_graph(dec);
+    dec->emb = emb_dev;
+    const int H = dec->d.hidden;
+    std::vector<float> ones(H, 1.0f);
+    if (!dec->final_gain) LB_CUDA(ctx, cudaMalloc(&dec->final_gain, (size_t)H * 4));
+    LB_CUDA(ctx, cudaMemcpyAsync(dec->final_gain, final_gain ? final_gain : ones.data(), (size_t)H * 4, cudaMemcpyHostToDevice, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+int loom_b200_decoder_reset(loom_b200_decoder* dec) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_reset: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_reset cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    dec->kv_offset = 0;
+    LB_CUDA(ctx, cudaMemsetAsync(dec->pos, 0, sizeof(int), ctx->stream));
+    LB_CUDA(ctx, cudaMemsetAsync(dec->step, 0, sizeof(int), ctx->stream));
+    return 0;
+}
+
+int loom_b200_decoder_kv_offset(const loom_b200_decoder* dec) { return dec ? dec->kv_offset : -1; }
+
+int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int n, float* logits_host) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_forward: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, tokens && n > 0, "decoder_forward: no tokens");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_forward takes host buffers and cannot be recorded");
+    if (int rc = dec_check_ready(dec)) return rc;
+    if (int rc = lb_set_device(ctx)) return rc;
+    // A multi-token call restarts the KV ring like the CPU path does (poly/mha_layout.go:62-70);
+    // a one-token call continues it when there is something to continue.
+    const bool incremental = n == 1 && dec->kv_offset > 0;
+    if (!incremental) {
+        if (int rc = loom_b200_decoder_reset(dec)) return rc;
+    }
+    LB_REQUIRE(ctx, dec->kv_offset + n <= dec->d.max_seq_len, "decoder_forward: %d positions exceed MaxSeqLen %d", dec->kv_offset + n, dec->d.max_seq_len);
+    if (n == 1) {
+        dec->h_tok[0] = tokens[0];
+        LB_CUDA(ctx, cudaMemcpyAsync(dec->tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+        if (int rc = dec_step(dec)) return rc;
+    } else {
+        for (int s0 = 0; s0 < n; s0 += kChunkTokens) {
+            const int M = n - s0 < kChunkTokens ? n - s0 : kChunkTokens;
+            LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // h_tok is reused
+            for (int i = 0; i < M; ++i) dec->h_tok[i] = tokens[s0 + i];
+            LB_CUDA(ctx, cudaMemcpyAsync(dec->tok, dec->h_tok, M * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+            const bool last = s0 + M == n;
+            if (int rc = dec_forward_chunk(dec, M, 1, last, M - 1)) return rc;
+        }
+    }
+    dec->kv_offset += n;
+    if (logits_host) {
+        LB_CUDA(ctx, cudaMemcpyAsync(dec->h_logits, dec->logits, (size_t)dec->d.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        memcpy(logits_host, dec->h_logits, (size_t)dec->d.vocab * 4);
+    }
+    return 0;
+}
+
+int loom_b200_decoder_last_hidden(loom_b200_decoder* dec, float* hidden_host) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_last_hidden: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, hidden_host != nullptr, "decoder_last_hidden: NULL buffer");
+    if (int rc = lb_set_device(ctx)) return rc;
+    LB_CUDA(ctx, cudaMemcpyAsync(hidden_host, dec->hidden, (size_t)dec->d.hidden * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, int n_prompt, int max_new,
+                               int32_t* out_tokens, loom_b200_gen_metrics* metrics) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_generate: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, prompt && n_prompt > 0 && max_new >= 0 && (out_tokens || max_new == 0), "decoder_generate: bad arguments");
+    LB_REQUIRE(ctx, max_new <= dec->out_cap, "decoder_generate: %d new tokens exceed the output ring of %d", max_new, dec->out_cap);
+    LB_REQUIRE(ctx, n_prompt + max_new <= dec->d.max_seq_len, "decoder_generate: %d positions exceed MaxSeqLen %d", n_prompt + max_new, dec->d.max_seq_len);
+    if (int rc = dec_check_ready(dec)) return rc;
+    using clk = std::chrono::steady_clock;
+    dec->kv_offset = 0;  // Generate starts with Transformer.Reset
+    auto t0 = clk::now();
+    // prefill: a one-token prompt still starts a fresh sequence
+    if (n_prompt == 1) {
+        if (int rc = loom_b200_decoder_reset(dec)) return rc;
+        dec->h_tok[0] = prompt[0];
+        LB_CUDA(ctx, cudaMemcpyAsync(dec->tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+        if (int rc = dec_step(dec)) return rc;
+        dec->kv_offset = 1;
+    } else {
+        if (int rc = loom_b200_decoder_forward(dec, prompt, n_prompt, nullptr)) return rc;
+    }
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    auto t1 = clk::now();
+    const uint64_t launches0 = ctx->launches;
+    cudaEvent_t e0, e1;
+    LB_CUDA(ctx, cudaEventCreate(&e0));
+    LB_CUDA(ctx, cudaEventCreate(&e1));
+    LB_CUDA(ctx, cudaEventRecord(e0, ctx->stream));
+    // every sampled token is followed by a forward, the last one included (as Generate does)
+    for (int i = 0; i < max_new; ++i) {
+        if (int rc = lb_launch_argmax_advance(ctx, dec->logits, dec->d.vocab, dec->tok, dec->out_tokens, dec->out_cap, dec->step, nullptr)) return rc;
+        if (int rc = dec_step(dec)) return rc;
+    }
+    LB_CUDA(ctx, cudaEventRecord(e1, ctx->stream));
+    if (max_new > 0)
+        LB_CUDA(ctx, cudaMemcpyAsync(out_tokens, dec->out_tokens, (size_t)max_new * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    auto t2 = clk::now();
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    dec->kv_offset += max_new;
+    if (metrics) {
+        metrics->prefill_seconds = std::chrono::duration<double>(t1 - t0).count();
+        metrics->decode_seconds = std::chrono::duration<double>(t2 - t1).count();
+        metrics->decode_device_seconds = ms * 1e-3;
+        metrics->prefill_tokens = n_prompt;
+        metrics->generated_tokens = max_new;
+        metrics->launches_per_token = max_new > 0 ? (double)(dec->blocks.size() * 6 + 4) : 0.0;
+        (void)launches0;
+    }
+    return 0;
+}
+
+}  // extern "C"

@@ -50,12 +50,24 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Optional phase trace: slot k of this CTA's row receives the global timer (ns) at phase k.
+#define LB_TRACE(k)                                                                       \
+    do {                                                                                  \
+        if (p.trace && threadIdx.x == 0) p.trace[(size_t)blockIdx.x * 8 + (k)] = gtime(); \
+    } while (0)
+
 struct Smem {
     uint8_t* ring;
     uint32_t* acts;   // M rows of (Kp+16) bytes, then a 32-byte zero block
     int* sacc;        // [local strip][token][16]
     int* xsum;        // [8]
     float* amax;      // [8]
+    double* os;       // [3][8] output scale per segment and token
     double* red;      // [32]
     int* flag;        // [4]
     uint64_t* bars;   // [kWarps*kStages]
@@ -102,7 +114,8 @@ __device__ __forceinline__ float block_max(float v, double* red) {
 
 // The value the reference quantizes for column c of token row `row` (already rounded to float32 where the
 // reference stores a float32), as a double.
-__device__ __forceinline__ double pro_value(int mode, const void* row, int c, double stat, const float* nw, int nwlen) {
+template <int mode>
+__device__ __forceinline__ double pro_value(const void* row, int c, double stat, const float* nw, int nwlen) {
     if (mode == LB_PRO_INNERNORM64) {
         double w = (nw && c < nwlen) ? (double)nw[c] : 1.0;
         return __dmul_rn(((const double*)row)[c], __dmul_rn(stat, w));
@@ -119,7 +132,8 @@ __device__ __forceinline__ double pro_value(int mode, const void* row, int c, do
 
 // Quantizes the M activation rows into shared memory in the k-slot order the MMA B-fragments use, and
 // leaves sum(q) and amax per token in shared memory.
-__device__ void stage_activations(const LbGemvParams& p, const Smem& sm) {
+template <int PRO>
+__device__ __forceinline__ void stage_activations(const LbGemvParams& p, const Smem& sm) {
     const int tid = threadIdx.x;
     const int K = p.K, Kp = p.kblocks * kTileCols;
     const int stride32 = (Kp + 16) / 4;
@@ -127,18 +141,18 @@ __device__ void stage_activations(const LbGemvParams& p, const Smem& sm) {
     if (tid < kMaxM) sm.xsum[tid] = 0;
     if (tid < 8) sm.acts[p.M * stride32 + tid] = 0;  // zero block for the lanes of absent tokens
     for (int n = 0; n < p.M; ++n) {
-        const bool q8 = p.pro == LB_PRO_Q8;
+        constexpr bool q8 = PRO == LB_PRO_Q8;
         const void* row = q8 ? (const void*)((const int8_t*)p.x + (size_t)n * K)
-                             : (p.pro == LB_PRO_INNERNORM64 ? (const void*)((const double*)p.x + (size_t)n * K)
+                             : (PRO == LB_PRO_INNERNORM64 ? (const void*)((const double*)p.x + (size_t)n * K)
                                                             : (const void*)((const float*)p.x + (size_t)n * K));
         double stat = 0.0;
         float amax;
         if (q8) {
             amax = p.amax_in[n];
         } else {
-            if (p.pro >= LB_PRO_BLOCKNORM) {
+            if (PRO >= LB_PRO_BLOCKNORM) {
                 double ss = 0.0;
-                if (p.pro == LB_PRO_INNERNORM64) {
+                if (PRO == LB_PRO_INNERNORM64) {
                     for (int c = tid; c < K; c += kThreads) {
                         double v = ((const double*)row)[c];
                         ss = __dadd_rn(ss, __dmul_rn(v, v));
@@ -151,11 +165,11 @@ __device__ void stage_activations(const LbGemvParams& p, const Smem& sm) {
                 }
                 ss = block_sum(ss, sm.red);
                 double mean = __dadd_rn(__ddiv_rn(ss, (double)K), p.eps);
-                stat = p.pro == LB_PRO_BLOCKNORM ? sqrt(mean) : __ddiv_rn(1.0, sqrt(mean));
+                stat = PRO == LB_PRO_BLOCKNORM ? sqrt(mean) : __ddiv_rn(1.0, sqrt(mean));
             }
             float m = 0.0f;
             for (int c = tid; c < K; c += kThreads)
-                m = fmaxf(m, (float)fabs(pro_value(p.pro, row, c, stat, p.norm_w, p.norm_w_len)));
+                m = fmaxf(m, (float)fabs(pro_value<PRO>(row, c, stat, p.norm_w, p.norm_w_len)));
             m = block_max(m, sm.red);
             amax = m < 1e-5f ? 1e-5f : m;
         }
@@ -178,15 +192,12 @@ __device__ void stage_activations(const LbGemvParams& p, const Smem& sm) {
                 for (int k = 0; k < 16; ++k) {
                     int c = c0 + k;
                     if (c < K) {
-                        double v = pro_value(p.pro, row, c, stat, p.norm_w, p.norm_w_len);
+                        double v = pro_value<PRO>(row, c, stat, p.norm_w, p.norm_w_len);
                         int q = lb_quant_i8(v, s);
                         r[k >> 2] |= (uint32_t)(q & 0xff) << (8 * (k & 3));
                         if (side) {
                             if (p.q_out) p.q_out[(size_t)n * K + c] = (int8_t)q;
-                            if (p.norm_out) {
-                                if (p.pro == LB_PRO_INNERNORM64) ((double*)p.norm_out)[(size_t)n * K + c] = v;
-                                else ((float*)p.norm_out)[(size_t)n * K + c] = (float)v;
-                            }
+                            if (p.norm_out) p.norm_out[(size_t)n * K + c] = (float)v;
                         }
                     }
                 }
@@ -204,6 +215,7 @@ __device__ void stage_activations(const LbGemvParams& p, const Smem& sm) {
         }
         local_sum = lb_warp_sum_i(local_sum);
         if ((tid & 31) == 0 && local_sum != 0) atomicAdd(&sm.xsum[n], local_sum);
+        if (tid < 3) sm.os[tid * kMaxM + n] = tid < p.nseg ? lb_output_scale(p.seg[tid].scale, amax) : 1.0;
         if (tid == 0) {
             sm.amax[n] = amax;
             if (side && p.amax_out) p.amax_out[n] = amax;
@@ -212,54 +224,81 @@ __device__ void stage_activations(const LbGemvParams& p, const Smem& sm) {
     __syncthreads();
 }
 
-// Epilogue of one finished row (or gate/up row pair).
+// Activations other than linear/ReLU/ReLU2 pull in transcendental code: keep it out of the straight-line path.
+__device__ __noinline__ float activate_slow(float v, int act) { return lb_activate(v, act); }
+
+__device__ __forceinline__ size_t out_index(const LbGemvParams& p, const LbGemvSeg& sg, int n, int r) {
+    if (sg.out_ring > 0) return (size_t)((*p.pos_ptr + n) % sg.out_ring) * sg.rows + r;
+    return (size_t)n * sg.rows + r;
+}
+
+// Epilogue of one finished row (or gate/up row pair).  vals = [group][M][16] complete sums of sum(code*x).
+template <int EPI>
 __device__ __forceinline__ void finish_row(const LbGemvParams& p, const Smem& sm, int group_first_vstrip, int e, int n,
-                                           int i, const int* vals /* [group][M][16] */) {
+                                           int i, const int* vals) {
     const int M = p.M;
-    if (p.interleave2) {
+    if (EPI == LB_EPI_SWIGLU) {
         if (e != 0) return;  // pairs are finished from the gate side
-        const int local = group_first_vstrip >> 1;
-        const int r = local * kTileRows + i;
+        const int r = (group_first_vstrip >> 1) * kTileRows + i;
         const LbGemvSeg& sg = p.seg[0];
         const LbGemvSeg& su = p.seg[1];
         if (r >= sg.rows) return;
-        int ag = vals[(0 * M + n) * 16 + i] - sm.xsum[n];
-        int au = vals[(1 * M + n) * 16 + i] - sm.xsum[n];
-        if (sg.acc_out) sg.acc_out[(size_t)n * sg.rows + r] = ag;
-        if (su.acc_out) su.acc_out[(size_t)n * su.rows + r] = au;
-        double yg = __dmul_rn((double)ag, lb_output_scale(sg.scale, sm.amax[n]));
-        double yu = __dmul_rn((double)au, lb_output_scale(su.scale, sm.amax[n]));
+        const int ag = vals[(0 * M + n) * 16 + i] - sm.xsum[n];
+        const int au = vals[(1 * M + n) * 16 + i] - sm.xsum[n];
+        double yg = __dmul_rn((double)ag, sm.os[0 * kMaxM + n]);
+        double yu = __dmul_rn((double)au, sm.os[1 * kMaxM + n]);
         if (sg.bias) yg = __dadd_rn(yg, (double)sg.bias[r]);
         if (su.bias) yu = __dadd_rn(yu, (double)su.bias[r]);
-        if (sg.out) ((float*)sg.out)[(size_t)n * sg.rows + r] = (float)lb_gate_product(yg, yu, p.act);
+        ((float*)sg.out)[(size_t)n * sg.rows + r] = (float)lb_gate_product(yg, yu, p.act);
         return;
     }
     const int v = group_first_vstrip + e;
     int s = 0;
-    if (p.nseg > 1 && v >= p.seg[1].vstrip0) s = 1;
-    if (p.nseg > 2 && v >= p.seg[2].vstrip0) s = 2;
+    if (EPI == LB_EPI_QKV || EPI == LB_EPI_GENERIC) {
+        if (p.nseg > 1 && v >= p.seg[1].vstrip0) s = 1;
+        if (p.nseg > 2 && v >= p.seg[2].vstrip0) s = 2;
+    }
     const LbGemvSeg& sg = p.seg[s];
     const int r = (v - sg.vstrip0) * kTileRows + i;
     if (r >= sg.rows) return;
     const int acc = vals[(e * M + n) * 16 + i] - sm.xsum[n];
-    const size_t o = (size_t)n * sg.rows + r;
-    if (sg.acc_out) sg.acc_out[o] = acc;
-    if (sg.kind == LB_OUT_ACC || !sg.out) return;
-    double y = __dmul_rn((double)acc, lb_output_scale(sg.scale, sm.amax[n]));
+    if (EPI == LB_EPI_GENERIC) {
+        const size_t o = (size_t)n * sg.rows + r;
+        if (sg.acc_out) sg.acc_out[o] = acc;
+        if (sg.kind == LB_OUT_ACC || !sg.out) return;
+    }
+    double y = __dmul_rn((double)acc, sm.os[s * kMaxM + n]);
     if (sg.bias) y = __dadd_rn(y, (double)sg.bias[r]);
+    if (EPI == LB_EPI_QKV) {
+        const size_t o = out_index(p, sg, n, r);
+        if (s == 0) ((double*)sg.out)[o] = y;
+        else ((float*)sg.out)[o] = (float)y;
+        return;
+    }
+    if (EPI == LB_EPI_RESID) {
+        const size_t o = (size_t)n * sg.rows + r;
+        float f = (float)y;
+        if (p.residual) f = __fadd_rn(f, p.residual[o]);
+        ((float*)sg.out)[o] = f;
+        return;
+    }
+    // generic: per-segment kind, any activation, optional pre-activation copy
+    const size_t o = (size_t)n * sg.rows + r;
     if (sg.kind == LB_OUT_F64) {
         ((double*)sg.out)[o] = y;
         return;
     }
     float f = (float)y;
     if (sg.pre_out) sg.pre_out[o] = f;
-    f = lb_activate(f, p.act);
+    if (p.act == LOOM_B200_ACT_RELU) f = f < 0.f ? 0.f : f;
+    else if (p.act == LOOM_B200_ACT_RELU2) f = f < 0.f ? 0.f : __fmul_rn(f, f);
+    else if (p.act != LOOM_B200_ACT_LINEAR) f = activate_slow(f, p.act);
     if (p.residual && s == 0) f = __fadd_rn(f, p.residual[o]);
     ((float*)sg.out)[o] = f;
 }
 
-template <bool MMA>
-__global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const LbGemvParams p) {
+template <bool MMA, int PRO, int EPI>
+__global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __grid_constant__ LbGemvParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int KB = p.kblocks, M = p.M;
@@ -282,20 +321,32 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const LbGe
         ptr += 32;
         sm.red = reinterpret_cast<double*>(ptr);
         ptr += 256;
+        sm.os = reinterpret_cast<double*>(ptr);
+        ptr += 3 * kMaxM * 8;
         sm.flag = reinterpret_cast<int*>(ptr);
         ptr += 16;
         sm.bars = reinterpret_cast<uint64_t*>(ptr);
     }
 
     // ---- tile ranges --------------------------------------------------------------------------------
-    const long long T = p.total_tiles;
-    const int t0 = (int)(T * blockIdx.x / gridDim.x), t1 = (int)(T * (blockIdx.x + 1) / gridDim.x);
+    // aligned: every CTA owns whole strip groups (no cross-CTA fix-up); otherwise stream-K over tiles.
+    int t0, t1;
+    if (p.aligned) {
+        const long long NG = p.total_tiles / (p.group * KB);
+        t0 = (int)(NG * blockIdx.x / gridDim.x) * p.group * KB;
+        t1 = (int)(NG * (blockIdx.x + 1) / gridDim.x) * p.group * KB;
+    } else {
+        const long long T = p.total_tiles;
+        t0 = (int)(T * blockIdx.x / gridDim.x);
+        t1 = (int)(T * (blockIdx.x + 1) / gridDim.x);
+    }
     const int cta_tiles = t1 - t0;
     const int w0 = t0 + (int)((long long)cta_tiles * warp / kWarps);
     const int w1 = t0 + (int)((long long)cta_tiles * (warp + 1) / kWarps);
     const int first_group = cta_tiles > 0 ? (t0 / KB) / p.group : 0;
     const int local_v0 = first_group * p.group;  // virtual strip held in sacc slot 0
 
+    LB_TRACE(0);
     if (tid < kWarps * kStages) lb_mbar_init(&sm.bars[tid], 1);
     for (int i = tid; i < p.max_local_strips * M * 16; i += kThreads) sm.sacc[i] = 0;
     if (tid == 0) lb_fence_mbar_init();
@@ -324,7 +375,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const LbGe
         }
     };
     auto issue = [&](int stage, const Cursor& c, int len) {  // lane 0 only
-        if (p.debug == 2) return;
+        if (p.debug >= 2) return;
         lb_mbar_expect_tx(&my_bars[stage], (uint32_t)len * kTileBytes);
         lb_bulk_g2s(my_ring + (size_t)stage * kStageBytes, tile_ptr(p, c.v, c.kb), (uint32_t)len * kTileBytes,
                     &my_bars[stage]);
@@ -342,9 +393,14 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const LbGe
         advance(ic, len);
     }
 
-    lb_pdl_wait();  // everything below may read what earlier launches wrote
-    stage_activations(p, sm);
-    lb_pdl_launch_dependents();
+    lb_pdl_launch_dependents();  // the next launch may start prefetching its weights
+    LB_TRACE(1);
+    lb_pdl_wait();               // everything below may read what earlier launches wrote
+    LB_TRACE(2);
+    if (p.debug == 3) return;
+    stage_activations<PRO>(p, sm);
+    LB_TRACE(3);
+    if (p.debug == 4) return;
 
     // ---- main loop ------------------------------------------------------------------------------------
     const int g = lane >> 2, t = lane & 3;
@@ -472,42 +528,65 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const LbGe
     }
     flush();
     __syncthreads();
+    LB_TRACE(4);
 
     // ---- strip groups: finish what this CTA owns entirely, hand the rest to the fix-up ------------------
     if (cta_tiles <= 0) return;
     const int group_tiles = p.group * KB;
     const int last_group = ((t1 - 1) / KB) / p.group;
     const int per_group = p.group * M * 16;
-    for (int G = first_group; G <= last_group; ++G) {
+    const int ngl = last_group - first_group + 1;
+    // Only the first and the last group of a stream-K range can be shared with another CTA.
+    auto mine_of = [&](int G) {
         const int gs = G * group_tiles, ge = gs + group_tiles;
-        const int mine = (t1 < ge ? t1 : ge) - (t0 > gs ? t0 : gs);
-        int* vals = sm.sacc + (size_t)(G - first_group) * per_group;
-        if (mine != group_tiles) {
-            int* gacc = p.fix_acc + (size_t)G * per_group;
-            for (int i = tid; i < per_group; i += kThreads) {
-                int v = vals[i];
-                if (v != 0) atomicAdd(&gacc[i], v);
-            }
-            __threadfence();
-            __syncthreads();
-            if (tid == 0) {
-                unsigned old = atomicAdd(&p.fix_cnt[G], (unsigned)mine);
-                sm.flag[0] = (old + (unsigned)mine == (unsigned)group_tiles) ? 1 : 0;
-            }
-            __syncthreads();
-            const bool last = sm.flag[0] != 0;
-            __syncthreads();
-            if (!last) continue;
-            __threadfence();
-            for (int i = tid; i < per_group; i += kThreads) vals[i] = atomicExch(&gacc[i], 0);
-            if (tid == 0) p.fix_cnt[G] = 0;
-            __syncthreads();
+        return (t1 < ge ? t1 : ge) - (t0 > gs ? t0 : gs);
+    };
+    const int mine_first = mine_of(first_group), mine_last = mine_of(last_group);
+    const bool part_first = mine_first != group_tiles;
+    const bool part_last = ngl > 1 && mine_last != group_tiles;
+    if (tid < 2) sm.flag[tid] = 1;  // 1 = this CTA finishes the group
+    if (part_first || part_last) {
+        for (int i = tid; i < 2 * per_group; i += kThreads) {
+            const int which = i / per_group, k = i - which * per_group;
+            if (which == 0 ? !part_first : !part_last) continue;
+            const int G = which == 0 ? first_group : last_group;
+            const int v = sm.sacc[(size_t)(G - first_group) * per_group + k];
+            if (v != 0) atomicAdd(&p.fix_acc[(size_t)G * per_group + k], v);
         }
-        for (int i = tid; i < per_group; i += kThreads) {
-            const int e = i / (M * 16), rem = i - e * (M * 16);
-            finish_row(p, sm, G * p.group, e, rem >> 4, rem & 15, vals);
+        __threadfence();
+        __syncthreads();
+        if (tid == 0 && part_first) {
+            unsigned old = atomicAdd(&p.fix_cnt[first_group], (unsigned)mine_first);
+            sm.flag[0] = (old + (unsigned)mine_first == (unsigned)group_tiles) ? 1 : 0;
+        }
+        if (tid == 32 && part_last) {
+            unsigned old = atomicAdd(&p.fix_cnt[last_group], (unsigned)mine_last);
+            sm.flag[1] = (old + (unsigned)mine_last == (unsigned)group_tiles) ? 1 : 0;
+        }
+        __syncthreads();
+        const bool take_first = part_first && sm.flag[0], take_last = part_last && sm.flag[1];
+        if (take_first || take_last) {
+            __threadfence();
+            for (int i = tid; i < 2 * per_group; i += kThreads) {
+                const int which = i / per_group, k = i - which * per_group;
+                if (which == 0 ? !take_first : !take_last) continue;
+                const int G = which == 0 ? first_group : last_group;
+                sm.sacc[(size_t)(G - first_group) * per_group + k] = atomicExch(&p.fix_acc[(size_t)G * per_group + k], 0);
+            }
+            if (tid == 0 && take_first) p.fix_cnt[first_group] = 0;
+            if (tid == 32 && take_last) p.fix_cnt[last_group] = 0;
         }
     }
+    __syncthreads();
+    const bool do_first = sm.flag[0] != 0, do_last = sm.flag[1] != 0;
+    for (int idx = tid; idx < ngl * per_group; idx += kThreads) {
+        const int gl = idx / per_group, i = idx - gl * per_group;
+        if (gl == 0 && !do_first) continue;
+        if (gl == ngl - 1 && ngl > 1 && !do_last) continue;
+        const int e = i / (M * 16), rem = i - e * (M * 16);
+        finish_row<EPI>(p, sm, (first_group + gl) * p.group, e, rem >> 4, rem & 15, sm.sacc + (size_t)gl * per_group);
+    }
+    LB_TRACE(5);
 }
 
 size_t gemv_smem_bytes(const LbGemvParams& p, int max_local) {
@@ -516,7 +595,7 @@ size_t gemv_smem_bytes(const LbGemvParams& p, int max_local) {
     b += (size_t)(p.M * ((Kp + 16) / 4) + 8) * 4;
     b = (b + 15) & ~(size_t)15;
     b += (size_t)max_local * p.M * 16 * 4;
-    b += 32 + 32 + 256 + 16;
+    b += 32 + 32 + 256 + 3 * kMaxM * 8 + 16;
     b += (size_t)kWarps * kStages * 8;
     return b;
 }
@@ -535,8 +614,10 @@ int lb_gemv_finalize_params(loom_b200_ctx* ctx, LbGemvParams& p) {
         p.seg[s].vstrip0 = v;
         v += p.seg[s].strips;
     }
+    p.interleave2 = p.epi == LB_EPI_SWIGLU ? 1 : 0;
     if (p.interleave2) {
         LB_REQUIRE(ctx, p.nseg == 2 && p.seg[0].rows == p.seg[1].rows, "gemv: gate/up pair needs two equal matrices");
+        LB_REQUIRE(ctx, p.seg[0].out != nullptr, "gemv: gate/up pair needs an output buffer");
         p.seg[0].vstrip0 = p.seg[1].vstrip0 = 0;
         p.group = 2;
     } else {
@@ -550,24 +631,55 @@ int lb_gemv_finalize_params(loom_b200_ctx* ctx, LbGemvParams& p) {
 
 int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     LbGemvParams p = pin;
-    int grid = ctx->sm_count * ctx->opt_gemv_ctas_per_sm;
-    if (grid > p.total_tiles) grid = p.total_tiles;
-    if (grid < 1) grid = 1;
-    int tpc = (p.total_tiles + grid - 1) / grid;
-    p.max_local_strips = (tpc + p.kblocks - 2) / p.kblocks + 1 + 2 * (p.group - 1);
     int vstrips = p.total_tiles / p.kblocks;
     int ngroups = (vstrips + p.group - 1) / p.group;
+    int grid = ctx->sm_count * ctx->opt_gemv_ctas_per_sm;
+    // Enough strip groups to occupy the SMs: give every CTA whole groups and skip the cross-CTA fix-up.
+    p.aligned = ctx->opt_gemv_partition == 1 ? 0 : (ctx->opt_gemv_partition == 2 ? 1 : (ngroups * 2 >= ctx->sm_count ? 1 : 0));
+    if (p.aligned) {
+        if (grid > ngroups) grid = ngroups;
+        int gpc = (ngroups + grid - 1) / grid;
+        p.max_local_strips = gpc * p.group;
+    } else {
+        if (grid > p.total_tiles) grid = p.total_tiles;
+        if (grid < 1) grid = 1;
+        int tpc = (p.total_tiles + grid - 1) / grid;
+        p.max_local_strips = (tpc + p.kblocks - 2) / p.kblocks + 1 + 2 * (p.group - 1);
+    }
     if (int rc = lb_ensure_fixup(ctx, (size_t)ngroups * p.group * p.M * 16, (size_t)ngroups)) return rc;
     p.fix_acc = ctx->fix_acc;
     p.fix_cnt = ctx->fix_cnt;
     p.status = ctx->status_dev;
     p.debug = ctx->opt_debug;
+    p.trace = grid <= kTraceCtas ? ctx->trace_dev : nullptr;
     size_t smem = gemv_smem_bytes(p, p.max_local_strips);
     if (smem > 227 * 1024)
         return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: K=%d with %d tokens needs %zu B of shared memory", p.K, p.M, smem);
-    const bool use_dp4a = ctx->opt_gemv_variant == 1 && p.M == 1;
-    auto kern = use_dp4a ? lb_gemv_ternary_kernel<false> : lb_gemv_ternary_kernel<true>;
-    const unsigned attr_bit = use_dp4a ? 2u : 1u;
+    // one instantiation per (inner loop, prologue, epilogue) combination that a caller can reach
+    using Kern = void (*)(const LbGemvParams);
+    Kern kern = nullptr;
+    int kid = -1;
+    const bool use_dp4a = ctx->opt_gemv_variant == 1 && p.M == 1 && p.pro == LB_PRO_Q8 && p.epi == LB_EPI_GENERIC;
+#define LB_PICK(id, mma, pro_, epi_)                                \
+    if (kid < 0 && p.pro == pro_ && p.epi == epi_ && (mma) == !use_dp4a) { \
+        kern = lb_gemv_ternary_kernel<mma, pro_, epi_>;             \
+        kid = id;                                                   \
+    }
+    LB_PICK(0, true, LB_PRO_Q8, LB_EPI_GENERIC)
+    LB_PICK(1, false, LB_PRO_Q8, LB_EPI_GENERIC)
+    LB_PICK(2, true, LB_PRO_F32, LB_EPI_GENERIC)
+    LB_PICK(3, true, LB_PRO_BLOCKNORM, LB_EPI_QKV)
+    LB_PICK(4, true, LB_PRO_F32, LB_EPI_QKV)
+    LB_PICK(5, true, LB_PRO_INNERNORM64, LB_EPI_RESID)
+    LB_PICK(6, true, LB_PRO_BLOCKNORM, LB_EPI_SWIGLU)
+    LB_PICK(7, true, LB_PRO_F32, LB_EPI_SWIGLU)
+    LB_PICK(8, true, LB_PRO_INNERNORM, LB_EPI_RESID)
+    LB_PICK(9, true, LB_PRO_INNERNORM64, LB_EPI_GENERIC)
+    LB_PICK(10, true, LB_PRO_INNERNORM, LB_EPI_GENERIC)
+    LB_PICK(11, true, LB_PRO_Q8, LB_EPI_SWIGLU)
+#undef LB_PICK
+    if (!kern) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: no kernel for prologue %d with epilogue %d", p.pro, p.epi);
+    const unsigned attr_bit = 1u << kid;
     if (!(ctx->func_attr_mask & attr_bit)) {  // per device: the context pins the device
         LB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         ctx->func_attr_mask |= attr_bit;
@@ -608,6 +720,7 @@ extern "C" int loom_b200_ternary_linear(loom_b200_ctx* ctx, const loom_b200_weig
         p.seg[0].out = out ? (void*)(out + (size_t)b0 * w->rows) : nullptr;
         p.seg[0].acc_out = acc_out ? acc_out + (size_t)b0 * w->rows : nullptr;
         p.seg[0].kind = out ? LB_OUT_F32 : LB_OUT_ACC;
+        p.epi = LB_EPI_GENERIC;
         p.K = w->cols;
         p.M = batch - b0 < kMaxM ? batch - b0 : kMaxM;
         p.pro = LB_PRO_Q8;

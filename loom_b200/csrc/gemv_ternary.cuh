@@ -19,6 +19,14 @@ enum LbOutKind : int {
     LB_OUT_ACC = 3,    // raw int32 accumulators only
 };
 
+// Compile-time epilogue families (one kernel instantiation each).
+enum LbEpi : int {
+    LB_EPI_GENERIC = 0,  // per-segment LbOutKind, any activation, bias, residual, pre/acc side outputs
+    LB_EPI_QKV = 1,      // segment 0 -> fp64 (query), segments 1,2 -> fp32 rows of the KV ring (poly/mha.go:274-283)
+    LB_EPI_RESID = 2,    // float(y + bias) + residual (O and down projections; poly/mha.go:365, poly/swiglu.go:317)
+    LB_EPI_SWIGLU = 3,   // gate/up pair -> float(gateProduct) (poly/swiglu.go:306-310)
+};
+
 struct LbGemvSeg {
     const uint32_t* tiles;  // tiled weights of this matrix
     const float* bias;      // [rows] or null
@@ -30,6 +38,7 @@ struct LbGemvSeg {
     int vstrip0;            // first virtual strip (concatenated order)
     float scale;
     int kind;
+    int out_ring;  // > 0: token n goes to row (*pos_ptr + n) % out_ring of `out` (the KV ring), else row n
 };
 
 struct LbGemvParams {
@@ -40,6 +49,7 @@ struct LbGemvParams {
     int K, kblocks, M;
     int total_tiles;  // virtual strips * kblocks
     int max_local_strips;
+    int aligned;  // 1: CTAs own whole strip groups; 0: stream-K with the int32 fix-up
     // prologue
     int pro;
     const void* x;
@@ -49,14 +59,17 @@ struct LbGemvParams {
     double eps;
     int8_t* q_out;     // optional side outputs, written by CTA 0
     float* amax_out;
-    void* norm_out;    // normalised row (float for 2/3, double for 4)
+    float* norm_out;   // normalised row as float32 (what the layers report as preAct)
     // epilogue
+    int epi;             // LbEpi
+    const int* pos_ptr;  // device scalar: position of token 0 (KV ring rows), or null
     int act;
     const float* residual;  // [M, rows of segment 0] or null
     // stream-K fix-up scratch (zero between launches)
     int32_t* fix_acc;
     unsigned int* fix_cnt;
     int* status;
+    unsigned long long* trace;  // optional [grid][8] phase timestamps (ns), or null
     int debug;  // timing experiments only: 1 = skip the arithmetic, 2 = skip the weight copies
 };
 

@@ -1,0 +1,389 @@
+// glue.cu -- decoder steps around the ternary projections (see glue.cuh).  Arithmetic follows the reference's
+// CPU decoder: poly/mha.go:285-354 (q/k norm, RoPE, attention in float64 over a float32 KV ring),
+// poly/norm.go:102-138 (RMSNorm), poly/transformer.go:659-719 (fp32 LM head, float64 accumulation),
+// poly/sampling.go:45-55 (greedy = first maximum).
+#include "glue.cuh"
+
+namespace {
+
+__device__ __forceinline__ double warp_max_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmax(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// block-wide reductions for blockDim.x <= 1024; every thread gets the same bits
+__device__ __forceinline__ double block_sum_d(double v, double* red) {
+    v = lb_warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    double r = 0.0;
+    for (int i = 0; i < nw; ++i) r += red[i];
+    return r;
+}
+__device__ __forceinline__ double block_max_d(double v, double* red) {
+    v = warp_max_d(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    double r = red[0];
+    for (int i = 1; i < nw; ++i) r = fmax(r, red[i]);
+    return r;
+}
+
+__global__ void lb_embed_kernel(const float* __restrict__ emb, int vocab, int hidden, const int* __restrict__ tok,
+                                float* __restrict__ x) {
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    const int n = blockIdx.x;
+    const int t = tok[n];
+    const bool ok = t >= 0 && t < vocab;
+    const float* src = emb + (size_t)(ok ? t : 0) * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) x[(size_t)n * hidden + i] = ok ? src[i] : 0.0f;
+}
+
+// One CTA per (token, head) over Q heads then K heads; hd/2 threads, thread d owns the pair (d, d+hd/2).
+__global__ void lb_rope_kernel(const LbRopeParams p) {
+    __shared__ double red[32];
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    const int n = blockIdx.y, h = blockIdx.x, half = p.hd / 2, d = threadIdx.x;
+    const int pos = *p.pos_ptr + n;
+    const bool is_q = h < p.heads;
+    double v0, v1;
+    float* krow = nullptr;
+    double* qrow = nullptr;
+    if (is_q) {
+        qrow = p.q + (size_t)n * p.heads * p.hd + (size_t)h * p.hd;
+        v0 = qrow[d];
+        v1 = qrow[d + half];
+    } else {
+        const int kh = h - p.heads;
+        krow = p.cache_k + (size_t)(pos % p.msl) * p.kv_heads * p.hd + (size_t)kh * p.hd;
+        v0 = (double)krow[d];
+        v1 = (double)krow[d + half];
+    }
+    const float* gamma = is_q ? p.q_norm : p.k_norm;
+    const int glen = is_q ? p.q_norm_len : p.k_norm_len;
+    if (gamma && glen > 0) {  // per-head RMSNorm, poly/mha.go:584-646
+        double ss = block_sum_d(__dadd_rn(__dmul_rn(v0, v0), __dmul_rn(v1, v1)), red);
+        double rms = sqrt(__dadd_rn(__ddiv_rn(ss, (double)p.hd), p.qk_eps));
+        if (rms != 0.0) {
+            const int hh = is_q ? h : h - p.heads;
+            const int nh = is_q ? p.heads : p.kv_heads;
+            double inv = __ddiv_rn(1.0, rms);
+            double s0 = 1.0, s1 = 1.0;
+            if (glen == p.hd) {
+                s0 = (double)gamma[d];
+                s1 = (double)gamma[d + half];
+            } else if (glen == nh * p.hd) {
+                s0 = (double)gamma[(size_t)hh * p.hd + d];
+                s1 = (double)gamma[(size_t)hh * p.hd + d + half];
+            }
+            v0 = __dmul_rn(__dmul_rn(v0, inv), s0);
+            v1 = __dmul_rn(__dmul_rn(v1, inv), s1);
+            if (!is_q) {  // the K row is float32 storage: the norm result is rounded before RoPE reads it back
+                v0 = (double)(float)v0;
+                v1 = (double)(float)v1;
+            }
+        }
+    }
+    const double angle = __ddiv_rn((double)pos, p.rope_div[d]);
+    double sn, c;
+    sincos(angle, &sn, &c);
+    const double r0 = __dsub_rn(__dmul_rn(v0, c), __dmul_rn(v1, sn));
+    const double r1 = __dadd_rn(__dmul_rn(v0, sn), __dmul_rn(v1, c));
+    if (is_q) {
+        qrow[d] = r0;
+        qrow[d + half] = r1;
+    } else {
+        krow[d] = (float)r0;
+        krow[d + half] = (float)r1;
+    }
+}
+
+// One CTA per (head, token, split).  Thread j scores position k0+j (+blockDim ...), thread d (< hd) owns output
+// dimension d.  With splits > 1 the partial (max, sum, weighted V) of every split goes to scratch and the CTA
+// that arrives last combines them.
+constexpr int kAttnThreads = 128;
+
+__global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttnParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __shared__ double red[32];
+    __shared__ int s_last;
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    const int h = blockIdx.x, n = blockIdx.y, sp = blockIdx.z, tid = threadIdx.x;
+    const int hd = p.hd, kvd = p.kv_heads * hd, qd = p.heads * hd;
+    double* sq = reinterpret_cast<double*>(smem_raw);  // [hd]
+    double* sc = sq + hd;                               // [max_chunk]
+    const int last = *p.pos_ptr + n;                    // attends to positions 0..last
+    const int total = last + 1;
+    const int per = (total + p.splits - 1) / p.splits;
+    const int k0 = sp * per;
+    int k1 = k0 + per;
+    if (k1 > total) k1 = total;
+    const int cnt = k1 > k0 ? k1 - k0 : 0;
+    const int kvh = h / (p.heads / p.kv_heads);
+    const double scale = __ddiv_rn(1.0, sqrt((double)hd));
+
+    for (int d = tid; d < hd; d += kAttnThreads) sq[d] = p.q[(size_t)n * qd + (size_t)h * hd + d];
+    __syncthreads();
+
+    double mx = -1e9;
+    for (int j = tid; j < cnt; j += kAttnThreads) {
+        const float* kr = p.cache_k + (size_t)((k0 + j) % p.msl) * kvd + (size_t)kvh * hd;
+        double dot = 0.0;
+        for (int d = 0; d < hd; d += 4) {
+            const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+            dot = __dadd_rn(dot, __dmul_rn(sq[d], (double)kv.x));
+            dot = __dadd_rn(dot, __dmul_rn(sq[d + 1], (double)kv.y));
+            dot = __dadd_rn(dot, __dmul_rn(sq[d + 2], (double)kv.z));
+            dot = __dadd_rn(dot, __dmul_rn(sq[d + 3], (double)kv.w));
+        }
+        const double s = __dmul_rn(dot, scale);
+        sc[j] = s;
+        mx = fmax(mx, s);
+    }
+    mx = block_max_d(mx, red);
+    double den = 0.0;
+    for (int j = tid; j < cnt; j += kAttnThreads) {
+        const double e = exp(__dsub_rn(sc[j], mx));
+        sc[j] = e;
+        den = __dadd_rn(den, e);
+    }
+    den = block_sum_d(den, red);  // also orders the sc[] writes before the reads below
+
+    for (int d = tid; d < hd; d += kAttnThreads) {
+        double acc = 0.0;
+        const float* vb = p.cache_v + (size_t)kvh * hd + d;
+        for (int j = 0; j < cnt; ++j) acc = __dadd_rn(acc, __dmul_rn(sc[j], (double)vb[(size_t)((k0 + j) % p.msl) * kvd]));
+        if (p.splits == 1) {
+            p.out[(size_t)n * qd + (size_t)h * hd + d] = __ddiv_rn(acc, den);
+        } else {
+            double* part = p.part + ((size_t)(n * p.heads + h) * p.splits + sp) * (hd + 2);
+            part[2 + d] = acc;
+            if (d == 0) {
+                part[0] = mx;
+                part[1] = den;
+            }
+        }
+    }
+    if (p.splits == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned old = atomicAdd(&p.cnt[n * p.heads + h], 1u);
+        s_last = old + 1 == (unsigned)p.splits;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const double* base = p.part + (size_t)(n * p.heads + h) * p.splits * (hd + 2);
+    double gm = -1e9;
+    for (int s = 0; s < p.splits; ++s) gm = fmax(gm, __ldcg(base + (size_t)s * (hd + 2)));
+    for (int d = tid; d < hd; d += kAttnThreads) {
+        double num = 0.0, dn = 0.0;
+        for (int s = 0; s < p.splits; ++s) {
+            const double* ps = base + (size_t)s * (hd + 2);
+            const double l = __ldcg(ps + 1);
+            if (l == 0.0) continue;  // an empty split
+            const double w = exp(__dsub_rn(__ldcg(ps), gm));
+            num = __dadd_rn(num, __dmul_rn(__ldcg(ps + 2 + d), w));
+            dn = __dadd_rn(dn, __dmul_rn(l, w));
+        }
+        p.out[(size_t)n * qd + (size_t)h * hd + d] = __ddiv_rn(num, dn);
+    }
+    if (tid == 0) p.cnt[n * p.heads + h] = 0;
+}
+
+// fp32 LM head: every warp walks vocabulary rows; the hidden row is normalised once per CTA into shared
+// memory as doubles.  Products of two floats are exact in double; only the summation order differs from
+// the reference's sequential loop.
+constexpr int kHeadThreads = 256;
+
+__global__ void __launch_bounds__(kHeadThreads) lb_lm_head_kernel(const LbLmHeadParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __shared__ double red[32];
+    double* sh = reinterpret_cast<double*>(smem_raw);  // [hidden]
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    const int H = p.hidden, tid = threadIdx.x;
+    double ss = 0.0;
+    for (int i = tid; i < H; i += kHeadThreads) {
+        double v = (double)p.x[i];
+        ss = __dadd_rn(ss, __dmul_rn(v, v));
+    }
+    ss = block_sum_d(ss, red);
+    const double rms = sqrt(__dadd_rn(__ddiv_rn(ss, (double)H), p.eps));
+    for (int i = tid; i < H; i += kHeadThreads) {
+        double g = p.gain ? (double)p.gain[i] : 1.0;
+        float y = (float)__dmul_rn(__ddiv_rn((double)p.x[i], rms), g);
+        sh[i] = (double)y;
+        if (blockIdx.x == 0 && p.hidden_out) p.hidden_out[i] = y;
+    }
+    __syncthreads();
+    const int lane = tid & 31;
+    const int warps_total = gridDim.x * (kHeadThreads / 32);
+    const int H4 = H / 4;
+    for (int v = blockIdx.x * (kHeadThreads / 32) + (tid >> 5); v < p.vocab; v += warps_total) {
+        const float* row = p.head + (size_t)v * H;
+        double acc = 0.0;
+        if ((H & 3) == 0) {
+            const float4* r4 = reinterpret_cast<const float4*>(row);
+            int i = lane;
+            for (; i + 96 < H4; i += 128) {
+                const float4 a = __ldcs(r4 + i), b = __ldcs(r4 + i + 32), c = __ldcs(r4 + i + 64), d = __ldcs(r4 + i + 96);
+                const double* s0 = sh + 4 * i;
+                acc = fma((double)a.x, s0[0], acc); acc = fma((double)a.y, s0[1], acc);
+                acc = fma((double)a.z, s0[2], acc); acc = fma((double)a.w, s0[3], acc);
+                acc = fma((double)b.x, s0[128], acc); acc = fma((double)b.y, s0[129], acc);
+                acc = fma((double)b.z, s0[130], acc); acc = fma((double)b.w, s0[131], acc);
+                acc = fma((double)c.x, s0[256], acc); acc = fma((double)c.y, s0[257], acc);
+                acc = fma((double)c.z, s0[258], acc); acc = fma((double)c.w, s0[259], acc);
+                acc = fma((double)d.x, s0[384], acc); acc = fma((double)d.y, s0[385], acc);
+                acc = fma((double)d.z, s0[386], acc); acc = fma((double)d.w, s0[387], acc);
+            }
+            for (; i < H4; i += 32) {
+                const float4 a = __ldcs(r4 + i);
+                const double* s0 = sh + 4 * i;
+                acc = fma((double)a.x, s0[0], acc); acc = fma((double)a.y, s0[1], acc);
+                acc = fma((double)a.z, s0[2], acc); acc = fma((double)a.w, s0[3], acc);
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) acc = fma((double)row[i], sh[i], acc);
+        }
+        acc = lb_warp_sum(acc);
+        if (lane == 0) p.logits[v] = (float)acc;
+    }
+}
+
+__global__ void __launch_bounds__(1024) lb_argmax_advance_kernel(const float* __restrict__ logits, int vocab, int* tok,
+                                                                 int* out_tokens, int out_cap, int* step, int* pos) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    float best = logits[0];
+    int idx = 0;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        float v = logits[i];
+        if (v > best || (v == best && i < idx)) {
+            best = v;
+            idx = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) {
+            best = ov;
+            idx = oi;
+        }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) {
+        sv[warp] = best;
+        si[warp] = idx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (sv[w] > best || (sv[w] == best && si[w] < idx)) {
+                best = sv[w];
+                idx = si[w];
+            }
+        tok[0] = idx;
+        if (out_tokens && step) {
+            int s = *step;
+            if (s < out_cap) out_tokens[s] = idx;
+            *step = s + 1;
+        }
+        if (pos) *pos += 1;
+    }
+}
+
+__global__ void lb_add_scalar_kernel(int* p, int delta) {
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    if (threadIdx.x == 0) *p += delta;
+}
+
+template <typename... Args>
+cudaError_t launch_pdl(loom_b200_ctx* ctx, void (*kern)(Args...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+}  // namespace
+
+int lb_launch_embed(loom_b200_ctx* ctx, const float* emb, int vocab, int hidden, const int* tok_dev, int n, float* x) {
+    LB_CUDA(ctx, launch_pdl(ctx, lb_embed_kernel, dim3(n), dim3(256), 0, emb, vocab, hidden, tok_dev, x));
+    ctx->launches++;
+    return 0;
+}
+
+int lb_launch_rope(loom_b200_ctx* ctx, const LbRopeParams& p) {
+    LB_REQUIRE(ctx, p.hd % 2 == 0 && p.hd / 2 <= 1024, "rope: head_dim %d", p.hd);
+    LB_CUDA(ctx, launch_pdl(ctx, lb_rope_kernel, dim3(p.heads + p.kv_heads, p.M), dim3(p.hd / 2), 0, p));
+    ctx->launches++;
+    return 0;
+}
+
+size_t lb_attn_part_elems(int M, int heads, int hd, int splits) { return (size_t)M * heads * splits * (hd + 2); }
+
+int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p) {
+    LB_REQUIRE(ctx, p.hd % 4 == 0, "attention: head_dim %d must be a multiple of 4", p.hd);
+    LB_REQUIRE(ctx, p.heads % p.kv_heads == 0, "attention: %d heads over %d kv heads", p.heads, p.kv_heads);
+    size_t smem = (size_t)(p.hd + p.max_chunk) * sizeof(double);
+    if (smem > 200 * 1024) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "attention: %d positions per CTA need %zu B of shared memory", p.max_chunk, smem);
+    if (smem > 48 * 1024 && !(ctx->func_attr_mask & (1u << 30))) {
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        ctx->func_attr_mask |= 1u << 30;
+    }
+    LB_CUDA(ctx, launch_pdl(ctx, lb_attention_kernel, dim3(p.heads, p.M, p.splits), dim3(kAttnThreads), smem, p));
+    ctx->launches++;
+    return 0;
+}
+
+int lb_launch_lm_head(loom_b200_ctx* ctx, const LbLmHeadParams& p) {
+    size_t smem = (size_t)p.hidden * sizeof(double);
+    if (smem > 200 * 1024) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "lm_head: hidden %d too large", p.hidden);
+    if (smem > 48 * 1024 && !(ctx->func_attr_mask & (1u << 29))) {
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        ctx->func_attr_mask |= 1u << 29;
+    }
+    int grid = ctx->sm_count * 4;
+    int rows_per = (p.vocab + 7) / 8;
+    if (grid > rows_per) grid = rows_per > 0 ? rows_per : 1;
+    LB_CUDA(ctx, launch_pdl(ctx, lb_lm_head_kernel, dim3(grid), dim3(kHeadThreads), smem, p));
+    ctx->launches++;
+    return 0;
+}
+
+int lb_launch_argmax_advance(loom_b200_ctx* ctx, const float* logits, int vocab, int* tok, int* out_tokens, int out_cap,
+                             int* step, int* pos) {
+    LB_CUDA(ctx, launch_pdl(ctx, lb_argmax_advance_kernel, dim3(1), dim3(1024), 0, logits, vocab, tok, out_tokens, out_cap,
+                            step, pos));
+    ctx->launches++;
+    return 0;
+}
+
+int lb_launch_add_scalar(loom_b200_ctx* ctx, int* pos, int delta) {
+    LB_CUDA(ctx, launch_pdl(ctx, lb_add_scalar_kernel, dim3(1), dim3(32), 0, pos, delta));
+    ctx->launches++;
+    return 0;
+}

@@ -1,0 +1,54 @@
+// glue.cuh -- the steps either side of the ternary projections inside the decoder block loop:
+// embedding gather, q/k norm + RoPE, causal GQA attention over the fp32 KV ring, the fp32 tied LM head
+// with the final RMSNorm fused in, and greedy argmax.  Launch wrappers only; kernels are in glue.cu.
+#pragma once
+#include "common.cuh"
+
+// x[n,:] = emb[tok[n],:]; token ids outside [0,vocab) give a zero row (poly/transformer.go:551-577)
+int lb_launch_embed(loom_b200_ctx* ctx, const float* emb, int vocab, int hidden, const int* tok_dev, int n, float* x);
+
+struct LbRopeParams {
+    double* q;          // [M, heads*hd] fp64, rotated in place
+    float* cache_k;     // [msl, kv_heads*hd] fp32 ring; rows (pos0+n)%msl rotated in place
+    const int* pos_ptr; // device scalar: position of token 0
+    const double* rope_div;  // [hd/2] = pow(theta, 2d/hd), computed on the host in double
+    const float* q_norm;     // per-head RMSNorm gains or null (poly/mha.go:285-290)
+    int q_norm_len;
+    const float* k_norm;
+    int k_norm_len;
+    double qk_eps;
+    int M, heads, kv_heads, hd, msl;
+};
+int lb_launch_rope(loom_b200_ctx* ctx, const LbRopeParams& p);
+
+struct LbAttnParams {
+    const double* q;       // [M, heads*hd] after RoPE
+    const float* cache_k;  // [msl, kv_heads*hd]
+    const float* cache_v;
+    const int* pos_ptr;
+    double* out;           // [M, heads*hd] fp64 attention output (before the inner norm)
+    double* part;          // split scratch [M*heads*splits*(hd+2)]
+    unsigned int* cnt;     // [M*heads], zero between launches
+    int M, heads, kv_heads, hd, msl, splits;
+    int max_chunk;         // positions one CTA may hold scores for (shared memory sizing)
+};
+int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p);
+size_t lb_attn_part_elems(int M, int heads, int hd, int splits);
+
+struct LbLmHeadParams {
+    const float* x;        // [hidden] last hidden row (before the final norm)
+    const float* gain;     // final RMSNorm gain [hidden] or null (= 1)
+    double eps;
+    const float* head;     // [vocab, hidden] fp32 (tied embedding)
+    int vocab, hidden;
+    float* logits;         // [vocab]
+    float* hidden_out;     // optional [hidden]: the normalised row
+};
+int lb_launch_lm_head(loom_b200_ctx* ctx, const LbLmHeadParams& p);
+
+// Greedy step: first index of the maximum (poly/sampling.go:45-55) -> tok[0]; appends it to
+// out_tokens[*step]; then *step += 1 and *pos += 1 so that a recorded frame can be replayed as is.
+int lb_launch_argmax_advance(loom_b200_ctx* ctx, const float* logits, int vocab, int* tok, int* out_tokens,
+                             int out_cap, int* step, int* pos);
+// *pos += delta (after a prefill chunk)
+int lb_launch_add_scalar(loom_b200_ctx* ctx, int* pos, int delta);

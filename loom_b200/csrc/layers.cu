@@ -1,0 +1,427 @@
+// layers.cu -- packed-ternary Dense / SwiGLU / MHA layer forwards behind the C ABI.
+// Reference: DenseForwardPackedTernaryCPU (poly/dense.go:66-101), SwiGLUForwardPackedTernaryCPU
+// (poly/swiglu.go:270-322), MHAForwardPackedTernaryCPU (poly/mha.go:204-371).
+#include "layers.cuh"
+
+#include <cmath>
+#include <vector>
+
+namespace {
+
+void fill_seg(LbGemvSeg& s, const loom_b200_weight* w, const float* bias, void* out) {
+    s = LbGemvSeg{};
+    s.tiles = w->tiles;
+    s.rows = w->rows;
+    s.scale = w->scale;
+    s.bias = bias;
+    s.out = out;
+}
+
+}  // namespace
+
+int lb_swiglu_dev(loom_b200_ctx* ctx, const LbSwigluArgs& a) {
+    const int H = a.gate->cols, I = a.gate->rows;
+    LB_REQUIRE(ctx, a.up->cols == H && a.up->rows == I && a.down->cols == I && a.down->rows == H,
+               "swiglu: gate %dx%d, up %dx%d, down %dx%d do not fit together", a.gate->rows, a.gate->cols, a.up->rows,
+               a.up->cols, a.down->rows, a.down->cols);
+    // gate + up, one quantization shared by both, gate product in the epilogue
+    LbGemvParams p = {};
+    p.nseg = 2;
+    fill_seg(p.seg[0], a.gate, a.bias_gate, a.prod);
+    fill_seg(p.seg[1], a.up, a.bias_up, nullptr);
+    p.K = H;
+    p.M = a.M;
+    p.pro = a.pro_mode;
+    p.x = a.x;
+    p.norm_w = a.gain;
+    p.norm_w_len = a.gain ? H : 0;
+    p.eps = a.block_eps;
+    p.epi = LB_EPI_SWIGLU;
+    p.act = a.act;
+    if (int rc = lb_gemv_finalize_params(ctx, p)) return rc;
+    if (int rc = lb_launch_gemv(ctx, p)) return rc;
+    // inner RMSNorm (always applied) + requantize + down projection (+ bias, + residual)
+    LbGemvParams d = {};
+    d.nseg = 1;
+    fill_seg(d.seg[0], a.down, a.bias_down, a.out);
+    d.K = I;
+    d.M = a.M;
+    d.pro = LB_PRO_INNERNORM;
+    d.x = a.prod;
+    d.norm_w = a.inner_w;
+    d.norm_w_len = a.inner_w ? a.inner_w_len : 0;
+    d.eps = a.inner_eps > 0 ? a.inner_eps : 1e-5;
+    d.norm_out = a.pre_out;
+    d.epi = LB_EPI_RESID;
+    d.residual = a.residual;
+    d.act = LOOM_B200_ACT_LINEAR;
+    if (int rc = lb_gemv_finalize_params(ctx, d)) return rc;
+    return lb_launch_gemv(ctx, d);
+}
+
+int lb_mha_alloc(loom_b200_ctx* ctx, loom_b200_mha* m, int max_splits) {
+    m->ctx = ctx;
+    const size_t cache = (size_t)m->msl * m->kv_dim * sizeof(float);
+    LB_CUDA(ctx, cudaMalloc(&m->cache_k, cache));
+    LB_CUDA(ctx, cudaMalloc(&m->cache_v, cache));
+    LB_CUDA(ctx, cudaMemsetAsync(m->cache_k, 0, cache, ctx->stream));
+    LB_CUDA(ctx, cudaMemsetAsync(m->cache_v, 0, cache, ctx->stream));
+    LB_CUDA(ctx, cudaMalloc(&m->q, (size_t)kChunkTokens * m->q_dim * sizeof(double)));
+    LB_CUDA(ctx, cudaMalloc(&m->attn, (size_t)kChunkTokens * m->q_dim * sizeof(double)));
+    LB_CUDA(ctx, cudaMalloc(&m->part, lb_attn_part_elems(kChunkTokens, m->heads, m->head_dim, max_splits) * sizeof(double)));
+    LB_CUDA(ctx, cudaMalloc(&m->cnt, (size_t)kChunkTokens * m->heads * sizeof(unsigned int)));
+    LB_CUDA(ctx, cudaMemsetAsync(m->cnt, 0, (size_t)kChunkTokens * m->heads * sizeof(unsigned int), ctx->stream));
+    LB_CUDA(ctx, cudaMalloc(&m->pos_dev, sizeof(int)));
+    LB_CUDA(ctx, cudaMemsetAsync(m->pos_dev, 0, sizeof(int), ctx->stream));
+    // pow(theta, 2d/hd) in double on the host: the same libm call the CPU path makes once per use
+    const int half = m->head_dim / 2;
+    std::vector<double> div(half);
+    for (int d = 0; d < half; ++d) div[d] = std::pow(m->theta, (double)(2 * d) / (double)m->head_dim);
+    LB_CUDA(ctx, cudaMalloc(&m->rope_div, half * sizeof(double)));
+    LB_CUDA(ctx, cudaMemcpyAsync(m->rope_div, div.data(), half * sizeof(double), cudaMemcpyHostToDevice, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    m->splits = max_splits;
+    return 0;
+}
+
+void lb_mha_release(loom_b200_mha* m) {
+    void* ptrs[] = {m->bq, m->bk, m->bv, m->bo, m->q_norm, m->k_norm, m->inner, m->cache_k, m->cache_v,
+                    m->rope_div, m->q, m->attn, m->part, m->cnt, m->pos_dev};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+}
+
+int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
+    loom_b200_ctx* ctx = m->ctx;
+    // Q (fp64), K and V (fp32, written straight into the ring rows of these positions)
+    LbGemvParams p = {};
+    p.nseg = 3;
+    fill_seg(p.seg[0], m->wq, m->bq, m->q);
+    fill_seg(p.seg[1], m->wk, m->bk, m->cache_k);
+    fill_seg(p.seg[2], m->wv, m->bv, m->cache_v);
+    p.seg[1].out_ring = m->msl;
+    p.seg[2].out_ring = m->msl;
+    p.K = m->d_model;
+    p.M = a.M;
+    p.pro = a.pro_mode;
+    p.x = a.x;
+    p.norm_w = a.gain;
+    p.norm_w_len = a.gain ? m->d_model : 0;
+    p.eps = a.block_eps;
+    p.epi = LB_EPI_QKV;
+    p.pos_ptr = m->pos_dev;
+    p.act = LOOM_B200_ACT_LINEAR;
+    if (int rc = lb_gemv_finalize_params(ctx, p)) return rc;
+    if (int rc = lb_launch_gemv(ctx, p)) return rc;
+
+    LbRopeParams r = {};
+    r.q = m->q;
+    r.cache_k = m->cache_k;
+    r.pos_ptr = m->pos_dev;
+    r.rope_div = m->rope_div;
+    r.q_norm = m->q_norm;
+    r.q_norm_len = m->q_norm_len;
+    r.k_norm = m->k_norm;
+    r.k_norm_len = m->k_norm_len;
+    r.qk_eps = m->rms_eps > 0 ? m->rms_eps : 1e-6;
+    r.M = a.M;
+    r.heads = m->heads;
+    r.kv_heads = m->kv_heads;
+    r.hd = m->head_dim;
+    r.msl = m->msl;
+    if (int rc = lb_launch_rope(ctx, r)) return rc;
+
+    LbAttnParams t = {};
+    t.q = m->q;
+    t.cache_k = m->cache_k;
+    t.cache_v = m->cache_v;
+    t.pos_ptr = m->pos_dev;
+    t.out = m->attn;
+    t.part = m->part;
+    t.cnt = m->cnt;
+    t.M = a.M;
+    t.heads = m->heads;
+    t.kv_heads = m->kv_heads;
+    t.hd = m->head_dim;
+    t.msl = m->msl;
+    t.splits = a.splits < 1 ? 1 : (a.splits > m->splits ? m->splits : a.splits);
+    t.max_chunk = (m->msl + t.splits - 1) / t.splits;
+    if (int rc = lb_launch_attention(ctx, t)) return rc;
+
+    LbGemvParams o = {};
+    o.nseg = 1;
+    fill_seg(o.seg[0], m->wo, m->bo, a.out);
+    o.K = m->q_dim;
+    o.M = a.M;
+    o.pro = LB_PRO_INNERNORM64;
+    o.x = m->attn;
+    o.norm_w = m->inner;
+    o.norm_w_len = m->inner ? m->inner_len : 0;
+    o.eps = m->rms_eps > 0 ? m->rms_eps : 1e-5;
+    o.norm_out = a.pre_out;
+    o.epi = LB_EPI_RESID;
+    o.residual = a.residual;
+    o.act = LOOM_B200_ACT_LINEAR;
+    if (int rc = lb_gemv_finalize_params(ctx, o)) return rc;
+    return lb_launch_gemv(ctx, o);
+}
+
+// ---- host-buffer layer calls (the C ABI) -------------------------------------------------------------
+
+namespace {
+
+// bump allocator over the context scratch buffer
+struct Arena {
+    char* base;
+    size_t off = 0;
+    explicit Arena(void* b) : base((char*)b) {}
+    template <typename T>
+    T* take(size_t n) {
+        off = (off + 255) & ~(size_t)255;
+        T* p = (T*)(base + off);
+        off += n * sizeof(T);
+        return p;
+    }
+};
+
+size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+int upload_opt(loom_b200_ctx* ctx, const float* host, size_t n, float** dev) {
+    *dev = nullptr;
+    if (!host || n == 0) return 0;
+    LB_CUDA(ctx, cudaMalloc(dev, n * sizeof(float)));
+    LB_CUDA(ctx, cudaMemcpyAsync(*dev, host, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int loom_b200_dense_forward(loom_b200_ctx* ctx, const loom_b200_weight* w, int activation, const float* in_host,
+                            int batch, float* pre_host, float* post_host) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "dense_forward: ctx is NULL");
+    LB_REQUIRE(ctx, w != nullptr, "dense_forward: weight is NULL");
+    LB_REQUIRE(ctx, batch >= 0, "dense_forward: batch=%d", batch);
+    if (batch == 0) return 0;
+    LB_REQUIRE(ctx, in_host && (pre_host || post_host), "dense_forward: NULL buffer");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "dense_forward takes host buffers and cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    const int K = w->cols, N = w->rows;
+    size_t need = align256((size_t)batch * K * 4) + 2 * align256((size_t)batch * N * 4) + 1024;
+    if (int rc = lb_ensure_scratch(ctx, need)) return rc;
+    Arena ar(ctx->scratch);
+    float* x = ar.take<float>((size_t)batch * K);
+    float* pre = ar.take<float>((size_t)batch * N);
+    float* post = ar.take<float>((size_t)batch * N);
+    LB_CUDA(ctx, cudaMemcpyAsync(x, in_host, (size_t)batch * K * 4, cudaMemcpyHostToDevice, ctx->stream));
+    for (int b0 = 0; b0 < batch; b0 += kChunkTokens) {
+        LbGemvParams p = {};
+        p.nseg = 1;
+        fill_seg(p.seg[0], w, nullptr, post + (size_t)b0 * N);
+        p.seg[0].pre_out = pre + (size_t)b0 * N;
+        p.seg[0].kind = LB_OUT_F32;
+        p.K = K;
+        p.M = batch - b0 < kChunkTokens ? batch - b0 : kChunkTokens;
+        p.pro = LB_PRO_F32;
+        p.x = x + (size_t)b0 * K;
+        p.epi = LB_EPI_GENERIC;
+        p.act = activation;
+        if (int rc = lb_gemv_finalize_params(ctx, p)) return rc;
+        if (int rc = lb_launch_gemv(ctx, p)) return rc;
+    }
+    if (pre_host) LB_CUDA(ctx, cudaMemcpyAsync(pre_host, pre, (size_t)batch * N * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (post_host) LB_CUDA(ctx, cudaMemcpyAsync(post_host, post, (size_t)batch * N * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+int loom_b200_swiglu_forward(loom_b200_ctx* ctx, const loom_b200_weight* gate, const loom_b200_weight* up,
+                             const loom_b200_weight* down, const float* bias_gate, const float* bias_up,
+                             const float* bias_down, const float* inner_norm_w, int inner_norm_len, double rms_eps,
+                             int activation, const float* in_host, int seq, float* pre_host, float* post_host) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "swiglu_forward: ctx is NULL");
+    LB_REQUIRE(ctx, gate && up && down, "swiglu_forward: weight is NULL");
+    LB_REQUIRE(ctx, seq >= 0, "swiglu_forward: seq=%d", seq);
+    if (seq == 0) return 0;
+    LB_REQUIRE(ctx, in_host && (pre_host || post_host), "swiglu_forward: NULL buffer");
+    LB_REQUIRE(ctx, inner_norm_len >= 0 && (inner_norm_w || inner_norm_len == 0), "swiglu_forward: inner norm length without weights");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "swiglu_forward takes host buffers and cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    const int H = gate->cols, I = gate->rows;
+    size_t need = 2 * align256((size_t)seq * H * 4) + 2 * align256((size_t)seq * I * 4) + 3 * align256((size_t)I * 4) +
+                  align256((size_t)H * 4) + 4096;
+    if (int rc = lb_ensure_scratch(ctx, need)) return rc;
+    Arena ar(ctx->scratch);
+    float* x = ar.take<float>((size_t)seq * H);
+    float* out = ar.take<float>((size_t)seq * H);
+    float* prod = ar.take<float>((size_t)seq * I);
+    float* pre = ar.take<float>((size_t)seq * I);
+    float* bg = bias_gate ? ar.take<float>(I) : nullptr;
+    float* bu = bias_up ? ar.take<float>(I) : nullptr;
+    float* iw = inner_norm_len > 0 ? ar.take<float>(inner_norm_len) : nullptr;
+    float* bd = bias_down ? ar.take<float>(H) : nullptr;
+    auto h2d = [&](float* d, const float* h, size_t n) {
+        return d ? cudaMemcpyAsync(d, h, n * 4, cudaMemcpyHostToDevice, ctx->stream) : cudaSuccess;
+    };
+    LB_CUDA(ctx, h2d(x, in_host, (size_t)seq * H));
+    LB_CUDA(ctx, h2d(bg, bias_gate, I));
+    LB_CUDA(ctx, h2d(bu, bias_up, I));
+    LB_CUDA(ctx, h2d(bd, bias_down, H));
+    LB_CUDA(ctx, h2d(iw, inner_norm_w, inner_norm_len));
+    for (int s0 = 0; s0 < seq; s0 += kChunkTokens) {
+        LbSwigluArgs a = {};
+        a.gate = gate;
+        a.up = up;
+        a.down = down;
+        a.bias_gate = bg;
+        a.bias_up = bu;
+        a.bias_down = bd;
+        a.inner_w = iw;
+        a.inner_w_len = inner_norm_len;
+        a.inner_eps = rms_eps;
+        a.act = activation;
+        a.pro_mode = LB_PRO_F32;
+        a.x = x + (size_t)s0 * H;
+        a.prod = prod + (size_t)s0 * I;
+        a.pre_out = pre + (size_t)s0 * I;
+        a.out = out + (size_t)s0 * H;
+        a.M = seq - s0 < kChunkTokens ? seq - s0 : kChunkTokens;
+        if (int rc = lb_swiglu_dev(ctx, a)) return rc;
+    }
+    if (pre_host) LB_CUDA(ctx, cudaMemcpyAsync(pre_host, pre, (size_t)seq * I * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (post_host) LB_CUDA(ctx, cudaMemcpyAsync(post_host, out, (size_t)seq * H * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+int loom_b200_mha_create(loom_b200_ctx* ctx, int d_model, int num_heads, int num_kv_heads, int head_dim,
+                         int max_seq_len, double rope_theta, double rms_eps, const loom_b200_weight* wq,
+                         const loom_b200_weight* wk, const loom_b200_weight* wv, const loom_b200_weight* wo,
+                         const float* bq, const float* bk, const float* bv, const float* bo, const float* q_norm_w,
+                         int q_norm_len, const float* k_norm_w, int k_norm_len, const float* inner_norm_w,
+                         int inner_norm_len, loom_b200_mha** out) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "mha_create: ctx is NULL");
+    LB_REQUIRE(ctx, out != nullptr, "mha_create: out is NULL");
+    *out = nullptr;
+    LB_REQUIRE(ctx, wq && wk && wv && wo, "mha_create: weight is NULL");
+    LB_REQUIRE(ctx, d_model > 0 && num_heads > 0 && head_dim > 0 && head_dim % 4 == 0, "mha_create: bad dimensions");
+    if (num_kv_heads == 0) num_kv_heads = num_heads;
+    LB_REQUIRE(ctx, num_heads % num_kv_heads == 0, "mha_create: %d heads over %d kv heads", num_heads, num_kv_heads);
+    const int qd = num_heads * head_dim, kvd = num_kv_heads * head_dim;
+    LB_REQUIRE(ctx, wq->rows == qd && wq->cols == d_model && wk->rows == kvd && wk->cols == d_model &&
+                        wv->rows == kvd && wv->cols == d_model && wo->rows == d_model && wo->cols == qd,
+               "mha_create: projection shapes do not match the layer dimensions");
+    LB_REQUIRE(ctx, qd == d_model, "mha_create: query width %d != d_model %d is not supported", qd, d_model);
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "mha_create cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    auto* m = new loom_b200_mha();
+    m->d_model = d_model;
+    m->heads = num_heads;
+    m->kv_heads = num_kv_heads;
+    m->head_dim = head_dim;
+    m->q_dim = qd;
+    m->kv_dim = kvd;
+    m->msl = max_seq_len == 0 ? 512 : max_seq_len;  // poly/mha.go:217-220
+    m->theta = rope_theta > 0 ? rope_theta : 10000.0;
+    m->rms_eps = rms_eps;
+    m->wq = wq;
+    m->wk = wk;
+    m->wv = wv;
+    m->wo = wo;
+    m->q_norm_len = q_norm_w ? q_norm_len : 0;
+    m->k_norm_len = k_norm_w ? k_norm_len : 0;
+    m->inner_len = inner_norm_w ? inner_norm_len : 0;
+    int rc = lb_mha_alloc(ctx, m, 16);
+    if (!rc) rc = upload_opt(ctx, bq, qd, &m->bq);
+    if (!rc) rc = upload_opt(ctx, bk, kvd, &m->bk);
+    if (!rc) rc = upload_opt(ctx, bv, kvd, &m->bv);
+    if (!rc) rc = upload_opt(ctx, bo, d_model, &m->bo);
+    if (!rc) rc = upload_opt(ctx, q_norm_w, m->q_norm_len, &m->q_norm);
+    if (!rc) rc = upload_opt(ctx, k_norm_w, m->k_norm_len, &m->k_norm);
+    if (!rc) rc = upload_opt(ctx, inner_norm_w, m->inner_len, &m->inner);
+    if (rc) {
+        lb_mha_release(m);
+        delete m;
+        return rc;
+    }
+    *out = m;
+    return 0;
+}
+
+void loom_b200_mha_destroy(loom_b200_mha* m) {
+    if (!m) return;
+    if (m->ctx) {
+        cudaSetDevice(m->ctx->device);
+        cudaStreamSynchronize(m->ctx->stream);
+    }
+    lb_mha_release(m);
+    delete m;
+}
+
+int loom_b200_mha_reset(loom_b200_mha* m) {
+    if (!m) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "mha_reset: layer is NULL");
+    m->kv_offset = 0;
+    return 0;
+}
+
+int loom_b200_mha_kv_offset(const loom_b200_mha* m) { return m ? m->kv_offset : -1; }
+
+int loom_b200_mha_forward(loom_b200_mha* m, const float* in_host, int batch, int seq, float* pre_host, float* post_host) {
+    if (!m) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "mha_forward: layer is NULL");
+    loom_b200_ctx* ctx = m->ctx;
+    LB_REQUIRE(ctx, batch > 0 && seq > 0, "mha_forward: batch=%d seq=%d", batch, seq);
+    LB_REQUIRE(ctx, in_host && (pre_host || post_host), "mha_forward: NULL buffer");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "mha_forward takes host buffers and cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    // mhaPrepareKVForForward, poly/mha_layout.go:62-70: the ring keeps its contents only for a one-token step
+    const bool incremental = batch == 1 && seq == 1 && m->cache_live && m->kv_offset > 0;
+    if (!incremental) {
+        const size_t cache = (size_t)m->msl * m->kv_dim * sizeof(float);
+        LB_CUDA(ctx, cudaMemsetAsync(m->cache_k, 0, cache, ctx->stream));
+        LB_CUDA(ctx, cudaMemsetAsync(m->cache_v, 0, cache, ctx->stream));
+        m->cache_live = true;
+        m->kv_offset = 0;
+    }
+    const int total = batch * seq, D = m->d_model;
+    LB_REQUIRE(ctx, m->kv_offset + total <= m->msl, "mha_forward: %d positions exceed MaxSeqLen %d (the reference's ring would wrap)", m->kv_offset + total, m->msl);
+    size_t need = 3 * align256((size_t)total * D * 4) + 1024;
+    if (int rc = lb_ensure_scratch(ctx, need)) return rc;
+    Arena ar(ctx->scratch);
+    float* x = ar.take<float>((size_t)total * D);
+    float* pre = ar.take<float>((size_t)total * D);
+    float* post = ar.take<float>((size_t)total * D);
+    LB_CUDA(ctx, cudaMemcpyAsync(x, in_host, (size_t)total * D * 4, cudaMemcpyHostToDevice, ctx->stream));
+    LB_CUDA(ctx, cudaMemcpyAsync(m->pos_dev, &m->kv_offset, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int s0 = 0; s0 < total; s0 += kChunkTokens) {
+        LbMhaStepArgs a = {};
+        a.pro_mode = LB_PRO_F32;
+        a.x = x + (size_t)s0 * D;
+        a.pre_out = pre + (size_t)s0 * D;
+        a.out = post + (size_t)s0 * D;
+        a.M = total - s0 < kChunkTokens ? total - s0 : kChunkTokens;
+        a.splits = a.M == 1 ? 8 : 1;
+        if (int rc = lb_mha_step_dev(m, a)) return rc;
+        if (int rc = lb_launch_add_scalar(ctx, m->pos_dev, a.M)) return rc;
+    }
+    m->kv_offset += total;
+    if (pre_host) LB_CUDA(ctx, cudaMemcpyAsync(pre_host, pre, (size_t)total * D * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (post_host) LB_CUDA(ctx, cudaMemcpyAsync(post_host, post, (size_t)total * D * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+int loom_b200_mha_download_cache(loom_b200_mha* m, float* k_host, float* v_host) {
+    if (!m) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "mha_download_cache: layer is NULL");
+    loom_b200_ctx* ctx = m->ctx;
+    if (int rc = lb_set_device(ctx)) return rc;
+    const size_t cache = (size_t)m->msl * m->kv_dim * sizeof(float);
+    if (k_host) LB_CUDA(ctx, cudaMemcpyAsync(k_host, m->cache_k, cache, cudaMemcpyDeviceToHost, ctx->stream));
+    if (v_host) LB_CUDA(ctx, cudaMemcpyAsync(v_host, m->cache_v, cache, cudaMemcpyDeviceToHost, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+}  // extern "C"

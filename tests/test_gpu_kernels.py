@@ -123,11 +123,12 @@ def test_quantize_ties_round_away(ctx):
         ctx.free(p)
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant,part", [(0, 1), (0, 2), (1, 1), (1, 2)])
 @pytest.mark.parametrize("rows,cols", SWEEP)
-def test_linear_reference_sweep_bit_exact(ctx, rows, cols, variant):
+def test_linear_reference_sweep_bit_exact(ctx, rows, cols, variant, part):
     # the reference's SIMD-vs-scalar sweep, batch 2, difference must be exactly 0
     ctx.set_option("gemv_variant", variant)
+    ctx.set_option("gemv_partition", part)
     m = orc.Matrix.from_f32(deterministic_weights(rows * cols), rows, cols)
     x = deterministic_weights(2 * cols).reshape(2, cols)
     xq, amax = orc.quantize_rows_f32(x)
@@ -135,15 +136,17 @@ def test_linear_reference_sweep_bit_exact(ctx, rows, cols, variant):
     out, acc = gpu_linear(ctx, w, xq, amax, 2)
     eo, ea = oracle_linear(m, xq, amax)
     ctx.set_option("gemv_variant", 0)
+    ctx.set_option("gemv_partition", 0)
     assert (acc == ea).all()
     assert (out.view(np.uint32) == eo.view(np.uint32)).all()
 
 
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 @pytest.mark.parametrize("rows,cols,batch", [(6912, 2560, 1), (2560, 6912, 1), (6912, 2560, 5), (2560, 6912, 19),
                                              (3840, 2560, 8), (1000, 300, 3)])
 def test_linear_benchmark_shapes_bit_exact(ctx, rows, cols, batch, variant):
-    ctx.set_option("gemv_variant", variant)
+    ctx.set_option("gemv_variant", variant & 1)
+    ctx.set_option("gemv_partition", 1 + (variant >> 1))
     rng = np.random.default_rng(rows + cols + batch)
     master = (rng.standard_normal(rows * cols) * 0.02).astype(np.float32)
     m = orc.Matrix.from_f32(master, rows, cols)
@@ -159,6 +162,7 @@ def test_linear_benchmark_shapes_bit_exact(ctx, rows, cols, batch, variant):
         assert (acc == ea).all()
         assert (out.view(np.uint32) == eo.view(np.uint32)).all(), kw
     ctx.set_option("gemv_variant", 0)
+    ctx.set_option("gemv_partition", 0)
 
 
 def test_linear_extreme_activations(ctx):
@@ -188,10 +192,12 @@ def test_linear_repeat_is_stable(ctx):
     first, _ = gpu_linear(ctx, w, xq, amax, 1)
     for grid in (1, 2, 3):
         ctx.set_option("gemv_ctas_per_sm", grid)
-        for pdl in (0, 1):
-            ctx.set_option("pdl", pdl)
-            again, _ = gpu_linear(ctx, w, xq, amax, 1)
-            assert (again.view(np.uint32) == first.view(np.uint32)).all()
+        for part in (1, 2, 0):
+            ctx.set_option("gemv_partition", part)
+            for pdl in (0, 1):
+                ctx.set_option("pdl", pdl)
+                again, _ = gpu_linear(ctx, w, xq, amax, 1)
+                assert (again.view(np.uint32) == first.view(np.uint32)).all()
     ctx.set_option("gemv_ctas_per_sm", 2)
     ctx.set_option("pdl", 1)
 
