@@ -245,6 +245,8 @@ int loom_b200_decoder_kv_offset(const loom_b200_decoder* dec);
 int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int n, float* logits_host);
 /* the last token's hidden row after the final RMSNorm [hidden] */
 int loom_b200_decoder_last_hidden(loom_b200_decoder* dec, float* hidden_host);
+/* copies block's KV ring [max_seq_len, kv_heads*head_dim] to the host (layer.KVCacheK / KVCacheV) */
+int loom_b200_decoder_download_cache(loom_b200_decoder* dec, int block, float* k_host, float* v_host);
 /* Transformer.Generate with deterministic (greedy) sampling: prefill the prompt, then max_new times
  * {first-maximum token, forward it}.  The loop runs on the device; tokens come back once at the end. */
 int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, int n_prompt, int max_new,

@@ -83,6 +83,7 @@ SIGNATURES = {
     "loom_b200_decoder_kv_offset": (_i, [_vp]),
     "loom_b200_decoder_forward": (_i, [_vp, _vp, _i, _vp]),
     "loom_b200_decoder_last_hidden": (_i, [_vp, _vp]),
+    "loom_b200_decoder_download_cache": (_i, [_vp, _i, _vp, _vp]),
     "loom_b200_decoder_generate": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
 }
 
@@ -417,6 +418,13 @@ class Decoder:
         out = np.empty(self.dims.hidden, np.float32)
         self.ctx._check(lib().loom_b200_decoder_last_hidden(self.h, out.ctypes.data))
         return out
+
+    def cache(self, block: int):
+        kvd = self.dims.num_kv_heads * self.dims.head_dim
+        k = np.empty((self.dims.max_seq_len, kvd), np.float32)
+        v = np.empty((self.dims.max_seq_len, kvd), np.float32)
+        self.ctx._check(lib().loom_b200_decoder_download_cache(self.h, block, k.ctypes.data, v.ctypes.data))
+        return k, v
 
     def generate(self, prompt, max_new):
         prompt = np.ascontiguousarray(prompt, np.int32).ravel()

@@ -327,6 +327,13 @@ int loom_b200_decoder_last_hidden(loom_b200_decoder* dec, float* hidden_host) {
     return 0;
 }
 
+int loom_b200_decoder_download_cache(loom_b200_decoder* dec, int block, float* k_host, float* v_host) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_download_cache: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, block >= 0 && block < (int)dec->blocks.size() && dec->blocks[block].ready, "decoder_download_cache: block %d is not set", block);
+    return loom_b200_mha_download_cache(&dec->blocks[block].mha, k_host, v_host);
+}
+
 int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, int n_prompt, int max_new,
                                int32_t* out_tokens, loom_b200_gen_metrics* metrics) {
     if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_generate: decoder is NULL");

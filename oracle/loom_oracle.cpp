@@ -622,6 +622,15 @@ orc_mha* orc_mha_create(int d_model, int num_heads, int num_kv_heads, int head_d
 void orc_mha_free(orc_mha* l) { delete l; }
 void orc_mha_reset(orc_mha* l) { l->kv_offset = 0; }
 int orc_mha_kv_offset(const orc_mha* l) { return l->kv_offset; }
+int orc_mha_set_state(orc_mha* l, int kv_offset, const float* k, const float* v) {
+    if (!l || kv_offset < 0 || kv_offset > l->msl || !k || !v) return -1;
+    size_t n = (size_t)l->msl * l->kv_dim;
+    l->cache_k.assign(k, k + n);
+    l->cache_v.assign(v, v + n);
+    l->cache_live = true;
+    l->kv_offset = kv_offset;
+    return 0;
+}
 const float* orc_mha_cache_k(const orc_mha* l) { return l->cache_k.data(); }
 const float* orc_mha_cache_v(const orc_mha* l) { return l->cache_v.data(); }
 
@@ -865,6 +874,11 @@ int orc_decoder_set_embeddings(orc_decoder* d, const float* emb, const float* fi
     d->final_gain.assign(d->hidden, 1.0f);
     if (final_gain) d->final_gain.assign(final_gain, final_gain + d->hidden);
     return 0;
+}
+
+int orc_decoder_set_kv(orc_decoder* d, int block, int kv_offset, const float* k, const float* v) {
+    if (!d || block < 0 || block >= d->layers || !d->blocks[block].mha) return -1;
+    return orc_mha_set_state(d->blocks[block].mha, kv_offset, k, v);
 }
 
 void orc_decoder_reset(orc_decoder* d) {

@@ -124,6 +124,9 @@ orc_mha* orc_mha_create(int d_model, int num_heads, int num_kv_heads, int head_d
 void orc_mha_free(orc_mha* l);
 void orc_mha_reset(orc_mha* l); /* Transformer.Reset: KVOffset = 0, poly/transformer.go:119-127 */
 int orc_mha_kv_offset(const orc_mha* l);
+/* installs a KV ring state (layer.KVCacheK/V + KVOffset) so that a decode step can be timed or checked at a
+ * given context length without replaying the prompt; k, v are [max_seq_len, kvDim] */
+int orc_mha_set_state(orc_mha* l, int kv_offset, const float* k, const float* v);
 const float* orc_mha_cache_k(const orc_mha* l); /* [max_seq_len, kvDim] */
 const float* orc_mha_cache_v(const orc_mha* l);
 /* in [batch,seq,dModel].  pre (normalised attention rows) and post [batch,seq,dModel].  Optional taps:
@@ -153,6 +156,8 @@ int orc_decoder_set_block_packed(orc_decoder* d, int block, const float* norm1_g
 /* tied fp32 embedding / LM head [vocab,hidden] (borrowed pointer: must outlive the decoder) and final gain */
 int orc_decoder_set_embeddings(orc_decoder* d, const float* emb, const float* final_gain);
 void orc_decoder_reset(orc_decoder* d);
+/* orc_mha_set_state on one block */
+int orc_decoder_set_kv(orc_decoder* d, int block, int kv_offset, const float* k, const float* v);
 /* forwardOnCPUNormal over n tokens (poly/transformer_forward.go:220-253) then ApplyLMHead on the last row
  * (poly/transformer.go:635-719).  hidden_out [n,hidden] and logits_out [vocab] may be NULL. */
 int orc_decoder_forward(orc_decoder* d, const int32_t* tokens, int n, float* hidden_out, float* logits_out,
