@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 BitNet ternary x int8 linear path: batch-1 greedy decode of a BitNet-b1.58-2B-shaped
+ternary decoder (30 blocks, hidden 2560, FFN 6912, 20 query / 5 KV heads x 128, vocab 128256, fp32 tied head).
+
+A step is one decode token.  Weights are synthetic (seeded N(0, 0.02) masters ternarised per matrix by absmean
+on the device); the prompt is seeded uniform token ids.  One JSON line is printed by rank 0.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--prompt P] [--layers L]
+
+N > 1: the 2B shape has 5 KV heads, which no tensor-parallel degree above 1 divides, so every rank runs an
+independent replica ("replicas only", weak scaling) and the value is the sum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPE = dict(layers=30, hidden=2560, heads=20, kv_heads=5, head_dim=128, inter=6912, vocab=128256, eps=1e-5,
+             theta=500000.0, max_seq_len=2048)
+METRIC = "decode tok/s (BitNet-2B shape, bs=1); ternary-linear HBM GB/s vs peak"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def algorithmic_bytes(shape, ctx_len):
+    """Bytes one decode token has to move: packed weights once, int8 activations, fp32/fp64 vectors, KV, head."""
+    H, I, qd, kvd = shape["hidden"], shape["inter"], shape["heads"] * shape["head_dim"], shape["kv_heads"] * shape["head_dim"]
+
+    def lin(rows, cols):  # packed words + int8 activations + fp32 outputs
+        return rows * ((cols + 15) // 16) * 4 + cols + rows * 4
+
+    per_block = lin(qd, H) + 2 * lin(kvd, H) + lin(H, qd) + 2 * lin(I, H) + lin(H, I)
+    ternary = shape["layers"] * per_block
+    kv = shape["layers"] * 2 * ctx_len * kvd * 4
+    head = shape["vocab"] * H * 4 + shape["vocab"] * 4
+    return ternary, kv, head
+
+
+def build_model(ctx, torch, shape, seed):
+    from loom_b200 import cabi
+    dev = torch.device("cuda", ctx.device)
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    H, I, hd = shape["hidden"], shape["inter"], shape["head_dim"]
+    qd, kvd = shape["heads"] * hd, shape["kv_heads"] * hd
+    dims = ((qd, H), (kvd, H), (kvd, H), (H, qd), (I, H), (I, H), (H, I))
+    dec = cabi.Decoder(ctx, shape["layers"], H, shape["heads"], shape["kv_heads"], hd, I, shape["vocab"], shape["eps"],
+                       shape["theta"], cabi.ACT_SILU, shape["max_seq_len"])
+    weights = []
+    for b in range(shape["layers"]):
+        ws = []
+        for r, c in dims:
+            master = torch.randn(r * c, device=dev, generator=g, dtype=torch.float32) * 0.02
+            ws.append(ctx.pack_ternary_f32(master, r, c))
+            del master
+        dec.set_block(b, ws)
+        weights.append(ws)
+    emb = torch.randn(shape["vocab"], H, device=dev, generator=g, dtype=torch.float32) * 0.02
+    dec.set_embeddings(emb)
+    return dec, weights, emb
+
+
+def gemv_roofline(ctx, torch, weights, shape, reps=20):
+    """Average launch duration of the ternary GEMV over every block's gate and down matrix (60 distinct
+    matrices of 4.4 MB, more than L2), replayed as one recorded frame; CUDA events on the launching stream."""
+    dev = torch.device("cuda", ctx.device)
+    H, I = shape["hidden"], shape["inter"]
+    xg = torch.randn(1, H, device=dev)
+    xd = torch.randn(1, I, device=dev)
+    qg, ag = torch.empty(1, H, dtype=torch.int8, device=dev), torch.empty(1, device=dev)
+    qd_, ad = torch.empty(1, I, dtype=torch.int8, device=dev), torch.empty(1, device=dev)
+    ctx.quantize_activation(1, H, xg, qg, ag)
+    ctx.quantize_activation(1, I, xd, qd_, ad)
+    og, od = torch.empty(1, I, device=dev), torch.empty(1, H, device=dev)
+
+    def run():
+        for ws in weights:
+            ctx.ternary_linear(ws[4], 1, qg, ag, og)
+            ctx.ternary_linear(ws[6], 1, qd_, ad, od)
+
+    run()
+    ctx.sync()
+    ctx.graph_begin()
+    run()
+    gr = ctx.graph_end()
+    for _ in range(3):
+        ctx.graph_launch(gr)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        ctx.graph_launch(gr)
+    e1.record()
+    torch.cuda.synchronize()
+    launches = reps * 2 * len(weights)
+    us = e0.elapsed_time(e1) * 1e3 / launches
+    ctx.graph_free(gr)
+    bytes_gate = I * ((H + 15) // 16) * 4 + H + I * 4
+    bytes_down = H * ((I + 15) // 16) * 4 + I + H * 4
+    per_launch = 0.5 * (bytes_gate + bytes_down)
+    return per_launch, us, launches
+
+
+def cpu_sample(dec, weights, emb_host, shape, ctx_len, token, sample_blocks, tokens, threads):
+    """Times the CPU oracle (restatement of the reference's Go path, AVX2 byte-code kernel, `threads` workers) on
+    a bounded sample: `sample_blocks` full-width blocks at the same context length plus the full fp32 head."""
+    from oracle import oracle as orc
+    s = dict(shape)
+    odec = orc.Decoder(sample_blocks, s["hidden"], s["heads"], s["kv_heads"], s["head_dim"], s["inter"], s["vocab"],
+                       s["eps"], s["theta"], orc.ACT_SILU, s["max_seq_len"])
+    for b in range(sample_blocks):
+        words = [w.words() for w in weights[b]]
+        scales = [w.scale for w in weights[b]]
+        odec.set_block_packed(b, words, scales)
+        k, v = dec.cache(b)
+        odec.set_kv(b, ctx_len, k, v)
+    odec.set_embeddings(emb_host)
+    tok = np.array([token], np.int32)
+    odec.forward(tok, simd=1, threads=threads)  # builds the byte-code caches; not timed (as the reference's bench)
+    t_blocks = []
+    for _ in range(tokens):
+        t0 = time.perf_counter()
+        _, hid = odec.forward(tok, simd=1, threads=threads, want_hidden=True)
+        t_blocks.append(time.perf_counter() - t0)
+    # forward() above includes the head; time the head alone to separate the two
+    t_head = []
+    for _ in range(tokens):
+        t0 = time.perf_counter()
+        orc.lm_head(hid[-1], emb_host, threads=threads)
+        t_head.append(time.perf_counter() - t0)
+    th = float(np.median(t_head))
+    tb = max(float(np.median(t_blocks)) - th, 1e-9)
+    per_token = tb * (shape["layers"] / sample_blocks) + th
+    return 1.0 / per_token, tb, th
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=SHAPE["layers"])
+    ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    shape = dict(SHAPE, layers=args.layers)
+
+    if args.impl == "reference" and rank != 0:
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    import loom_b200
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1 and args.impl == "ours":
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    tstream = torch.cuda.Stream()
+    torch.cuda.set_stream(tstream)
+    ctx = loom_b200.Context(local, tstream.cuda_stream)
+
+    dec, weights, emb = build_model(ctx, torch, shape, args.seed)
+    rng = np.random.default_rng(args.seed)
+    prompt = rng.integers(0, shape["vocab"], args.prompt).astype(np.int32)
+    assert args.prompt + args.warmup + 2 * args.steps + 8 <= shape["max_seq_len"], "prompt + steps exceed MaxSeqLen"
+
+    # prefill + warm-up tokens (untimed); the decode frame is recorded during warm-up
+    t0 = time.perf_counter()
+    _, m0 = dec.generate(prompt, args.warmup)
+    prefill_s = m0.prefill_seconds
+    ctx_len = args.prompt + args.warmup
+    logits = dec.forward(np.array([int(prompt[0])], np.int32))  # one more step through the host path (warm)
+    ctx_len += 1
+    peak, peak_kind = measured_peaks()
+
+    if args.impl == "reference":
+        from oracle import oracle as orc
+        threads = orc.host_threads()
+        emb_host = emb.cpu().numpy()
+        sample_blocks = 2
+        tokps, tb, th = cpu_sample(dec, weights, emb_host, shape, ctx_len, int(np.argmax(logits)), sample_blocks,
+                                   max(args.steps // 16, 3), threads)
+        line = {"impl": "reference", "metric": METRIC, "value": tokps, "unit": "tok/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / tokps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic",
+                "config": {"workload": "BitNet-b1.58-2B-shape ternary decoder, batch-1 greedy decode", "prompt": args.prompt,
+                           "context": ctx_len},
+                "cpu_baseline": {"value": tokps, "unit": "tok/s", "cores": threads, "kind": "port",
+                                 "sample": "%d of %d blocks at full width (AVX2 byte-code kernel) at context %d + the full "
+                                           "fp32 head; blocks x%g, head x1" % (sample_blocks, shape["layers"], ctx_len,
+                                                                              shape["layers"] / sample_blocks)},
+                "e2e": {"value": tokps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return 0
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timed region: K decode steps, frame replay, no host round trip ---------------------
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    # the greedy loop continues from the current logits: K x {argmax, forward}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    dec.continue_greedy(args.steps)
+    e1.record()
+    barrier()
+    dev_s = e0.elapsed_time(e1) * 1e-3
+    clocks = sampler.stop()
+    ctx_mid = ctx_len + args.steps // 2
+    ctx_len += args.steps
+    if world > 1:
+        t = torch.tensor([dev_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_s = float(t.item())
+    value = world * args.steps / dev_s
+
+    # ---- end to end through the host-facing call: token id in (pinned H2D), logits out (D2H), host argmax -------
+    tok = int(np.argmax(logits))
+    for _ in range(3):
+        logits = dec.forward(np.array([tok], np.int32))
+        tok = int(np.argmax(logits))
+    ctx_len += 3
+    e2e_steps = min(args.steps, shape["max_seq_len"] - ctx_len - 1)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        logits = dec.forward(np.array([tok], np.int32))
+        tok = int(np.argmax(logits))
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = world * e2e_steps / e2e_s
+
+    tern_b, kv_b, head_b = algorithmic_bytes(shape, ctx_mid)
+    per_launch, gemv_us, gemv_launches = gemv_roofline(ctx, torch, weights, shape)
+    achieved = per_launch / gemv_us / 1e3  # GB/s
+    launches_per_token = shape["layers"] * 6 + 4  # 6 per block + embed + head + position + argmax
+    line = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * dev_s / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic",
+        "config": {"workload": "BitNet-b1.58-2B-shape ternary decoder, batch-1 greedy decode (configs[2])",
+                   "layers": shape["layers"], "prompt": args.prompt, "context_mid": ctx_mid,
+                   "parallelism": "replicas only" if world > 1 else "single GPU",
+                   "l2": "every step streams 0.5 GB of packed weights + 1.3 GB fp32 head, far beyond the 126 MB L2"},
+        "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": shape["vocab"] * 4,
+                "steps": e2e_steps},
+        "gpu_launches": args.steps * launches_per_token,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "lb_gemv_ternary_kernel (gate 6912x2560 and down "
+                     "2560x6912, batch 1, 60 distinct matrices per replay)", "bytes_per_launch": per_launch,
+                     "us_per_launch": gemv_us, "launches_timed": gemv_launches},
+        "decode_bytes": {"ternary": tern_b, "kv": kv_b, "fp32_head": head_b,
+                         "gbs_all": (tern_b + kv_b + head_b) / (dev_s / args.steps) / 1e9,
+                         "frac_of_peak": (tern_b + kv_b + head_b) / (dev_s / args.steps) / 1e9 / peak},
+        "prefill": {"tokens": args.prompt, "seconds": prefill_s, "tok_per_s": args.prompt / prefill_s},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            from oracle import oracle as orc
+            threads = orc.host_threads()
+            emb_host = emb.cpu().numpy()
+            tokps, tb, th = cpu_sample(dec, weights, emb_host, shape, min(ctx_len, shape["max_seq_len"] - 2), tok, 2, 3, threads)
+            line["cpu_baseline"] = {"value": tokps, "unit": "tok/s", "cores": threads, "kind": "port",
+                                    "sample": "2 of %d blocks at full width (AVX2 byte-code kernel, %d threads) at context "
+                                              "%d + the full fp32 head, 3 tokens; blocks x%g, head x1" %
+                                              (shape["layers"], threads, ctx_len, shape["layers"] / 2)}
+        except Exception as exc:  # the baseline is reported, never required for the GPU number
+            line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": "failed: %r" % (exc,)}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -245,6 +245,10 @@ int loom_b200_decoder_kv_offset(const loom_b200_decoder* dec);
 int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int n, float* logits_host);
 /* the last token's hidden row after the final RMSNorm [hidden] */
 int loom_b200_decoder_last_hidden(loom_b200_decoder* dec, float* hidden_host);
+/* Continues the greedy loop for `steps` more tokens from the logits of the last forward, entirely on the
+ * device and without waiting for it (call loom_b200_sync to wait).  The body of Generate's loop,
+ * poly/transformer.go:434-485. */
+int loom_b200_decoder_continue(loom_b200_decoder* dec, int steps);
 /* copies block's KV ring [max_seq_len, kv_heads*head_dim] to the host (layer.KVCacheK / KVCacheV) */
 int loom_b200_decoder_download_cache(loom_b200_decoder* dec, int block, float* k_host, float* v_host);
 /* Transformer.Generate with deterministic (greedy) sampling: prefill the prompt, then max_new times

@@ -83,6 +83,7 @@ SIGNATURES = {
     "loom_b200_decoder_kv_offset": (_i, [_vp]),
     "loom_b200_decoder_forward": (_i, [_vp, _vp, _i, _vp]),
     "loom_b200_decoder_last_hidden": (_i, [_vp, _vp]),
+    "loom_b200_decoder_continue": (_i, [_vp, _i]),
     "loom_b200_decoder_download_cache": (_i, [_vp, _i, _vp, _vp]),
     "loom_b200_decoder_generate": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
 }
@@ -418,6 +419,10 @@ class Decoder:
         out = np.empty(self.dims.hidden, np.float32)
         self.ctx._check(lib().loom_b200_decoder_last_hidden(self.h, out.ctypes.data))
         return out
+
+    def continue_greedy(self, steps: int):
+        """`steps` more greedy tokens on the device; returns without waiting."""
+        self.ctx._check(lib().loom_b200_decoder_continue(self.h, steps))
 
     def cache(self, block: int):
         kvd = self.dims.num_kv_heads * self.dims.head_dim

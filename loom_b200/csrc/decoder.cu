@@ -327,6 +327,22 @@ int loom_b200_decoder_last_hidden(loom_b200_decoder* dec, float* hidden_host) {
     return 0;
 }
 
+int loom_b200_decoder_continue(loom_b200_decoder* dec, int steps) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_continue: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, steps >= 0, "decoder_continue: steps=%d", steps);
+    LB_REQUIRE(ctx, dec->kv_offset > 0, "decoder_continue: nothing to continue (run a prompt first)");
+    LB_REQUIRE(ctx, dec->kv_offset + steps <= dec->d.max_seq_len, "decoder_continue: %d positions exceed MaxSeqLen %d", dec->kv_offset + steps, dec->d.max_seq_len);
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_continue cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    for (int i = 0; i < steps; ++i) {
+        if (int rc = lb_launch_argmax_advance(ctx, dec->logits, dec->d.vocab, dec->tok, dec->out_tokens, dec->out_cap, dec->step, nullptr)) return rc;
+        if (int rc = dec_step(dec)) return rc;
+    }
+    dec->kv_offset += steps;
+    return 0;
+}
+
 int loom_b200_decoder_download_cache(loom_b200_decoder* dec, int block, float* k_host, float* v_host) {
     if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_download_cache: decoder is NULL");
     loom_b200_ctx* ctx = dec->ctx;
