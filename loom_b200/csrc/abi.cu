@@ -345,6 +345,7 @@ void loom_b200_ctx_destroy(loom_b200_ctx* ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->trace_dev) cudaFree(ctx->trace_dev);
+    if (ctx->argmax_scratch) cudaFree(ctx->argmax_scratch);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }

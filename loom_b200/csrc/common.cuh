@@ -56,6 +56,7 @@ struct loom_b200_ctx {
     size_t scratch_bytes = 0;
     // device status word written by kernels with bounded waits (0 = ok)
     int* status_dev = nullptr;
+    void* argmax_scratch = nullptr;  // per-CTA partial maxima of the greedy argmax
     unsigned func_attr_mask = 0;  // kernels whose shared-memory limit was raised on this device
     // tuning knobs (loom_b200_ctx_set_option; initial values from LOOM_B200_* environment variables)
     int opt_gemv_variant = 0;      // 0 = integer-MMA inner loop, 1 = dp4a inner loop (batch 1 only)
@@ -106,11 +107,29 @@ static inline int lb_set_device(loom_b200_ctx* ctx) {
 
 __device__ __forceinline__ float lb_abs_to_f32(float v) { return fabsf(v); }
 
+// Round half away from zero, exactly (Go's math.Round): trunc(x), then one step away when the discarded
+// fraction is at least one half.  x - trunc(x) is exact, so no double rounding can occur (the library
+// round() gives the same result but costs a long dependent sequence).
+__device__ __forceinline__ double lb_round_half_away(double x) {
+    const double t = trunc(x);
+    const double d = __dsub_rn(x, t);
+    return fabs(d) >= 0.5 ? __dadd_rn(t, copysign(1.0, x)) : t;
+}
+
 // bitNetQuantizedActivation: int8(clamp(Round(float64(v) * (127/float64(amax))), -128, 127))
 __device__ __forceinline__ int lb_quant_i8(double v, double s) {
-    double r = round(__dmul_rn(v, s));  // round(): half away from zero, like Go's math.Round
+    double r = lb_round_half_away(__dmul_rn(v, s));
     r = fmin(fmax(r, -128.0), 127.0);
     return (int)r;
+}
+
+// a / b with the reciprocal r = RN(1/b) computed once by the caller: q0 = RN(a*r), the exact remainder
+// e = a - b*q0 (one FMA), q1 = RN(q0 + e*r).  With a correctly rounded reciprocal this is the correctly
+// rounded quotient (Markstein), i.e. the same bits as an IEEE division, without its long latency.
+__device__ __forceinline__ double lb_div_by(double a, double b, double r) {
+    const double q0 = __dmul_rn(a, r);
+    const double e = fma(-b, q0, a);
+    return fma(e, r, q0);
 }
 
 // outputScale = float64(scale) * float64(amax) / 127, zero -> 1

@@ -36,7 +36,7 @@ struct loom_b200_decoder {
     int* h_tok = nullptr;       // pinned
     float* h_logits = nullptr;  // pinned [vocab]
     loom_b200_graph* step_graph = nullptr;
-    int decode_splits = 8;
+    int decode_splits = 16;
 };
 
 namespace {
@@ -135,6 +135,7 @@ int loom_b200_decoder_create(loom_b200_ctx* ctx, const loom_b200_decoder_dims* d
     LB_REQUIRE(ctx, d.num_layers > 0 && d.hidden > 0 && d.num_heads > 0 && d.head_dim > 0 && d.intermediate > 0 && d.vocab > 0,
                "decoder_create: bad dimensions");
     LB_REQUIRE(ctx, d.num_heads * d.head_dim == d.hidden, "decoder_create: heads*head_dim must equal hidden");
+    LB_REQUIRE(ctx, d.head_dim % 8 == 0, "decoder_create: head_dim %d must be a multiple of 8", d.head_dim);
     if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_create cannot be recorded");
     if (int rc = lb_set_device(ctx)) return rc;
     auto* dec = new loom_b200_decoder();

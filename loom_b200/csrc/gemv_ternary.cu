@@ -115,7 +115,7 @@ __device__ __forceinline__ float block_max(float v, double* red) {
 // The value the reference quantizes for column c of token row `row` (already rounded to float32 where the
 // reference stores a float32), as a double.
 template <int mode>
-__device__ __forceinline__ double pro_value(const void* row, int c, double stat, const float* nw, int nwlen) {
+__device__ __forceinline__ double pro_value(const void* row, int c, double stat, double rstat, const float* nw, int nwlen) {
     if (mode == LB_PRO_INNERNORM64) {
         double w = (nw && c < nwlen) ? (double)nw[c] : 1.0;
         return __dmul_rn(((const double*)row)[c], __dmul_rn(stat, w));
@@ -124,7 +124,7 @@ __device__ __forceinline__ double pro_value(const void* row, int c, double stat,
     if (mode == LB_PRO_F32) return (double)x;
     if (mode == LB_PRO_BLOCKNORM) {
         double g = nw ? (double)nw[c] : 1.0;
-        return (double)(float)__dmul_rn(__ddiv_rn((double)x, stat), g);
+        return (double)(float)__dmul_rn(lb_div_by((double)x, stat, rstat), g);
     }
     double w = (nw && c < nwlen) ? (double)nw[c] : 1.0;  // LB_PRO_INNERNORM
     return (double)(float)__dmul_rn(__dmul_rn((double)x, stat), w);
@@ -145,7 +145,7 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
         const void* row = q8 ? (const void*)((const int8_t*)p.x + (size_t)n * K)
                              : (PRO == LB_PRO_INNERNORM64 ? (const void*)((const double*)p.x + (size_t)n * K)
                                                             : (const void*)((const float*)p.x + (size_t)n * K));
-        double stat = 0.0;
+        double stat = 0.0, rstat = 0.0;  // rms (or 1/rms for the inner norms) and, for the block norm, RN(1/rms)
         float amax;
         if (q8) {
             amax = p.amax_in[n];
@@ -166,10 +166,11 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
                 ss = block_sum(ss, sm.red);
                 double mean = __dadd_rn(__ddiv_rn(ss, (double)K), p.eps);
                 stat = PRO == LB_PRO_BLOCKNORM ? sqrt(mean) : __ddiv_rn(1.0, sqrt(mean));
+                if (PRO == LB_PRO_BLOCKNORM) rstat = __ddiv_rn(1.0, stat);
             }
             float m = 0.0f;
             for (int c = tid; c < K; c += kThreads)
-                m = fmaxf(m, (float)fabs(pro_value<PRO>(row, c, stat, p.norm_w, p.norm_w_len)));
+                m = fmaxf(m, (float)fabs(pro_value<PRO>(row, c, stat, rstat, p.norm_w, p.norm_w_len)));
             m = block_max(m, sm.red);
             amax = m < 1e-5f ? 1e-5f : m;
         }
@@ -192,7 +193,7 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
                 for (int k = 0; k < 16; ++k) {
                     int c = c0 + k;
                     if (c < K) {
-                        double v = pro_value<PRO>(row, c, stat, p.norm_w, p.norm_w_len);
+                        double v = pro_value<PRO>(row, c, stat, rstat, p.norm_w, p.norm_w_len);
                         int q = lb_quant_i8(v, s);
                         r[k >> 2] |= (uint32_t)(q & 0xff) << (8 * (k & 3));
                         if (side) {

@@ -105,10 +105,12 @@ __global__ void lb_rope_kernel(const LbRopeParams p) {
     }
 }
 
-// One CTA per (head, token, split).  Thread j scores position k0+j (+blockDim ...), thread d (< hd) owns output
-// dimension d.  With splits > 1 the partial (max, sum, weighted V) of every split goes to scratch and the CTA
-// that arrives last combines them.
-constexpr int kAttnThreads = 128;
+// One CTA per (head, token, split).  A pair of threads scores one position (half of the head dimension each);
+// output dimension d is owned by thread d of each of G = 256/hd position groups.  With splits > 1 the partial
+// (max, sum, weighted V) of every split goes to scratch and the CTA that arrives last combines them.
+// Sums run in float64 like the reference's; their order (and the fused multiply-adds) differ from its
+// sequential loops only in the last bits of a double.
+constexpr int kAttnThreads = 256;
 
 __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttnParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -118,8 +120,10 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     lb_pdl_wait();
     const int h = blockIdx.x, n = blockIdx.y, sp = blockIdx.z, tid = threadIdx.x;
     const int hd = p.hd, kvd = p.kv_heads * hd, qd = p.heads * hd;
+    const int G = hd >= kAttnThreads ? 1 : kAttnThreads / hd;
     double* sq = reinterpret_cast<double*>(smem_raw);  // [hd]
-    double* sc = sq + hd;                               // [max_chunk]
+    double* sacc = sq + hd;                             // [G, hd]
+    double* sc = sacc + (size_t)G * hd;                 // [max_chunk]
     const int last = *p.pos_ptr + n;                    // attends to positions 0..last
     const int total = last + 1;
     const int per = (total + p.splits - 1) / p.splits;
@@ -133,20 +137,30 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     for (int d = tid; d < hd; d += kAttnThreads) sq[d] = p.q[(size_t)n * qd + (size_t)h * hd + d];
     __syncthreads();
 
+    // scores: thread pair (2j, 2j+1) handles position j, each over half of the dimensions
     double mx = -1e9;
-    for (int j = tid; j < cnt; j += kAttnThreads) {
-        const float* kr = p.cache_k + (size_t)((k0 + j) % p.msl) * kvd + (size_t)kvh * hd;
+    const int half = tid & 1, hlen = hd / 2;
+    for (int j = tid >> 1; j < ((cnt + kAttnThreads / 2 - 1) / (kAttnThreads / 2)) * (kAttnThreads / 2); j += kAttnThreads / 2) {
         double dot = 0.0;
-        for (int d = 0; d < hd; d += 4) {
-            const float4 kv = *reinterpret_cast<const float4*>(kr + d);
-            dot = __dadd_rn(dot, __dmul_rn(sq[d], (double)kv.x));
-            dot = __dadd_rn(dot, __dmul_rn(sq[d + 1], (double)kv.y));
-            dot = __dadd_rn(dot, __dmul_rn(sq[d + 2], (double)kv.z));
-            dot = __dadd_rn(dot, __dmul_rn(sq[d + 3], (double)kv.w));
+        if (j < cnt) {
+            const float* kr = p.cache_k + (size_t)((k0 + j) % p.msl) * kvd + (size_t)kvh * hd + half * hlen;
+            const double* qh = sq + half * hlen;
+            double d0 = 0.0, d1 = 0.0;
+            for (int d = 0; d < hlen; d += 4) {
+                const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+                d0 = fma(qh[d], (double)kv.x, d0);
+                d1 = fma(qh[d + 1], (double)kv.y, d1);
+                d0 = fma(qh[d + 2], (double)kv.z, d0);
+                d1 = fma(qh[d + 3], (double)kv.w, d1);
+            }
+            dot = d0 + d1;
         }
-        const double s = __dmul_rn(dot, scale);
-        sc[j] = s;
-        mx = fmax(mx, s);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        if (j < cnt) {
+            const double s = __dmul_rn(dot, scale);
+            if (half == 0) sc[j] = s;
+            mx = fmax(mx, s);
+        }
     }
     mx = block_max_d(mx, red);
     double den = 0.0;
@@ -157,20 +171,36 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     }
     den = block_sum_d(den, red);  // also orders the sc[] writes before the reads below
 
-    for (int d = tid; d < hd; d += kAttnThreads) {
-        double acc = 0.0;
-        const float* vb = p.cache_v + (size_t)kvh * hd + d;
-        for (int j = 0; j < cnt; ++j) acc = __dadd_rn(acc, __dmul_rn(sc[j], (double)vb[(size_t)((k0 + j) % p.msl) * kvd]));
-        if (p.splits == 1) {
-            p.out[(size_t)n * qd + (size_t)h * hd + d] = __ddiv_rn(acc, den);
-        } else {
-            double* part = p.part + ((size_t)(n * p.heads + h) * p.splits + sp) * (hd + 2);
-            part[2 + d] = acc;
-            if (d == 0) {
-                part[0] = mx;
-                part[1] = den;
+    // weighted V: group g takes positions g, g+G, ...
+    for (int d0 = 0; d0 < hd; d0 += kAttnThreads) {
+        const int d = d0 + (G > 1 ? tid % hd : tid), grp = G > 1 ? tid / hd : 0;
+        if (d < hd && grp < G) {
+            double a0 = 0.0, a1 = 0.0;
+            const float* vb = p.cache_v + (size_t)kvh * hd + d;
+            int j = grp;
+            for (; j + G < cnt; j += 2 * G) {
+                a0 = fma(sc[j], (double)vb[(size_t)((k0 + j) % p.msl) * kvd], a0);
+                a1 = fma(sc[j + G], (double)vb[(size_t)((k0 + j + G) % p.msl) * kvd], a1);
+            }
+            if (j < cnt) a0 = fma(sc[j], (double)vb[(size_t)((k0 + j) % p.msl) * kvd], a0);
+            sacc[(size_t)grp * hd + d] = a0 + a1;
+        }
+        __syncthreads();
+        if (d < hd && grp == 0) {
+            double acc = sacc[d];
+            for (int g = 1; g < G; ++g) acc += sacc[(size_t)g * hd + d];
+            if (p.splits == 1) {
+                p.out[(size_t)n * qd + (size_t)h * hd + d] = __ddiv_rn(acc, den);
+            } else {
+                double* part = p.part + ((size_t)(n * p.heads + h) * p.splits + sp) * (hd + 2);
+                part[2 + d] = acc;
+                if (d == 0) {
+                    part[0] = mx;
+                    part[1] = den;
+                }
             }
         }
+        __syncthreads();
     }
     if (p.splits == 1) return;
     __threadfence();
@@ -192,8 +222,8 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
             const double l = __ldcg(ps + 1);
             if (l == 0.0) continue;  // an empty split
             const double w = exp(__dsub_rn(__ldcg(ps), gm));
-            num = __dadd_rn(num, __dmul_rn(__ldcg(ps + 2 + d), w));
-            dn = __dadd_rn(dn, __dmul_rn(l, w));
+            num = fma(__ldcg(ps + 2 + d), w, num);
+            dn = fma(l, w, dn);
         }
         p.out[(size_t)n * qd + (size_t)h * hd + d] = __ddiv_rn(num, dn);
     }
@@ -219,9 +249,10 @@ __global__ void __launch_bounds__(kHeadThreads) lb_lm_head_kernel(const LbLmHead
     }
     ss = block_sum_d(ss, red);
     const double rms = sqrt(__dadd_rn(__ddiv_rn(ss, (double)H), p.eps));
+    const double rrms = __ddiv_rn(1.0, rms);
     for (int i = tid; i < H; i += kHeadThreads) {
         double g = p.gain ? (double)p.gain[i] : 1.0;
-        float y = (float)__dmul_rn(__ddiv_rn((double)p.x[i], rms), g);
+        float y = (float)__dmul_rn(lb_div_by((double)p.x[i], rms, rrms), g);
         sh[i] = (double)y;
         if (blockIdx.x == 0 && p.hidden_out) p.hidden_out[i] = y;
     }
@@ -261,29 +292,35 @@ __global__ void __launch_bounds__(kHeadThreads) lb_lm_head_kernel(const LbLmHead
     }
 }
 
-__global__ void __launch_bounds__(1024) lb_argmax_advance_kernel(const float* __restrict__ logits, int vocab, int* tok,
-                                                                 int* out_tokens, int out_cap, int* step, int* pos) {
-    __shared__ float sv[32];
-    __shared__ int si[32];
+// Greedy argmax in two levels: every CTA reduces a slice to (value, first index); the CTA that arrives last
+// reduces the per-CTA results, publishes the token and advances the cursors.
+constexpr int kArgmaxCtas = 64;
+
+__device__ __forceinline__ void argmax_merge(float& best, int& idx, float ov, int oi) {
+    if (ov > best || (ov == best && oi < idx)) {
+        best = ov;
+        idx = oi;
+    }
+}
+
+__global__ void __launch_bounds__(256) lb_argmax_advance_kernel(const float* __restrict__ logits, int vocab, int* tok,
+                                                                int* out_tokens, int out_cap, int* step, int* pos,
+                                                                float* part_val, int* part_idx, unsigned int* cnt) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ int s_last;
     lb_pdl_launch_dependents();
     lb_pdl_wait();
-    float best = logits[0];
-    int idx = 0;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        float v = logits[i];
-        if (v > best || (v == best && i < idx)) {
-            best = v;
-            idx = i;
-        }
-    }
+    const int per = (vocab + gridDim.x - 1) / gridDim.x;
+    const int lo = blockIdx.x * per, hi = min(vocab, lo + per);
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) argmax_merge(best, idx, logits[i], i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         float ov = __shfl_xor_sync(0xffffffffu, best, o);
         int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) {
-            best = ov;
-            idx = oi;
-        }
+        argmax_merge(best, idx, ov, oi);
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) {
@@ -292,11 +329,27 @@ __global__ void __launch_bounds__(1024) lb_argmax_advance_kernel(const float* __
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-            if (sv[w] > best || (sv[w] == best && si[w] < idx)) {
-                best = sv[w];
-                idx = si[w];
-            }
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) argmax_merge(best, idx, sv[w], si[w]);
+        part_val[blockIdx.x] = best;
+        part_idx[blockIdx.x] = idx;
+        __threadfence();
+        unsigned old = atomicAdd(cnt, 1u);
+        s_last = old + 1 == gridDim.x;
+    }
+    __syncthreads();
+    if (!s_last || threadIdx.x >= 32) return;
+    __threadfence();
+    best = -INFINITY;
+    idx = 0x7fffffff;
+    for (int i = lane; i < (int)gridDim.x; i += 32) argmax_merge(best, idx, __ldcg(part_val + i), __ldcg(part_idx + i));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        argmax_merge(best, idx, ov, oi);
+    }
+    if (lane == 0) {
+        if (idx == 0x7fffffff) idx = 0;  // only NaNs: the reference keeps index 0
         tok[0] = idx;
         if (out_tokens && step) {
             int s = *step;
@@ -304,6 +357,7 @@ __global__ void __launch_bounds__(1024) lb_argmax_advance_kernel(const float* __
             *step = s + 1;
         }
         if (pos) *pos += 1;
+        *cnt = 0;
     }
 }
 
@@ -346,9 +400,10 @@ int lb_launch_rope(loom_b200_ctx* ctx, const LbRopeParams& p) {
 size_t lb_attn_part_elems(int M, int heads, int hd, int splits) { return (size_t)M * heads * splits * (hd + 2); }
 
 int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p) {
-    LB_REQUIRE(ctx, p.hd % 4 == 0, "attention: head_dim %d must be a multiple of 4", p.hd);
+    LB_REQUIRE(ctx, p.hd % 8 == 0, "attention: head_dim %d must be a multiple of 8", p.hd);
     LB_REQUIRE(ctx, p.heads % p.kv_heads == 0, "attention: %d heads over %d kv heads", p.heads, p.kv_heads);
-    size_t smem = (size_t)(p.hd + p.max_chunk) * sizeof(double);
+    const int G = p.hd >= kAttnThreads ? 1 : kAttnThreads / p.hd;
+    size_t smem = (size_t)(p.hd + (size_t)G * p.hd + p.max_chunk) * sizeof(double);
     if (smem > 200 * 1024) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "attention: %d positions per CTA need %zu B of shared memory", p.max_chunk, smem);
     if (smem > 48 * 1024 && !(ctx->func_attr_mask & (1u << 30))) {
         LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -376,8 +431,20 @@ int lb_launch_lm_head(loom_b200_ctx* ctx, const LbLmHeadParams& p) {
 
 int lb_launch_argmax_advance(loom_b200_ctx* ctx, const float* logits, int vocab, int* tok, int* out_tokens, int out_cap,
                              int* step, int* pos) {
-    LB_CUDA(ctx, launch_pdl(ctx, lb_argmax_advance_kernel, dim3(1), dim3(1024), 0, logits, vocab, tok, out_tokens, out_cap,
-                            step, pos));
+    // partial results live in the context scratch of the argmax (allocated once)
+    if (!ctx->argmax_scratch) {
+        if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "argmax scratch would be allocated while recording a graph");
+        LB_CUDA(ctx, cudaMalloc(&ctx->argmax_scratch, kArgmaxCtas * 8 + 16));
+        LB_CUDA(ctx, cudaMemsetAsync(ctx->argmax_scratch, 0, kArgmaxCtas * 8 + 16, ctx->stream));
+    }
+    float* pv = (float*)ctx->argmax_scratch;
+    int* pi = (int*)(pv + kArgmaxCtas);
+    unsigned int* cnt = (unsigned int*)(pi + kArgmaxCtas);
+    int grid = kArgmaxCtas;
+    if (grid > (vocab + 255) / 256) grid = (vocab + 255) / 256;
+    if (grid < 1) grid = 1;
+    LB_CUDA(ctx, launch_pdl(ctx, lb_argmax_advance_kernel, dim3(grid), dim3(256), 0, logits, vocab, tok, out_tokens, out_cap,
+                            step, pos, pv, pi, cnt));
     ctx->launches++;
     return 0;
 }

@@ -306,7 +306,7 @@ int loom_b200_mha_create(loom_b200_ctx* ctx, int d_model, int num_heads, int num
     LB_REQUIRE(ctx, out != nullptr, "mha_create: out is NULL");
     *out = nullptr;
     LB_REQUIRE(ctx, wq && wk && wv && wo, "mha_create: weight is NULL");
-    LB_REQUIRE(ctx, d_model > 0 && num_heads > 0 && head_dim > 0 && head_dim % 4 == 0, "mha_create: bad dimensions");
+    LB_REQUIRE(ctx, d_model > 0 && num_heads > 0 && head_dim > 0 && head_dim % 8 == 0, "mha_create: bad dimensions");
     if (num_kv_heads == 0) num_kv_heads = num_heads;
     LB_REQUIRE(ctx, num_heads % num_kv_heads == 0, "mha_create: %d heads over %d kv heads", num_heads, num_kv_heads);
     const int qd = num_heads * head_dim, kvd = num_kv_heads * head_dim;
