@@ -87,12 +87,14 @@ void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
  * 2 = whole strips per CTA; "pdl" 0/1 = programmatic dependent launch.  Results never depend on them
  * ("debug" is for timing experiments only and does change results). */
 int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value);
-/* Phase trace of the ternary GEMV, the counterpart of WGPUContext.TimeCommands
- * (poly/wgpu_context_native.go:553): with option "trace" = 1 every CTA of a GEMV launch records the
- * GPU global timer (ns) at: 0 start, 1 weights requested, 2 upstream data ready, 3 activations staged,
- * 4 dot products done, 5 epilogue done.  trace_read copies the first `ctas` rows of 8 values; rows of
- * launches with a larger grid are limited to 2048 CTAs. */
-int loom_b200_trace_read(loom_b200_ctx* ctx, uint64_t* host, int ctas);
+/* Phase trace, the counterpart of WGPUContext.TimeCommands (poly/wgpu_context_native.go:553) and of the
+ * per-layer timing ForwardTokenIDsWGPU emits (poly/wgpu_forward.go:121-127).  With option "trace" = 1 every
+ * GEMV / RoPE / attention / LM-head launch (also inside a recorded frame) gets a row of eight 64-bit slots, in
+ * launch order modulo 1024, and its first CTA writes the GPU global timer (ns): 0 start, 1 weights requested,
+ * 2 upstream data ready, 3 activations staged (attention: scores done), 4 dot products done, 5 end.  Unused
+ * slots stay 0.  trace_read copies the first `rows` rows; trace_label names the kernel of a row. */
+int loom_b200_trace_read(loom_b200_ctx* ctx, uint64_t* host, int rows);
+const char* loom_b200_trace_label(const loom_b200_ctx* ctx, int row);
 /* number of kernels of this library launched on the context since creation */
 uint64_t loom_b200_launch_count(const loom_b200_ctx* ctx);
 

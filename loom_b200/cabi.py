@@ -48,6 +48,7 @@ SIGNATURES = {
     "loom_b200_graph_free": (None, [_vp, _vp]),
     "loom_b200_launch_count": (C.c_uint64, [_vp]),
     "loom_b200_trace_read": (_i, [_vp, _vp, _i]),
+    "loom_b200_trace_label": (C.c_char_p, [_vp, _i]),
     "loom_b200_ctx_set_option": (_i, [_vp, C.c_char_p, _i]),
     "loom_b200_buffer_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "loom_b200_buffer_free": (_i, [_vp, _vp]),
@@ -215,6 +216,9 @@ class Context:
         out = np.zeros((ctas, 8), np.uint64)
         self._check(lib().loom_b200_trace_read(self.h, out.ctypes.data, ctas))
         return out
+
+    def trace_label(self, row: int) -> str:
+        return (lib().loom_b200_trace_label(self.h, row) or b"").decode()
 
     def set_option(self, key: str, value: int):
         self._check(lib().loom_b200_ctx_set_option(self.h, key.encode(), int(value)))

@@ -319,9 +319,10 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
         LB_NO_CAPTURE(ctx, "switching the trace");
         if (int rc = lb_set_device(ctx)) return rc;
         LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        ctx->trace_seq = 0;
         if (value && !ctx->trace_dev) {
-            LB_CUDA(ctx, cudaMalloc(&ctx->trace_dev, (size_t)kTraceCtas * 8 * sizeof(unsigned long long)));
-            LB_CUDA(ctx, cudaMemset(ctx->trace_dev, 0, (size_t)kTraceCtas * 8 * sizeof(unsigned long long)));
+            LB_CUDA(ctx, cudaMalloc(&ctx->trace_dev, (size_t)kTraceSlots * 8 * sizeof(unsigned long long)));
+            LB_CUDA(ctx, cudaMemset(ctx->trace_dev, 0, (size_t)kTraceSlots * 8 * sizeof(unsigned long long)));
         } else if (!value && ctx->trace_dev) {
             cudaFree(ctx->trace_dev);
             ctx->trace_dev = nullptr;
@@ -411,9 +412,14 @@ void loom_b200_graph_free(loom_b200_ctx* ctx, loom_b200_graph* graph) {
     delete graph;
 }
 
+const char* loom_b200_trace_label(const loom_b200_ctx* ctx, int slot) {
+    if (!ctx || slot < 0 || slot >= kTraceSlots || !ctx->trace_label[slot]) return "";
+    return ctx->trace_label[slot];
+}
+
 int loom_b200_trace_read(loom_b200_ctx* ctx, uint64_t* host, int ctas) {
     if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "trace_read: ctx is NULL");
-    LB_REQUIRE(ctx, host && ctas > 0 && ctas <= kTraceCtas, "trace_read: bad arguments");
+    LB_REQUIRE(ctx, host && ctas > 0 && ctas <= kTraceSlots, "trace_read: bad arguments");
     LB_REQUIRE(ctx, ctx->trace_dev != nullptr, "trace_read: tracing is off (set option \"trace\" to 1)");
     LB_NO_CAPTURE(ctx, "trace_read");
     if (int rc = lb_set_device(ctx)) return rc;

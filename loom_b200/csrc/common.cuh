@@ -28,7 +28,7 @@ constexpr int kTileRows = 16;
 constexpr int kTileCols = 128;
 constexpr int kTileBytes = 512;
 constexpr int kTileWords = 128;
-constexpr int kTraceCtas = 2048;
+constexpr int kTraceSlots = 1024;  // launches remembered by the phase trace
 
 struct loom_b200_weight {
     int rows = 0, cols = 0, row_words = 0;
@@ -63,7 +63,9 @@ struct loom_b200_ctx {
     int opt_gemv_ctas_per_sm = 2;  // grid = SMs * this
     int opt_pdl = 1;               // programmatic dependent launch on/off
     int opt_gemv_partition = 0;    // 0 = choose, 1 = always stream-K, 2 = always whole strip groups
-    unsigned long long* trace_dev = nullptr;  // [kTraceCtas][8] phase timestamps of the last GEMV launch
+    unsigned long long* trace_dev = nullptr;  // [kTraceSlots][8] phase timestamps, one row per launch
+    int trace_seq = 0;                          // next row
+    const char* trace_label[kTraceSlots] = {};  // kernel that wrote each row
     int opt_debug = 0;             // timing experiments (results are wrong when non-zero)
     bool capturing = false;        // between graph_begin and graph_end
 };
@@ -94,6 +96,13 @@ int lb_ensure_scratch(loom_b200_ctx* ctx, size_t bytes);
     do {                                                                                            \
         if (!(cond)) return lb_fail((ctx), LOOM_B200_ERR_INVALID, __VA_ARGS__);                     \
     } while (0)
+
+static inline unsigned long long* lb_trace_row(loom_b200_ctx* ctx, const char* label) {
+    if (!ctx->trace_dev) return nullptr;
+    int slot = ctx->trace_seq++ % kTraceSlots;
+    ctx->trace_label[slot] = label;
+    return ctx->trace_dev + (size_t)slot * 8;
+}
 
 static inline int lb_set_device(loom_b200_ctx* ctx) {
     cudaError_t e = cudaSetDevice(ctx->device);
@@ -180,6 +189,17 @@ __device__ __forceinline__ int lb_warp_sum_i(int v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
+}
+
+// Phase trace: when tracing is on, every launch gets a row of eight 64-bit slots and CTA 0 writes the GPU
+// global timer (ns) into slot k at phase k.  Rows are assigned at launch (or recording) time.
+__device__ __forceinline__ unsigned long long lb_gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void lb_trace(unsigned long long* row, int k) {
+    if (row && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) row[k] = lb_gtime();
 }
 
 // ---- sm_100a plumbing: mbarrier, bulk async copy (TMA engine), programmatic dependent launch ------

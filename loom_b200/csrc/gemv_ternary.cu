@@ -23,6 +23,8 @@
 //     associative, so the result is bit-identical to the sequential CPU loop whatever the arrival order.
 #include "gemv_ternary.cuh"
 
+#include <type_traits>
+
 
 namespace {
 
@@ -50,16 +52,7 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// Optional phase trace: slot k of this CTA's row receives the global timer (ns) at phase k.
-#define LB_TRACE(k)                                                                       \
-    do {                                                                                  \
-        if (p.trace && threadIdx.x == 0) p.trace[(size_t)blockIdx.x * 8 + (k)] = gtime(); \
-    } while (0)
+#define LB_TRACE(k) lb_trace(p.trace, (k))
 
 struct Smem {
     uint8_t* ring;
@@ -130,6 +123,123 @@ __device__ __forceinline__ double pro_value(const void* row, int c, double stat,
     return (double)(float)__dmul_rn(__dmul_rn((double)x, stat), w);
 }
 
+// Register-resident prologue for fp32/fp64 inputs with K % 4 == 0 and K <= 1024*UMAX: every thread loads its
+// 4-column units (and their gains) once, then the sum of squares, the absmax and the quantization run on
+// registers -- one global round trip and two block reductions per token.
+template <int PRO, int UMAX>
+__device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem& sm, int n, const void* row) {
+    const int tid = threadIdx.x, K = p.K, units = K >> 2;
+    const int Kp = p.kblocks * kTileCols, stride32 = (Kp + 16) / 4;
+    constexpr bool f64 = PRO == LB_PRO_INNERNORM64;
+    // fp32 paths hold float32 values at every step (the reference rounds to float32 there too)
+    using VT = typename std::conditional<f64, double, float>::type;
+    VT v[UMAX][4];
+    float w[UMAX][4];
+#pragma unroll
+    for (int u = 0; u < UMAX; ++u) {
+        const int idx = tid + u * kThreads;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            v[u][k] = (VT)0;
+            w[u][k] = 1.0f;
+        }
+        if (idx < units) {
+            if (f64) {
+                const double2 a = reinterpret_cast<const double2*>(row)[2 * idx], b = reinterpret_cast<const double2*>(row)[2 * idx + 1];
+                v[u][0] = a.x; v[u][1] = a.y; v[u][2] = b.x; v[u][3] = b.y;
+            } else {
+                const float4 a = reinterpret_cast<const float4*>(row)[idx];
+                v[u][0] = (VT)a.x; v[u][1] = (VT)a.y; v[u][2] = (VT)a.z; v[u][3] = (VT)a.w;
+            }
+            if (PRO != LB_PRO_F32 && p.norm_w) {
+                if (4 * idx + 4 <= p.norm_w_len) {
+                    const float4 g = reinterpret_cast<const float4*>(p.norm_w)[idx];
+                    w[u][0] = g.x; w[u][1] = g.y; w[u][2] = g.z; w[u][3] = g.w;
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (4 * idx + k < p.norm_w_len) w[u][k] = p.norm_w[4 * idx + k];
+                }
+            }
+        }
+    }
+    if (PRO >= LB_PRO_BLOCKNORM) {
+        double ss = 0.0;
+#pragma unroll
+        for (int u = 0; u < UMAX; ++u)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ss = __dadd_rn(ss, __dmul_rn((double)v[u][k], (double)v[u][k]));
+        ss = block_sum(ss, sm.red);
+        const double mean = __dadd_rn(__ddiv_rn(ss, (double)K), p.eps);
+        if (PRO == LB_PRO_BLOCKNORM) {
+            const double rms = sqrt(mean), rr = __ddiv_rn(1.0, rms);
+#pragma unroll
+            for (int u = 0; u < UMAX; ++u)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v[u][k] = (VT)(float)__dmul_rn(lb_div_by((double)v[u][k], rms, rr), (double)w[u][k]);
+        } else {
+            const double sc = __ddiv_rn(1.0, sqrt(mean));
+#pragma unroll
+            for (int u = 0; u < UMAX; ++u)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (f64) v[u][k] = (VT)__dmul_rn((double)v[u][k], __dmul_rn(sc, (double)w[u][k]));
+                    else v[u][k] = (VT)(float)__dmul_rn(__dmul_rn((double)v[u][k], sc), (double)w[u][k]);
+                }
+        }
+    }
+    float m = 0.0f;
+#pragma unroll
+    for (int u = 0; u < UMAX; ++u)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m = fmaxf(m, (float)fabs((double)v[u][k]));
+    m = block_max(m, sm.red);
+    const float amax = m < 1e-5f ? 1e-5f : m;
+    const double s = __ddiv_rn(127.0, (double)amax);
+    const bool side = blockIdx.x == 0;
+    int local_sum = 0;
+    uint8_t* abytes = reinterpret_cast<uint8_t*>(sm.acts + (size_t)n * stride32);
+#pragma unroll
+    for (int u = 0; u < UMAX; ++u) {
+        const int idx = tid + u * kThreads;
+        if (idx < units) {
+            const int q0 = lb_quant_i8((double)v[u][0], s), q1 = lb_quant_i8((double)v[u][1], s),
+                      q2 = lb_quant_i8((double)v[u][2], s), q3 = lb_quant_i8((double)v[u][3], s);
+            local_sum += q0 + q1 + q2 + q3;
+            // unit idx = word r_b of 16-column chunk i: byte j of r_b is byte b of B_j
+            const int i = idx >> 2, b = idx & 3;
+            const int kb = i >> 3, w8 = i & 7, h = w8 >> 2, t = w8 & 3;
+            uint8_t* dst = abytes + (size_t)(kb * 32 + t * 8 + h) * 4 + b;
+            dst[0] = (uint8_t)q0;
+            dst[8] = (uint8_t)q1;
+            dst[16] = (uint8_t)q2;
+            dst[24] = (uint8_t)q3;
+            if (side) {
+                if (p.q_out)
+                    reinterpret_cast<uint32_t*>(p.q_out + (size_t)n * K)[idx] =
+                        (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+                if (p.norm_out)
+                    reinterpret_cast<float4*>(p.norm_out + (size_t)n * K)[idx] =
+                        make_float4((float)v[u][0], (float)v[u][1], (float)v[u][2], (float)v[u][3]);
+            }
+        }
+    }
+    // columns K..Kp-1 of the padded row are zero
+    for (int idx = units + tid; idx < (Kp >> 2); idx += kThreads) {
+        const int i = idx >> 2, b = idx & 3;
+        const int kb = i >> 3, w8 = i & 7, h = w8 >> 2, t = w8 & 3;
+        uint8_t* dst = abytes + (size_t)(kb * 32 + t * 8 + h) * 4 + b;
+        dst[0] = 0; dst[8] = 0; dst[16] = 0; dst[24] = 0;
+    }
+    local_sum = lb_warp_sum_i(local_sum);
+    if ((tid & 31) == 0 && local_sum != 0) atomicAdd(&sm.xsum[n], local_sum);
+    if (tid < 3) sm.os[tid * kMaxM + n] = tid < p.nseg ? lb_output_scale(p.seg[tid].scale, amax) : 1.0;
+    if (tid == 0) {
+        sm.amax[n] = amax;
+        if (side && p.amax_out) p.amax_out[n] = amax;
+    }
+}
+
 // Quantizes the M activation rows into shared memory in the k-slot order the MMA B-fragments use, and
 // leaves sum(q) and amax per token in shared memory.
 template <int PRO>
@@ -145,6 +255,15 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
         const void* row = q8 ? (const void*)((const int8_t*)p.x + (size_t)n * K)
                              : (PRO == LB_PRO_INNERNORM64 ? (const void*)((const double*)p.x + (size_t)n * K)
                                                             : (const void*)((const float*)p.x + (size_t)n * K));
+        if (!q8) {
+            constexpr int UMAX = PRO == LB_PRO_INNERNORM64 ? 4 : 8;
+            const bool aligned16 = (((uintptr_t)row) & 15) == 0 && (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) &&
+                                   (!p.q_out || (K & 3) == 0) && (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0);
+            if ((K & 3) == 0 && (K >> 2) <= kThreads * UMAX && aligned16) {
+                stage_row_fast<PRO == LB_PRO_Q8 ? LB_PRO_F32 : PRO, UMAX>(p, sm, n, row);
+                continue;
+            }
+        }
         double stat = 0.0, rstat = 0.0;  // rms (or 1/rms for the inner norms) and, for the block norm, RN(1/rms)
         float amax;
         if (q8) {
@@ -652,7 +771,7 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     p.fix_cnt = ctx->fix_cnt;
     p.status = ctx->status_dev;
     p.debug = ctx->opt_debug;
-    p.trace = grid <= kTraceCtas ? ctx->trace_dev : nullptr;
+    p.trace = lb_trace_row(ctx, "gemv");
     size_t smem = gemv_smem_bytes(p, p.max_local_strips);
     if (smem > 227 * 1024)
         return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: K=%d with %d tokens needs %zu B of shared memory", p.K, p.M, smem);

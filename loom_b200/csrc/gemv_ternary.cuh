@@ -69,7 +69,7 @@ struct LbGemvParams {
     int32_t* fix_acc;
     unsigned int* fix_cnt;
     int* status;
-    unsigned long long* trace;  // optional [grid][8] phase timestamps (ns), or null
+    unsigned long long* trace;  // optional row of 8 phase timestamps (ns) written by CTA 0, or null
     int debug;  // timing experiments only: 1 = skip the arithmetic, 2 = skip the weight copies
 };
 

@@ -50,6 +50,7 @@ __global__ void lb_rope_kernel(const LbRopeParams p) {
     __shared__ double red[32];
     lb_pdl_launch_dependents();
     lb_pdl_wait();
+    lb_trace(p.trace, 2);
     const int n = blockIdx.y, h = blockIdx.x, half = p.hd / 2, d = threadIdx.x;
     const int pos = *p.pos_ptr + n;
     const bool is_q = h < p.heads;
@@ -103,6 +104,7 @@ __global__ void lb_rope_kernel(const LbRopeParams p) {
         krow[d] = (float)r0;
         krow[d + half] = (float)r1;
     }
+    lb_trace(p.trace, 5);
 }
 
 // One CTA per (head, token, split).  A pair of threads scores one position (half of the head dimension each);
@@ -118,6 +120,7 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     __shared__ int s_last;
     lb_pdl_launch_dependents();
     lb_pdl_wait();
+    lb_trace(p.trace, 2);
     const int h = blockIdx.x, n = blockIdx.y, sp = blockIdx.z, tid = threadIdx.x;
     const int hd = p.hd, kvd = p.kv_heads * hd, qd = p.heads * hd;
     const int G = hd >= kAttnThreads ? 1 : kAttnThreads / hd;
@@ -163,6 +166,7 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
         }
     }
     mx = block_max_d(mx, red);
+    lb_trace(p.trace, 3);
     double den = 0.0;
     for (int j = tid; j < cnt; j += kAttnThreads) {
         const double e = exp(__dsub_rn(sc[j], mx));
@@ -202,6 +206,7 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
         }
         __syncthreads();
     }
+    lb_trace(p.trace, 4);
     if (p.splits == 1) return;
     __threadfence();
     __syncthreads();
@@ -241,6 +246,7 @@ __global__ void __launch_bounds__(kHeadThreads) lb_lm_head_kernel(const LbLmHead
     double* sh = reinterpret_cast<double*>(smem_raw);  // [hidden]
     lb_pdl_launch_dependents();
     lb_pdl_wait();
+    lb_trace(p.trace, 2);
     const int H = p.hidden, tid = threadIdx.x;
     double ss = 0.0;
     for (int i = tid; i < H; i += kHeadThreads) {
@@ -290,6 +296,7 @@ __global__ void __launch_bounds__(kHeadThreads) lb_lm_head_kernel(const LbLmHead
         acc = lb_warp_sum(acc);
         if (lane == 0) p.logits[v] = (float)acc;
     }
+    lb_trace(p.trace, 5);
 }
 
 // Greedy argmax in two levels: every CTA reduces a slice to (value, first index); the CTA that arrives last
@@ -390,7 +397,9 @@ int lb_launch_embed(loom_b200_ctx* ctx, const float* emb, int vocab, int hidden,
     return 0;
 }
 
-int lb_launch_rope(loom_b200_ctx* ctx, const LbRopeParams& p) {
+int lb_launch_rope(loom_b200_ctx* ctx, const LbRopeParams& pin) {
+    LbRopeParams p = pin;
+    p.trace = lb_trace_row(ctx, "rope");
     LB_REQUIRE(ctx, p.hd % 2 == 0 && p.hd / 2 <= 1024, "rope: head_dim %d", p.hd);
     LB_CUDA(ctx, launch_pdl(ctx, lb_rope_kernel, dim3(p.heads + p.kv_heads, p.M), dim3(p.hd / 2), 0, p));
     ctx->launches++;
@@ -399,7 +408,9 @@ int lb_launch_rope(loom_b200_ctx* ctx, const LbRopeParams& p) {
 
 size_t lb_attn_part_elems(int M, int heads, int hd, int splits) { return (size_t)M * heads * splits * (hd + 2); }
 
-int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p) {
+int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& pin) {
+    LbAttnParams p = pin;
+    p.trace = lb_trace_row(ctx, "attention");
     LB_REQUIRE(ctx, p.hd % 8 == 0, "attention: head_dim %d must be a multiple of 8", p.hd);
     LB_REQUIRE(ctx, p.heads % p.kv_heads == 0, "attention: %d heads over %d kv heads", p.heads, p.kv_heads);
     const int G = p.hd >= kAttnThreads ? 1 : kAttnThreads / p.hd;
@@ -414,7 +425,9 @@ int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p) {
     return 0;
 }
 
-int lb_launch_lm_head(loom_b200_ctx* ctx, const LbLmHeadParams& p) {
+int lb_launch_lm_head(loom_b200_ctx* ctx, const LbLmHeadParams& pin) {
+    LbLmHeadParams p = pin;
+    p.trace = lb_trace_row(ctx, "lm_head");
     size_t smem = (size_t)p.hidden * sizeof(double);
     if (smem > 200 * 1024) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "lm_head: hidden %d too large", p.hidden);
     if (smem > 48 * 1024 && !(ctx->func_attr_mask & (1u << 29))) {

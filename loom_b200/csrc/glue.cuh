@@ -18,6 +18,7 @@ struct LbRopeParams {
     int k_norm_len;
     double qk_eps;
     int M, heads, kv_heads, hd, msl;
+    unsigned long long* trace;
 };
 int lb_launch_rope(loom_b200_ctx* ctx, const LbRopeParams& p);
 
@@ -31,6 +32,7 @@ struct LbAttnParams {
     unsigned int* cnt;     // [M*heads], zero between launches
     int M, heads, kv_heads, hd, msl, splits;
     int max_chunk;         // positions one CTA may hold scores for (shared memory sizing)
+    unsigned long long* trace;
 };
 int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p);
 size_t lb_attn_part_elems(int M, int heads, int hd, int splits);
@@ -43,6 +45,7 @@ struct LbLmHeadParams {
     int vocab, hidden;
     float* logits;         // [vocab]
     float* hidden_out;     // optional [hidden]: the normalised row
+    unsigned long long* trace;
 };
 int lb_launch_lm_head(loom_b200_ctx* ctx, const LbLmHeadParams& p);
 
