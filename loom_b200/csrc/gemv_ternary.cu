@@ -31,9 +31,8 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kStageTiles = 8;                          // tiles per ring stage (4 KB)
-constexpr int kStages = 3;                              // stages per warp
+constexpr int kStages = 3;                              // most stages per warp (the launch picks 1..3)
 constexpr int kStageBytes = kStageTiles * kTileBytes;   // 4096
-constexpr int kRingBytes = kWarps * kStages * kStageBytes;  // 98304
 constexpr int kMaxM = 8;
 
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -64,6 +63,7 @@ struct Smem {
     double* red;      // [32]
     int* flag;        // [4]
     uint64_t* bars;   // [kWarps*kStages]
+    void* stage;      // K floats (doubles for fp64 input) of prologue staging, or null
 };
 
 __device__ __forceinline__ const uint32_t* tile_ptr(const LbGemvParams& p, int v, int kb) {
@@ -123,113 +123,102 @@ __device__ __forceinline__ double pro_value(const void* row, int c, double stat,
     return (double)(float)__dmul_rn(__dmul_rn((double)x, stat), w);
 }
 
-// Register-resident prologue for fp32/fp64 inputs with K % 4 == 0 and K <= 1024*UMAX: every thread loads its
-// 4-column units (and their gains) once, then the sum of squares, the absmax and the quantization run on
-// registers -- one global round trip and two block reductions per token.
-template <int PRO, int UMAX>
+// Prologue for fp32/fp64 inputs with K % 4 == 0: the row is copied once from global into a shared staging
+// buffer (loads of several units in flight), then normalisation, absmax and quantization run as short rolled
+// loops over 4-column units.  Code executed once per CTA is fetched cold, so the loops are kept small and
+// reused rather than unrolled; the four columns of a unit give the instruction-level parallelism.
+template <int PRO>
 __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem& sm, int n, const void* row) {
     const int tid = threadIdx.x, K = p.K, units = K >> 2;
     const int Kp = p.kblocks * kTileCols, stride32 = (Kp + 16) / 4;
     constexpr bool f64 = PRO == LB_PRO_INNERNORM64;
-    // fp32 paths hold float32 values at every step (the reference rounds to float32 there too)
     using VT = typename std::conditional<f64, double, float>::type;
-    VT v[UMAX][4];
-    float w[UMAX][4];
-#pragma unroll
-    for (int u = 0; u < UMAX; ++u) {
-        const int idx = tid + u * kThreads;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            v[u][k] = (VT)0;
-            w[u][k] = 1.0f;
+    VT* tmp = reinterpret_cast<VT*>(sm.stage);
+    const bool have_w = PRO != LB_PRO_F32 && p.norm_w != nullptr;
+    double ss = 0.0;
+    float m = 0.0f;
+#pragma unroll 4
+    for (int idx = tid; idx < units; idx += kThreads) {
+        VT a0, a1, a2, a3;
+        if (f64) {
+            const double2 a = reinterpret_cast<const double2*>(row)[2 * idx], b = reinterpret_cast<const double2*>(row)[2 * idx + 1];
+            a0 = (VT)a.x; a1 = (VT)a.y; a2 = (VT)b.x; a3 = (VT)b.y;
+        } else {
+            const float4 a = reinterpret_cast<const float4*>(row)[idx];
+            a0 = (VT)a.x; a1 = (VT)a.y; a2 = (VT)a.z; a3 = (VT)a.w;
         }
-        if (idx < units) {
-            if (f64) {
-                const double2 a = reinterpret_cast<const double2*>(row)[2 * idx], b = reinterpret_cast<const double2*>(row)[2 * idx + 1];
-                v[u][0] = a.x; v[u][1] = a.y; v[u][2] = b.x; v[u][3] = b.y;
-            } else {
-                const float4 a = reinterpret_cast<const float4*>(row)[idx];
-                v[u][0] = (VT)a.x; v[u][1] = (VT)a.y; v[u][2] = (VT)a.z; v[u][3] = (VT)a.w;
-            }
-            if (PRO != LB_PRO_F32 && p.norm_w) {
-                if (4 * idx + 4 <= p.norm_w_len) {
-                    const float4 g = reinterpret_cast<const float4*>(p.norm_w)[idx];
-                    w[u][0] = g.x; w[u][1] = g.y; w[u][2] = g.z; w[u][3] = g.w;
-                } else {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        if (4 * idx + k < p.norm_w_len) w[u][k] = p.norm_w[4 * idx + k];
-                }
-            }
+        if (have_w && 4 * idx < p.norm_w_len) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.norm_w + 4 * idx));
+        tmp[4 * idx] = a0; tmp[4 * idx + 1] = a1; tmp[4 * idx + 2] = a2; tmp[4 * idx + 3] = a3;
+        if (PRO >= LB_PRO_BLOCKNORM) {
+            ss = __dadd_rn(ss, __dmul_rn((double)a0, (double)a0));
+            ss = __dadd_rn(ss, __dmul_rn((double)a1, (double)a1));
+            ss = __dadd_rn(ss, __dmul_rn((double)a2, (double)a2));
+            ss = __dadd_rn(ss, __dmul_rn((double)a3, (double)a3));
+        } else {
+            m = fmaxf(fmaxf(m, fabsf((float)a0)), fmaxf(fabsf((float)a1), fmaxf(fabsf((float)a2), fabsf((float)a3))));
         }
     }
     if (PRO >= LB_PRO_BLOCKNORM) {
-        double ss = 0.0;
-#pragma unroll
-        for (int u = 0; u < UMAX; ++u)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) ss = __dadd_rn(ss, __dmul_rn((double)v[u][k], (double)v[u][k]));
         ss = block_sum(ss, sm.red);
         const double mean = __dadd_rn(__ddiv_rn(ss, (double)K), p.eps);
-        if (PRO == LB_PRO_BLOCKNORM) {
-            const double rms = sqrt(mean), rr = __ddiv_rn(1.0, rms);
-#pragma unroll
-            for (int u = 0; u < UMAX; ++u)
-#pragma unroll
-                for (int k = 0; k < 4; ++k) v[u][k] = (VT)(float)__dmul_rn(lb_div_by((double)v[u][k], rms, rr), (double)w[u][k]);
-        } else {
-            const double sc = __ddiv_rn(1.0, sqrt(mean));
-#pragma unroll
-            for (int u = 0; u < UMAX; ++u)
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    if (f64) v[u][k] = (VT)__dmul_rn((double)v[u][k], __dmul_rn(sc, (double)w[u][k]));
-                    else v[u][k] = (VT)(float)__dmul_rn(__dmul_rn((double)v[u][k], sc), (double)w[u][k]);
+        const double root = sqrt(mean);
+        const double rr = __ddiv_rn(1.0, root);  // RN(1/rms): the inner norms' scale, the block norm's reciprocal
+#pragma unroll 1
+        for (int idx = tid; idx < units; idx += kThreads) {
+            double w[4] = {1.0, 1.0, 1.0, 1.0};
+            if (have_w) {
+                if (4 * idx + 4 <= p.norm_w_len) {
+                    const float4 g = reinterpret_cast<const float4*>(p.norm_w)[idx];
+                    w[0] = (double)g.x; w[1] = (double)g.y; w[2] = (double)g.z; w[3] = (double)g.w;
+                } else {
+                    for (int k = 0; k < 4; ++k)
+                        if (4 * idx + k < p.norm_w_len) w[k] = (double)p.norm_w[4 * idx + k];
                 }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const double x = (double)tmp[4 * idx + k];
+                VT y;
+                if (PRO == LB_PRO_BLOCKNORM) y = (VT)(float)__dmul_rn(lb_div_by(x, root, rr), w[k]);
+                else if (f64) y = (VT)__dmul_rn(x, __dmul_rn(rr, w[k]));
+                else y = (VT)(float)__dmul_rn(__dmul_rn(x, rr), w[k]);
+                tmp[4 * idx + k] = y;
+                m = fmaxf(m, (float)fabs((double)y));
+            }
         }
     }
-    float m = 0.0f;
-#pragma unroll
-    for (int u = 0; u < UMAX; ++u)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) m = fmaxf(m, (float)fabs((double)v[u][k]));
     m = block_max(m, sm.red);
     const float amax = m < 1e-5f ? 1e-5f : m;
     const double s = __ddiv_rn(127.0, (double)amax);
     const bool side = blockIdx.x == 0;
     int local_sum = 0;
     uint8_t* abytes = reinterpret_cast<uint8_t*>(sm.acts + (size_t)n * stride32);
-#pragma unroll
-    for (int u = 0; u < UMAX; ++u) {
-        const int idx = tid + u * kThreads;
+#pragma unroll 1
+    for (int idx = tid; idx < (Kp >> 2); idx += kThreads) {
+        int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
         if (idx < units) {
-            const int q0 = lb_quant_i8((double)v[u][0], s), q1 = lb_quant_i8((double)v[u][1], s),
-                      q2 = lb_quant_i8((double)v[u][2], s), q3 = lb_quant_i8((double)v[u][3], s);
+            const VT y0 = tmp[4 * idx], y1 = tmp[4 * idx + 1], y2 = tmp[4 * idx + 2], y3 = tmp[4 * idx + 3];
+            q0 = lb_quant_i8((double)y0, s);
+            q1 = lb_quant_i8((double)y1, s);
+            q2 = lb_quant_i8((double)y2, s);
+            q3 = lb_quant_i8((double)y3, s);
             local_sum += q0 + q1 + q2 + q3;
-            // unit idx = word r_b of 16-column chunk i: byte j of r_b is byte b of B_j
-            const int i = idx >> 2, b = idx & 3;
-            const int kb = i >> 3, w8 = i & 7, h = w8 >> 2, t = w8 & 3;
-            uint8_t* dst = abytes + (size_t)(kb * 32 + t * 8 + h) * 4 + b;
-            dst[0] = (uint8_t)q0;
-            dst[8] = (uint8_t)q1;
-            dst[16] = (uint8_t)q2;
-            dst[24] = (uint8_t)q3;
             if (side) {
                 if (p.q_out)
                     reinterpret_cast<uint32_t*>(p.q_out + (size_t)n * K)[idx] =
                         (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
                 if (p.norm_out)
-                    reinterpret_cast<float4*>(p.norm_out + (size_t)n * K)[idx] =
-                        make_float4((float)v[u][0], (float)v[u][1], (float)v[u][2], (float)v[u][3]);
+                    reinterpret_cast<float4*>(p.norm_out + (size_t)n * K)[idx] = make_float4((float)y0, (float)y1, (float)y2, (float)y3);
             }
         }
-    }
-    // columns K..Kp-1 of the padded row are zero
-    for (int idx = units + tid; idx < (Kp >> 2); idx += kThreads) {
+        // unit idx = word r_b of 16-column chunk i: byte j of r_b is byte b of B_j (columns >= K stay zero)
         const int i = idx >> 2, b = idx & 3;
         const int kb = i >> 3, w8 = i & 7, h = w8 >> 2, t = w8 & 3;
         uint8_t* dst = abytes + (size_t)(kb * 32 + t * 8 + h) * 4 + b;
-        dst[0] = 0; dst[8] = 0; dst[16] = 0; dst[24] = 0;
+        dst[0] = (uint8_t)q0;
+        dst[8] = (uint8_t)q1;
+        dst[16] = (uint8_t)q2;
+        dst[24] = (uint8_t)q3;
     }
     local_sum = lb_warp_sum_i(local_sum);
     if ((tid & 31) == 0 && local_sum != 0) atomicAdd(&sm.xsum[n], local_sum);
@@ -238,6 +227,7 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
         sm.amax[n] = amax;
         if (side && p.amax_out) p.amax_out[n] = amax;
     }
+    __syncthreads();  // the staging buffer is reused by the next token
 }
 
 // Quantizes the M activation rows into shared memory in the k-slot order the MMA B-fragments use, and
@@ -256,11 +246,10 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
                              : (PRO == LB_PRO_INNERNORM64 ? (const void*)((const double*)p.x + (size_t)n * K)
                                                             : (const void*)((const float*)p.x + (size_t)n * K));
         if (!q8) {
-            constexpr int UMAX = PRO == LB_PRO_INNERNORM64 ? 4 : 8;
             const bool aligned16 = (((uintptr_t)row) & 15) == 0 && (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) &&
-                                   (!p.q_out || (K & 3) == 0) && (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0);
-            if ((K & 3) == 0 && (K >> 2) <= kThreads * UMAX && aligned16) {
-                stage_row_fast<PRO == LB_PRO_Q8 ? LB_PRO_F32 : PRO, UMAX>(p, sm, n, row);
+                                   (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) && (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0);
+            if ((K & 3) == 0 && sm.stage && aligned16) {
+                stage_row_fast<PRO == LB_PRO_Q8 ? LB_PRO_F32 : PRO>(p, sm, n, row);
                 continue;
             }
         }
@@ -429,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     {
         uint8_t* ptr = smem_raw;
         sm.ring = ptr;
-        ptr += kRingBytes;
+        ptr += (size_t)kWarps * p.stages * kStageBytes;
         sm.acts = reinterpret_cast<uint32_t*>(ptr);
         ptr += (size_t)(M * stride32 + 8) * 4;
         ptr = reinterpret_cast<uint8_t*>(((uintptr_t)ptr + 15) & ~(uintptr_t)15);
@@ -446,6 +435,8 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         sm.flag = reinterpret_cast<int*>(ptr);
         ptr += 16;
         sm.bars = reinterpret_cast<uint64_t*>(ptr);
+        ptr += kWarps * kStages * 8;
+        sm.stage = p.stage_bytes > 0 ? (void*)ptr : nullptr;
     }
 
     // ---- tile ranges --------------------------------------------------------------------------------
@@ -472,7 +463,8 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     if (tid == 0) lb_fence_mbar_init();
     __syncthreads();
 
-    uint8_t* my_ring = sm.ring + (size_t)warp * kStages * kStageBytes;
+    const int nstages = p.stages;
+    uint8_t* my_ring = sm.ring + (size_t)warp * nstages * kStageBytes;
     uint64_t* my_bars = sm.bars + warp * kStages;
 
     // Cursors walk the warp's tile range chunk by chunk; a chunk never crosses a strip, so (strip, kblock)
@@ -507,7 +499,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     ic.v = w0 / KB;
     ic.kb = w0 - ic.v * KB;
     Cursor cc = ic;
-    for (int s = 0; s < kStages && ic.pos < w1; ++s) {
+    for (int s = 0; s < nstages && ic.pos < w1; ++s) {
         int len = chunk_len(ic);
         if (lane == 0) issue(s, ic, len);
         advance(ic, len);
@@ -641,7 +633,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
             }
             advance(ic, len2);
         }
-        if (++cstage == kStages) {
+        if (++cstage == nstages) {
             cstage = 0;
             cphase ^= 1u;
         }
@@ -711,12 +703,14 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
 
 size_t gemv_smem_bytes(const LbGemvParams& p, int max_local) {
     int Kp = p.kblocks * kTileCols;
-    size_t b = kRingBytes;
+    size_t b = (size_t)kWarps * p.stages * kStageBytes;
     b += (size_t)(p.M * ((Kp + 16) / 4) + 8) * 4;
     b = (b + 15) & ~(size_t)15;
     b += (size_t)max_local * p.M * 16 * 4;
     b += 32 + 32 + 256 + 3 * kMaxM * 8 + 16;
     b += (size_t)kWarps * kStages * 8;
+    b = (b + 15) & ~(size_t)15;
+    b += (size_t)p.stage_bytes;
     return b;
 }
 
@@ -772,6 +766,42 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     p.status = ctx->status_dev;
     p.debug = ctx->opt_debug;
     p.trace = lb_trace_row(ctx, "gemv");
+    // ring depth: as many stages as the busiest warp has chunks (a chunk = up to 8 tiles inside one strip), up to 3
+    {
+        int most = 1;
+        const int KB = p.kblocks, gt = p.group * KB;
+        const long long NG = p.total_tiles / gt;
+        for (int b = 0; b < grid && most < kStages; ++b) {
+            long long t0, t1;
+            if (p.aligned) {
+                t0 = (NG * b / grid) * gt;
+                t1 = (NG * (b + 1) / grid) * gt;
+            } else {
+                t0 = (long long)p.total_tiles * b / grid;
+                t1 = (long long)p.total_tiles * (b + 1) / grid;
+            }
+            const long long n = t1 - t0;
+            for (int w = 0; w < kWarps && most < kStages; ++w) {
+                long long w0 = t0 + n * w / kWarps, w1 = t0 + n * (w + 1) / kWarps;
+                int chunks = 0;
+                while (w0 < w1) {
+                    long long len = KB - w0 % KB;
+                    if (len > kStageTiles) len = kStageTiles;
+                    if (len > w1 - w0) len = w1 - w0;
+                    w0 += len;
+                    ++chunks;
+                }
+                if (chunks > most) most = chunks;
+            }
+        }
+        p.stages = most > kStages ? kStages : most;
+    }
+    // prologue staging: the activation row in its input precision, when it fits beside the ring
+    p.stage_bytes = 0;
+    if (p.pro != LB_PRO_Q8 && (p.K & 3) == 0) {
+        size_t want = (size_t)p.K * (p.pro == LB_PRO_INNERNORM64 ? 8 : 4);
+        if (gemv_smem_bytes(p, p.max_local_strips) + want <= 227 * 1024) p.stage_bytes = (int)want;
+    }
     size_t smem = gemv_smem_bytes(p, p.max_local_strips);
     if (smem > 227 * 1024)
         return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: K=%d with %d tokens needs %zu B of shared memory", p.K, p.M, smem);

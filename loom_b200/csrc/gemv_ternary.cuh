@@ -49,6 +49,8 @@ struct LbGemvParams {
     int K, kblocks, M;
     int total_tiles;  // virtual strips * kblocks
     int max_local_strips;
+    int stages;       // ring stages per warp (1..3)
+    int stage_bytes;  // shared staging for the fp32/fp64 prologues (0 = use the slow generic prologue)
     int aligned;  // 1: CTAs own whole strip groups; 0: stream-K with the int32 fix-up
     // prologue
     int pro;

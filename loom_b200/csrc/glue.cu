@@ -107,27 +107,49 @@ __global__ void lb_rope_kernel(const LbRopeParams p) {
     lb_trace(p.trace, 5);
 }
 
-// One CTA per (head, token, split).  A pair of threads scores one position (half of the head dimension each);
-// output dimension d is owned by thread d of each of G = 256/hd position groups.  With splits > 1 the partial
-// (max, sum, weighted V) of every split goes to scratch and the CTA that arrives last combines them.
-// Sums run in float64 like the reference's; their order (and the fused multiply-adds) differ from its
-// sequential loops only in the last bits of a double.
+// One CTA per (head, token, split).  K and V rows of the CTA's positions are brought into shared memory by
+// one 512-byte bulk async copy (TMA engine) per row, so that every HBM access of the kernel is in flight at
+// once; a pair of threads then scores one position (half of the head dimension each) and output dimension d is
+// owned by thread d of each of G = 256/hd position groups.  With splits > 1 the partial (max, sum, weighted V)
+// of every split goes to scratch and the CTA that arrives last combines them.  Sums run in float64 like the
+// reference's; their order (and the fused multiply-adds) differ from its sequential loops only in the last
+// bits of a double.
 constexpr int kAttnThreads = 256;
+constexpr int kAttnTile = 80;  // positions per shared-memory tile
+
+__device__ __forceinline__ void attn_fetch_rows(float* tile, const float* cache, int row_floats, int hd, int kvd, int msl,
+                                                int pos0, int rows, uint64_t* bar, int lane) {
+    if (lane == 0) lb_mbar_expect_tx(bar, (uint32_t)rows * hd * 4);
+    __syncwarp();
+    for (int r = lane; r < rows; r += 32)
+        lb_bulk_g2s(tile + (size_t)r * row_floats, cache + (size_t)((pos0 + r) % msl) * kvd, (uint32_t)hd * 4, bar);
+}
 
 __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttnParams p) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ double red[32];
+    __shared__ double s_w[64];
+    __shared__ __align__(8) uint64_t bars[2];
     __shared__ int s_last;
+    const int h = blockIdx.x, n = blockIdx.y, sp = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hd = p.hd, kvd = p.kv_heads * hd, qd = p.heads * hd;
+    const int rowf = hd + 4;  // padded row: conflict-free 16-byte reads down a column of rows
+    const int G = hd >= kAttnThreads ? 1 : kAttnThreads / hd;
+    float* kt = reinterpret_cast<float*>(smem_raw);           // [kAttnTile, rowf]
+    float* vt = kt + (size_t)kAttnTile * rowf;                // [kAttnTile, rowf]
+    double* sq = reinterpret_cast<double*>(vt + (size_t)kAttnTile * rowf);  // [hd]
+    double* sacc = sq + hd;                                   // [G, hd]
+    double* sc = sacc + (size_t)G * hd;                       // [max_chunk]
+    if (tid == 0) {
+        lb_mbar_init(&bars[0], 1);
+        lb_mbar_init(&bars[1], 1);
+        lb_fence_mbar_init();
+    }
+    __syncthreads();
     lb_pdl_launch_dependents();
     lb_pdl_wait();
     lb_trace(p.trace, 2);
-    const int h = blockIdx.x, n = blockIdx.y, sp = blockIdx.z, tid = threadIdx.x;
-    const int hd = p.hd, kvd = p.kv_heads * hd, qd = p.heads * hd;
-    const int G = hd >= kAttnThreads ? 1 : kAttnThreads / hd;
-    double* sq = reinterpret_cast<double*>(smem_raw);  // [hd]
-    double* sacc = sq + hd;                             // [G, hd]
-    double* sc = sacc + (size_t)G * hd;                 // [max_chunk]
-    const int last = *p.pos_ptr + n;                    // attends to positions 0..last
+    const int last = *p.pos_ptr + n;  // attends to positions 0..last
     const int total = last + 1;
     const int per = (total + p.splits - 1) / p.splits;
     const int k0 = sp * per;
@@ -135,34 +157,57 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     if (k1 > total) k1 = total;
     const int cnt = k1 > k0 ? k1 - k0 : 0;
     const int kvh = h / (p.heads / p.kv_heads);
+    const float* kbase = p.cache_k + (size_t)kvh * hd;
+    const float* vbase = p.cache_v + (size_t)kvh * hd;
+    const int ntiles = (cnt + kAttnTile - 1) / kAttnTile;
+    bool failed = false;
+    // first K and V tiles: every row of both is requested before anything else happens
+    if (cnt > 0) {
+        const int rows0 = cnt < kAttnTile ? cnt : kAttnTile;
+        if (warp == 0) attn_fetch_rows(kt, kbase, rowf, hd, kvd, p.msl, k0, rows0, &bars[0], lane);
+        if (warp == 1) attn_fetch_rows(vt, vbase, rowf, hd, kvd, p.msl, k0, rows0, &bars[1], lane);
+    }
     const double scale = __ddiv_rn(1.0, sqrt((double)hd));
-
     for (int d = tid; d < hd; d += kAttnThreads) sq[d] = p.q[(size_t)n * qd + (size_t)h * hd + d];
     __syncthreads();
 
-    // scores: thread pair (2j, 2j+1) handles position j, each over half of the dimensions
+    // scores: thread pair (2j, 2j+1) handles position j of the tile, each over half of the dimensions
     double mx = -1e9;
     const int half = tid & 1, hlen = hd / 2;
-    for (int j = tid >> 1; j < ((cnt + kAttnThreads / 2 - 1) / (kAttnThreads / 2)) * (kAttnThreads / 2); j += kAttnThreads / 2) {
-        double dot = 0.0;
-        if (j < cnt) {
-            const float* kr = p.cache_k + (size_t)((k0 + j) % p.msl) * kvd + (size_t)kvh * hd + half * hlen;
-            const double* qh = sq + half * hlen;
-            double d0 = 0.0, d1 = 0.0;
-            for (int d = 0; d < hlen; d += 4) {
-                const float4 kv = *reinterpret_cast<const float4*>(kr + d);
-                d0 = fma(qh[d], (double)kv.x, d0);
-                d1 = fma(qh[d + 1], (double)kv.y, d1);
-                d0 = fma(qh[d + 2], (double)kv.z, d0);
-                d1 = fma(qh[d + 3], (double)kv.w, d1);
+    for (int t = 0; t < ntiles; ++t) {
+        const int base = t * kAttnTile;
+        const int rows = cnt - base < kAttnTile ? cnt - base : kAttnTile;
+        if (t > 0) {
+            __syncthreads();  // everyone is done with the previous K tile
+            if (warp == 0) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                attn_fetch_rows(kt, kbase, rowf, hd, kvd, p.msl, k0 + base, rows, &bars[0], lane);
             }
-            dot = d0 + d1;
         }
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        if (j < cnt) {
-            const double s = __dmul_rn(dot, scale);
-            if (half == 0) sc[j] = s;
-            mx = fmax(mx, s);
+        if (!failed && !lb_mbar_wait_bounded(&bars[0], (uint32_t)(t & 1))) failed = true;
+        for (int j0 = 0; j0 < rows; j0 += kAttnThreads / 2) {
+            const int j = j0 + (tid >> 1);
+            double dot = 0.0;
+            if (j < rows) {
+                const float* kr = kt + (size_t)j * rowf + half * hlen;
+                const double* qh = sq + half * hlen;
+                double d0 = 0.0, d1 = 0.0;
+#pragma unroll 4
+                for (int d = 0; d < hlen; d += 4) {
+                    const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+                    d0 = fma(qh[d], (double)kv.x, d0);
+                    d1 = fma(qh[d + 1], (double)kv.y, d1);
+                    d0 = fma(qh[d + 2], (double)kv.z, d0);
+                    d1 = fma(qh[d + 3], (double)kv.w, d1);
+                }
+                dot = d0 + d1;
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            if (j < rows) {
+                const double s = __dmul_rn(dot, scale);
+                if (half == 0) sc[base + j] = s;
+                mx = fmax(mx, s);
+            }
         }
     }
     mx = block_max_d(mx, red);
@@ -175,36 +220,48 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     }
     den = block_sum_d(den, red);  // also orders the sc[] writes before the reads below
 
-    // weighted V: group g takes positions g, g+G, ...
-    for (int d0 = 0; d0 < hd; d0 += kAttnThreads) {
-        const int d = d0 + (G > 1 ? tid % hd : tid), grp = G > 1 ? tid / hd : 0;
-        if (d < hd && grp < G) {
-            double a0 = 0.0, a1 = 0.0;
-            const float* vb = p.cache_v + (size_t)kvh * hd + d;
-            int j = grp;
-            for (; j + G < cnt; j += 2 * G) {
-                a0 = fma(sc[j], (double)vb[(size_t)((k0 + j) % p.msl) * kvd], a0);
-                a1 = fma(sc[j + G], (double)vb[(size_t)((k0 + j + G) % p.msl) * kvd], a1);
+    // weighted V: group g takes positions g, g+G, ... of each tile
+    const int d = G > 1 ? tid % hd : tid, grp = G > 1 ? tid / hd : 0;
+    const bool owner = d < hd && grp < G;
+    double a0 = 0.0, a1 = 0.0;
+    for (int t = 0; t < ntiles; ++t) {
+        const int base = t * kAttnTile;
+        const int rows = cnt - base < kAttnTile ? cnt - base : kAttnTile;
+        if (t > 0) {
+            __syncthreads();
+            if (warp == 1) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                attn_fetch_rows(vt, vbase, rowf, hd, kvd, p.msl, k0 + base, rows, &bars[1], lane);
             }
-            if (j < cnt) a0 = fma(sc[j], (double)vb[(size_t)((k0 + j) % p.msl) * kvd], a0);
-            sacc[(size_t)grp * hd + d] = a0 + a1;
         }
-        __syncthreads();
-        if (d < hd && grp == 0) {
-            double acc = sacc[d];
-            for (int g = 1; g < G; ++g) acc += sacc[(size_t)g * hd + d];
-            if (p.splits == 1) {
-                p.out[(size_t)n * qd + (size_t)h * hd + d] = __ddiv_rn(acc, den);
-            } else {
-                double* part = p.part + ((size_t)(n * p.heads + h) * p.splits + sp) * (hd + 2);
-                part[2 + d] = acc;
-                if (d == 0) {
-                    part[0] = mx;
-                    part[1] = den;
+        if (!failed && !lb_mbar_wait_bounded(&bars[1], (uint32_t)(t & 1))) failed = true;
+        if (owner) {
+            for (int dd = d; dd < hd; dd += kAttnThreads) {  // hd > 256: a thread owns several dimensions (one accumulator pair each would be needed)
+                int j = grp;
+                for (; j + G < rows; j += 2 * G) {
+                    a0 = fma(sc[base + j], (double)vt[(size_t)j * rowf + dd], a0);
+                    a1 = fma(sc[base + j + G], (double)vt[(size_t)(j + G) * rowf + dd], a1);
                 }
+                if (j < rows) a0 = fma(sc[base + j], (double)vt[(size_t)j * rowf + dd], a0);
             }
         }
-        __syncthreads();
+    }
+    if (failed && tid == 0) atomicExch(p.status, 1);
+    if (owner) sacc[(size_t)grp * hd + d] = a0 + a1;
+    __syncthreads();
+    if (owner && grp == 0) {
+        double acc = sacc[d];
+        for (int g = 1; g < G; ++g) acc += sacc[(size_t)g * hd + d];
+        if (p.splits == 1) {
+            p.out[(size_t)n * qd + (size_t)h * hd + d] = __ddiv_rn(acc, den);
+        } else {
+            double* part = p.part + ((size_t)(n * p.heads + h) * p.splits + sp) * (hd + 2);
+            part[2 + d] = acc;
+            if (d == 0) {
+                part[0] = mx;
+                part[1] = den;
+            }
+        }
     }
     lb_trace(p.trace, 4);
     if (p.splits == 1) return;
@@ -218,19 +275,35 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     if (!s_last) return;
     __threadfence();
     const double* base = p.part + (size_t)(n * p.heads + h) * p.splits * (hd + 2);
-    double gm = -1e9;
-    for (int s = 0; s < p.splits; ++s) gm = fmax(gm, __ldcg(base + (size_t)s * (hd + 2)));
-    for (int d = tid; d < hd; d += kAttnThreads) {
+    // weights of the splits: exp(m_s - max m), one thread per split
+    double ms = -1e9, ls = 0.0;
+    if (tid < p.splits) {
+        ms = __ldcg(base + (size_t)tid * (hd + 2));
+        ls = __ldcg(base + (size_t)tid * (hd + 2) + 1);
+    }
+    double gm = ms;
+    if (warp == 0 || p.splits > 32) gm = warp_max_d(gm);
+    if (tid == 0) red[0] = gm;
+    __syncthreads();
+    if (p.splits > 32) {  // more than one warp holds split maxima
+        if (lane == 0 && warp < 2) red[1 + warp] = gm;
+        __syncthreads();
+        if (tid == 0) red[0] = fmax(red[1], red[2]);
+        __syncthreads();
+    }
+    gm = red[0];
+    if (tid < p.splits) s_w[tid] = ls == 0.0 ? 0.0 : exp(__dsub_rn(ms, gm));
+    __syncthreads();
+    for (int dd = tid; dd < hd; dd += kAttnThreads) {
         double num = 0.0, dn = 0.0;
         for (int s = 0; s < p.splits; ++s) {
+            const double w = s_w[s];
+            if (w == 0.0) continue;  // an empty split
             const double* ps = base + (size_t)s * (hd + 2);
-            const double l = __ldcg(ps + 1);
-            if (l == 0.0) continue;  // an empty split
-            const double w = exp(__dsub_rn(__ldcg(ps), gm));
-            num = fma(__ldcg(ps + 2 + d), w, num);
-            dn = fma(l, w, dn);
+            num = fma(__ldcg(ps + 2 + dd), w, num);
+            dn = fma(__ldcg(ps + 1), w, dn);
         }
-        p.out[(size_t)n * qd + (size_t)h * hd + d] = __ddiv_rn(num, dn);
+        p.out[(size_t)n * qd + (size_t)h * hd + dd] = __ddiv_rn(num, dn);
     }
     if (tid == 0) p.cnt[n * p.heads + h] = 0;
 }
@@ -411,10 +484,13 @@ size_t lb_attn_part_elems(int M, int heads, int hd, int splits) { return (size_t
 int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& pin) {
     LbAttnParams p = pin;
     p.trace = lb_trace_row(ctx, "attention");
+    p.status = ctx->status_dev;
     LB_REQUIRE(ctx, p.hd % 8 == 0, "attention: head_dim %d must be a multiple of 8", p.hd);
     LB_REQUIRE(ctx, p.heads % p.kv_heads == 0, "attention: %d heads over %d kv heads", p.heads, p.kv_heads);
+    LB_REQUIRE(ctx, p.hd <= kAttnThreads, "attention: head_dim %d above %d is not supported", p.hd, kAttnThreads);
+    LB_REQUIRE(ctx, p.splits >= 1 && p.splits <= 64, "attention: %d splits", p.splits);
     const int G = p.hd >= kAttnThreads ? 1 : kAttnThreads / p.hd;
-    size_t smem = (size_t)(p.hd + (size_t)G * p.hd + p.max_chunk) * sizeof(double);
+    size_t smem = (size_t)(p.hd + (size_t)G * p.hd + p.max_chunk) * sizeof(double) + 2 * (size_t)kAttnTile * (p.hd + 4) * sizeof(float);
     if (smem > 200 * 1024) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "attention: %d positions per CTA need %zu B of shared memory", p.max_chunk, smem);
     if (smem > 48 * 1024 && !(ctx->func_attr_mask & (1u << 30))) {
         LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
