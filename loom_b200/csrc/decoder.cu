@@ -144,6 +144,10 @@ int loom_b200_decoder_create(loom_b200_ctx* ctx, const loom_b200_decoder_dims* d
     if (dec->d.num_kv_heads == 0) dec->d.num_kv_heads = d.num_heads;
     if (dec->d.max_seq_len <= 0) dec->d.max_seq_len = 2048;  // NewTransformer default, poly/transformer.go:111-113
     dec->blocks.resize(d.num_layers);
+    // attention splits for one-token steps: heads x splits CTAs should be resident together (two per SM)
+    dec->decode_splits = (2 * ctx->sm_count) / d.num_heads;
+    if (dec->decode_splits > 16) dec->decode_splits = 16;
+    if (dec->decode_splits < 1) dec->decode_splits = 1;
     dec->out_cap = dec->d.max_seq_len;
     cudaError_t e = cudaSuccess;
     auto A = [&](void** p, size_t bytes) {
