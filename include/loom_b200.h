@@ -154,6 +154,23 @@ int loom_b200_ternary_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, int 
                              const float* amax, const float* bias, const float* residual, int activation,
                              float* out, int32_t* acc_out);
 
+/* No counterpart in the reference.  The same computation as loom_b200_ternary_linear (without the raw
+ * accumulator output) for hosts that must not allocate device memory while they run inference: an embedder
+ * with a fixed, already-spent device-memory budget, a frame loop that promised "no allocation after load", or
+ * code running where the CUDA allocator may not be entered.  The regular entry point may grow its fix-up
+ * scratch with cudaMalloc when a larger shape first arrives; this one keeps that scratch in a fixed
+ * 1.02 MiB array inside the library image (held by every GPU that loads the library until the process exits)
+ * and calls no cudaMalloc, cudaFree or allocating routine.
+ *   Limits: rows <= 65,536 and 16*ceil(rows/16)*min(batch,8) <= 262,144; beyond them the call fails with
+ *   LOOM_B200_ERR_UNSUPPORTED and a message naming loom_b200_ternary_linear.
+ *   The first call on a device looks the array's address up (cudaGetSymbolAddress); make that call before
+ *   starting any stream capture.  Every call clears the part of the array it is about to use.  The array is
+ *   shared by all contexts of the process: two calls whose GPU work overlaps in time (different streams or
+ *   contexts on the same device) race on it -- run them one after the other. */
+int loom_b200_ternary_linear_no_alloc(loom_b200_ctx* ctx, const loom_b200_weight* w, int batch, const int8_t* q,
+                                      const float* amax, const float* bias, const float* residual, int activation,
+                                      float* out);
+
 /* WGPUContext.DispatchBitNetGateProduct(batch, hidden, act, gate, up, out), poly/wgpu_kernels.go:477-507;
  * arithmetic of swigluGateProduct in float64, poly/swiglu.go:37-46 */
 int loom_b200_gate_product(loom_b200_ctx* ctx, int batch, int hidden, int activation, const float* gate,

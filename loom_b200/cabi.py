@@ -65,6 +65,7 @@ SIGNATURES = {
     "loom_b200_quantize_activation": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "loom_b200_quantize_activation_f64": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "loom_b200_ternary_linear": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
+    "loom_b200_ternary_linear_no_alloc": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp]),
     "loom_b200_gate_product": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "loom_b200_inner_rmsnorm": (_i, [_vp, _i, _i, _vp, _vp, _i, _d]),
     "loom_b200_dense_forward": (_i, [_vp, _vp, _i, _vp, _i, _vp, _vp]),
@@ -288,6 +289,11 @@ class Context:
     def ternary_linear(self, w: Weight, batch, q, amax, out, bias=None, residual=None, act=ACT_LINEAR, acc_out=None):
         self._check(lib().loom_b200_ternary_linear(self.h, w.h, batch, _ptr(q), _ptr(amax), _ptr(bias),
                                                    _ptr(residual), act, _ptr(out), _ptr(acc_out)))
+
+    def ternary_linear_no_alloc(self, w: Weight, batch, q, amax, out, bias=None, residual=None, act=ACT_LINEAR):
+        """The ternary linear with its scratch in the library's built-in array: allocates nothing."""
+        self._check(lib().loom_b200_ternary_linear_no_alloc(self.h, w.h, batch, _ptr(q), _ptr(amax), _ptr(bias),
+                                                            _ptr(residual), act, _ptr(out)))
 
     def gate_product(self, batch, hidden, act, gate, up, out):
         self._check(lib().loom_b200_gate_product(self.h, batch, hidden, act, _ptr(gate), _ptr(up), _ptr(out)))
