@@ -5,7 +5,7 @@ ternary decoder (30 blocks, hidden 2560, FFN 6912, 20 query / 5 KV heads x 128, 
 A step is one decode token.  Weights are synthetic (seeded N(0, 0.02) masters ternarised per matrix by absmean
 on the device); the prompt is seeded uniform token ids.  One JSON line is printed by rank 0.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--prompt P] [--layers L]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--prompt P] [--layers L] [--vocab V]
 
 N > 1: the 2B shape has 5 KV heads, which no tensor-parallel degree above 1 divides, so every rank runs an
 independent replica ("replicas only", weak scaling) and the value is the sum over ranks.
@@ -210,6 +210,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=SHAPE["layers"])
+    ap.add_argument("--vocab", type=int, default=SHAPE["vocab"], help="smaller vocabularies are for profiling captures only")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -218,7 +219,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    shape = dict(SHAPE, layers=args.layers)
+    shape = dict(SHAPE, layers=args.layers, vocab=args.vocab)
 
     if args.impl == "reference" and rank != 0:
         return 0
