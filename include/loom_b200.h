@@ -154,6 +154,15 @@ int loom_b200_ternary_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, int 
                              const float* amax, const float* bias, const float* residual, int activation,
                              float* out, int32_t* acc_out);
 
+/* The batched (prompt) form of DispatchBitNetQuantizeActivation + DispatchDenseBitNetTernaryQuantized
+ * (poly/wgpu_forward.go:167-180, poly/wgpu_kernels.go:384-475) as one tensor-core GEMM: x [tokens, cols] fp32 on the
+ * device is quantized per token (absmax int8, poly/bitnet_cpu.go:45-106) and multiplied with the packed ternary
+ * matrix on tcgen05 (kind::i8, int32 accumulators in tensor memory); the epilogue is the one of
+ * loom_b200_ternary_linear.  out [tokens, rows] fp32 and/or acc_out [tokens, rows] int32; amax_out [tokens] or NULL.
+ * Same bits as the per-token path. */
+int loom_b200_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const float* x, const float* bias,
+                           const float* residual, int activation, float* out, int32_t* acc_out, float* amax_out);
+
 /* A frame of DispatchDenseBitNetTernaryQuantized calls (BeginFrame ... FlushFrame, poly/wgpu_context_native.go:263-276,
  * poly/wgpu_kernels.go:416-475) compiled into a program that ONE persistent launch executes: a CTA per SM walks
  * the jobs in order and streams every job's packed weights through shared memory several jobs ahead, so HBM

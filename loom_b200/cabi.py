@@ -65,6 +65,7 @@ SIGNATURES = {
     "loom_b200_quantize_activation": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "loom_b200_quantize_activation_f64": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "loom_b200_ternary_linear": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
+    "loom_b200_ternary_gemm": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp]),
     "loom_b200_linear_program_create": (_i, [_vp, _i, _vp, C.POINTER(_vp)]),
     "loom_b200_program_run": (_i, [_vp, _vp]),
     "loom_b200_program_bytes": (C.c_uint64, [_vp]),
@@ -303,6 +304,10 @@ class Context:
         """The ternary linear with its scratch in the library's built-in array: allocates nothing."""
         self._check(lib().loom_b200_ternary_linear_no_alloc(self.h, w.h, batch, _ptr(q), _ptr(amax), _ptr(bias),
                                                             _ptr(residual), act, _ptr(out)))
+
+    def ternary_gemm(self, w: Weight, tokens, x, out=None, bias=None, residual=None, act=ACT_LINEAR, acc_out=None, amax_out=None):
+        self._check(lib().loom_b200_ternary_gemm(self.h, w.h, tokens, _ptr(x), _ptr(bias), _ptr(residual), act, _ptr(out),
+                                                 _ptr(acc_out), _ptr(amax_out)))
 
     def linear_program(self, jobs):
         """jobs: list of dicts(w, batch, q, amax, out, bias=None, residual=None, act=ACT_LINEAR, depends=False)."""

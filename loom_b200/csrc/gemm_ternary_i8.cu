@@ -1,0 +1,328 @@
+// gemm_ternary_i8.cu -- batched-prefill ternary x int8 GEMM on the 5th-generation tensor cores (tcgen05, kind::i8).
+//
+// For a block of tokens the projection really is a dense contraction, so it runs on tcgen05.mma with the int32
+// accumulator in tensor memory.  Replaces the per-token re-read of the weight row that
+// ShaderTiledDenseBitNetTernaryQuantizedReduce does for prompts (poly/wgpu_shaders.go:512-642, dispatched once
+// per (row, token) by poly/wgpu_kernels.go:416-475); arithmetic contract poly/bitnet_cpu.go:536-546,752-776.
+//
+//   D[128 weight rows, 128 tokens] (int32, TMEM) += A[128, 32] (u8 codes 0/1/2, shared) * B[128 tokens, 32]^T (s8, shared)
+//
+//   * A: the 2-bit packed tiles are expanded to one byte per weight by four producer warps:
+//     (word >> 2j) & 0x03030303 for j = 0..3 -- four instructions per 16 weights, no transpose: byte b of
+//     result j is the code of column 4b+j, and the activation bytes are stored in the same order by the
+//     quantizer that feeds this kernel, so the K permutation cancels in the dot product.
+//     Codes stay unsigned (kind::i8 takes u8 x s8): sum(code*x) - sum(x) = sum(w*x), the same correction as
+//     the GEMV, applied in the epilogue from the per-token sum the quantizer produced.
+//   * B: int8 activations [tokens, Kp] in global memory, copied with 16-byte cp.async into the canonical
+//     K-major no-swizzle core-matrix layout (8 rows x 16 bytes contiguous; LBO = 128 B along K, SBO = 1024 B
+//     along rows) -- the same layout the producers write A in.
+//   * A four-stage ring of (A, B) K-slices of 128 columns; one elected thread issues four K=32 MMAs per stage
+//     and commits them to the stage's "empty" mbarrier; the last commit releases the epilogue.
+//   * Epilogue: the producer warps read their 32 TMEM lanes (= weight rows) with tcgen05.ld and apply the
+//     float64 rescale, bias, activation and residual exactly like the GEMV epilogue.
+// Every mbarrier wait is bounded; on expiry the kernel raises the context's status word, frees its tensor
+// memory and returns.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kRowsPerCta = 128;   // weight rows = TMEM lanes = MMA M
+constexpr int kTokPerCta = 128;    // tokens = TMEM columns = MMA N
+constexpr int kSliceK = 128;       // K columns (= bytes) per pipeline stage
+constexpr int kGemmStages = 4;
+constexpr int kProducerThreads = 128;
+constexpr int kGemmThreads = kProducerThreads + 32;  // + the MMA warp
+constexpr int kSliceBytesA = kRowsPerCta * kSliceK;  // 16 KB
+constexpr int kSliceBytesB = kTokPerCta * kSliceK;   // 16 KB
+constexpr uint32_t kWaitLimit = 20000000u;
+
+struct GemmParams {
+    const uint32_t* tiles;   // packed weights, tiled layout
+    int rows, strips, kblocks;
+    float scale;
+    const int8_t* q;         // [tokens, Kp] int8 in the kernel's K order (see lb_quantize_gemm_kernel)
+    const float* amax;       // [tokens]
+    const int* xsum;         // [tokens]
+    int tokens, Kp;
+    const float* bias;       // [rows] or null
+    const float* residual;   // [tokens, rows] or null
+    int act;
+    float* out;              // [tokens, rows] or null
+    int32_t* acc_out;        // [tokens, rows] or null
+    int* status;
+};
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    // K-major, no swizzle: start address, LBO = 128 B (next 16-byte K chunk), SBO = 1024 B (next 8 rows), version 1
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46);
+}
+
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(lb_smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(lb_smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i)
+        if (lb_mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// activation bytes (tokens x Kp int8) -> shared core-matrix layout; rows beyond `tokens` are zero-filled
+__device__ __forceinline__ void copy_b_slice(uint8_t* dst, const int8_t* q, int tok0, int tokens, int Kp, int k0, int tid) {
+    for (int c = tid; c < kTokPerCta * (kSliceK / 16); c += kProducerThreads) {
+        const int row = c >> 3, kc = c & 7;
+        const int tok = tok0 + row;
+        const bool ok = tok < tokens;
+        const int8_t* src = q + (size_t)(ok ? tok : 0) * Kp + k0 + kc * 16;
+        const uint32_t d = lb_smem_u32(dst + (row >> 3) * 1024 + kc * 128 + (row & 7) * 16);
+        const int bytes = ok ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+    }
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bar[kGemmStages], empty_bar[kGemmStages], done_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ double s_os[kTokPerCta];
+    __shared__ int s_xsum[kTokPerCta];
+    __shared__ int s_failed;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row0 = blockIdx.x * kRowsPerCta, tok0 = blockIdx.y * kTokPerCta;
+    uint8_t* a_ring = smem;
+    uint8_t* b_ring = smem + kGemmStages * kSliceBytesA;
+    const int nslices = p.kblocks;  // one 128-column k-block per stage
+
+    if (tid == 0) {
+        for (int s = 0; s < kGemmStages; ++s) {
+            lb_mbar_init(&full_bar[s], kProducerThreads);
+            lb_mbar_init(&empty_bar[s], 1);
+        }
+        lb_mbar_init(&done_bar, 1);
+        lb_fence_mbar_init();
+        s_failed = 0;
+    }
+    if (warp == 4) {  // the MMA warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lb_smem_u32(&tmem_base_s)), "r"(kTokPerCta) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp < 4) {
+        // ---------------- producers: expand A, copy B ----------------
+        for (int i = tid; i < kTokPerCta; i += kProducerThreads) {
+            const int tok = tok0 + i;
+            s_os[i] = tok < p.tokens ? lb_output_scale(p.scale, p.amax[tok]) : 0.0;
+            s_xsum[i] = tok < p.tokens ? p.xsum[tok] : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the per-token scales are read by other producer warps later
+        const int g = lane >> 2, t = lane & 3;
+        bool failed = false;
+        for (int ks = 0; ks < nslices; ++ks) {
+            const int s = ks % kGemmStages;
+            if (ks >= kGemmStages && !failed && !wait_bounded(&empty_bar[s], (uint32_t)((ks / kGemmStages - 1) & 1))) failed = true;
+            uint8_t* a_dst = a_ring + (size_t)s * kSliceBytesA;
+            uint8_t* b_dst = b_ring + (size_t)s * kSliceBytesB;
+            copy_b_slice(b_dst, p.q, tok0, p.tokens, p.Kp, ks * kSliceK, tid);
+            // A: this warp expands strips 2*warp and 2*warp+1 of the 128-row block
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int sl = 2 * warp + h;  // strip inside the block (16 rows each)
+                const int strip = blockIdx.x * (kRowsPerCta / kTileRows) + sl;
+                uint4 w = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
+                if (strip < p.strips) w = reinterpret_cast<const uint4*>(p.tiles + ((size_t)strip * p.kblocks + ks) * kTileWords)[lane];
+                // lane (g,t) holds [row g, word t] [row g+8, word t] [row g, word 4+t] [row g+8, word 4+t]
+                const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int row = sl * 16 + g + 8 * (k & 1);  // row inside the 128-row block
+                    const int kc = t + 4 * (k >> 1);            // 16-byte K chunk inside the slice
+                    const uint32_t x = words[k];
+                    const uint4 e = make_uint4(x & 0x03030303u, (x >> 2) & 0x03030303u, (x >> 4) & 0x03030303u, (x >> 6) & 0x03030303u);
+                    *reinterpret_cast<uint4*>(a_dst + (row >> 3) * 1024 + kc * 128 + (row & 7) * 16) = e;
+                }
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
+            mbar_arrive(&full_bar[s]);
+        }
+        // ---------------- epilogue ----------------
+        if (!failed && !wait_bounded(&done_bar, 0)) failed = true;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (failed) atomicExch(&s_failed, 1);
+        const int r = row0 + warp * 32 + lane;
+        const bool row_ok = r < p.rows;
+        const double bias = (row_ok && p.bias) ? (double)p.bias[r] : 0.0;
+        for (int c0 = 0; c0 < kTokPerCta; c0 += 32) {
+            uint32_t v[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                  "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                  "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                  "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                : "r"(taddr)
+                : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row_ok && !failed) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int tok = tok0 + c0 + j;
+                    if (tok >= p.tokens) break;
+                    const int acc = (int)v[j] - s_xsum[c0 + j];
+                    const size_t o = (size_t)tok * p.rows + r;
+                    if (p.acc_out) p.acc_out[o] = acc;
+                    if (p.out) {
+                        double y = __dmul_rn((double)acc, s_os[c0 + j]);
+                        if (p.bias) y = __dadd_rn(y, bias);
+                        float f = (float)y;
+                        if (p.act == LOOM_B200_ACT_RELU) f = f < 0.f ? 0.f : f;
+                        else if (p.act == LOOM_B200_ACT_RELU2) f = f < 0.f ? 0.f : __fmul_rn(f, f);
+                        else if (p.act != LOOM_B200_ACT_LINEAR) f = lb_activate(f, p.act);
+                        if (p.residual) f = __fadd_rn(f, p.residual[o]);
+                        p.out[o] = f;
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    } else {
+        // ---------------- MMA issuer ----------------
+        // instruction descriptor: D = S32, A = U8, B = S8, both K-major, N = 128, M = 128
+        const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(kTokPerCta >> 3) << 17) | ((uint32_t)(kRowsPerCta >> 4) << 24);
+        bool failed = false;
+        for (int ks = 0; ks < nslices; ++ks) {
+            const int s = ks % kGemmStages;
+            if (!failed && !wait_bounded(&full_bar[s], (uint32_t)((ks / kGemmStages) & 1))) failed = true;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (lane == 0 && !failed) {
+                const uint32_t a_addr = lb_smem_u32(a_ring + (size_t)s * kSliceBytesA);
+                const uint32_t b_addr = lb_smem_u32(b_ring + (size_t)s * kSliceBytesB);
+#pragma unroll
+                for (int k = 0; k < kSliceK / 32; ++k)  // K = 32 per instruction = two 16-byte chunks = 256 B further
+                    mma_i8(tmem_base, smem_desc(a_addr + k * 256), smem_desc(b_addr + k * 256), idesc, (ks > 0 || k > 0) ? 1u : 0u);
+                mma_commit(&empty_bar[s]);  // arrives when the MMAs that read this stage are done
+            }
+            __syncwarp();
+        }
+        if (lane == 0) {
+            if (failed) atomicExch(&s_failed, 1);
+            mma_commit(&done_bar);
+        }
+        __syncwarp();
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 4) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTokPerCta) : "memory");
+    }
+    if (tid == 0 && s_failed) atomicExch(p.status, 3);
+}
+
+// Quantizer of the GEMM path: same arithmetic as lb_quantize_kernel, but the bytes of every 16-column group are
+// stored in the order the A expansion produces (position 4j+b holds column 4b+j), rows are padded with zeros
+// to Kp, and the per-token sum of the quantized values is written next to amax.
+__global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const float* __restrict__ x, int K, int Kp, int8_t* __restrict__ q,
+                                                               float* __restrict__ amax_out, int* __restrict__ xsum_out) {
+    __shared__ float red[8];
+    __shared__ int redi[8];
+    const float* row = x + (size_t)blockIdx.x * K;
+    int8_t* qrow = q + (size_t)blockIdx.x * Kp;
+    float m = 0.0f;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) m = fmaxf(m, fabsf(row[i]));
+    m = lb_warp_max(m);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = red[0];
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+    if (m < 1e-5f) m = 1e-5f;
+    const double s = __ddiv_rn(127.0, (double)m);
+    int sum = 0;
+    for (int c = threadIdx.x; c < Kp; c += blockDim.x) {
+        // destination byte c of the row: group base + 4j + b  <-  column base + 4b + j
+        const int base = c & ~15, pos = c & 15, j = pos >> 2, b = pos & 3;
+        const int col = base + 4 * b + j;
+        int v = 0;
+        if (col < K) v = lb_quant_i8((double)row[col], s);
+        qrow[c] = (int8_t)v;
+        sum += v;
+    }
+    sum = lb_warp_sum_i(sum);
+    if ((threadIdx.x & 31) == 0) redi[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tot = 0;
+        for (int i = 0; i < 8; ++i) tot += redi[i];
+        amax_out[blockIdx.x] = m;
+        xsum_out[blockIdx.x] = tot;
+    }
+}
+
+}  // namespace
+
+extern "C" int loom_b200_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const float* x, const float* bias,
+                                      const float* residual, int activation, float* out, int32_t* acc_out, float* amax_out) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "ternary_gemm: ctx is NULL");
+    LB_REQUIRE(ctx, w != nullptr, "ternary_gemm: weight is NULL");
+    LB_REQUIRE(ctx, tokens >= 0, "ternary_gemm: tokens=%d", tokens);
+    if (tokens == 0) return 0;
+    LB_REQUIRE(ctx, x && (out || acc_out), "ternary_gemm: NULL buffer");
+    LB_REQUIRE(ctx, w->device == ctx->device, "ternary_gemm: weight lives on device %d, context on %d", w->device, ctx->device);
+    if (int rc = lb_set_device(ctx)) return rc;
+    const int Kp = w->kblocks * kTileCols;
+    // scratch: permuted int8 activations, amax, sum per token
+    size_t need = (size_t)tokens * Kp + 256 + (size_t)tokens * 8 + 256;
+    if (int rc = lb_ensure_scratch(ctx, need)) return rc;
+    int8_t* q = (int8_t*)ctx->scratch;
+    float* amax = (float*)((char*)ctx->scratch + (((size_t)tokens * Kp + 255) & ~(size_t)255));
+    int* xsum = (int*)(amax + tokens);
+    lb_quantize_gemm_kernel<<<tokens, 256, 0, ctx->stream>>>(x, w->cols, Kp, q, amax, xsum);
+    LB_CHECK_LAUNCH(ctx, "lb_quantize_gemm_kernel");
+    GemmParams p = {};
+    p.tiles = w->tiles;
+    p.rows = w->rows;
+    p.strips = w->strips;
+    p.kblocks = w->kblocks;
+    p.scale = w->scale;
+    p.q = q;
+    p.amax = amax;
+    p.xsum = xsum;
+    p.tokens = tokens;
+    p.Kp = Kp;
+    p.bias = bias;
+    p.residual = residual;
+    p.act = activation;
+    p.out = out;
+    p.acc_out = acc_out;
+    p.status = ctx->status_dev;
+    const size_t smem = (size_t)kGemmStages * (kSliceBytesA + kSliceBytesB) + 1024;
+    if (!(ctx->func_attr_mask & (1u << 27))) {
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        ctx->func_attr_mask |= 1u << 27;
+    }
+    dim3 grid((w->rows + kRowsPerCta - 1) / kRowsPerCta, (tokens + kTokPerCta - 1) / kTokPerCta);
+    lb_gemm_ternary_i8_kernel<<<grid, kGemmThreads, smem, ctx->stream>>>(p);
+    LB_CHECK_LAUNCH(ctx, "lb_gemm_ternary_i8_kernel");
+    if (amax_out) LB_CUDA(ctx, cudaMemcpyAsync(amax_out, amax, (size_t)tokens * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    return 0;
+}
