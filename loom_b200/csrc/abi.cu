@@ -347,6 +347,7 @@ void loom_b200_ctx_destroy(loom_b200_ctx* ctx) {
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->trace_dev) cudaFree(ctx->trace_dev);
     if (ctx->argmax_scratch) cudaFree(ctx->argmax_scratch);
+    if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }

@@ -56,6 +56,8 @@ struct loom_b200_ctx {
     size_t scratch_bytes = 0;
     // device status word written by kernels with bounded waits (0 = ok)
     int* status_dev = nullptr;
+    void* gemm_scratch = nullptr;    // int8 activations, amax and sums of the tensor-core GEMM path
+    size_t gemm_scratch_bytes = 0;
     void* argmax_scratch = nullptr;  // per-CTA partial maxima of the greedy argmax
     unsigned func_attr_mask = 0;  // kernels whose shared-memory limit was raised on this device
     // tuning knobs (loom_b200_ctx_set_option; initial values from LOOM_B200_* environment variables)

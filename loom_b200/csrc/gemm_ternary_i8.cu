@@ -48,6 +48,7 @@ struct GemmParams {
     const float* residual;   // [tokens, rows] or null
     int act;
     float* out;              // [tokens, rows] or null
+    float* pre_out;          // [tokens, rows] value before the activation, or null
     int32_t* acc_out;        // [tokens, rows] or null
     int* status;
 };
@@ -195,6 +196,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
                         double y = __dmul_rn((double)acc, s_os[c0 + j]);
                         if (p.bias) y = __dadd_rn(y, bias);
                         float f = (float)y;
+                        if (p.pre_out) p.pre_out[o] = f;
                         if (p.act == LOOM_B200_ACT_RELU) f = f < 0.f ? 0.f : f;
                         else if (p.act == LOOM_B200_ACT_RELU2) f = f < 0.f ? 0.f : __fmul_rn(f, f);
                         else if (p.act != LOOM_B200_ACT_LINEAR) f = lb_activate(f, p.act);
@@ -280,8 +282,16 @@ __global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const float* __re
 
 }  // namespace
 
+int lb_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const float* x, const float* bias,
+                    const float* residual, int activation, float* out, float* pre_out, int32_t* acc_out, float* amax_out);
+
 extern "C" int loom_b200_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const float* x, const float* bias,
                                       const float* residual, int activation, float* out, int32_t* acc_out, float* amax_out) {
+    return lb_ternary_gemm(ctx, w, tokens, x, bias, residual, activation, out, nullptr, acc_out, amax_out);
+}
+
+int lb_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const float* x, const float* bias,
+                    const float* residual, int activation, float* out, float* pre_out, int32_t* acc_out, float* amax_out) {
     if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "ternary_gemm: ctx is NULL");
     LB_REQUIRE(ctx, w != nullptr, "ternary_gemm: weight is NULL");
     LB_REQUIRE(ctx, tokens >= 0, "ternary_gemm: tokens=%d", tokens);
@@ -292,9 +302,17 @@ extern "C" int loom_b200_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight
     const int Kp = w->kblocks * kTileCols;
     // scratch: permuted int8 activations, amax, sum per token
     size_t need = (size_t)tokens * Kp + 256 + (size_t)tokens * 8 + 256;
-    if (int rc = lb_ensure_scratch(ctx, need)) return rc;
-    int8_t* q = (int8_t*)ctx->scratch;
-    float* amax = (float*)((char*)ctx->scratch + (((size_t)tokens * Kp + 255) & ~(size_t)255));
+    if (need > ctx->gemm_scratch_bytes) {  // its own buffer: layer calls keep their tensors in ctx->scratch
+        if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "ternary_gemm: scratch would grow while recording a graph");
+        LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+        ctx->gemm_scratch = nullptr;
+        ctx->gemm_scratch_bytes = 0;
+        LB_CUDA(ctx, cudaMalloc(&ctx->gemm_scratch, need + need / 4));
+        ctx->gemm_scratch_bytes = need + need / 4;
+    }
+    int8_t* q = (int8_t*)ctx->gemm_scratch;
+    float* amax = (float*)((char*)ctx->gemm_scratch + (((size_t)tokens * Kp + 255) & ~(size_t)255));
     int* xsum = (int*)(amax + tokens);
     lb_quantize_gemm_kernel<<<tokens, 256, 0, ctx->stream>>>(x, w->cols, Kp, q, amax, xsum);
     LB_CHECK_LAUNCH(ctx, "lb_quantize_gemm_kernel");
@@ -313,6 +331,7 @@ extern "C" int loom_b200_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight
     p.residual = residual;
     p.act = activation;
     p.out = out;
+    p.pre_out = pre_out;
     p.acc_out = acc_out;
     p.status = ctx->status_dev;
     const size_t smem = (size_t)kGemmStages * (kSliceBytesA + kSliceBytesB) + 1024;

@@ -6,6 +6,10 @@
 #include <cmath>
 #include <vector>
 
+int lb_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const float* x, const float* bias,
+                    const float* residual, int activation, float* out, float* pre_out, int32_t* acc_out, float* amax_out);
+constexpr int kGemmMinTokens = 32;
+
 namespace {
 
 void fill_seg(LbGemvSeg& s, const loom_b200_weight* w, const float* bias, void* out) {
@@ -216,6 +220,10 @@ int loom_b200_dense_forward(loom_b200_ctx* ctx, const loom_b200_weight* w, int a
     float* pre = ar.take<float>((size_t)batch * N);
     float* post = ar.take<float>((size_t)batch * N);
     LB_CUDA(ctx, cudaMemcpyAsync(x, in_host, (size_t)batch * K * 4, cudaMemcpyHostToDevice, ctx->stream));
+    // a block of tokens is a dense contraction: tensor cores (tcgen05) from kGemmMinTokens on, the GEMV below it
+    if (batch >= kGemmMinTokens) {
+        if (int rc = lb_ternary_gemm(ctx, w, batch, x, nullptr, nullptr, activation, post, pre, nullptr, nullptr)) return rc;
+    } else
     for (int b0 = 0; b0 < batch; b0 += kChunkTokens) {
         LbGemvParams p = {};
         p.nseg = 1;
