@@ -202,6 +202,54 @@ def cpu_sample(dec, weights, emb_host, shape, ctx_len, token, sample_blocks, tok
     return 1.0 / per_token, tb, th
 
 
+def gemm_mode(args):
+    """Config 1 (batched prefill): M tokens through the gate (2560->6912) and down (6912->2560) projections on
+    the tcgen05 GEMM, per-token quantization included; eight distinct matrices per shape, CUDA events."""
+    import torch
+
+    import loom_b200
+
+    torch.cuda.set_device(0)
+    ts = torch.cuda.Stream()
+    torch.cuda.set_stream(ts)
+    ctx = loom_b200.Context(0, ts.cuda_stream)
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(args.seed)
+    M = args.tokens
+    res = {}
+    for name, rows, cols in (("gate", 6912, 2560), ("down", 2560, 6912)):
+        ws = [ctx.pack_ternary_f32(torch.randn(rows * cols, device=dev, generator=g) * 0.02, rows, cols) for _ in range(8)]
+        x = torch.randn(M, cols, device=dev, generator=g)
+        out = torch.empty(M, rows, device=dev)
+        for i in range(max(args.warmup, 3)):
+            ctx.ternary_gemm(ws[i % 8], M, x, out=out)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            ctx.ternary_gemm(ws[i % 8], M, x, out=out)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / args.steps
+        res[name] = {"us": us, "tops": 2.0 * M * rows * cols / us / 1e6}
+    peak_bf16 = 1610.8
+    try:
+        peak_bf16 = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        pass
+    tops = 0.5 * (res["gate"]["tops"] + res["down"]["tops"])
+    print(json.dumps({"metric": "prefill GEMM TOP/s (M=%d, 2560<->6912 ternary x int8, tcgen05 kind::i8)" % M, "value": tops,
+                      "unit": "TOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+                      "ms_per_step": 1e-3 * 0.5 * (res["gate"]["us"] + res["down"]["us"]), "higher_is_better": True,
+                      "dtype": "u8 codes x s8 -> s32 (tcgen05), fp64 rescale", "data": "synthetic",
+                      "config": {"workload": "configs[1]: batched prefill, M=%d tokens" % M, "detail": res},
+                      "roofline": {"bound": "tensor", "achieved": tops, "peak": 2 * peak_bf16, "unit": "TOP/s",
+                                   "frac": tops / (2 * peak_bf16), "traffic": None,
+                                   "peak_kind": "2 x measured bf16 cuBLAS burst (no int8 peak was measured)"}}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -213,7 +261,11 @@ def main():
     ap.add_argument("--vocab", type=int, default=SHAPE["vocab"], help="smaller vocabularies are for profiling captures only")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="decode", choices=["decode", "gemm"], help="gemm: the batched-prefill GEMM microbenchmark")
+    ap.add_argument("--tokens", type=int, default=512)
     args = ap.parse_args()
+    if args.mode == "gemm":
+        return gemm_mode(args)
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))

@@ -29,7 +29,9 @@ namespace {
 constexpr int kRowsPerCta = 128;   // weight rows = TMEM lanes = MMA M
 constexpr int kTokPerCta = 128;    // tokens = TMEM columns = MMA N
 constexpr int kSliceK = 128;       // K columns (= bytes) per pipeline stage
-constexpr int kGemmStages = 4;
+constexpr int kGemmStages = 5;
+constexpr int kLag = 3;             // k-slices whose global loads are in flight before their stage is finished
+constexpr int kRawBytesA = (kRowsPerCta / kTileRows) * kTileBytes;  // packed weights of one slice: 8 tiles = 4 KB
 constexpr int kProducerThreads = 128;
 constexpr int kGemmThreads = kProducerThreads + 32;  // + the MMA warp
 constexpr int kSliceBytesA = kRowsPerCta * kSliceK;  // 16 KB
@@ -107,6 +109,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
     const int row0 = blockIdx.x * kRowsPerCta, tok0 = blockIdx.y * kTokPerCta;
     uint8_t* a_ring = smem;
     uint8_t* b_ring = smem + kGemmStages * kSliceBytesA;
+    uint8_t* raw_ring = b_ring + kGemmStages * kSliceBytesB;
     const int nslices = p.kblocks;  // one 128-column k-block per stage
 
     if (tid == 0) {
@@ -137,33 +140,50 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the per-token scales are read by other producer warps later
         const int g = lane >> 2, t = lane & 3;
         bool failed = false;
-        for (int ks = 0; ks < nslices; ++ks) {
-            const int s = ks % kGemmStages;
-            if (ks >= kGemmStages && !failed && !wait_bounded(&empty_bar[s], (uint32_t)((ks / kGemmStages - 1) & 1))) failed = true;
-            uint8_t* a_dst = a_ring + (size_t)s * kSliceBytesA;
-            uint8_t* b_dst = b_ring + (size_t)s * kSliceBytesB;
-            copy_b_slice(b_dst, p.q, tok0, p.tokens, p.Kp, ks * kSliceK, tid);
-            // A: this warp expands strips 2*warp and 2*warp+1 of the 128-row block
+        // Software pipeline: the cp.async copies of slice ks (activations into the B stage, packed weights into a
+        // raw staging area) are committed as one group; a slice is expanded and handed to the MMA warp kLag
+        // iterations later, when its group has landed, so global latency overlaps across kLag slices.
+        for (int it = 0; it < nslices + kLag; ++it) {
+            if (it < nslices) {
+                const int ks = it, s = ks % kGemmStages;
+                if (ks >= kGemmStages && !failed && !wait_bounded(&empty_bar[s], (uint32_t)((ks / kGemmStages - 1) & 1))) failed = true;
+                copy_b_slice(b_ring + (size_t)s * kSliceBytesB, p.q, tok0, p.tokens, p.Kp, ks * kSliceK, tid);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int sl = 2 * warp + h;  // strip inside the block (16 rows each)
-                const int strip = blockIdx.x * (kRowsPerCta / kTileRows) + sl;
-                uint4 w = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
-                if (strip < p.strips) w = reinterpret_cast<const uint4*>(p.tiles + ((size_t)strip * p.kblocks + ks) * kTileWords)[lane];
-                // lane (g,t) holds [row g, word t] [row g+8, word t] [row g, word 4+t] [row g+8, word 4+t]
-                const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int row = sl * 16 + g + 8 * (k & 1);  // row inside the 128-row block
-                    const int kc = t + 4 * (k >> 1);            // 16-byte K chunk inside the slice
-                    const uint32_t x = words[k];
-                    const uint4 e = make_uint4(x & 0x03030303u, (x >> 2) & 0x03030303u, (x >> 4) & 0x03030303u, (x >> 6) & 0x03030303u);
-                    *reinterpret_cast<uint4*>(a_dst + (row >> 3) * 1024 + kc * 128 + (row & 7) * 16) = e;
+                for (int h = 0; h < 2; ++h) {
+                    const int sl = 2 * warp + h;
+                    const int strip = blockIdx.x * (kRowsPerCta / kTileRows) + sl;
+                    if (strip < p.strips) {
+                        const uint32_t d = lb_smem_u32(raw_ring + (size_t)s * kRawBytesA + sl * kTileBytes + lane * 16);
+                        const uint32_t* src = p.tiles + ((size_t)strip * p.kblocks + ks) * kTileWords + lane * 4;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+                    }
                 }
             }
-            asm volatile("cp.async.wait_all;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
-            mbar_arrive(&full_bar[s]);
+            asm volatile("cp.async.commit_group;" ::: "memory");  // (possibly empty) group of this iteration
+            if (it >= kLag) {
+                const int ks = it - kLag, s = ks % kGemmStages;
+                asm volatile("cp.async.wait_group %0;" ::"n"(kLag) : "memory");
+                uint8_t* a_dst = a_ring + (size_t)s * kSliceBytesA;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int sl = 2 * warp + h;
+                    const int strip = blockIdx.x * (kRowsPerCta / kTileRows) + sl;
+                    uint4 w = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);  // rows past the matrix: weight 0
+                    if (strip < p.strips) w = *reinterpret_cast<const uint4*>(raw_ring + (size_t)s * kRawBytesA + sl * kTileBytes + lane * 16);
+                    // lane (g,t) holds [row g, word t] [row g+8, word t] [row g, word 4+t] [row g+8, word 4+t]
+                    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int row = sl * 16 + g + 8 * (k & 1);  // row inside the 128-row block
+                        const int kc = t + 4 * (k >> 1);            // 16-byte K chunk inside the slice
+                        const uint32_t x = words[k];
+                        const uint4 e = make_uint4(x & 0x03030303u, (x >> 2) & 0x03030303u, (x >> 4) & 0x03030303u, (x >> 6) & 0x03030303u);
+                        *reinterpret_cast<uint4*>(a_dst + (row >> 3) * 1024 + kc * 128 + (row & 7) * 16) = e;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
+                mbar_arrive(&full_bar[s]);
+            }
         }
         // ---------------- epilogue ----------------
         if (!failed && !wait_bounded(&done_bar, 0)) failed = true;
@@ -334,7 +354,7 @@ int lb_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, c
     p.pre_out = pre_out;
     p.acc_out = acc_out;
     p.status = ctx->status_dev;
-    const size_t smem = (size_t)kGemmStages * (kSliceBytesA + kSliceBytesB) + 1024;
+    const size_t smem = (size_t)kGemmStages * (kSliceBytesA + kSliceBytesB + kRawBytesA) + 1024;
     if (!(ctx->func_attr_mask & (1u << 27))) {
         LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         ctx->func_attr_mask |= 1u << 27;
