@@ -32,7 +32,7 @@ constexpr int kSliceK = 128;       // K columns (= bytes) per pipeline stage
 constexpr int kGemmStages = 5;
 constexpr int kLag = 3;             // k-slices whose global loads are in flight before their stage is finished
 constexpr int kRawBytesA = (kRowsPerCta / kTileRows) * kTileBytes;  // packed weights of one slice: 8 tiles = 4 KB
-constexpr int kProducerThreads = 128;
+constexpr int kProducerThreads = 256;  // eight warps: one 16-row strip each; also the epilogue warps
 constexpr int kGemmThreads = kProducerThreads + 32;  // + the MMA warp
 constexpr int kSliceBytesA = kRowsPerCta * kSliceK;  // 16 KB
 constexpr int kSliceBytesB = kTokPerCta * kSliceK;   // 16 KB
@@ -53,6 +53,7 @@ struct GemmParams {
     float* pre_out;          // [tokens, rows] value before the activation, or null
     int32_t* acc_out;        // [tokens, rows] or null
     int* status;
+    int debug;  // timing experiments only
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         lb_fence_mbar_init();
         s_failed = 0;
     }
-    if (warp == 4) {  // the MMA warp owns the tensor-memory allocation
+    if (warp == kProducerThreads / 32) {  // the MMA warp owns the tensor-memory allocation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lb_smem_u32(&tmem_base_s)), "r"(kTokPerCta) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -130,14 +131,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
 
-    if (warp < 4) {
+    if (warp < kProducerThreads / 32) {
         // ---------------- producers: expand A, copy B ----------------
         for (int i = tid; i < kTokPerCta; i += kProducerThreads) {
             const int tok = tok0 + i;
             s_os[i] = tok < p.tokens ? lb_output_scale(p.scale, p.amax[tok]) : 0.0;
             s_xsum[i] = tok < p.tokens ? p.xsum[tok] : 0;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the per-token scales are read by other producer warps later
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // the per-token scales are read by other producer warps later
         const int g = lane >> 2, t = lane & 3;
         bool failed = false;
         // Software pipeline: the cp.async copies of slice ks (activations into the B stage, packed weights into a
@@ -148,9 +149,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
                 const int ks = it, s = ks % kGemmStages;
                 if (ks >= kGemmStages && !failed && !wait_bounded(&empty_bar[s], (uint32_t)((ks / kGemmStages - 1) & 1))) failed = true;
                 copy_b_slice(b_ring + (size_t)s * kSliceBytesB, p.q, tok0, p.tokens, p.Kp, ks * kSliceK, tid);
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int sl = 2 * warp + h;
+                {
+                    const int sl = warp;  // this warp's strip of the 128-row block
                     const int strip = blockIdx.x * (kRowsPerCta / kTileRows) + sl;
                     if (strip < p.strips) {
                         const uint32_t d = lb_smem_u32(raw_ring + (size_t)s * kRawBytesA + sl * kTileBytes + lane * 16);
@@ -164,9 +164,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
                 const int ks = it - kLag, s = ks % kGemmStages;
                 asm volatile("cp.async.wait_group %0;" ::"n"(kLag) : "memory");
                 uint8_t* a_dst = a_ring + (size_t)s * kSliceBytesA;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int sl = 2 * warp + h;
+                {
+                    const int sl = warp;
                     const int strip = blockIdx.x * (kRowsPerCta / kTileRows) + sl;
                     uint4 w = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);  // rows past the matrix: weight 0
                     if (strip < p.strips) w = *reinterpret_cast<const uint4*>(raw_ring + (size_t)s * kRawBytesA + sl * kTileBytes + lane * 16);
@@ -181,7 +180,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
                         *reinterpret_cast<uint4*>(a_dst + (row >> 3) * 1024 + kc * 128 + (row & 7) * 16) = e;
                     }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
+                if (p.debug != 1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
                 mbar_arrive(&full_bar[s]);
             }
         }
@@ -189,12 +188,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         if (!failed && !wait_bounded(&done_bar, 0)) failed = true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (failed) atomicExch(&s_failed, 1);
-        const int r = row0 + warp * 32 + lane;
+        // a warp may only touch the 32 TMEM lanes of its quarter (warp % 4); the two warps of a quarter split the columns
+        const int quarter = warp & 3, chalf = warp >> 2;
+        const int r = row0 + quarter * 32 + lane;
         const bool row_ok = r < p.rows;
         const double bias = (row_ok && p.bias) ? (double)p.bias[r] : 0.0;
-        for (int c0 = 0; c0 < kTokPerCta; c0 += 32) {
+        for (int c0 = chalf * (kTokPerCta / 2); c0 < (chalf + 1) * (kTokPerCta / 2); c0 += 32) {
             uint32_t v[32];
-            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
             asm volatile(
                 "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
@@ -254,7 +255,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 4) {
+    if (warp == kProducerThreads / 32) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTokPerCta) : "memory");
     }
@@ -354,6 +355,7 @@ int lb_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, c
     p.pre_out = pre_out;
     p.acc_out = acc_out;
     p.status = ctx->status_dev;
+    p.debug = ctx->opt_debug;
     const size_t smem = (size_t)kGemmStages * (kSliceBytesA + kSliceBytesB + kRawBytesA) + 1024;
     if (!(ctx->func_attr_mask & (1u << 27))) {
         LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
