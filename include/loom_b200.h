@@ -84,7 +84,8 @@ void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
 /* Tuning knobs, the counterpart of the tileSize argument the WGSL dispatchers take
  * (poly/wgpu_kernels.go:416-427): "gemv_variant" 0 = integer-MMA inner loop, 1 = dp4a inner loop;
  * "gemv_ctas_per_sm" 1..8; "gemv_partition" 0 = choose, 1 = stream-K over tiles with the int32 fix-up,
- * 2 = whole strips per CTA; "pdl" 0/1 = programmatic dependent launch.  Results never depend on them
+ * 2 = whole strips per CTA; "pdl" 0/1 = programmatic dependent launch; "tp_graph" 0/1 = record the
+ * tensor-parallel decode step, collectives included, as a graph.  Results never depend on them
  * ("debug" is for timing experiments only and does change results). */
 int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value);
 /* Phase trace, the counterpart of WGPUContext.TimeCommands (poly/wgpu_context_native.go:553) and of the
@@ -308,6 +309,44 @@ int loom_b200_decoder_download_cache(loom_b200_decoder* dec, int block, float* k
  * {first-maximum token, forward it}.  The loop runs on the device; tokens come back once at the end. */
 int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, int n_prompt, int max_new,
                                int32_t* out_tokens, loom_b200_gen_metrics* metrics);
+
+/* ---- tensor parallelism over the GPUs of one box --------------------------------------------------
+ * The reference has no multi-device path (its only sharding notion is the per-layer tile size,
+ * poly/wgpu_context.go).  The split used here is the one the integer arithmetic allows without changing a bit
+ * of the result: Q/K/V/gate/up hold a contiguous slice of their ROWS (heads, intermediate units), O/down the
+ * matching slice of their COLUMNS; the partial int32 accumulators of O/down are summed across ranks (exact),
+ * after the ranks have agreed on the per-token sum of squares (float64) and absmax (float32) of the sharded
+ * vector.  One process per GPU; each process owns one context.  NCCL is loaded at run time (libnccl.so.2).
+ *
+ * A weight slice must carry the scale of the WHOLE matrix (absmean over all rows and columns,
+ * NewBitNetPackedMatrixFromFloat32, poly/bitnet_cpu.go:97-131): ternarize first, slice the codes after. */
+
+/* Fills id128 (128 bytes) with a fresh NCCL unique id; rank 0 calls it and hands the bytes to every rank. */
+int loom_b200_tp_unique_id(uint8_t* id128);
+/* Joins the group (collective: every rank calls it with the same id).  world == 1 is accepted and a no-op. */
+int loom_b200_tp_init(loom_b200_ctx* ctx, int rank, int world, const uint8_t* id128);
+/* Leaves the group (also done by loom_b200_ctx_destroy). */
+void loom_b200_tp_finalize(loom_b200_ctx* ctx);
+int loom_b200_tp_rank(const loom_b200_ctx* ctx);
+int loom_b200_tp_world(const loom_b200_ctx* ctx);
+/* In-place sum of n int32 values across the group, ordered on the context's stream. */
+int loom_b200_tp_allreduce_i32(loom_b200_ctx* ctx, int32_t* buf, size_t n);
+/* Row-sharded ternary linear on device buffers: x_local [batch, w->cols] holds this rank's slice of a vector of
+ * cols_global entries; the always-on inner RMSNorm (bitNetRMSNormTensorRowWeighted, poly/bitnet_cpu.go:893-913)
+ * runs over the whole vector, inner_w_local is this rank's slice of its weight (or NULL).  out [batch, w->rows]
+ * = float(sum over ranks of acc * outputScale + bias) + residual, the same bits on every rank and the same bits
+ * as the unsharded loom_b200_ternary_linear after loom_b200_inner_rmsnorm.  bias and residual may be NULL;
+ * residual may alias out.  batch <= 8. */
+int loom_b200_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, int batch, const float* x_local,
+                                   int cols_global, const float* inner_w_local, int inner_w_len, double eps,
+                                   const float* bias, const float* residual, float* out);
+/* With a group of more than one rank on the context, loom_b200_decoder_create takes the UNSHARDED dimensions
+ * and builds rank tp_rank's part: num_heads, num_kv_heads and intermediate must be multiples of the world
+ * size; loom_b200_decoder_set_block then expects the slices q [heads/W*hd, hidden], k/v [kv_heads/W*hd, hidden],
+ * o [hidden, heads/W*hd], gate/up [inter/W, hidden], down [hidden, inter/W] and the matching slices of the
+ * inner-norm vectors; embeddings stay whole on every rank, the LM head is computed in vocabulary slices and
+ * gathered when vocab is a multiple of the world size.  Every rank makes the same calls with the same tokens
+ * and ends with the same logits and tokens. */
 
 #ifdef __cplusplus
 }

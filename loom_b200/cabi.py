@@ -93,6 +93,13 @@ SIGNATURES = {
     "loom_b200_decoder_continue": (_i, [_vp, _i]),
     "loom_b200_decoder_download_cache": (_i, [_vp, _i, _vp, _vp]),
     "loom_b200_decoder_generate": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
+    "loom_b200_tp_unique_id": (_i, [_vp]),
+    "loom_b200_tp_init": (_i, [_vp, _i, _i, _vp]),
+    "loom_b200_tp_finalize": (None, [_vp]),
+    "loom_b200_tp_rank": (_i, [_vp]),
+    "loom_b200_tp_world": (_i, [_vp]),
+    "loom_b200_tp_allreduce_i32": (_i, [_vp, _vp, _sz]),
+    "loom_b200_tp_rowsharded_linear": (_i, [_vp, _vp, _i, _vp, _i, _vp, _i, _d, _vp, _vp, _vp]),
 }
 
 
@@ -328,6 +335,39 @@ class Context:
     def program_free(self, prog):
         lib().loom_b200_program_free(self.h, prog)
 
+    # ---- tensor parallelism: one process per GPU, one context per process ----
+    @staticmethod
+    def tp_unique_id() -> bytes:
+        """128 bytes that rank 0 creates and hands to every rank (any transport: a file, a store, a broadcast)."""
+        buf = C.create_string_buffer(128)
+        rc = lib().loom_b200_tp_unique_id(buf)
+        if rc != 0:
+            raise LoomB200Error(rc, (lib().loom_b200_last_error(None) or b"").decode())
+        return buf.raw
+
+    def tp_init(self, rank: int, world: int, unique_id: bytes):
+        assert len(unique_id) == 128
+        self._check(lib().loom_b200_tp_init(self.h, rank, world, C.c_char_p(unique_id)))
+
+    def tp_finalize(self):
+        lib().loom_b200_tp_finalize(self.h)
+
+    @property
+    def tp_rank(self) -> int:
+        return lib().loom_b200_tp_rank(self.h)
+
+    @property
+    def tp_world(self) -> int:
+        return lib().loom_b200_tp_world(self.h)
+
+    def tp_allreduce_i32(self, buf, n: int):
+        self._check(lib().loom_b200_tp_allreduce_i32(self.h, _ptr(buf), n))
+
+    def tp_rowsharded_linear(self, w: Weight, batch, x_local, cols_global, out, inner_w=None, inner_w_len=0, eps=0.0,
+                             bias=None, residual=None):
+        self._check(lib().loom_b200_tp_rowsharded_linear(self.h, w.h, batch, _ptr(x_local), cols_global, _ptr(inner_w),
+                                                         inner_w_len, eps, _ptr(bias), _ptr(residual), _ptr(out)))
+
     def gate_product(self, batch, hidden, act, gate, up, out):
         self._check(lib().loom_b200_gate_product(self.h, batch, hidden, act, _ptr(gate), _ptr(up), _ptr(out)))
 
@@ -468,7 +508,7 @@ class Decoder:
         self.ctx._check(lib().loom_b200_decoder_continue(self.h, steps))
 
     def cache(self, block: int):
-        kvd = self.dims.num_kv_heads * self.dims.head_dim
+        kvd = self.dims.num_kv_heads * self.dims.head_dim // max(1, self.ctx.tp_world)  # this rank's KV heads
         k = np.empty((self.dims.max_seq_len, kvd), np.float32)
         v = np.empty((self.dims.max_seq_len, kvd), np.float32)
         self.ctx._check(lib().loom_b200_decoder_download_cache(self.h, block, k.ctypes.data, v.ctypes.data))

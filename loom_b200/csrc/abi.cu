@@ -331,6 +331,8 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
         ctx->opt_debug = value;
     } else if (!strcmp(key, "pdl")) {
         ctx->opt_pdl = value != 0;
+    } else if (!strcmp(key, "tp_graph")) {
+        ctx->opt_tp_graph = value != 0;
     } else {
         return lb_fail(ctx, LOOM_B200_ERR_INVALID, "ctx_set_option: unknown key '%s'", key);
     }
@@ -339,6 +341,7 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
 
 void loom_b200_ctx_destroy(loom_b200_ctx* ctx) {
     if (!ctx) return;
+    loom_b200_tp_finalize(ctx);
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->fix_acc) cudaFree(ctx->fix_acc);

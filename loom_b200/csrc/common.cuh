@@ -70,6 +70,10 @@ struct loom_b200_ctx {
     const char* trace_label[kTraceSlots] = {};  // kernel that wrote each row
     int opt_debug = 0;             // timing experiments (results are wrong when non-zero)
     bool capturing = false;        // between graph_begin and graph_end
+    // tensor parallelism (tp.cu): rank and world size of this context's group; the NCCL communicator or null
+    int tp_rank = 0, tp_world = 1;
+    int opt_tp_graph = 1;          // record the sharded decode step (collectives included) as a graph
+    void* nccl_comm = nullptr;
 };
 
 int lb_fail(loom_b200_ctx* ctx, int code, const char* fmt, ...);

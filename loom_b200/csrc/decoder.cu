@@ -37,6 +37,12 @@ struct loom_b200_decoder {
     float* h_logits = nullptr;  // pinned [vocab]
     loom_b200_graph* step_graph = nullptr;
     int decode_splits = 16;
+    // tensor parallelism: this rank's part of the stack (world 1 = everything)
+    int tp_world = 1, tp_rank = 0;
+    int heads_l = 0, kv_heads_l = 0, inter_l = 0;  // local heads, KV heads and intermediate units
+    bool head_sharded = false;                     // LM head computed in vocabulary slices and gathered
+    double* tp_stats = nullptr;
+    int32_t* tp_acc = nullptr;
 };
 
 namespace {
@@ -72,6 +78,11 @@ int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int 
         s.out = dec->x;
         s.residual = dec->x;
         s.M = M;
+        if (dec->tp_world > 1) {
+            s.inter_global = d.intermediate;
+            s.tp_stats = dec->tp_stats;
+            s.tp_acc = dec->tp_acc;
+        }
         if (int rc = lb_swiglu_dev(ctx, s)) return rc;
     }
     if (head) {
@@ -84,7 +95,15 @@ int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int 
         h.hidden = d.hidden;
         h.logits = dec->logits;
         h.hidden_out = dec->hidden;
+        if (dec->head_sharded) {
+            const int vl = d.vocab / dec->tp_world;
+            h.head = dec->emb + (size_t)dec->tp_rank * vl * d.hidden;
+            h.vocab = vl;
+            h.logits = dec->logits + (size_t)dec->tp_rank * vl;
+        }
         if (int rc = lb_launch_lm_head(ctx, h)) return rc;
+        if (dec->head_sharded)
+            if (int rc = lb_tp_allgather_f32(ctx, h.logits, dec->logits, (size_t)h.vocab)) return rc;
     }
     return lb_launch_add_scalar(ctx, dec->pos, M);
 }
@@ -108,6 +127,7 @@ void dec_drop_graph(loom_b200_decoder* dec) {
 int dec_step(loom_b200_decoder* dec) {
     loom_b200_ctx* ctx = dec->ctx;
     if (dec->step_graph) return loom_b200_graph_launch(ctx, dec->step_graph);
+    if (dec->tp_world > 1 && !ctx->opt_tp_graph) return dec_forward_chunk(dec, 1, dec->decode_splits, true, 0);
     if (int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0)) return rc;  // warm-up run, counts as the step
     // record the same step for all later tokens
     if (int rc = loom_b200_graph_begin(ctx)) return rc;
@@ -138,14 +158,25 @@ int loom_b200_decoder_create(loom_b200_ctx* ctx, const loom_b200_decoder_dims* d
     LB_REQUIRE(ctx, d.head_dim % 8 == 0, "decoder_create: head_dim %d must be a multiple of 8", d.head_dim);
     if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_create cannot be recorded");
     if (int rc = lb_set_device(ctx)) return rc;
+    const int W = ctx->tp_world, kvh = d.num_kv_heads == 0 ? d.num_heads : d.num_kv_heads;
+    LB_REQUIRE(ctx, d.num_heads % W == 0 && kvh % W == 0 && d.intermediate % W == 0,
+               "decoder_create: heads %d, kv heads %d and intermediate %d must be multiples of the group size %d", d.num_heads, kvh,
+               d.intermediate, W);
+    LB_REQUIRE(ctx, W == 1 || (d.intermediate / W) % 4 == 0, "decoder_create: intermediate slice %d must be a multiple of 4", d.intermediate / W);
     auto* dec = new loom_b200_decoder();
     dec->ctx = ctx;
     dec->d = d;
     if (dec->d.num_kv_heads == 0) dec->d.num_kv_heads = d.num_heads;
     if (dec->d.max_seq_len <= 0) dec->d.max_seq_len = 2048;  // NewTransformer default, poly/transformer.go:111-113
     dec->blocks.resize(d.num_layers);
+    dec->tp_world = ctx->tp_world;
+    dec->tp_rank = ctx->tp_rank;
+    dec->heads_l = d.num_heads / W;
+    dec->kv_heads_l = dec->d.num_kv_heads / W;
+    dec->inter_l = d.intermediate / W;
+    dec->head_sharded = W > 1 && d.vocab % W == 0;
     // attention splits for one-token steps: heads x splits CTAs should be resident together (two per SM)
-    dec->decode_splits = (2 * ctx->sm_count) / d.num_heads;
+    dec->decode_splits = (2 * ctx->sm_count) / dec->heads_l;
     if (dec->decode_splits > 16) dec->decode_splits = 16;
     if (dec->decode_splits < 1) dec->decode_splits = 1;
     dec->out_cap = dec->d.max_seq_len;
@@ -155,13 +186,17 @@ int loom_b200_decoder_create(loom_b200_ctx* ctx, const loom_b200_decoder_dims* d
         if (e == cudaSuccess) e = cudaMemsetAsync(*p, 0, bytes, ctx->stream);
     };
     A((void**)&dec->x, (size_t)kChunkTokens * d.hidden * 4);
-    A((void**)&dec->prod, (size_t)kChunkTokens * d.intermediate * 4);
+    A((void**)&dec->prod, (size_t)kChunkTokens * dec->inter_l * 4);
     A((void**)&dec->logits, (size_t)d.vocab * 4);
     A((void**)&dec->hidden, (size_t)d.hidden * 4);
     A((void**)&dec->tok, kChunkTokens * sizeof(int));
     A((void**)&dec->pos, sizeof(int));
     A((void**)&dec->step, sizeof(int));
     A((void**)&dec->out_tokens, (size_t)dec->out_cap * sizeof(int));
+    if (W > 1) {
+        A((void**)&dec->tp_stats, 2 * kChunkTokens * sizeof(double));
+        A((void**)&dec->tp_acc, (size_t)kChunkTokens * d.hidden * sizeof(int32_t));
+    }
     if (e == cudaSuccess) e = cudaMallocHost((void**)&dec->h_tok, kChunkTokens * sizeof(int));
     if (e == cudaSuccess) e = cudaMallocHost((void**)&dec->h_logits, (size_t)d.vocab * 4);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
@@ -189,7 +224,8 @@ void loom_b200_decoder_destroy(loom_b200_decoder* dec) {
         if (b.g2) cudaFree(b.g2);
         if (b.ffn_inner) cudaFree(b.ffn_inner);
     }
-    void* ptrs[] = {dec->final_gain, dec->x, dec->prod, dec->logits, dec->hidden, dec->tok, dec->pos, dec->step, dec->out_tokens};
+    void* ptrs[] = {dec->final_gain, dec->x, dec->prod, dec->logits, dec->hidden, dec->tok, dec->pos, dec->step, dec->out_tokens,
+                    dec->tp_stats, dec->tp_acc};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     if (dec->h_tok) cudaFreeHost(dec->h_tok);
@@ -208,7 +244,8 @@ int loom_b200_decoder_set_block(loom_b200_decoder* dec, int block, const float* 
     for (int i = 0; i < 7; ++i) LB_REQUIRE(ctx, w7[i] != nullptr, "decoder_set_block: weight %d is NULL", i);
     if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_set_block cannot be recorded");
     if (int rc = lb_set_device(ctx)) return rc;
-    const int H = d.hidden, I = d.intermediate, qd = d.num_heads * d.head_dim, kvd = d.num_kv_heads * d.head_dim;
+    // with a group of W ranks these are the slice shapes: heads/W heads, kv_heads/W KV heads, intermediate/W units
+    const int H = d.hidden, I = dec->inter_l, qd = dec->heads_l * d.head_dim, kvd = dec->kv_heads_l * d.head_dim;
     const int rows[7] = {qd, kvd, kvd, H, I, I, H}, cols[7] = {H, H, H, qd, H, H, I};
     for (int i = 0; i < 7; ++i)
         LB_REQUIRE(ctx, w7[i]->rows == rows[i] && w7[i]->cols == cols[i], "decoder_set_block: weight %d is %dx%d, expected %dx%d", i,
@@ -218,8 +255,13 @@ int loom_b200_decoder_set_block(loom_b200_decoder* dec, int block, const float* 
     dec_drop_graph(dec);
     loom_b200_mha& m = b.mha;
     m.d_model = H;
-    m.heads = d.num_heads;
-    m.kv_heads = d.num_kv_heads;
+    m.heads = dec->heads_l;
+    m.kv_heads = dec->kv_heads_l;
+    if (dec->tp_world > 1) {
+        m.q_dim_global = d.num_heads * d.head_dim;
+        m.tp_stats = dec->tp_stats;
+        m.tp_acc = dec->tp_acc;
+    }
     m.head_dim = d.head_dim;
     m.q_dim = qd;
     m.kv_dim = kvd;

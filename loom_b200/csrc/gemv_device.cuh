@@ -139,8 +139,10 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
         }
     }
     if (PRO >= LB_PRO_BLOCKNORM) {
-        ss = block_sum(ss, sm.red);
-        const double mean = __dadd_rn(__ddiv_rn(ss, (double)K), p.eps);
+        // tensor-parallel row shards: the sum of squares over the whole (sharded) vector is supplied by the caller
+        if (p.given_ss) ss = p.given_ss[n];
+        else ss = block_sum(ss, sm.red);
+        const double mean = __dadd_rn(__ddiv_rn(ss, (double)(p.norm_count > 0 ? p.norm_count : K)), p.eps);
         const double root = sqrt(mean);
         const double rr = __ddiv_rn(1.0, root);  // RN(1/rms): the inner norms' scale, the block norm's reciprocal
 #pragma unroll 1
@@ -167,7 +169,8 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
             }
         }
     }
-    m = block_max(m, sm.red);
+    if (p.given_amax) m = p.given_amax[n];  // absmax over the whole sharded vector (already floored by the caller or below)
+    else m = block_max(m, sm.red);
     const float amax = m < 1e-5f ? 1e-5f : m;
     const double s = __ddiv_rn(127.0, (double)amax);
     const bool side = blockIdx.x == 0;
@@ -252,7 +255,8 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
                     }
                 }
                 ss = block_sum(ss, sm.red);
-                double mean = __dadd_rn(__ddiv_rn(ss, (double)K), p.eps);
+                if (p.given_ss) ss = p.given_ss[n];
+                double mean = __dadd_rn(__ddiv_rn(ss, (double)(p.norm_count > 0 ? p.norm_count : K)), p.eps);
                 stat = PRO == LB_PRO_BLOCKNORM ? sqrt(mean) : __ddiv_rn(1.0, sqrt(mean));
                 if (PRO == LB_PRO_BLOCKNORM) rstat = __ddiv_rn(1.0, stat);
             }
@@ -260,6 +264,7 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
             for (int c = tid; c < K; c += kThreads)
                 m = fmaxf(m, (float)fabs(pro_value<PRO>(row, c, stat, rstat, p.norm_w, p.norm_w_len)));
             m = block_max(m, sm.red);
+            if (p.given_amax) m = p.given_amax[n];
             amax = m < 1e-5f ? 1e-5f : m;
         }
         const double s = __ddiv_rn(127.0, (double)amax);

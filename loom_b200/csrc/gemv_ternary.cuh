@@ -59,6 +59,9 @@ struct LbGemvParams {
     const float* norm_w;  // gain / inner-norm weights or null
     int norm_w_len;
     double eps;
+    const double* given_ss;   // optional [M]: sum of squares over the full vector (tensor-parallel row shards)
+    const float* given_amax;  // optional [M]: absmax of the normalised full vector
+    int norm_count;           // elements the mean runs over (0 = K)
     int8_t* q_out;     // optional side outputs, written by CTA 0
     float* amax_out;
     float* norm_out;   // normalised row as float32 (what the layers report as preAct)

@@ -44,6 +44,11 @@ int lb_swiglu_dev(loom_b200_ctx* ctx, const LbSwigluArgs& a) {
     p.act = a.act;
     if (int rc = lb_gemv_finalize_params(ctx, p)) return rc;
     if (int rc = lb_launch_gemv(ctx, p)) return rc;
+    if (a.inter_global > 0 && ctx->tp_world > 1) {
+        LB_REQUIRE(ctx, a.pre_out == nullptr && a.tp_stats && a.tp_acc, "swiglu: sharded down projection without scratch");
+        return lb_tp_rowsharded_linear(ctx, a.down, false, a.prod, a.M, a.inter_global, a.inner_w, a.inner_w_len,
+                                       a.inner_eps > 0 ? a.inner_eps : 1e-5, a.bias_down, a.residual, a.out, a.tp_stats, a.tp_acc);
+    }
     // inner RMSNorm (always applied) + requantize + down projection (+ bias, + residual)
     LbGemvParams d = {};
     d.nseg = 1;
@@ -152,6 +157,11 @@ int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     t.max_chunk = (m->msl + t.splits - 1) / t.splits;
     if (int rc = lb_launch_attention(ctx, t)) return rc;
 
+    if (m->q_dim_global > 0 && ctx->tp_world > 1) {
+        LB_REQUIRE(ctx, a.pre_out == nullptr && m->tp_stats && m->tp_acc, "mha: sharded output projection without scratch");
+        return lb_tp_rowsharded_linear(ctx, m->wo, true, m->attn, a.M, m->q_dim_global, m->inner, m->inner_len,
+                                       m->rms_eps > 0 ? m->rms_eps : 1e-5, m->bo, a.residual, a.out, m->tp_stats, m->tp_acc);
+    }
     LbGemvParams o = {};
     o.nseg = 1;
     fill_seg(o.seg[0], m->wo, m->bo, a.out);

@@ -24,6 +24,11 @@ struct LbSwigluArgs {
     float* out;           // [M, hidden]
     const float* residual;  // optional [M, hidden], may alias out
     int M;
+    // tensor parallelism: > 0 when gate/up hold a slice of the rows and down the matching slice of the columns;
+    // the value is the unsharded intermediate size.  tp_stats: 2*M doubles, tp_acc: M*hidden int32 (device scratch).
+    int inter_global = 0;
+    double* tp_stats = nullptr;
+    int32_t* tp_acc = nullptr;
 };
 int lb_swiglu_dev(loom_b200_ctx* ctx, const LbSwigluArgs& a);
 
@@ -45,6 +50,11 @@ struct loom_b200_mha {
     unsigned int* cnt = nullptr;
     int* pos_dev = nullptr;
     int splits = 1, max_total = 0;
+    // tensor parallelism: > 0 when this object holds heads/world heads (wq/wk/wv row slices, wo a column slice);
+    // the value is the unsharded heads*head_dim.  Scratch as for the SwiGLU arguments, borrowed from the decoder.
+    int q_dim_global = 0;
+    double* tp_stats = nullptr;
+    int32_t* tp_acc = nullptr;
 };
 
 struct LbMhaStepArgs {
@@ -63,3 +73,14 @@ struct LbMhaStepArgs {
 int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a);
 int lb_mha_alloc(loom_b200_ctx* ctx, loom_b200_mha* m, int max_splits);
 void lb_mha_release(loom_b200_mha* m);
+
+// ---- tensor parallelism (tp.cu) -------------------------------------------------------------------------
+// NCCL data types and reductions by their ABI values (the library is loaded at run time)
+constexpr int kTpInt32 = 2, kTpFloat32 = 7, kTpFloat64 = 8, kTpSum = 0, kTpMax = 2;
+int lb_tp_allreduce(loom_b200_ctx* ctx, void* buf, size_t count, int dtype, int op);
+int lb_tp_allgather_f32(loom_b200_ctx* ctx, const float* send, float* recv, size_t count_per_rank);
+// Row-sharded ternary linear whose inner RMSNorm spans the sharded dimension: x_local [M, w->cols] (float or double)
+// -> out [M, w->rows] (+ residual), identical on every rank.  stats: 2*M doubles of scratch; acc: M*w->rows int32.
+int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool x_is_f64, const void* x, int M, int K_global,
+                            const float* inner_w, int inner_w_len, double eps, const float* bias, const float* residual,
+                            float* out, double* stats, int32_t* acc);

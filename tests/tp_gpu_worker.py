@@ -1,0 +1,127 @@
+"""One rank of the tensor-parallel GPU test (run by test_gpu_tp.py under torch.distributed.run, one process per
+GPU).  Every rank builds the same weights, keeps only its slices on its GPU, and must end with the logits and
+greedy tokens of the CPU oracle's UNSHARDED decoder.  gloo (CPU) carries the NCCL unique id."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from loom_b200 import cabi  # noqa: E402
+from loom_b200.tp import ShardPlan, slice_cols  # noqa: E402
+from oracle import oracle as orc  # noqa: E402
+
+
+def share_unique_id(rank: int) -> bytes:
+    t = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        t = torch.frombuffer(bytearray(cabi.Context.tp_unique_id()), dtype=torch.uint8).clone()
+    dist.broadcast(t, 0)
+    return bytes(t.numpy().tobytes())
+
+
+def main():
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    ctx = cabi.Context(device=local)
+    ctx.tp_init(rank, world, share_unique_id(rank))
+    assert ctx.tp_rank == rank and ctx.tp_world == world
+    if len(sys.argv) > 1 and sys.argv[1] == "nograph":
+        ctx.set_option("tp_graph", 0)
+    failures = []
+
+    # ---- the exact int32 sum ----
+    n = 5000
+    host = (np.arange(n, dtype=np.int32) * (rank + 1)) - 7
+    buf = ctx.to_device(host)
+    ctx.tp_allreduce_i32(buf, n)
+    got = ctx.download(buf, (n,), np.int32)
+    want = np.arange(n, dtype=np.int64) * (world * (world + 1) // 2) - 7 * world
+    if not np.array_equal(got.astype(np.int64), want):
+        failures.append("allreduce_i32 wrong")
+    ctx.free(buf)
+
+    # ---- a row-sharded linear with inner-norm weights, bias and residual ----
+    rng = np.random.default_rng(77)
+    rows, K, batch = 96, 256 * world, 3
+    master = (rng.standard_normal(rows * K) * 0.05).astype(np.float32)
+    words, scale = orc.pack_f32(master, rows, K)
+    inner = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    bias = (0.01 * rng.standard_normal(rows)).astype(np.float32)
+    resid = rng.standard_normal((batch, rows)).astype(np.float32)
+    x = rng.standard_normal((batch, K)).astype(np.float32)
+    c0, c1 = rank * K // world, (rank + 1) * K // world
+    w_l = ctx.upload_ternary(slice_cols(words, rows, K, c0, c1), rows, c1 - c0, scale)
+    d_x = ctx.to_device(np.ascontiguousarray(x[:, c0:c1]))
+    d_in, d_b, d_r = ctx.to_device(np.ascontiguousarray(inner[c0:c1])), ctx.to_device(bias), ctx.to_device(resid)
+    d_out = ctx.alloc(batch * rows * 4)
+    ctx.tp_rowsharded_linear(w_l, batch, d_x, K, d_out, inner_w=d_in, inner_w_len=c1 - c0, eps=1e-5, bias=d_b, residual=d_r)
+    got = ctx.download(d_out, (batch, rows), np.float32)
+    for t in range(batch):
+        y = orc.inner_rmsnorm_f32(x[t], inner, 1e-5)
+        xq, amax = orc.quantize_f32(y)
+        acc = orc.matvec_i32(words, rows, K, xq).astype(np.float64)
+        os_ = float(np.float64(scale) * np.float64(amax) / 127.0)
+        want = (acc * os_ + bias.astype(np.float64)).astype(np.float32) + resid[t]
+        if not np.array_equal(got[t], want):
+            failures.append("row-sharded linear token %d differs in %d of %d" % (t, int((got[t] != want).sum()), rows))
+
+    # ---- the decoder: logits and greedy tokens of the unsharded oracle ----
+    L, H, heads, kvh, hd, I, V, msl = 2, 256, 4, 2, 64, 512, 512, 96
+    eps, theta, act = 1e-5, 500000.0, cabi.ACT_SILU
+    plan = ShardPlan(world, rank, H, heads, kvh, hd, I, V)
+    odec = orc.Decoder(L, H, heads, kvh, hd, I, V, eps, theta, act, msl)
+    gdec = cabi.Decoder(ctx, L, H, heads, kvh, hd, I, V, eps, theta, act, msl)
+    shapes = ((heads * hd, H), (kvh * hd, H), (kvh * hd, H), (H, heads * hd), (I, H), (I, H), (H, I))
+    for b in range(L):
+        masters = [(rng.standard_normal(r * c) * 0.02).astype(np.float32) for r, c in shapes]
+        g1 = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+        g2 = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+        odec.set_block(b, *masters, g1=g1, g2=g2)
+        packed = [orc.pack_f32(m, r, c) for m, (r, c) in zip(masters, shapes)]
+        slices, _, _ = plan.shard_block([p[0] for p in packed])
+        ws = [ctx.upload_ternary(sw, sr, sc, packed[i][1]) for i, (sw, sr, sc) in enumerate(slices)]
+        gdec.set_block(b, ws, g1=g1, g2=g2)
+    emb = (rng.standard_normal((V, H)) * 0.02).astype(np.float32)
+    fg = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    odec.set_embeddings(emb, fg)
+    gdec.set_embeddings(ctx.to_device(emb), fg)
+    prompt = rng.integers(0, V, 13).astype(np.int32)
+    elog = odec.forward(prompt)
+    glog = gdec.forward(prompt)
+    tol = 1e-5 * max(1.0, float(np.max(np.abs(elog))))
+    if not np.max(np.abs(glog - elog)) <= tol:
+        failures.append("prompt logits differ by %g" % float(np.max(np.abs(glog - elog))))
+    nxt = np.array([orc.argmax(elog)], np.int32)
+    e2, g2_ = odec.forward(nxt), gdec.forward(nxt)
+    if not np.max(np.abs(g2_ - e2)) <= tol:
+        failures.append("step logits differ by %g" % float(np.max(np.abs(g2_ - e2))))
+    etok, _, _ = odec.generate(prompt, 20, threads=4, attn_threads=2)
+    gtok, m = gdec.generate(prompt, 20)
+    if not (gtok == etok).all():
+        failures.append("greedy tokens differ: %s vs %s" % (gtok.tolist(), etok.tolist()))
+    # every rank must hold the same logits bit for bit
+    mine = torch.from_numpy(gdec.forward(prompt).view(np.int32).astype(np.int64))
+    lo, hi = mine.clone(), mine.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    if not torch.equal(lo, hi):
+        failures.append("ranks disagree on the logits")
+    ctx.sync()
+    gdec.close()
+    dist.barrier()  # nobody leaves while a peer may still be inside a collective
+    ctx.tp_finalize()
+    dist.destroy_process_group()
+    if failures:
+        print("rank %d FAILED: %s" % (rank, "; ".join(failures)), flush=True)
+        sys.exit(1)
+    print("rank %d ok (%.1f us/token sharded decode)" % (rank, 1e6 * m.decode_device_seconds / max(1, m.generated_tokens)), flush=True)
+
+
+if __name__ == "__main__":
+    main()
