@@ -99,8 +99,8 @@ __global__ void __launch_bounds__(256) lb_scaled_absmax_kernel(const T* __restri
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
-        out[blockIdx.x] = fmaxf(m, red[0]);
+        for (int i = 0; i < 8; ++i) m = fmaxf(m, red[i]);
+        out[blockIdx.x] = m < 1e-5f ? 1e-5f : m;  // the quantizer's floor (poly/bitnet_cpu.go:53-55), so that the rescale sees it too
     }
 }
 
