@@ -250,6 +250,134 @@ def gemm_mode(args):
     return 0
 
 
+TP_SHAPES = {
+    "8b": dict(layers=32, hidden=4096, heads=32, kv_heads=8, head_dim=128, inter=14336, vocab=128256, eps=1e-5,
+               theta=500000.0, max_seq_len=1024),
+    "70b": dict(layers=80, hidden=8192, heads=64, kv_heads=8, head_dim=128, inter=28672, vocab=128256, eps=1e-5,
+                theta=500000.0, max_seq_len=1024),
+}
+
+
+def tp_mode(args):
+    """Tensor-parallel batch-1 decode of an 8B / 70B-shaped ternary decoder: one process per GPU (torchrun), column-
+    sharded Q/K/V/gate/up, row-sharded O/down with exact int32 all-reduces, vocabulary-sharded head.  Strong scaling:
+    the model is fixed and the group grows.  Each rank ternarises its own slices (synthetic weights, so the per-slice
+    absmean scale stands in for the whole-matrix one; timing does not depend on it)."""
+    import torch
+    import torch.distributed as dist
+
+    import loom_b200
+    from loom_b200 import cabi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    shape = dict(TP_SHAPES[args.shape])
+    if args.layers != SHAPE["layers"]:
+        shape["layers"] = args.layers
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tstream = torch.cuda.Stream()
+    torch.cuda.set_stream(tstream)
+    ctx = loom_b200.Context(local, tstream.cuda_stream)
+    if world > 1:
+        idt = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            idt.copy_(torch.frombuffer(bytearray(cabi.Context.tp_unique_id()), dtype=torch.uint8))
+        dist.broadcast(idt, 0)
+        torch.cuda.synchronize()
+        ctx.tp_init(rank, world, bytes(idt.cpu().numpy().tobytes()))
+    H, I, hd = shape["hidden"], shape["inter"], shape["head_dim"]
+    qd_l, kvd_l, I_l = shape["heads"] // world * hd, shape["kv_heads"] // world * hd, I // world
+    dims = ((qd_l, H), (kvd_l, H), (kvd_l, H), (H, qd_l), (I_l, H), (I_l, H), (H, I_l))
+    g = torch.Generator(device=dev)
+    g.manual_seed(args.seed + rank)
+    dec = cabi.Decoder(ctx, shape["layers"], H, shape["heads"], shape["kv_heads"], hd, I, shape["vocab"], shape["eps"],
+                       shape["theta"], cabi.ACT_SILU, shape["max_seq_len"])
+    keep = []
+    for b in range(shape["layers"]):
+        ws = []
+        for r, c in dims:
+            master = torch.randn(r * c, device=dev, generator=g, dtype=torch.float32) * 0.02
+            ws.append(ctx.pack_ternary_f32(master, r, c))
+            del master
+        dec.set_block(b, ws)
+        keep.append(ws)
+    ge = torch.Generator(device=dev)
+    ge.manual_seed(args.seed)  # the embedding table is replicated: the same on every rank
+    emb = torch.randn(shape["vocab"], H, device=dev, generator=ge, dtype=torch.float32) * 0.02
+    dec.set_embeddings(emb)
+    rng = np.random.default_rng(args.seed)
+    n_prompt = min(args.prompt, 64)
+    prompt = rng.integers(0, shape["vocab"], n_prompt).astype(np.int32)
+    args.warmup = max(args.warmup, 3)
+    assert n_prompt + args.warmup + args.steps + 2 <= shape["max_seq_len"]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    toks, _ = dec.generate(prompt, args.warmup)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    dec.continue_greedy(args.steps)
+    e1.record()
+    barrier()
+    dev_s = e0.elapsed_time(e1) * 1e-3
+    clocks = sampler.stop()
+    # end to end: token id in, logits out, host argmax
+    logits = dec.forward(np.array([int(prompt[0])], np.int32))
+    tok = int(np.argmax(logits))
+    e2e_steps = min(args.steps, 32)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        logits = dec.forward(np.array([tok], np.int32))
+        tok = int(np.argmax(logits))
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([dev_s, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_s, e2e_s = float(t[0].item()), float(t[1].item())
+    tern_b, kv_b, head_b = algorithmic_bytes(shape, n_prompt + args.warmup + args.steps // 2)
+    peak, peak_kind = measured_peaks()
+    step_s = dev_s / args.steps
+    launches = shape["layers"] * (6 if world == 1 else 12) + 4  # kernels of this library; the collectives are NCCL's
+    line = {
+        "metric": "decode tok/s (%s-shape ternary decoder, bs=1, tensor parallel)" % args.shape.upper(), "value": args.steps / dev_s,
+        "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * step_s,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x ternary -> int32, fp64 rescale",
+        "data": "synthetic",
+        "config": {"workload": "Llama-3-%s-shape ternary decoder, batch-1 greedy decode" % args.shape.upper(),
+                   "layers": shape["layers"], "prompt": n_prompt, "parallelism": "tp%d" % world,
+                   "l2": "every step streams the rank's packed weights and head slice, far beyond the 126 MB L2"},
+        "e2e": {"value": e2e_steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": shape["vocab"] * 4,
+                "steps": e2e_steps},
+        "gpu_launches": args.steps * launches, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": (tern_b + kv_b + head_b) / world / step_s / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": (tern_b + kv_b + head_b) / world / step_s / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "whole decode step, per-GPU bytes (packed weights + KV + fp32 head slice) / step time"},
+        "collectives_per_token": 0 if world == 1 else shape["layers"] * 6 + 1,
+    }
+    if rank == 0:
+        print(json.dumps(line))
+    ctx.sync()
+    dec.close()
+    barrier()
+    ctx.tp_finalize()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -261,11 +389,15 @@ def main():
     ap.add_argument("--vocab", type=int, default=SHAPE["vocab"], help="smaller vocabularies are for profiling captures only")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--mode", default="decode", choices=["decode", "gemm"], help="gemm: the batched-prefill GEMM microbenchmark")
+    ap.add_argument("--mode", default="decode", choices=["decode", "gemm", "tp"],
+                    help="gemm: the batched-prefill GEMM microbenchmark; tp: tensor-parallel decode of --shape under torchrun")
+    ap.add_argument("--shape", default="8b", choices=sorted(TP_SHAPES))
     ap.add_argument("--tokens", type=int, default=512)
     args = ap.parse_args()
     if args.mode == "gemm":
         return gemm_mode(args)
+    if args.mode == "tp":
+        return tp_mode(args)
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))

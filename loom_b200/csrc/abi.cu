@@ -78,6 +78,20 @@ int lb_ensure_scratch(loom_b200_ctx* ctx, size_t bytes) {
     return 0;
 }
 
+int lb_ensure_quant_scratch(loom_b200_ctx* ctx, size_t bytes) {
+    if (bytes <= ctx->quant_scratch_bytes) return 0;
+    LB_NO_CAPTURE(ctx, "growing the quantization scratch buffer");
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->quant_scratch) cudaFree(ctx->quant_scratch);
+    ctx->quant_scratch = nullptr;
+    ctx->quant_scratch_bytes = 0;
+    // sized for a full pass of kMaxM tokens at this width, so that later calls with more tokens find it large enough
+    size_t n = bytes * 2 + 4096;
+    LB_CUDA(ctx, cudaMalloc(&ctx->quant_scratch, n));
+    ctx->quant_scratch_bytes = n;
+    return 0;
+}
+
 // ---- re-tiling kernels -------------------------------------------------------------------------
 
 // One thread per output u32 of the tiled layout.
@@ -351,6 +365,7 @@ void loom_b200_ctx_destroy(loom_b200_ctx* ctx) {
     if (ctx->trace_dev) cudaFree(ctx->trace_dev);
     if (ctx->argmax_scratch) cudaFree(ctx->argmax_scratch);
     if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+    if (ctx->quant_scratch) cudaFree(ctx->quant_scratch);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }

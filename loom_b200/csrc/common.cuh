@@ -56,6 +56,8 @@ struct loom_b200_ctx {
     size_t scratch_bytes = 0;
     // device status word written by kernels with bounded waits (0 = ok)
     int* status_dev = nullptr;
+    void* quant_scratch = nullptr;   // int8 row and absmax of the stand-alone GEMV prologue (wide inputs)
+    size_t quant_scratch_bytes = 0;
     void* gemm_scratch = nullptr;    // int8 activations, amax and sums of the tensor-core GEMM path
     size_t gemm_scratch_bytes = 0;
     void* argmax_scratch = nullptr;  // per-CTA partial maxima of the greedy argmax
@@ -80,6 +82,7 @@ int lb_fail(loom_b200_ctx* ctx, int code, const char* fmt, ...);
 const char* lb_global_error();
 int lb_ensure_fixup(loom_b200_ctx* ctx, size_t acc_elems, size_t cnt_elems);
 int lb_ensure_scratch(loom_b200_ctx* ctx, size_t bytes);
+int lb_ensure_quant_scratch(loom_b200_ctx* ctx, size_t bytes);
 
 #define LB_CUDA(ctx, expr)                                                                          \
     do {                                                                                            \

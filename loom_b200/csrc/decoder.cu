@@ -346,8 +346,11 @@ int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int
         LB_CUDA(ctx, cudaMemcpyAsync(dec->tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
         if (int rc = dec_step(dec)) return rc;
     } else {
-        for (int s0 = 0; s0 < n; s0 += kChunkTokens) {
-            const int M = n - s0 < kChunkTokens ? n - s0 : kChunkTokens;
+        // tokens per pass: what the widest input row (hidden, or this rank's slice of the intermediate) leaves room for
+        const int widest = dec->inter_l > dec->d.hidden ? dec->inter_l : dec->d.hidden;
+        const int chunk = lb_gemv_max_tokens(widest) < kChunkTokens ? lb_gemv_max_tokens(widest) : kChunkTokens;
+        for (int s0 = 0; s0 < n; s0 += chunk) {
+            const int M = n - s0 < chunk ? n - s0 : chunk;
             LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // h_tok is reused
             for (int i = 0; i < M; ++i) dec->h_tok[i] = tokens[s0 + i];
             LB_CUDA(ctx, cudaMemcpyAsync(dec->tok, dec->h_tok, M * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));

@@ -337,6 +337,13 @@ size_t gemv_smem_bytes(const LbGemvParams& p, int max_local) {
 
 }  // namespace
 
+int lb_gemv_max_tokens(int K) {
+    const int Kp = (K + kTileCols - 1) / kTileCols * kTileCols;
+    const long long budget = 227 * 1024 - 2 * kWarps * kStageBytes - 12 * 1024;  // two ring stages, epilogue values, bookkeeping
+    long long m = budget / (Kp + 16);
+    return m >= kMaxM ? kMaxM : (m < 1 ? 1 : (int)m);
+}
+
 int lb_gemv_finalize_params(loom_b200_ctx* ctx, LbGemvParams& p) {
     LB_REQUIRE(ctx, p.nseg >= 1 && p.nseg <= 3, "gemv: %d segments", p.nseg);
     LB_REQUIRE(ctx, p.M >= 1 && p.M <= kMaxM, "gemv: %d tokens per pass (max %d)", p.M, kMaxM);
@@ -364,11 +371,11 @@ int lb_gemv_finalize_params(loom_b200_ctx* ctx, LbGemvParams& p) {
     return 0;
 }
 
-int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
-    LbGemvParams p = pin;
+// Partition, ring depth and shared-memory footprint for a grid of SMs x cps CTAs.
+static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int* grid_out, size_t* smem_out) {
     int vstrips = p.total_tiles / p.kblocks;
     int ngroups = (vstrips + p.group - 1) / p.group;
-    int grid = ctx->sm_count * ctx->opt_gemv_ctas_per_sm;
+    int grid = ctx->sm_count * cps;
     // Enough strip groups to occupy the SMs: give every CTA whole groups and skip the cross-CTA fix-up.
     p.aligned = ctx->opt_gemv_partition == 1 ? 0 : (ctx->opt_gemv_partition == 2 ? 1 : (ngroups * 2 >= ctx->sm_count ? 1 : 0));
     if (p.aligned) {
@@ -381,12 +388,6 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
         int tpc = (p.total_tiles + grid - 1) / grid;
         p.max_local_strips = (tpc + p.kblocks - 2) / p.kblocks + 1 + 2 * (p.group - 1);
     }
-    if (int rc = lb_ensure_fixup(ctx, (size_t)ngroups * p.group * p.M * 16, (size_t)ngroups)) return rc;
-    p.fix_acc = ctx->fix_acc;
-    p.fix_cnt = ctx->fix_cnt;
-    p.status = ctx->status_dev;
-    p.debug = ctx->opt_debug;
-    p.trace = lb_trace_row(ctx, "gemv");
     // ring depth: as many stages as the busiest warp has chunks (a chunk = up to 8 tiles inside one strip), up to 3
     {
         int most = 1;
@@ -424,6 +425,54 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
         if (gemv_smem_bytes(p, p.max_local_strips) + want <= 227 * 1024) p.stage_bytes = (int)want;
     }
     size_t smem = gemv_smem_bytes(p, p.max_local_strips);
+    while (smem > 227 * 1024 && p.stages > 1) {  // wide inputs: a shallower ring before giving up
+        --p.stages;
+        smem = gemv_smem_bytes(p, p.max_local_strips);
+    }
+    *grid_out = grid;
+    *smem_out = smem;
+}
+
+int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
+    LbGemvParams p = pin;
+    // Wide inputs: normalise and quantize once in a launch of its own, then stream the weights against the int8 row.
+    if (p.pro != LB_PRO_Q8 && p.K >= kSplitQuantK && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
+        (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) && (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) &&
+        (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0)) {
+        const size_t qbytes = ((size_t)p.M * p.K + 255) & ~(size_t)255;
+        if (int rc = lb_ensure_quant_scratch(ctx, qbytes + kMaxM * sizeof(float))) return rc;
+        int8_t* q = p.q_out ? p.q_out : reinterpret_cast<int8_t*>(ctx->quant_scratch);
+        float* amax = p.amax_out ? p.amax_out : reinterpret_cast<float*>((char*)ctx->quant_scratch + qbytes);
+        if (int rc = lb_launch_norm_quantize(ctx, p, q, amax)) return rc;
+        p.pro = LB_PRO_Q8;
+        p.x = q;
+        p.amax_in = amax;
+        p.norm_w = nullptr;
+        p.norm_w_len = 0;
+        p.given_ss = nullptr;
+        p.given_amax = nullptr;
+        p.q_out = nullptr;
+        p.amax_out = nullptr;
+        p.norm_out = nullptr;
+    }
+    int vstrips = p.total_tiles / p.kblocks;
+    int ngroups = (vstrips + p.group - 1) / p.group;
+    int grid = 0;
+    size_t smem = 0;
+    int cps = ctx->opt_gemv_ctas_per_sm;
+    gemv_plan(ctx, p, cps, &grid, &smem);
+    // A grid sized for more CTAs per SM than the shared memory lets be resident would run in waves, and every
+    // wave repeats the prologue: fall back to what fits (228 KB per SM, 1 KB reserved per CTA).
+    while (cps > 1 && (smem + 1024) * (size_t)cps > 228 * 1024) {
+        --cps;
+        gemv_plan(ctx, p, cps, &grid, &smem);
+    }
+    if (int rc = lb_ensure_fixup(ctx, (size_t)ngroups * p.group * p.M * 16, (size_t)ngroups)) return rc;
+    p.fix_acc = ctx->fix_acc;
+    p.fix_cnt = ctx->fix_cnt;
+    p.status = ctx->status_dev;
+    p.debug = ctx->opt_debug;
+    p.trace = lb_trace_row(ctx, "gemv");
     if (smem > 227 * 1024)
         return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: K=%d with %d tokens needs %zu B of shared memory", p.K, p.M, smem);
     // one instantiation per (inner loop, prologue, epilogue) combination that a caller can reach
@@ -448,6 +497,8 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     LB_PICK(9, true, LB_PRO_INNERNORM64, LB_EPI_GENERIC)
     LB_PICK(10, true, LB_PRO_INNERNORM, LB_EPI_GENERIC)
     LB_PICK(11, true, LB_PRO_Q8, LB_EPI_SWIGLU)
+    LB_PICK(12, true, LB_PRO_Q8, LB_EPI_QKV)
+    LB_PICK(13, true, LB_PRO_Q8, LB_EPI_RESID)
 #undef LB_PICK
     if (!kern) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: no kernel for prologue %d with epilogue %d", p.pro, p.epi);
     const unsigned attr_bit = 1u << kid;

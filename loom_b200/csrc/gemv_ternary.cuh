@@ -41,6 +41,10 @@ struct LbGemvSeg {
     int out_ring;  // > 0: token n goes to row (*pos_ptr + n) % out_ring of `out` (the KV ring), else row n
 };
 
+// Tokens one pass can carry for K input columns: the int8 activations of all tokens sit in shared memory beside a
+// weight ring of at least two stages.  8 for every K up to ~19,000; 5 for K = 28,672.
+int lb_gemv_max_tokens(int K);
+
 struct LbGemvParams {
     LbGemvSeg seg[3];
     int nseg;
@@ -82,3 +86,8 @@ struct LbGemvParams {
 int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& p);
 // Fills in the derived fields (vstrip0, total_tiles, max_local_strips) and checks shapes.
 int lb_gemv_finalize_params(loom_b200_ctx* ctx, LbGemvParams& p);
+
+// Inputs at least this wide are normalised and quantized by one stand-alone launch (lb_launch_norm_quantize)
+// instead of inside every CTA of the GEMV.
+constexpr int kSplitQuantK = 8192;
+int lb_launch_norm_quantize(loom_b200_ctx* ctx, const LbGemvParams& p, int8_t* q, float* amax);

@@ -230,18 +230,19 @@ int loom_b200_dense_forward(loom_b200_ctx* ctx, const loom_b200_weight* w, int a
     float* pre = ar.take<float>((size_t)batch * N);
     float* post = ar.take<float>((size_t)batch * N);
     LB_CUDA(ctx, cudaMemcpyAsync(x, in_host, (size_t)batch * K * 4, cudaMemcpyHostToDevice, ctx->stream));
+    const int chunk = lb_gemv_max_tokens(K) < kChunkTokens ? lb_gemv_max_tokens(K) : kChunkTokens;
     // a block of tokens is a dense contraction: tensor cores (tcgen05) from kGemmMinTokens on, the GEMV below it
     if (batch >= kGemmMinTokens) {
         if (int rc = lb_ternary_gemm(ctx, w, batch, x, nullptr, nullptr, activation, post, pre, nullptr, nullptr)) return rc;
     } else
-    for (int b0 = 0; b0 < batch; b0 += kChunkTokens) {
+    for (int b0 = 0; b0 < batch; b0 += chunk) {
         LbGemvParams p = {};
         p.nseg = 1;
         fill_seg(p.seg[0], w, nullptr, post + (size_t)b0 * N);
         p.seg[0].pre_out = pre + (size_t)b0 * N;
         p.seg[0].kind = LB_OUT_F32;
         p.K = K;
-        p.M = batch - b0 < kChunkTokens ? batch - b0 : kChunkTokens;
+        p.M = batch - b0 < chunk ? batch - b0 : chunk;
         p.pro = LB_PRO_F32;
         p.x = x + (size_t)b0 * K;
         p.epi = LB_EPI_GENERIC;
@@ -288,7 +289,8 @@ int loom_b200_swiglu_forward(loom_b200_ctx* ctx, const loom_b200_weight* gate, c
     LB_CUDA(ctx, h2d(bu, bias_up, I));
     LB_CUDA(ctx, h2d(bd, bias_down, H));
     LB_CUDA(ctx, h2d(iw, inner_norm_w, inner_norm_len));
-    for (int s0 = 0; s0 < seq; s0 += kChunkTokens) {
+    const int sw_chunk = lb_gemv_max_tokens(I > H ? I : H) < kChunkTokens ? lb_gemv_max_tokens(I > H ? I : H) : kChunkTokens;
+    for (int s0 = 0; s0 < seq; s0 += sw_chunk) {
         LbSwigluArgs a = {};
         a.gate = gate;
         a.up = up;
@@ -305,7 +307,7 @@ int loom_b200_swiglu_forward(loom_b200_ctx* ctx, const loom_b200_weight* gate, c
         a.prod = prod + (size_t)s0 * I;
         a.pre_out = pre + (size_t)s0 * I;
         a.out = out + (size_t)s0 * H;
-        a.M = seq - s0 < kChunkTokens ? seq - s0 : kChunkTokens;
+        a.M = seq - s0 < sw_chunk ? seq - s0 : sw_chunk;
         if (int rc = lb_swiglu_dev(ctx, a)) return rc;
     }
     if (pre_host) LB_CUDA(ctx, cudaMemcpyAsync(pre_host, pre, (size_t)seq * I * 4, cudaMemcpyDeviceToHost, ctx->stream));
@@ -413,13 +415,15 @@ int loom_b200_mha_forward(loom_b200_mha* m, const float* in_host, int batch, int
     LB_CUDA(ctx, cudaMemcpyAsync(x, in_host, (size_t)total * D * 4, cudaMemcpyHostToDevice, ctx->stream));
     LB_CUDA(ctx, cudaMemcpyAsync(m->pos_dev, &m->kv_offset, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
     LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    for (int s0 = 0; s0 < total; s0 += kChunkTokens) {
+    const int widest = m->q_dim > D ? m->q_dim : D;
+    const int mh_chunk = lb_gemv_max_tokens(widest) < kChunkTokens ? lb_gemv_max_tokens(widest) : kChunkTokens;
+    for (int s0 = 0; s0 < total; s0 += mh_chunk) {
         LbMhaStepArgs a = {};
         a.pro_mode = LB_PRO_F32;
         a.x = x + (size_t)s0 * D;
         a.pre_out = pre + (size_t)s0 * D;
         a.out = post + (size_t)s0 * D;
-        a.M = total - s0 < kChunkTokens ? total - s0 : kChunkTokens;
+        a.M = total - s0 < mh_chunk ? total - s0 : mh_chunk;
         a.splits = a.M == 1 ? 8 : 1;
         if (int rc = lb_mha_step_dev(m, a)) return rc;
         if (int rc = lb_launch_add_scalar(ctx, m->pos_dev, a.M)) return rc;

@@ -1,6 +1,6 @@
 // quantize.cu -- per-token absmax int8 activation quantization, the SwiGLU gate product and the
 // BitNet inner RMSNorm as stand-alone dispatches (the decode path fuses them into the GEMV instead).
-#include "common.cuh"
+#include "gemv_ternary.cuh"
 
 namespace {
 
@@ -78,7 +78,131 @@ __global__ void __launch_bounds__(kThreads) lb_inner_rmsnorm_kernel(float* __res
     }
 }
 
+// ---- stand-alone prologue of the GEMV for wide inputs ---------------------------------------------------------
+// The GEMV normally normalises and quantizes its input row inside every CTA (nothing to launch, nothing to
+// write).  That costs time proportional to K in each CTA; from kSplitQuantK columns on it is cheaper to do it
+// once, here, with one 1024-thread CTA per token, and let the GEMV load the int8 row.  Same operations in the
+// same order per element as stage_row_fast, so the int8 values and the absmax are the same bits.
+constexpr int kNqThreads = 1024;
+
+template <int PRO>
+__device__ __forceinline__ double nq_value(double x, double root, double rr, double w) {
+    if (PRO == LB_PRO_BLOCKNORM) return (double)(float)__dmul_rn(lb_div_by(x, root, rr), w);
+    if (PRO == LB_PRO_INNERNORM64) return __dmul_rn(x, __dmul_rn(rr, w));
+    if (PRO == LB_PRO_INNERNORM) return (double)(float)__dmul_rn(__dmul_rn(x, rr), w);
+    return x;
+}
+
+template <int PRO>
+__global__ void __launch_bounds__(kNqThreads) lb_norm_quantize_kernel(const LbGemvParams p, int8_t* __restrict__ q,
+                                                                      float* __restrict__ amax_out) {
+    __shared__ double red_d[32];
+    __shared__ float red_f[32];
+    constexpr bool f64 = PRO == LB_PRO_INNERNORM64;
+    const int n = blockIdx.x, tid = threadIdx.x, K = p.K, units = K >> 2;
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    const void* row = f64 ? (const void*)((const double*)p.x + (size_t)n * K) : (const void*)((const float*)p.x + (size_t)n * K);
+    auto load4 = [&](int idx, double* v) {
+        if (f64) {
+            const double2 a = reinterpret_cast<const double2*>(row)[2 * idx], b = reinterpret_cast<const double2*>(row)[2 * idx + 1];
+            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+        } else {
+            const float4 a = reinterpret_cast<const float4*>(row)[idx];
+            v[0] = (double)a.x; v[1] = (double)a.y; v[2] = (double)a.z; v[3] = (double)a.w;
+        }
+    };
+    const bool have_w = PRO != LB_PRO_F32 && p.norm_w != nullptr;
+    auto weights4 = [&](int idx, double* w) {
+        w[0] = w[1] = w[2] = w[3] = 1.0;
+        if (!have_w) return;
+        if (4 * idx + 4 <= p.norm_w_len) {
+            const float4 g = reinterpret_cast<const float4*>(p.norm_w)[idx];
+            w[0] = (double)g.x; w[1] = (double)g.y; w[2] = (double)g.z; w[3] = (double)g.w;
+        } else {
+            for (int k = 0; k < 4; ++k)
+                if (4 * idx + k < p.norm_w_len) w[k] = (double)p.norm_w[4 * idx + k];
+        }
+    };
+    double root = 1.0, rr = 1.0;
+    if (PRO >= LB_PRO_BLOCKNORM) {
+        double ss = 0.0;
+        if (p.given_ss) {
+            ss = p.given_ss[n];
+        } else {
+#pragma unroll 2
+            for (int idx = tid; idx < units; idx += kNqThreads) {
+                double v[4];
+                load4(idx, v);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) ss = __dadd_rn(ss, __dmul_rn(v[k], v[k]));
+            }
+            ss = block_sum(ss, red_d);
+        }
+        const double mean = __dadd_rn(__ddiv_rn(ss, (double)(p.norm_count > 0 ? p.norm_count : K)), p.eps);
+        root = sqrt(mean);
+        rr = __ddiv_rn(1.0, root);
+    }
+    float m = 0.0f;
+    if (p.given_amax) {
+        m = p.given_amax[n];
+    } else {
+#pragma unroll 2
+        for (int idx = tid; idx < units; idx += kNqThreads) {
+            double v[4], w[4];
+            load4(idx, v);
+            weights4(idx, w);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) m = fmaxf(m, (float)fabs(nq_value<PRO>(v[k], root, rr, w[k])));
+        }
+        m = block_max(m, red_f);
+    }
+    const float amax = m < 1e-5f ? 1e-5f : m;
+    const double s = __ddiv_rn(127.0, (double)amax);
+#pragma unroll 2
+    for (int idx = tid; idx < units; idx += kNqThreads) {
+        double v[4], w[4];
+        load4(idx, v);
+        weights4(idx, w);
+        uint32_t packed = 0;
+        float y4[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const double y = nq_value<PRO>(v[k], root, rr, w[k]);
+            y4[k] = (float)y;
+            packed |= (uint32_t)(lb_quant_i8(y, s) & 0xff) << (8 * k);
+        }
+        reinterpret_cast<uint32_t*>(q + (size_t)n * K)[idx] = packed;
+        if (p.norm_out) reinterpret_cast<float4*>(p.norm_out + (size_t)n * K)[idx] = make_float4(y4[0], y4[1], y4[2], y4[3]);
+    }
+    if (tid == 0) amax_out[n] = amax;
+}
+
 }  // namespace
+
+int lb_launch_norm_quantize(loom_b200_ctx* ctx, const LbGemvParams& p, int8_t* q, float* amax) {
+    using Kern = void (*)(const LbGemvParams, int8_t*, float*);
+    Kern kern = nullptr;
+    switch (p.pro) {
+        case LB_PRO_F32: kern = lb_norm_quantize_kernel<LB_PRO_F32>; break;
+        case LB_PRO_BLOCKNORM: kern = lb_norm_quantize_kernel<LB_PRO_BLOCKNORM>; break;
+        case LB_PRO_INNERNORM: kern = lb_norm_quantize_kernel<LB_PRO_INNERNORM>; break;
+        case LB_PRO_INNERNORM64: kern = lb_norm_quantize_kernel<LB_PRO_INNERNORM64>; break;
+        default: return lb_fail(ctx, LOOM_B200_ERR_INVALID, "norm_quantize: prologue %d has nothing to quantize", p.pro);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.M);
+    cfg.blockDim = dim3(kNqThreads);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+    LB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p, q, amax));
+    ctx->launches++;
+    return 0;
+}
 
 extern "C" {
 

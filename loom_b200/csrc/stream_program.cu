@@ -359,7 +359,11 @@ int lb_program_build(loom_b200_ctx* ctx, const std::vector<LbJob>& jobs_in, loom
     acts_bytes = (acts_bytes + 15) & ~15;
     size_t fixed = (size_t)acts_bytes + (size_t)sacc_ints * 4 + 32 + 32 + 256 + 3 * kMaxM * 8 + 16 + (size_t)kWarps * kPStagesMax * 8 + 16;
     size_t stage_room = (size_t)((stage_bytes + 15) & ~15);
-    const size_t budget = 225 * 1024;
+    // dynamic shared memory left beside the kernel's static part (the job block and the job table)
+    cudaFuncAttributes fattr;
+    LB_CUDA(ctx, cudaFuncGetAttributes(&fattr, lb_stream_kernel));
+    const size_t dyn_max = ((size_t)227 * 1024 - fattr.sharedSizeBytes) & ~(size_t)1023;
+    const size_t budget = dyn_max - 1024;
     // the staging buffer is optional (the slow generic prologue works without it); the ring needs at least 2 stages
     if (fixed + stage_room + (size_t)kWarps * 2 * kStageBytes > budget) {
         stage_room = 0;
@@ -379,7 +383,7 @@ int lb_program_build(loom_b200_ctx* ctx, const std::vector<LbJob>& jobs_in, loom
     if (e == cudaSuccess) e = cudaMemsetAsync(prog->barrier_dev, 0, 64, ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e == cudaSuccess && !(ctx->func_attr_mask & (1u << 28))) {
-        e = cudaFuncSetAttribute(lb_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        e = cudaFuncSetAttribute(lb_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_max);
         ctx->func_attr_mask |= 1u << 28;
     }
     if (e != cudaSuccess) {

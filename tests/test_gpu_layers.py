@@ -38,7 +38,8 @@ def pair(ctx, master, rows, cols):
 
 @pytest.mark.parametrize("rows,cols,batch,act", [(40, 70, 2, cabi.ACT_LINEAR), (6912, 2560, 1, cabi.ACT_LINEAR),
                                                  (128, 6912, 11, cabi.ACT_RELU2), (33, 65, 3, cabi.ACT_SILU),
-                                                 (16, 128, 2, cabi.ACT_GELU), (7, 191, 2, cabi.ACT_LEAKY_RELU)])
+                                                 (16, 128, 2, cabi.ACT_GELU), (7, 191, 2, cabi.ACT_LEAKY_RELU),
+                                                 (48, 8192, 3, cabi.ACT_LINEAR), (96, 28672, 7, cabi.ACT_RELU2)])
 def test_dense_forward(ctx, rows, cols, batch, act):
     rng = np.random.default_rng(rows + cols)
     m, w = pair(ctx, (rng.standard_normal(rows * cols) * 0.02).astype(np.float32), rows, cols)
@@ -64,7 +65,9 @@ def test_dense_reference_fixture(ctx):
 @pytest.mark.parametrize("H,I,seq,act,bias,inner", [(4, 6, 2, cabi.ACT_SILU, True, False),
                                                     (2560, 6912, 1, cabi.ACT_SILU, False, False),
                                                     (2560, 6912, 3, cabi.ACT_RELU2, False, True),
-                                                    (128, 200, 9, cabi.ACT_SILU, True, True)])
+                                                    (128, 200, 9, cabi.ACT_SILU, True, True),
+                                                    (128, 8192, 3, cabi.ACT_RELU2, True, True),
+                                                    (8192, 256, 2, cabi.ACT_SILU, False, False)])
 def test_swiglu_forward(ctx, H, I, seq, act, bias, inner):
     rng = np.random.default_rng(H + I)
     if H == 4:  # TestPackedTernarySwiGLUProducesFiniteOutput fixture, poly/tests/bitnet_cpu_test.go:388-409
@@ -216,5 +219,21 @@ def test_decoder_logits_and_greedy_tokens(ctx, L, H, heads, kvh, hd, I, V, act):
     # and again from a one-token prompt (fresh sequence, replayed frame)
     etok, _, _ = odec.generate(prompt[:1], 8)
     gtok, _ = gdec.generate(prompt[:1], 8)
+    assert (gtok == etok).all()
+    gdec.close()
+
+
+def test_decoder_with_wide_rows(ctx):
+    # hidden and heads*head_dim of 8192 columns: the block norms and the attention inner norm take the stand-alone
+    # normalise-and-quantize launch instead of the prologue fused into the GEMV
+    L, H, heads, kvh, hd, I, V = 1, 8192, 64, 8, 128, 512, 64
+    rng = np.random.default_rng(8192)
+    odec, gdec = make_decoder(ctx, rng, L, H, heads, kvh, hd, I, V, 1e-5, 500000.0, cabi.ACT_SILU, 32)
+    prompt = rng.integers(0, V, 11).astype(np.int32)
+    elog = odec.forward(prompt, threads=4)
+    glog = gdec.forward(prompt)
+    assert np.max(np.abs(glog - elog)) <= 1e-5 * max(1.0, float(np.max(np.abs(elog))))
+    etok, _, _ = odec.generate(prompt, 6, threads=4, attn_threads=4)
+    gtok, _ = gdec.generate(prompt, 6)
     assert (gtok == etok).all()
     gdec.close()
