@@ -43,9 +43,180 @@ struct loom_b200_decoder {
     bool head_sharded = false;                     // LM head computed in vocabulary slices and gathered
     double* tp_stats = nullptr;
     int32_t* tp_acc = nullptr;
+    // prompt blocks on the tensor cores: residual stream, queries, attention output, gate product and the raw
+    // gate/up accumulators of up to pf_cap tokens
+    int pf_cap = 0;
+    int* pf_tok = nullptr;
+    float *pf_x = nullptr, *pf_prod = nullptr;
+    double *pf_q = nullptr, *pf_attn = nullptr;
+    int32_t *pf_accg = nullptr, *pf_accu = nullptr;
 };
 
 namespace {
+
+constexpr int kPrefillBlock = 1024;  // prompt tokens per pass of the tensor-core path
+
+void dec_free_prefill(loom_b200_decoder* dec) {
+    void* ptrs[] = {dec->pf_tok, dec->pf_x, dec->pf_prod, dec->pf_q, dec->pf_attn, dec->pf_accg, dec->pf_accu};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    dec->pf_tok = nullptr;
+    dec->pf_x = dec->pf_prod = nullptr;
+    dec->pf_q = dec->pf_attn = nullptr;
+    dec->pf_accg = dec->pf_accu = nullptr;
+    dec->pf_cap = 0;
+}
+
+int dec_ensure_prefill(loom_b200_decoder* dec, int tokens) {
+    loom_b200_ctx* ctx = dec->ctx;
+    if (tokens <= dec->pf_cap) return 0;
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    dec_free_prefill(dec);
+    const loom_b200_decoder_dims& d = dec->d;
+    const size_t T = (size_t)tokens, qd = (size_t)d.num_heads * d.head_dim;
+    LB_CUDA(ctx, cudaMalloc(&dec->pf_tok, T * sizeof(int)));
+    LB_CUDA(ctx, cudaMalloc(&dec->pf_x, T * d.hidden * sizeof(float)));
+    LB_CUDA(ctx, cudaMalloc(&dec->pf_prod, T * d.intermediate * sizeof(float)));
+    LB_CUDA(ctx, cudaMalloc(&dec->pf_q, T * qd * sizeof(double)));
+    LB_CUDA(ctx, cudaMalloc(&dec->pf_attn, T * qd * sizeof(double)));
+    LB_CUDA(ctx, cudaMalloc(&dec->pf_accg, T * d.intermediate * sizeof(int32_t)));
+    LB_CUDA(ctx, cudaMalloc(&dec->pf_accu, T * d.intermediate * sizeof(int32_t)));
+    dec->pf_cap = tokens;
+    return 0;
+}
+
+// A block of M prompt tokens (already in pf_tok) at positions pos0..pos0+M-1 through the whole stack, every
+// projection as a token-block GEMM on the tensor cores.  Same arithmetic as dec_forward_chunk: the quantizer applies
+// the same norms, the GEMM accumulates the same int32 sums, the epilogues rescale in float64.
+int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
+    loom_b200_ctx* ctx = dec->ctx;
+    const loom_b200_decoder_dims& d = dec->d;
+    const int H = d.hidden, I = d.intermediate;
+    const double block_eps = d.rms_eps > 0 ? d.rms_eps : 1e-6;
+    if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, H, dec->pf_tok, M, dec->pf_x)) return rc;
+    for (auto& b : dec->blocks) {
+        loom_b200_mha& m = b.mha;
+        LbGemmQuant qa = {};
+        qa.pro = LB_PRO_BLOCKNORM;
+        qa.x = dec->pf_x;
+        qa.K = H;
+        qa.tokens = M;
+        qa.norm_w = b.g1;
+        qa.norm_w_len = H;
+        qa.eps = block_eps;
+        if (int rc = lb_gemm_quantize(ctx, qa)) return rc;
+        LbGemmOut o = {};
+        o.act = LOOM_B200_ACT_LINEAR;
+        o.bias = m.bq;
+        o.out_f64 = dec->pf_q;
+        if (int rc = lb_gemm_run(ctx, m.wq, M, o)) return rc;
+        o = LbGemmOut{};
+        o.act = LOOM_B200_ACT_LINEAR;
+        o.bias = m.bk;
+        o.out = m.cache_k + (size_t)pos0 * m.kv_dim;  // ring rows pos0.. are contiguous: a prompt never wraps
+        if (int rc = lb_gemm_run(ctx, m.wk, M, o)) return rc;
+        o.bias = m.bv;
+        o.out = m.cache_v + (size_t)pos0 * m.kv_dim;
+        if (int rc = lb_gemm_run(ctx, m.wv, M, o)) return rc;
+
+        LbRopeParams r = {};
+        r.q = dec->pf_q;
+        r.cache_k = m.cache_k;
+        r.pos_ptr = m.pos_dev;
+        r.rope_div = m.rope_div;
+        r.q_norm = m.q_norm;
+        r.q_norm_len = m.q_norm_len;
+        r.k_norm = m.k_norm;
+        r.k_norm_len = m.k_norm_len;
+        r.qk_eps = m.rms_eps > 0 ? m.rms_eps : 1e-6;
+        r.M = M;
+        r.heads = m.heads;
+        r.kv_heads = m.kv_heads;
+        r.hd = m.head_dim;
+        r.msl = m.msl;
+        if (int rc = lb_launch_rope(ctx, r)) return rc;
+
+        LbAttnParams t = {};
+        t.q = dec->pf_q;
+        t.cache_k = m.cache_k;
+        t.cache_v = m.cache_v;
+        t.pos_ptr = m.pos_dev;
+        t.out = dec->pf_attn;
+        t.part = m.part;
+        t.cnt = m.cnt;
+        t.M = M;
+        t.heads = m.heads;
+        t.kv_heads = m.kv_heads;
+        t.hd = m.head_dim;
+        t.msl = m.msl;
+        t.splits = 1;
+        t.max_chunk = pos0 + M;
+        if (int rc = lb_launch_attention(ctx, t)) return rc;
+
+        qa = LbGemmQuant{};
+        qa.pro = LB_PRO_INNERNORM64;
+        qa.x = dec->pf_attn;
+        qa.K = m.q_dim;
+        qa.tokens = M;
+        qa.norm_w = m.inner;
+        qa.norm_w_len = m.inner ? m.inner_len : 0;
+        qa.eps = m.rms_eps > 0 ? m.rms_eps : 1e-5;
+        if (int rc = lb_gemm_quantize(ctx, qa)) return rc;
+        o = LbGemmOut{};
+        o.act = LOOM_B200_ACT_LINEAR;
+        o.bias = m.bo;
+        o.out = dec->pf_x;
+        o.residual = dec->pf_x;
+        if (int rc = lb_gemm_run(ctx, m.wo, M, o)) return rc;
+
+        qa = LbGemmQuant{};
+        qa.pro = LB_PRO_BLOCKNORM;
+        qa.x = dec->pf_x;
+        qa.K = H;
+        qa.tokens = M;
+        qa.norm_w = b.g2;
+        qa.norm_w_len = H;
+        qa.eps = block_eps;
+        if (int rc = lb_gemm_quantize(ctx, qa)) return rc;
+        o = LbGemmOut{};
+        o.act = LOOM_B200_ACT_LINEAR;
+        o.acc_out = dec->pf_accg;
+        if (int rc = lb_gemm_run(ctx, b.gate, M, o)) return rc;
+        o.acc_out = dec->pf_accu;
+        if (int rc = lb_gemm_run(ctx, b.up, M, o)) return rc;
+        if (int rc = lb_gemm_gate_product(ctx, dec->pf_accg, dec->pf_accu, M, I, H, b.gate->scale, b.up->scale, nullptr, nullptr,
+                                          d.activation, dec->pf_prod))
+            return rc;
+
+        qa = LbGemmQuant{};
+        qa.pro = LB_PRO_INNERNORM;
+        qa.x = dec->pf_prod;
+        qa.K = I;
+        qa.tokens = M;
+        qa.norm_w = b.ffn_inner;
+        qa.norm_w_len = b.ffn_inner ? b.ffn_inner_len : 0;
+        qa.eps = 1e-5;  // the decoder builder never sets RMSNormEps on the SwiGLU layer
+        if (int rc = lb_gemm_quantize(ctx, qa)) return rc;
+        o = LbGemmOut{};
+        o.act = LOOM_B200_ACT_LINEAR;
+        o.out = dec->pf_x;
+        o.residual = dec->pf_x;
+        if (int rc = lb_gemm_run(ctx, b.down, M, o)) return rc;
+    }
+    if (head) {
+        LbLmHeadParams h = {};
+        h.x = dec->pf_x + (size_t)(M - 1) * H;
+        h.gain = dec->final_gain;
+        h.eps = block_eps;
+        h.head = dec->emb;
+        h.vocab = d.vocab;
+        h.hidden = H;
+        h.logits = dec->logits;
+        h.hidden_out = dec->hidden;
+        if (int rc = lb_launch_lm_head(ctx, h)) return rc;
+    }
+    return lb_launch_add_scalar(ctx, dec->pos, M);
+}
 
 int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int head_row) {
     loom_b200_ctx* ctx = dec->ctx;
@@ -224,6 +395,7 @@ void loom_b200_decoder_destroy(loom_b200_decoder* dec) {
         if (b.g2) cudaFree(b.g2);
         if (b.ffn_inner) cudaFree(b.ffn_inner);
     }
+    dec_free_prefill(dec);
     void* ptrs[] = {dec->final_gain, dec->x, dec->prod, dec->logits, dec->hidden, dec->tok, dec->pos, dec->step, dec->out_tokens,
                     dec->tp_stats, dec->tp_acc};
     for (void* p : ptrs)
@@ -345,6 +517,14 @@ int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int
         dec->h_tok[0] = tokens[0];
         LB_CUDA(ctx, cudaMemcpyAsync(dec->tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
         if (int rc = dec_step(dec)) return rc;
+    } else if (n >= kGemmMinTokens && dec->tp_world == 1 && ctx->opt_prefill_gemm) {
+        const int cap = n < kPrefillBlock ? n : kPrefillBlock;
+        if (int rc = dec_ensure_prefill(dec, cap)) return rc;
+        for (int s0 = 0; s0 < n; s0 += cap) {
+            const int M = n - s0 < cap ? n - s0 : cap;
+            LB_CUDA(ctx, cudaMemcpyAsync(dec->pf_tok, tokens + s0, (size_t)M * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+            if (int rc = dec_prefill_block(dec, M, dec->kv_offset + s0, s0 + M == n)) return rc;
+        }
     } else {
         // tokens per pass: what the widest input row (hidden, or this rank's slice of the intermediate) leaves room for
         const int widest = dec->inter_l > dec->d.hidden ? dec->inter_l : dec->d.hidden;

@@ -22,7 +22,7 @@
 //     float64 rescale, bias, activation and residual exactly like the GEMV epilogue.
 // Every mbarrier wait is bounded; on expiry the kernel raises the context's status word, frees its tensor
 // memory and returns.
-#include "common.cuh"
+#include "layers.cuh"
 
 namespace {
 
@@ -50,6 +50,7 @@ struct GemmParams {
     const float* residual;   // [tokens, rows] or null
     int act;
     float* out;              // [tokens, rows] or null
+    double* out_f64;         // [tokens, rows] float64 value before rounding (the attention query), or null
     float* pre_out;          // [tokens, rows] value before the activation, or null
     int32_t* acc_out;        // [tokens, rows] or null
     int* status;
@@ -213,6 +214,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
                     const int acc = (int)v[j] - s_xsum[c0 + j];
                     const size_t o = (size_t)tok * p.rows + r;
                     if (p.acc_out) p.acc_out[o] = acc;
+                    if (p.out_f64) {
+                        double y = __dmul_rn((double)acc, s_os[c0 + j]);
+                        if (p.bias) y = __dadd_rn(y, bias);
+                        p.out_f64[o] = y;
+                    }
                     if (p.out) {
                         double y = __dmul_rn((double)acc, s_os[c0 + j]);
                         if (p.bias) y = __dadd_rn(y, bias);
@@ -262,38 +268,65 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
     if (tid == 0 && s_failed) atomicExch(p.status, 3);
 }
 
-// Quantizer of the GEMM path: same arithmetic as lb_quantize_kernel, but the bytes of every 16-column group are
-// stored in the order the A expansion produces (position 4j+b holds column 4b+j), rows are padded with zeros
-// to Kp, and the per-token sum of the quantized values is written next to amax.
-__global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const float* __restrict__ x, int K, int Kp, int8_t* __restrict__ q,
+// Quantizer of the GEMM path: the GEMV prologues' arithmetic (plain absmax, or a block / inner RMSNorm first), but the
+// bytes of every 16-column group are stored in the order the A expansion produces (position 4j+b holds column
+// 4b+j), rows are padded with zeros to Kp, and the per-token sum of the quantized values is written next to amax.
+// One CTA per token.
+template <int PRO>
+__global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const LbGemmQuant a, int Kp, int8_t* __restrict__ q,
                                                                float* __restrict__ amax_out, int* __restrict__ xsum_out) {
     __shared__ float red[8];
+    __shared__ double redd[8];
     __shared__ int redi[8];
-    const float* row = x + (size_t)blockIdx.x * K;
+    constexpr bool f64 = PRO == LB_PRO_INNERNORM64;
+    const int K = a.K, tid = threadIdx.x;
+    const float* rowf = (const float*)a.x + (size_t)blockIdx.x * K;
+    const double* rowd = (const double*)a.x + (size_t)blockIdx.x * K;
+    auto ld = [&](int i) { return f64 ? rowd[i] : (double)rowf[i]; };
+    auto wt = [&](int i) { return (PRO != LB_PRO_F32 && a.norm_w && i < a.norm_w_len) ? (double)a.norm_w[i] : 1.0; };
     int8_t* qrow = q + (size_t)blockIdx.x * Kp;
+    double root = 1.0, rr = 1.0;
+    if (PRO >= LB_PRO_BLOCKNORM) {
+        double ss = 0.0;
+        for (int i = tid; i < K; i += blockDim.x) {
+            const double v = ld(i);
+            ss = __dadd_rn(ss, __dmul_rn(v, v));
+        }
+        ss = lb_warp_sum(ss);
+        if ((tid & 31) == 0) redd[tid >> 5] = ss;
+        __syncthreads();
+        ss = 0.0;
+        for (int i = 0; i < 8; ++i) ss += redd[i];
+        root = sqrt(__dadd_rn(__ddiv_rn(ss, (double)K), a.eps));
+        rr = __ddiv_rn(1.0, root);
+    }
     float m = 0.0f;
-    for (int i = threadIdx.x; i < K; i += blockDim.x) m = fmaxf(m, fabsf(row[i]));
+    for (int i = tid; i < K; i += blockDim.x) {
+        const double y = lb_pro_value<PRO>(ld(i), root, rr, wt(i));
+        if (a.norm_out) a.norm_out[(size_t)blockIdx.x * K + i] = (float)y;
+        m = fmaxf(m, (float)fabs(y));
+    }
     m = lb_warp_max(m);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    if ((tid & 31) == 0) red[tid >> 5] = m;
     __syncthreads();
     m = red[0];
     for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
     if (m < 1e-5f) m = 1e-5f;
     const double s = __ddiv_rn(127.0, (double)m);
     int sum = 0;
-    for (int c = threadIdx.x; c < Kp; c += blockDim.x) {
+    for (int c = tid; c < Kp; c += blockDim.x) {
         // destination byte c of the row: group base + 4j + b  <-  column base + 4b + j
         const int base = c & ~15, pos = c & 15, j = pos >> 2, b = pos & 3;
         const int col = base + 4 * b + j;
         int v = 0;
-        if (col < K) v = lb_quant_i8((double)row[col], s);
+        if (col < K) v = lb_quant_i8(lb_pro_value<PRO>(ld(col), root, rr, wt(col)), s);
         qrow[c] = (int8_t)v;
         sum += v;
     }
     sum = lb_warp_sum_i(sum);
-    if ((threadIdx.x & 31) == 0) redi[threadIdx.x >> 5] = sum;
+    if ((tid & 31) == 0) redi[tid >> 5] = sum;
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         int tot = 0;
         for (int i = 0; i < 8; ++i) tot += redi[i];
         amax_out[blockIdx.x] = m;
@@ -301,7 +334,117 @@ __global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const float* __re
     }
 }
 
+// gate product of a token block from the raw accumulators of the gate and up GEMMs (swigluGateProduct in float64,
+// poly/swiglu.go:37-46,299-306): prod = float32(f(acc_g * os_g + b_g) * (acc_u * os_u + b_u))
+__global__ void lb_gate_product_acc_kernel(const int32_t* __restrict__ acc_g, const int32_t* __restrict__ acc_u,
+                                           const float* __restrict__ amax, int tokens, int inter, float scale_g, float scale_u,
+                                           const float* __restrict__ bias_g, const float* __restrict__ bias_u, int act,
+                                           float* __restrict__ prod) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)tokens * inter) return;
+    const int tok = (int)(i / inter), r = (int)(i % inter);
+    double yg = __dmul_rn((double)acc_g[i], lb_output_scale(scale_g, amax[tok]));
+    double yu = __dmul_rn((double)acc_u[i], lb_output_scale(scale_u, amax[tok]));
+    if (bias_g) yg = __dadd_rn(yg, (double)bias_g[r]);
+    if (bias_u) yu = __dadd_rn(yu, (double)bias_u[r]);
+    prod[i] = (float)lb_gate_product(yg, yu, act);
+}
+
+// layout of the GEMM scratch for `tokens` rows of Kp bytes: int8 rows, amax, sums
+struct GemmScratch {
+    int8_t* q;
+    float* amax;
+    int* xsum;
+};
+GemmScratch gemm_scratch_at(void* base, int tokens, int Kp) {
+    GemmScratch g;
+    g.q = (int8_t*)base;
+    g.amax = (float*)((char*)base + (((size_t)tokens * Kp + 255) & ~(size_t)255));
+    g.xsum = (int*)(g.amax + tokens);
+    return g;
+}
+
 }  // namespace
+
+int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a) {
+    LB_REQUIRE(ctx, a.x && a.tokens > 0 && a.K > 0, "gemm_quantize: bad arguments");
+    const int Kp = (a.K + kTileCols - 1) / kTileCols * kTileCols;
+    // scratch: permuted int8 activations, amax, sum per token
+    size_t need = (size_t)a.tokens * Kp + 256 + (size_t)a.tokens * 8 + 256;
+    if (need > ctx->gemm_scratch_bytes) {  // its own buffer: layer calls keep their tensors in ctx->scratch
+        if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "ternary_gemm: scratch would grow while recording a graph");
+        LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+        ctx->gemm_scratch = nullptr;
+        ctx->gemm_scratch_bytes = 0;
+        LB_CUDA(ctx, cudaMalloc(&ctx->gemm_scratch, need + need / 4));
+        ctx->gemm_scratch_bytes = need + need / 4;
+    }
+    GemmScratch g = gemm_scratch_at(ctx->gemm_scratch, a.tokens, Kp);
+    switch (a.pro) {
+        case LB_PRO_F32: lb_quantize_gemm_kernel<LB_PRO_F32><<<a.tokens, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_BLOCKNORM: lb_quantize_gemm_kernel<LB_PRO_BLOCKNORM><<<a.tokens, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_INNERNORM: lb_quantize_gemm_kernel<LB_PRO_INNERNORM><<<a.tokens, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_INNERNORM64: lb_quantize_gemm_kernel<LB_PRO_INNERNORM64><<<a.tokens, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        default: return lb_fail(ctx, LOOM_B200_ERR_INVALID, "gemm_quantize: prologue %d", a.pro);
+    }
+    LB_CHECK_LAUNCH(ctx, "lb_quantize_gemm_kernel");
+    ctx->launches++;
+    return 0;
+}
+
+const float* lb_gemm_last_amax(loom_b200_ctx* ctx, int tokens, int K) {
+    const int Kp = (K + kTileCols - 1) / kTileCols * kTileCols;
+    return gemm_scratch_at(ctx->gemm_scratch, tokens, Kp).amax;
+}
+
+int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const LbGemmOut& o) {
+    LB_REQUIRE(ctx, w && tokens > 0 && (o.out || o.out_f64 || o.acc_out), "gemm_run: bad arguments");
+    LB_REQUIRE(ctx, w->device == ctx->device, "ternary_gemm: weight lives on device %d, context on %d", w->device, ctx->device);
+    const int Kp = w->kblocks * kTileCols;
+    LB_REQUIRE(ctx, (size_t)tokens * Kp <= ctx->gemm_scratch_bytes, "gemm_run: no quantized activations for %d tokens of %d columns", tokens, w->cols);
+    GemmScratch g = gemm_scratch_at(ctx->gemm_scratch, tokens, Kp);
+    GemmParams p = {};
+    p.tiles = w->tiles;
+    p.rows = w->rows;
+    p.strips = w->strips;
+    p.kblocks = w->kblocks;
+    p.scale = w->scale;
+    p.q = g.q;
+    p.amax = g.amax;
+    p.xsum = g.xsum;
+    p.tokens = tokens;
+    p.Kp = Kp;
+    p.bias = o.bias;
+    p.residual = o.residual;
+    p.act = o.act;
+    p.out = o.out;
+    p.out_f64 = o.out_f64;
+    p.pre_out = o.pre_out;
+    p.acc_out = o.acc_out;
+    p.status = ctx->status_dev;
+    p.debug = ctx->opt_debug;
+    const size_t smem = (size_t)kGemmStages * (kSliceBytesA + kSliceBytesB + kRawBytesA) + 1024;
+    if (!(ctx->func_attr_mask & (1u << 27))) {
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        ctx->func_attr_mask |= 1u << 27;
+    }
+    dim3 grid((w->rows + kRowsPerCta - 1) / kRowsPerCta, (tokens + kTokPerCta - 1) / kTokPerCta);
+    lb_gemm_ternary_i8_kernel<<<grid, kGemmThreads, smem, ctx->stream>>>(p);
+    LB_CHECK_LAUNCH(ctx, "lb_gemm_ternary_i8_kernel");
+    ctx->launches++;
+    return 0;
+}
+
+int lb_gemm_gate_product(loom_b200_ctx* ctx, const int32_t* acc_g, const int32_t* acc_u, int tokens, int inter, int K, float scale_g,
+                         float scale_u, const float* bias_g, const float* bias_u, int act, float* prod) {
+    const size_t n = (size_t)tokens * inter;
+    lb_gate_product_acc_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(acc_g, acc_u, lb_gemm_last_amax(ctx, tokens, K), tokens, inter,
+                                                                                      scale_g, scale_u, bias_g, bias_u, act, prod);
+    LB_CHECK_LAUNCH(ctx, "lb_gate_product_acc_kernel");
+    ctx->launches++;
+    return 0;
+}
 
 int lb_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const float* x, const float* bias,
                     const float* residual, int activation, float* out, float* pre_out, int32_t* acc_out, float* amax_out);
@@ -318,52 +461,22 @@ int lb_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, c
     LB_REQUIRE(ctx, tokens >= 0, "ternary_gemm: tokens=%d", tokens);
     if (tokens == 0) return 0;
     LB_REQUIRE(ctx, x && (out || acc_out), "ternary_gemm: NULL buffer");
-    LB_REQUIRE(ctx, w->device == ctx->device, "ternary_gemm: weight lives on device %d, context on %d", w->device, ctx->device);
     if (int rc = lb_set_device(ctx)) return rc;
-    const int Kp = w->kblocks * kTileCols;
-    // scratch: permuted int8 activations, amax, sum per token
-    size_t need = (size_t)tokens * Kp + 256 + (size_t)tokens * 8 + 256;
-    if (need > ctx->gemm_scratch_bytes) {  // its own buffer: layer calls keep their tensors in ctx->scratch
-        if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "ternary_gemm: scratch would grow while recording a graph");
-        LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
-        ctx->gemm_scratch = nullptr;
-        ctx->gemm_scratch_bytes = 0;
-        LB_CUDA(ctx, cudaMalloc(&ctx->gemm_scratch, need + need / 4));
-        ctx->gemm_scratch_bytes = need + need / 4;
-    }
-    int8_t* q = (int8_t*)ctx->gemm_scratch;
-    float* amax = (float*)((char*)ctx->gemm_scratch + (((size_t)tokens * Kp + 255) & ~(size_t)255));
-    int* xsum = (int*)(amax + tokens);
-    lb_quantize_gemm_kernel<<<tokens, 256, 0, ctx->stream>>>(x, w->cols, Kp, q, amax, xsum);
-    LB_CHECK_LAUNCH(ctx, "lb_quantize_gemm_kernel");
-    GemmParams p = {};
-    p.tiles = w->tiles;
-    p.rows = w->rows;
-    p.strips = w->strips;
-    p.kblocks = w->kblocks;
-    p.scale = w->scale;
-    p.q = q;
-    p.amax = amax;
-    p.xsum = xsum;
-    p.tokens = tokens;
-    p.Kp = Kp;
-    p.bias = bias;
-    p.residual = residual;
-    p.act = activation;
-    p.out = out;
-    p.pre_out = pre_out;
-    p.acc_out = acc_out;
-    p.status = ctx->status_dev;
-    p.debug = ctx->opt_debug;
-    const size_t smem = (size_t)kGemmStages * (kSliceBytesA + kSliceBytesB + kRawBytesA) + 1024;
-    if (!(ctx->func_attr_mask & (1u << 27))) {
-        LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        ctx->func_attr_mask |= 1u << 27;
-    }
-    dim3 grid((w->rows + kRowsPerCta - 1) / kRowsPerCta, (tokens + kTokPerCta - 1) / kTokPerCta);
-    lb_gemm_ternary_i8_kernel<<<grid, kGemmThreads, smem, ctx->stream>>>(p);
-    LB_CHECK_LAUNCH(ctx, "lb_gemm_ternary_i8_kernel");
-    if (amax_out) LB_CUDA(ctx, cudaMemcpyAsync(amax_out, amax, (size_t)tokens * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    LbGemmQuant qa = {};
+    qa.pro = LB_PRO_F32;
+    qa.x = x;
+    qa.K = w->cols;
+    qa.tokens = tokens;
+    if (int rc = lb_gemm_quantize(ctx, qa)) return rc;
+    LbGemmOut o = {};
+    o.bias = bias;
+    o.residual = residual;
+    o.act = activation;
+    o.out = out;
+    o.pre_out = pre_out;
+    o.acc_out = acc_out;
+    if (int rc = lb_gemm_run(ctx, w, tokens, o)) return rc;
+    if (amax_out)
+        LB_CUDA(ctx, cudaMemcpyAsync(amax_out, lb_gemm_last_amax(ctx, tokens, w->cols), (size_t)tokens * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
     return 0;
 }

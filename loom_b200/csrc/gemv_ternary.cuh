@@ -87,6 +87,17 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& p);
 // Fills in the derived fields (vstrip0, total_tiles, max_local_strips) and checks shapes.
 int lb_gemv_finalize_params(loom_b200_ctx* ctx, LbGemvParams& p);
 
+// The value a prologue hands to the quantizer for input x: block RMSNorm (x / rms) * g rounded to float32
+// (poly/norm.go:102-138), inner RMSNorm (x * (1/rms)) * w rounded to float32 (poly/bitnet_cpu.go:893-913) or,
+// on the float64 attention output, x * ((1/rms) * w) kept in float64 (poly/bitnet_cpu.go:868-887); plain rows pass through.
+template <int PRO>
+__device__ __forceinline__ double lb_pro_value(double x, double root, double rr, double w) {
+    if (PRO == LB_PRO_BLOCKNORM) return (double)(float)__dmul_rn(lb_div_by(x, root, rr), w);
+    if (PRO == LB_PRO_INNERNORM64) return __dmul_rn(x, __dmul_rn(rr, w));
+    if (PRO == LB_PRO_INNERNORM) return (double)(float)__dmul_rn(__dmul_rn(x, rr), w);
+    return x;
+}
+
 // Inputs at least this wide are normalised and quantized by one stand-alone launch (lb_launch_norm_quantize)
 // instead of inside every CTA of the GEMV.
 constexpr int kSplitQuantK = 8192;

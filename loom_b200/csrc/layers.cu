@@ -8,7 +8,6 @@
 
 int lb_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const float* x, const float* bias,
                     const float* residual, int activation, float* out, float* pre_out, int32_t* acc_out, float* amax_out);
-constexpr int kGemmMinTokens = 32;
 
 namespace {
 

@@ -84,3 +84,31 @@ int lb_tp_allgather_f32(loom_b200_ctx* ctx, const float* send, float* recv, size
 int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool x_is_f64, const void* x, int M, int K_global,
                             const float* inner_w, int inner_w_len, double eps, const float* bias, const float* residual,
                             float* out, double* stats, int32_t* acc);
+
+// ---- token blocks on the tensor cores (gemm_ternary_i8.cu) ------------------------------------------------
+// A block of tokens is quantized once (optionally through a block or inner RMSNorm, LbPrologue) into the
+// context's GEMM scratch, then any number of projections run against those int8 rows.
+struct LbGemmQuant {
+    int pro;              // LbPrologue: LB_PRO_F32, LB_PRO_BLOCKNORM, LB_PRO_INNERNORM, LB_PRO_INNERNORM64
+    const void* x;        // [tokens, K] float32 (float64 for LB_PRO_INNERNORM64)
+    int K, tokens;
+    const float* norm_w;  // gain / inner-norm weight or null
+    int norm_w_len;
+    double eps;
+    float* norm_out;      // optional [tokens, K]: the normalised rows as float32
+};
+struct LbGemmOut {
+    const float* bias;      // [rows] or null
+    const float* residual;  // [tokens, rows] or null, may alias out
+    int act;
+    float* out;             // [tokens, rows] float32 or null
+    double* out_f64;        // [tokens, rows] float64 (before rounding and activation) or null
+    float* pre_out;         // [tokens, rows] value before the activation or null
+    int32_t* acc_out;       // [tokens, rows] raw accumulators or null
+};
+int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a);
+int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const LbGemmOut& o);
+// gate product from the raw accumulators of the gate and up projections of the block quantized last (K columns)
+int lb_gemm_gate_product(loom_b200_ctx* ctx, const int32_t* acc_g, const int32_t* acc_u, int tokens, int inter, int K, float scale_g,
+                         float scale_u, const float* bias_g, const float* bias_u, int act, float* prod);
+constexpr int kGemmMinTokens = 32;  // from this many tokens on a projection runs on the tensor cores

@@ -86,14 +86,6 @@ __global__ void __launch_bounds__(kThreads) lb_inner_rmsnorm_kernel(float* __res
 constexpr int kNqThreads = 1024;
 
 template <int PRO>
-__device__ __forceinline__ double nq_value(double x, double root, double rr, double w) {
-    if (PRO == LB_PRO_BLOCKNORM) return (double)(float)__dmul_rn(lb_div_by(x, root, rr), w);
-    if (PRO == LB_PRO_INNERNORM64) return __dmul_rn(x, __dmul_rn(rr, w));
-    if (PRO == LB_PRO_INNERNORM) return (double)(float)__dmul_rn(__dmul_rn(x, rr), w);
-    return x;
-}
-
-template <int PRO>
 __global__ void __launch_bounds__(kNqThreads) lb_norm_quantize_kernel(const LbGemvParams p, int8_t* __restrict__ q,
                                                                       float* __restrict__ amax_out) {
     __shared__ double red_d[32];
@@ -153,7 +145,7 @@ __global__ void __launch_bounds__(kNqThreads) lb_norm_quantize_kernel(const LbGe
             load4(idx, v);
             weights4(idx, w);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) m = fmaxf(m, (float)fabs(nq_value<PRO>(v[k], root, rr, w[k])));
+            for (int k = 0; k < 4; ++k) m = fmaxf(m, (float)fabs(lb_pro_value<PRO>(v[k], root, rr, w[k])));
         }
         m = block_max(m, red_f);
     }
@@ -168,7 +160,7 @@ __global__ void __launch_bounds__(kNqThreads) lb_norm_quantize_kernel(const LbGe
         float y4[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const double y = nq_value<PRO>(v[k], root, rr, w[k]);
+            const double y = lb_pro_value<PRO>(v[k], root, rr, w[k]);
             y4[k] = (float)y;
             packed |= (uint32_t)(lb_quant_i8(y, s) & 0xff) << (8 * k);
         }

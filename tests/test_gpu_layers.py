@@ -237,3 +237,31 @@ def test_decoder_with_wide_rows(ctx):
     gtok, _ = gdec.generate(prompt, 6)
     assert (gtok == etok).all()
     gdec.close()
+
+
+@pytest.mark.parametrize("n_prompt", [32, 70, 150])
+def test_decoder_prompt_blocks_on_tensor_cores(ctx, n_prompt):
+    # prompts of 32+ tokens run every projection as a token-block GEMM (tcgen05); the logits, the KV rings and the
+    # greedy continuation must be those of the oracle, and of the eight-token GEMV path
+    L, H, heads, kvh, hd, I, V = 2, 256, 4, 2, 64, 384, 300
+    rng = np.random.default_rng(n_prompt)
+    odec, gdec = make_decoder(ctx, rng, L, H, heads, kvh, hd, I, V, 1e-5, 500000.0, cabi.ACT_SILU, 256)
+    prompt = rng.integers(0, V, n_prompt).astype(np.int32)
+    elog = odec.forward(prompt, threads=4)
+    glog = gdec.forward(prompt)
+    tol = 1e-5 * max(1.0, float(np.max(np.abs(elog))))
+    assert np.max(np.abs(glog - elog)) <= tol
+    k_gemm, v_gemm = gdec.cache(L - 1)
+    ctx.set_option("prefill_gemm", 0)
+    try:
+        slog = gdec.forward(prompt)
+        k_gemv, v_gemv = gdec.cache(L - 1)
+    finally:
+        ctx.set_option("prefill_gemm", 1)
+    assert np.max(np.abs(glog - slog)) <= tol
+    assert np.allclose(k_gemm[:n_prompt], k_gemv[:n_prompt], rtol=1e-5, atol=1e-6)
+    assert np.allclose(v_gemm[:n_prompt], v_gemv[:n_prompt], rtol=1e-5, atol=1e-6)
+    etok, _, _ = odec.generate(prompt, 12, threads=4, attn_threads=4)
+    gtok, _ = gdec.generate(prompt, 12)
+    assert (gtok == etok).all()
+    gdec.close()
