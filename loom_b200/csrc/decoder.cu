@@ -151,7 +151,11 @@ int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
         t.msl = m.msl;
         t.splits = 1;
         t.max_chunk = pos0 + M;
-        if (int rc = lb_launch_attention(ctx, t)) return rc;
+        if (lb_attention_prefill_supported(t)) {
+            if (int rc = lb_launch_attention_prefill(ctx, t)) return rc;
+        } else if (int rc = lb_launch_attention(ctx, t)) {
+            return rc;
+        }
 
         qa = LbGemmQuant{};
         qa.pro = LB_PRO_INNERNORM64;

@@ -447,6 +447,186 @@ __global__ void lb_add_scalar_kernel(int* p, int delta) {
     if (threadIdx.x == 0) *p += delta;
 }
 
+// Causal attention of a block of prompt tokens.  One CTA per (KV head, tile of query tokens): the 64 query rows of
+// a CTA are the heads of one GQA group times 64/group consecutive tokens, so every K and V tile that is brought
+// into shared memory (64 positions, one 512-byte bulk copy per row) serves all of them.  Scores, the running
+// softmax (maximum, sum, rescaling of the partial output when the maximum moves) and the weighted V sum are float64
+// like the reference's loops (poly/mha.go:296-356); only the order of the float64 additions differs.
+// Threads form a 16 x 16 grid: thread (ty, tx) owns score rows ty+16i and key columns tx+16j, and output rows
+// ty+16i, dimensions tx+16j.
+constexpr int kPfRows = 64, kPfKeys = 64, kPfThreads = 256;
+
+__global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(const LbAttnParams p) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2];
+    __shared__ double s_m[kPfRows], s_l[kPfRows], s_alpha[kPfRows];
+    __shared__ int s_qpos[kPfRows];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, ty = tid >> 4, tx = tid & 15;
+    const int hd = p.hd, kvd = p.kv_heads * hd, qd = p.heads * hd;
+    const int group = p.heads / p.kv_heads, TQ = kPfRows / group;
+    const int kvh = blockIdx.x, qt = (int)gridDim.y - 1 - (int)blockIdx.y;  // long rows first
+    const int tok0 = qt * TQ;
+    const int qstride = hd + 2, rowf = hd + 4, sstride = kPfKeys + 1;
+    double* Qs = reinterpret_cast<double*>(smem_raw);                    // [64, hd+2]
+    double* Ss = Qs + (size_t)kPfRows * qstride;                         // [64, 65]
+    float* Kt = reinterpret_cast<float*>(Ss + (size_t)kPfRows * sstride);  // [64, hd+4]
+    float* Vt = Kt + (size_t)kPfKeys * rowf;                             // [64, hd+4]
+    if (tid == 0) {
+        lb_mbar_init(&bars[0], 1);
+        lb_mbar_init(&bars[1], 1);
+        lb_fence_mbar_init();
+    }
+    __syncthreads();
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    const int pos0 = *p.pos_ptr;
+    const int ntok = p.M - tok0 < TQ ? p.M - tok0 : TQ;  // tokens of this tile
+    const int max_pos = pos0 + tok0 + ntok - 1;
+    const int ntiles = max_pos / kPfKeys + 1;
+    const float* kbase = p.cache_k + (size_t)kvh * hd;
+    const float* vbase = p.cache_v + (size_t)kvh * hd;
+    {
+        const int rows0 = max_pos + 1 < kPfKeys ? max_pos + 1 : kPfKeys;
+        if (warp == 0) attn_fetch_rows(Kt, kbase, rowf, hd, kvd, p.msl, 0, rows0, &bars[0], lane);
+        if (warp == 1) attn_fetch_rows(Vt, vbase, rowf, hd, kvd, p.msl, 0, rows0, &bars[1], lane);
+    }
+    // query rows: row r = (head hi of the group, token ti); rows of absent tokens are zero and never written back
+    for (int idx = tid; idx < kPfRows * hd; idx += kPfThreads) {
+        const int r = idx / hd, d = idx - r * hd;
+        const int hi = r / TQ, ti = r - hi * TQ;
+        double v = 0.0;
+        if (ti < ntok) v = p.q[(size_t)(tok0 + ti) * qd + (size_t)(kvh * group + hi) * hd + d];
+        Qs[(size_t)r * qstride + d] = v;
+    }
+    if (tid < kPfRows) {
+        const int ti = tid % TQ;
+        s_qpos[tid] = ti < ntok ? pos0 + tok0 + ti : -1;  // -1: nothing is attended, the row stays empty
+        s_m[tid] = -1e300;
+        s_l[tid] = 0.0;
+    }
+    __syncthreads();
+    const double scale = __ddiv_rn(1.0, sqrt((double)hd));
+    double o[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[i][j] = 0.0;
+    const int ndim = hd / 16;  // output dimensions per thread (8 for head_dim 128)
+    bool failed = false;
+    for (int t = 0; t < ntiles; ++t) {
+        const int kbase_pos = t * kPfKeys;
+        const int krows = max_pos + 1 - kbase_pos < kPfKeys ? max_pos + 1 - kbase_pos : kPfKeys;
+        if (!failed && !lb_mbar_wait_bounded(&bars[0], (uint32_t)(t & 1))) failed = true;
+        // ---- scores of this tile ----
+        double acc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
+        for (int d = 0; d < hd; d += 4) {
+            double qv[4][4];
+            float4 kv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const double2 a = *reinterpret_cast<const double2*>(Qs + (size_t)(ty + 16 * i) * qstride + d);
+                const double2 b = *reinterpret_cast<const double2*>(Qs + (size_t)(ty + 16 * i) * qstride + d + 2);
+                qv[i][0] = a.x; qv[i][1] = a.y; qv[i][2] = b.x; qv[i][3] = b.y;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(Kt + (size_t)(tx + 16 * j) * rowf + d);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fma(qv[i][0], (double)kv[j].x, acc[i][j]);
+                    acc[i][j] = fma(qv[i][1], (double)kv[j].y, acc[i][j]);
+                    acc[i][j] = fma(qv[i][2], (double)kv[j].z, acc[i][j]);
+                    acc[i][j] = fma(qv[i][3], (double)kv[j].w, acc[i][j]);
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) Ss[(size_t)(ty + 16 * i) * sstride + tx + 16 * j] = __dmul_rn(acc[i][j], scale);
+        __syncthreads();  // scores complete, K tile free
+        if (t + 1 < ntiles && warp == 0) {
+            const int nrows = max_pos + 1 - (kbase_pos + kPfKeys) < kPfKeys ? max_pos + 1 - (kbase_pos + kPfKeys) : kPfKeys;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            attn_fetch_rows(Kt, kbase, rowf, hd, kvd, p.msl, kbase_pos + kPfKeys, nrows, &bars[0], lane);
+        }
+        // ---- running softmax: four threads per row, sixteen keys each ----
+        {
+            const int r = tid >> 2, part = tid & 3;
+            const int qpos = s_qpos[r];
+            double* srow = Ss + (size_t)r * sstride + part * 16;
+            double tmax = -1e300;
+#pragma unroll 4
+            for (int k = 0; k < 16; ++k)
+                if (kbase_pos + part * 16 + k <= qpos) tmax = fmax(tmax, srow[k]);
+            tmax = fmax(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmax(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            const double m_old = s_m[r];
+            const double m_new = fmax(m_old, tmax);
+            double sum = 0.0;
+#pragma unroll 4
+            for (int k = 0; k < 16; ++k) {
+                double e = 0.0;
+                if (kbase_pos + part * 16 + k <= qpos) e = exp(__dsub_rn(srow[k], m_new));
+                srow[k] = e;
+                sum = __dadd_rn(sum, e);
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if (part == 0) {
+                const double alpha = m_old > -1e299 ? exp(__dsub_rn(m_old, m_new)) : 0.0;
+                s_alpha[r] = alpha;
+                s_l[r] = __dadd_rn(__dmul_rn(s_l[r], alpha), sum);
+                s_m[r] = m_new;
+            }
+        }
+        __syncthreads();  // weights and rescale factors visible
+        if (!failed && !lb_mbar_wait_bounded(&bars[1], (uint32_t)(t & 1))) failed = true;
+        // ---- weighted V ----
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const double al = s_alpha[ty + 16 * i];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[i][j] = __dmul_rn(o[i][j], al);
+        }
+        for (int k = 0; k < krows; ++k) {
+            double pw[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pw[i] = Ss[(size_t)(ty + 16 * i) * sstride + k];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j < ndim) {
+                    const double v = (double)Vt[(size_t)k * rowf + tx + 16 * j];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[i][j] = fma(pw[i], v, o[i][j]);
+                }
+            }
+        }
+        __syncthreads();  // V tile and weights free
+        if (t + 1 < ntiles && warp == 1) {
+            const int nrows = max_pos + 1 - (kbase_pos + kPfKeys) < kPfKeys ? max_pos + 1 - (kbase_pos + kPfKeys) : kPfKeys;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            attn_fetch_rows(Vt, vbase, rowf, hd, kvd, p.msl, kbase_pos + kPfKeys, nrows, &bars[1], lane);
+        }
+    }
+    if (failed && tid == 0) atomicExch(p.status, 1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty + 16 * i;
+        const int hi = r / TQ, ti = r - hi * TQ;
+        if (ti >= ntok) continue;
+        const double den = s_l[r];
+        double* orow = p.out + (size_t)(tok0 + ti) * qd + (size_t)(kvh * group + hi) * hd;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j < ndim) orow[tx + 16 * j] = __ddiv_rn(o[i][j], den);
+    }
+}
+
 template <typename... Args>
 cudaError_t launch_pdl(loom_b200_ctx* ctx, void (*kern)(Args...), dim3 grid, dim3 block, size_t smem, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -497,6 +677,30 @@ int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& pin) {
         ctx->func_attr_mask |= 1u << 30;
     }
     LB_CUDA(ctx, launch_pdl(ctx, lb_attention_kernel, dim3(p.heads, p.M, p.splits), dim3(kAttnThreads), smem, p));
+    ctx->launches++;
+    return 0;
+}
+
+bool lb_attention_prefill_supported(const LbAttnParams& p) {
+    const int group = p.kv_heads > 0 ? p.heads / p.kv_heads : 0;
+    return p.kv_heads > 0 && p.heads % p.kv_heads == 0 && group >= 1 && group <= kPfRows && (kPfRows % group) == 0 &&
+           p.hd % 16 == 0 && p.hd >= 16 && p.hd <= 128;
+}
+
+int lb_launch_attention_prefill(loom_b200_ctx* ctx, const LbAttnParams& pin) {
+    LbAttnParams p = pin;
+    p.trace = nullptr;
+    p.status = ctx->status_dev;
+    LB_REQUIRE(ctx, lb_attention_prefill_supported(p), "attention (prompt block): %d heads over %d kv heads of %d dimensions", p.heads,
+               p.kv_heads, p.hd);
+    const int TQ = kPfRows / (p.heads / p.kv_heads);
+    const size_t smem = (size_t)kPfRows * (p.hd + 2) * sizeof(double) + (size_t)kPfRows * (kPfKeys + 1) * sizeof(double) +
+                        2 * (size_t)kPfKeys * (p.hd + 4) * sizeof(float);
+    if (!(ctx->func_attr_mask & (1u << 26))) {
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        ctx->func_attr_mask |= 1u << 26;
+    }
+    LB_CUDA(ctx, launch_pdl(ctx, lb_attention_prefill_kernel, dim3(p.kv_heads, (p.M + TQ - 1) / TQ), dim3(kPfThreads), smem, p));
     ctx->launches++;
     return 0;
 }

@@ -37,6 +37,11 @@ struct LbAttnParams {
 };
 int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p);
 size_t lb_attn_part_elems(int M, int heads, int hd, int splits);
+// The same attention for a block of M prompt tokens at once (splits, part and cnt are not used): K/V tiles are shared
+// by the heads of a GQA group and by 64/group consecutive query tokens.  Needs head_dim % 16 == 0, head_dim <= 128
+// and a group size that divides 64; lb_attention_prefill_supported says whether a shape qualifies.
+bool lb_attention_prefill_supported(const LbAttnParams& p);
+int lb_launch_attention_prefill(loom_b200_ctx* ctx, const LbAttnParams& p);
 
 struct LbLmHeadParams {
     const float* x;        // [hidden] last hidden row (before the final norm)
