@@ -233,6 +233,50 @@ def gemm_mode(args):
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / args.steps
         res[name] = {"us": us, "tops": 2.0 * M * rows * cols / us / 1e6}
+    # config 0 beside it: the same two shapes at M = 1 through the decode GEMV (16 distinct matrices per replay)
+    gemv = {}
+    for name, rows, cols in (("gate", 6912, 2560), ("down", 2560, 6912)):
+        ws = [ctx.pack_ternary_f32(torch.randn(rows * cols, device=dev, generator=g) * 0.02, rows, cols) for _ in range(16)]
+        x = torch.randn(1, cols, device=dev, generator=g)
+        q, am = torch.empty(1, cols, dtype=torch.int8, device=dev), torch.empty(1, device=dev)
+        ctx.quantize_activation(1, cols, x, q, am)
+        out1 = torch.empty(1, rows, device=dev)
+        for w in ws:
+            ctx.ternary_linear(w, 1, q, am, out1)
+        ctx.sync()
+        ctx.graph_begin()
+        for w in ws:
+            ctx.ternary_linear(w, 1, q, am, out1)
+        gr = ctx.graph_end()
+        for _ in range(3):
+            ctx.graph_launch(gr)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            ctx.graph_launch(gr)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (20 * len(ws))
+        nbytes = rows * ((cols + 15) // 16) * 4 + cols + rows * 4
+        gemv[name] = {"us": us, "gbs": nbytes / us / 1e3, "bytes": nbytes}
+        ctx.graph_free(gr)
+    # CPU baseline on a bounded sample: the oracle's Dense forward (scalar packed path and AVX2 byte-code path, all host
+    # threads), one token at a time like the reference, 8 tokens per shape; M tokens cost M times as much
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import oracle as orc
+        threads = orc.host_threads()
+        rng = np.random.default_rng(args.seed)
+        cpu = {"cores": threads}
+        for name, rows, cols in (("gate", 6912, 2560), ("down", 2560, 6912)):
+            m = orc.Matrix.from_f32((rng.standard_normal(rows * cols) * 0.02).astype(np.float32), rows, cols)
+            xs = rng.standard_normal((8, cols)).astype(np.float32)
+            for simd in (0, 1):
+                orc.dense_forward(m, orc.ACT_LINEAR, xs[:1], simd=simd, threads=threads)  # builds the byte-code cache (simd=1), untimed
+                t0 = time.perf_counter()
+                orc.dense_forward(m, orc.ACT_LINEAR, xs, simd=simd, threads=threads)
+                cpu["%s_%s_us_per_token" % (name, "avx2" if simd else "scalar")] = (time.perf_counter() - t0) / 8 * 1e6
     peak_bf16 = 1610.8
     try:
         peak_bf16 = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
@@ -243,7 +287,13 @@ def gemm_mode(args):
                       "unit": "TOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
                       "ms_per_step": 1e-3 * 0.5 * (res["gate"]["us"] + res["down"]["us"]), "higher_is_better": True,
                       "dtype": "u8 codes x s8 -> s32 (tcgen05), fp64 rescale", "data": "synthetic",
-                      "config": {"workload": "configs[1]: batched prefill, M=%d tokens" % M, "detail": res},
+                      "config": {"workload": "configs[1]: batched prefill, M=%d tokens" % M, "detail": res,
+                                 "config0_gemv_m1": gemv},
+                      "cpu_baseline": None if cpu is None else {
+                          "value": 2.0 * 6912 * 2560 / (0.5 * (cpu["gate_avx2_us_per_token"] + cpu["down_avx2_us_per_token"])) / 1e6,
+                          "unit": "TOP/s", "cores": cpu["cores"], "kind": "port",
+                          "sample": "8 tokens per shape, one at a time like the reference; per-token microseconds in detail",
+                          "detail": cpu},
                       "roofline": {"bound": "tensor", "achieved": tops, "peak": 2 * peak_bf16, "unit": "TOP/s",
                                    "frac": tops / (2 * peak_bf16), "traffic": None,
                                    "peak_kind": "2 x measured bf16 cuBLAS burst (no int8 peak was measured)"}}))
