@@ -569,7 +569,9 @@ def main():
         "gpu_launches": args.steps * launches_per_token,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "lb_gemv_ternary_kernel (gate 6912x2560 and down "
+                     "traffic": 4.52e6, "traffic_source": "ncu dram__bytes_read+write per matrix of the same kernel inside the "
+                     "decode step (gate+up pair 8.96 MB, down 4.56 MB, writes 0): profiles/gemv_ternary_decode_bitnet2b.md",
+                     "peak_kind": peak_kind, "kernel": "lb_gemv_ternary_kernel (gate 6912x2560 and down "
                      "2560x6912, batch 1, 60 distinct matrices per replay)", "bytes_per_launch": per_launch,
                      "us_per_launch": gemv_us, "launches_timed": gemv_launches},
         "decode_bytes": {"ternary": tern_b, "kv": kv_b, "fp32_head": head_b,
