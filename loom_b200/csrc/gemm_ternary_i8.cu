@@ -5,44 +5,45 @@
 // ShaderTiledDenseBitNetTernaryQuantizedReduce does for prompts (poly/wgpu_shaders.go:512-642, dispatched once
 // per (row, token) by poly/wgpu_kernels.go:416-475); arithmetic contract poly/bitnet_cpu.go:536-546,752-776.
 //
-//   D[128 weight rows, 128 tokens] (int32, TMEM) += A[128, 32] (u8 codes 0/1/2, shared) * B[128 tokens, 32]^T (s8, shared)
+//   D[128 weight rows, N tokens] (int32, TMEM) += A[128, 32] (u8 codes 0/1/2, shared) * B[N tokens, 32]^T (s8, shared)
+//   N = 128 or 256 tokens per CTA.
 //
-//   * A: the 2-bit packed tiles are expanded to one byte per weight by four producer warps:
-//     (word >> 2j) & 0x03030303 for j = 0..3 -- four instructions per 16 weights, no transpose: byte b of
-//     result j is the code of column 4b+j, and the activation bytes are stored in the same order by the
-//     quantizer that feeds this kernel, so the K permutation cancels in the dot product.
-//     Codes stay unsigned (kind::i8 takes u8 x s8): sum(code*x) - sum(x) = sum(w*x), the same correction as
-//     the GEMV, applied in the epilogue from the per-token sum the quantizer produced.
-//   * B: int8 activations [tokens, Kp] in global memory, copied with 16-byte cp.async into the canonical
-//     K-major no-swizzle core-matrix layout (8 rows x 16 bytes contiguous; LBO = 128 B along K, SBO = 1024 B
-//     along rows) -- the same layout the producers write A in.
-//   * A four-stage ring of (A, B) K-slices of 128 columns; one elected thread issues four K=32 MMAs per stage
-//     and commits them to the stage's "empty" mbarrier; the last commit releases the epilogue.
-//   * Epilogue: the producer warps read their 32 TMEM lanes (= weight rows) with tcgen05.ld and apply the
-//     float64 rescale, bias, activation and residual exactly like the GEMV epilogue.
-// Every mbarrier wait is bounded; on expiry the kernel raises the context's status word, frees its tensor
-// memory and returns.
+// Warp roles (320 threads):
+//   * load warp: ONE bulk async copy (TMA engine, mbarrier complete_tx) per 128-column k-slice brings the CTA's
+//     activations.  The quantizer that feeds this kernel stores the int8 activations as the shared-memory image the
+//     tensor core wants -- per (256-token tile, k-slice) a contiguous 32 KB block in K-major no-swizzle core-matrix
+//     order [token/8][16-byte K chunk][token%8][16 B] (LBO = 128 B along K, SBO = 1024 B per eight tokens) -- because
+//     the TMA engine is slow on many small copies (forty 0.5-1 KB copies per slice took 1.3 us).
+//   * eight expansion warps (one 16-row strip each) read their packed tile (512 B per warp and slice) straight from
+//     global memory, two slices ahead in registers, and expand 2-bit codes -> one byte per weight with
+//     (word >> 2j) & 0x03030303 for j = 0..3 -- no transpose: byte b of result j is the code of column 4b+j, and the
+//     quantizer stores the activation bytes of every 16-column group in the same order, so the K permutation cancels
+//     in the dot product.  Codes stay unsigned (kind::i8 takes u8 x s8): sum(code*x) - sum(x) = sum(w*x), the same
+//     correction as the GEMV, applied in the epilogue from the per-token sum the quantizer produced.
+//   * MMA warp: one elected thread issues four K=32 MMAs per slice and commits them to the stage's "empty" mbarrier;
+//     the last commit releases the epilogue.
+//   * Epilogue: the expansion warps read their 32 TMEM lanes (= weight rows) with tcgen05.ld and apply the float64
+//     rescale, bias, activation and residual exactly like the GEMV epilogue.
+// Every mbarrier wait is bounded; on expiry the kernel raises the context's status word, frees its tensor memory
+// and returns.
 #include "layers.cuh"
 
 namespace {
 
 constexpr int kRowsPerCta = 128;   // weight rows = TMEM lanes = MMA M
-constexpr int kTokPerCta = 128;    // tokens = TMEM columns = MMA N
 constexpr int kSliceK = 128;       // K columns (= bytes) per pipeline stage
-constexpr int kGemmStages = 5;
-constexpr int kLag = 3;             // k-slices whose global loads are in flight before their stage is finished
-constexpr int kRawBytesA = (kRowsPerCta / kTileRows) * kTileBytes;  // packed weights of one slice: 8 tiles = 4 KB
-constexpr int kProducerThreads = 256;  // eight warps: one 16-row strip each; also the epilogue warps
-constexpr int kGemmThreads = kProducerThreads + 32;  // + the MMA warp
+constexpr int kExpandThreads = 256;  // eight warps: one 16-row strip each; also the epilogue warps
+constexpr int kMmaWarp = kExpandThreads / 32, kLoadWarp = kMmaWarp + 1;
+constexpr int kGemmThreads = kExpandThreads + 64;
 constexpr int kSliceBytesA = kRowsPerCta * kSliceK;  // 16 KB
-constexpr int kSliceBytesB = kTokPerCta * kSliceK;   // 16 KB
+constexpr int kMaxStages = 6;
 constexpr uint32_t kWaitLimit = 20000000u;
 
 struct GemmParams {
     const uint32_t* tiles;   // packed weights, tiled layout
     int rows, strips, kblocks;
     float scale;
-    const int8_t* q;         // [tokens, Kp] int8 in the kernel's K order (see lb_quantize_gemm_kernel)
+    const int8_t* q;         // int8 activations in core-matrix order (see lb_quantize_gemm_kernel), padded to whole CTA tiles
     const float* amax;       // [tokens]
     const int* xsum;         // [tokens]
     int tokens, Kp;
@@ -55,6 +56,7 @@ struct GemmParams {
     int32_t* acc_out;        // [tokens, rows] or null
     int* status;
     int debug;  // timing experiments only
+    unsigned long long* trace;  // optional: row 0 = kernel phases, row 1+i = ring phases of k-slice i (CTA 0 only)
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
@@ -87,44 +89,47 @@ __device__ __forceinline__ bool wait_bounded(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
-// activation bytes (tokens x Kp int8) -> shared core-matrix layout; rows beyond `tokens` are zero-filled
-__device__ __forceinline__ void copy_b_slice(uint8_t* dst, const int8_t* q, int tok0, int tokens, int Kp, int k0, int tid) {
-    for (int c = tid; c < kTokPerCta * (kSliceK / 16); c += kProducerThreads) {
-        const int row = c >> 3, kc = c & 7;
-        const int tok = tok0 + row;
-        const bool ok = tok < tokens;
-        const int8_t* src = q + (size_t)(ok ? tok : 0) * Kp + k0 + kc * 16;
-        const uint32_t d = lb_smem_u32(dst + (row >> 3) * 1024 + kc * 128 + (row & 7) * 16);
-        const int bytes = ok ? 16 : 0;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
-    }
-}
+// stages that fit beside 1 KB of alignment slack: 5 for 128 tokens per CTA, 4 for 256
+template <int NTOK>
+struct GemmCfg {
+    static constexpr int kSliceBytesB = NTOK * kSliceK;
+    static constexpr int kStageBytes = kSliceBytesA + kSliceBytesB;
+    static constexpr int kStages = NTOK == 128 ? 6 : 4;
+    static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024;
+};
 
+template <int NTOK>
 __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(const GemmParams p) {
+    using Cfg = GemmCfg<NTOK>;
+    constexpr int kStages = Cfg::kStages;
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full_bar[kGemmStages], empty_bar[kGemmStages], done_bar;
+    __shared__ __align__(8) uint64_t load_bar[kMaxStages], a_bar[kMaxStages], empty_bar[kMaxStages], done_bar;
     __shared__ uint32_t tmem_base_s;
-    __shared__ double s_os[kTokPerCta];
-    __shared__ int s_xsum[kTokPerCta];
+    __shared__ double s_os[NTOK];
+    __shared__ int s_xsum[NTOK];
     __shared__ int s_failed;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row0 = blockIdx.x * kRowsPerCta, tok0 = blockIdx.y * kTokPerCta;
+    const int row0 = blockIdx.x * kRowsPerCta, tok0 = blockIdx.y * NTOK;
     uint8_t* a_ring = smem;
-    uint8_t* b_ring = smem + kGemmStages * kSliceBytesA;
-    uint8_t* raw_ring = b_ring + kGemmStages * kSliceBytesB;
+    uint8_t* b_ring = smem + kStages * kSliceBytesA;
     const int nslices = p.kblocks;  // one 128-column k-block per stage
+    const int strip0 = blockIdx.x * (kRowsPerCta / kTileRows);
+    const int nstrips = p.strips - strip0 < kRowsPerCta / kTileRows ? p.strips - strip0 : kRowsPerCta / kTileRows;
+    unsigned long long* tr = (p.trace && blockIdx.x == 0 && blockIdx.y == 0) ? p.trace : nullptr;
+    if (tr && tid == 0) tr[0] = lb_gtime();
 
     if (tid == 0) {
-        for (int s = 0; s < kGemmStages; ++s) {
-            lb_mbar_init(&full_bar[s], kProducerThreads);
+        for (int s = 0; s < kStages; ++s) {
+            lb_mbar_init(&load_bar[s], 1);
+            lb_mbar_init(&a_bar[s], kExpandThreads / 32);  // one arrival per expansion warp
             lb_mbar_init(&empty_bar[s], 1);
         }
         lb_mbar_init(&done_bar, 1);
         lb_fence_mbar_init();
         s_failed = 0;
     }
-    if (warp == kProducerThreads / 32) {  // the MMA warp owns the tensor-memory allocation
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lb_smem_u32(&tmem_base_s)), "r"(kTokPerCta) : "memory");
+    if (warp == kMmaWarp) {  // the MMA warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lb_smem_u32(&tmem_base_s)), "r"(NTOK) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -132,61 +137,68 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
 
-    if (warp < kProducerThreads / 32) {
-        // ---------------- producers: expand A, copy B ----------------
-        for (int i = tid; i < kTokPerCta; i += kProducerThreads) {
+    if (warp == kLoadWarp) {
+        // ---------------- loads: packed weight tiles and activation groups of every k-slice ----------------
+        bool failed = false;
+        // activations of (256-token tile T, slice ks): 32 KB at ((T * nslices) + ks) * 32 KB; a 128-token CTA takes one half
+        const int8_t* qbase = p.q + (size_t)(tok0 >> 8) * nslices * 32768 + (size_t)((tok0 & 255) >> 3) * 1024;
+        for (int ks = 0; ks < nslices; ++ks) {
+            const int s = ks % kStages;
+            if (ks >= kStages && !failed && !wait_bounded(&empty_bar[s], (uint32_t)((ks / kStages - 1) & 1))) failed = true;
+            if (failed) break;
+            if (lane == 0) {
+                lb_mbar_expect_tx(&load_bar[s], (uint32_t)Cfg::kSliceBytesB);
+                lb_bulk_g2s(b_ring + (size_t)s * Cfg::kSliceBytesB, qbase + (size_t)ks * 32768, (uint32_t)Cfg::kSliceBytesB, &load_bar[s]);
+                if (tr) tr[(1 + ks) * 8 + 0] = lb_gtime();
+            }
+            __syncwarp();
+        }
+        if (failed && lane == 0) atomicExch(&s_failed, 1);
+    } else if (warp < kMmaWarp) {
+        // ---------------- expansion warps ----------------
+        for (int i = tid; i < NTOK; i += kExpandThreads) {
             const int tok = tok0 + i;
             s_os[i] = tok < p.tokens ? lb_output_scale(p.scale, p.amax[tok]) : 0.0;
             s_xsum[i] = tok < p.tokens ? p.xsum[tok] : 0;
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");  // the per-token scales are read by other producer warps later
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // the per-token scales are read by other expansion warps later
+        if (tr && tid == 0) tr[1] = lb_gtime();
         const int g = lane >> 2, t = lane & 3;
         bool failed = false;
-        // Software pipeline: the cp.async copies of slice ks (activations into the B stage, packed weights into a
-        // raw staging area) are committed as one group; a slice is expanded and handed to the MMA warp kLag
-        // iterations later, when its group has landed, so global latency overlaps across kLag slices.
-        for (int it = 0; it < nslices + kLag; ++it) {
-            if (it < nslices) {
-                const int ks = it, s = ks % kGemmStages;
-                if (ks >= kGemmStages && !failed && !wait_bounded(&empty_bar[s], (uint32_t)((ks / kGemmStages - 1) & 1))) failed = true;
-                copy_b_slice(b_ring + (size_t)s * kSliceBytesB, p.q, tok0, p.tokens, p.Kp, ks * kSliceK, tid);
-                {
-                    const int sl = warp;  // this warp's strip of the 128-row block
-                    const int strip = blockIdx.x * (kRowsPerCta / kTileRows) + sl;
-                    if (strip < p.strips) {
-                        const uint32_t d = lb_smem_u32(raw_ring + (size_t)s * kRawBytesA + sl * kTileBytes + lane * 16);
-                        const uint32_t* src = p.tiles + ((size_t)strip * p.kblocks + ks) * kTileWords + lane * 4;
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
-                    }
-                }
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");  // (possibly empty) group of this iteration
-            if (it >= kLag) {
-                const int ks = it - kLag, s = ks % kGemmStages;
-                asm volatile("cp.async.wait_group %0;" ::"n"(kLag) : "memory");
-                uint8_t* a_dst = a_ring + (size_t)s * kSliceBytesA;
-                {
-                    const int sl = warp;
-                    const int strip = blockIdx.x * (kRowsPerCta / kTileRows) + sl;
-                    uint4 w = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);  // rows past the matrix: weight 0
-                    if (strip < p.strips) w = *reinterpret_cast<const uint4*>(raw_ring + (size_t)s * kRawBytesA + sl * kTileBytes + lane * 16);
-                    // lane (g,t) holds [row g, word t] [row g+8, word t] [row g, word 4+t] [row g+8, word 4+t]
-                    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+        const bool have_strip = warp < nstrips;
+        // packed tile of (this warp's strip, slice ks): 512 contiguous bytes, 16 per lane; rows past the matrix: weight 0
+        const uint4 pad = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
+        const uint4* tile0 = reinterpret_cast<const uint4*>(p.tiles + (size_t)(strip0 + (have_strip ? warp : 0)) * p.kblocks * kTileWords) + lane;
+        auto fetch = [&](int ks) { return (have_strip && ks < nslices) ? __ldg(tile0 + (size_t)ks * (kTileWords / 4)) : pad; };
+        uint4 w0 = fetch(0), w1 = fetch(1);
+        for (int ks = 0; ks < nslices; ++ks) {
+            const int s = ks % kStages;
+            const uint4 w = w0;
+            w0 = w1;
+            w1 = fetch(ks + 2);
+            // the stage's previous occupant must have been consumed by the tensor core
+            if (ks >= kStages && !failed && !wait_bounded(&empty_bar[s], (uint32_t)((ks / kStages - 1) & 1))) failed = true;
+            if (tr && tid == 0) tr[(1 + ks) * 8 + 2] = lb_gtime();
+            uint8_t* a_dst = a_ring + (size_t)s * kSliceBytesA;
+            // lane (g,t) holds [row g, word t] [row g+8, word t] [row g, word 4+t] [row g+8, word 4+t]
+            const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const int row = sl * 16 + g + 8 * (k & 1);  // row inside the 128-row block
-                        const int kc = t + 4 * (k >> 1);            // 16-byte K chunk inside the slice
-                        const uint32_t x = words[k];
-                        const uint4 e = make_uint4(x & 0x03030303u, (x >> 2) & 0x03030303u, (x >> 4) & 0x03030303u, (x >> 6) & 0x03030303u);
-                        *reinterpret_cast<uint4*>(a_dst + (row >> 3) * 1024 + kc * 128 + (row & 7) * 16) = e;
-                    }
-                }
-                if (p.debug != 1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
-                mbar_arrive(&full_bar[s]);
+            for (int k = 0; k < 4; ++k) {
+                const int row = warp * 16 + g + 8 * (k & 1);  // row inside the 128-row block
+                const int kc = t + 4 * (k >> 1);              // 16-byte K chunk inside the slice
+                const uint32_t x = words[k];
+                const uint4 e = make_uint4(x & 0x03030303u, (x >> 2) & 0x03030303u, (x >> 4) & 0x03030303u, (x >> 6) & 0x03030303u);
+                *reinterpret_cast<uint4*>(a_dst + (row >> 3) * 1024 + kc * 128 + (row & 7) * 16) = e;
             }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA
+            __syncwarp();  // every lane's writes and fence are ordered before the warp's single arrival
+            if (lane == 0) mbar_arrive(&a_bar[s]);
+            if (tr && tid == 0) tr[(1 + ks) * 8 + 3] = lb_gtime();
         }
         // ---------------- epilogue ----------------
+        if (tr && tid == 0) tr[2] = lb_gtime();
         if (!failed && !wait_bounded(&done_bar, 0)) failed = true;
+        if (tr && tid == 0) tr[3] = lb_gtime();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (failed) atomicExch(&s_failed, 1);
         // a warp may only touch the 32 TMEM lanes of its quarter (warp % 4); the two warps of a quarter split the columns
@@ -194,62 +206,93 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         const int r = row0 + quarter * 32 + lane;
         const bool row_ok = r < p.rows;
         const double bias = (row_ok && p.bias) ? (double)p.bias[r] : 0.0;
-        for (int c0 = chalf * (kTokPerCta / 2); c0 < (chalf + 1) * (kTokPerCta / 2); c0 += 32) {
-            uint32_t v[32];
+        // Sixteen columns per step in a rolled loop.  The values of a step are first all computed in straight-line code
+        // (sixteen independent int -> float64 -> float32 chains in flight: with two warps per scheduler the epilogue is
+        // bound by instruction latency, not throughput), then stored under the per-output conditions.
+        const bool has_bias = row_ok && p.bias != nullptr;
+#pragma unroll 1
+        for (int c0 = chalf * (NTOK / 2); c0 < (chalf + 1) * (NTOK / 2); c0 += 16) {
+            uint32_t v[16];
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-                  "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
-                  "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-                  "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                : "r"(taddr)
-                : "memory");
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                         : "r"(taddr)
+                         : "memory");
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (row_ok && !failed) {
+            if (tr && tid == 0 && c0 == 0) tr[5] = lb_gtime();
+            int acc[16];
+            double y[16];
+            float f[16];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int tok = tok0 + c0 + j;
-                    if (tok >= p.tokens) break;
-                    const int acc = (int)v[j] - s_xsum[c0 + j];
-                    const size_t o = (size_t)tok * p.rows + r;
-                    if (p.acc_out) p.acc_out[o] = acc;
-                    if (p.out_f64) {
-                        double y = __dmul_rn((double)acc, s_os[c0 + j]);
-                        if (p.bias) y = __dadd_rn(y, bias);
-                        p.out_f64[o] = y;
+            for (int j = 0; j < 16; ++j) {
+                acc[j] = (int)v[j] - s_xsum[c0 + j];
+                const double t = __dmul_rn((double)acc[j], s_os[c0 + j]);
+                y[j] = has_bias ? __dadd_rn(t, bias) : t;
+                f[j] = (float)y[j];
+            }
+            if (row_ok && !failed) {
+                const int ntok = p.tokens - (tok0 + c0);  // columns of this step that are real tokens
+                const size_t o0 = (size_t)(tok0 + c0) * p.rows + r;
+                if (p.acc_out) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (j < ntok) p.acc_out[o0 + (size_t)j * p.rows] = acc[j];
+                }
+                if (p.out_f64) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (j < ntok) p.out_f64[o0 + (size_t)j * p.rows] = y[j];
+                }
+                if (p.out) {
+                    if (p.pre_out) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < ntok) p.pre_out[o0 + (size_t)j * p.rows] = f[j];
                     }
-                    if (p.out) {
-                        double y = __dmul_rn((double)acc, s_os[c0 + j]);
-                        if (p.bias) y = __dadd_rn(y, bias);
-                        float f = (float)y;
-                        if (p.pre_out) p.pre_out[o] = f;
-                        if (p.act == LOOM_B200_ACT_RELU) f = f < 0.f ? 0.f : f;
-                        else if (p.act == LOOM_B200_ACT_RELU2) f = f < 0.f ? 0.f : __fmul_rn(f, f);
-                        else if (p.act != LOOM_B200_ACT_LINEAR) f = lb_activate(f, p.act);
-                        if (p.residual) f = __fadd_rn(f, p.residual[o]);
-                        p.out[o] = f;
+                    if (p.act != LOOM_B200_ACT_LINEAR) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (p.act == LOOM_B200_ACT_RELU) f[j] = f[j] < 0.f ? 0.f : f[j];
+                            else if (p.act == LOOM_B200_ACT_RELU2) f[j] = f[j] < 0.f ? 0.f : __fmul_rn(f[j], f[j]);
+                            else f[j] = lb_activate(f[j], p.act);
+                        }
                     }
+                    if (p.residual) {
+                        float rs[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) rs[j] = j < ntok ? p.residual[o0 + (size_t)j * p.rows] : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) f[j] = __fadd_rn(f[j], rs[j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (j < ntok) p.out[o0 + (size_t)j * p.rows] = f[j];
                 }
             }
+            if (tr && tid == 0 && c0 == 0) tr[6] = lb_gtime();
         }
+        if (tr && tid == 0) tr[7] = lb_gtime();
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     } else {
         // ---------------- MMA issuer ----------------
-        // instruction descriptor: D = S32, A = U8, B = S8, both K-major, N = 128, M = 128
-        const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(kTokPerCta >> 3) << 17) | ((uint32_t)(kRowsPerCta >> 4) << 24);
+        // instruction descriptor: D = S32, A = U8, B = S8, both K-major, N tokens, M = 128
+        const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(NTOK >> 3) << 17) | ((uint32_t)(kRowsPerCta >> 4) << 24);
         bool failed = false;
         for (int ks = 0; ks < nslices; ++ks) {
-            const int s = ks % kGemmStages;
-            if (!failed && !wait_bounded(&full_bar[s], (uint32_t)((ks / kGemmStages) & 1))) failed = true;
+            const int s = ks % kStages;
+            if (!failed && !wait_bounded(&a_bar[s], (uint32_t)((ks / kStages) & 1))) failed = true;
+            if (!failed && !wait_bounded(&load_bar[s], (uint32_t)((ks / kStages) & 1))) failed = true;  // the activations (long complete)
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (tr && lane == 0) tr[(1 + ks) * 8 + 4] = lb_gtime();
             if (lane == 0 && !failed) {
                 const uint32_t a_addr = lb_smem_u32(a_ring + (size_t)s * kSliceBytesA);
-                const uint32_t b_addr = lb_smem_u32(b_ring + (size_t)s * kSliceBytesB);
+                const uint32_t b_addr = lb_smem_u32(b_ring + (size_t)s * Cfg::kSliceBytesB);
 #pragma unroll
                 for (int k = 0; k < kSliceK / 32; ++k)  // K = 32 per instruction = two 16-byte chunks = 256 B further
                     mma_i8(tmem_base, smem_desc(a_addr + k * 256), smem_desc(b_addr + k * 256), idesc, (ks > 0 || k > 0) ? 1u : 0u);
                 mma_commit(&empty_bar[s]);  // arrives when the MMAs that read this stage are done
+                if (tr) tr[(1 + ks) * 8 + 5] = lb_gtime();
             }
             __syncwarp();
         }
@@ -261,17 +304,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
-    if (warp == kProducerThreads / 32) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTokPerCta) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(NTOK) : "memory");
     }
     if (tid == 0 && s_failed) atomicExch(p.status, 3);
+    if (tr && tid == 0) tr[4] = lb_gtime();
 }
 
-// Quantizer of the GEMM path: the GEMV prologues' arithmetic (plain absmax, or a block / inner RMSNorm first), but the
-// bytes of every 16-column group are stored in the order the A expansion produces (position 4j+b holds column
-// 4b+j), rows are padded with zeros to Kp, and the per-token sum of the quantized values is written next to amax.
-// One CTA per token.
+// Quantizer of the GEMM path: the GEMV prologues' arithmetic (plain absmax, or a block / inner RMSNorm first).  The
+// output is laid out for the tensor core: [token/8][Kp/16][token%8][16 bytes], the bytes of every 16-column group in
+// the order the A expansion produces (position 4j+b holds column 4b+j); columns up to Kp and tokens up to the padded
+// count are zero; the per-token sum of the quantized values is written next to amax.  One CTA per (padded) token.
 template <int PRO>
 __global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const LbGemmQuant a, int Kp, int8_t* __restrict__ q,
                                                                float* __restrict__ amax_out, int* __restrict__ xsum_out) {
@@ -280,11 +324,18 @@ __global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const LbGemmQuant
     __shared__ int redi[8];
     constexpr bool f64 = PRO == LB_PRO_INNERNORM64;
     const int K = a.K, tid = threadIdx.x;
+    // byte c of this token's row lives at: (256-token tile, k-slice c/128) block of 32 KB, + (token%256)/8 * 1 KB
+    // + (16-byte chunk (c/16)%8) * 128 + (token%8) * 16 + c%16
+    int8_t* qrow = q + (size_t)(blockIdx.x >> 8) * (Kp >> 7) * 32768 + (size_t)((blockIdx.x & 255) >> 3) * 1024 + (blockIdx.x & 7) * 16;
+    auto at = [&](int c) -> int8_t& { return qrow[(size_t)(c >> 7) * 32768 + ((c >> 4) & 7) * 128 + (c & 15)]; };
+    if ((int)blockIdx.x >= a.tokens) {  // padding token: zeros
+        for (int c = tid; c < Kp; c += blockDim.x) at(c) = 0;
+        return;
+    }
     const float* rowf = (const float*)a.x + (size_t)blockIdx.x * K;
     const double* rowd = (const double*)a.x + (size_t)blockIdx.x * K;
     auto ld = [&](int i) { return f64 ? rowd[i] : (double)rowf[i]; };
     auto wt = [&](int i) { return (PRO != LB_PRO_F32 && a.norm_w && i < a.norm_w_len) ? (double)a.norm_w[i] : 1.0; };
-    int8_t* qrow = q + (size_t)blockIdx.x * Kp;
     double root = 1.0, rr = 1.0;
     if (PRO >= LB_PRO_BLOCKNORM) {
         double ss = 0.0;
@@ -320,7 +371,7 @@ __global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const LbGemmQuant
         const int col = base + 4 * b + j;
         int v = 0;
         if (col < K) v = lb_quant_i8(lb_pro_value<PRO>(ld(col), root, rr, wt(col)), s);
-        qrow[c] = (int8_t)v;
+        at(c) = (int8_t)v;
         sum += v;
     }
     sum = lb_warp_sum_i(sum);
@@ -356,11 +407,14 @@ struct GemmScratch {
     float* amax;
     int* xsum;
 };
+constexpr int kTokPad = 256;  // the activations are padded with zero rows to whole CTA tiles of either size
+int padded_tokens(int tokens) { return (tokens + kTokPad - 1) / kTokPad * kTokPad; }
 GemmScratch gemm_scratch_at(void* base, int tokens, int Kp) {
     GemmScratch g;
+    const int pt = padded_tokens(tokens);
     g.q = (int8_t*)base;
-    g.amax = (float*)((char*)base + (((size_t)tokens * Kp + 255) & ~(size_t)255));
-    g.xsum = (int*)(g.amax + tokens);
+    g.amax = (float*)((char*)base + (((size_t)pt * Kp + 255) & ~(size_t)255));
+    g.xsum = (int*)(g.amax + pt);
     return g;
 }
 
@@ -370,7 +424,8 @@ int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a) {
     LB_REQUIRE(ctx, a.x && a.tokens > 0 && a.K > 0, "gemm_quantize: bad arguments");
     const int Kp = (a.K + kTileCols - 1) / kTileCols * kTileCols;
     // scratch: permuted int8 activations, amax, sum per token
-    size_t need = (size_t)a.tokens * Kp + 256 + (size_t)a.tokens * 8 + 256;
+    const int pt = padded_tokens(a.tokens);
+    size_t need = (size_t)pt * Kp + 256 + (size_t)pt * 8 + 256;
     if (need > ctx->gemm_scratch_bytes) {  // its own buffer: layer calls keep their tensors in ctx->scratch
         if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "ternary_gemm: scratch would grow while recording a graph");
         LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -382,10 +437,10 @@ int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a) {
     }
     GemmScratch g = gemm_scratch_at(ctx->gemm_scratch, a.tokens, Kp);
     switch (a.pro) {
-        case LB_PRO_F32: lb_quantize_gemm_kernel<LB_PRO_F32><<<a.tokens, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
-        case LB_PRO_BLOCKNORM: lb_quantize_gemm_kernel<LB_PRO_BLOCKNORM><<<a.tokens, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
-        case LB_PRO_INNERNORM: lb_quantize_gemm_kernel<LB_PRO_INNERNORM><<<a.tokens, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
-        case LB_PRO_INNERNORM64: lb_quantize_gemm_kernel<LB_PRO_INNERNORM64><<<a.tokens, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_F32: lb_quantize_gemm_kernel<LB_PRO_F32><<<pt, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_BLOCKNORM: lb_quantize_gemm_kernel<LB_PRO_BLOCKNORM><<<pt, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_INNERNORM: lb_quantize_gemm_kernel<LB_PRO_INNERNORM><<<pt, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_INNERNORM64: lb_quantize_gemm_kernel<LB_PRO_INNERNORM64><<<pt, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
         default: return lb_fail(ctx, LOOM_B200_ERR_INVALID, "gemm_quantize: prologue %d", a.pro);
     }
     LB_CHECK_LAUNCH(ctx, "lb_quantize_gemm_kernel");
@@ -402,7 +457,7 @@ int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const
     LB_REQUIRE(ctx, w && tokens > 0 && (o.out || o.out_f64 || o.acc_out), "gemm_run: bad arguments");
     LB_REQUIRE(ctx, w->device == ctx->device, "ternary_gemm: weight lives on device %d, context on %d", w->device, ctx->device);
     const int Kp = w->kblocks * kTileCols;
-    LB_REQUIRE(ctx, (size_t)tokens * Kp <= ctx->gemm_scratch_bytes, "gemm_run: no quantized activations for %d tokens of %d columns", tokens, w->cols);
+    LB_REQUIRE(ctx, (size_t)padded_tokens(tokens) * Kp <= ctx->gemm_scratch_bytes, "gemm_run: no quantized activations for %d tokens of %d columns", tokens, w->cols);
     GemmScratch g = gemm_scratch_at(ctx->gemm_scratch, tokens, Kp);
     GemmParams p = {};
     p.tiles = w->tiles;
@@ -424,13 +479,33 @@ int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const
     p.acc_out = o.acc_out;
     p.status = ctx->status_dev;
     p.debug = ctx->opt_debug;
-    const size_t smem = (size_t)kGemmStages * (kSliceBytesA + kSliceBytesB + kRawBytesA) + 1024;
+    // phase trace: one row for the kernel and one per k-slice, kept contiguous (skipped if the ring of rows would wrap)
+    p.trace = nullptr;
+    if (ctx->trace_dev && (ctx->trace_seq % kTraceSlots) + w->kblocks + 2 < kTraceSlots) {
+        p.trace = lb_trace_row(ctx, "gemm");
+        for (int i = 0; i < w->kblocks; ++i) lb_trace_row(ctx, "gemm-slice");
+    }
+    // Tokens per CTA: 256 halves the weight expansion per MMA but also the number of CTAs; take the variant with the
+    // smaller (waves x relative tile time), a 256-token tile costing about 1.6 times a 128-token one.
+    const int row_tiles = (w->rows + kRowsPerCta - 1) / kRowsPerCta;
+    const int ct128 = row_tiles * ((tokens + 127) / 128), ct256 = row_tiles * ((tokens + 255) / 256);
+    const int sms = ctx->sm_count;
+    const double cost128 = (double)((ct128 + sms - 1) / sms), cost256 = 1.6 * (double)((ct256 + sms - 1) / sms);
+    bool wide = tokens > 128 && cost256 < cost128;
+    if (ctx->opt_gemm_tile == 128) wide = false;
+    if (ctx->opt_gemm_tile == 256) wide = true;
     if (!(ctx->func_attr_mask & (1u << 27))) {
-        LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<128>::kSmem));
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<256>::kSmem));
         ctx->func_attr_mask |= 1u << 27;
     }
-    dim3 grid((w->rows + kRowsPerCta - 1) / kRowsPerCta, (tokens + kTokPerCta - 1) / kTokPerCta);
-    lb_gemm_ternary_i8_kernel<<<grid, kGemmThreads, smem, ctx->stream>>>(p);
+    if (wide) {
+        dim3 grid(row_tiles, (tokens + 255) / 256);
+        lb_gemm_ternary_i8_kernel<256><<<grid, kGemmThreads, GemmCfg<256>::kSmem, ctx->stream>>>(p);
+    } else {
+        dim3 grid(row_tiles, (tokens + 127) / 128);
+        lb_gemm_ternary_i8_kernel<128><<<grid, kGemmThreads, GemmCfg<128>::kSmem, ctx->stream>>>(p);
+    }
     LB_CHECK_LAUNCH(ctx, "lb_gemm_ternary_i8_kernel");
     ctx->launches++;
     return 0;
