@@ -300,6 +300,90 @@ def gemm_mode(args):
     return 0
 
 
+def sweep_mode(args):
+    """Batch sweep of one ternary projection pair (gate: inter x hidden, down: hidden x inter of --shape) at M = 1 ... 256
+    tokens: the decode GEMV (eight tokens per weight pass) against the tcgen05 GEMM (quantizer included), with the
+    fraction of the HBM roofline (packed weight bytes per pass / time) and of the int8 tensor roofline (2*M*K*N / time)
+    for each, and the crossover batch.  Kernel-level stand-in for the decode batch sweeps of configs 3-4."""
+    import torch
+
+    import loom_b200
+
+    shape = {"2b": SHAPE, **TP_SHAPES}[args.shape]
+    H, I = shape["hidden"], shape["inter"]
+    torch.cuda.set_device(0)
+    ts = torch.cuda.Stream()
+    torch.cuda.set_stream(ts)
+    ctx = loom_b200.Context(0, ts.cuda_stream)
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(args.seed)
+    peak, peak_kind = measured_peaks()
+    peak_bf16 = 1610.8
+    try:
+        peak_bf16 = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        pass
+    rows_out = []
+    for name, rows, cols in (("gate", I, H), ("down", H, I)):
+        wbytes = rows * ((cols + 15) // 16) * 4
+        nmat = max(2, min(16, int(300e6 // wbytes) + 1))  # distinct matrices beyond the 126 MB L2
+        ws = [ctx.pack_ternary_f32(torch.randn(rows * cols, device=dev, generator=g) * 0.02, rows, cols) for _ in range(nmat)]
+        for M in (1, 8, 16, 32, 64, 128, 256):
+            x = torch.randn(M, cols, device=dev, generator=g)
+            q, am = torch.empty(M, cols, dtype=torch.int8, device=dev), torch.empty(M, device=dev)
+            out = torch.empty(M, rows, device=dev)
+
+            def gemv():
+                ctx.quantize_activation(M, cols, x, q, am)
+                for w in ws:
+                    ctx.ternary_linear(w, M, q, am, out)
+
+            def gemm():
+                for w in ws:
+                    ctx.ternary_gemm(w, M, x, out=out)
+
+            res = {}
+            for kind, fn in (("gemv", gemv), ("gemm", gemm)):
+                fn()  # sizes every scratch buffer
+                ctx.sync()
+                ctx.graph_begin()  # a recorded frame: the Python launch loop would otherwise be what is timed
+                fn()
+                gr = ctx.graph_end()
+                for _ in range(3):
+                    ctx.graph_launch(gr)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.steps):
+                    ctx.graph_launch(gr)
+                e1.record()
+                torch.cuda.synchronize()
+                res[kind] = e0.elapsed_time(e1) * 1e3 / (args.steps * nmat)
+                ctx.graph_free(gr)
+            per_pass = 8 if cols <= 19000 else 5  # tokens one GEMV pass carries (shared-memory bound for very wide rows)
+            passes = (M + per_pass - 1) // per_pass
+            rows_out.append({"matrix": "%s %dx%d" % (name, rows, cols), "M": M, "gemv_us": res["gemv"], "gemm_us": res["gemm"],
+                             "gemv_hbm_frac": passes * wbytes / res["gemv"] / 1e3 / peak,
+                             "gemm_tensor_frac": 2.0 * M * rows * cols / res["gemm"] / 1e6 / (2 * peak_bf16),
+                             "gemm_hbm_frac": wbytes / res["gemm"] / 1e3 / peak,
+                             "faster": "gemm" if res["gemm"] < res["gemv"] else "gemv"})
+        del ws
+    cross = {}
+    for r in rows_out:
+        if r["faster"] == "gemm" and r["matrix"] not in cross:
+            cross[r["matrix"]] = r["M"]
+    best = max(r["gemv_hbm_frac"] for r in rows_out if r["M"] == 1)
+    print(json.dumps({"metric": "ternary projection batch sweep (%s shape): GEMV vs tcgen05 GEMM" % args.shape.upper(), "value": best,
+                      "unit": "fraction of measured HBM peak, GEMV at M=1", "n_gpus": 1, "steps": args.steps, "warmup": 3,
+                      "higher_is_better": True, "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic",
+                      "config": {"workload": "gate and down projections of the %s shape, M = 1..256 tokens" % args.shape.upper(),
+                                 "crossover_M": cross, "peaks": {"hbm_gbs": peak, "int8_tops": 2 * peak_bf16,
+                                                                 "int8_kind": "2 x measured bf16 cuBLAS burst"}},
+                      "sweep": rows_out}))
+    return 0
+
+
 TP_SHAPES = {
     "8b": dict(layers=32, hidden=4096, heads=32, kv_heads=8, head_dim=128, inter=14336, vocab=128256, eps=1e-5,
                theta=500000.0, max_seq_len=1024),
@@ -439,15 +523,19 @@ def main():
     ap.add_argument("--vocab", type=int, default=SHAPE["vocab"], help="smaller vocabularies are for profiling captures only")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--mode", default="decode", choices=["decode", "gemm", "tp"],
-                    help="gemm: the batched-prefill GEMM microbenchmark; tp: tensor-parallel decode of --shape under torchrun")
-    ap.add_argument("--shape", default="8b", choices=sorted(TP_SHAPES))
+    ap.add_argument("--mode", default="decode", choices=["decode", "gemm", "tp", "sweep"],
+                    help="gemm: the batched-prefill GEMM microbenchmark; tp: tensor-parallel decode of --shape under torchrun; "
+                         "sweep: GEMV vs GEMM over batch sizes for the gate/down projections of --shape")
+    ap.add_argument("--shape", default="8b", choices=sorted(TP_SHAPES) + ["2b"])
     ap.add_argument("--tokens", type=int, default=512)
     args = ap.parse_args()
     if args.mode == "gemm":
         return gemm_mode(args)
     if args.mode == "tp":
         return tp_mode(args)
+    if args.mode == "sweep":
+        args.steps = min(args.steps, 20)
+        return sweep_mode(args)
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))

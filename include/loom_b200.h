@@ -122,6 +122,14 @@ int loom_b200_upload_ternary(loom_b200_ctx* ctx, const uint32_t* words, int rows
  * master_dev points at rows*cols fp32 values in device memory. */
 int loom_b200_pack_ternary_f32(loom_b200_ctx* ctx, const float* master_dev, int rows, int cols,
                                loom_b200_weight** out);
+/* A BITNET_TERNARY blob of an .entity checkpoint as encodeEntityBitNetTernaryBlob writes it
+ * (poly/entity_bitnet.go:38-88): 24-byte little-endian header {rows, cols, offset, float32 scale bits, rowWords,
+ * nWords} followed by nWords packed words.  Validated like decodeEntityBitNetTernaryBlob (short or truncated
+ * blobs are errors; rowWords 0 means ceil(cols/16)).  *offset_out (may be NULL) receives the slab offset the
+ * reference keys the matrix by (10000 + offset, poly/bitnet_cpu.go:286-292). */
+int loom_b200_upload_entity_blob(loom_b200_ctx* ctx, const uint8_t* blob, size_t len, int* offset_out,
+                                 loom_b200_weight** out);
+
 /* SetMicrosoftBitNetPackedMatrixBytes, poly/bitnet_cpu.go:1031-1052,1078-1098: host bytes of the
  * microsoft/bitnet-b1.58 offline layout ((rows/4)*cols bytes); scale as SetBitNetPackedScale. */
 int loom_b200_upload_microsoft_u8(loom_b200_ctx* ctx, const uint8_t* packed, int rows, int cols, float scale,

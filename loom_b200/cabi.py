@@ -58,6 +58,7 @@ SIGNATURES = {
     "loom_b200_upload_ternary": (_i, [_vp, _vp, _i, _i, _i, _f, C.POINTER(_vp)]),
     "loom_b200_pack_ternary_f32": (_i, [_vp, _vp, _i, _i, C.POINTER(_vp)]),
     "loom_b200_upload_microsoft_u8": (_i, [_vp, _vp, _i, _i, _f, C.POINTER(_vp)]),
+    "loom_b200_upload_entity_blob": (_i, [_vp, _vp, _sz, C.POINTER(_i), C.POINTER(_vp)]),
     "loom_b200_weight_info": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_f)]),
     "loom_b200_weight_set_scale": (_i, [_vp, _f]),
     "loom_b200_weight_download_words": (_i, [_vp, _vp, _vp]),
@@ -288,6 +289,12 @@ class Context:
         h = _vp()
         self._check(lib().loom_b200_pack_ternary_f32(self.h, _ptr(master_dev), rows, cols, C.byref(h)))
         return Weight(self, h)
+
+    def upload_entity_blob(self, blob: bytes):
+        """A BITNET_TERNARY blob of an .entity checkpoint -> (Weight, slab offset)."""
+        h, off = _vp(), _i(0)
+        self._check(lib().loom_b200_upload_entity_blob(self.h, C.c_char_p(blob), len(blob), C.byref(off), C.byref(h)))
+        return Weight(self, h), off.value
 
     def upload_microsoft_u8(self, packed: np.ndarray, rows: int, cols: int, scale: float) -> Weight:
         packed = np.ascontiguousarray(packed, np.uint8)

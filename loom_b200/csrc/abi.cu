@@ -581,6 +581,28 @@ int loom_b200_pack_ternary_f32(loom_b200_ctx* ctx, const float* master_dev, int 
     return 0;
 }
 
+int loom_b200_upload_entity_blob(loom_b200_ctx* ctx, const uint8_t* blob, size_t len, int* offset_out, loom_b200_weight** out) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "upload_entity_blob: ctx is NULL");
+    LB_REQUIRE(ctx, out != nullptr, "upload_entity_blob: out is NULL");
+    *out = nullptr;
+    LB_REQUIRE(ctx, blob != nullptr, "upload_entity_blob: blob is NULL");
+    LB_REQUIRE(ctx, len >= 24, "upload_entity_blob: blob of %zu bytes is shorter than its 24-byte header", len);
+    auto le32 = [&](size_t at) { return (uint32_t)blob[at] | ((uint32_t)blob[at + 1] << 8) | ((uint32_t)blob[at + 2] << 16) | ((uint32_t)blob[at + 3] << 24); };
+    const uint32_t rows = le32(0), cols = le32(4), offset = le32(8), scale_bits = le32(12), n_words = le32(20);
+    uint32_t row_words = le32(16);
+    if (row_words == 0) row_words = (cols + 15) / 16;  // decodeEntityBitNetTernaryBlob's default
+    LB_REQUIRE(ctx, rows > 0 && cols > 0 && rows < (1u << 24) && cols < (1u << 24), "upload_entity_blob: header says %u x %u", rows, cols);
+    LB_REQUIRE(ctx, len >= 24 + (size_t)n_words * 4, "upload_entity_blob: truncated: have %zu bytes, need %zu", len, 24 + (size_t)n_words * 4);
+    LB_REQUIRE(ctx, row_words >= (cols + 15) / 16 && (size_t)n_words >= (size_t)rows * row_words,
+               "upload_entity_blob: %u words do not cover %u rows of %u words", n_words, rows, row_words);
+    float scale;
+    memcpy(&scale, &scale_bits, 4);
+    std::vector<uint32_t> words((size_t)rows * row_words);
+    for (size_t i = 0; i < words.size(); ++i) words[i] = le32(24 + 4 * i);  // little-endian on any host
+    if (offset_out) *offset_out = (int)offset;
+    return loom_b200_upload_ternary(ctx, words.data(), (int)rows, (int)cols, (int)row_words, scale, out);
+}
+
 int loom_b200_upload_microsoft_u8(loom_b200_ctx* ctx, const uint8_t* packed, int rows, int cols, float scale,
                                   loom_b200_weight** out) {
     if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "upload_microsoft_u8: ctx is NULL");

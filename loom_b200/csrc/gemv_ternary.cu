@@ -460,6 +460,7 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     int grid = 0;
     size_t smem = 0;
     int cps = ctx->opt_gemv_ctas_per_sm;
+    if (p.K >= 16384 && cps > 1) cps = 1;  // very wide rows: every CTA stages the whole int8 row, so fewer, longer CTAs win (measured)
     gemv_plan(ctx, p, cps, &grid, &smem);
     // A grid sized for more CTAs per SM than the shared memory lets be resident would run in waves, and every
     // wave repeats the prologue: fall back to what fits (228 KB per SM, 1 KB reserved per CTA).
@@ -532,7 +533,8 @@ extern "C" int loom_b200_ternary_linear(loom_b200_ctx* ctx, const loom_b200_weig
     LB_REQUIRE(ctx, out || acc_out, "ternary_linear: no output buffer");
     LB_REQUIRE(ctx, w->device == ctx->device, "ternary_linear: weight lives on device %d, context on %d", w->device, ctx->device);
     if (int rc = lb_set_device(ctx)) return rc;
-    for (int b0 = 0; b0 < batch; b0 += kMaxM) {
+    const int pass = lb_gemv_max_tokens(w->cols);  // tokens one pass carries: 8, fewer for very wide inputs
+    for (int b0 = 0; b0 < batch; b0 += pass) {
         LbGemvParams p = {};
         p.nseg = 1;
         p.seg[0].tiles = w->tiles;
@@ -544,7 +546,7 @@ extern "C" int loom_b200_ternary_linear(loom_b200_ctx* ctx, const loom_b200_weig
         p.seg[0].kind = out ? LB_OUT_F32 : LB_OUT_ACC;
         p.epi = LB_EPI_GENERIC;
         p.K = w->cols;
-        p.M = batch - b0 < kMaxM ? batch - b0 : kMaxM;
+        p.M = batch - b0 < pass ? batch - b0 : pass;
         p.pro = LB_PRO_Q8;
         p.x = q + (size_t)b0 * w->cols;
         p.amax_in = amax + b0;

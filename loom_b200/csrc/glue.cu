@@ -452,13 +452,16 @@ __global__ void lb_add_scalar_kernel(int* p, int delta) {
 // into shared memory (64 positions, one 512-byte bulk copy per row) serves all of them.  Scores, the running
 // softmax (maximum, sum, rescaling of the partial output when the maximum moves) and the weighted V sum are float64
 // like the reference's loops (poly/mha.go:296-356); only the order of the float64 additions differs.
+// A tile arrives as float32 in a staging buffer and is widened to float64 once, into a buffer K and V take turns
+// in: converting inside the products would repeat every conversion sixteen times, and float32 -> float64 conversions
+// issue on the float64 pipe at a fraction of the FMA rate (they held the first version at 39 % FMA-pipe use).
 // Threads form a 16 x 16 grid: thread (ty, tx) owns score rows ty+16i and key columns tx+16j, and output rows
 // ty+16i, dimensions tx+16j.
 constexpr int kPfRows = 64, kPfKeys = 64, kPfThreads = 256;
 
 __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(const LbAttnParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2];
+    __shared__ __align__(8) uint64_t bar;
     __shared__ double s_m[kPfRows], s_l[kPfRows], s_alpha[kPfRows];
     __shared__ int s_qpos[kPfRows];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, ty = tid >> 4, tx = tid & 15;
@@ -466,14 +469,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
     const int group = p.heads / p.kv_heads, TQ = kPfRows / group;
     const int kvh = blockIdx.x, qt = (int)gridDim.y - 1 - (int)blockIdx.y;  // long rows first
     const int tok0 = qt * TQ;
-    const int qstride = hd + 2, rowf = hd + 4, sstride = kPfKeys + 1;
-    double* Qs = reinterpret_cast<double*>(smem_raw);                    // [64, hd+2]
-    double* Ss = Qs + (size_t)kPfRows * qstride;                         // [64, 65]
-    float* Kt = reinterpret_cast<float*>(Ss + (size_t)kPfRows * sstride);  // [64, hd+4]
-    float* Vt = Kt + (size_t)kPfKeys * rowf;                             // [64, hd+4]
+    const int dstride = hd + 2, rowf = hd + 4, sstride = kPfKeys + 1;
+    double* Qs = reinterpret_cast<double*>(smem_raw);                      // [64, hd+2] queries
+    double* KV = Qs + (size_t)kPfRows * dstride;                           // [64, hd+2] the K tile, then the V tile, as float64
+    double* Ss = KV + (size_t)kPfKeys * dstride;                           // [64, 65] scores, then softmax weights
+    float* stage = reinterpret_cast<float*>(Ss + (size_t)kPfRows * sstride);  // [64, hd+4] float32 tile as copied
     if (tid == 0) {
-        lb_mbar_init(&bars[0], 1);
-        lb_mbar_init(&bars[1], 1);
+        lb_mbar_init(&bar, 1);
         lb_fence_mbar_init();
     }
     __syncthreads();
@@ -485,18 +487,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
     const int ntiles = max_pos / kPfKeys + 1;
     const float* kbase = p.cache_k + (size_t)kvh * hd;
     const float* vbase = p.cache_v + (size_t)kvh * hd;
-    {
-        const int rows0 = max_pos + 1 < kPfKeys ? max_pos + 1 : kPfKeys;
-        if (warp == 0) attn_fetch_rows(Kt, kbase, rowf, hd, kvd, p.msl, 0, rows0, &bars[0], lane);
-        if (warp == 1) attn_fetch_rows(Vt, vbase, rowf, hd, kvd, p.msl, 0, rows0, &bars[1], lane);
-    }
+    auto tile_rows = [&](int t) { return max_pos + 1 - t * kPfKeys < kPfKeys ? max_pos + 1 - t * kPfKeys : kPfKeys; };
+    if (warp == 0) attn_fetch_rows(stage, kbase, rowf, hd, kvd, p.msl, 0, tile_rows(0), &bar, lane);
     // query rows: row r = (head hi of the group, token ti); rows of absent tokens are zero and never written back
     for (int idx = tid; idx < kPfRows * hd; idx += kPfThreads) {
         const int r = idx / hd, d = idx - r * hd;
         const int hi = r / TQ, ti = r - hi * TQ;
         double v = 0.0;
         if (ti < ntok) v = p.q[(size_t)(tok0 + ti) * qd + (size_t)(kvh * group + hi) * hd + d];
-        Qs[(size_t)r * qstride + d] = v;
+        Qs[(size_t)r * dstride + d] = v;
     }
     if (tid < kPfRows) {
         const int ti = tid % TQ;
@@ -513,47 +512,57 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
         for (int j = 0; j < 8; ++j) o[i][j] = 0.0;
     const int ndim = hd / 16;  // output dimensions per thread (8 for head_dim 128)
     bool failed = false;
+    uint32_t phase = 0;
+    // staging (float32, rows of hd+4) -> KV (float64, rows of hd+2); rows beyond `rows` become zero
+    auto widen = [&](int rows) {
+        const int quads = hd / 4;
+        for (int idx = tid; idx < kPfKeys * quads; idx += kPfThreads) {
+            const int r = idx / quads, c = (idx - r * quads) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < rows) v = *reinterpret_cast<const float4*>(stage + (size_t)r * rowf + c);
+            double2* dst = reinterpret_cast<double2*>(KV + (size_t)r * dstride + c);
+            dst[0] = make_double2((double)v.x, (double)v.y);
+            dst[1] = make_double2((double)v.z, (double)v.w);
+        }
+    };
     for (int t = 0; t < ntiles; ++t) {
-        const int kbase_pos = t * kPfKeys;
-        const int krows = max_pos + 1 - kbase_pos < kPfKeys ? max_pos + 1 - kbase_pos : kPfKeys;
-        if (!failed && !lb_mbar_wait_bounded(&bars[0], (uint32_t)(t & 1))) failed = true;
+        const int kpos0 = t * kPfKeys;
+        const int krows = tile_rows(t);
+        // ---- K tile: wait, widen, then the staging buffer is free for the V tile of the same positions ----
+        if (!failed && !lb_mbar_wait_bounded(&bar, phase)) failed = true;
+        phase ^= 1;
+        widen(krows);
+        __syncthreads();
+        if (warp == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            attn_fetch_rows(stage, vbase, rowf, hd, kvd, p.msl, kpos0, krows, &bar, lane);
+        }
         // ---- scores of this tile ----
         double acc[4][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
-        for (int d = 0; d < hd; d += 4) {
-            double qv[4][4];
-            float4 kv[4];
+#pragma unroll 2
+        for (int d = 0; d < (p.debug == 10 ? 2 : hd); d += 2) {
+            double2 qv[4], kv[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const double2 a = *reinterpret_cast<const double2*>(Qs + (size_t)(ty + 16 * i) * qstride + d);
-                const double2 b = *reinterpret_cast<const double2*>(Qs + (size_t)(ty + 16 * i) * qstride + d + 2);
-                qv[i][0] = a.x; qv[i][1] = a.y; qv[i][2] = b.x; qv[i][3] = b.y;
-            }
+            for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const double2*>(Qs + (size_t)(ty + 16 * i) * dstride + d);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(Kt + (size_t)(tx + 16 * j) * rowf + d);
+            for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const double2*>(KV + (size_t)(tx + 16 * j) * dstride + d);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[i][j] = fma(qv[i][0], (double)kv[j].x, acc[i][j]);
-                    acc[i][j] = fma(qv[i][1], (double)kv[j].y, acc[i][j]);
-                    acc[i][j] = fma(qv[i][2], (double)kv[j].z, acc[i][j]);
-                    acc[i][j] = fma(qv[i][3], (double)kv[j].w, acc[i][j]);
+                    acc[i][j] = fma(qv[i].x, kv[j].x, acc[i][j]);
+                    acc[i][j] = fma(qv[i].y, kv[j].y, acc[i][j]);
                 }
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) Ss[(size_t)(ty + 16 * i) * sstride + tx + 16 * j] = __dmul_rn(acc[i][j], scale);
-        __syncthreads();  // scores complete, K tile free
-        if (t + 1 < ntiles && warp == 0) {
-            const int nrows = max_pos + 1 - (kbase_pos + kPfKeys) < kPfKeys ? max_pos + 1 - (kbase_pos + kPfKeys) : kPfKeys;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            attn_fetch_rows(Kt, kbase, rowf, hd, kvd, p.msl, kbase_pos + kPfKeys, nrows, &bars[0], lane);
-        }
+        __syncthreads();  // scores complete, the float64 K tile is free
         // ---- running softmax: four threads per row, sixteen keys each ----
         {
             const int r = tid >> 2, part = tid & 3;
@@ -562,7 +571,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
             double tmax = -1e300;
 #pragma unroll 4
             for (int k = 0; k < 16; ++k)
-                if (kbase_pos + part * 16 + k <= qpos) tmax = fmax(tmax, srow[k]);
+                if (kpos0 + part * 16 + k <= qpos) tmax = fmax(tmax, srow[k]);
             tmax = fmax(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
             tmax = fmax(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
             const double m_old = s_m[r];
@@ -571,7 +580,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
 #pragma unroll 4
             for (int k = 0; k < 16; ++k) {
                 double e = 0.0;
-                if (kbase_pos + part * 16 + k <= qpos) e = exp(__dsub_rn(srow[k], m_new));
+                if (kpos0 + part * 16 + k <= qpos) e = p.debug == 8 ? 1.0 : exp(__dsub_rn(srow[k], m_new));
                 srow[k] = e;
                 sum = __dadd_rn(sum, e);
             }
@@ -584,8 +593,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
                 s_m[r] = m_new;
             }
         }
-        __syncthreads();  // weights and rescale factors visible
-        if (!failed && !lb_mbar_wait_bounded(&bars[1], (uint32_t)(t & 1))) failed = true;
+        // ---- V tile: wait, widen into the buffer K just left, request the next K tile ----
+        if (!failed && !lb_mbar_wait_bounded(&bar, phase)) failed = true;
+        phase ^= 1;
+        widen(krows);
+        __syncthreads();  // weights, rescale factors and the float64 V tile visible; staging free
+        if (t + 1 < ntiles && warp == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            attn_fetch_rows(stage, kbase, rowf, hd, kvd, p.msl, kpos0 + kPfKeys, tile_rows(t + 1), &bar, lane);
+        }
         // ---- weighted V ----
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -593,25 +609,21 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
 #pragma unroll
             for (int j = 0; j < 8; ++j) o[i][j] = __dmul_rn(o[i][j], al);
         }
-        for (int k = 0; k < krows; ++k) {
+#pragma unroll 2
+        for (int k = 0; k < (p.debug == 9 ? 1 : krows); ++k) {
             double pw[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) pw[i] = Ss[(size_t)(ty + 16 * i) * sstride + k];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 if (j < ndim) {
-                    const double v = (double)Vt[(size_t)k * rowf + tx + 16 * j];
+                    const double v = KV[(size_t)k * dstride + tx + 16 * j];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) o[i][j] = fma(pw[i], v, o[i][j]);
                 }
             }
         }
-        __syncthreads();  // V tile and weights free
-        if (t + 1 < ntiles && warp == 1) {
-            const int nrows = max_pos + 1 - (kbase_pos + kPfKeys) < kPfKeys ? max_pos + 1 - (kbase_pos + kPfKeys) : kPfKeys;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            attn_fetch_rows(Vt, vbase, rowf, hd, kvd, p.msl, kbase_pos + kPfKeys, nrows, &bars[1], lane);
-        }
+        __syncthreads();  // the float64 V tile and the weights are free
     }
     if (failed && tid == 0) atomicExch(p.status, 1);
 #pragma unroll
@@ -691,13 +703,14 @@ int lb_launch_attention_prefill(loom_b200_ctx* ctx, const LbAttnParams& pin) {
     LbAttnParams p = pin;
     p.trace = nullptr;
     p.status = ctx->status_dev;
+    p.debug = ctx->opt_debug;
     LB_REQUIRE(ctx, lb_attention_prefill_supported(p), "attention (prompt block): %d heads over %d kv heads of %d dimensions", p.heads,
                p.kv_heads, p.hd);
     const int TQ = kPfRows / (p.heads / p.kv_heads);
-    const size_t smem = (size_t)kPfRows * (p.hd + 2) * sizeof(double) + (size_t)kPfRows * (kPfKeys + 1) * sizeof(double) +
-                        2 * (size_t)kPfKeys * (p.hd + 4) * sizeof(float);
+    const size_t smem = (size_t)(kPfRows + kPfKeys) * (p.hd + 2) * sizeof(double) + (size_t)kPfRows * (kPfKeys + 1) * sizeof(double) +
+                        (size_t)kPfKeys * (p.hd + 4) * sizeof(float);
     if (!(ctx->func_attr_mask & (1u << 26))) {
-        LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
         ctx->func_attr_mask |= 1u << 26;
     }
     LB_CUDA(ctx, launch_pdl(ctx, lb_attention_prefill_kernel, dim3(p.kv_heads, (p.M + TQ - 1) / TQ), dim3(kPfThreads), smem, p));

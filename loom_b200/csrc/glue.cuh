@@ -34,6 +34,7 @@ struct LbAttnParams {
     int max_chunk;         // positions one CTA may hold scores for (shared memory sizing)
     unsigned long long* trace;
     int* status;           // device status word for bounded waits
+    int debug;             // timing experiments only (results are wrong when non-zero)
 };
 int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p);
 size_t lb_attn_part_elems(int M, int heads, int hd, int splits);

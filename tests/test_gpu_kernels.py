@@ -211,6 +211,35 @@ def test_microsoft_layout_upload(ctx):
     assert np.max(np.abs(out[0] - np.array([1.5, -2.5, -2.5, -2.5, 1, 1.5, 2.5, 2.5]))) <= 1e-6
 
 
+def entity_blob(words, rows, cols, offset, scale, row_words=None):
+    """encodeEntityBitNetTernaryBlob (poly/entity_bitnet.go:38-55): 24-byte little-endian header + words."""
+    import struct
+    words = np.ascontiguousarray(words, dtype="<u4").ravel()
+    rw = (cols + 15) // 16 if row_words is None else row_words
+    return struct.pack("<IIIfII", rows, cols, offset, float(scale), rw, words.size) + words.tobytes()
+
+
+def test_entity_blob_upload(ctx):
+    # the round trip the reference pins in TestEntityBitNetTernaryBlobRoundTrip (poly/tests/entity_test.go:331-348),
+    # here blob -> device: words, shape, scale and slab offset survive, and the matrix computes
+    rng = np.random.default_rng(11)
+    rows, cols = 24, 70
+    words, scale = orc.pack_f32((rng.standard_normal(rows * cols) * 0.05).astype(np.float32), rows, cols)
+    w, off = ctx.upload_entity_blob(entity_blob(words, rows, cols, 1792, scale))
+    assert off == 1792 and (w.words() == words).all() and w.scale == scale
+    xq, amax = orc.quantize_f32(rng.standard_normal(cols).astype(np.float32))
+    out, _ = gpu_linear(ctx, w, xq[None, :], np.array([amax], np.float32), 1)
+    want = (orc.matvec_i32(words, rows, cols, xq).astype(np.float64) * (np.float64(scale) * np.float64(amax) / 127.0)).astype(np.float32)
+    assert (out[0] == want).all()
+    # rowWords = 0 in the header means ceil(cols/16)
+    w2, _ = ctx.upload_entity_blob(entity_blob(words, rows, cols, 0, scale, row_words=0))
+    assert (w2.words() == words).all()
+    blob = entity_blob(words, rows, cols, 0, scale)
+    for bad in (blob[:10], blob[:-4], b""):
+        with pytest.raises(cabi.LoomB200Error):
+            ctx.upload_entity_blob(bad)
+
+
 @pytest.mark.parametrize("act", [cabi.ACT_SILU, cabi.ACT_RELU2])
 def test_gate_product(ctx, act):
     rng = np.random.default_rng(3)
