@@ -423,6 +423,12 @@ def tp_mode(args):
         dist.broadcast(idt, 0)
         torch.cuda.synchronize()
         ctx.tp_init(rank, world, bytes(idt.cpu().numpy().tobytes()))
+        if args.tp_exchange == "peer":  # row-parallel projections exchange through peer mailboxes (CUDA IPC over NVLink)
+            mine = torch.frombuffer(bytearray(ctx.tp_peer_handle()), dtype=torch.uint8).to(dev)
+            allh = [torch.zeros(64, dtype=torch.uint8, device=dev) for _ in range(world)]
+            dist.all_gather(allh, mine)
+            torch.cuda.synchronize()
+            ctx.tp_attach_peers(b"".join(bytes(t.cpu().numpy().tobytes()) for t in allh))
     H, I, hd = shape["hidden"], shape["inter"], shape["head_dim"]
     qd_l, kvd_l, I_l = shape["heads"] // world * hd, shape["kv_heads"] // world * hd, I // world
     dims = ((qd_l, H), (kvd_l, H), (kvd_l, H), (H, qd_l), (I_l, H), (I_l, H), (H, I_l))
@@ -484,7 +490,8 @@ def tp_mode(args):
     tern_b, kv_b, head_b = algorithmic_bytes(shape, n_prompt + args.warmup + args.steps // 2)
     peak, peak_kind = measured_peaks()
     step_s = dev_s / args.steps
-    launches = shape["layers"] * (6 if world == 1 else 12) + 4  # kernels of this library; the collectives are NCCL's
+    # kernels of this library per token (NCCL's collectives are not counted)
+    launches = shape["layers"] * (6 if world == 1 else (10 if args.tp_exchange == "peer" else 12)) + 4
     line = {
         "metric": "decode tok/s (%s-shape ternary decoder, bs=1, tensor parallel)" % args.shape.upper(), "value": args.steps / dev_s,
         "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * step_s,
@@ -492,6 +499,7 @@ def tp_mode(args):
         "data": "synthetic",
         "config": {"workload": "Llama-3-%s-shape ternary decoder, batch-1 greedy decode" % args.shape.upper(),
                    "layers": shape["layers"], "prompt": n_prompt, "parallelism": "tp%d" % world,
+                   "exchange": "none" if world == 1 else args.tp_exchange,
                    "l2": "every step streams the rank's packed weights and head slice, far beyond the 126 MB L2"},
         "e2e": {"value": e2e_steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": shape["vocab"] * 4,
                 "steps": e2e_steps},
@@ -499,7 +507,7 @@ def tp_mode(args):
         "roofline": {"bound": "hbm", "achieved": (tern_b + kv_b + head_b) / world / step_s / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": (tern_b + kv_b + head_b) / world / step_s / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
                      "kernel": "whole decode step, per-GPU bytes (packed weights + KV + fp32 head slice) / step time"},
-        "collectives_per_token": 0 if world == 1 else shape["layers"] * 6 + 1,
+        "collectives_per_token": 0 if world == 1 else (1 if args.tp_exchange == "peer" else shape["layers"] * 6 + 1),
     }
     if rank == 0:
         print(json.dumps(line))
@@ -527,6 +535,8 @@ def main():
                     help="gemm: the batched-prefill GEMM microbenchmark; tp: tensor-parallel decode of --shape under torchrun; "
                          "sweep: GEMV vs GEMM over batch sizes for the gate/down projections of --shape")
     ap.add_argument("--shape", default="8b", choices=sorted(TP_SHAPES) + ["2b"])
+    ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
+                    help="tp mode: how the row-parallel projections exchange their partial results")
     ap.add_argument("--tokens", type=int, default=512)
     args = ap.parse_args()
     if args.mode == "gemm":

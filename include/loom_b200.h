@@ -86,7 +86,8 @@ void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
  * "gemv_ctas_per_sm" 1..8; "gemv_partition" 0 = choose, 1 = stream-K over tiles with the int32 fix-up,
  * 2 = whole strips per CTA; "pdl" 0/1 = programmatic dependent launch; "tp_graph" 0/1 = record the
  * tensor-parallel decode step, collectives included, as a graph; "gemm_tile" 0 / 128 / 256 = tokens per CTA of the
- * token-block GEMM (0 = choose); "prefill_gemm" 0/1 = prompts of 32 or more tokens
+ * token-block GEMM (0 = choose); "tp_peer" 0/1 = use the peer mailboxes when attached;
+ * "prefill_gemm" 0/1 = prompts of 32 or more tokens
  * run their projections as token-block GEMMs on the tensor cores (1) or eight tokens at a time through the GEMV (0).  Results never depend on them
  * ("debug" is for timing experiments only and does change results). */
 int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value);
@@ -335,6 +336,15 @@ int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, in
 int loom_b200_tp_unique_id(uint8_t* id128);
 /* Joins the group (collective: every rank calls it with the same id).  world == 1 is accepted and a no-op. */
 int loom_b200_tp_init(loom_b200_ctx* ctx, int rank, int world, const uint8_t* id128);
+/* Optional, after tp_init: exchange through peer memory instead of NCCL for the row-parallel projections.  Every
+ * rank calls tp_peer_handle (allocates its 8.4 MB mailbox, returns a 64-byte CUDA IPC handle), the host gathers the
+ * handles of all ranks in rank order (world x 64 bytes, any transport), and every rank calls tp_attach_peers.  The
+ * three per-projection exchanges (sum of squares, absmax, int32 accumulators) then travel as 8-byte {value,
+ * sequence} stores straight into the receivers' mailboxes over NVLink, inside the library's own kernels; polls are
+ * bounded (status word 5, LOOM_B200_ERR_TIMEOUT semantics) so a missing rank cannot hang a GPU.  Option "tp_peer" 0
+ * switches back to NCCL.  The LM-head gather stays on NCCL. */
+int loom_b200_tp_peer_handle(loom_b200_ctx* ctx, uint8_t* handle64);
+int loom_b200_tp_attach_peers(loom_b200_ctx* ctx, const uint8_t* handles);
 /* Leaves the group (also done by loom_b200_ctx_destroy). */
 void loom_b200_tp_finalize(loom_b200_ctx* ctx);
 int loom_b200_tp_rank(const loom_b200_ctx* ctx);

@@ -96,6 +96,8 @@ SIGNATURES = {
     "loom_b200_decoder_generate": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "loom_b200_tp_unique_id": (_i, [_vp]),
     "loom_b200_tp_init": (_i, [_vp, _i, _i, _vp]),
+    "loom_b200_tp_peer_handle": (_i, [_vp, _vp]),
+    "loom_b200_tp_attach_peers": (_i, [_vp, _vp]),
     "loom_b200_tp_finalize": (None, [_vp]),
     "loom_b200_tp_rank": (_i, [_vp]),
     "loom_b200_tp_world": (_i, [_vp]),
@@ -355,6 +357,16 @@ class Context:
     def tp_init(self, rank: int, world: int, unique_id: bytes):
         assert len(unique_id) == 128
         self._check(lib().loom_b200_tp_init(self.h, rank, world, C.c_char_p(unique_id)))
+
+    def tp_peer_handle(self) -> bytes:
+        """This rank's mailbox as a 64-byte CUDA IPC handle; gather all ranks' handles in rank order for tp_attach_peers."""
+        buf = C.create_string_buffer(64)
+        self._check(lib().loom_b200_tp_peer_handle(self.h, buf))
+        return buf.raw
+
+    def tp_attach_peers(self, handles: bytes):
+        assert len(handles) % 64 == 0
+        self._check(lib().loom_b200_tp_attach_peers(self.h, C.c_char_p(handles)))
 
     def tp_finalize(self):
         lib().loom_b200_tp_finalize(self.h)

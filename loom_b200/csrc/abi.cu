@@ -350,6 +350,8 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
         ctx->opt_gemm_tile = value;
     } else if (!strcmp(key, "prefill_gemm")) {
         ctx->opt_prefill_gemm = value != 0;
+    } else if (!strcmp(key, "tp_peer")) {
+        ctx->opt_tp_peer = value != 0;
     } else if (!strcmp(key, "tp_graph")) {
         ctx->opt_tp_graph = value != 0;
     } else {

@@ -78,6 +78,14 @@ struct loom_b200_ctx {
     int opt_prefill_gemm = 1;      // prompts of 32+ tokens run their projections as token-block GEMMs
     int opt_tp_graph = 1;          // record the sharded decode step (collectives included) as a graph
     void* nccl_comm = nullptr;
+    // peer mailboxes (tp.cu): this rank's exchange buffer, the device table of every rank's buffer (own included) as
+    // mapped into this process, and the device counters of the exchange sequence
+    void* xbuf = nullptr;
+    void** peer_xbuf_dev = nullptr;
+    void* peer_xbuf_host[8] = {};
+    unsigned int* x_ctr = nullptr;
+    bool tp_peer = false;          // peers attached: row-parallel projections exchange through the mailboxes
+    int opt_tp_peer = 1;           // 0 = keep the NCCL exchange even when peers are attached
 };
 
 int lb_fail(loom_b200_ctx* ctx, int code, const char* fmt, ...);

@@ -119,6 +119,176 @@ __global__ void lb_tp_finalize_kernel(const int32_t* __restrict__ acc, int M, in
     out[i] = f;
 }
 
+// ---- exchange through peer memory ---------------------------------------------------------------------------
+// Every rank owns a mailbox in its own HBM and maps every other rank's mailbox (CUDA IPC).  A value travels as an
+// 8-byte {data, sequence} pair written with one store straight into the receiver's mailbox over NVLink; the receiver
+// polls its own memory until the sequence number of the current exchange shows up (the scheme NCCL calls LL).  No
+// kernel ever loads from a peer, and nothing here uses multicast.  Two alternating halves per region let a rank run
+// one exchange ahead of a slow peer without overwriting what that peer has not read yet; it cannot run two ahead
+// because finishing an exchange needs every peer's contribution to it.  Every poll is bounded: on expiry the kernel
+// raises the context status word (5) and carries on with whatever it has, so a missing peer never hangs the GPU.
+constexpr int kXMaxRanks = 8;
+constexpr int kXMaxAcc = 8 * 8192;  // int32 accumulators one exchange can carry (tokens x rows)
+constexpr size_t kXRegionA = 0;                                                     // [2][ranks][8 tokens][lo, hi] sum of squares
+constexpr size_t kXRegionB = kXRegionA + 2 * kXMaxRanks * 8 * 2 * 8;                // [2][ranks][8 tokens] absmax
+constexpr size_t kXRegionC = kXRegionB + 2 * kXMaxRanks * 8 * 8;                    // [2][ranks][kXMaxAcc] accumulators
+constexpr size_t kXBytes = kXRegionC + 2 * (size_t)kXMaxRanks * kXMaxAcc * 8;
+constexpr unsigned int kXSpin = 40000000u;  // polls before giving up (of the order of a second)
+
+__device__ __forceinline__ void ll_store(void* p, uint32_t data, uint32_t seq) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(seq) : "memory");
+}
+__device__ __forceinline__ bool ll_wait(const void* p, uint32_t seq, uint32_t* data) {
+    for (unsigned int i = 0; i < kXSpin; ++i) {
+        uint32_t d, f;
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(d), "=r"(f) : "l"(p) : "memory");
+        if (f == seq) {
+            *data = d;
+            return true;
+        }
+    }
+    *data = 0;
+    return false;
+}
+// the kernel's last block moves the exchange counter on: a block that starts late still reads the old value
+__device__ __forceinline__ void x_finish(unsigned int* ctr, unsigned int* done, uint32_t seq) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int t = atomicAdd(done, 1u);
+        if (t == gridDim.x - 1) {
+            *done = 0;
+            __threadfence();
+            *ctr = seq + 1;
+        }
+    }
+}
+
+// Per token: partial sum of squares -> exchange -> scale -> partial absmax of the normalised slice -> exchange.
+// Writes ss[n] (whole-vector sum of squares) and amax[n] (whole-vector absmax, floored) for the GEMV prologue.
+template <typename T>
+__global__ void __launch_bounds__(256) lb_tp_stats_peer_kernel(const T* __restrict__ x, int n_local, int norm_count, double eps,
+                                                               const float* __restrict__ w, int wlen, void* const* peers, int rank,
+                                                               int world, unsigned int* ctr, double* __restrict__ ss_out,
+                                                               float* __restrict__ amax_out, int* status) {
+    __shared__ double red[8];
+    __shared__ float redf[8];
+    __shared__ uint32_t s_part[kXMaxRanks * 2];
+    __shared__ uint32_t s_seq;
+    __shared__ double s_ss;
+    __shared__ int s_bad;
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    const int n = blockIdx.x, tid = threadIdx.x;
+    if (tid == 0) {
+        s_seq = ctr[0];
+        s_bad = 0;
+    }
+    const T* row = x + (size_t)n * n_local;
+    double ss = 0.0;
+    for (int i = tid; i < n_local; i += blockDim.x) {
+        const double v = (double)row[i];
+        ss = __dadd_rn(ss, __dmul_rn(v, v));
+    }
+    ss = lb_warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    const uint32_t seq = s_seq;
+    const size_t half = (size_t)(seq & 1);
+    if (tid == 0) {
+        double t = 0.0;
+        for (int i = 0; i < 8; ++i) t += red[i];
+        s_ss = t;
+    }
+    __syncthreads();
+    if (tid < world * 2) {  // my partial to every rank (own mailbox included), low and high word
+        const int peer = tid >> 1, hw = tid & 1;
+        const unsigned long long bits = (unsigned long long)__double_as_longlong(s_ss);
+        char* dst = (char*)peers[peer] + kXRegionA + ((((half * kXMaxRanks + rank) * 8 + n) * 2 + hw) * 8);
+        ll_store(dst, (uint32_t)(bits >> (32 * hw)), seq);
+    }
+    if (tid < world * 2) {  // every rank's partial from my mailbox
+        const int r = tid >> 1, hw = tid & 1;
+        const char* src = (const char*)peers[rank] + kXRegionA + ((((half * kXMaxRanks + r) * 8 + n) * 2 + hw) * 8);
+        if (!ll_wait(src, seq, &s_part[tid])) s_bad = 1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        double t = 0.0;
+        for (int r = 0; r < world; ++r)  // rank order on every rank: identical bits everywhere
+            t = __dadd_rn(t, __longlong_as_double((long long)(((unsigned long long)s_part[2 * r + 1] << 32) | s_part[2 * r])));
+        s_ss = t;
+        ss_out[n] = t;
+    }
+    __syncthreads();
+    const double sc = __ddiv_rn(1.0, sqrt(__dadd_rn(__ddiv_rn(s_ss, (double)norm_count), eps)));
+    float m = 0.0f;
+    for (int i = tid; i < n_local; i += blockDim.x) {
+        const double wi = (w && i < wlen) ? (double)w[i] : 1.0;
+        double y;
+        if (sizeof(T) == 8) y = __dmul_rn((double)row[i], __dmul_rn(sc, wi));
+        else y = (double)(float)__dmul_rn(__dmul_rn((double)row[i], sc), wi);
+        m = fmaxf(m, (float)fabs(y));
+    }
+    m = lb_warp_max(m);
+    if ((tid & 31) == 0) redf[tid >> 5] = m;
+    __syncthreads();
+    if (tid < world) {
+        float t = 0.0f;
+        for (int i = 0; i < 8; ++i) t = fmaxf(t, redf[i]);
+        char* dst = (char*)peers[tid] + kXRegionB + (((half * kXMaxRanks + rank) * 8 + n) * 8);
+        ll_store(dst, __float_as_uint(t), seq);
+    }
+    if (tid < world) {
+        const char* src = (const char*)peers[rank] + kXRegionB + (((half * kXMaxRanks + tid) * 8 + n) * 8);
+        if (!ll_wait(src, seq, &s_part[tid])) s_bad = 1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.0f;
+        for (int r = 0; r < world; ++r) t = fmaxf(t, __uint_as_float(s_part[r]));
+        amax_out[n] = t < 1e-5f ? 1e-5f : t;  // the quantizer's floor (poly/bitnet_cpu.go:53-55)
+        if (s_bad) atomicExch(status, 5);
+    }
+    x_finish(ctr, ctr + 1, seq);
+}
+
+// out[n,r] = float(sum over ranks of acc[n,r] * os[n] + bias[r]) + residual[n,r]: every thread sends its partial
+// accumulator to every rank, then adds up what the ranks sent it, in rank order.
+__global__ void __launch_bounds__(256) lb_tp_finalize_peer_kernel(const int32_t* __restrict__ acc, int M, int rows, float scale,
+                                                                  const float* __restrict__ amax, const float* __restrict__ bias,
+                                                                  const float* residual, float* out, void* const* peers, int rank,
+                                                                  int world, unsigned int* ctr, int* status) {
+    __shared__ uint32_t s_seq;
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    if (threadIdx.x == 0) s_seq = ctr[0];
+    __syncthreads();
+    const uint32_t seq = s_seq;
+    const size_t half = (size_t)(seq & 1);
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < (size_t)M * rows) {
+        const uint32_t mine = (uint32_t)acc[i];
+        for (int r = 0; r < world; ++r)
+            ll_store((char*)peers[r] + kXRegionC + ((half * kXMaxRanks + rank) * kXMaxAcc + i) * 8, mine, seq);
+        int sum = 0;
+        bool ok = true;
+        for (int r = 0; r < world; ++r) {
+            uint32_t d;
+            ok = ll_wait((const char*)peers[rank] + kXRegionC + ((half * kXMaxRanks + r) * kXMaxAcc + i) * 8, seq, &d) && ok;
+            sum += (int)d;
+        }
+        if (!ok) atomicExch(status, 5);
+        const int n = (int)(i / rows), r = (int)(i % rows);
+        double y = __dmul_rn((double)sum, lb_output_scale(scale, amax[n]));
+        if (bias) y = __dadd_rn(y, (double)bias[r]);
+        float f = (float)y;
+        if (residual) f = __fadd_rn(f, residual[i]);
+        out[i] = f;
+    }
+    x_finish(ctr, ctr + 1, seq);
+}
+
 }  // namespace
 
 int lb_tp_allreduce(loom_b200_ctx* ctx, void* buf, size_t count, int dtype, int op) {
@@ -144,6 +314,19 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
     const int Kl = w->cols;
     double* ss = stats;
     float* amax = reinterpret_cast<float*>(stats + M);
+    const bool peer = ctx->tp_peer && ctx->opt_tp_peer && ctx->tp_world > 1 && (size_t)M * w->rows <= (size_t)kXMaxAcc && M <= 8;
+    if (peer) {
+        LB_REQUIRE(ctx, (Kl & 3) == 0, "tensor-parallel shard width %d must be a multiple of 4", Kl);
+        void* const* peers = (void* const*)ctx->peer_xbuf_dev;
+        if (x_is_f64)
+            lb_tp_stats_peer_kernel<double><<<M, 256, 0, ctx->stream>>>((const double*)x, Kl, K_global, eps, inner_w, inner_w ? inner_w_len : 0, peers,
+                                                                        ctx->tp_rank, ctx->tp_world, ctx->x_ctr, ss, amax, ctx->status_dev);
+        else
+            lb_tp_stats_peer_kernel<float><<<M, 256, 0, ctx->stream>>>((const float*)x, Kl, K_global, eps, inner_w, inner_w ? inner_w_len : 0, peers,
+                                                                       ctx->tp_rank, ctx->tp_world, ctx->x_ctr, ss, amax, ctx->status_dev);
+        LB_CHECK_LAUNCH(ctx, "lb_tp_stats_peer_kernel");
+        ctx->launches++;
+    } else {
     if (x_is_f64) lb_sumsq_kernel<double><<<M, 256, 0, ctx->stream>>>((const double*)x, Kl, ss);
     else lb_sumsq_kernel<float><<<M, 256, 0, ctx->stream>>>((const float*)x, Kl, ss);
     LB_CHECK_LAUNCH(ctx, "lb_sumsq_kernel");
@@ -154,6 +337,7 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
         lb_scaled_absmax_kernel<float><<<M, 256, 0, ctx->stream>>>((const float*)x, Kl, ss, K_global, eps, inner_w, inner_w_len, amax);
     LB_CHECK_LAUNCH(ctx, "lb_scaled_absmax_kernel");
     if (int rc = lb_tp_allreduce(ctx, amax, (size_t)M, kNcclFloat32, kNcclMax)) return rc;
+    }
     LbGemvParams p = {};
     p.nseg = 1;
     p.seg[0].tiles = w->tiles;
@@ -176,8 +360,16 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
     LB_REQUIRE(ctx, (Kl & 3) == 0, "tensor-parallel shard width %d must be a multiple of 4", Kl);
     if (int rc = lb_gemv_finalize_params(ctx, p)) return rc;
     if (int rc = lb_launch_gemv(ctx, p)) return rc;
-    if (int rc = lb_tp_allreduce(ctx, acc, (size_t)M * w->rows, kNcclInt32, kNcclSum)) return rc;
     const size_t n = (size_t)M * w->rows;
+    if (peer) {
+        lb_tp_finalize_peer_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(acc, M, w->rows, w->scale, amax, bias, residual, out,
+                                                                                          (void* const*)ctx->peer_xbuf_dev, ctx->tp_rank,
+                                                                                          ctx->tp_world, ctx->x_ctr + 2, ctx->status_dev);
+        LB_CHECK_LAUNCH(ctx, "lb_tp_finalize_peer_kernel");
+        ctx->launches++;
+        return 0;
+    }
+    if (int rc = lb_tp_allreduce(ctx, acc, (size_t)M * w->rows, kNcclInt32, kNcclSum)) return rc;
     lb_tp_finalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(acc, M, w->rows, w->scale, amax, bias, residual, out);
     LB_CHECK_LAUNCH(ctx, "lb_tp_finalize_kernel");
     return 0;
@@ -217,12 +409,79 @@ int loom_b200_tp_init(loom_b200_ctx* ctx, int rank, int world, const uint8_t* id
     return 0;
 }
 
+int loom_b200_tp_peer_handle(loom_b200_ctx* ctx, uint8_t* handle64) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "tp_peer_handle: ctx is NULL");
+    LB_REQUIRE(ctx, handle64 != nullptr, "tp_peer_handle: NULL buffer");
+    LB_REQUIRE(ctx, ctx->tp_world > 1 && ctx->tp_world <= kXMaxRanks, "tp_peer_handle: needs a group of 2..%d ranks (tp_init first)", kXMaxRanks);
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "tp_peer_handle cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the C ABI passes IPC handles as 64 bytes");
+    if (!ctx->xbuf) {
+        LB_CUDA(ctx, cudaMalloc(&ctx->xbuf, kXBytes));
+        LB_CUDA(ctx, cudaMemset(ctx->xbuf, 0, kXBytes));
+        LB_CUDA(ctx, cudaMalloc(&ctx->x_ctr, 4 * sizeof(unsigned int)));
+        const unsigned int init[4] = {1u, 0u, 1u, 0u};  // sequence numbers start at 1: a zeroed mailbox never matches
+        LB_CUDA(ctx, cudaMemcpy(ctx->x_ctr, init, sizeof(init), cudaMemcpyHostToDevice));
+    }
+    cudaIpcMemHandle_t h;
+    LB_CUDA(ctx, cudaIpcGetMemHandle(&h, ctx->xbuf));
+    memcpy(handle64, &h, 64);
+    return 0;
+}
+
+int loom_b200_tp_attach_peers(loom_b200_ctx* ctx, const uint8_t* handles) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "tp_attach_peers: ctx is NULL");
+    LB_REQUIRE(ctx, handles != nullptr, "tp_attach_peers: NULL handles");
+    LB_REQUIRE(ctx, ctx->xbuf != nullptr, "tp_attach_peers: call tp_peer_handle first");
+    LB_REQUIRE(ctx, !ctx->tp_peer, "tp_attach_peers: peers are already attached");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "tp_attach_peers cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    for (int r = 0; r < ctx->tp_world; ++r) {
+        if (r == ctx->tp_rank) {
+            ctx->peer_xbuf_host[r] = ctx->xbuf;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * 64, 64);
+        void* p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            for (int q = 0; q < r; ++q)
+                if (q != ctx->tp_rank && ctx->peer_xbuf_host[q]) cudaIpcCloseMemHandle(ctx->peer_xbuf_host[q]);
+            memset(ctx->peer_xbuf_host, 0, sizeof(ctx->peer_xbuf_host));
+            return lb_fail(ctx, LOOM_B200_ERR_COMM, "cudaIpcOpenMemHandle for rank %d: %s", r, cudaGetErrorString(e));
+        }
+        ctx->peer_xbuf_host[r] = p;
+    }
+    LB_CUDA(ctx, cudaMalloc(&ctx->peer_xbuf_dev, kXMaxRanks * sizeof(void*)));
+    LB_CUDA(ctx, cudaMemcpy(ctx->peer_xbuf_dev, ctx->peer_xbuf_host, kXMaxRanks * sizeof(void*), cudaMemcpyHostToDevice));
+    ctx->tp_peer = true;
+    return 0;
+}
+
 void loom_b200_tp_finalize(loom_b200_ctx* ctx) {
-    if (!ctx || !ctx->nccl_comm) return;
-    cudaSetDevice(ctx->device);
-    cudaStreamSynchronize(ctx->stream);
-    g_nccl.CommDestroy(ctx->nccl_comm);
-    ctx->nccl_comm = nullptr;
+    if (!ctx) return;
+    if (ctx->xbuf || ctx->nccl_comm) {
+        cudaSetDevice(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+    }
+    if (ctx->tp_peer) {
+        for (int r = 0; r < ctx->tp_world; ++r)
+            if (r != ctx->tp_rank && ctx->peer_xbuf_host[r]) cudaIpcCloseMemHandle(ctx->peer_xbuf_host[r]);
+        ctx->tp_peer = false;
+    }
+    memset(ctx->peer_xbuf_host, 0, sizeof(ctx->peer_xbuf_host));
+    if (ctx->peer_xbuf_dev) cudaFree(ctx->peer_xbuf_dev);
+    if (ctx->x_ctr) cudaFree(ctx->x_ctr);
+    if (ctx->xbuf) cudaFree(ctx->xbuf);
+    ctx->peer_xbuf_dev = nullptr;
+    ctx->x_ctr = nullptr;
+    ctx->xbuf = nullptr;
+    if (ctx->nccl_comm) {
+        g_nccl.CommDestroy(ctx->nccl_comm);
+        ctx->nccl_comm = nullptr;
+    }
     ctx->tp_world = 1;
     ctx->tp_rank = 0;
 }

@@ -31,8 +31,14 @@ def main():
     ctx = cabi.Context(device=local)
     ctx.tp_init(rank, world, share_unique_id(rank))
     assert ctx.tp_rank == rank and ctx.tp_world == world
-    if len(sys.argv) > 1 and sys.argv[1] == "nograph":
+    mode = sys.argv[1] if len(sys.argv) > 1 else "graph"
+    if mode == "nograph":
         ctx.set_option("tp_graph", 0)
+    if mode == "peer":  # exchange through peer mailboxes instead of NCCL: gather every rank's IPC handle
+        mine = torch.frombuffer(bytearray(ctx.tp_peer_handle()), dtype=torch.uint8).clone()
+        allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+        dist.all_gather(allh, mine)
+        ctx.tp_attach_peers(b"".join(bytes(t.numpy().tobytes()) for t in allh))
     failures = []
 
     # ---- the exact int32 sum ----
