@@ -55,6 +55,8 @@ struct GemmParams {
     float* pre_out;          // [tokens, rows] value before the activation, or null
     int32_t* acc_out;        // [tokens, rows] or null
     int* status;
+    int32_t* part_acc;       // split-K: [tokens, rows] partial sums, zero between launches
+    unsigned int* part_cnt;  // split-K: arrivals per (row tile, token tile), zero between launches
     int debug;  // timing experiments only
     unsigned long long* trace;  // optional: row 0 = kernel phases, row 1+i = ring phases of k-slice i (CTA 0 only)
 };
@@ -112,10 +114,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
     const int row0 = blockIdx.x * kRowsPerCta, tok0 = blockIdx.y * NTOK;
     uint8_t* a_ring = smem;
     uint8_t* b_ring = smem + kStages * kSliceBytesA;
-    const int nslices = p.kblocks;  // one 128-column k-block per stage
+    // one 128-column k-block per stage; with split-K (gridDim.z > 1) this CTA covers k-blocks [kbase, kbase + nslices)
+    const int ktot = p.kblocks;
+    const int kbase = (int)((long long)ktot * blockIdx.z / gridDim.z);
+    const int nslices = (int)((long long)ktot * (blockIdx.z + 1) / gridDim.z) - kbase;
     const int strip0 = blockIdx.x * (kRowsPerCta / kTileRows);
     const int nstrips = p.strips - strip0 < kRowsPerCta / kTileRows ? p.strips - strip0 : kRowsPerCta / kTileRows;
-    unsigned long long* tr = (p.trace && blockIdx.x == 0 && blockIdx.y == 0) ? p.trace : nullptr;
+    unsigned long long* tr = (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
     if (tr && tid == 0) tr[0] = lb_gtime();
 
     if (tid == 0) {
@@ -141,7 +146,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         // ---------------- loads: packed weight tiles and activation groups of every k-slice ----------------
         bool failed = false;
         // activations of (256-token tile T, slice ks): 32 KB at ((T * nslices) + ks) * 32 KB; a 128-token CTA takes one half
-        const int8_t* qbase = p.q + (size_t)(tok0 >> 8) * nslices * 32768 + (size_t)((tok0 & 255) >> 3) * 1024;
+        const int8_t* qbase = p.q + ((size_t)(tok0 >> 8) * ktot + kbase) * 32768 + (size_t)((tok0 & 255) >> 3) * 1024;
         for (int ks = 0; ks < nslices; ++ks) {
             const int s = ks % kStages;
             if (ks >= kStages && !failed && !wait_bounded(&empty_bar[s], (uint32_t)((ks / kStages - 1) & 1))) failed = true;
@@ -169,7 +174,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         // packed tile of (this warp's strip, slice ks): 512 contiguous bytes, 16 per lane; rows past the matrix: weight 0
         const uint4 pad = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
         const uint4* tile0 = reinterpret_cast<const uint4*>(p.tiles + (size_t)(strip0 + (have_strip ? warp : 0)) * p.kblocks * kTileWords) + lane;
-        auto fetch = [&](int ks) { return (have_strip && ks < nslices) ? __ldg(tile0 + (size_t)ks * (kTileWords / 4)) : pad; };
+        auto fetch = [&](int ks) { return (have_strip && ks < nslices) ? __ldg(tile0 + (size_t)(kbase + ks) * (kTileWords / 4)) : pad; };
         uint4 w0 = fetch(0), w1 = fetch(1);
         for (int ks = 0; ks < nslices; ++ks) {
             const int s = ks % kStages;
@@ -210,23 +215,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         // (sixteen independent int -> float64 -> float32 chains in flight: with two warps per scheduler the epilogue is
         // bound by instruction latency, not throughput), then stored under the per-output conditions.
         const bool has_bias = row_ok && p.bias != nullptr;
-#pragma unroll 1
-        for (int c0 = chalf * (NTOK / 2); c0 < (chalf + 1) * (NTOK / 2); c0 += 16) {
-            uint32_t v[16];
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                         : "r"(taddr)
-                         : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (tr && tid == 0 && c0 == 0) tr[5] = lb_gtime();
+        auto emit = [&](int c0, const int* raw) {  // raw[j] = sum(code * x) of column c0 + j
             int acc[16];
             double y[16];
             float f[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                acc[j] = (int)v[j] - s_xsum[c0 + j];
+                acc[j] = raw[j] - s_xsum[c0 + j];
                 const double t = __dmul_rn((double)acc[j], s_os[c0 + j]);
                 y[j] = has_bias ? __dadd_rn(t, bias) : t;
                 f[j] = (float)y[j];
@@ -270,7 +265,59 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
                         if (j < ntok) p.out[o0 + (size_t)j * p.rows] = f[j];
                 }
             }
+        };
+        const bool split = gridDim.z > 1;
+#pragma unroll 1
+        for (int c0 = chalf * (NTOK / 2); c0 < (chalf + 1) * (NTOK / 2); c0 += 16) {
+            uint32_t v[16];
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                         : "r"(taddr)
+                         : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (tr && tid == 0 && c0 == 0) tr[5] = lb_gtime();
+            if (!split) {
+                int raw[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) raw[j] = (int)v[j];
+                emit(c0, raw);
+            } else if (row_ok && !failed) {  // split-K: add this CTA's part to the tile's sums (integer addition: any order, same bits)
+                const int ntok = p.tokens - (tok0 + c0);
+                int32_t* dst = p.part_acc + (size_t)(tok0 + c0) * p.rows + r;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (j < ntok) atomicAdd(dst + (size_t)j * p.rows, (int)v[j]);
+            }
             if (tr && tid == 0 && c0 == 0) tr[6] = lb_gtime();
+        }
+        if (split) {
+            // the CTA that completes the tile's sums runs the float epilogue on them and clears them for the next launch
+            __shared__ int s_last;
+            __threadfence();
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (tid == 0) s_last = atomicAdd(&p.part_cnt[blockIdx.y * gridDim.x + blockIdx.x], 1u) == gridDim.z - 1 ? 1 : 0;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (s_last) {
+                __threadfence();
+#pragma unroll 1
+                for (int c0 = chalf * (NTOK / 2); c0 < (chalf + 1) * (NTOK / 2); c0 += 16) {
+                    int raw[16];
+                    const int ntok = p.tokens - (tok0 + c0);
+                    int32_t* src = p.part_acc + (size_t)(tok0 + c0) * p.rows + r;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        raw[j] = 0;
+                        if (row_ok && j < ntok) {
+                            raw[j] = __ldcg(src + (size_t)j * p.rows);
+                            src[(size_t)j * p.rows] = 0;
+                        }
+                    }
+                    emit(c0, raw);
+                }
+                if (tid == 0) p.part_cnt[blockIdx.y * gridDim.x + blockIdx.x] = 0;
+            }
         }
         if (tr && tid == 0) tr[7] = lb_gtime();
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -499,11 +546,29 @@ int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const
         LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<256>::kSmem));
         ctx->func_attr_mask |= 1u << 27;
     }
+    // Split-K when the output tiles alone would leave more than half of the SMs idle: up to eight CTAs share a tile,
+    // each at least four k-slices deep; their int32 partial sums meet in a zero-initialised scratch (exact).
+    const int tiles = wide ? ct256 : ct128;
+    int splits = 1;
+    if (ctx->opt_gemm_splitk && tiles * 2 <= sms) {
+        splits = sms / tiles;
+        if (splits > w->kblocks / 4) splits = w->kblocks / 4;
+        if (splits > 8) splits = 8;
+        if (splits < 1) splits = 1;
+        // measured: a k-slice costs a CTA about 0.5 us, the atomic hand-over of a split about 0.15 us per token of the tile + 2 us
+        const int tile_tokens = tokens < (wide ? 256 : 128) ? tokens : (wide ? 256 : 128);
+        if (splits > 1 && 0.5 * w->kblocks * (1.0 - 1.0 / splits) <= 0.15 * tile_tokens + 2.0) splits = 1;
+    }
+    if (splits > 1) {
+        if (int rc = lb_ensure_fixup(ctx, (size_t)tokens * w->rows, (size_t)tiles)) return rc;
+        p.part_acc = ctx->fix_acc;
+        p.part_cnt = ctx->fix_cnt;
+    }
     if (wide) {
-        dim3 grid(row_tiles, (tokens + 255) / 256);
+        dim3 grid(row_tiles, (tokens + 255) / 256, splits);
         lb_gemm_ternary_i8_kernel<256><<<grid, kGemmThreads, GemmCfg<256>::kSmem, ctx->stream>>>(p);
     } else {
-        dim3 grid(row_tiles, (tokens + 127) / 128);
+        dim3 grid(row_tiles, (tokens + 127) / 128, splits);
         lb_gemm_ternary_i8_kernel<128><<<grid, kGemmThreads, GemmCfg<128>::kSmem, ctx->stream>>>(p);
     }
     LB_CHECK_LAUNCH(ctx, "lb_gemm_ternary_i8_kernel");
