@@ -164,18 +164,25 @@ __device__ __forceinline__ void x_finish(unsigned int* ctr, unsigned int* done, 
     }
 }
 
-// Per token: partial sum of squares -> exchange -> scale -> partial absmax of the normalised slice -> exchange.
-// Writes ss[n] (whole-vector sum of squares) and amax[n] (whole-vector absmax, floored) for the GEMV prologue.
+// Per token (one CTA of 1024 threads): partial sum of squares -> exchange -> scale -> partial absmax of the normalised
+// slice -> exchange -> quantize the slice.  Writes ss[n], amax[n] (whole-vector absmax, floored) and the int8 slice
+// q[n, :], which the GEMV then takes as it is: the same per-element operations as the single-GPU prologue
+// (lb_pro_value, lb_quant_i8), so the same bytes.
+constexpr int kStatThreads = 1024;
+
 template <typename T>
-__global__ void __launch_bounds__(256) lb_tp_stats_peer_kernel(const T* __restrict__ x, int n_local, int norm_count, double eps,
-                                                               const float* __restrict__ w, int wlen, void* const* peers, int rank,
-                                                               int world, unsigned int* ctr, double* __restrict__ ss_out,
-                                                               float* __restrict__ amax_out, int* status) {
-    __shared__ double red[8];
-    __shared__ float redf[8];
+__global__ void __launch_bounds__(kStatThreads) lb_tp_stats_peer_kernel(const T* __restrict__ x, int n_local, int norm_count, double eps,
+                                                                        const float* __restrict__ w, int wlen, void* const* peers,
+                                                                        int rank, int world, unsigned int* ctr, double* __restrict__ ss_out,
+                                                                        float* __restrict__ amax_out, int8_t* __restrict__ q_out,
+                                                                        int* status) {
+    constexpr int PRO = sizeof(T) == 8 ? LB_PRO_INNERNORM64 : LB_PRO_INNERNORM;
+    __shared__ double red[32];
+    __shared__ float redf[32];
     __shared__ uint32_t s_part[kXMaxRanks * 2];
     __shared__ uint32_t s_seq;
     __shared__ double s_ss;
+    __shared__ float s_amax;
     __shared__ int s_bad;
     lb_pdl_launch_dependents();
     lb_pdl_wait();
@@ -186,7 +193,7 @@ __global__ void __launch_bounds__(256) lb_tp_stats_peer_kernel(const T* __restri
     }
     const T* row = x + (size_t)n * n_local;
     double ss = 0.0;
-    for (int i = tid; i < n_local; i += blockDim.x) {
+    for (int i = tid; i < n_local; i += kStatThreads) {
         const double v = (double)row[i];
         ss = __dadd_rn(ss, __dmul_rn(v, v));
     }
@@ -197,7 +204,7 @@ __global__ void __launch_bounds__(256) lb_tp_stats_peer_kernel(const T* __restri
     const size_t half = (size_t)(seq & 1);
     if (tid == 0) {
         double t = 0.0;
-        for (int i = 0; i < 8; ++i) t += red[i];
+        for (int i = 0; i < 32; ++i) t += red[i];
         s_ss = t;
     }
     __syncthreads();
@@ -221,21 +228,19 @@ __global__ void __launch_bounds__(256) lb_tp_stats_peer_kernel(const T* __restri
         ss_out[n] = t;
     }
     __syncthreads();
-    const double sc = __ddiv_rn(1.0, sqrt(__dadd_rn(__ddiv_rn(s_ss, (double)norm_count), eps)));
+    const double root = sqrt(__dadd_rn(__ddiv_rn(s_ss, (double)norm_count), eps));
+    const double rr = __ddiv_rn(1.0, root);
     float m = 0.0f;
-    for (int i = tid; i < n_local; i += blockDim.x) {
+    for (int i = tid; i < n_local; i += kStatThreads) {
         const double wi = (w && i < wlen) ? (double)w[i] : 1.0;
-        double y;
-        if (sizeof(T) == 8) y = __dmul_rn((double)row[i], __dmul_rn(sc, wi));
-        else y = (double)(float)__dmul_rn(__dmul_rn((double)row[i], sc), wi);
-        m = fmaxf(m, (float)fabs(y));
+        m = fmaxf(m, (float)fabs(lb_pro_value<PRO>((double)row[i], root, rr, wi)));
     }
     m = lb_warp_max(m);
     if ((tid & 31) == 0) redf[tid >> 5] = m;
     __syncthreads();
     if (tid < world) {
         float t = 0.0f;
-        for (int i = 0; i < 8; ++i) t = fmaxf(t, redf[i]);
+        for (int i = 0; i < 32; ++i) t = fmaxf(t, redf[i]);
         char* dst = (char*)peers[tid] + kXRegionB + (((half * kXMaxRanks + rank) * 8 + n) * 8);
         ll_store(dst, __float_as_uint(t), seq);
     }
@@ -247,8 +252,23 @@ __global__ void __launch_bounds__(256) lb_tp_stats_peer_kernel(const T* __restri
     if (tid == 0) {
         float t = 0.0f;
         for (int r = 0; r < world; ++r) t = fmaxf(t, __uint_as_float(s_part[r]));
-        amax_out[n] = t < 1e-5f ? 1e-5f : t;  // the quantizer's floor (poly/bitnet_cpu.go:53-55)
+        t = t < 1e-5f ? 1e-5f : t;  // the quantizer's floor (poly/bitnet_cpu.go:53-55)
+        s_amax = t;
+        amax_out[n] = t;
         if (s_bad) atomicExch(status, 5);
+    }
+    __syncthreads();
+    const double qs = __ddiv_rn(127.0, (double)s_amax);
+    uint32_t* qrow = reinterpret_cast<uint32_t*>(q_out + (size_t)n * n_local);
+    for (int u = tid; u < (n_local >> 2); u += kStatThreads) {
+        uint32_t packed = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = 4 * u + k;
+            const double wi = (w && i < wlen) ? (double)w[i] : 1.0;
+            packed |= (uint32_t)(lb_quant_i8(lb_pro_value<PRO>((double)row[i], root, rr, wi), qs) & 0xff) << (8 * k);
+        }
+        qrow[u] = packed;
     }
     x_finish(ctr, ctr + 1, seq);
 }
@@ -315,15 +335,20 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
     double* ss = stats;
     float* amax = reinterpret_cast<float*>(stats + M);
     const bool peer = ctx->tp_peer && ctx->opt_tp_peer && ctx->tp_world > 1 && (size_t)M * w->rows <= (size_t)kXMaxAcc && M <= 8;
+    int8_t* q8 = nullptr;
     if (peer) {
         LB_REQUIRE(ctx, (Kl & 3) == 0, "tensor-parallel shard width %d must be a multiple of 4", Kl);
+        if (int rc = lb_ensure_quant_scratch(ctx, (size_t)kChunkTokens * Kl + 256)) return rc;
+        q8 = reinterpret_cast<int8_t*>(ctx->quant_scratch);
         void* const* peers = (void* const*)ctx->peer_xbuf_dev;
         if (x_is_f64)
-            lb_tp_stats_peer_kernel<double><<<M, 256, 0, ctx->stream>>>((const double*)x, Kl, K_global, eps, inner_w, inner_w ? inner_w_len : 0, peers,
-                                                                        ctx->tp_rank, ctx->tp_world, ctx->x_ctr, ss, amax, ctx->status_dev);
+            lb_tp_stats_peer_kernel<double><<<M, kStatThreads, 0, ctx->stream>>>((const double*)x, Kl, K_global, eps, inner_w, inner_w ? inner_w_len : 0,
+                                                                                 peers, ctx->tp_rank, ctx->tp_world, ctx->x_ctr, ss, amax, q8,
+                                                                                 ctx->status_dev);
         else
-            lb_tp_stats_peer_kernel<float><<<M, 256, 0, ctx->stream>>>((const float*)x, Kl, K_global, eps, inner_w, inner_w ? inner_w_len : 0, peers,
-                                                                       ctx->tp_rank, ctx->tp_world, ctx->x_ctr, ss, amax, ctx->status_dev);
+            lb_tp_stats_peer_kernel<float><<<M, kStatThreads, 0, ctx->stream>>>((const float*)x, Kl, K_global, eps, inner_w, inner_w ? inner_w_len : 0,
+                                                                                peers, ctx->tp_rank, ctx->tp_world, ctx->x_ctr, ss, amax, q8,
+                                                                                ctx->status_dev);
         LB_CHECK_LAUNCH(ctx, "lb_tp_stats_peer_kernel");
         ctx->launches++;
     } else {
@@ -347,14 +372,20 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
     p.seg[0].kind = LB_OUT_ACC;
     p.K = Kl;
     p.M = M;
-    p.pro = x_is_f64 ? LB_PRO_INNERNORM64 : LB_PRO_INNERNORM;
-    p.x = x;
-    p.norm_w = inner_w;
-    p.norm_w_len = inner_w ? inner_w_len : 0;
-    p.eps = eps;
-    p.given_ss = ss;
-    p.given_amax = amax;
-    p.norm_count = K_global;
+    if (peer) {  // the statistics kernel already quantized the slice
+        p.pro = LB_PRO_Q8;
+        p.x = q8;
+        p.amax_in = amax;
+    } else {
+        p.pro = x_is_f64 ? LB_PRO_INNERNORM64 : LB_PRO_INNERNORM;
+        p.x = x;
+        p.norm_w = inner_w;
+        p.norm_w_len = inner_w ? inner_w_len : 0;
+        p.eps = eps;
+        p.given_ss = ss;
+        p.given_amax = amax;
+        p.norm_count = K_global;
+    }
     p.epi = LB_EPI_GENERIC;
     p.act = LOOM_B200_ACT_LINEAR;
     LB_REQUIRE(ctx, (Kl & 3) == 0, "tensor-parallel shard width %d must be a multiple of 4", Kl);
