@@ -366,30 +366,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
 template <int PRO>
 __global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const LbGemmQuant a, int Kp, int8_t* __restrict__ q,
                                                                float* __restrict__ amax_out, int* __restrict__ xsum_out) {
+    extern __shared__ __align__(16) uint8_t qsm[];  // the token's row in its input precision: read from memory once
     __shared__ float red[8];
     __shared__ double redd[8];
     __shared__ int redi[8];
     constexpr bool f64 = PRO == LB_PRO_INNERNORM64;
+    using VT = typename std::conditional<f64, double, float>::type;
+    VT* vals = reinterpret_cast<VT*>(qsm);
     const int K = a.K, tid = threadIdx.x;
     // byte c of this token's row lives at: (256-token tile, k-slice c/128) block of 32 KB, + (token%256)/8 * 1 KB
     // + (16-byte chunk (c/16)%8) * 128 + (token%8) * 16 + c%16
     int8_t* qrow = q + (size_t)(blockIdx.x >> 8) * (Kp >> 7) * 32768 + (size_t)((blockIdx.x & 255) >> 3) * 1024 + (blockIdx.x & 7) * 16;
-    auto at = [&](int c) -> int8_t& { return qrow[(size_t)(c >> 7) * 32768 + ((c >> 4) & 7) * 128 + (c & 15)]; };
+    auto chunk_ptr = [&](int ch) { return reinterpret_cast<uint4*>(qrow + (size_t)(ch >> 3) * 32768 + (ch & 7) * 128); };
+    const int nchunks = Kp >> 4;
     if ((int)blockIdx.x >= a.tokens) {  // padding token: zeros
-        for (int c = tid; c < Kp; c += blockDim.x) at(c) = 0;
+        for (int ch = tid; ch < nchunks; ch += blockDim.x) *chunk_ptr(ch) = make_uint4(0u, 0u, 0u, 0u);
         return;
     }
-    const float* rowf = (const float*)a.x + (size_t)blockIdx.x * K;
-    const double* rowd = (const double*)a.x + (size_t)blockIdx.x * K;
-    auto ld = [&](int i) { return f64 ? rowd[i] : (double)rowf[i]; };
+    const VT* row = reinterpret_cast<const VT*>(a.x) + (size_t)blockIdx.x * K;
     auto wt = [&](int i) { return (PRO != LB_PRO_F32 && a.norm_w && i < a.norm_w_len) ? (double)a.norm_w[i] : 1.0; };
+    // pass 1: stage the row, sum of squares (norms) or absmax (plain rows)
+    double ss = 0.0;
+    float m = 0.0f;
+    for (int i = tid; i < K; i += blockDim.x) {
+        const VT v = row[i];
+        vals[i] = v;
+        if (PRO >= LB_PRO_BLOCKNORM) ss = __dadd_rn(ss, __dmul_rn((double)v, (double)v));
+        else m = fmaxf(m, (float)fabs((double)v));
+    }
     double root = 1.0, rr = 1.0;
     if (PRO >= LB_PRO_BLOCKNORM) {
-        double ss = 0.0;
-        for (int i = tid; i < K; i += blockDim.x) {
-            const double v = ld(i);
-            ss = __dadd_rn(ss, __dmul_rn(v, v));
-        }
         ss = lb_warp_sum(ss);
         if ((tid & 31) == 0) redd[tid >> 5] = ss;
         __syncthreads();
@@ -397,29 +403,36 @@ __global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const LbGemmQuant
         for (int i = 0; i < 8; ++i) ss += redd[i];
         root = sqrt(__dadd_rn(__ddiv_rn(ss, (double)K), a.eps));
         rr = __ddiv_rn(1.0, root);
-    }
-    float m = 0.0f;
-    for (int i = tid; i < K; i += blockDim.x) {
-        const double y = lb_pro_value<PRO>(ld(i), root, rr, wt(i));
-        if (a.norm_out) a.norm_out[(size_t)blockIdx.x * K + i] = (float)y;
-        m = fmaxf(m, (float)fabs(y));
+        // pass 2: normalise in place (each thread revisits the elements it staged), absmax of the result
+        for (int i = tid; i < K; i += blockDim.x) {
+            const double y = lb_pro_value<PRO>((double)vals[i], root, rr, wt(i));
+            vals[i] = (VT)y;
+            if (a.norm_out) a.norm_out[(size_t)blockIdx.x * K + i] = (float)y;
+            m = fmaxf(m, (float)fabs(y));
+        }
     }
     m = lb_warp_max(m);
     if ((tid & 31) == 0) red[tid >> 5] = m;
-    __syncthreads();
+    __syncthreads();  // also: every staged / normalised value is visible to the whole CTA
     m = red[0];
     for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
     if (m < 1e-5f) m = 1e-5f;
     const double s = __ddiv_rn(127.0, (double)m);
+    // pass 3: one 16-column chunk per thread and step -> one 16-byte store; byte 4j+b of the chunk holds column 4b+j
     int sum = 0;
-    for (int c = tid; c < Kp; c += blockDim.x) {
-        // destination byte c of the row: group base + 4j + b  <-  column base + 4b + j
-        const int base = c & ~15, pos = c & 15, j = pos >> 2, b = pos & 3;
-        const int col = base + 4 * b + j;
-        int v = 0;
-        if (col < K) v = lb_quant_i8(lb_pro_value<PRO>(ld(col), root, rr, wt(col)), s);
-        at(c) = (int8_t)v;
-        sum += v;
+    for (int ch = tid; ch < nchunks; ch += blockDim.x) {
+        uint32_t wds[4] = {0u, 0u, 0u, 0u};
+        const int base = ch << 4;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const int col = base + k;  // k = 4b + j -> destination byte 4j + b
+            int v = 0;
+            if (col < K) v = lb_quant_i8((double)vals[col], s);
+            sum += v;
+            const int j = k & 3, b = k >> 2;
+            wds[j] |= (uint32_t)(v & 0xff) << (8 * b);
+        }
+        *chunk_ptr(ch) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
     }
     sum = lb_warp_sum_i(sum);
     if ((tid & 31) == 0) redi[tid >> 5] = sum;
@@ -483,11 +496,20 @@ int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a) {
         ctx->gemm_scratch_bytes = need + need / 4;
     }
     GemmScratch g = gemm_scratch_at(ctx->gemm_scratch, a.tokens, Kp);
+    const size_t qsmem = (size_t)a.K * (a.pro == LB_PRO_INNERNORM64 ? 8 : 4);
+    LB_REQUIRE(ctx, qsmem <= 200 * 1024, "gemm_quantize: rows of %d columns do not fit in shared memory", a.K);
+    if (!(ctx->func_attr_mask & (1u << 25))) {
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_quantize_gemm_kernel<LB_PRO_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_quantize_gemm_kernel<LB_PRO_BLOCKNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_quantize_gemm_kernel<LB_PRO_INNERNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_quantize_gemm_kernel<LB_PRO_INNERNORM64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        ctx->func_attr_mask |= 1u << 25;
+    }
     switch (a.pro) {
-        case LB_PRO_F32: lb_quantize_gemm_kernel<LB_PRO_F32><<<pt, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
-        case LB_PRO_BLOCKNORM: lb_quantize_gemm_kernel<LB_PRO_BLOCKNORM><<<pt, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
-        case LB_PRO_INNERNORM: lb_quantize_gemm_kernel<LB_PRO_INNERNORM><<<pt, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
-        case LB_PRO_INNERNORM64: lb_quantize_gemm_kernel<LB_PRO_INNERNORM64><<<pt, 256, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_F32: lb_quantize_gemm_kernel<LB_PRO_F32><<<pt, 256, qsmem, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_BLOCKNORM: lb_quantize_gemm_kernel<LB_PRO_BLOCKNORM><<<pt, 256, qsmem, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_INNERNORM: lb_quantize_gemm_kernel<LB_PRO_INNERNORM><<<pt, 256, qsmem, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
+        case LB_PRO_INNERNORM64: lb_quantize_gemm_kernel<LB_PRO_INNERNORM64><<<pt, 256, qsmem, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum); break;
         default: return lb_fail(ctx, LOOM_B200_ERR_INVALID, "gemm_quantize: prologue %d", a.pro);
     }
     LB_CHECK_LAUNCH(ctx, "lb_quantize_gemm_kernel");

@@ -515,6 +515,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
     uint32_t phase = 0;
     // staging (float32, rows of hd+4) -> KV (float64, rows of hd+2); rows beyond `rows` become zero
     auto widen = [&](int rows) {
+        if (p.debug == 12) return;
         const int quads = hd / 4;
         for (int idx = tid; idx < kPfKeys * quads; idx += kPfThreads) {
             const int r = idx / quads, c = (idx - r * quads) * 4;
@@ -544,7 +545,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
 #pragma unroll 2
-        for (int d = 0; d < (p.debug == 10 ? 2 : hd); d += 2) {
+        for (int d = 0; d < (p.debug >= 10 ? 2 : hd); d += 2) {
             double2 qv[4], kv[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const double2*>(Qs + (size_t)(ty + 16 * i) * dstride + d);
@@ -580,7 +581,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
 #pragma unroll 4
             for (int k = 0; k < 16; ++k) {
                 double e = 0.0;
-                if (kpos0 + part * 16 + k <= qpos) e = p.debug == 8 ? 1.0 : exp(__dsub_rn(srow[k], m_new));
+                if (kpos0 + part * 16 + k <= qpos) e = (p.debug == 8 || p.debug >= 11) ? 1.0 : exp(__dsub_rn(srow[k], m_new));
                 srow[k] = e;
                 sum = __dadd_rn(sum, e);
             }
@@ -610,7 +611,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
             for (int j = 0; j < 8; ++j) o[i][j] = __dmul_rn(o[i][j], al);
         }
 #pragma unroll 2
-        for (int k = 0; k < (p.debug == 9 ? 1 : krows); ++k) {
+        for (int k = 0; k < ((p.debug == 9 || p.debug >= 11) ? 1 : krows); ++k) {
             double pw[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) pw[i] = Ss[(size_t)(ty + 16 * i) * sstride + k];
