@@ -123,7 +123,7 @@ __global__ void lb_tp_finalize_kernel(const int32_t* __restrict__ acc, int M, in
 // Every rank owns a mailbox in its own HBM and maps every other rank's mailbox (CUDA IPC).  A value travels as an
 // 8-byte {data, sequence} pair written with one store straight into the receiver's mailbox over NVLink; the receiver
 // polls its own memory until the sequence number of the current exchange shows up (the scheme NCCL calls LL).  No
-// kernel ever loads from a peer, and nothing here uses multicast.  Two alternating halves per region let a rank run
+// kernel ever loads from a peer: only plain stores cross NVLink.  Two alternating halves per region let a rank run
 // one exchange ahead of a slow peer without overwriting what that peer has not read yet; it cannot run two ahead
 // because finishing an exchange needs every peer's contribution to it.  Every poll is bounded: on expiry the kernel
 // raises the context status word (5) and carries on with whatever it has, so a missing peer never hangs the GPU.
