@@ -68,8 +68,15 @@ const char* loom_b200_last_error(const loom_b200_ctx* ctx);
  * existing cudaStream_t to launch on, or NULL to let the context create its own. */
 int loom_b200_ctx_create(int device, void* stream, loom_b200_ctx** out);
 void loom_b200_ctx_destroy(loom_b200_ctx* ctx);
-/* FlushFrame + wait, poly/wgpu_context_native.go:276 */
+/* FlushFrame + wait, poly/wgpu_context_native.go:276.  Also reports a bounded device-side wait that ran out since the
+ * last sync (LOOM_B200_ERR_TIMEOUT; the results of the calls in between are invalid) and clears that condition. */
 int loom_b200_sync(loom_b200_ctx* ctx);
+/* Failure-detection self-test (no counterpart in the reference): launches one thread that polls a flag nothing ever
+ * sets, gives up after `polls` reads and raises the context's device status word, exactly as the bounded waits inside
+ * the kernels do (tile copies, the GEMM pipeline, tensor-parallel peers).  Returns LOOM_B200_ERR_TIMEOUT through the
+ * same path loom_b200_sync uses, clears the word, and leaves the context usable.  Nothing faults, traps or hangs. */
+int loom_b200_selftest_wait_timeout(loom_b200_ctx* ctx, unsigned int polls);
+
 /* BeginFrame ... FlushFrame (poly/wgpu_context_native.go:263-276, used once per forward by
  * ForwardTokenIDsWGPU, poly/wgpu_forward.go:99,564): the dispatches issued between begin and end are
  * recorded into a CUDA graph instead of running; graph_launch replays them with one submission.

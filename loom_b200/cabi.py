@@ -15,6 +15,9 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 ACT_RELU, ACT_SILU, ACT_GELU, ACT_TANH, ACT_SIGMOID, ACT_LEAKY_RELU, ACT_RELU2, ACT_LINEAR = 0, 1, 2, 3, 4, 5, 6, -1
 
 
+ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_NO_DEVICE, ERR_TIMEOUT, ERR_COMM = -1, -2, -3, -4, -5, -6
+
+
 class LoomB200Error(RuntimeError):
     def __init__(self, code, msg):
         super().__init__("loom_b200 error %d: %s" % (code, msg))
@@ -41,6 +44,7 @@ SIGNATURES = {
     "loom_b200_ctx_create": (_i, [_i, _vp, C.POINTER(_vp)]),
     "loom_b200_ctx_destroy": (None, [_vp]),
     "loom_b200_sync": (_i, [_vp]),
+    "loom_b200_selftest_wait_timeout": (_i, [_vp, C.c_uint]),
     "loom_b200_ctx_stream": (_vp, [_vp]),
     "loom_b200_graph_begin": (_i, [_vp]),
     "loom_b200_graph_end": (_i, [_vp, C.POINTER(_vp)]),
@@ -218,6 +222,10 @@ class Context:
 
     def sync(self):
         self._check(lib().loom_b200_sync(self.h))
+
+    def selftest_wait_timeout(self, polls: int = 100000):
+        """Makes a bounded device-side wait run out; raises LoomB200Error(LOOM_B200_ERR_TIMEOUT)."""
+        self._check(lib().loom_b200_selftest_wait_timeout(self.h, polls))
 
     def graph_begin(self):
         self._check(lib().loom_b200_graph_begin(self.h))

@@ -78,6 +78,20 @@ int lb_ensure_scratch(loom_b200_ctx* ctx, size_t bytes) {
     return 0;
 }
 
+int lb_sync_checked(loom_b200_ctx* ctx) {
+    LB_CUDA(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const int code = *ctx->status_host;
+    if (code == 0) return 0;
+    *ctx->status_host = 0;
+    LB_CUDA(ctx, cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), ctx->stream));
+    static const char* what[] = {"", "a shared-memory tile copy did not complete", "the grid barrier of a program did not complete",
+                                 "the tensor-core pipeline of the GEMM stalled", "", "a tensor-parallel peer did not answer",
+                                 "self-test: a flag that nothing sets"};
+    return lb_fail(ctx, LOOM_B200_ERR_TIMEOUT, "a bounded device-side wait ran out (%d: %s); results of the calls since the last sync are invalid",
+                   code, code >= 1 && code <= 6 ? what[code] : "unknown");
+}
+
 int lb_ensure_quant_scratch(loom_b200_ctx* ctx, size_t bytes) {
     if (bytes <= ctx->quant_scratch_bytes) return 0;
     LB_NO_CAPTURE(ctx, "growing the quantization scratch buffer");
@@ -310,6 +324,12 @@ int loom_b200_ctx_create(int device, void* stream, loom_b200_ctx** out) {
         delete ctx;
         return lb_fail(nullptr, LOOM_B200_ERR_CUDA, "status word: %s", cudaGetErrorString(e));
     }
+    if ((e = cudaMallocHost(&ctx->status_host, sizeof(int))) != cudaSuccess) {
+        cudaFree(ctx->status_dev);
+        delete ctx;
+        return lb_fail(nullptr, LOOM_B200_ERR_CUDA, "status word: %s", cudaGetErrorString(e));
+    }
+    *ctx->status_host = 0;
     if (const char* v = getenv("LOOM_B200_GEMV_VARIANT")) ctx->opt_gemv_variant = atoi(v) == 1 ? 1 : 0;
     if (const char* v = getenv("LOOM_B200_GEMV_CTAS_PER_SM")) ctx->opt_gemv_ctas_per_sm = atoi(v) > 0 ? atoi(v) : 2;
     if (const char* v = getenv("LOOM_B200_PDL")) ctx->opt_pdl = atoi(v) != 0;
@@ -371,6 +391,7 @@ void loom_b200_ctx_destroy(loom_b200_ctx* ctx) {
     if (ctx->fix_cnt) cudaFree(ctx->fix_cnt);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->trace_dev) cudaFree(ctx->trace_dev);
     if (ctx->argmax_scratch) cudaFree(ctx->argmax_scratch);
     if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
@@ -383,8 +404,25 @@ int loom_b200_sync(loom_b200_ctx* ctx) {
     if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "sync: ctx is NULL");
     LB_NO_CAPTURE(ctx, "sync");
     if (int rc = lb_set_device(ctx)) return rc;
-    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return 0;
+    return lb_sync_checked(ctx);
+}
+
+__global__ void lb_selftest_wait_kernel(const volatile int* flag, unsigned int polls, int* status) {
+    for (unsigned int i = 0; i < polls; ++i)
+        if (*flag != 0) return;
+    atomicExch(status, 6);  // nothing set the flag: report instead of waiting on
+}
+
+int loom_b200_selftest_wait_timeout(loom_b200_ctx* ctx, unsigned int polls) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "selftest_wait_timeout: ctx is NULL");
+    LB_REQUIRE(ctx, polls >= 1 && polls <= 10000000u, "selftest_wait_timeout: %u polls (1..10,000,000)", polls);
+    LB_NO_CAPTURE(ctx, "selftest_wait_timeout");
+    if (int rc = lb_set_device(ctx)) return rc;
+    if (int rc = lb_ensure_scratch(ctx, 256)) return rc;
+    LB_CUDA(ctx, cudaMemsetAsync(ctx->scratch, 0, sizeof(int), ctx->stream));
+    lb_selftest_wait_kernel<<<1, 1, 0, ctx->stream>>>((const volatile int*)ctx->scratch, polls, ctx->status_dev);
+    LB_CHECK_LAUNCH(ctx, "lb_selftest_wait_kernel");
+    return lb_sync_checked(ctx);
 }
 
 int loom_b200_graph_begin(loom_b200_ctx* ctx) {

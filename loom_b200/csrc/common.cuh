@@ -56,6 +56,7 @@ struct loom_b200_ctx {
     size_t scratch_bytes = 0;
     // device status word written by kernels with bounded waits (0 = ok)
     int* status_dev = nullptr;
+    int* status_host = nullptr;    // pinned mirror, refreshed by lb_sync_checked
     void* quant_scratch = nullptr;   // int8 row and absmax of the stand-alone GEMV prologue (wide inputs)
     size_t quant_scratch_bytes = 0;
     void* gemm_scratch = nullptr;    // int8 activations, amax and sums of the tensor-core GEMM path
@@ -93,6 +94,9 @@ int lb_fail(loom_b200_ctx* ctx, int code, const char* fmt, ...);
 const char* lb_global_error();
 int lb_ensure_fixup(loom_b200_ctx* ctx, size_t acc_elems, size_t cnt_elems);
 int lb_ensure_scratch(loom_b200_ctx* ctx, size_t bytes);
+// Waits for the context's stream and reads the device status word with it: a bounded device-side wait that ran out
+// (a copy that never landed, a peer that never answered) comes back as LOOM_B200_ERR_TIMEOUT, and the word is cleared.
+int lb_sync_checked(loom_b200_ctx* ctx);
 int lb_ensure_quant_scratch(loom_b200_ctx* ctx, size_t bytes);
 
 #define LB_CUDA(ctx, expr)                                                                          \

@@ -545,7 +545,7 @@ int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int
     dec->kv_offset += n;
     if (logits_host) {
         LB_CUDA(ctx, cudaMemcpyAsync(dec->h_logits, dec->logits, (size_t)dec->d.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
-        LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (int rc = lb_sync_checked(ctx)) return rc;
         memcpy(logits_host, dec->h_logits, (size_t)dec->d.vocab * 4);
     }
     return 0;
@@ -620,7 +620,7 @@ int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, in
     LB_CUDA(ctx, cudaEventRecord(e1, ctx->stream));
     if (max_new > 0)
         LB_CUDA(ctx, cudaMemcpyAsync(out_tokens, dec->out_tokens, (size_t)max_new * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
-    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (int rc = lb_sync_checked(ctx)) return rc;
     auto t2 = clk::now();
     float ms = 0.f;
     cudaEventElapsedTime(&ms, e0, e1);

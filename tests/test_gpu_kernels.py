@@ -332,3 +332,18 @@ def test_linear_program_matches_individual_calls(ctx):
     got = ctx.download(bufs[6], (rows,), np.float32)
     assert (got.view(np.uint32) == ref.view(np.uint32)).all()
     ctx.program_free(prog)
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(ctx):
+    # failure detection without a fault: a device-side wait on a flag nothing sets gives up after its poll limit, the
+    # status word comes back through sync as LOOM_B200_ERR_TIMEOUT, and the context keeps working afterwards
+    with pytest.raises(cabi.LoomB200Error) as err:
+        ctx.selftest_wait_timeout(200000)
+    assert err.value.code == cabi.ERR_TIMEOUT and "bounded device-side wait" in str(err.value)
+    ctx.sync()  # the condition was cleared
+    rng = np.random.default_rng(1)
+    words, scale = orc.pack_f32((rng.standard_normal(32 * 64) * 0.05).astype(np.float32), 32, 64)
+    w = ctx.upload_ternary(words, 32, 64, scale)
+    xq, amax = orc.quantize_f32(rng.standard_normal(64).astype(np.float32))
+    _, acc = gpu_linear(ctx, w, xq[None, :], np.array([amax], np.float32), 1)
+    assert (acc[0] == orc.matvec_i32(words, 32, 64, xq)).all()
