@@ -65,6 +65,19 @@ def test_gemm_ragged_shapes(ctx, rows, cols, tokens):
     run_case(ctx, rows, cols, tokens, rows + tokens, bias=True, residual=True, act=cabi.ACT_RELU)
 
 
+@pytest.mark.parametrize("rows,cols,tokens", [(2560, 6912, 64), (512, 8192, 20), (100, 4096, 130)])
+def test_gemm_split_k(ctx, rows, cols, tokens):
+    # few output tiles and a long K: several CTAs share a tile and hand their int32 partial sums over through atomics;
+    # the result must be the same bits, and a second run must find the scratch clean again
+    run_case(ctx, rows, cols, tokens, 3 * rows + tokens, bias=True, residual=True, act=cabi.ACT_RELU2)
+    run_case(ctx, rows, cols, tokens, 5 * rows + tokens, bias=False, residual=False)
+    ctx.set_option("gemm_splitk", 0)
+    try:
+        run_case(ctx, rows, cols, tokens, 7 * rows + tokens, bias=True, residual=False)
+    finally:
+        ctx.set_option("gemm_splitk", 1)
+
+
 @pytest.mark.parametrize("rows,cols", [(6912, 2560), (2560, 6912)])
 def test_gemm_prefill_config(ctx, rows, cols):
     run_case(ctx, rows, cols, 512, 7, bias=False, residual=True)
