@@ -365,6 +365,9 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
         ctx->opt_debug = value;
     } else if (!strcmp(key, "pdl")) {
         ctx->opt_pdl = value != 0;
+    } else if (!strcmp(key, "decode_splits")) {
+        if (value < 0 || value > 32) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "ctx_set_option: decode_splits is 0..32");
+        ctx->opt_decode_splits = value;
     } else if (!strcmp(key, "gemm_splitk")) {
         ctx->opt_gemm_splitk = value != 0;
     } else if (!strcmp(key, "gemm_tile")) {

@@ -354,6 +354,7 @@ int loom_b200_decoder_create(loom_b200_ctx* ctx, const loom_b200_decoder_dims* d
     dec->decode_splits = (2 * ctx->sm_count) / dec->heads_l;
     if (dec->decode_splits > 16) dec->decode_splits = 16;
     if (dec->decode_splits < 1) dec->decode_splits = 1;
+    if (ctx->opt_decode_splits > 0) dec->decode_splits = ctx->opt_decode_splits;  // read when the decoder is created
     dec->out_cap = dec->d.max_seq_len;
     cudaError_t e = cudaSuccess;
     auto A = [&](void** p, size_t bytes) {
@@ -448,7 +449,7 @@ int loom_b200_decoder_set_block(loom_b200_decoder* dec, int block, const float* 
     m.wk = w7[1];
     m.wv = w7[2];
     m.wo = w7[3];
-    if (int rc = lb_mha_alloc(ctx, &m, 16)) return rc;
+    if (int rc = lb_mha_alloc(ctx, &m, 32)) return rc;
     cudaFree(m.pos_dev);
     m.pos_dev = dec->pos;
     b.gate = w7[4];

@@ -134,10 +134,11 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     const int h = blockIdx.x, n = blockIdx.y, sp = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hd = p.hd, kvd = p.kv_heads * hd, qd = p.heads * hd;
     const int rowf = hd + 4;  // padded row: conflict-free 16-byte reads down a column of rows
+    const int tile = p.tile;  // positions per shared-memory tile (at most kAttnTile)
     const int G = hd >= kAttnThreads ? 1 : kAttnThreads / hd;
-    float* kt = reinterpret_cast<float*>(smem_raw);           // [kAttnTile, rowf]
-    float* vt = kt + (size_t)kAttnTile * rowf;                // [kAttnTile, rowf]
-    double* sq = reinterpret_cast<double*>(vt + (size_t)kAttnTile * rowf);  // [hd]
+    float* kt = reinterpret_cast<float*>(smem_raw);           // [tile, rowf]
+    float* vt = kt + (size_t)tile * rowf;                // [tile, rowf]
+    double* sq = reinterpret_cast<double*>(vt + (size_t)tile * rowf);  // [hd]
     double* sacc = sq + hd;                                   // [G, hd]
     double* sc = sacc + (size_t)G * hd;                       // [max_chunk]
     if (tid == 0) {
@@ -159,11 +160,11 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     const int kvh = h / (p.heads / p.kv_heads);
     const float* kbase = p.cache_k + (size_t)kvh * hd;
     const float* vbase = p.cache_v + (size_t)kvh * hd;
-    const int ntiles = (cnt + kAttnTile - 1) / kAttnTile;
+    const int ntiles = (cnt + tile - 1) / tile;
     bool failed = false;
     // first K and V tiles: every row of both is requested before anything else happens
     if (cnt > 0) {
-        const int rows0 = cnt < kAttnTile ? cnt : kAttnTile;
+        const int rows0 = cnt < tile ? cnt : tile;
         if (warp == 0) attn_fetch_rows(kt, kbase, rowf, hd, kvd, p.msl, k0, rows0, &bars[0], lane);
         if (warp == 1) attn_fetch_rows(vt, vbase, rowf, hd, kvd, p.msl, k0, rows0, &bars[1], lane);
     }
@@ -175,8 +176,8 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     double mx = -1e9;
     const int half = tid & 1, hlen = hd / 2;
     for (int t = 0; t < ntiles; ++t) {
-        const int base = t * kAttnTile;
-        const int rows = cnt - base < kAttnTile ? cnt - base : kAttnTile;
+        const int base = t * tile;
+        const int rows = cnt - base < tile ? cnt - base : tile;
         if (t > 0) {
             __syncthreads();  // everyone is done with the previous K tile
             if (warp == 0) {
@@ -225,8 +226,8 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     const bool owner = d < hd && grp < G;
     double a0 = 0.0, a1 = 0.0;
     for (int t = 0; t < ntiles; ++t) {
-        const int base = t * kAttnTile;
-        const int rows = cnt - base < kAttnTile ? cnt - base : kAttnTile;
+        const int base = t * tile;
+        const int rows = cnt - base < tile ? cnt - base : tile;
         if (t > 0) {
             __syncthreads();
             if (warp == 1) {
@@ -683,7 +684,11 @@ int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& pin) {
     LB_REQUIRE(ctx, p.hd <= kAttnThreads, "attention: head_dim %d above %d is not supported", p.hd, kAttnThreads);
     LB_REQUIRE(ctx, p.splits >= 1 && p.splits <= 64, "attention: %d splits", p.splits);
     const int G = p.hd >= kAttnThreads ? 1 : kAttnThreads / p.hd;
-    size_t smem = (size_t)(p.hd + (size_t)G * p.hd + p.max_chunk) * sizeof(double) + 2 * (size_t)kAttnTile * (p.hd + 4) * sizeof(float);
+    // tile: short tiles let more CTAs share an SM
+    p.tile = ((p.max_chunk + 1) / 2 + 7) / 8 * 8;  // half of the longest chunk: two tiles at most when the ring is full
+    if (p.tile > kAttnTile) p.tile = kAttnTile;
+    if (p.tile < 8) p.tile = 8;
+    size_t smem = (size_t)(p.hd + (size_t)G * p.hd + p.max_chunk) * sizeof(double) + 2 * (size_t)p.tile * (p.hd + 4) * sizeof(float);
     if (smem > 200 * 1024) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "attention: %d positions per CTA need %zu B of shared memory", p.max_chunk, smem);
     if (smem > 48 * 1024 && !(ctx->func_attr_mask & (1u << 30))) {
         LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));

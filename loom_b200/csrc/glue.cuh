@@ -32,6 +32,7 @@ struct LbAttnParams {
     unsigned int* cnt;     // [M*heads], zero between launches
     int M, heads, kv_heads, hd, msl, splits;
     int max_chunk;         // positions one CTA may hold scores for (shared memory sizing)
+    int tile;              // positions per shared-memory tile (set by the launcher)
     unsigned long long* trace;
     int* status;           // device status word for bounded waits
     int debug;             // timing experiments only (results are wrong when non-zero)
