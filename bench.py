@@ -656,7 +656,7 @@ def main():
     tern_b, kv_b, head_b = algorithmic_bytes(shape, ctx_mid)
     per_launch, gemv_us, gemv_launches = gemv_roofline(ctx, torch, weights, shape)
     achieved = per_launch / gemv_us / 1e3  # GB/s
-    launches_per_token = shape["layers"] * 6 + 4  # 6 per block + embed + head + position + argmax
+    launches_per_token = shape["layers"] * 5 + 4  # 5 per block (RoPE is folded into attention) + embed + head + position + argmax
     line = {
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * dev_s / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

@@ -94,6 +94,7 @@ void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
  * 2 = whole strips per CTA; "pdl" 0/1 = programmatic dependent launch; "tp_graph" 0/1 = record the
  * tensor-parallel decode step, collectives included, as a graph; "gemm_tile" 0 / 128 / 256 = tokens per CTA of the
  * token-block GEMM (0 = choose); "gemm_splitk" 0/1 = let several CTAs share the K range of an output tile;
+ * "fold_rope" 0/1 = one-token decoder steps apply RoPE inside the attention kernel (one launch less per block);
  * "decode_splits" 0..32 = position splits of the one-token attention, read by loom_b200_decoder_create (0 = choose); "tp_peer" 0/1 = use the peer mailboxes when attached;
  * "prefill_gemm" 0/1 = prompts of 32 or more tokens
  * run their projections as token-block GEMMs on the tensor cores (1) or eight tokens at a time through the GEMV (0).  Results never depend on them

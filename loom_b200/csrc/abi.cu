@@ -365,6 +365,8 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
         ctx->opt_debug = value;
     } else if (!strcmp(key, "pdl")) {
         ctx->opt_pdl = value != 0;
+    } else if (!strcmp(key, "fold_rope")) {
+        ctx->opt_fold_rope = value != 0;
     } else if (!strcmp(key, "decode_splits")) {
         if (value < 0 || value > 32) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "ctx_set_option: decode_splits is 0..32");
         ctx->opt_decode_splits = value;

@@ -75,6 +75,7 @@ struct loom_b200_ctx {
     bool capturing = false;        // between graph_begin and graph_end
     // tensor parallelism (tp.cu): rank and world size of this context's group; the NCCL communicator or null
     int tp_rank = 0, tp_world = 1;
+    int opt_fold_rope = 1;         // one-token decoder steps rotate q and the newest K row inside the attention kernel
     int opt_decode_splits = 0;     // position splits of the one-token attention (0 = choose from the SM count)
     int opt_gemm_splitk = 1;       // split the K range of the GEMM over several CTAs when there are few output tiles
     int opt_gemm_tile = 0;         // tokens per CTA of the GEMM: 0 = choose, 128 or 256 = force

@@ -236,6 +236,7 @@ int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int 
         a.residual = dec->x;
         a.M = M;
         a.splits = splits;
+        a.fold_rope = M == 1;
         if (int rc = lb_mha_step_dev(&b.mha, a)) return rc;
         LbSwigluArgs s = {};
         s.gate = b.gate;
@@ -634,7 +635,8 @@ int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, in
         metrics->decode_device_seconds = ms * 1e-3;
         metrics->prefill_tokens = n_prompt;
         metrics->generated_tokens = max_new;
-        metrics->launches_per_token = max_new > 0 ? (double)(dec->blocks.size() * 6 + 4) : 0.0;
+        // per block: QKV, (RoPE unless folded into attention), attention, O, gate/up, down; + embed, head, position, argmax
+        metrics->launches_per_token = max_new > 0 ? (double)(dec->blocks.size() * (ctx->opt_fold_rope ? 5 : 6) + 4) : 0.0;
         (void)launches0;
     }
     return 0;

@@ -171,6 +171,18 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     const double scale = __ddiv_rn(1.0, sqrt((double)hd));
     for (int d = tid; d < hd; d += kAttnThreads) sq[d] = p.q[(size_t)n * qd + (size_t)h * hd + d];
     __syncthreads();
+    // RoPE folded in (one-token steps): thread d < hd/2 owns the pair (d, d + hd/2) of the query and of the newest K row
+    const bool fold_rope = p.rope_div != nullptr;
+    double rsn = 0.0, rc = 1.0;
+    if (fold_rope) {
+        if (tid < hd / 2) {
+            sincos(__ddiv_rn((double)last, p.rope_div[tid]), &rsn, &rc);
+            const double v0 = sq[tid], v1 = sq[tid + hd / 2];
+            sq[tid] = __dsub_rn(__dmul_rn(v0, rc), __dmul_rn(v1, rsn));
+            sq[tid + hd / 2] = __dadd_rn(__dmul_rn(v0, rsn), __dmul_rn(v1, rc));
+        }
+        __syncthreads();
+    }
 
     // scores: thread pair (2j, 2j+1) handles position j of the tile, each over half of the dimensions
     double mx = -1e9;
@@ -186,6 +198,24 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
             }
         }
         if (!failed && !lb_mbar_wait_bounded(&bars[0], (uint32_t)(t & 1))) failed = true;
+        if (fold_rope && last >= k0 + base && last < k0 + base + rows) {
+            // the newest position is in this tile: its ring row is not written yet; take the unrotated row from k_new,
+            // rotate it into the tile, and (one CTA per KV head) into the ring
+            if (tid < hd / 2) {
+                const double v0 = (double)p.k_new[(size_t)kvh * hd + tid], v1 = (double)p.k_new[(size_t)kvh * hd + tid + hd / 2];
+                const float r0 = (float)__dsub_rn(__dmul_rn(v0, rc), __dmul_rn(v1, rsn));
+                const float r1 = (float)__dadd_rn(__dmul_rn(v0, rsn), __dmul_rn(v1, rc));
+                float* trow = kt + (size_t)(last - k0 - base) * rowf;
+                trow[tid] = r0;
+                trow[tid + hd / 2] = r1;
+                if (h % (p.heads / p.kv_heads) == 0) {
+                    float* grow = p.cache_k_w + (size_t)(last % p.msl) * kvd + (size_t)kvh * hd;
+                    grow[tid] = r0;
+                    grow[tid + hd / 2] = r1;
+                }
+            }
+            __syncthreads();
+        }
         for (int j0 = 0; j0 < rows; j0 += kAttnThreads / 2) {
             const int j = j0 + (tid >> 1);
             double dot = 0.0;

@@ -33,6 +33,12 @@ struct LbAttnParams {
     int M, heads, kv_heads, hd, msl, splits;
     int max_chunk;         // positions one CTA may hold scores for (shared memory sizing)
     int tile;              // positions per shared-memory tile (set by the launcher)
+    // One-token steps without q/k norm can fold RoPE in (one launch less per block): q arrives unrotated, the newest K
+    // row arrives unrotated in k_new [kv_heads*hd] instead of the ring, and the kernel rotates both (same arithmetic as
+    // lb_rope_kernel) and stores the rotated K row into the ring for later steps.  rope_div == null: plain attention.
+    const double* rope_div;
+    const float* k_new;
+    float* cache_k_w;
     unsigned long long* trace;
     int* status;           // device status word for bounded waits
     int debug;             // timing experiments only (results are wrong when non-zero)

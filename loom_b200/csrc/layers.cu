@@ -79,6 +79,7 @@ int lb_mha_alloc(loom_b200_ctx* ctx, loom_b200_mha* m, int max_splits) {
     LB_CUDA(ctx, cudaMalloc(&m->part, lb_attn_part_elems(kChunkTokens, m->heads, m->head_dim, max_splits) * sizeof(double)));
     LB_CUDA(ctx, cudaMalloc(&m->cnt, (size_t)kChunkTokens * m->heads * sizeof(unsigned int)));
     LB_CUDA(ctx, cudaMemsetAsync(m->cnt, 0, (size_t)kChunkTokens * m->heads * sizeof(unsigned int), ctx->stream));
+    LB_CUDA(ctx, cudaMalloc(&m->k_new, (size_t)m->kv_dim * sizeof(float)));
     LB_CUDA(ctx, cudaMalloc(&m->pos_dev, sizeof(int)));
     LB_CUDA(ctx, cudaMemsetAsync(m->pos_dev, 0, sizeof(int), ctx->stream));
     // pow(theta, 2d/hd) in double on the host: the same libm call the CPU path makes once per use
@@ -94,7 +95,7 @@ int lb_mha_alloc(loom_b200_ctx* ctx, loom_b200_mha* m, int max_splits) {
 
 void lb_mha_release(loom_b200_mha* m) {
     void* ptrs[] = {m->bq, m->bk, m->bv, m->bo, m->q_norm, m->k_norm, m->inner, m->cache_k, m->cache_v,
-                    m->rope_div, m->q, m->attn, m->part, m->cnt, m->pos_dev};
+                    m->rope_div, m->q, m->attn, m->part, m->cnt, m->pos_dev, m->k_new};
     for (void* p : ptrs)
         if (p) cudaFree(p);
 }
@@ -107,8 +108,13 @@ int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     fill_seg(p.seg[0], m->wq, m->bq, m->q);
     fill_seg(p.seg[1], m->wk, m->bk, m->cache_k);
     fill_seg(p.seg[2], m->wv, m->bv, m->cache_v);
+    const bool fold_rope = a.fold_rope && a.M == 1 && !m->q_norm && !m->k_norm && ctx->opt_fold_rope;
     p.seg[1].out_ring = m->msl;
     p.seg[2].out_ring = m->msl;
+    if (fold_rope) {  // the unrotated K row goes to a side buffer; the attention kernel rotates it into the ring
+        p.seg[1].out = m->k_new;
+        p.seg[1].out_ring = 0;
+    }
     p.K = m->d_model;
     p.M = a.M;
     p.pro = a.pro_mode;
@@ -137,7 +143,8 @@ int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     r.kv_heads = m->kv_heads;
     r.hd = m->head_dim;
     r.msl = m->msl;
-    if (int rc = lb_launch_rope(ctx, r)) return rc;
+    if (!fold_rope)
+        if (int rc = lb_launch_rope(ctx, r)) return rc;
 
     LbAttnParams t = {};
     t.q = m->q;
@@ -154,6 +161,11 @@ int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     t.msl = m->msl;
     t.splits = a.splits < 1 ? 1 : (a.splits > m->splits ? m->splits : a.splits);
     t.max_chunk = (m->msl + t.splits - 1) / t.splits;
+    if (fold_rope) {
+        t.rope_div = m->rope_div;
+        t.k_new = m->k_new;
+        t.cache_k_w = m->cache_k;
+    }
     if (int rc = lb_launch_attention(ctx, t)) return rc;
 
     if (m->q_dim_global > 0 && ctx->tp_world > 1) {

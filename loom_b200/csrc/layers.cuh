@@ -50,6 +50,7 @@ struct loom_b200_mha {
     unsigned int* cnt = nullptr;
     int* pos_dev = nullptr;
     int splits = 1, max_total = 0;
+    float* k_new = nullptr;                        // [kv_dim] the newest K row before RoPE (one-token steps with RoPE folded into attention)
     // tensor parallelism: > 0 when this object holds heads/world heads (wq/wk/wv row slices, wo a column slice);
     // the value is the unsharded heads*head_dim.  Scratch as for the SwiGLU arguments, borrowed from the decoder.
     int q_dim_global = 0;
@@ -67,6 +68,7 @@ struct LbMhaStepArgs {
     const float* residual;  // optional, may alias out
     int M;
     int splits;           // attention splits along positions
+    bool fold_rope;       // one-token step: let the attention kernel rotate q and the newest K row (no q/k norm only)
 };
 // One chunk (M <= 8 tokens at positions *pos_dev ...): QKV -> q/k norm + RoPE -> attention -> inner norm -> O.
 // Does not advance pos_dev.
