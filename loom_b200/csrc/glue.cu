@@ -483,27 +483,33 @@ __global__ void lb_add_scalar_kernel(int* p, int delta) {
 // into shared memory (64 positions, one 512-byte bulk copy per row) serves all of them.  Scores, the running
 // softmax (maximum, sum, rescaling of the partial output when the maximum moves) and the weighted V sum are float64
 // like the reference's loops (poly/mha.go:296-356); only the order of the float64 additions differs.
-// A tile arrives as float32 in a staging buffer and is widened to float64 once, into a buffer K and V take turns
-// in: converting inside the products would repeat every conversion sixteen times, and float32 -> float64 conversions
-// issue on the float64 pipe at a fraction of the FMA rate (they held the first version at 39 % FMA-pipe use).
-// Threads form a 16 x 16 grid: thread (ty, tx) owns score rows ty+16i and key columns tx+16j, and output rows
-// ty+16i, dimensions tx+16j.
+// A tile arrives as float32 in a staging buffer and is widened to float64 once, into a buffer K and V take turns in.
+// Both products run on the float64 tensor-core MMA (mma.sync m8n8k4: 256 FMAs per instruction at the same peak as
+// scalar FMAs, measured 63.9 FMA/clk/SM, but a quarter of the shared-memory traffic and an eighth of the issue
+// slots): warp w owns score rows 16*(w/2).. and key columns 32*(w%2).., then output rows 16*(w/2).. and the
+// dimensions of half w%2.  Row strides are chosen so that a fragment load touches every bank once.
 constexpr int kPfRows = 64, kPfKeys = 64, kPfThreads = 256;
+
+__device__ __forceinline__ void dmma_884(double (&c)[2], double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};" : "+d"(c[0]), "+d"(c[1]) : "d"(a), "d"(b));
+}
 
 __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(const LbAttnParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar;
     __shared__ double s_m[kPfRows], s_l[kPfRows], s_alpha[kPfRows];
     __shared__ int s_qpos[kPfRows];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, ty = tid >> 4, tx = tid & 15;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hd = p.hd, kvd = p.kv_heads * hd, qd = p.heads * hd;
     const int group = p.heads / p.kv_heads, TQ = kPfRows / group;
     const int kvh = blockIdx.x, qt = (int)gridDim.y - 1 - (int)blockIdx.y;  // long rows first
     const int tok0 = qt * TQ;
-    const int dstride = hd + 2, rowf = hd + 4, sstride = kPfKeys + 1;
-    double* Qs = reinterpret_cast<double*>(smem_raw);                      // [64, hd+2] queries
-    double* KV = Qs + (size_t)kPfRows * dstride;                           // [64, hd+2] the K tile, then the V tile, as float64
-    double* Ss = KV + (size_t)kPfKeys * dstride;                           // [64, 65] scores, then softmax weights
+    // row strides in elements: +4 doubles (32 B) puts the 8 rows x 4 k of an A or K fragment on 32 distinct banks,
+    // +8 doubles (64 B) does the same for the 4 keys x 8 dimensions of a V fragment
+    const int qstride = hd + 4, kstride = hd + 4, vstride = hd + 8, rowf = hd + 4, sstride = kPfKeys + 4;
+    double* Qs = reinterpret_cast<double*>(smem_raw);                      // [64, hd+4] queries
+    double* KV = Qs + (size_t)kPfRows * qstride;                           // [64, hd+8] the K tile, then the V tile, as float64
+    double* Ss = KV + (size_t)kPfKeys * vstride;                           // [64, 68] scores, then softmax weights
     float* stage = reinterpret_cast<float*>(Ss + (size_t)kPfRows * sstride);  // [64, hd+4] float32 tile as copied
     if (tid == 0) {
         lb_mbar_init(&bar, 1);
@@ -526,7 +532,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
         const int hi = r / TQ, ti = r - hi * TQ;
         double v = 0.0;
         if (ti < ntok) v = p.q[(size_t)(tok0 + ti) * qd + (size_t)(kvh * group + hi) * hd + d];
-        Qs[(size_t)r * dstride + d] = v;
+        Qs[(size_t)r * qstride + d] = v;
     }
     if (tid < kPfRows) {
         const int ti = tid % TQ;
@@ -536,23 +542,28 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
     }
     __syncthreads();
     const double scale = __ddiv_rn(1.0, sqrt((double)hd));
-    double o[4][8];
+    // fragment coordinates: an m8n8k4 A fragment is A[lane/4][lane%4], B is B[lane%4][lane/4], C is C[lane/4][2*(lane%4) + {0,1}]
+    const int g = lane >> 2, t4 = lane & 3;
+    const int wr = (warp >> 1) * 16;          // first score / output row of this warp
+    const int wc = (warp & 1) * 32;           // first key column of this warp's scores
+    const int wd = (warp & 1) * (hd / 2);     // first output dimension of this warp
+    const int nfr = hd / 16;                  // 8-dimension fragments per warp (8 for head_dim 128)
+    double o[2][8][2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[i][j] = 0.0;
-    const int ndim = hd / 16;  // output dimensions per thread (8 for head_dim 128)
+        for (int j = 0; j < 8; ++j) o[i][j][0] = o[i][j][1] = 0.0;
     bool failed = false;
     uint32_t phase = 0;
-    // staging (float32, rows of hd+4) -> KV (float64, rows of hd+2); rows beyond `rows` become zero
-    auto widen = [&](int rows) {
+    // staging (float32, rows of hd+4) -> KV (float64, rows of `stride`); rows beyond `rows` become zero
+    auto widen = [&](int rows, int stride) {
         if (p.debug == 12) return;
         const int quads = hd / 4;
         for (int idx = tid; idx < kPfKeys * quads; idx += kPfThreads) {
             const int r = idx / quads, c = (idx - r * quads) * 4;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (r < rows) v = *reinterpret_cast<const float4*>(stage + (size_t)r * rowf + c);
-            double2* dst = reinterpret_cast<double2*>(KV + (size_t)r * dstride + c);
+            double2* dst = reinterpret_cast<double2*>(KV + (size_t)r * stride + c);
             dst[0] = make_double2((double)v.x, (double)v.y);
             dst[1] = make_double2((double)v.z, (double)v.w);
         }
@@ -563,37 +574,40 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
         // ---- K tile: wait, widen, then the staging buffer is free for the V tile of the same positions ----
         if (!failed && !lb_mbar_wait_bounded(&bar, phase)) failed = true;
         phase ^= 1;
-        widen(krows);
+        widen(krows, kstride);
         __syncthreads();
         if (warp == 0) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             attn_fetch_rows(stage, vbase, rowf, hd, kvd, p.msl, kpos0, krows, &bar, lane);
         }
-        // ---- scores of this tile ----
-        double acc[4][4];
+        // ---- scores of this tile: S[16 x 32 per warp] = Q[16 x hd] * K^T ----
+        {
+            double c[2][4][2];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 2; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
-#pragma unroll 2
-        for (int d = 0; d < (p.debug >= 10 ? 2 : hd); d += 2) {
-            double2 qv[4], kv[4];
+                for (int j = 0; j < 4; ++j) c[i][j][0] = c[i][j][1] = 0.0;
+            const double* qa = Qs + (size_t)(wr + g) * qstride + t4;
+            const double* kb = KV + (size_t)(wc + g) * kstride + t4;
+#pragma unroll 4
+            for (int d = 0; d < (p.debug >= 10 ? 4 : hd); d += 4) {
+                const double a0 = qa[d], a1 = qa[(size_t)8 * qstride + d];
+                double b[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const double2*>(Qs + (size_t)(ty + 16 * i) * dstride + d);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const double2*>(KV + (size_t)(tx + 16 * j) * dstride + d);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
+                for (int j = 0; j < 4; ++j) b[j] = kb[(size_t)(8 * j) * kstride + d];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[i][j] = fma(qv[i].x, kv[j].x, acc[i][j]);
-                    acc[i][j] = fma(qv[i].y, kv[j].y, acc[i][j]);
+                    dmma_884(c[0][j], a0, b[j]);
+                    dmma_884(c[1][j], a1, b[j]);
                 }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<double2*>(Ss + (size_t)(wr + 8 * i + g) * sstride + wc + 8 * j + 2 * t4) =
+                        make_double2(__dmul_rn(c[i][j][0], scale), __dmul_rn(c[i][j][1], scale));
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) Ss[(size_t)(ty + 16 * i) * sstride + tx + 16 * j] = __dmul_rn(acc[i][j], scale);
         __syncthreads();  // scores complete, the float64 K tile is free
         // ---- running softmax: four threads per row, sixteen keys each ----
         {
@@ -628,30 +642,35 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
         // ---- V tile: wait, widen into the buffer K just left, request the next K tile ----
         if (!failed && !lb_mbar_wait_bounded(&bar, phase)) failed = true;
         phase ^= 1;
-        widen(krows);
+        widen(krows, vstride);
         __syncthreads();  // weights, rescale factors and the float64 V tile visible; staging free
         if (t + 1 < ntiles && warp == 0) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             attn_fetch_rows(stage, kbase, rowf, hd, kvd, p.msl, kpos0 + kPfKeys, tile_rows(t + 1), &bar, lane);
         }
-        // ---- weighted V ----
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const double al = s_alpha[ty + 16 * i];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[i][j] = __dmul_rn(o[i][j], al);
-        }
-#pragma unroll 2
-        for (int k = 0; k < ((p.debug == 9 || p.debug >= 11) ? 1 : krows); ++k) {
-            double pw[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) pw[i] = Ss[(size_t)(ty + 16 * i) * sstride + k];
+        // ---- weighted V: O[16 x hd/2 per warp] = alpha * O + P[16 x 64] * V ----
+        {
+            const double al0 = s_alpha[wr + g], al1 = s_alpha[wr + 8 + g];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                if (j < ndim) {
-                    const double v = KV[(size_t)k * dstride + tx + 16 * j];
+                o[0][j][0] = __dmul_rn(o[0][j][0], al0);
+                o[0][j][1] = __dmul_rn(o[0][j][1], al0);
+                o[1][j][0] = __dmul_rn(o[1][j][0], al1);
+                o[1][j][1] = __dmul_rn(o[1][j][1], al1);
+            }
+            const double* pa = Ss + (size_t)(wr + g) * sstride + t4;
+            const double* vb = KV + (size_t)t4 * vstride + wd + g;
+            const int kend = (p.debug == 9 || p.debug >= 11) ? 4 : (krows + 3) & ~3;  // keys past krows carry zero weights and zero rows
+#pragma unroll 2
+            for (int k = 0; k < kend; k += 4) {
+                const double a0 = pa[k], a1 = pa[(size_t)8 * sstride + k];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) o[i][j] = fma(pw[i], v, o[i][j]);
+                for (int j = 0; j < 8; ++j) {
+                    if (j < nfr) {
+                        const double b = vb[(size_t)k * vstride + 8 * j];
+                        dmma_884(o[0][j], a0, b);
+                        dmma_884(o[1][j], a1, b);
+                    }
                 }
             }
         }
@@ -659,15 +678,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
     }
     if (failed && tid == 0) atomicExch(p.status, 1);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = ty + 16 * i;
+    for (int i = 0; i < 2; ++i) {
+        const int r = wr + 8 * i + g;
         const int hi = r / TQ, ti = r - hi * TQ;
         if (ti >= ntok) continue;
         const double den = s_l[r];
-        double* orow = p.out + (size_t)(tok0 + ti) * qd + (size_t)(kvh * group + hi) * hd;
+        double* orow = p.out + (size_t)(tok0 + ti) * qd + (size_t)(kvh * group + hi) * hd + wd + 2 * t4;
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-            if (j < ndim) orow[tx + 16 * j] = __ddiv_rn(o[i][j], den);
+            if (j < nfr) *reinterpret_cast<double2*>(orow + 8 * j) = make_double2(__ddiv_rn(o[i][j][0], den), __ddiv_rn(o[i][j][1], den));
     }
 }
 
@@ -743,10 +762,10 @@ int lb_launch_attention_prefill(loom_b200_ctx* ctx, const LbAttnParams& pin) {
     LB_REQUIRE(ctx, lb_attention_prefill_supported(p), "attention (prompt block): %d heads over %d kv heads of %d dimensions", p.heads,
                p.kv_heads, p.hd);
     const int TQ = kPfRows / (p.heads / p.kv_heads);
-    const size_t smem = (size_t)(kPfRows + kPfKeys) * (p.hd + 2) * sizeof(double) + (size_t)kPfRows * (kPfKeys + 1) * sizeof(double) +
-                        (size_t)kPfKeys * (p.hd + 4) * sizeof(float);
+    const size_t smem = (size_t)kPfRows * (p.hd + 4) * sizeof(double) + (size_t)kPfKeys * (p.hd + 8) * sizeof(double) +
+                        (size_t)kPfRows * (kPfKeys + 4) * sizeof(double) + (size_t)kPfKeys * (p.hd + 4) * sizeof(float);
     if (!(ctx->func_attr_mask & (1u << 26))) {
-        LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024));
         ctx->func_attr_mask |= 1u << 26;
     }
     LB_CUDA(ctx, launch_pdl(ctx, lb_attention_prefill_kernel, dim3(p.kv_heads, (p.M + TQ - 1) / TQ), dim3(kPfThreads), smem, p));
