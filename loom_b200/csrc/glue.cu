@@ -128,7 +128,7 @@ __device__ __forceinline__ void attn_fetch_rows(float* tile, const float* cache,
 __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttnParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ double red[32];
-    __shared__ double s_w[64];
+    __shared__ double s_w[64], s_ls[64];
     __shared__ __align__(8) uint64_t bars[2];
     __shared__ int s_last;
     const int h = blockIdx.x, n = blockIdx.y, sp = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -323,16 +323,28 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
         __syncthreads();
     }
     gm = red[0];
-    if (tid < p.splits) s_w[tid] = ls == 0.0 ? 0.0 : exp(__dsub_rn(ms, gm));
+    if (tid < p.splits) {
+        s_w[tid] = ls == 0.0 ? 0.0 : exp(__dsub_rn(ms, gm));
+        s_ls[tid] = ls;
+    }
     __syncthreads();
     for (int dd = tid; dd < hd; dd += kAttnThreads) {
         double num = 0.0, dn = 0.0;
-        for (int s = 0; s < p.splits; ++s) {
-            const double w = s_w[s];
-            if (w == 0.0) continue;  // an empty split
-            const double* ps = base + (size_t)s * (hd + 2);
-            num = fma(__ldcg(ps + 2 + dd), w, num);
-            dn = fma(__ldcg(ps + 1), w, dn);
+        // eight partial sums are requested before any is used: one L2 round trip per eight splits instead of one per split
+        for (int s0 = 0; s0 < p.splits; s0 += 8) {
+            double v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = s0 + k < p.splits ? __ldcg(base + (size_t)(s0 + k) * (hd + 2) + 2 + dd) : 0.0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (s0 + k < p.splits) {
+                    const double w = s_w[s0 + k];
+                    if (w != 0.0) {  // not an empty split
+                        num = fma(v[k], w, num);
+                        dn = fma(s_ls[s0 + k], w, dn);
+                    }
+                }
+            }
         }
         p.out[(size_t)n * qd + (size_t)h * hd + dd] = __ddiv_rn(num, dn);
     }
