@@ -151,11 +151,18 @@ __device__ __forceinline__ double lb_round_half_away(double x) {
     return fabs(d) >= 0.5 ? __dadd_rn(t, copysign(1.0, x)) : t;
 }
 
-// bitNetQuantizedActivation: int8(clamp(Round(float64(v) * (127/float64(amax))), -128, 127))
+// bitNetQuantizedActivation: int8(clamp(Round(float64(v) * (127/float64(amax))), -128, 127)), Round = half away from
+// zero.  Without conversion instructions: |r| + 2^52 rounds to the nearest integer (ties to even) in the low mantissa
+// bits; a tie that went to the even integer below is the only case where half-away differs, and |r| - n == 0.5 finds
+// it exactly.  Sign and clamp are applied to the integer.
 __device__ __forceinline__ int lb_quant_i8(double v, double s) {
-    double r = lb_round_half_away(__dmul_rn(v, s));
-    r = fmin(fmax(r, -128.0), 127.0);
-    return (int)r;
+    const double r = __dmul_rn(v, s);
+    const double a = fmin(fabs(r), 1048576.0);
+    const double magic = 4503599627370496.0;  // 2^52
+    const double u = __dadd_rn(a, magic);
+    int n = __double2loint(u);
+    if (__dsub_rn(a, __dsub_rn(u, magic)) == 0.5) n += 1;
+    return r < 0.0 ? -(n < 128 ? n : 128) : (n < 127 ? n : 127);
 }
 
 // a / b with the reciprocal r = RN(1/b) computed once by the caller: q0 = RN(a*r), the exact remainder

@@ -44,6 +44,7 @@ struct Smem {
     int* flag;        // [4]
     uint64_t* bars;   // [kWarps*kStages]
     void* stage;      // K floats (doubles for fp64 input) of prologue staging, or null
+    float* gain;      // norm_w copied before the dependency wait, or null
 };
 
 __device__ __forceinline__ const uint32_t* tile_ptr(const LbGemvParams& p, int v, int kb) {
@@ -107,6 +108,9 @@ __device__ __forceinline__ double pro_value(const void* row, int c, double stat,
 // buffer (loads of several units in flight), then normalisation, absmax and quantization run as short rolled
 // loops over 4-column units.  Code executed once per CTA is fetched cold, so the loops are kept small and
 // reused rather than unrolled; the four columns of a unit give the instruction-level parallelism.
+__device__ __forceinline__ double lb_wide(float v) { return (double)v; }
+__device__ __forceinline__ double lb_wide(double v) { return v; }
+
 template <int PRO>
 __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem& sm, int n, const void* row) {
     const int tid = threadIdx.x, K = p.K, units = K >> 2;
@@ -115,7 +119,7 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
     using VT = typename std::conditional<f64, double, float>::type;
     VT* tmp = reinterpret_cast<VT*>(sm.stage);
     const bool have_w = PRO != LB_PRO_F32 && p.norm_w != nullptr;
-    double ss = 0.0;
+    double ss = 0.0, md = 0.0;
     float m = 0.0f;
 #pragma unroll 4
     for (int idx = tid; idx < units; idx += kThreads) {
@@ -127,13 +131,14 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
             const float4 a = reinterpret_cast<const float4*>(row)[idx];
             a0 = (VT)a.x; a1 = (VT)a.y; a2 = (VT)a.z; a3 = (VT)a.w;
         }
-        if (have_w && 4 * idx < p.norm_w_len) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.norm_w + 4 * idx));
+        if (have_w && !sm.gain && 4 * idx < p.norm_w_len) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.norm_w + 4 * idx));
         tmp[4 * idx] = a0; tmp[4 * idx + 1] = a1; tmp[4 * idx + 2] = a2; tmp[4 * idx + 3] = a3;
         if (PRO >= LB_PRO_BLOCKNORM) {
-            ss = __dadd_rn(ss, __dmul_rn((double)a0, (double)a0));
-            ss = __dadd_rn(ss, __dmul_rn((double)a1, (double)a1));
-            ss = __dadd_rn(ss, __dmul_rn((double)a2, (double)a2));
-            ss = __dadd_rn(ss, __dmul_rn((double)a3, (double)a3));
+            const double d0 = lb_wide(a0), d1 = lb_wide(a1), d2 = lb_wide(a2), d3 = lb_wide(a3);
+            ss = __dadd_rn(ss, __dmul_rn(d0, d0));
+            ss = __dadd_rn(ss, __dmul_rn(d1, d1));
+            ss = __dadd_rn(ss, __dmul_rn(d2, d2));
+            ss = __dadd_rn(ss, __dmul_rn(d3, d3));
         } else {
             m = fmaxf(fmaxf(m, fabsf((float)a0)), fmaxf(fabsf((float)a1), fmaxf(fabsf((float)a2), fabsf((float)a3))));
         }
@@ -145,30 +150,33 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
         const double mean = __dadd_rn(__ddiv_rn(ss, (double)(p.norm_count > 0 ? p.norm_count : K)), p.eps);
         const double root = sqrt(mean);
         const double rr = __ddiv_rn(1.0, root);  // RN(1/rms): the inner norms' scale, the block norm's reciprocal
-#pragma unroll 1
+        const float* gw = sm.gain ? sm.gain : p.norm_w;  // the shared copy was made while waiting for the producer of the row
+#pragma unroll 2
         for (int idx = tid; idx < units; idx += kThreads) {
             double w[4] = {1.0, 1.0, 1.0, 1.0};
             if (have_w) {
                 if (4 * idx + 4 <= p.norm_w_len) {
-                    const float4 g = reinterpret_cast<const float4*>(p.norm_w)[idx];
+                    const float4 g = reinterpret_cast<const float4*>(gw)[idx];
                     w[0] = (double)g.x; w[1] = (double)g.y; w[2] = (double)g.z; w[3] = (double)g.w;
                 } else {
                     for (int k = 0; k < 4; ++k)
-                        if (4 * idx + k < p.norm_w_len) w[k] = (double)p.norm_w[4 * idx + k];
+                        if (4 * idx + k < p.norm_w_len) w[k] = (double)gw[4 * idx + k];
                 }
             }
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const double x = (double)tmp[4 * idx + k];
+                const double x = lb_wide(tmp[4 * idx + k]);
                 VT y;
                 if (PRO == LB_PRO_BLOCKNORM) y = (VT)(float)__dmul_rn(lb_div_by(x, root, rr), w[k]);
                 else if (f64) y = (VT)__dmul_rn(x, __dmul_rn(rr, w[k]));
                 else y = (VT)(float)__dmul_rn(__dmul_rn(x, rr), w[k]);
                 tmp[4 * idx + k] = y;
-                m = fmaxf(m, (float)fabs((double)y));
+                if (f64) md = fmax(md, fabs((double)y));  // one narrowing at the end: rounding is monotone
+                else m = fmaxf(m, fabsf((float)y));
             }
         }
     }
+    if (f64) m = fmaxf(m, (float)md);
     if (p.given_amax) m = p.given_amax[n];  // absmax over the whole sharded vector (already floored by the caller or below)
     else m = block_max(m, sm.red);
     const float amax = m < 1e-5f ? 1e-5f : m;
@@ -176,15 +184,20 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
     const bool side = blockIdx.x == 0;
     int local_sum = 0;
     uint8_t* abytes = reinterpret_cast<uint8_t*>(sm.acts + (size_t)n * stride32);
-#pragma unroll 1
+    // the output scales need a float64 division: the last threads (which own the fewest units) start it before their loop
+    if (tid >= kThreads - 3) {
+        const int sg = tid - (kThreads - 3);
+        sm.os[sg * kMaxM + n] = sg < p.nseg ? lb_output_scale(p.seg[sg].scale, amax) : 1.0;
+    }
+#pragma unroll 2
     for (int idx = tid; idx < (Kp >> 2); idx += kThreads) {
         int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
         if (idx < units) {
             const VT y0 = tmp[4 * idx], y1 = tmp[4 * idx + 1], y2 = tmp[4 * idx + 2], y3 = tmp[4 * idx + 3];
-            q0 = lb_quant_i8((double)y0, s);
-            q1 = lb_quant_i8((double)y1, s);
-            q2 = lb_quant_i8((double)y2, s);
-            q3 = lb_quant_i8((double)y3, s);
+            q0 = lb_quant_i8(lb_wide(y0), s);
+            q1 = lb_quant_i8(lb_wide(y1), s);
+            q2 = lb_quant_i8(lb_wide(y2), s);
+            q3 = lb_quant_i8(lb_wide(y3), s);
             local_sum += q0 + q1 + q2 + q3;
             if (side) {
                 if (p.q_out)
@@ -205,7 +218,6 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
     }
     local_sum = lb_warp_sum_i(local_sum);
     if ((tid & 31) == 0 && local_sum != 0) atomicAdd(&sm.xsum[n], local_sum);
-    if (tid < 3) sm.os[tid * kMaxM + n] = tid < p.nseg ? lb_output_scale(p.seg[tid].scale, amax) : 1.0;
     if (tid == 0) {
         sm.amax[n] = amax;
         if (side && p.amax_out) p.amax_out[n] = amax;

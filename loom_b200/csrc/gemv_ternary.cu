@@ -58,6 +58,8 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         sm.bars = reinterpret_cast<uint64_t*>(ptr);
         ptr += kWarps * kStages * 8;
         sm.stage = p.stage_bytes > 0 ? (void*)ptr : nullptr;
+        ptr += p.stage_bytes;
+        sm.gain = p.gain_bytes > 0 ? reinterpret_cast<float*>(ptr) : nullptr;
     }
 
     // ---- tile ranges --------------------------------------------------------------------------------
@@ -126,6 +128,12 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         advance(ic, len);
     }
 
+    // the norm gains are weights too: copy them while the producer of the activations is still running
+    if (sm.gain) {
+        const int n4 = p.norm_w_len >> 2;
+        for (int i = tid; i < n4; i += kThreads) reinterpret_cast<float4*>(sm.gain)[i] = __ldg(reinterpret_cast<const float4*>(p.norm_w) + i);
+        for (int i = (n4 << 2) + tid; i < p.norm_w_len; i += kThreads) sm.gain[i] = __ldg(p.norm_w + i);
+    }
     lb_pdl_launch_dependents();  // the next launch may start prefetching its weights
     LB_TRACE(1);
     lb_pdl_wait();               // everything below may read what earlier launches wrote
@@ -332,6 +340,7 @@ size_t gemv_smem_bytes(const LbGemvParams& p, int max_local) {
     b += (size_t)kWarps * kStages * 8;
     b = (b + 15) & ~(size_t)15;
     b += (size_t)p.stage_bytes;
+    b += (size_t)p.gain_bytes;
     return b;
 }
 
@@ -420,9 +429,15 @@ static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int* g
     }
     // prologue staging: the activation row in its input precision, when it fits beside the ring
     p.stage_bytes = 0;
+    p.gain_bytes = 0;
     if (p.pro != LB_PRO_Q8 && (p.K & 3) == 0) {
         size_t want = (size_t)p.K * (p.pro == LB_PRO_INNERNORM64 ? 8 : 4);
         if (gemv_smem_bytes(p, p.max_local_strips) + want <= 227 * 1024) p.stage_bytes = (int)want;
+    }
+    p.gain_bytes = 0;
+    if (p.stage_bytes > 0 && p.pro >= LB_PRO_BLOCKNORM && p.norm_w && p.norm_w_len > 0 && (((uintptr_t)p.norm_w) & 15) == 0) {
+        const size_t want = ((size_t)p.norm_w_len * 4 + 15) & ~(size_t)15;
+        if (gemv_smem_bytes(p, p.max_local_strips) + want <= 227 * 1024) p.gain_bytes = (int)want;
     }
     size_t smem = gemv_smem_bytes(p, p.max_local_strips);
     while (smem > 227 * 1024 && p.stages > 1) {  // wide inputs: a shallower ring before giving up

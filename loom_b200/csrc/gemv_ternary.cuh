@@ -55,6 +55,7 @@ struct LbGemvParams {
     int max_local_strips;
     int stages;       // ring stages per warp (1..3)
     int stage_bytes;  // shared staging for the fp32/fp64 prologues (0 = use the slow generic prologue)
+    int gain_bytes;   // shared copy of norm_w, made before the dependency wait (0 = read norm_w from global memory)
     int aligned;  // 1: CTAs own whole strip groups; 0: stream-K with the int32 fix-up
     // prologue
     int pro;

@@ -159,6 +159,7 @@ __global__ void __launch_bounds__(kThreads, 1) lb_stream_kernel(const __grid_con
         sm.bars = reinterpret_cast<uint64_t*>(ptr);
         ptr += kWarps * kPStagesMax * 8;
         sm.stage = sp.stage_bytes > 0 ? (void*)ptr : nullptr;
+        sm.gain = nullptr;  // the program reads norm gains from global memory
     }
     if (tid < kWarps * nstages) lb_mbar_init(&sm.bars[tid], 1);
     if (tid == 0) lb_fence_mbar_init();
