@@ -113,10 +113,13 @@ int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
         o = LbGemmOut{};
         o.act = LOOM_B200_ACT_LINEAR;
         o.bias = m.bk;
-        o.out = m.cache_k + (size_t)pos0 * m.kv_dim;  // ring rows pos0.. are contiguous: a prompt never wraps
+        o.out = m.cache_k;  // head-major ring: token t of the block goes to position pos0 + t of every KV head (a prompt never wraps)
+        o.kv_hd = m.head_dim;
+        o.kv_msl = m.msl;
+        o.kv_pos0 = pos0;
         if (int rc = lb_gemm_run(ctx, m.wk, M, o)) return rc;
         o.bias = m.bv;
-        o.out = m.cache_v + (size_t)pos0 * m.kv_dim;
+        o.out = m.cache_v;
         if (int rc = lb_gemm_run(ctx, m.wv, M, o)) return rc;
 
         LbRopeParams r = {};

@@ -54,6 +54,7 @@ struct GemmParams {
     double* out_f64;         // [tokens, rows] float64 value before rounding (the attention query), or null
     float* pre_out;          // [tokens, rows] value before the activation, or null
     int32_t* acc_out;        // [tokens, rows] or null
+    int kv_hd, kv_msl, kv_pos0;  // kv_hd > 0: `out` is a head-major KV ring [rows/kv_hd][kv_msl][kv_hd], token t goes to position kv_pos0 + t
     int* status;
     int32_t* part_acc;       // split-K: [tokens, rows] partial sums, zero between launches
     unsigned int* part_cnt;  // split-K: arrivals per (row tile, token tile), zero between launches
@@ -228,22 +229,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
             }
             if (row_ok && !failed) {
                 const int ntok = p.tokens - (tok0 + c0);  // columns of this step that are real tokens
-                const size_t o0 = (size_t)(tok0 + c0) * p.rows + r;
+                size_t o0 = (size_t)(tok0 + c0) * p.rows + r, ostride = (size_t)p.rows;
+                if (p.kv_hd > 0) {
+                    o0 = ((size_t)(r / p.kv_hd) * p.kv_msl + p.kv_pos0 + tok0 + c0) * p.kv_hd + r % p.kv_hd;
+                    ostride = (size_t)p.kv_hd;
+                }
                 if (p.acc_out) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (j < ntok) p.acc_out[o0 + (size_t)j * p.rows] = acc[j];
+                        if (j < ntok) p.acc_out[o0 + j * ostride] = acc[j];
                 }
                 if (p.out_f64) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (j < ntok) p.out_f64[o0 + (size_t)j * p.rows] = y[j];
+                        if (j < ntok) p.out_f64[o0 + j * ostride] = y[j];
                 }
                 if (p.out) {
                     if (p.pre_out) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            if (j < ntok) p.pre_out[o0 + (size_t)j * p.rows] = f[j];
+                            if (j < ntok) p.pre_out[o0 + j * ostride] = f[j];
                     }
                     if (p.act != LOOM_B200_ACT_LINEAR) {
 #pragma unroll
@@ -256,13 +261,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
                     if (p.residual) {
                         float rs[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) rs[j] = j < ntok ? p.residual[o0 + (size_t)j * p.rows] : 0.f;
+                        for (int j = 0; j < 16; ++j) rs[j] = j < ntok ? p.residual[o0 + j * ostride] : 0.f;
 #pragma unroll
                         for (int j = 0; j < 16; ++j) f[j] = __fadd_rn(f[j], rs[j]);
                     }
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (j < ntok) p.out[o0 + (size_t)j * p.rows] = f[j];
+                        if (j < ntok) p.out[o0 + j * ostride] = f[j];
                 }
             }
         };
@@ -546,6 +551,9 @@ int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const
     p.out_f64 = o.out_f64;
     p.pre_out = o.pre_out;
     p.acc_out = o.acc_out;
+    p.kv_hd = o.kv_hd;
+    p.kv_msl = o.kv_msl;
+    p.kv_pos0 = o.kv_pos0;
     p.status = ctx->status_dev;
     p.debug = ctx->opt_debug;
     // phase trace: one row for the kernel and one per k-slice, kept contiguous (skipped if the ring of rows would wrap)

@@ -334,7 +334,11 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
 __device__ __noinline__ float activate_slow(float v, int act) { return lb_activate(v, act); }
 
 __device__ __forceinline__ size_t out_index(const LbGemvParams& p, const LbGemvSeg& sg, int n, int r) {
-    if (sg.out_ring > 0) return (size_t)((*p.pos_ptr + n) % sg.out_ring) * sg.rows + r;
+    if (sg.out_ring > 0) {
+        const int pos = (*p.pos_ptr + n) % sg.out_ring;
+        if (sg.ring_hd > 0) return ((size_t)(r / sg.ring_hd) * sg.out_ring + pos) * sg.ring_hd + r % sg.ring_hd;  // head-major KV ring
+        return (size_t)pos * sg.rows + r;
+    }
     return (size_t)n * sg.rows + r;
 }
 

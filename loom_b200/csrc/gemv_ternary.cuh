@@ -38,6 +38,7 @@ struct LbGemvSeg {
     int vstrip0;            // first virtual strip (concatenated order)
     float scale;
     int kind;
+    int ring_hd;            // with out_ring: the ring is head-major [rows/ring_hd][out_ring][ring_hd] (0 = position-major rows)
     int out_ring;  // > 0: token n goes to row (*pos_ptr + n) % out_ring of `out` (the KV ring), else row n
 };
 

@@ -63,7 +63,7 @@ __global__ void lb_rope_kernel(const LbRopeParams p) {
         v1 = qrow[d + half];
     } else {
         const int kh = h - p.heads;
-        krow = p.cache_k + (size_t)(pos % p.msl) * p.kv_heads * p.hd + (size_t)kh * p.hd;
+        krow = p.cache_k + ((size_t)kh * p.msl + (size_t)(pos % p.msl)) * p.hd;  // ring is head-major: [kv head][position][hd]
         v0 = (double)krow[d];
         v1 = (double)krow[d + half];
     }
@@ -117,12 +117,16 @@ __global__ void lb_rope_kernel(const LbRopeParams p) {
 constexpr int kAttnThreads = 256;
 constexpr int kAttnTile = 80;  // positions per shared-memory tile
 
-__device__ __forceinline__ void attn_fetch_rows(float* tile, const float* cache, int row_floats, int hd, int kvd, int msl,
-                                                int pos0, int rows, uint64_t* bar, int lane) {
-    if (lane == 0) lb_mbar_expect_tx(bar, (uint32_t)rows * hd * 4);
+// K or V rows of positions pos0 .. pos0+rows-1 of one KV head: the ring is head-major ([kv head][position][hd]), so
+// they are one contiguous block and ONE bulk copy brings them (the copy engine costs ~30 ns per copy whatever its
+// size: a copy per 512-byte row, as a position-major ring needs, made the loads the longest part of the kernel).
+// `head_ring` points at position 0 of the head; a chunk never wraps (positions stay below MaxSeqLen).
+__device__ __forceinline__ void attn_fetch_rows(float* tile, const float* head_ring, int hd, int pos0, int rows, uint64_t* bar, int lane) {
+    if (lane == 0) {
+        lb_mbar_expect_tx(bar, (uint32_t)rows * hd * 4);
+        lb_bulk_g2s(tile, head_ring + (size_t)pos0 * hd, (uint32_t)rows * hd * 4, bar);
+    }
     __syncwarp();
-    for (int r = lane; r < rows; r += 32)
-        lb_bulk_g2s(tile + (size_t)r * row_floats, cache + (size_t)((pos0 + r) % msl) * kvd, (uint32_t)hd * 4, bar);
 }
 
 __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttnParams p) {
@@ -133,7 +137,7 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     __shared__ int s_last;
     const int h = blockIdx.x, n = blockIdx.y, sp = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hd = p.hd, kvd = p.kv_heads * hd, qd = p.heads * hd;
-    const int rowf = hd + 4;  // padded row: conflict-free 16-byte reads down a column of rows
+    const int rowf = hd;      // tile rows are dense (one bulk copy per tile); the score loop staggers its start per position instead
     const int tile = p.tile;  // positions per shared-memory tile (at most kAttnTile)
     const int G = hd >= kAttnThreads ? 1 : kAttnThreads / hd;
     float* kt = reinterpret_cast<float*>(smem_raw);           // [tile, rowf]
@@ -158,15 +162,15 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     if (k1 > total) k1 = total;
     const int cnt = k1 > k0 ? k1 - k0 : 0;
     const int kvh = h / (p.heads / p.kv_heads);
-    const float* kbase = p.cache_k + (size_t)kvh * hd;
-    const float* vbase = p.cache_v + (size_t)kvh * hd;
+    const float* kbase = p.cache_k + (size_t)kvh * p.msl * hd;
+    const float* vbase = p.cache_v + (size_t)kvh * p.msl * hd;
     const int ntiles = (cnt + tile - 1) / tile;
     bool failed = false;
     // first K and V tiles: every row of both is requested before anything else happens
     if (cnt > 0) {
         const int rows0 = cnt < tile ? cnt : tile;
-        if (warp == 0) attn_fetch_rows(kt, kbase, rowf, hd, kvd, p.msl, k0, rows0, &bars[0], lane);
-        if (warp == 1) attn_fetch_rows(vt, vbase, rowf, hd, kvd, p.msl, k0, rows0, &bars[1], lane);
+        if (warp == 0) attn_fetch_rows(kt, kbase, hd, k0, rows0, &bars[0], lane);
+        if (warp == 1) attn_fetch_rows(vt, vbase, hd, k0, rows0, &bars[1], lane);
     }
     const double scale = __ddiv_rn(1.0, sqrt((double)hd));
     for (int d = tid; d < hd; d += kAttnThreads) sq[d] = p.q[(size_t)n * qd + (size_t)h * hd + d];
@@ -194,7 +198,7 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
             __syncthreads();  // everyone is done with the previous K tile
             if (warp == 0) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                attn_fetch_rows(kt, kbase, rowf, hd, kvd, p.msl, k0 + base, rows, &bars[0], lane);
+                attn_fetch_rows(kt, kbase, hd, k0 + base, rows, &bars[0], lane);
             }
         }
         if (!failed && !lb_mbar_wait_bounded(&bars[0], (uint32_t)(t & 1))) failed = true;
@@ -209,7 +213,7 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
                 trow[tid] = r0;
                 trow[tid + hd / 2] = r1;
                 if (h % (p.heads / p.kv_heads) == 0) {
-                    float* grow = p.cache_k_w + (size_t)(last % p.msl) * kvd + (size_t)kvh * hd;
+                    float* grow = p.cache_k_w + ((size_t)kvh * p.msl + (size_t)(last % p.msl)) * hd;
                     grow[tid] = r0;
                     grow[tid + hd / 2] = r1;
                 }
@@ -223,8 +227,12 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
                 const float* kr = kt + (size_t)j * rowf + half * hlen;
                 const double* qh = sq + half * hlen;
                 double d0 = 0.0, d1 = 0.0;
+                // rows are 512 B apart: starting every position four columns further keeps the 16-byte reads off each other's banks
+                const int rot = (4 * (tid >> 1)) % hlen;
 #pragma unroll 4
-                for (int d = 0; d < hlen; d += 4) {
+                for (int dd = 0; dd < hlen; dd += 4) {
+                    int d = dd + rot;
+                    if (d >= hlen) d -= hlen;
                     const float4 kv = *reinterpret_cast<const float4*>(kr + d);
                     d0 = fma(qh[d], (double)kv.x, d0);
                     d1 = fma(qh[d + 1], (double)kv.y, d1);
@@ -262,7 +270,7 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
             __syncthreads();
             if (warp == 1) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                attn_fetch_rows(vt, vbase, rowf, hd, kvd, p.msl, k0 + base, rows, &bars[1], lane);
+                attn_fetch_rows(vt, vbase, hd, k0 + base, rows, &bars[1], lane);
             }
         }
         if (!failed && !lb_mbar_wait_bounded(&bars[1], (uint32_t)(t & 1))) failed = true;
@@ -518,11 +526,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
     const int tok0 = qt * TQ;
     // row strides in elements: +4 doubles (32 B) puts the 8 rows x 4 k of an A or K fragment on 32 distinct banks,
     // +8 doubles (64 B) does the same for the 4 keys x 8 dimensions of a V fragment
-    const int qstride = hd + 4, kstride = hd + 4, vstride = hd + 8, rowf = hd + 4, sstride = kPfKeys + 4;
+    const int qstride = hd + 4, kstride = hd + 4, vstride = hd + 8, rowf = hd, sstride = kPfKeys + 4;
     double* Qs = reinterpret_cast<double*>(smem_raw);                      // [64, hd+4] queries
     double* KV = Qs + (size_t)kPfRows * qstride;                           // [64, hd+8] the K tile, then the V tile, as float64
     double* Ss = KV + (size_t)kPfKeys * vstride;                           // [64, 68] scores, then softmax weights
-    float* stage = reinterpret_cast<float*>(Ss + (size_t)kPfRows * sstride);  // [64, hd+4] float32 tile as copied
+    float* stage = reinterpret_cast<float*>(Ss + (size_t)kPfRows * sstride);  // [64, hd] float32 tile as copied
     if (tid == 0) {
         lb_mbar_init(&bar, 1);
         lb_fence_mbar_init();
@@ -534,10 +542,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
     const int ntok = p.M - tok0 < TQ ? p.M - tok0 : TQ;  // tokens of this tile
     const int max_pos = pos0 + tok0 + ntok - 1;
     const int ntiles = max_pos / kPfKeys + 1;
-    const float* kbase = p.cache_k + (size_t)kvh * hd;
-    const float* vbase = p.cache_v + (size_t)kvh * hd;
+    const float* kbase = p.cache_k + (size_t)kvh * p.msl * hd;
+    const float* vbase = p.cache_v + (size_t)kvh * p.msl * hd;
     auto tile_rows = [&](int t) { return max_pos + 1 - t * kPfKeys < kPfKeys ? max_pos + 1 - t * kPfKeys : kPfKeys; };
-    if (warp == 0) attn_fetch_rows(stage, kbase, rowf, hd, kvd, p.msl, 0, tile_rows(0), &bar, lane);
+    if (warp == 0) attn_fetch_rows(stage, kbase, hd, 0, tile_rows(0), &bar, lane);
     // query rows: row r = (head hi of the group, token ti); rows of absent tokens are zero and never written back
     for (int idx = tid; idx < kPfRows * hd; idx += kPfThreads) {
         const int r = idx / hd, d = idx - r * hd;
@@ -590,7 +598,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
         __syncthreads();
         if (warp == 0) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            attn_fetch_rows(stage, vbase, rowf, hd, kvd, p.msl, kpos0, krows, &bar, lane);
+            attn_fetch_rows(stage, vbase, hd, kpos0, krows, &bar, lane);
         }
         // ---- scores of this tile: S[16 x 32 per warp] = Q[16 x hd] * K^T ----
         {
@@ -658,7 +666,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
         __syncthreads();  // weights, rescale factors and the float64 V tile visible; staging free
         if (t + 1 < ntiles && warp == 0) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            attn_fetch_rows(stage, kbase, rowf, hd, kvd, p.msl, kpos0 + kPfKeys, tile_rows(t + 1), &bar, lane);
+            attn_fetch_rows(stage, kbase, hd, kpos0 + kPfKeys, tile_rows(t + 1), &bar, lane);
         }
         // ---- weighted V: O[16 x hd/2 per warp] = alpha * O + P[16 x 64] * V ----
         {
@@ -749,7 +757,7 @@ int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& pin) {
     p.tile = ((p.max_chunk + 1) / 2 + 7) / 8 * 8;  // half of the longest chunk: two tiles at most when the ring is full
     if (p.tile > kAttnTile) p.tile = kAttnTile;
     if (p.tile < 8) p.tile = 8;
-    size_t smem = (size_t)(p.hd + (size_t)G * p.hd + p.max_chunk) * sizeof(double) + 2 * (size_t)p.tile * (p.hd + 4) * sizeof(float);
+    size_t smem = (size_t)(p.hd + (size_t)G * p.hd + p.max_chunk) * sizeof(double) + 2 * (size_t)p.tile * p.hd * sizeof(float);
     if (smem > 200 * 1024) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "attention: %d positions per CTA need %zu B of shared memory", p.max_chunk, smem);
     if (smem > 48 * 1024 && !(ctx->func_attr_mask & (1u << 30))) {
         LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -775,7 +783,7 @@ int lb_launch_attention_prefill(loom_b200_ctx* ctx, const LbAttnParams& pin) {
                p.kv_heads, p.hd);
     const int TQ = kPfRows / (p.heads / p.kv_heads);
     const size_t smem = (size_t)kPfRows * (p.hd + 4) * sizeof(double) + (size_t)kPfKeys * (p.hd + 8) * sizeof(double) +
-                        (size_t)kPfRows * (kPfKeys + 4) * sizeof(double) + (size_t)kPfKeys * (p.hd + 4) * sizeof(float);
+                        (size_t)kPfRows * (kPfKeys + 4) * sizeof(double) + (size_t)kPfKeys * p.hd * sizeof(float);
     if (!(ctx->func_attr_mask & (1u << 26))) {
         LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024));
         ctx->func_attr_mask |= 1u << 26;

@@ -9,7 +9,7 @@ int lb_launch_embed(loom_b200_ctx* ctx, const float* emb, int vocab, int hidden,
 
 struct LbRopeParams {
     double* q;          // [M, heads*hd] fp64, rotated in place
-    float* cache_k;     // [msl, kv_heads*hd] fp32 ring; rows (pos0+n)%msl rotated in place
+    float* cache_k;     // [kv_heads, msl, hd] fp32 ring (head-major); rows (pos0+n)%msl of every head rotated in place
     const int* pos_ptr; // device scalar: position of token 0
     const double* rope_div;  // [hd/2] = pow(theta, 2d/hd), computed on the host in double
     const float* q_norm;     // per-head RMSNorm gains or null (poly/mha.go:285-290)
@@ -24,7 +24,7 @@ int lb_launch_rope(loom_b200_ctx* ctx, const LbRopeParams& p);
 
 struct LbAttnParams {
     const double* q;       // [M, heads*hd] after RoPE
-    const float* cache_k;  // [msl, kv_heads*hd]
+    const float* cache_k;  // [kv_heads, msl, hd]: head-major, so the positions of one head are contiguous
     const float* cache_v;
     const int* pos_ptr;
     double* out;           // [M, heads*hd] fp64 attention output (before the inner norm)

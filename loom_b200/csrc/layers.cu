@@ -111,6 +111,8 @@ int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     const bool fold_rope = a.fold_rope && a.M == 1 && !m->q_norm && !m->k_norm && ctx->opt_fold_rope;
     p.seg[1].out_ring = m->msl;
     p.seg[2].out_ring = m->msl;
+    p.seg[1].ring_hd = m->head_dim;
+    p.seg[2].ring_hd = m->head_dim;
     if (fold_rope) {  // the unrotated K row goes to a side buffer; the attention kernel rotates it into the ring
         p.seg[1].out = m->k_new;
         p.seg[1].out_ring = 0;
@@ -450,9 +452,19 @@ int loom_b200_mha_download_cache(loom_b200_mha* m, float* k_host, float* v_host)
     if (!m) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "mha_download_cache: layer is NULL");
     loom_b200_ctx* ctx = m->ctx;
     if (int rc = lb_set_device(ctx)) return rc;
-    const size_t cache = (size_t)m->msl * m->kv_dim * sizeof(float);
-    if (k_host) LB_CUDA(ctx, cudaMemcpyAsync(k_host, m->cache_k, cache, cudaMemcpyDeviceToHost, ctx->stream));
-    if (v_host) LB_CUDA(ctx, cudaMemcpyAsync(v_host, m->cache_v, cache, cudaMemcpyDeviceToHost, ctx->stream));
+    // the device ring is head-major [kv head][position][hd]; the caller gets the reference's [position][kv head * hd]
+    const size_t elems = (size_t)m->msl * m->kv_dim;
+    std::vector<float> tmp(elems);
+    for (int which = 0; which < 2; ++which) {
+        float* host = which == 0 ? k_host : v_host;
+        if (!host) continue;
+        LB_CUDA(ctx, cudaMemcpyAsync(tmp.data(), which == 0 ? m->cache_k : m->cache_v, elems * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+        LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        for (int h = 0; h < m->kv_heads; ++h)
+            for (int pos = 0; pos < m->msl; ++pos)
+                memcpy(host + (size_t)pos * m->kv_dim + (size_t)h * m->head_dim, tmp.data() + ((size_t)h * m->msl + pos) * m->head_dim,
+                       (size_t)m->head_dim * sizeof(float));
+    }
     LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return 0;
 }

@@ -107,6 +107,8 @@ struct LbGemmOut {
     double* out_f64;        // [tokens, rows] float64 (before rounding and activation) or null
     float* pre_out;         // [tokens, rows] value before the activation or null
     int32_t* acc_out;       // [tokens, rows] raw accumulators or null
+    // kv_hd > 0: `out` is a head-major KV ring [rows/kv_hd][kv_msl][kv_hd] and token t is written at position kv_pos0 + t
+    int kv_hd, kv_msl, kv_pos0;
 };
 int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a);
 int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const LbGemmOut& o);
