@@ -71,6 +71,10 @@ void loom_b200_ctx_destroy(loom_b200_ctx* ctx);
 /* FlushFrame + wait, poly/wgpu_context_native.go:276.  Also reports a bounded device-side wait that ran out since the
  * last sync (LOOM_B200_ERR_TIMEOUT; the results of the calls in between are invalid) and clears that condition. */
 int loom_b200_sync(loom_b200_ctx* ctx);
+/* Tensor-pipe micro-peak (no counterpart in the reference): one CTA per SM issues iters x 4 tcgen05.mma kind::i8
+ * instructions of M = 128, N = 256, K = 32 on operands resident in shared memory and reports dense int8 TOP/s.  The
+ * denominator for the GEMM's tensor roofline on the GPU at hand. */
+int loom_b200_selftest_i8_peak(loom_b200_ctx* ctx, int iters, double* tops_out);
 /* Failure-detection self-test (no counterpart in the reference): launches one thread that polls a flag nothing ever
  * sets, gives up after `polls` reads and raises the context's device status word, exactly as the bounded waits inside
  * the kernels do (tile copies, the GEMM pipeline, tensor-parallel peers).  Returns LOOM_B200_ERR_TIMEOUT through the

@@ -45,6 +45,7 @@ SIGNATURES = {
     "loom_b200_ctx_destroy": (None, [_vp]),
     "loom_b200_sync": (_i, [_vp]),
     "loom_b200_selftest_wait_timeout": (_i, [_vp, C.c_uint]),
+    "loom_b200_selftest_i8_peak": (_i, [_vp, _i, C.POINTER(_d)]),
     "loom_b200_ctx_stream": (_vp, [_vp]),
     "loom_b200_graph_begin": (_i, [_vp]),
     "loom_b200_graph_end": (_i, [_vp, C.POINTER(_vp)]),
@@ -222,6 +223,12 @@ class Context:
 
     def sync(self):
         self._check(lib().loom_b200_sync(self.h))
+
+    def i8_peak_tops(self, iters: int = 20000) -> float:
+        """Dense int8 TOP/s of back-to-back tcgen05 kind::i8 MMAs on operands resident in shared memory."""
+        t = _d(0.0)
+        self._check(lib().loom_b200_selftest_i8_peak(self.h, iters, C.byref(t)))
+        return t.value
 
     def selftest_wait_timeout(self, polls: int = 100000):
         """Makes a bounded device-side wait run out; raises LoomB200Error(LOOM_B200_ERR_TIMEOUT)."""

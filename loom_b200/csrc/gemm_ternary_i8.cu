@@ -364,6 +364,50 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
     if (tr && tid == 0) tr[4] = lb_gtime();
 }
 
+// Measures what the tensor pipe can do on this shape of instruction: one CTA per SM, operands resident in shared memory
+// (zeros), one thread issuing `iters` x 4 MMAs of M = 128, N = 256, K = 32 into one TMEM accumulator.  No loads, no
+// expansion, no epilogue: the number the GEMM's tensor-pipe fraction is quoted against.
+__global__ void __launch_bounds__(128, 1) lb_i8_peak_kernel(int iters, int* status) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t done_bar;
+    __shared__ uint32_t tmem_base_s;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < (kSliceBytesA + 256 * kSliceK) / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (tid == 0) {
+        lb_mbar_init(&done_bar, 1);
+        lb_fence_mbar_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lb_smem_u32(&tmem_base_s)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    if (warp == 0) {
+        const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(kRowsPerCta >> 4) << 24);
+        if (lane == 0) {
+            const uint32_t a_addr = lb_smem_u32(smem), b_addr = lb_smem_u32(smem + kSliceBytesA);
+            for (int it = 0; it < iters; ++it) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) mma_i8(tmem_base, smem_desc(a_addr + k * 256), smem_desc(b_addr + k * 256), idesc, (it > 0 || k > 0) ? 1u : 0u);
+            }
+            mma_commit(&done_bar);
+        }
+        __syncwarp();
+        if (!wait_bounded(&done_bar, 0) && lane == 0) atomicExch(status, 3);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+    }
+}
+
 // Quantizer of the GEMM path: the GEMV prologues' arithmetic (plain absmax, or a block / inner RMSNorm first).  The
 // output is laid out for the tensor core: [token/8][Kp/16][token%8][16 bytes], the bytes of every 16-column group in
 // the order the A expansion produces (position 4j+b holds column 4b+j); columns up to Kp and tokens up to the padded
@@ -613,6 +657,30 @@ int lb_gemm_gate_product(loom_b200_ctx* ctx, const int32_t* acc_g, const int32_t
                                                                                       scale_g, scale_u, bias_g, bias_u, act, prod);
     LB_CHECK_LAUNCH(ctx, "lb_gate_product_acc_kernel");
     ctx->launches++;
+    return 0;
+}
+
+extern "C" int loom_b200_selftest_i8_peak(loom_b200_ctx* ctx, int iters, double* tops_out) {
+    if (!ctx) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "selftest_i8_peak: ctx is NULL");
+    LB_REQUIRE(ctx, iters >= 1 && iters <= 1000000 && tops_out, "selftest_i8_peak: bad arguments");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "selftest_i8_peak cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    const size_t smem = kSliceBytesA + 256 * kSliceK + 1024;
+    LB_CUDA(ctx, cudaFuncSetAttribute(lb_i8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaEvent_t e0, e1;
+    LB_CUDA(ctx, cudaEventCreate(&e0));
+    LB_CUDA(ctx, cudaEventCreate(&e1));
+    lb_i8_peak_kernel<<<ctx->sm_count, 128, smem, ctx->stream>>>(iters / 8 + 1, ctx->status_dev);  // warm-up
+    LB_CUDA(ctx, cudaEventRecord(e0, ctx->stream));
+    lb_i8_peak_kernel<<<ctx->sm_count, 128, smem, ctx->stream>>>(iters, ctx->status_dev);
+    LB_CUDA(ctx, cudaEventRecord(e1, ctx->stream));
+    LB_CHECK_LAUNCH(ctx, "lb_i8_peak_kernel");
+    if (int rc = lb_sync_checked(ctx)) return rc;
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *tops_out = 2.0 * 128.0 * 256.0 * 32.0 * 4.0 * (double)iters * ctx->sm_count / ((double)ms * 1e-3) / 1e12;
     return 0;
 }
 

@@ -81,3 +81,10 @@ def test_gemm_split_k(ctx, rows, cols, tokens):
 @pytest.mark.parametrize("rows,cols", [(6912, 2560), (2560, 6912)])
 def test_gemm_prefill_config(ctx, rows, cols):
     run_case(ctx, rows, cols, 512, 7, bias=False, residual=True)
+
+
+def test_i8_micro_peak_is_plausible(ctx):
+    # the denominator of the GEMM's tensor roofline: dense int8 on tcgen05 with nothing but MMAs in flight.  The B200's
+    # nominal figure is 4,500 TOP/s; anything below 1,000 or above 6,000 means the measurement, not the GPU, is off
+    tops = ctx.i8_peak_tops(5000)
+    assert 1000.0 < tops < 6000.0, tops
