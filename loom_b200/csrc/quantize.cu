@@ -204,6 +204,15 @@ int loom_b200_quantize_activation(loom_b200_ctx* ctx, int batch, int in, const f
     if (batch == 0) return 0;
     LB_REQUIRE(ctx, x && q && amax, "quantize_activation: NULL buffer");
     if (int rc = lb_set_device(ctx)) return rc;
+    // wide rows: the 1024-thread kernel with vector loads (same operations per element, same bytes out)
+    if (in >= 2048 && (in & 3) == 0 && (((uintptr_t)x) & 15) == 0 && (((uintptr_t)q) & 3) == 0) {
+        LbGemvParams p = {};
+        p.pro = LB_PRO_F32;
+        p.x = x;
+        p.K = in;
+        p.M = batch;
+        return lb_launch_norm_quantize(ctx, p, q, amax);
+    }
     lb_quantize_kernel<float><<<batch, kThreads, 0, ctx->stream>>>(x, in, q, amax);
     LB_CHECK_LAUNCH(ctx, "lb_quantize_kernel<float>");
     return 0;
