@@ -101,8 +101,7 @@ void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
  * "fold_rope" 0/1 = one-token decoder steps apply RoPE inside the attention kernel (one launch less per block);
  * "decode_splits" 0..32 = position splits of the one-token attention, read by loom_b200_decoder_create (0 = choose); "tp_peer" 0/1 = use the peer mailboxes when attached;
  * "prefill_gemm" 0/1 = prompts of 32 or more tokens
- * run their projections as token-block GEMMs on the tensor cores (1) or eight tokens at a time through the GEMV (0).  Results never depend on them
- * ("debug" is for timing experiments only and does change results). */
+ * run their projections as token-block GEMMs on the tensor cores (1) or eight tokens at a time through the GEMV (0).  Results never depend on them. */
 int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value);
 /* Phase trace, the counterpart of WGPUContext.TimeCommands (poly/wgpu_context_native.go:553) and of the
  * per-layer timing ForwardTokenIDsWGPU emits (poly/wgpu_forward.go:121-127).  With option "trace" = 1 every
@@ -220,8 +219,11 @@ void loom_b200_program_free(loom_b200_ctx* ctx, loom_b200_program* prog);
  * scratch with cudaMalloc when a larger shape first arrives; this one keeps that scratch in a fixed
  * 1.02 MiB array inside the library image (held by every GPU that loads the library until the process exits)
  * and calls no cudaMalloc, cudaFree or allocating routine.
- *   Limits: rows <= 65,536 and 16*ceil(rows/16)*min(batch,8) <= 262,144; beyond them the call fails with
- *   LOOM_B200_ERR_UNSUPPORTED and a message naming loom_b200_ternary_linear.
+ *   Limits: rows <= 65,536 and 16*ceil(rows/16)*tokens_per_pass <= 262,144, where tokens_per_pass is
+ *   min(batch, 8) for inputs of up to about 19,000 columns and fewer beyond (5 at 28,672 columns: the same
+ *   rule as loom_b200_ternary_linear); beyond them the call fails with LOOM_B200_ERR_UNSUPPORTED and a message
+ *   naming loom_b200_ternary_linear.  A bounded device-side wait that runs out inside this call is reported
+ *   by loom_b200_sync like one inside the regular call (the context's own status word is used).
  *   The first call on a device looks the array's address up (cudaGetSymbolAddress); make that call before
  *   starting any stream capture.  Every call clears the part of the array it is about to use.  The array is
  *   shared by all contexts of the process: two calls whose GPU work overlaps in time (different streams or

@@ -361,8 +361,6 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
             cudaFree(ctx->trace_dev);
             ctx->trace_dev = nullptr;
         }
-    } else if (!strcmp(key, "debug")) {
-        ctx->opt_debug = value;
     } else if (!strcmp(key, "pdl")) {
         ctx->opt_pdl = value != 0;
     } else if (!strcmp(key, "fold_rope")) {

@@ -71,7 +71,6 @@ struct loom_b200_ctx {
     unsigned long long* trace_dev = nullptr;  // [kTraceSlots][8] phase timestamps, one row per launch
     int trace_seq = 0;                          // next row
     const char* trace_label[kTraceSlots] = {};  // kernel that wrote each row
-    int opt_debug = 0;             // timing experiments (results are wrong when non-zero)
     bool capturing = false;        // between graph_begin and graph_end
     // tensor parallelism (tp.cu): rank and world size of this context's group; the NCCL communicator or null
     int tp_rank = 0, tp_world = 1;

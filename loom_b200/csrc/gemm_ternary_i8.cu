@@ -58,7 +58,6 @@ struct GemmParams {
     int* status;
     int32_t* part_acc;       // split-K: [tokens, rows] partial sums, zero between launches
     unsigned int* part_cnt;  // split-K: arrivals per (row tile, token tile), zero between launches
-    int debug;  // timing experiments only
     unsigned long long* trace;  // optional: row 0 = kernel phases, row 1+i = ring phases of k-slice i (CTA 0 only)
 };
 
@@ -599,7 +598,6 @@ int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const
     p.kv_msl = o.kv_msl;
     p.kv_pos0 = o.kv_pos0;
     p.status = ctx->status_dev;
-    p.debug = ctx->opt_debug;
     // phase trace: one row for the kernel and one per k-slice, kept contiguous (skipped if the ring of rows would wrap)
     p.trace = nullptr;
     if (ctx->trace_dev && (ctx->trace_seq % kTraceSlots) + w->kblocks + 2 < kTraceSlots) {

@@ -110,7 +110,6 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         }
     };
     auto issue = [&](int stage, const Cursor& c, int len) {  // lane 0 only
-        if (p.debug >= 2) return;
         lb_mbar_expect_tx(&my_bars[stage], (uint32_t)len * kTileBytes);
         lb_bulk_g2s(my_ring + (size_t)stage * kStageBytes, tile_ptr(p, c.v, c.kb), (uint32_t)len * kTileBytes,
                     &my_bars[stage]);
@@ -138,10 +137,8 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     LB_TRACE(1);
     lb_pdl_wait();               // everything below may read what earlier launches wrote
     LB_TRACE(2);
-    if (p.debug == 3) return;
     stage_activations<PRO>(p, sm);
     LB_TRACE(3);
-    if (p.debug == 4) return;
 
     // ---- main loop ------------------------------------------------------------------------------------
     const int g = lane >> 2, t = lane & 3;
@@ -234,7 +231,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     uint32_t cphase = 0;
     while (cc.pos < w1) {
         const int len = chunk_len(cc);
-        if (p.debug != 2 && !failed && !lb_mbar_wait_bounded(&my_bars[cstage], cphase)) {
+        if (!failed && !lb_mbar_wait_bounded(&my_bars[cstage], cphase)) {
             failed = true;
             if (lane == 0) atomicExch(p.status, 1);
         }
@@ -244,7 +241,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         }
         const uint8_t* tile = my_ring + (size_t)cstage * kStageBytes + lane * 16;
         const uint32_t* ab = act_base + cc.kb * act_kb_mul;
-        if (!failed && p.debug != 1) {
+        if (!failed) {
             if (len == kStageTiles) {
 #pragma unroll
                 for (int i = 0; i < kStageTiles; ++i) tile_step(tile + i * kTileBytes, ab + i * act_kb_mul);
@@ -487,7 +484,6 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     p.fix_acc = ctx->fix_acc;
     p.fix_cnt = ctx->fix_cnt;
     p.status = ctx->status_dev;
-    p.debug = ctx->opt_debug;
     p.trace = lb_trace_row(ctx, "gemv");
     if (smem > 227 * 1024)
         return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: K=%d with %d tokens needs %zu B of shared memory", p.K, p.M, smem);

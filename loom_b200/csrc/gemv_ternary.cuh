@@ -81,7 +81,6 @@ struct LbGemvParams {
     unsigned int* fix_cnt;
     int* status;
     unsigned long long* trace;  // optional row of 8 phase timestamps (ns) written by CTA 0, or null
-    int debug;  // timing experiments only: 1 = skip the arithmetic, 2 = skip the weight copies
 };
 
 // Launches the GEMV on ctx->stream (programmatic dependent launch unless disabled).

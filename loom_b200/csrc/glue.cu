@@ -577,7 +577,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
     uint32_t phase = 0;
     // staging (float32, rows of hd+4) -> KV (float64, rows of `stride`); rows beyond `rows` become zero
     auto widen = [&](int rows, int stride) {
-        if (p.debug == 12) return;
         const int quads = hd / 4;
         for (int idx = tid; idx < kPfKeys * quads; idx += kPfThreads) {
             const int r = idx / quads, c = (idx - r * quads) * 4;
@@ -610,7 +609,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
             const double* qa = Qs + (size_t)(wr + g) * qstride + t4;
             const double* kb = KV + (size_t)(wc + g) * kstride + t4;
 #pragma unroll 4
-            for (int d = 0; d < (p.debug >= 10 ? 4 : hd); d += 4) {
+            for (int d = 0; d < hd; d += 4) {
                 const double a0 = qa[d], a1 = qa[(size_t)8 * qstride + d];
                 double b[4];
 #pragma unroll
@@ -646,7 +645,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
 #pragma unroll 4
             for (int k = 0; k < 16; ++k) {
                 double e = 0.0;
-                if (kpos0 + part * 16 + k <= qpos) e = (p.debug == 8 || p.debug >= 11) ? 1.0 : exp(__dsub_rn(srow[k], m_new));
+                if (kpos0 + part * 16 + k <= qpos) e = exp(__dsub_rn(srow[k], m_new));
                 srow[k] = e;
                 sum = __dadd_rn(sum, e);
             }
@@ -680,7 +679,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) lb_attention_prefill_kernel(con
             }
             const double* pa = Ss + (size_t)(wr + g) * sstride + t4;
             const double* vb = KV + (size_t)t4 * vstride + wd + g;
-            const int kend = (p.debug == 9 || p.debug >= 11) ? 4 : (krows + 3) & ~3;  // keys past krows carry zero weights and zero rows
+            const int kend = (krows + 3) & ~3;  // keys past krows carry zero weights and zero rows
 #pragma unroll 2
             for (int k = 0; k < kend; k += 4) {
                 const double a0 = pa[k], a1 = pa[(size_t)8 * sstride + k];
@@ -778,7 +777,6 @@ int lb_launch_attention_prefill(loom_b200_ctx* ctx, const LbAttnParams& pin) {
     LbAttnParams p = pin;
     p.trace = nullptr;
     p.status = ctx->status_dev;
-    p.debug = ctx->opt_debug;
     LB_REQUIRE(ctx, lb_attention_prefill_supported(p), "attention (prompt block): %d heads over %d kv heads of %d dimensions", p.heads,
                p.kv_heads, p.hd);
     const int TQ = kPfRows / (p.heads / p.kv_heads);

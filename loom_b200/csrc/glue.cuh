@@ -41,7 +41,6 @@ struct LbAttnParams {
     float* cache_k_w;
     unsigned long long* trace;
     int* status;           // device status word for bounded waits
-    int debug;             // timing experiments only (results are wrong when non-zero)
 };
 int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p);
 size_t lb_attn_part_elems(int M, int heads, int hd, int splits);

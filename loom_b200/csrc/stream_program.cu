@@ -352,7 +352,6 @@ int lb_program_build(loom_b200_ctx* ctx, const std::vector<LbJob>& jobs_in, loom
         p.fix_acc = nullptr;
         p.fix_cnt = nullptr;
         p.status = ctx->status_dev;
-        p.debug = 0;
         p.trace = lb_trace_row(ctx, "stream-job");
         for (int s2 = 0; s2 < p.nseg; ++s2) bytes += (uint64_t)p.seg[s2].strips * p.kblocks * kTileBytes + (uint64_t)p.M * p.seg[s2].rows * 4;
         bytes += (uint64_t)p.M * p.K;
