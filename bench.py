@@ -166,40 +166,127 @@ def gemv_roofline(ctx, torch, weights, shape, reps=20):
     bytes_gate = I * ((H + 15) // 16) * 4 + H + I * 4
     bytes_down = H * ((I + 15) // 16) * 4 + I + H * 4
     per_launch = 0.5 * (bytes_gate + bytes_down)
-    return per_launch, us, launches
+    return {"bytes": per_launch, "us": us, "launches": launches, "gbs": per_launch / us / 1e3}
 
 
-def cpu_sample(dec, weights, emb_host, shape, ctx_len, token, sample_blocks, tokens, threads):
-    """Times the CPU oracle (restatement of the reference's Go path, AVX2 byte-code kernel, `threads` workers) on
-    a bounded sample: `sample_blocks` full-width blocks at the same context length plus the full fp32 head."""
+def linears_roofline(ctx, torch, dec, shape, reps=20):
+    """The ternary projections of one decode step as the step runs them (the fused-prologue instantiations: QKV with the
+    block norm, O with the inner norm from float64 + residual, gate+up with the block norm + SwiGLU, down with the inner
+    norm + residual; every block, so 30 x 17.4 MB of distinct packed weights, far beyond L2), without attention and head,
+    replayed as one recorded frame; CUDA events on the launching stream.  Algorithmic bytes = packed words + int8 rows
+    + fp32 outputs of the seven matrices of every block."""
+    dec.linears_frame()
+    ctx.sync()
+    ctx.graph_begin()
+    dec.linears_frame()
+    gr = ctx.graph_end()
+    for _ in range(3):
+        ctx.graph_launch(gr)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        ctx.graph_launch(gr)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    ctx.graph_free(gr)
+    tern_b, _, _ = algorithmic_bytes(shape, 0)
+    # ncu: 2.57 + 1.76 + 8.96 + 4.56 MB read per block for 17.39 MB algorithmic, 0 written
+    traffic = 17.85e6 * shape["layers"]
+    return {"bytes": tern_b, "us": us, "gbs": tern_b / us / 1e3, "traffic": traffic}
+
+
+def run_tp_check(dist, local, world):
+    """Before a multi-GPU run is timed: the tensor-parallel path on these GPUs against the CPU oracle's unsharded
+    decoder (a small sharded decoder; exact int32 all-reduce; row-sharded linear bit-exact; every rank's logits
+    bit-identical; greedy tokens equal to the oracle's), once over NCCL inside the recorded frame and once over the
+    peer mailboxes.  The oracle is the checker here, nothing of it is timed.  Returns "ok" or "failed: ..."."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    try:
+        import datetime
+
+        import tp_gpu_worker
+        gloo = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=180))
+        problems = []
+        for mode in ("graph", "peer"):
+            try:
+                failures, _ = tp_gpu_worker.run_checks(mode, local, group=gloo)
+            except Exception as exc:
+                failures = ["%s: %r" % (type(exc).__name__, exc)]
+            problems += ["%s: %s" % (mode, f) for f in failures]
+        flag = [None] * world
+        dist.all_gather_object(flag, problems, group=gloo)
+        allp = ["rank %d %s" % (r, p) for r, ps in enumerate(flag) for p in ps]
+        return "ok" if not allp else "failed: " + "; ".join(allp)[:600]
+    except Exception as exc:
+        return "failed: %r" % (exc,)
+
+
+def bench_config(args, shape, world):
+    """The `config` object of the JSON line: a function of the command line only, so that the two arms of a run
+    (`--impl ours` and `--impl reference`) print the same object."""
+    return {"workload": "BitNet-b1.58-2B-shape ternary decoder, batch-1 greedy decode (configs[2])",
+            "layers": shape["layers"], "hidden": shape["hidden"], "vocab": shape["vocab"], "prompt": args.prompt,
+            "context_first_timed_step": args.prompt + args.warmup + 1,
+            "parallelism": "replicas only" if world > 1 else "single GPU",
+            "l2": "every step streams 0.5 GB of packed weights + 1.3 GB fp32 head, far beyond the 126 MB L2"}
+
+
+def host_decoder(shape, blocks, ctx_len, seed):
+    """A `blocks`-deep decoder of the benchmark's widths for the CPU oracle, built on the host only (no GPU, nothing
+    of the CUDA library): packed words drawn with the code frequencies that absmean ternarisation gives N(0, sigma)
+    masters (P(0) = P(|z| < 0.399) = 0.310, P(+1) = P(-1) = 0.345), per-matrix scale 0.798 * 0.02, seeded N(0, 1) KV rows
+    for `ctx_len` positions, seeded N(0, 0.02) tied embedding / head.  The CPU kernels' time does not depend on the values."""
     from oracle import oracle as orc
-    s = dict(shape)
-    odec = orc.Decoder(sample_blocks, s["hidden"], s["heads"], s["kv_heads"], s["head_dim"], s["inter"], s["vocab"],
-                       s["eps"], s["theta"], orc.ACT_SILU, s["max_seq_len"])
-    for b in range(sample_blocks):
-        words = [w.words() for w in weights[b]]
-        scales = [w.scale for w in weights[b]]
-        odec.set_block_packed(b, words, scales)
-        k, v = dec.cache(b)
+    s = shape
+    rng = np.random.default_rng(seed)
+    H, I, hd = s["hidden"], s["inter"], s["head_dim"]
+    qd, kvd = s["heads"] * hd, s["kv_heads"] * hd
+    dims = ((qd, H), (kvd, H), (kvd, H), (H, qd), (I, H), (I, H), (H, I))
+    odec = orc.Decoder(blocks, H, s["heads"], s["kv_heads"], hd, I, s["vocab"], s["eps"], s["theta"], orc.ACT_SILU, s["max_seq_len"])
+    shifts = (2 * np.arange(16, dtype=np.uint32)).reshape(1, 1, 16)
+    for b in range(blocks):
+        words = []
+        for r, c in dims:
+            assert c % 16 == 0
+            u = rng.random((r, c // 16, 16), dtype=np.float32)
+            codes = (u >= 0.345).astype(np.uint32) + (u >= 0.655).astype(np.uint32)  # 0 / 1 / 2 = weight -1 / 0 / +1
+            words.append(np.bitwise_or.reduce(codes << shifts, axis=2).astype(np.uint32))
+        odec.set_block_packed(b, words, [np.float32(0.798 * 0.02)] * 7)
+        k = rng.standard_normal((ctx_len, kvd), dtype=np.float32)
+        v = rng.standard_normal((ctx_len, kvd), dtype=np.float32)
         odec.set_kv(b, ctx_len, k, v)
-    odec.set_embeddings(emb_host)
-    tok = np.array([token], np.int32)
-    odec.forward(tok, simd=1, threads=threads)  # builds the byte-code caches; not timed (as the reference's bench)
-    t_blocks = []
+    emb = rng.standard_normal((s["vocab"], H), dtype=np.float32) * np.float32(0.02)
+    odec.set_embeddings(emb)
+    return odec, emb
+
+
+def cpu_decode_rate(shape, blocks, ctx_len, tokens, threads, seed):
+    """Greedy decode tokens/s of the CPU oracle (restatement of the reference's Go path: AVX2 byte-code kernel, rows
+    fanned out over `threads` workers, float64 attention and head) on a `blocks`-deep decoder at context `ctx_len`.
+    When `blocks` is less than the model's depth the block time is scaled by depth / blocks and the head counted once."""
+    from oracle import oracle as orc
+    odec, emb = host_decoder(shape, blocks, ctx_len, seed)
+    tok = np.array([1], np.int32)
+    logits = odec.forward(tok, simd=1, threads=threads)  # builds the byte-code caches: untimed, like the reference's bench
+    times = []
     for _ in range(tokens):
+        tok[0] = orc.argmax(logits)
         t0 = time.perf_counter()
-        _, hid = odec.forward(tok, simd=1, threads=threads, want_hidden=True)
-        t_blocks.append(time.perf_counter() - t0)
-    # forward() above includes the head; time the head alone to separate the two
-    t_head = []
-    for _ in range(tokens):
-        t0 = time.perf_counter()
-        orc.lm_head(hid[-1], emb_host, threads=threads)
-        t_head.append(time.perf_counter() - t0)
-    th = float(np.median(t_head))
-    tb = max(float(np.median(t_blocks)) - th, 1e-9)
-    per_token = tb * (shape["layers"] / sample_blocks) + th
-    return 1.0 / per_token, tb, th
+        logits = odec.forward(tok, simd=1, threads=threads)  # attention single-threaded, as in the reference
+        times.append(time.perf_counter() - t0)
+    per_token = float(np.mean(times))
+    if blocks < shape["layers"]:
+        hid = np.zeros(shape["hidden"], np.float32)
+        th = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            orc.lm_head(hid, emb, threads=threads)
+            th.append(time.perf_counter() - t0)
+        head = float(np.median(th))
+        per_token = max(per_token - head, 1e-9) * (shape["layers"] / blocks) + head
+    return 1.0 / per_token, tokens
 
 
 def gemm_mode(args):
@@ -556,8 +643,30 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     shape = dict(SHAPE, layers=args.layers, vocab=args.vocab)
+    config = bench_config(args, shape, world)
+    ctx_first = config["context_first_timed_step"]
 
-    if args.impl == "reference" and rank != 0:
+    if args.impl == "reference":
+        # The reference's own GPU path is WGSL over wgpu (no graphics stack here) and its CPU path is Go (no toolchain
+        # here): this arm times the C++ restatement of that CPU path on the host cores.  Nothing of the CUDA library,
+        # and no GPU, is touched.  Rank 0 alone works.
+        if rank != 0:
+            return 0
+        from oracle import oracle as orc
+        threads = orc.host_threads()
+        tokens = max(8, min(args.steps, 16))
+        tokps, timed = cpu_decode_rate(shape, shape["layers"], ctx_first, tokens, threads, args.seed)
+        line = {"impl": "reference", "metric": METRIC, "value": tokps, "unit": "tok/s", "n_gpus": args.gpus,
+                "steps": args.steps, "tokens_timed": timed, "warmup": args.warmup, "ms_per_step": 1e3 / tokps,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": tokps, "unit": "tok/s", "cores": threads, "kind": "port",
+                                 "sample": "all %d blocks at full width + the full fp32 head on the host (C++ restatement of the "
+                                           "Go CPU path, AVX2 byte-code kernel, %d threads), %d greedy tokens from context %d; "
+                                           "weights and KV rows are synthetic with the benchmark's shapes and code frequencies"
+                                           % (shape["layers"], threads, timed, ctx_first)},
+                "e2e": {"value": tokps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
         return 0
 
     import torch
@@ -568,8 +677,12 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
     torch.cuda.set_device(local)
-    if world > 1 and args.impl == "ours":
+    tp_check = None
+    if world > 1:
+        # the check below makes ranks leave and re-join NCCL groups inside one process: keep NVLink multicast objects out of it
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        tp_check = run_tp_check(dist, local, world)
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     ctx = loom_b200.Context(local, tstream.cuda_stream)
@@ -583,67 +696,56 @@ def main():
     # measured prefill so that the prefill figure does not include first-call allocations.
     dec.forward(prompt, want_logits=False)
     ctx.sync()
-    t0 = time.perf_counter()
     _, m0 = dec.generate(prompt, args.warmup)
     prefill_s = m0.prefill_seconds
     ctx_len = args.prompt + args.warmup
     logits = dec.forward(np.array([int(prompt[0])], np.int32))  # one more step through the host path (warm)
     ctx_len += 1
+    assert ctx_len == ctx_first
     peak, peak_kind = measured_peaks()
-
-    if args.impl == "reference":
-        from oracle import oracle as orc
-        threads = orc.host_threads()
-        emb_host = emb.cpu().numpy()
-        sample_blocks = 2
-        tokps, tb, th = cpu_sample(dec, weights, emb_host, shape, ctx_len, int(np.argmax(logits)), sample_blocks,
-                                   max(args.steps // 16, 3), threads)
-        line = {"impl": "reference", "metric": METRIC, "value": tokps, "unit": "tok/s", "n_gpus": args.gpus,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / tokps, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic",
-                "config": {"workload": "BitNet-b1.58-2B-shape ternary decoder, batch-1 greedy decode", "prompt": args.prompt,
-                           "context": ctx_len},
-                "cpu_baseline": {"value": tokps, "unit": "tok/s", "cores": threads, "kind": "port",
-                                 "sample": "%d of %d blocks at full width (AVX2 byte-code kernel) at context %d + the full "
-                                           "fp32 head; blocks x%g, head x1" % (sample_blocks, shape["layers"], ctx_len,
-                                                                              shape["layers"] / sample_blocks)},
-                "e2e": {"value": tokps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
-        return 0
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident timed region: K decode steps, frame replay, no host round trip ---------------------
+    # ---- device-resident timed region: exactly K decode steps, no host round trip ------------------------------
+    # K steps can be as short as a few tens of milliseconds, less than one nvidia-smi sample: the region is repeated
+    # from the same KV offset (the sequence is cut back to ctx_first positions) until at least 0.5 s have been timed,
+    # every repetition bracketed by barrier + synchronize and timed with CUDA events; the median repetition counts.
     sampler = ClockSampler(local)
     barrier()
     sampler.start()
-    # the greedy loop continues from the current logits: K x {argmax, forward}
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    dec.continue_greedy(args.steps)
-    e1.record()
-    barrier()
-    dev_s = e0.elapsed_time(e1) * 1e-3
+    reps, rep_s, total_s = 0, [], 0.0
+    while reps < 3 or (total_s < 0.5 and reps < 200):
+        dec.set_kv_offset(ctx_first)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        dec.continue_greedy(args.steps)
+        e1.record()
+        barrier()
+        t = e0.elapsed_time(e1) * 1e-3
+        if world > 1:
+            tt = torch.tensor([t], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = float(tt.item())
+        rep_s.append(t)
+        total_s += t
+        reps += 1
     clocks = sampler.stop()
-    ctx_mid = ctx_len + args.steps // 2
-    ctx_len += args.steps
-    if world > 1:
-        t = torch.tensor([dev_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_s = float(t.item())
+    dev_s = float(np.median(rep_s))
+    ctx_mid = ctx_first + args.steps // 2
+    ctx_len = ctx_first + args.steps
     value = world * args.steps / dev_s
 
     # ---- end to end through the host-facing call: token id in (pinned H2D), logits out (D2H), host argmax -------
+    dec.set_kv_offset(ctx_first)
     tok = int(np.argmax(logits))
     for _ in range(3):
         logits = dec.forward(np.array([tok], np.int32))
         tok = int(np.argmax(logits))
-    ctx_len += 3
-    e2e_steps = min(args.steps, shape["max_seq_len"] - ctx_len - 1)
+    e2e_steps = min(args.steps, shape["max_seq_len"] - ctx_first - 4)
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
@@ -658,42 +760,52 @@ def main():
     e2e = world * e2e_steps / e2e_s
 
     tern_b, kv_b, head_b = algorithmic_bytes(shape, ctx_mid)
-    per_launch, gemv_us, gemv_launches = gemv_roofline(ctx, torch, weights, shape)
-    achieved = per_launch / gemv_us / 1e3  # GB/s
-    launches_per_token = shape["layers"] * 5 + 4  # 5 per block (RoPE is folded into attention) + embed + head + position + argmax
+    step_linears = linears_roofline(ctx, torch, dec, shape)
+    c0 = gemv_roofline(ctx, torch, weights, shape)
+    launches_per_token = dec.launches_per_token()
     line = {
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * dev_s / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic",
-        "config": {"workload": "BitNet-b1.58-2B-shape ternary decoder, batch-1 greedy decode (configs[2])",
-                   "layers": shape["layers"], "prompt": args.prompt, "context_mid": ctx_mid,
-                   "parallelism": "replicas only" if world > 1 else "single GPU",
-                   "l2": "every step streams 0.5 GB of packed weights + 1.3 GB fp32 head, far beyond the 126 MB L2"},
+        "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic", "config": config,
+        "timed_region": {"repetitions": reps, "seconds_each_median": dev_s, "seconds_total": total_s,
+                         "note": "every repetition is exactly `steps` decode steps from context_first_timed_step"},
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": shape["vocab"] * 4,
                 "steps": e2e_steps},
-        "gpu_launches": args.steps * launches_per_token,
+        "gpu_launches": int(args.steps * launches_per_token),
+        "launches_per_token": launches_per_token,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": 4.52e6, "traffic_source": "ncu dram__bytes_read+write per matrix of the same kernel inside the "
-                     "decode step (gate+up pair 8.96 MB, down 4.56 MB, writes 0): profiles/gemv_ternary_decode_bitnet2b.md",
-                     "peak_kind": peak_kind, "kernel": "lb_gemv_ternary_kernel (gate 6912x2560 and down "
-                     "2560x6912, batch 1, 60 distinct matrices per replay)", "bytes_per_launch": per_launch,
-                     "us_per_launch": gemv_us, "launches_timed": gemv_launches},
+        "roofline": {"bound": "hbm", "achieved": step_linears["gbs"], "peak": peak, "unit": "GB/s",
+                     "frac": step_linears["gbs"] / peak, "traffic": step_linears["traffic"],
+                     "traffic_source": "ncu dram__bytes_read+write of the ternary projections of one decoder block inside the "
+                                       "decode step, scaled by the number of blocks (writes 0: outputs stay in L2)",
+                     "peak_kind": peak_kind,
+                     "kernel": "the ternary projections of one decode step as the step runs them (QKV, O, gate+up, down of every "
+                               "block with their fused normalise/quantize prologues and epilogues; no attention, no head), "
+                               "replayed as one recorded frame",
+                     "bytes_per_frame": step_linears["bytes"], "us_per_frame": step_linears["us"],
+                     "c0_gemv": {"achieved": c0["gbs"], "frac": c0["gbs"] / peak, "bytes_per_launch": c0["bytes"],
+                                 "us_per_launch": c0["us"], "launches_timed": c0["launches"],
+                                 "kernel": "configs[0]: int8 row in, gate 6912x2560 and down 2560x6912, batch 1, 60 distinct "
+                                           "matrices per replay, independent launches"}},
         "decode_bytes": {"ternary": tern_b, "kv": kv_b, "fp32_head": head_b,
                          "gbs_all": (tern_b + kv_b + head_b) / (dev_s / args.steps) / 1e9,
                          "frac_of_peak": (tern_b + kv_b + head_b) / (dev_s / args.steps) / 1e9 / peak},
         "prefill": {"tokens": args.prompt, "seconds": prefill_s, "tok_per_s": args.prompt / prefill_s},
     }
+    if tp_check is not None:
+        line["tp_check"] = tp_check
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
             from oracle import oracle as orc
             threads = orc.host_threads()
-            emb_host = emb.cpu().numpy()
-            tokps, tb, th = cpu_sample(dec, weights, emb_host, shape, min(ctx_len, shape["max_seq_len"] - 2), tok, 2, 3, threads)
+            sample_blocks = 4
+            tokps, timed = cpu_decode_rate(shape, min(sample_blocks, shape["layers"]), ctx_first, 4, threads, args.seed)
             line["cpu_baseline"] = {"value": tokps, "unit": "tok/s", "cores": threads, "kind": "port",
-                                    "sample": "2 of %d blocks at full width (AVX2 byte-code kernel, %d threads) at context "
-                                              "%d + the full fp32 head, 3 tokens; blocks x%g, head x1" %
-                                              (shape["layers"], threads, ctx_len, shape["layers"] / 2)}
+                                    "sample": "%d of %d blocks at full width (C++ restatement of the Go CPU path, AVX2 byte-code "
+                                              "kernel, %d threads) at context %d + the full fp32 head, %d tokens; block time x%g, "
+                                              "head x1.  `--impl reference` runs all blocks" %
+                                              (min(sample_blocks, shape["layers"]), shape["layers"], threads, ctx_first, timed,
+                                               shape["layers"] / min(sample_blocks, shape["layers"]))}
         except Exception as exc:  # the baseline is reported, never required for the GPU number
             line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": "failed: %r" % (exc,)}
     if rank == 0:

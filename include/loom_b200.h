@@ -329,8 +329,34 @@ int loom_b200_decoder_last_hidden(loom_b200_decoder* dec, float* hidden_host);
  * device and without waiting for it (call loom_b200_sync to wait).  The body of Generate's loop,
  * poly/transformer.go:434-485. */
 int loom_b200_decoder_continue(loom_b200_decoder* dec, int steps);
+/* Cuts the sequence back to its first kv_offset positions (0 < kv_offset <= the current offset), like assigning
+ * layer.KVOffset on every MHA layer: the next one-token forward writes position kv_offset.  Ring rows beyond stay
+ * until they are overwritten. */
+int loom_b200_decoder_set_kv_offset(loom_b200_decoder* dec, int kv_offset);
+/* Kernels of this library one greedy decode step launches (argmax included); 1 before the first step was recorded. */
+int loom_b200_decoder_step_launches(const loom_b200_decoder* dec);
+/* Measurement aid, the counterpart of timing the BitNet dispatches alone (WGPUContext.TimeCommands around
+ * DispatchDenseBitNetTernaryQuantized, poly/wgpu_context_native.go:553): enqueues the ternary projections of ONE
+ * one-token decode step exactly as the step runs them -- QKV, O, gate+up, down of every block with their fused
+ * normalise/quantize prologues and epilogues, on the step's own buffers -- without attention, embedding, head or
+ * position update.  May be recorded between graph_begin and graph_end.  The newest K/V ring row and the residual
+ * scratch are overwritten; the next real step rewrites both. */
+int loom_b200_decoder_linears_frame(loom_b200_decoder* dec);
+/* The last n tokens the device-resident greedy loop (decoder_continue / decoder_generate) sampled, oldest first;
+ * waits for the device.  n must not exceed the number sampled since the last reset. */
+int loom_b200_decoder_read_tokens(loom_b200_decoder* dec, int32_t* tokens_host, int n);
 /* copies block's KV ring [max_seq_len, kv_heads*head_dim] to the host (layer.KVCacheK / KVCacheV) */
 int loom_b200_decoder_download_cache(loom_b200_decoder* dec, int block, float* k_host, float* v_host);
+/* The inverse: installs positions 0..kv_offset-1 of block's KV ring from host rows [kv_offset, kv_heads*head_dim]
+ * (position-major like layer.KVCacheK / KVCacheV, poly/mha.go:262-270) and, like assigning layer.KVOffset, makes
+ * kv_offset the position of the next token for the whole decoder: restoring a saved sequence.  Call it for every
+ * block with the same kv_offset before the next one-token forward. */
+int loom_b200_decoder_upload_cache(loom_b200_decoder* dec, int block, int kv_offset, const float* k_host, const float* v_host);
+/* The residual stream after the last block, before the final norm, for the tokens of the last forward call's last
+ * pass (the x that forwardOnCPUNormal returns, poly/transformer_forward.go:236-253): up to max_rows rows of
+ * [hidden] floats; *rows_out = rows written.  A prompt of up to 1024 tokens that took the token-block path is one
+ * pass; the eight-tokens-per-pass path leaves its last pass. */
+int loom_b200_decoder_last_residual(loom_b200_decoder* dec, float* rows_host, int max_rows, int* rows_out);
 /* Transformer.Generate with deterministic (greedy) sampling: prefill the prompt, then max_new times
  * {first-maximum token, forward it}.  The loop runs on the device; tokens come back once at the end. */
 int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, int n_prompt, int max_new,

@@ -99,6 +99,12 @@ SIGNATURES = {
     "loom_b200_decoder_continue": (_i, [_vp, _i]),
     "loom_b200_decoder_download_cache": (_i, [_vp, _i, _vp, _vp]),
     "loom_b200_decoder_generate": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
+    "loom_b200_decoder_upload_cache": (_i, [_vp, _i, _i, _vp, _vp]),
+    "loom_b200_decoder_read_tokens": (_i, [_vp, _vp, _i]),
+    "loom_b200_decoder_set_kv_offset": (_i, [_vp, _i]),
+    "loom_b200_decoder_step_launches": (_i, [_vp]),
+    "loom_b200_decoder_linears_frame": (_i, [_vp]),
+    "loom_b200_decoder_last_residual": (_i, [_vp, _vp, _i, C.POINTER(_i)]),
     "loom_b200_tp_unique_id": (_i, [_vp]),
     "loom_b200_tp_init": (_i, [_vp, _i, _i, _vp]),
     "loom_b200_tp_peer_handle": (_i, [_vp, _vp]),
@@ -547,6 +553,35 @@ class Decoder:
         v = np.empty((self.dims.max_seq_len, kvd), np.float32)
         self.ctx._check(lib().loom_b200_decoder_download_cache(self.h, block, k.ctypes.data, v.ctypes.data))
         return k, v
+
+    def set_kv_offset(self, kv_offset: int):
+        """Cuts the sequence back to its first kv_offset positions."""
+        self.ctx._check(lib().loom_b200_decoder_set_kv_offset(self.h, kv_offset))
+
+    def launches_per_token(self) -> int:
+        return int(lib().loom_b200_decoder_step_launches(self.h))
+
+    def linears_frame(self):
+        """Enqueues the ternary projections of one decode step as the step runs them (no attention, no head)."""
+        self.ctx._check(lib().loom_b200_decoder_linears_frame(self.h))
+
+    def generated_tokens(self, n: int) -> np.ndarray:
+        """The last n tokens sampled by the device-resident greedy loop (waits for the device)."""
+        out = np.zeros(n, np.int32)
+        self.ctx._check(lib().loom_b200_decoder_read_tokens(self.h, out.ctypes.data, n))
+        return out
+
+    def upload_cache(self, block: int, kv_offset: int, k, v):
+        """Installs positions 0..kv_offset-1 of a block's KV ring from host rows [kv_offset, kv_dim]."""
+        k, v = _f32(k), _f32(v)
+        self.ctx._check(lib().loom_b200_decoder_upload_cache(self.h, block, kv_offset, k.ctypes.data, v.ctypes.data))
+
+    def last_residual(self, max_rows: int):
+        """Residual stream after the last block (before the final norm) for the tokens of the last pass."""
+        out = np.empty((max_rows, self.dims.hidden), np.float32)
+        n = _i(0)
+        self.ctx._check(lib().loom_b200_decoder_last_residual(self.h, out.ctypes.data, max_rows, C.byref(n)))
+        return out[:n.value]
 
     def generate(self, prompt, max_new):
         prompt = np.ascontiguousarray(prompt, np.int32).ravel()

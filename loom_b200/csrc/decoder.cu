@@ -50,6 +50,9 @@ struct loom_b200_decoder {
     float *pf_x = nullptr, *pf_prod = nullptr;
     double *pf_q = nullptr, *pf_attn = nullptr;
     int32_t *pf_accg = nullptr, *pf_accu = nullptr;
+    const float* last_resid = nullptr;  // residual stream of the last pass (x or pf_x) and its rows
+    int last_resid_rows = 0;
+    int step_launches = 0;              // kernels of one recorded decode step (without the argmax)
 };
 
 namespace {
@@ -222,13 +225,18 @@ int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
         h.hidden_out = dec->hidden;
         if (int rc = lb_launch_lm_head(ctx, h)) return rc;
     }
+    dec->last_resid = dec->pf_x;
+    dec->last_resid_rows = M;
     return lb_launch_add_scalar(ctx, dec->pos, M);
 }
 
-int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int head_row) {
+// linears_only: just the ternary projections of the step, on the step's own buffers (a measurement frame: the
+// attention, the embedding, the head and the position update are left out, so nothing of the sequence state moves)
+int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int head_row, bool linears_only = false) {
     loom_b200_ctx* ctx = dec->ctx;
     const loom_b200_decoder_dims& d = dec->d;
-    if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, d.hidden, dec->tok, M, dec->x)) return rc;
+    if (!linears_only)
+        if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, d.hidden, dec->tok, M, dec->x)) return rc;
     for (auto& b : dec->blocks) {
         LbMhaStepArgs a = {};
         a.pro_mode = LB_PRO_BLOCKNORM;
@@ -240,7 +248,10 @@ int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int 
         a.M = M;
         a.splits = splits;
         a.fold_rope = M == 1;
-        if (int rc = lb_mha_step_dev(&b.mha, a)) return rc;
+        if (int rc = lb_mha_qkv_dev(&b.mha, a)) return rc;
+        if (!linears_only)
+            if (int rc = lb_mha_attn_dev(&b.mha, a)) return rc;
+        if (int rc = lb_mha_o_dev(&b.mha, a)) return rc;
         LbSwigluArgs s = {};
         s.gate = b.gate;
         s.up = b.up;
@@ -264,6 +275,7 @@ int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int 
         }
         if (int rc = lb_swiglu_dev(ctx, s)) return rc;
     }
+    if (linears_only) return 0;
     if (head) {
         LbLmHeadParams h = {};
         h.x = dec->x + (size_t)head_row * d.hidden;
@@ -284,6 +296,8 @@ int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int 
         if (dec->head_sharded)
             if (int rc = lb_tp_allgather_f32(ctx, h.logits, dec->logits, (size_t)h.vocab)) return rc;
     }
+    dec->last_resid = dec->x;
+    dec->last_resid_rows = M;
     return lb_launch_add_scalar(ctx, dec->pos, M);
 }
 
@@ -310,7 +324,9 @@ int dec_step(loom_b200_decoder* dec) {
     if (int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0)) return rc;  // warm-up run, counts as the step
     // record the same step for all later tokens
     if (int rc = loom_b200_graph_begin(ctx)) return rc;
+    const uint64_t l0 = ctx->launches;
     int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0);
+    dec->step_launches = (int)(ctx->launches - l0);
     loom_b200_graph* g = nullptr;
     int rc2 = loom_b200_graph_end(ctx, &g);
     if (rc) {
@@ -587,6 +603,83 @@ int loom_b200_decoder_download_cache(loom_b200_decoder* dec, int block, float* k
     loom_b200_ctx* ctx = dec->ctx;
     LB_REQUIRE(ctx, block >= 0 && block < (int)dec->blocks.size() && dec->blocks[block].ready, "decoder_download_cache: block %d is not set", block);
     return loom_b200_mha_download_cache(&dec->blocks[block].mha, k_host, v_host);
+}
+
+int loom_b200_decoder_set_kv_offset(loom_b200_decoder* dec, int kv_offset) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_set_kv_offset: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, kv_offset > 0 && kv_offset <= dec->kv_offset, "decoder_set_kv_offset: %d outside (0, %d]: a sequence can only be cut back", kv_offset, dec->kv_offset);
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_set_kv_offset cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    LB_CUDA(ctx, cudaMemcpy(dec->pos, &kv_offset, sizeof(int), cudaMemcpyHostToDevice));
+    dec->kv_offset = kv_offset;
+    return 0;
+}
+
+int loom_b200_decoder_step_launches(const loom_b200_decoder* dec) { return dec ? dec->step_launches + 1 : -1; }
+
+int loom_b200_decoder_linears_frame(loom_b200_decoder* dec) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_linears_frame: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    if (int rc = dec_check_ready(dec)) return rc;
+    LB_REQUIRE(ctx, dec->tp_world == 1, "decoder_linears_frame: not available under a tensor-parallel group");
+    if (int rc = lb_set_device(ctx)) return rc;
+    return dec_forward_chunk(dec, 1, dec->decode_splits, false, 0, true);
+}
+
+int loom_b200_decoder_read_tokens(loom_b200_decoder* dec, int32_t* tokens_host, int n) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_read_tokens: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, tokens_host && n > 0, "decoder_read_tokens: bad arguments");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_read_tokens takes host buffers and cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    if (int rc = lb_sync_checked(ctx)) return rc;
+    int step = 0;
+    LB_CUDA(ctx, cudaMemcpy(&step, dec->step, sizeof(int), cudaMemcpyDeviceToHost));
+    LB_REQUIRE(ctx, n <= step && step <= dec->out_cap, "decoder_read_tokens: %d tokens asked, %d sampled since the last reset (ring of %d)", n, step, dec->out_cap);
+    LB_CUDA(ctx, cudaMemcpy(tokens_host, dec->out_tokens + (step - n), (size_t)n * sizeof(int), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int loom_b200_decoder_upload_cache(loom_b200_decoder* dec, int block, int kv_offset, const float* k_host, const float* v_host) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_upload_cache: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, block >= 0 && block < (int)dec->blocks.size() && dec->blocks[block].ready, "decoder_upload_cache: block %d is not set", block);
+    LB_REQUIRE(ctx, k_host && v_host, "decoder_upload_cache: NULL buffer");
+    LB_REQUIRE(ctx, kv_offset > 0 && kv_offset < dec->d.max_seq_len, "decoder_upload_cache: kv_offset %d outside (0, MaxSeqLen %d)", kv_offset, dec->d.max_seq_len);
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_upload_cache takes host buffers and cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    loom_b200_mha& m = dec->blocks[block].mha;
+    // host rows are position-major [position][kv head * hd]; the device ring is head-major [kv head][position][hd]
+    std::vector<float> tmp((size_t)kv_offset * m.head_dim);
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int which = 0; which < 2; ++which) {
+        const float* host = which == 0 ? k_host : v_host;
+        float* ring = which == 0 ? m.cache_k : m.cache_v;
+        for (int h = 0; h < m.kv_heads; ++h) {
+            for (int pos = 0; pos < kv_offset; ++pos)
+                memcpy(tmp.data() + (size_t)pos * m.head_dim, host + (size_t)pos * m.kv_dim + (size_t)h * m.head_dim, (size_t)m.head_dim * sizeof(float));
+            LB_CUDA(ctx, cudaMemcpy(ring + (size_t)h * m.msl * m.head_dim, tmp.data(), tmp.size() * sizeof(float), cudaMemcpyHostToDevice));
+        }
+    }
+    dec->kv_offset = kv_offset;
+    LB_CUDA(ctx, cudaMemcpy(dec->pos, &kv_offset, sizeof(int), cudaMemcpyHostToDevice));
+    return 0;
+}
+
+int loom_b200_decoder_last_residual(loom_b200_decoder* dec, float* rows_host, int max_rows, int* rows_out) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_last_residual: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, rows_host && max_rows > 0, "decoder_last_residual: NULL buffer");
+    LB_REQUIRE(ctx, dec->last_resid && dec->last_resid_rows > 0, "decoder_last_residual: nothing has been forwarded yet");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_last_residual takes host buffers and cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    const int rows = dec->last_resid_rows < max_rows ? dec->last_resid_rows : max_rows;
+    LB_CUDA(ctx, cudaMemcpyAsync(rows_host, dec->last_resid, (size_t)rows * dec->d.hidden * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    if (int rc = lb_sync_checked(ctx)) return rc;
+    if (rows_out) *rows_out = rows;
+    return 0;
 }
 
 int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, int n_prompt, int max_new,

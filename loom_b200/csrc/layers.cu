@@ -100,7 +100,11 @@ void lb_mha_release(loom_b200_mha* m) {
         if (p) cudaFree(p);
 }
 
-int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
+static bool mha_folds_rope(const loom_b200_mha* m, const LbMhaStepArgs& a) {
+    return a.fold_rope && a.M == 1 && !m->q_norm && !m->k_norm && m->ctx->opt_fold_rope;
+}
+
+int lb_mha_qkv_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     loom_b200_ctx* ctx = m->ctx;
     // Q (fp64), K and V (fp32, written straight into the ring rows of these positions)
     LbGemvParams p = {};
@@ -108,7 +112,7 @@ int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     fill_seg(p.seg[0], m->wq, m->bq, m->q);
     fill_seg(p.seg[1], m->wk, m->bk, m->cache_k);
     fill_seg(p.seg[2], m->wv, m->bv, m->cache_v);
-    const bool fold_rope = a.fold_rope && a.M == 1 && !m->q_norm && !m->k_norm && ctx->opt_fold_rope;
+    const bool fold_rope = mha_folds_rope(m, a);
     p.seg[1].out_ring = m->msl;
     p.seg[2].out_ring = m->msl;
     p.seg[1].ring_hd = m->head_dim;
@@ -128,8 +132,12 @@ int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     p.pos_ptr = m->pos_dev;
     p.act = LOOM_B200_ACT_LINEAR;
     if (int rc = lb_gemv_finalize_params(ctx, p)) return rc;
-    if (int rc = lb_launch_gemv(ctx, p)) return rc;
+    return lb_launch_gemv(ctx, p);
+}
 
+int lb_mha_attn_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
+    loom_b200_ctx* ctx = m->ctx;
+    const bool fold_rope = mha_folds_rope(m, a);
     LbRopeParams r = {};
     r.q = m->q;
     r.cache_k = m->cache_k;
@@ -168,8 +176,11 @@ int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
         t.k_new = m->k_new;
         t.cache_k_w = m->cache_k;
     }
-    if (int rc = lb_launch_attention(ctx, t)) return rc;
+    return lb_launch_attention(ctx, t);
+}
 
+int lb_mha_o_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
+    loom_b200_ctx* ctx = m->ctx;
     if (m->q_dim_global > 0 && ctx->tp_world > 1) {
         LB_REQUIRE(ctx, a.pre_out == nullptr && m->tp_stats && m->tp_acc, "mha: sharded output projection without scratch");
         return lb_tp_rowsharded_linear(ctx, m->wo, true, m->attn, a.M, m->q_dim_global, m->inner, m->inner_len,
@@ -191,6 +202,12 @@ int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     o.act = LOOM_B200_ACT_LINEAR;
     if (int rc = lb_gemv_finalize_params(ctx, o)) return rc;
     return lb_launch_gemv(ctx, o);
+}
+
+int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
+    if (int rc = lb_mha_qkv_dev(m, a)) return rc;
+    if (int rc = lb_mha_attn_dev(m, a)) return rc;
+    return lb_mha_o_dev(m, a);
 }
 
 // ---- host-buffer layer calls (the C ABI) -------------------------------------------------------------

@@ -73,6 +73,10 @@ struct LbMhaStepArgs {
 // One chunk (M <= 8 tokens at positions *pos_dev ...): QKV -> q/k norm + RoPE -> attention -> inner norm -> O.
 // Does not advance pos_dev.
 int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a);
+// its three parts: the QKV projection, q/k norm + RoPE + attention, inner norm + output projection
+int lb_mha_qkv_dev(loom_b200_mha* m, const LbMhaStepArgs& a);
+int lb_mha_attn_dev(loom_b200_mha* m, const LbMhaStepArgs& a);
+int lb_mha_o_dev(loom_b200_mha* m, const LbMhaStepArgs& a);
 int lb_mha_alloc(loom_b200_ctx* ctx, loom_b200_mha* m, int max_splits);
 void lb_mha_release(loom_b200_mha* m);
 

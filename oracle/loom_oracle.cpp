@@ -888,6 +888,11 @@ void orc_decoder_reset(orc_decoder* d) {
 
 int orc_decoder_forward(orc_decoder* d, const int32_t* tokens, int n, float* hidden_out, float* logits_out,
                         int simd, int threads, int attn_threads) {
+    return orc_decoder_forward_taps(d, tokens, n, hidden_out, logits_out, nullptr, simd, threads, attn_threads);
+}
+
+int orc_decoder_forward_taps(orc_decoder* d, const int32_t* tokens, int n, float* hidden_out, float* logits_out,
+                             float* block_out, int simd, int threads, int attn_threads) {
     if (!d || !d->emb || n <= 0) return -1;
     const int H = d->hidden;
     std::vector<float> x((size_t)n * H), resid, normed((size_t)n * H), sub((size_t)n * H);
@@ -910,6 +915,10 @@ int orc_decoder_forward(orc_decoder* d, const int32_t* tokens, int n, float* hid
         orc_swiglu_forward(b.m[4], b.m[5], b.m[6], nullptr, nullptr, nullptr, nullptr, 0, 0.0, d->act, normed.data(), n,
                            nullptr, sub.data(), nullptr, nullptr, nullptr, nullptr, nullptr, simd, threads);
         for (size_t i = 0; i < x.size(); ++i) x[i] = sub[i] + resid[i];
+        if (block_out) {  // the residual stream after this block, [n, H]
+            std::memcpy(block_out, x.data(), sizeof(float) * x.size());
+            block_out += x.size();
+        }
     }
     orc_block_rmsnorm(x.data(), n, H, d->final_gain.data(), d->eps, normed.data(), nullptr);
     if (hidden_out) std::memcpy(hidden_out, normed.data(), sizeof(float) * (size_t)n * H);

@@ -162,6 +162,10 @@ int orc_decoder_set_kv(orc_decoder* d, int block, int kv_offset, const float* k,
  * (poly/transformer.go:635-719).  hidden_out [n,hidden] and logits_out [vocab] may be NULL. */
 int orc_decoder_forward(orc_decoder* d, const int32_t* tokens, int n, float* hidden_out, float* logits_out,
                         int simd, int threads, int attn_threads);
+/* the same forward; block_out (may be NULL) receives the residual stream after every block, [layers][n][hidden]:
+ * the x that forwardOnCPUNormal hands from block to block (poly/transformer_forward.go:236-251) */
+int orc_decoder_forward_taps(orc_decoder* d, const int32_t* tokens, int n, float* hidden_out, float* logits_out,
+                             float* block_out, int simd, int threads, int attn_threads);
 /* Generate's greedy loop (poly/transformer.go:341-485, poly/sampling.go:44-55): prefill the prompt, then
  * max_new tokens.  out_tokens [max_new].  decode_seconds (may be NULL) = wall time of the decode loop. */
 int orc_decoder_generate(orc_decoder* d, const int32_t* prompt, int n_prompt, int max_new, int32_t* out_tokens,

@@ -143,6 +143,8 @@ def _declare(L):
     L.orc_decoder_reset.argtypes = [_vp]
     L.orc_decoder_forward.restype = C.c_int
     L.orc_decoder_forward.argtypes = [_vp, _i32p, C.c_int, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
+    L.orc_decoder_forward_taps.restype = C.c_int
+    L.orc_decoder_forward_taps.argtypes = [_vp, _i32p, C.c_int, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
     L.orc_decoder_generate.restype = C.c_int
     L.orc_decoder_generate.argtypes = [_vp, _i32p, C.c_int, C.c_int, _i32p, _f64p, _f64p, C.c_int, C.c_int, C.c_int]
     L.orc_argmax.restype = C.c_int
@@ -481,6 +483,16 @@ class Decoder:
                                        simd, threads, attn_threads)
         assert rc == 0
         return (logits, hidden) if want_hidden else logits
+
+    def forward_taps(self, tokens, simd=0, threads=1, attn_threads=1):
+        """forward() that also returns the residual stream after every block: (logits, [layers, n, hidden])."""
+        tokens = _c(tokens, np.int32).ravel()
+        logits = np.empty(self.dims["vocab"], np.float32)
+        taps = np.empty((self.dims["layers"], tokens.size, self.dims["hidden"]), np.float32)
+        rc = lib().orc_decoder_forward_taps(self.h, _p(tokens, _i32p), tokens.size, None, _p(logits, _f32p),
+                                            _p(taps, _f32p), simd, threads, attn_threads)
+        assert rc == 0
+        return logits, taps
 
     def generate(self, prompt, max_new, simd=0, threads=1, attn_threads=1):
         prompt = _c(prompt, np.int32).ravel()

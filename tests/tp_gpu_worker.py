@@ -1,6 +1,7 @@
-"""One rank of the tensor-parallel GPU test (run by test_gpu_tp.py under torch.distributed.run, one process per
-GPU).  Every rank builds the same weights, keeps only its slices on its GPU, and must end with the logits and
-greedy tokens of the CPU oracle's UNSHARDED decoder.  gloo (CPU) carries the NCCL unique id."""
+"""One rank of the tensor-parallel GPU check.  Run by test_gpu_tp.py under torch.distributed.run (one process per
+GPU), and called by bench.py on every rank before it times a multi-GPU run.  Every rank builds the same weights,
+keeps only its slices on its GPU, and must end with the logits and greedy tokens of the CPU oracle's UNSHARDED
+decoder.  A gloo (CPU) group carries the NCCL unique id and the mailbox handles."""
 import os
 import sys
 
@@ -16,28 +17,27 @@ from loom_b200.tp import ShardPlan, slice_cols  # noqa: E402
 from oracle import oracle as orc  # noqa: E402
 
 
-def share_unique_id(rank: int) -> bytes:
+def share_unique_id(rank: int, group=None) -> bytes:
     t = torch.zeros(128, dtype=torch.uint8)
     if rank == 0:
         t = torch.frombuffer(bytearray(cabi.Context.tp_unique_id()), dtype=torch.uint8).clone()
-    dist.broadcast(t, 0)
+    dist.broadcast(t, 0, group=group)
     return bytes(t.numpy().tobytes())
 
 
-def main():
-    dist.init_process_group("gloo")
-    rank, world = dist.get_rank(), dist.get_world_size()
-    local = int(os.environ.get("LOCAL_RANK", rank))
+def run_checks(mode: str, local: int, group=None):
+    """The whole check on this rank: (failures, microseconds per sharded decode token).  `group` is a gloo group over
+    all ranks (None = the default group, which must then be gloo).  Collective: every rank calls it."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
     ctx = cabi.Context(device=local)
-    ctx.tp_init(rank, world, share_unique_id(rank))
+    ctx.tp_init(rank, world, share_unique_id(rank, group))
     assert ctx.tp_rank == rank and ctx.tp_world == world
-    mode = sys.argv[1] if len(sys.argv) > 1 else "graph"
     if mode == "nograph":
         ctx.set_option("tp_graph", 0)
     if mode == "peer":  # exchange through peer mailboxes instead of NCCL: gather every rank's IPC handle
         mine = torch.frombuffer(bytearray(ctx.tp_peer_handle()), dtype=torch.uint8).clone()
         allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
-        dist.all_gather(allh, mine)
+        dist.all_gather(allh, mine, group=group)
         ctx.tp_attach_peers(b"".join(bytes(t.numpy().tobytes()) for t in allh))
     failures = []
 
@@ -78,7 +78,7 @@ def main():
             failures.append("row-sharded linear token %d differs in %d of %d" % (t, int((got[t] != want).sum()), rows))
 
     # ---- the decoder: logits and greedy tokens of the unsharded oracle ----
-    L, H, heads, kvh, hd, I, V, msl = 2, 256, 4, 2, 64, 512, 512, 96
+    L, H, heads, kvh, hd, I, V, msl = 2, 512, 8, 8, 64, 1024, 512, 96  # 8 heads / 8 KV heads: any group of up to 8 ranks divides them
     eps, theta, act = 1e-5, 500000.0, cabi.ACT_SILU
     plan = ShardPlan(world, rank, H, heads, kvh, hd, I, V)
     odec = orc.Decoder(L, H, heads, kvh, hd, I, V, eps, theta, act, msl)
@@ -114,19 +114,29 @@ def main():
     # every rank must hold the same logits bit for bit
     mine = torch.from_numpy(gdec.forward(prompt).view(np.int32).astype(np.int64))
     lo, hi = mine.clone(), mine.clone()
-    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
-    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
     if not torch.equal(lo, hi):
         failures.append("ranks disagree on the logits")
     ctx.sync()
     gdec.close()
-    dist.barrier()  # nobody leaves while a peer may still be inside a collective
+    dist.barrier(group=group)  # nobody leaves while a peer may still be inside a collective
     ctx.tp_finalize()
+    ctx.close()
+    return failures, 1e6 * m.decode_device_seconds / max(1, m.generated_tokens)
+
+
+def main():
+    dist.init_process_group("gloo")
+    rank = dist.get_rank()
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    mode = sys.argv[1] if len(sys.argv) > 1 else "graph"
+    failures, us = run_checks(mode, local)
     dist.destroy_process_group()
     if failures:
         print("rank %d FAILED: %s" % (rank, "; ".join(failures)), flush=True)
         sys.exit(1)
-    print("rank %d ok (%.1f us/token sharded decode)" % (rank, 1e6 * m.decode_device_seconds / max(1, m.generated_tokens)), flush=True)
+    print("rank %d ok (%.1f us/token sharded decode)" % (rank, us), flush=True)
 
 
 if __name__ == "__main__":
