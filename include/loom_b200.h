@@ -101,7 +101,16 @@ void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
  * "fold_rope" 0/1 = one-token decoder steps apply RoPE inside the attention kernel (one launch less per block);
  * "decode_splits" 0..32 = position splits of the one-token attention, read by loom_b200_decoder_create (0 = choose); "tp_peer" 0/1 = use the peer mailboxes when attached;
  * "prefill_gemm" 0/1 = prompts of 32 or more tokens
- * run their projections as token-block GEMMs on the tensor cores (1) or eight tokens at a time through the GEMV (0).  Results never depend on them. */
+ * run their projections as token-block GEMMs on the tensor cores (1) or eight tokens at a time through the GEMV (0).  "gemv_wide" 0/1/2 = one- and two-token launches with a fused normalise/quantize prologue
+ * run one sixteen-warp CTA per SM that keeps the activation row in registers: never (0), for the float64 attention
+ * output only (1, the default) or always (2);
+ * "head_stream" 0/1 = the fp32 LM head streams
+ * its rows through shared memory with bulk copies and folds the greedy step (argmax, position, next embedding row) into
+ * its tail (1), or runs as a warp-per-row kernel followed by separate launches (0; read when the embeddings are set);
+ * "attn_cluster" 0/1 = one-token decoder steps run their attention
+ * as one thread-block cluster per KV head that combines its position slices through distributed shared memory (1) or as
+ * independent (head, slice) CTAs with a last-arriver combine (0).  Results never depend on them beyond the order of
+ * float64 additions. */
 int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value);
 /* Phase trace, the counterpart of WGPUContext.TimeCommands (poly/wgpu_context_native.go:553) and of the
  * per-layer timing ForwardTokenIDsWGPU emits (poly/wgpu_forward.go:121-127).  With option "trace" = 1 every
@@ -342,8 +351,8 @@ int loom_b200_decoder_step_launches(const loom_b200_decoder* dec);
  * position update.  May be recorded between graph_begin and graph_end.  The newest K/V ring row and the residual
  * scratch are overwritten; the next real step rewrites both. */
 int loom_b200_decoder_linears_frame(loom_b200_decoder* dec);
-/* The last n tokens the device-resident greedy loop (decoder_continue / decoder_generate) sampled, oldest first;
- * waits for the device.  n must not exceed the number sampled since the last reset. */
+/* The last n tokens the device-resident greedy loop (decoder_continue / decoder_generate) fed to a forward, oldest
+ * first; waits for the device.  n must not exceed the number of such tokens since the last reset. */
 int loom_b200_decoder_read_tokens(loom_b200_decoder* dec, int32_t* tokens_host, int n);
 /* copies block's KV ring [max_seq_len, kv_heads*head_dim] to the host (layer.KVCacheK / KVCacheV) */
 int loom_b200_decoder_download_cache(loom_b200_decoder* dec, int block, float* k_host, float* v_host);

@@ -361,6 +361,13 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
             cudaFree(ctx->trace_dev);
             ctx->trace_dev = nullptr;
         }
+    } else if (!strcmp(key, "gemv_wide")) {
+        LB_REQUIRE(ctx, value >= 0 && value <= 2, "ctx_set_option: gemv_wide is 0, 1 or 2");
+        ctx->opt_gemv_wide = value;
+    } else if (!strcmp(key, "head_stream")) {
+        ctx->opt_head_stream = value != 0;
+    } else if (!strcmp(key, "attn_cluster")) {
+        ctx->opt_attn_cluster = value != 0;
     } else if (!strcmp(key, "pdl")) {
         ctx->opt_pdl = value != 0;
     } else if (!strcmp(key, "fold_rope")) {
@@ -397,6 +404,7 @@ void loom_b200_ctx_destroy(loom_b200_ctx* ctx) {
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->trace_dev) cudaFree(ctx->trace_dev);
     if (ctx->argmax_scratch) cudaFree(ctx->argmax_scratch);
+    if (ctx->head_scratch) cudaFree(ctx->head_scratch);
     if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
     if (ctx->quant_scratch) cudaFree(ctx->quant_scratch);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);

@@ -62,7 +62,12 @@ struct loom_b200_ctx {
     void* gemm_scratch = nullptr;    // int8 activations, amax and sums of the tensor-core GEMM path
     size_t gemm_scratch_bytes = 0;
     void* argmax_scratch = nullptr;  // per-CTA partial maxima of the greedy argmax
+    void* head_scratch = nullptr;    // per-CTA partial maxima and arrival counter of the LM head's greedy tail
     unsigned func_attr_mask = 0;  // kernels whose shared-memory limit was raised on this device
+    unsigned func_attr_mask2 = 0; // the same for the cluster attention instantiations
+    int opt_gemv_wide = 1;        // sixteen-warp, one-CTA-per-SM GEMV: 0 = never, 1 = for float64 rows (after attention), 2 = every fused prologue
+    int opt_head_stream = 1;      // the LM head streams its rows through shared memory with bulk copies (0 = warp-per-row loads)
+    int opt_attn_cluster = 1;     // one-token decoder steps run the attention as a thread-block cluster per KV head
     // tuning knobs (loom_b200_ctx_set_option; initial values from LOOM_B200_* environment variables)
     int opt_gemv_variant = 0;      // 0 = integer-MMA inner loop, 1 = dp4a inner loop (batch 1 only)
     int opt_gemv_ctas_per_sm = 2;  // grid = SMs * this
@@ -151,17 +156,26 @@ __device__ __forceinline__ double lb_round_half_away(double x) {
 }
 
 // bitNetQuantizedActivation: int8(clamp(Round(float64(v) * (127/float64(amax))), -128, 127)), Round = half away from
-// zero.  Without conversion instructions: |r| + 2^52 rounds to the nearest integer (ties to even) in the low mantissa
-// bits; a tie that went to the even integer below is the only case where half-away differs, and |r| - n == 0.5 finds
-// it exactly.  Sign and clamp are applied to the integer.
+// zero = sign(r) * floor(|r| + 0.5).  Only full-rate instructions: float64 compares, min/max, rounding and conversions
+// issue at a quarter of the rate of add/multiply on this GPU (16 against 64 lanes per clock per SM, measured), so the
+// sign is handled on the bit pattern and the rounding by two additions.
 __device__ __forceinline__ int lb_quant_i8(double v, double s) {
     const double r = __dmul_rn(v, s);
-    const double a = fmin(fabs(r), 1048576.0);
-    const double magic = 4503599627370496.0;  // 2^52
-    const double u = __dadd_rn(a, magic);
-    int n = __double2loint(u);
-    if (__dsub_rn(a, __dsub_rn(u, magic)) == 0.5) n += 1;
-    return r < 0.0 ? -(n < 128 ? n : 128) : (n < 127 ? n : 127);
+    const int sgn = __double2hiint(r) & 0x80000000;
+    // copysign(0.5, r) and copysign(2^52, r).  Both additions round toward zero: |r| + 0.5 then never crosses an
+    // integer upwards (floor of the rounded sum = floor of the exact sum, because the floor itself is representable),
+    // and adding 2^52 leaves exactly floor(|r| + 0.5) = Round(|r|) in the low mantissa word, whatever the sign.
+    const double u = __dadd_rz(__dadd_rz(r, __hiloint2double(sgn | 0x3fe00000, 0)), __hiloint2double(sgn | 0x43300000, 0));
+    int n = __double2loint(u);  // |r| <= 127 (1 + 2^-52) by construction of s; anything larger saturates
+    const int lim = sgn ? 128 : 127;
+    n = (unsigned)n < (unsigned)lim ? n : lim;
+    return sgn ? -n : n;
+}
+
+// max(m, |y|) for float64 values kept as bit patterns: for non-negative doubles the integer order is the numeric order
+__device__ __forceinline__ unsigned long long lb_absmax_bits(unsigned long long m, double y) {
+    const unsigned long long b = (unsigned long long)__double_as_longlong(y) & 0x7fffffffffffffffull;
+    return b > m ? b : m;
 }
 
 // a / b with the reciprocal r = RN(1/b) computed once by the caller: q0 = RN(a*r), the exact remainder

@@ -53,6 +53,10 @@ struct loom_b200_decoder {
     const float* last_resid = nullptr;  // residual stream of the last pass (x or pf_x) and its rows
     int last_resid_rows = 0;
     int step_launches = 0;              // kernels of one recorded decode step (without the argmax)
+    // greedy step folded into the LM head's tail (one GPU, streaming head): the head's last CTA publishes the next token,
+    // appends it to the output ring, advances the position and gathers the next embedding row, so a step is
+    // {blocks, head} and needs no argmax, position or embedding launch
+    bool fused_tail = false;
 };
 
 namespace {
@@ -86,6 +90,19 @@ int dec_ensure_prefill(loom_b200_decoder* dec, int tokens) {
     LB_CUDA(ctx, cudaMalloc(&dec->pf_accu, T * d.intermediate * sizeof(int32_t)));
     dec->pf_cap = tokens;
     return 0;
+}
+
+// The greedy tail of a head launch that ends a pass of M tokens.
+void dec_fill_tail(loom_b200_decoder* dec, LbLmHeadParams& h, int M) {
+    h.tok_out = dec->tok;
+    h.out_tokens = dec->out_tokens;
+    h.out_cap = dec->out_cap;
+    h.step = dec->step;
+    h.pos = dec->pos;
+    h.pos_delta = M;
+    h.emb = dec->emb;
+    h.emb_vocab = dec->d.vocab;
+    h.x_next = dec->x;
 }
 
 // A block of M prompt tokens (already in pf_tok) at positions pos0..pos0+M-1 through the whole stack, every
@@ -223,19 +240,22 @@ int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
         h.hidden = H;
         h.logits = dec->logits;
         h.hidden_out = dec->hidden;
+        if (dec->fused_tail) dec_fill_tail(dec, h, M);
         if (int rc = lb_launch_lm_head(ctx, h)) return rc;
     }
     dec->last_resid = dec->pf_x;
     dec->last_resid_rows = M;
+    if (head && dec->fused_tail) return 0;  // the head's tail advanced the position
     return lb_launch_add_scalar(ctx, dec->pos, M);
 }
 
 // linears_only: just the ternary projections of the step, on the step's own buffers (a measurement frame: the
 // attention, the embedding, the head and the position update are left out, so nothing of the sequence state moves)
-int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int head_row, bool linears_only = false) {
+// embed: gather the rows of tok[0..M) first (false when the previous head's tail already left the row in x)
+int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int head_row, bool linears_only = false, bool embed = true) {
     loom_b200_ctx* ctx = dec->ctx;
     const loom_b200_decoder_dims& d = dec->d;
-    if (!linears_only)
+    if (!linears_only && embed)
         if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, d.hidden, dec->tok, M, dec->x)) return rc;
     for (auto& b : dec->blocks) {
         LbMhaStepArgs a = {};
@@ -292,12 +312,14 @@ int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int 
             h.vocab = vl;
             h.logits = dec->logits + (size_t)dec->tp_rank * vl;
         }
+        if (dec->fused_tail) dec_fill_tail(dec, h, M);
         if (int rc = lb_launch_lm_head(ctx, h)) return rc;
         if (dec->head_sharded)
             if (int rc = lb_tp_allgather_f32(ctx, h.logits, dec->logits, (size_t)h.vocab)) return rc;
     }
     dec->last_resid = dec->x;
     dec->last_resid_rows = M;
+    if (head && dec->fused_tail) return 0;  // the head's tail advanced the position
     return lb_launch_add_scalar(ctx, dec->pos, M);
 }
 
@@ -316,16 +338,22 @@ void dec_drop_graph(loom_b200_decoder* dec) {
     }
 }
 
-// One token from tok[0] at position *pos: eager the first time (sizes every scratch buffer), recorded after.
-int dec_step(loom_b200_decoder* dec) {
+// One token at position *pos: eager the first time (sizes every scratch buffer), recorded after.  The token is tok[0];
+// with the greedy tail folded into the head its embedding row is already in x unless the token came from the host
+// (host_token), in which case it is gathered by a launch of its own in front of the recorded frame.
+int dec_step(loom_b200_decoder* dec, bool host_token) {
     loom_b200_ctx* ctx = dec->ctx;
+    const loom_b200_decoder_dims& d = dec->d;
+    const bool in_frame = !dec->fused_tail;  // without the fused tail the gather is the first launch of the frame
+    if (dec->fused_tail && host_token)
+        if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, d.hidden, dec->tok, 1, dec->x)) return rc;
     if (dec->step_graph) return loom_b200_graph_launch(ctx, dec->step_graph);
     if (dec->tp_world > 1 && !ctx->opt_tp_graph) return dec_forward_chunk(dec, 1, dec->decode_splits, true, 0);
-    if (int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0)) return rc;  // warm-up run, counts as the step
+    if (int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0, false, in_frame)) return rc;  // warm-up run, counts as the step
     // record the same step for all later tokens
     if (int rc = loom_b200_graph_begin(ctx)) return rc;
     const uint64_t l0 = ctx->launches;
-    int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0);
+    int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0, false, in_frame);
     dec->step_launches = (int)(ctx->launches - l0);
     loom_b200_graph* g = nullptr;
     int rc2 = loom_b200_graph_end(ctx, &g);
@@ -492,6 +520,13 @@ int loom_b200_decoder_set_block(loom_b200_decoder* dec, int block, const float* 
     }
     LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     b.ready = true;
+    // the attention of a block prefetches the KV rows of the block that runs after it
+    for (size_t i = 0; i + 1 < dec->blocks.size(); ++i) {
+        if (dec->blocks[i].ready && dec->blocks[i + 1].ready) {
+            dec->blocks[i].mha.next_k = dec->blocks[i + 1].mha.cache_k;
+            dec->blocks[i].mha.next_v = dec->blocks[i + 1].mha.cache_v;
+        }
+    }
     return 0;
 }
 
@@ -503,6 +538,7 @@ int loom_b200_decoder_set_embeddings(loom_b200_decoder* dec, const float* emb_de
     if (int rc = lb_set_device(ctx)) return rc;
     dec_drop_graph(dec);
     dec->emb = emb_dev;
+    dec->fused_tail = dec->tp_world == 1 && lb_lm_head_streams(ctx, emb_dev, dec->d.hidden);
     const int H = dec->d.hidden;
     std::vector<float> ones(H, 1.0f);
     if (!dec->final_gain) LB_CUDA(ctx, cudaMalloc(&dec->final_gain, (size_t)H * 4));
@@ -541,7 +577,7 @@ int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int
     if (n == 1) {
         dec->h_tok[0] = tokens[0];
         LB_CUDA(ctx, cudaMemcpyAsync(dec->tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
-        if (int rc = dec_step(dec)) return rc;
+        if (int rc = dec_step(dec, true)) return rc;
     } else if (n >= kGemmMinTokens && dec->tp_world == 1 && ctx->opt_prefill_gemm) {
         const int cap = n < kPrefillBlock ? n : kPrefillBlock;
         if (int rc = dec_ensure_prefill(dec, cap)) return rc;
@@ -591,8 +627,9 @@ int loom_b200_decoder_continue(loom_b200_decoder* dec, int steps) {
     if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_continue cannot be recorded");
     if (int rc = lb_set_device(ctx)) return rc;
     for (int i = 0; i < steps; ++i) {
-        if (int rc = lb_launch_argmax_advance(ctx, dec->logits, dec->d.vocab, dec->tok, dec->out_tokens, dec->out_cap, dec->step, nullptr)) return rc;
-        if (int rc = dec_step(dec)) return rc;
+        if (!dec->fused_tail)
+            if (int rc = lb_launch_argmax_advance(ctx, dec->logits, dec->d.vocab, dec->tok, dec->out_tokens, dec->out_cap, dec->step, nullptr)) return rc;
+        if (int rc = dec_step(dec, false)) return rc;
     }
     dec->kv_offset += steps;
     return 0;
@@ -617,7 +654,7 @@ int loom_b200_decoder_set_kv_offset(loom_b200_decoder* dec, int kv_offset) {
     return 0;
 }
 
-int loom_b200_decoder_step_launches(const loom_b200_decoder* dec) { return dec ? dec->step_launches + 1 : -1; }
+int loom_b200_decoder_step_launches(const loom_b200_decoder* dec) { return dec ? dec->step_launches + (dec->fused_tail ? 0 : 1) : -1; }
 
 int loom_b200_decoder_linears_frame(loom_b200_decoder* dec) {
     if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_linears_frame: decoder is NULL");
@@ -637,8 +674,10 @@ int loom_b200_decoder_read_tokens(loom_b200_decoder* dec, int32_t* tokens_host, 
     if (int rc = lb_sync_checked(ctx)) return rc;
     int step = 0;
     LB_CUDA(ctx, cudaMemcpy(&step, dec->step, sizeof(int), cudaMemcpyDeviceToHost));
-    LB_REQUIRE(ctx, n <= step && step <= dec->out_cap, "decoder_read_tokens: %d tokens asked, %d sampled since the last reset (ring of %d)", n, step, dec->out_cap);
-    LB_CUDA(ctx, cudaMemcpy(tokens_host, dec->out_tokens + (step - n), (size_t)n * sizeof(int), cudaMemcpyDeviceToHost));
+    // with the greedy tail folded into the head, the newest entry of the ring is the token the NEXT step will consume
+    const int consumed = dec->fused_tail ? step - 1 : step;
+    LB_REQUIRE(ctx, n <= consumed && step <= dec->out_cap, "decoder_read_tokens: %d tokens asked, %d consumed since the last reset (ring of %d)", n, consumed, dec->out_cap);
+    LB_CUDA(ctx, cudaMemcpy(tokens_host, dec->out_tokens + (consumed - n), (size_t)n * sizeof(int), cudaMemcpyDeviceToHost));
     return 0;
 }
 
@@ -698,7 +737,7 @@ int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, in
         if (int rc = loom_b200_decoder_reset(dec)) return rc;
         dec->h_tok[0] = prompt[0];
         LB_CUDA(ctx, cudaMemcpyAsync(dec->tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
-        if (int rc = dec_step(dec)) return rc;
+        if (int rc = dec_step(dec, true)) return rc;
         dec->kv_offset = 1;
     } else {
         if (int rc = loom_b200_decoder_forward(dec, prompt, n_prompt, nullptr)) return rc;
@@ -712,8 +751,9 @@ int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, in
     LB_CUDA(ctx, cudaEventRecord(e0, ctx->stream));
     // every sampled token is followed by a forward, the last one included (as Generate does)
     for (int i = 0; i < max_new; ++i) {
-        if (int rc = lb_launch_argmax_advance(ctx, dec->logits, dec->d.vocab, dec->tok, dec->out_tokens, dec->out_cap, dec->step, nullptr)) return rc;
-        if (int rc = dec_step(dec)) return rc;
+        if (!dec->fused_tail)
+            if (int rc = lb_launch_argmax_advance(ctx, dec->logits, dec->d.vocab, dec->tok, dec->out_tokens, dec->out_cap, dec->step, nullptr)) return rc;
+        if (int rc = dec_step(dec, false)) return rc;
     }
     LB_CUDA(ctx, cudaEventRecord(e1, ctx->stream));
     if (max_new > 0)
@@ -731,8 +771,9 @@ int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, in
         metrics->decode_device_seconds = ms * 1e-3;
         metrics->prefill_tokens = n_prompt;
         metrics->generated_tokens = max_new;
-        // per block: QKV, (RoPE unless folded into attention), attention, O, gate/up, down; + embed, head, position, argmax
-        metrics->launches_per_token = max_new > 0 ? (double)(dec->blocks.size() * (ctx->opt_fold_rope ? 5 : 6) + 4) : 0.0;
+        // per block: QKV, (RoPE unless folded into attention), attention, O, gate/up, down; + head (+ argmax, embed, position
+        // when the greedy tail is not folded into the head)
+        metrics->launches_per_token = max_new > 0 ? (double)(dec->step_launches + (dec->fused_tail ? 0 : 1)) : 0.0;
         (void)launches0;
     }
     return 0;

@@ -27,9 +27,12 @@
 namespace {
 
 
-template <bool MMA, int PRO, int EPI>
-__global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __grid_constant__ LbGemvParams p) {
+// NW = warps per CTA: kWarps (eight, two CTAs per SM: the general kernel) or kWideWarps (sixteen, one CTA per SM, with the
+// register-resident prologue: one-token launches whose critical path is the activation prologue, not the weight stream)
+template <bool MMA, int PRO, int EPI, int NW = kWarps>
+__global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ternary_kernel(const __grid_constant__ LbGemvParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
+    constexpr int kWarps = NW, kThreads = NW * 32;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int KB = p.kblocks, M = p.M;
     const int Kp = KB * kTileCols;
@@ -59,25 +62,30 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         ptr += kWarps * kStages * 8;
         sm.stage = p.stage_bytes > 0 ? (void*)ptr : nullptr;
         ptr += p.stage_bytes;
-        sm.gain = p.gain_bytes > 0 ? reinterpret_cast<float*>(ptr) : nullptr;
+        sm.gain = (p.gain_bytes > 0 && NW != kWideWarps) ? reinterpret_cast<float*>(ptr) : nullptr;
+        sm.gaind = (p.gain_bytes > 0 && NW == kWideWarps) ? reinterpret_cast<double*>(ptr) : nullptr;
+        sm.pos0 = 0;
     }
 
     // ---- tile ranges --------------------------------------------------------------------------------
     // aligned: every CTA owns whole strip groups (no cross-CTA fix-up); otherwise stream-K over tiles.
-    int t0, t1;
+    int t0, t1, first_group;
     if (p.aligned) {
-        const long long NG = p.total_tiles / (p.group * KB);
-        t0 = (int)(NG * blockIdx.x / gridDim.x) * p.group * KB;
-        t1 = (int)(NG * (blockIdx.x + 1) / gridDim.x) * p.group * KB;
+        const int b = (int)blockIdx.x;
+        const int g0 = b * p.part_q + (b < p.part_r ? b : p.part_r);
+        const int g1 = g0 + p.part_q + (b < p.part_r ? 1 : 0);
+        t0 = g0 * p.group * KB;
+        t1 = g1 * p.group * KB;
+        first_group = g0;
     } else {
         const long long T = p.total_tiles;
         t0 = (int)(T * blockIdx.x / gridDim.x);
         t1 = (int)(T * (blockIdx.x + 1) / gridDim.x);
+        first_group = t1 > t0 ? (t0 / KB) / p.group : 0;
     }
     const int cta_tiles = t1 - t0;
-    const int w0 = t0 + (int)((long long)cta_tiles * warp / kWarps);
-    const int w1 = t0 + (int)((long long)cta_tiles * (warp + 1) / kWarps);
-    const int first_group = cta_tiles > 0 ? (t0 / KB) / p.group : 0;
+    const int w0 = t0 + (int)(((unsigned)cta_tiles * (unsigned)warp) / (unsigned)kWarps);  // kWarps is a power of two
+    const int w1 = t0 + (int)(((unsigned)cta_tiles * (unsigned)(warp + 1)) / (unsigned)kWarps);
     const int local_v0 = first_group * p.group;  // virtual strip held in sacc slot 0
 
     LB_TRACE(0);
@@ -118,8 +126,14 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     // first ring fill: weights do not depend on the producer of the activations
     Cursor ic;
     ic.pos = w0;
-    ic.v = w0 / KB;
-    ic.kb = w0 - ic.v * KB;
+    if (p.aligned && KB > 1 && KB <= 256 && (unsigned)(w0 - t0) < 65536u) {  // t0 is a strip boundary: only the small offset needs dividing
+        const int dv = (int)__umulhi((unsigned)(w0 - t0), p.kb_magic);
+        ic.v = local_v0 + dv;
+        ic.kb = (w0 - t0) - dv * KB;
+    } else {
+        ic.v = w0 / KB;
+        ic.kb = w0 - ic.v * KB;
+    }
     Cursor cc = ic;
     for (int s = 0; s < nstages && ic.pos < w1; ++s) {
         int len = chunk_len(ic);
@@ -133,11 +147,29 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         for (int i = tid; i < n4; i += kThreads) reinterpret_cast<float4*>(sm.gain)[i] = __ldg(reinterpret_cast<const float4*>(p.norm_w) + i);
         for (int i = (n4 << 2) + tid; i < p.norm_w_len; i += kThreads) sm.gain[i] = __ldg(p.norm_w + i);
     }
+    if (sm.gaind) {  // widened here, off the critical path, so that the prologue has no conversion per gain
+        const int n4 = p.norm_w_len >> 2;
+        for (int i = tid; i < n4; i += kThreads) {
+            const float4 g = __ldg(reinterpret_cast<const float4*>(p.norm_w) + i);
+            reinterpret_cast<double2*>(sm.gaind)[2 * i] = make_double2((double)g.x, (double)g.y);
+            reinterpret_cast<double2*>(sm.gaind)[2 * i + 1] = make_double2((double)g.z, (double)g.w);
+        }
+        for (int i = (n4 << 2) + tid; i < p.norm_w_len; i += kThreads) sm.gaind[i] = (double)__ldg(p.norm_w + i);
+    }
     lb_pdl_launch_dependents();  // the next launch may start prefetching its weights
     LB_TRACE(1);
     lb_pdl_wait();               // everything below may read what earlier launches wrote
     LB_TRACE(2);
-    stage_activations<PRO>(p, sm);
+    if (p.pos_ptr) sm.pos0 = *p.pos_ptr;
+    if (EPI == LB_EPI_RESID && M == 1 && cta_tiles > 0) {
+        // the epilogue's operands of this CTA's rows: requested now, so that they are in L1 when the sums are done
+        const int row0 = (t0 / KB) * kTileRows, nrows = ((t1 - 1) / KB + 1) * kTileRows - row0;
+        if (tid < nrows && row0 + tid < p.seg[0].rows) {
+            if (p.residual) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.residual + row0 + tid));
+            if (p.seg[0].bias) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.seg[0].bias + row0 + tid));
+        }
+    }
+    stage_activations<PRO, NW>(p, sm);
     LB_TRACE(3);
 
     // ---- main loop ------------------------------------------------------------------------------------
@@ -229,12 +261,18 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
 
     int cstage = 0;
     uint32_t cphase = 0;
+    long long lc[9];
+    lc[0] = clock64();
+#pragma unroll
+    for (int i = 1; i < 9; ++i) lc[i] = lc[0];
+    int n_iter = 0;
     while (cc.pos < w1) {
         const int len = chunk_len(cc);
         if (!failed && !lb_mbar_wait_bounded(&my_bars[cstage], cphase)) {
             failed = true;
             if (lane == 0) atomicExch(p.status, 1);
         }
+        if (n_iter == 0) lc[1] = clock64();
         if (cc.v != cur_v) {
             flush();
             cur_v = cc.v;
@@ -249,6 +287,8 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
                 for (int i = 0; i < len; ++i) tile_step(tile + i * kTileBytes, ab + i * act_kb_mul);
             }
         }
+        if (n_iter == 0 && acc[0][0] != 0x7fffffff) lc[2] = clock64();
+        ++n_iter;
         advance(cc, len);
         __syncwarp();
         if (ic.pos < w1) {
@@ -264,15 +304,42 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
             cphase ^= 1u;
         }
     }
+    lc[3] = clock64();
     flush();
+    lc[4] = clock64();
     __syncthreads();
+    lc[5] = clock64();
     LB_TRACE(4);
 
     // ---- strip groups: finish what this CTA owns entirely, hand the rest to the fix-up ------------------
     if (cta_tiles <= 0) return;
     const int group_tiles = p.group * KB;
-    const int last_group = ((t1 - 1) / KB) / p.group;
     const int per_group = p.group * M * 16;
+    if (p.aligned) {  // every group is this CTA's own: no fix-up, no flags
+        const int ngl_a = p.part_q + ((int)blockIdx.x < p.part_r ? 1 : 0);
+        lc[6] = clock64();
+        for (int idx = tid; idx < ngl_a * per_group; idx += kThreads) {
+            int gl, i;
+            if (per_group == 16) {
+                gl = idx >> 4;
+                i = idx & 15;
+            } else {
+                gl = idx / per_group;
+                i = idx - gl * per_group;
+            }
+            const int e = i / (M * 16), rem = i - e * (M * 16);
+            finish_row<EPI>(p, sm, (first_group + gl) * p.group, e, rem >> 4, rem & 15, sm.sacc + (size_t)gl * per_group);
+        }
+        if (p.trace_loop && blockIdx.x == 0 && tid == 0) {
+            lc[7] = clock64();
+#pragma unroll
+            for (int i = 0; i < 7; ++i) p.trace_loop[i] = (unsigned long long)(lc[i + 1] - lc[i]);
+            p.trace_loop[7] = (unsigned long long)(w1 - w0);
+        }
+        LB_TRACE(5);
+        return;
+    }
+    const int last_group = ((t1 - 1) / KB) / p.group;
     const int ngl = last_group - first_group + 1;
     // Only the first and the last group of a stream-K range can be shared with another CTA.
     auto mine_of = [&](int G) {
@@ -316,6 +383,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         }
     }
     __syncthreads();
+    lc[6] = clock64();
     const bool do_first = sm.flag[0] != 0, do_last = sm.flag[1] != 0;
     for (int idx = tid; idx < ngl * per_group; idx += kThreads) {
         const int gl = idx / per_group, i = idx - gl * per_group;
@@ -324,17 +392,24 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         const int e = i / (M * 16), rem = i - e * (M * 16);
         finish_row<EPI>(p, sm, (first_group + gl) * p.group, e, rem >> 4, rem & 15, sm.sacc + (size_t)gl * per_group);
     }
+    if (p.trace_loop && blockIdx.x == 0 && tid == 0) {
+        // thread 0's clocks: first weights there, first chunk done, loop done, flushed, all warps done, fix-up decided, rows finished; tiles of warp 0
+        lc[7] = clock64();
+#pragma unroll
+        for (int i = 0; i < 7; ++i) p.trace_loop[i] = (unsigned long long)(lc[i + 1] - lc[i]);
+        p.trace_loop[7] = (unsigned long long)(w1 - w0);
+    }
     LB_TRACE(5);
 }
 
-size_t gemv_smem_bytes(const LbGemvParams& p, int max_local) {
+size_t gemv_smem_bytes(const LbGemvParams& p, int max_local, int nw) {
     int Kp = p.kblocks * kTileCols;
-    size_t b = (size_t)kWarps * p.stages * kStageBytes;
+    size_t b = (size_t)nw * p.stages * kStageBytes;
     b += (size_t)(p.M * ((Kp + 16) / 4) + 8) * 4;
     b = (b + 15) & ~(size_t)15;
     b += (size_t)max_local * p.M * 16 * 4;
     b += 32 + 32 + 256 + 3 * kMaxM * 8 + 16;
-    b += (size_t)kWarps * kStages * 8;
+    b += (size_t)nw * kStages * 8;
     b = (b + 15) & ~(size_t)15;
     b += (size_t)p.stage_bytes;
     b += (size_t)p.gain_bytes;
@@ -378,7 +453,7 @@ int lb_gemv_finalize_params(loom_b200_ctx* ctx, LbGemvParams& p) {
 }
 
 // Partition, ring depth and shared-memory footprint for a grid of SMs x cps CTAs.
-static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int* grid_out, size_t* smem_out) {
+static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int nw, int* grid_out, size_t* smem_out) {
     int vstrips = p.total_tiles / p.kblocks;
     int ngroups = (vstrips + p.group - 1) / p.group;
     int grid = ctx->sm_count * cps;
@@ -388,6 +463,9 @@ static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int* g
         if (grid > ngroups) grid = ngroups;
         int gpc = (ngroups + grid - 1) / grid;
         p.max_local_strips = gpc * p.group;
+        p.part_q = ngroups / grid;
+        p.part_r = ngroups % grid;
+        p.kb_magic = (unsigned)((0x100000000ull + (unsigned long long)p.kblocks - 1) / (unsigned long long)p.kblocks);
     } else {
         if (grid > p.total_tiles) grid = p.total_tiles;
         if (grid < 1) grid = 1;
@@ -402,15 +480,16 @@ static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int* g
         for (int b = 0; b < grid && most < kStages; ++b) {
             long long t0, t1;
             if (p.aligned) {
-                t0 = (NG * b / grid) * gt;
-                t1 = (NG * (b + 1) / grid) * gt;
+                const long long g0 = (long long)b * p.part_q + (b < p.part_r ? b : p.part_r);
+                t0 = g0 * gt;
+                t1 = (g0 + p.part_q + (b < p.part_r ? 1 : 0)) * gt;
             } else {
                 t0 = (long long)p.total_tiles * b / grid;
                 t1 = (long long)p.total_tiles * (b + 1) / grid;
             }
             const long long n = t1 - t0;
-            for (int w = 0; w < kWarps && most < kStages; ++w) {
-                long long w0 = t0 + n * w / kWarps, w1 = t0 + n * (w + 1) / kWarps;
+            for (int w = 0; w < nw && most < kStages; ++w) {
+                long long w0 = t0 + n * w / nw, w1 = t0 + n * (w + 1) / nw;
                 int chunks = 0;
                 while (w0 < w1) {
                     long long len = KB - w0 % KB;
@@ -427,19 +506,19 @@ static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int* g
     // prologue staging: the activation row in its input precision, when it fits beside the ring
     p.stage_bytes = 0;
     p.gain_bytes = 0;
-    if (p.pro != LB_PRO_Q8 && (p.K & 3) == 0) {
+    const bool wide = nw == kWideWarps;  // the sixteen-warp variant keeps the row in registers: no staging buffer
+    if (!wide && p.pro != LB_PRO_Q8 && (p.K & 3) == 0) {
         size_t want = (size_t)p.K * (p.pro == LB_PRO_INNERNORM64 ? 8 : 4);
-        if (gemv_smem_bytes(p, p.max_local_strips) + want <= 227 * 1024) p.stage_bytes = (int)want;
+        if (gemv_smem_bytes(p, p.max_local_strips, nw) + want <= 227 * 1024) p.stage_bytes = (int)want;
     }
-    p.gain_bytes = 0;
-    if (p.stage_bytes > 0 && p.pro >= LB_PRO_BLOCKNORM && p.norm_w && p.norm_w_len > 0 && (((uintptr_t)p.norm_w) & 15) == 0) {
-        const size_t want = ((size_t)p.norm_w_len * 4 + 15) & ~(size_t)15;
-        if (gemv_smem_bytes(p, p.max_local_strips) + want <= 227 * 1024) p.gain_bytes = (int)want;
+    if ((wide || p.stage_bytes > 0) && p.pro >= LB_PRO_BLOCKNORM && p.norm_w && p.norm_w_len > 0 && (((uintptr_t)p.norm_w) & 15) == 0) {
+        const size_t want = ((size_t)p.norm_w_len * (wide ? 8 : 4) + 15) & ~(size_t)15;
+        if (gemv_smem_bytes(p, p.max_local_strips, nw) + want <= 227 * 1024) p.gain_bytes = (int)want;
     }
-    size_t smem = gemv_smem_bytes(p, p.max_local_strips);
+    size_t smem = gemv_smem_bytes(p, p.max_local_strips, nw);
     while (smem > 227 * 1024 && p.stages > 1) {  // wide inputs: a shallower ring before giving up
         --p.stages;
-        smem = gemv_smem_bytes(p, p.max_local_strips);
+        smem = gemv_smem_bytes(p, p.max_local_strips, nw);
     }
     *grid_out = grid;
     *smem_out = smem;
@@ -473,18 +552,33 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     size_t smem = 0;
     int cps = ctx->opt_gemv_ctas_per_sm;
     if (p.K >= 16384 && cps > 1) cps = 1;  // very wide rows: every CTA stages the whole int8 row, so fewer, longer CTAs win (measured)
-    gemv_plan(ctx, p, cps, &grid, &smem);
+    // One or two tokens with the inner norm of a float64 row fused in (the attention output): the prologue, which every CTA
+    // repeats, is the critical path, and the launch before it (the attention clusters) leaves SMs free, so one sixteen-warp
+    // CTA per SM with the row in registers beats two eight-warp CTAs that both stage it (measured: 6.1 against 7.1 us).  After
+    // a launch that fills every SM the sixteen-warp CTA cannot become resident early and loses what its prologue gains, so
+    // the other prologues keep the eight-warp kernel (option "gemv_wide" = 2 uses the sixteen-warp one for all of them).
+    const bool aligned_ptrs = (((uintptr_t)p.x) & 15) == 0 && (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) &&
+                              (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) && (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0);
+    const bool wide = (ctx->opt_gemv_wide == 2 || (ctx->opt_gemv_wide == 1 && p.pro == LB_PRO_INNERNORM64)) &&
+                      p.pro != LB_PRO_Q8 && p.M <= 2 && (p.K & 3) == 0 && aligned_ptrs &&
+                      p.kblocks * kTileCols <= kRegUnits * 4 * kWideWarps * 32 &&
+                      (p.epi == LB_EPI_QKV || p.epi == LB_EPI_RESID || p.epi == LB_EPI_SWIGLU || (p.epi == LB_EPI_GENERIC && p.pro == LB_PRO_F32));
+    const int nw = wide ? kWideWarps : kWarps;
+    if (wide) cps = 1;
+    gemv_plan(ctx, p, cps, nw, &grid, &smem);
     // A grid sized for more CTAs per SM than the shared memory lets be resident would run in waves, and every
     // wave repeats the prologue: fall back to what fits (228 KB per SM, 1 KB reserved per CTA).
     while (cps > 1 && (smem + 1024) * (size_t)cps > 228 * 1024) {
         --cps;
-        gemv_plan(ctx, p, cps, &grid, &smem);
+        gemv_plan(ctx, p, cps, nw, &grid, &smem);
     }
     if (int rc = lb_ensure_fixup(ctx, (size_t)ngroups * p.group * p.M * 16, (size_t)ngroups)) return rc;
     p.fix_acc = ctx->fix_acc;
     p.fix_cnt = ctx->fix_cnt;
     p.status = ctx->status_dev;
     p.trace = lb_trace_row(ctx, "gemv");
+    p.trace_pro = wide ? lb_trace_row(ctx, "gemv-pro") : nullptr;
+    p.trace_loop = ctx->trace_dev ? lb_trace_row(ctx, "gemv-loop") : nullptr;
     if (smem > 227 * 1024)
         return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: K=%d with %d tokens needs %zu B of shared memory", p.K, p.M, smem);
     // one instantiation per (inner loop, prologue, epilogue) combination that a caller can reach
@@ -493,8 +587,13 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     int kid = -1;
     const bool use_dp4a = ctx->opt_gemv_variant == 1 && p.M == 1 && p.pro == LB_PRO_Q8 && p.epi == LB_EPI_GENERIC;
 #define LB_PICK(id, mma, pro_, epi_)                                \
-    if (kid < 0 && p.pro == pro_ && p.epi == epi_ && (mma) == !use_dp4a) { \
+    if (kid < 0 && !wide && p.pro == pro_ && p.epi == epi_ && (mma) == !use_dp4a) { \
         kern = lb_gemv_ternary_kernel<mma, pro_, epi_>;             \
+        kid = id;                                                   \
+    }
+#define LB_PICK_WIDE(id, pro_, epi_)                                \
+    if (kid < 0 && wide && p.pro == pro_ && p.epi == epi_) {        \
+        kern = lb_gemv_ternary_kernel<true, pro_, epi_, kWideWarps>; \
         kid = id;                                                   \
     }
     LB_PICK(0, true, LB_PRO_Q8, LB_EPI_GENERIC)
@@ -511,7 +610,15 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     LB_PICK(11, true, LB_PRO_Q8, LB_EPI_SWIGLU)
     LB_PICK(12, true, LB_PRO_Q8, LB_EPI_QKV)
     LB_PICK(13, true, LB_PRO_Q8, LB_EPI_RESID)
+    LB_PICK_WIDE(14, LB_PRO_BLOCKNORM, LB_EPI_QKV)
+    LB_PICK_WIDE(15, LB_PRO_INNERNORM64, LB_EPI_RESID)
+    LB_PICK_WIDE(16, LB_PRO_BLOCKNORM, LB_EPI_SWIGLU)
+    LB_PICK_WIDE(17, LB_PRO_INNERNORM, LB_EPI_RESID)
+    LB_PICK_WIDE(18, LB_PRO_F32, LB_EPI_GENERIC)
+    LB_PICK_WIDE(19, LB_PRO_F32, LB_EPI_QKV)
+    LB_PICK_WIDE(20, LB_PRO_F32, LB_EPI_SWIGLU)
 #undef LB_PICK
+#undef LB_PICK_WIDE
     if (!kern) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: no kernel for prologue %d with epilogue %d", p.pro, p.epi);
     const unsigned attr_bit = 1u << kid;
     if (!(ctx->func_attr_mask & attr_bit)) {  // per device: the context pins the device
@@ -520,7 +627,7 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(nw * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];

@@ -58,6 +58,10 @@ struct LbGemvParams {
     int stage_bytes;  // shared staging for the fp32/fp64 prologues (0 = use the slow generic prologue)
     int gain_bytes;   // shared copy of norm_w, made before the dependency wait (0 = read norm_w from global memory)
     int aligned;  // 1: CTAs own whole strip groups; 0: stream-K with the int32 fix-up
+    // aligned partition without divisions in the kernel: CTA b owns groups [b*part_q + min(b, part_r), +part_q (+1 if b < part_r));
+    // kb_magic = ceil(2^32 / kblocks) turns an offset below 65536 tiles into (strip, k-block) with one multiply
+    int part_q, part_r;
+    unsigned kb_magic;
     // prologue
     int pro;
     const void* x;
@@ -81,6 +85,8 @@ struct LbGemvParams {
     unsigned int* fix_cnt;
     int* status;
     unsigned long long* trace;  // optional row of 8 phase timestamps (ns) written by CTA 0, or null
+    unsigned long long* trace_loop;  // optional third row: clock counts of warp 0's main loop and epilogue
+    unsigned long long* trace_pro;  // optional second row: clock counts of the prologue's parts (register-resident variant)
 };
 
 // Launches the GEMV on ctx->stream (programmatic dependent launch unless disabled).

@@ -791,7 +791,8 @@ int lb_launch_attention_prefill(loom_b200_ctx* ctx, const LbAttnParams& pin) {
     return 0;
 }
 
-int lb_launch_lm_head(loom_b200_ctx* ctx, const LbLmHeadParams& pin) {
+// the warp-per-row kernel with plain loads: hidden sizes the streaming kernel (lm_head.cu) has no room for, or unaligned tables
+int lb_launch_lm_head_legacy(loom_b200_ctx* ctx, const LbLmHeadParams& pin) {
     LbLmHeadParams p = pin;
     p.trace = lb_trace_row(ctx, "lm_head");
     size_t smem = (size_t)p.hidden * sizeof(double);

@@ -39,10 +39,17 @@ struct LbAttnParams {
     const double* rope_div;
     const float* k_new;
     float* cache_k_w;
+    // cluster kernel only: the K and V rings of the decoder block that runs next (same layout), prefetched into L2; or null
+    const float* next_k;
+    const float* next_v;
     unsigned long long* trace;
     int* status;           // device status word for bounded waits
 };
 int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p);
+// One-token steps with RoPE folded in: the cluster kernel (attention_decode.cu).  lb_attention_cluster_size returns the
+// cluster size to use (CTAs per KV head), or 0 when the shape or the device does not allow it; the launch takes that size.
+int lb_attention_cluster_size(loom_b200_ctx* ctx, const LbAttnParams& p);
+int lb_launch_attention_cluster(loom_b200_ctx* ctx, const LbAttnParams& p, int cluster);
 size_t lb_attn_part_elems(int M, int heads, int hd, int splits);
 // The same attention for a block of M prompt tokens at once (splits, part and cnt are not used): K/V tiles are shared
 // by the heads of a GQA group and by 64/group consecutive query tokens.  Needs head_dim % 16 == 0, head_dim <= 128
@@ -59,8 +66,28 @@ struct LbLmHeadParams {
     float* logits;         // [vocab]
     float* hidden_out;     // optional [hidden]: the normalised row
     unsigned long long* trace;
+    // Greedy tail (tok_out == null: none).  The CTA that finishes last takes the first maximum of the logits
+    // (poly/sampling.go:45-55), publishes it as the next token, appends it to the output ring (out_tokens[*step], then
+    // *step += 1), advances *pos by pos_delta (pos may be null) and gathers the token's embedding row into x_next
+    // (may be null): what lb_argmax_advance_kernel, lb_add_scalar_kernel and lb_embed_kernel did as three more launches.
+    int* tok_out;
+    int* out_tokens;
+    int out_cap;
+    int* step;
+    int* pos;
+    int pos_delta;
+    const float* emb;      // [emb_vocab, hidden] embedding table of the next token (the head itself when tied)
+    int emb_vocab;
+    float* x_next;
+    // scratch of the tail, set by the launcher: per-CTA (value, index) and the arrival counter (zero between launches)
+    float* part_val;
+    int* part_idx;
+    unsigned int* cnt;
+    int* status;
 };
 int lb_launch_lm_head(loom_b200_ctx* ctx, const LbLmHeadParams& p);
+// whether the streaming head (the one that can carry the greedy tail) takes this table
+bool lb_lm_head_streams(const loom_b200_ctx* ctx, const float* head, int hidden);
 
 // Greedy step: first index of the maximum (poly/sampling.go:45-55) -> tok[0]; appends it to
 // out_tokens[*step]; then *step += 1 and *pos += 1 so that a recorded frame can be replayed as is.

@@ -175,6 +175,14 @@ int lb_mha_attn_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
         t.rope_div = m->rope_div;
         t.k_new = m->k_new;
         t.cache_k_w = m->cache_k;
+        if (ctx->opt_attn_cluster) {
+            if (m->attn_cluster < 0) m->attn_cluster = lb_attention_cluster_size(ctx, t);
+            if (m->attn_cluster > 0) {
+                t.next_k = m->next_k;
+                t.next_v = m->next_v;
+                return lb_launch_attention_cluster(ctx, t, m->attn_cluster);
+            }
+        }
     }
     return lb_launch_attention(ctx, t);
 }

@@ -1,0 +1,235 @@
+// lm_head.cu -- the fp32 tied LM head as a streaming kernel: logits[v] = float(sum_d float64(h_d) * float64(W_vd)) over the
+// final-normalised hidden row (applyFP32LMHeadRows, poly/transformer.go:659-719; final RMSNorm poly/norm.go:102-138),
+// with the greedy step folded into its tail (poly/sampling.go:45-55, poly/transformer.go:434-485).
+//
+// The head is 63 % of the bytes of a BitNet-2B decode step (1.31 GB), so this kernel is a pure HBM stream: one CTA per
+// SM, every warp owns a contiguous range of vocabulary rows and pulls them through a private two-stage shared-memory
+// ring with one bulk async copy (TMA engine) per row, first two rows requested before the dependency wait.  The
+// normalised hidden row sits in shared memory as float64 in the order the lanes read it (conflict-free 16-byte loads).
+// The CTA that finishes last reduces the per-CTA maxima to the next token, appends it to the output ring, advances the
+// position and gathers the token's embedding row for the next step: no argmax, position or embedding launch.
+#include "glue.cuh"
+
+namespace {
+
+__device__ __forceinline__ void argmax_merge(float& best, int& idx, float ov, int oi) {
+    if (ov > best || (ov == best && oi < idx)) {
+        best = ov;
+        idx = oi;
+    }
+}
+
+template <int NW>
+__global__ void __launch_bounds__(NW * 32, 1) lb_lm_head_stream_kernel(const LbLmHeadParams p) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ double red[32];
+    __shared__ float sv[NW];
+    __shared__ int si[NW];
+    __shared__ int s_last, s_tok;
+    constexpr int T = NW * 32;
+    const int H = p.hidden, H4 = H >> 2, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kiter = (H4 + 31) >> 5;                       // float4 columns per lane
+    double* sh = reinterpret_cast<double*>(smem_raw);      // [kiter][2][32][2] doubles: the row in lane order, zero padded
+    const size_t sh_bytes = (size_t)kiter * 128 * sizeof(double);
+    float* ring = reinterpret_cast<float*>(smem_raw + sh_bytes) + (size_t)warp * 2 * H;  // this warp's two stages of one row
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + sh_bytes + (size_t)NW * 2 * H * sizeof(float)) + warp * 2;
+    // rows of this CTA and of this warp: contiguous slices
+    const int r0 = (int)((long long)p.vocab * blockIdx.x / gridDim.x), r1 = (int)((long long)p.vocab * (blockIdx.x + 1) / gridDim.x);
+    const int w0 = r0 + (r1 - r0) * warp / NW, w1 = r0 + (r1 - r0) * (warp + 1) / NW;
+    const uint32_t row_bytes = (uint32_t)H * 4;
+    if (lane == 0) {
+        lb_mbar_init(&bars[0], 1);
+        lb_mbar_init(&bars[1], 1);
+        lb_fence_mbar_init();
+    }
+    __syncwarp();
+    lb_pdl_launch_dependents();
+    // the head is a weight: its first rows are requested while the last block is still running
+    if (lane == 0) {
+        for (int s = 0; s < 2 && w0 + s < w1; ++s) {
+            lb_mbar_expect_tx(&bars[s], row_bytes);
+            lb_bulk_g2s(ring + (size_t)s * H, p.head + (size_t)(w0 + s) * H, row_bytes, &bars[s]);
+        }
+    }
+    lb_pdl_wait();
+    lb_trace(p.trace, 2);
+    // final RMSNorm of the hidden row (float64 like the reference), rounded to float32 and kept as float64
+    double ss = 0.0;
+    for (int i = tid; i < H; i += T) {
+        const double v = (double)p.x[i];
+        ss = __dadd_rn(ss, __dmul_rn(v, v));
+    }
+    ss = lb_warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    ss = 0.0;
+    for (int i = 0; i < NW; ++i) ss += red[i];
+    const double rms = sqrt(__dadd_rn(__ddiv_rn(ss, (double)H), p.eps));
+    const double rrms = __ddiv_rn(1.0, rms);
+    for (int i = tid; i < kiter * 128; i += T) {
+        // slot i holds column 4 * (k * 32 + l) + 2 * half + j
+        const int j = i & 1, l = (i >> 1) & 31, half = (i >> 6) & 1, k = i >> 7;
+        const int col = 4 * (k * 32 + l) + 2 * half + j;
+        double y = 0.0;
+        if (col < H) {
+            const double g = p.gain ? (double)p.gain[col] : 1.0;
+            const float yf = (float)__dmul_rn(lb_div_by((double)p.x[col], rms, rrms), g);
+            y = (double)yf;
+            if (blockIdx.x == 0 && p.hidden_out) p.hidden_out[col] = yf;
+        }
+        sh[i] = y;
+    }
+    __syncthreads();
+    lb_trace(p.trace, 3);
+
+    float best = -INFINITY;
+    int bidx = 0x7fffffff;
+    bool failed = false;
+    for (int r = w0; r < w1; ++r) {
+        const int st = (r - w0) & 1;
+        const uint32_t parity = (uint32_t)(((r - w0) >> 1) & 1);
+        if (!failed && !lb_mbar_wait_bounded(&bars[st], parity)) {
+            failed = true;
+            if (lane == 0) atomicExch(p.status, 1);
+        }
+        const float4* row = reinterpret_cast<const float4*>(ring + (size_t)st * H);
+        double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+        if (!failed) {
+#pragma unroll 4
+            for (int k = 0; k < kiter; ++k) {
+                const int c4 = k * 32 + lane;
+                float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (c4 < H4) w = row[c4];
+                const double2 s01 = *reinterpret_cast<const double2*>(sh + ((size_t)(k * 2 + 0) * 32 + lane) * 2);
+                const double2 s23 = *reinterpret_cast<const double2*>(sh + ((size_t)(k * 2 + 1) * 32 + lane) * 2);
+                a0 = fma((double)w.x, s01.x, a0);
+                a1 = fma((double)w.y, s01.y, a1);
+                a2 = fma((double)w.z, s23.x, a2);
+                a3 = fma((double)w.w, s23.y, a3);
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && r + 2 < w1) {  // the stage is free again: request the row after next
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            lb_mbar_expect_tx(&bars[st], row_bytes);
+            lb_bulk_g2s(ring + (size_t)st * H, p.head + (size_t)(r + 2) * H, row_bytes, &bars[st]);
+        }
+        const double acc = lb_warp_sum((a0 + a1) + (a2 + a3));
+        const float lg = (float)acc;
+        if (lane == 0) p.logits[r] = lg;
+        argmax_merge(best, bidx, lg, r);  // rows ascend: a later equal value never replaces an earlier one
+    }
+    lb_trace(p.trace, 4);
+    if (!p.tok_out) return;
+
+    // ---- greedy tail ----
+    if (lane == 0) {
+        sv[warp] = best;
+        si[warp] = bidx;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < NW; ++w) argmax_merge(best, bidx, sv[w], si[w]);
+        p.part_val[blockIdx.x] = best;
+        p.part_idx[blockIdx.x] = bidx;
+        __threadfence();
+        const unsigned old = atomicAdd(p.cnt, 1u);
+        s_last = old + 1 == gridDim.x;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (warp == 0) {
+        best = -INFINITY;
+        bidx = 0x7fffffff;
+        for (int i = lane; i < (int)gridDim.x; i += 32) argmax_merge(best, bidx, __ldcg(p.part_val + i), __ldcg(p.part_idx + i));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
+            argmax_merge(best, bidx, ov, oi);
+        }
+        if (lane == 0) {
+            if (bidx == 0x7fffffff) bidx = 0;  // only NaNs: the reference keeps index 0
+            s_tok = bidx;
+            p.tok_out[0] = bidx;
+            if (p.out_tokens && p.step) {
+                const int s = *p.step;
+                if (s < p.out_cap) p.out_tokens[s] = bidx;
+                *p.step = s + 1;
+            }
+            if (p.pos) *p.pos += p.pos_delta;
+            *p.cnt = 0;
+        }
+    }
+    __syncthreads();
+    if (p.x_next && p.emb) {  // the embedding row of the new token, for the step that follows (poly/transformer.go:551-577)
+        const int t = s_tok;
+        const bool ok = t >= 0 && t < p.emb_vocab;
+        const float* src = p.emb + (size_t)(ok ? t : 0) * H;
+        for (int i = tid; i < H; i += T) p.x_next[i] = ok ? src[i] : 0.0f;
+    }
+    lb_trace(p.trace, 5);
+}
+
+template <int NW>
+size_t head_smem(int H) {
+    const int kiter = ((H >> 2) + 31) >> 5;
+    return (size_t)kiter * 128 * sizeof(double) + (size_t)NW * 2 * H * sizeof(float) + (size_t)NW * 2 * sizeof(uint64_t);
+}
+
+template <int NW>
+int launch_stream(loom_b200_ctx* ctx, const LbLmHeadParams& p, unsigned attr_bit) {
+    auto kern = lb_lm_head_stream_kernel<NW>;
+    const size_t smem = head_smem<NW>(p.hidden);
+    if (!(ctx->func_attr_mask2 & attr_bit)) {
+        LB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        ctx->func_attr_mask2 |= attr_bit;
+    }
+    int grid = ctx->sm_count;
+    if (grid > p.vocab / NW) grid = p.vocab / NW > 0 ? p.vocab / NW : 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NW * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+    LB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
+    ctx->launches++;
+    return 0;
+}
+
+}  // namespace
+
+int lb_launch_lm_head_legacy(loom_b200_ctx* ctx, const LbLmHeadParams& p);
+
+bool lb_lm_head_streams(const loom_b200_ctx* ctx, const float* head, int hidden) {
+    return ctx->opt_head_stream && (hidden & 3) == 0 && (((uintptr_t)head) & 15) == 0 && head_smem<4>(hidden) <= 220 * 1024;
+}
+
+int lb_launch_lm_head(loom_b200_ctx* ctx, const LbLmHeadParams& pin) {
+    LbLmHeadParams p = pin;
+    p.status = ctx->status_dev;
+    const bool fits8 = head_smem<8>(p.hidden) <= 220 * 1024;
+    if (!lb_lm_head_streams(ctx, p.head, p.hidden)) {
+        if (p.tok_out) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "lm_head: the greedy tail needs the streaming kernel (hidden %d)", p.hidden);
+        return lb_launch_lm_head_legacy(ctx, p);
+    }
+    if (p.tok_out) {
+        if (!ctx->head_scratch) {
+            if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "lm_head scratch would be allocated while recording a graph");
+            const size_t bytes = (size_t)ctx->sm_count * 8 + 64;
+            LB_CUDA(ctx, cudaMalloc(&ctx->head_scratch, bytes));
+            LB_CUDA(ctx, cudaMemsetAsync(ctx->head_scratch, 0, bytes, ctx->stream));
+        }
+        p.part_val = reinterpret_cast<float*>(ctx->head_scratch);
+        p.part_idx = reinterpret_cast<int*>(p.part_val + ctx->sm_count);
+        p.cnt = reinterpret_cast<unsigned int*>(p.part_idx + ctx->sm_count);
+    }
+    p.trace = lb_trace_row(ctx, "lm_head");
+    return fits8 ? launch_stream<8>(ctx, p, 1u << 8) : launch_stream<4>(ctx, p, 1u << 9);
+}

@@ -160,6 +160,8 @@ __global__ void __launch_bounds__(kThreads, 1) lb_stream_kernel(const __grid_con
         ptr += kWarps * kPStagesMax * 8;
         sm.stage = sp.stage_bytes > 0 ? (void*)ptr : nullptr;
         sm.gain = nullptr;  // the program reads norm gains from global memory
+        sm.gaind = nullptr;
+        sm.pos0 = 0;
     }
     if (tid < kWarps * nstages) lb_mbar_init(&sm.bars[tid], 1);
     if (tid == 0) lb_fence_mbar_init();
@@ -206,6 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1) lb_stream_kernel(const __grid_con
         }
         __syncthreads();
         const LbGemvParams& p = job;
+        if (p.pos_ptr) sm.pos0 = *p.pos_ptr;
         const int KB = p.kblocks, M = p.M;
         const int gt = p.group * KB;
         const long long NG = p.total_tiles / gt;
