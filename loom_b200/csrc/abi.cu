@@ -361,9 +361,6 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
             cudaFree(ctx->trace_dev);
             ctx->trace_dev = nullptr;
         }
-    } else if (!strcmp(key, "gemv_wide")) {
-        LB_REQUIRE(ctx, value >= 0 && value <= 2, "ctx_set_option: gemv_wide is 0, 1 or 2");
-        ctx->opt_gemv_wide = value;
     } else if (!strcmp(key, "head_stream")) {
         ctx->opt_head_stream = value != 0;
     } else if (!strcmp(key, "attn_cluster")) {

@@ -65,7 +65,6 @@ struct loom_b200_ctx {
     void* head_scratch = nullptr;    // per-CTA partial maxima and arrival counter of the LM head's greedy tail
     unsigned func_attr_mask = 0;  // kernels whose shared-memory limit was raised on this device
     unsigned func_attr_mask2 = 0; // the same for the cluster attention instantiations
-    int opt_gemv_wide = 1;        // sixteen-warp, one-CTA-per-SM GEMV: 0 = never, 1 = for float64 rows (after attention), 2 = every fused prologue
     int opt_head_stream = 1;      // the LM head streams its rows through shared memory with bulk copies (0 = warp-per-row loads)
     int opt_attn_cluster = 1;     // one-token decoder steps run the attention as a thread-block cluster per KV head
     // tuning knobs (loom_b200_ctx_set_option; initial values from LOOM_B200_* environment variables)

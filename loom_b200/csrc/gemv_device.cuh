@@ -8,10 +8,8 @@
 
 namespace {
 
-constexpr int kWarps = 8;               // warps of the general kernel (two CTAs per SM) and of the streaming program
+constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kWideWarps = 16;          // warps of the one-CTA-per-SM variant used by one-token launches with a fused prologue
-constexpr int kRegUnits = 4;            // 4-column units a thread of that variant keeps in registers (K <= 4 * 4 * 512)
 constexpr int kStageTiles = 8;                          // tiles per ring stage (4 KB)
 constexpr int kStages = 3;                              // most stages per warp (the launch picks 1..3)
 constexpr int kStageBytes = kStageTiles * kTileBytes;   // 4096
@@ -47,7 +45,6 @@ struct Smem {
     uint64_t* bars;   // [kWarps*kStages]
     void* stage;      // K floats (doubles for fp64 input) of prologue staging, or null
     float* gain;      // norm_w copied before the dependency wait, or null
-    double* gaind;    // the same widened to float64 (register-resident prologue), or null
     int pos0;         // *pos_ptr, read once after the dependency wait (KV ring rows)
 };
 
@@ -72,12 +69,6 @@ __device__ __forceinline__ double block_sum(double v, double* red) {
     __syncthreads();
     if (lane == 0) red[warp] = v;
     __syncthreads();
-    if (NW == 16) {  // pairwise: a shorter dependent chain than sixteen sequential additions
-        double a[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) a[i] = red[2 * i] + red[2 * i + 1];
-        return ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
-    }
     double r = 0.0;
 #pragma unroll
     for (int i = 0; i < NW; ++i) r += red[i];
@@ -239,144 +230,6 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
     __syncthreads();  // the staging buffer is reused by the next token
 }
 
-// Prologue of the sixteen-warp variant for fp32/fp64 rows with K % 4 == 0 and K <= 8192: a thread keeps its (up to
-// four) 4-column units in registers as float64 from the load to the int8 bytes, so every element is widened once,
-// normalised once and never passes through shared memory; the norm gains arrive as float64 from the copy that was made
-// before the dependency wait.  Same per-element operations as stage_row_fast, hence the same bytes.
-template <int PRO, int NW>
-__device__ __forceinline__ void stage_row_regs(const LbGemvParams& p, const Smem& sm, int n, const void* row) {
-    constexpr int T = NW * 32, U = kRegUnits;
-    constexpr bool f64 = PRO == LB_PRO_INNERNORM64;
-    const int tid = threadIdx.x, K = p.K, units = K >> 2;
-    const int Kp = p.kblocks * kTileCols, stride32 = (Kp + 16) / 4;
-    const bool have_w = PRO != LB_PRO_F32 && p.norm_w != nullptr;
-    long long pc[9];
-    pc[0] = clock64();
-    double x[U][4];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-        const int idx = tid + u * T;
-        if (idx < units) {
-            if (f64) {
-                const double2 a = reinterpret_cast<const double2*>(row)[2 * idx], b = reinterpret_cast<const double2*>(row)[2 * idx + 1];
-                x[u][0] = a.x; x[u][1] = a.y; x[u][2] = b.x; x[u][3] = b.y;
-            } else {
-                const float4 a = reinterpret_cast<const float4*>(row)[idx];
-                x[u][0] = (double)a.x; x[u][1] = (double)a.y; x[u][2] = (double)a.z; x[u][3] = (double)a.w;
-            }
-        } else {
-            x[u][0] = x[u][1] = x[u][2] = x[u][3] = 0.0;
-        }
-    }
-    float mf = 0.0f;               // absmax of float32-valued rows
-    unsigned long long mbits = 0;  // absmax of float64-valued rows, as a bit pattern
-#pragma unroll
-    for (int i = 1; i < 9; ++i) pc[i] = pc[0];
-    if (PRO >= LB_PRO_BLOCKNORM) {
-        double s4[4] = {0.0, 0.0, 0.0, 0.0};  // four independent chains; absent units add exact zeros
-        if (x[0][0] != 123.456) pc[1] = clock64();  // the first use of a loaded value: the row has arrived
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) s4[k] = __dadd_rn(s4[k], __dmul_rn(x[u][k], x[u][k]));
-        double ss = __dadd_rn(__dadd_rn(s4[0], s4[1]), __dadd_rn(s4[2], s4[3]));
-        if (p.given_ss) ss = p.given_ss[n];  // tensor-parallel row shards: the sum over the whole vector comes from the caller
-        else ss = block_sum<NW>(ss, sm.red);
-        pc[2] = clock64();
-        const double mean = __dadd_rn(__ddiv_rn(ss, (double)(p.norm_count > 0 ? p.norm_count : K)), p.eps);
-        const double root = sqrt(mean);
-        const double rr = __ddiv_rn(1.0, root);
-        if (rr != 123.456) pc[3] = clock64();
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int idx = tid + u * T;
-            if (idx < units) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    double w = 1.0;
-                    if (have_w && 4 * idx + k < p.norm_w_len) w = sm.gaind ? sm.gaind[4 * idx + k] : (double)p.norm_w[4 * idx + k];
-                    if (f64) {
-                        const double y = __dmul_rn(x[u][k], __dmul_rn(rr, w));
-                        x[u][k] = y;
-                        mbits = lb_absmax_bits(mbits, y);
-                    } else {
-                        float yf;
-                        if (PRO == LB_PRO_BLOCKNORM) yf = (float)__dmul_rn(lb_div_by(x[u][k], root, rr), w);
-                        else yf = (float)__dmul_rn(__dmul_rn(x[u][k], rr), w);
-                        x[u][k] = (double)yf;
-                        mf = fmaxf(mf, fabsf(yf));
-                    }
-                }
-            }
-        }
-    } else {
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) mbits = lb_absmax_bits(mbits, x[u][k]);
-    }
-    // one narrowing at the end: rounding is monotone (exact when the values are float32 already)
-    float m = fmaxf(mf, (float)__longlong_as_double((long long)mbits));
-    if (m != 123.456f) pc[4] = clock64();
-    if (p.given_amax) m = p.given_amax[n];
-    else m = block_max<NW>(m, sm.red);
-    pc[5] = clock64();
-    const float amax = m < 1e-5f ? 1e-5f : m;
-    const double s = __ddiv_rn(127.0, (double)amax);
-    if (s != 123.456) pc[6] = clock64();
-    const bool side = blockIdx.x == 0;
-    if (tid >= T - 3) {  // the output scales need a float64 division: the last threads own the fewest units
-        const int sg = tid - (T - 3);
-        sm.os[sg * kMaxM + n] = sg < p.nseg ? lb_output_scale(p.seg[sg].scale, amax) : 1.0;
-    }
-    int local_sum = 0;
-    uint8_t* abytes = reinterpret_cast<uint8_t*>(sm.acts + (size_t)n * stride32);
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-        const int idx = tid + u * T;
-        if (idx < (Kp >> 2)) {
-            int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
-            if (idx < units) {
-                q0 = lb_quant_i8(x[u][0], s);
-                q1 = lb_quant_i8(x[u][1], s);
-                q2 = lb_quant_i8(x[u][2], s);
-                q3 = lb_quant_i8(x[u][3], s);
-                local_sum += q0 + q1 + q2 + q3;
-                if (side) {
-                    if (p.q_out)
-                        reinterpret_cast<uint32_t*>(p.q_out + (size_t)n * K)[idx] =
-                            (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
-                    if (p.norm_out)
-                        reinterpret_cast<float4*>(p.norm_out + (size_t)n * K)[idx] =
-                            make_float4((float)x[u][0], (float)x[u][1], (float)x[u][2], (float)x[u][3]);
-                }
-            }
-            // unit idx = word r_b of 16-column chunk i: byte j of r_b is byte b of B_j (columns >= K stay zero)
-            const int i = idx >> 2, b = idx & 3;
-            const int kb = i >> 3, w8 = i & 7, h = w8 >> 2, t = w8 & 3;
-            uint8_t* dst = abytes + (size_t)(kb * 32 + t * 8 + h) * 4 + b;
-            dst[0] = (uint8_t)q0;
-            dst[8] = (uint8_t)q1;
-            dst[16] = (uint8_t)q2;
-            dst[24] = (uint8_t)q3;
-        }
-    }
-    if (local_sum != 123456789) pc[7] = clock64();
-    local_sum = lb_warp_sum_i(local_sum);
-    if ((tid & 31) == 0 && local_sum != 0) atomicAdd(&sm.xsum[n], local_sum);
-    if (tid == 0) {
-        sm.amax[n] = amax;
-        if (side && p.amax_out) p.amax_out[n] = amax;
-    }
-    __syncthreads();  // red[] and the accumulators of xsum are reused by the next token
-    if (p.trace_pro && blockIdx.x == 0 && tid == 0) {
-        // thread 0's clocks: row arrived, sum of squares reduced, statistics, normalised, absmax reduced, scale, quantized, done
-        pc[8] = clock64();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) p.trace_pro[i] = (unsigned long long)(pc[i + 1] - pc[i]);
-    }
-}
-
 // Quantizes the M activation rows into shared memory in the k-slot order the MMA B-fragments use, and
 // leaves sum(q) and amax per token in shared memory.
 template <int PRO, int NW = kWarps>
@@ -396,10 +249,6 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
         if (!q8) {
             const bool aligned16 = (((uintptr_t)row) & 15) == 0 && (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) &&
                                    (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) && (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0);
-            if (NW == kWideWarps && (K & 3) == 0 && aligned16 && (p.kblocks * kTileCols) <= kRegUnits * 4 * kThreads) {
-                stage_row_regs<PRO == LB_PRO_Q8 ? LB_PRO_F32 : PRO, NW>(p, sm, n, row);
-                continue;
-            }
             if ((K & 3) == 0 && sm.stage && aligned16) {
                 stage_row_fast<PRO == LB_PRO_Q8 ? LB_PRO_F32 : PRO, NW>(p, sm, n, row);
                 continue;

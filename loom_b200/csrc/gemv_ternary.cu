@@ -27,12 +27,9 @@
 namespace {
 
 
-// NW = warps per CTA: kWarps (eight, two CTAs per SM: the general kernel) or kWideWarps (sixteen, one CTA per SM, with the
-// register-resident prologue: one-token launches whose critical path is the activation prologue, not the weight stream)
-template <bool MMA, int PRO, int EPI, int NW = kWarps>
-__global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ternary_kernel(const __grid_constant__ LbGemvParams p) {
+template <bool MMA, int PRO, int EPI>
+__global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __grid_constant__ LbGemvParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    constexpr int kWarps = NW, kThreads = NW * 32;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int KB = p.kblocks, M = p.M;
     const int Kp = KB * kTileCols;
@@ -62,8 +59,7 @@ __global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ter
         ptr += kWarps * kStages * 8;
         sm.stage = p.stage_bytes > 0 ? (void*)ptr : nullptr;
         ptr += p.stage_bytes;
-        sm.gain = (p.gain_bytes > 0 && NW != kWideWarps) ? reinterpret_cast<float*>(ptr) : nullptr;
-        sm.gaind = (p.gain_bytes > 0 && NW == kWideWarps) ? reinterpret_cast<double*>(ptr) : nullptr;
+        sm.gain = p.gain_bytes > 0 ? reinterpret_cast<float*>(ptr) : nullptr;
         sm.pos0 = 0;
     }
 
@@ -147,15 +143,6 @@ __global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ter
         for (int i = tid; i < n4; i += kThreads) reinterpret_cast<float4*>(sm.gain)[i] = __ldg(reinterpret_cast<const float4*>(p.norm_w) + i);
         for (int i = (n4 << 2) + tid; i < p.norm_w_len; i += kThreads) sm.gain[i] = __ldg(p.norm_w + i);
     }
-    if (sm.gaind) {  // widened here, off the critical path, so that the prologue has no conversion per gain
-        const int n4 = p.norm_w_len >> 2;
-        for (int i = tid; i < n4; i += kThreads) {
-            const float4 g = __ldg(reinterpret_cast<const float4*>(p.norm_w) + i);
-            reinterpret_cast<double2*>(sm.gaind)[2 * i] = make_double2((double)g.x, (double)g.y);
-            reinterpret_cast<double2*>(sm.gaind)[2 * i + 1] = make_double2((double)g.z, (double)g.w);
-        }
-        for (int i = (n4 << 2) + tid; i < p.norm_w_len; i += kThreads) sm.gaind[i] = (double)__ldg(p.norm_w + i);
-    }
     lb_pdl_launch_dependents();  // the next launch may start prefetching its weights
     LB_TRACE(1);
     lb_pdl_wait();               // everything below may read what earlier launches wrote
@@ -169,7 +156,7 @@ __global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ter
             if (p.seg[0].bias) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.seg[0].bias + row0 + tid));
         }
     }
-    stage_activations<PRO, NW>(p, sm);
+    stage_activations<PRO>(p, sm);
     LB_TRACE(3);
 
     // ---- main loop ------------------------------------------------------------------------------------
@@ -261,18 +248,12 @@ __global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ter
 
     int cstage = 0;
     uint32_t cphase = 0;
-    long long lc[9];
-    lc[0] = clock64();
-#pragma unroll
-    for (int i = 1; i < 9; ++i) lc[i] = lc[0];
-    int n_iter = 0;
     while (cc.pos < w1) {
         const int len = chunk_len(cc);
         if (!failed && !lb_mbar_wait_bounded(&my_bars[cstage], cphase)) {
             failed = true;
             if (lane == 0) atomicExch(p.status, 1);
         }
-        if (n_iter == 0) lc[1] = clock64();
         if (cc.v != cur_v) {
             flush();
             cur_v = cc.v;
@@ -287,8 +268,6 @@ __global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ter
                 for (int i = 0; i < len; ++i) tile_step(tile + i * kTileBytes, ab + i * act_kb_mul);
             }
         }
-        if (n_iter == 0 && acc[0][0] != 0x7fffffff) lc[2] = clock64();
-        ++n_iter;
         advance(cc, len);
         __syncwarp();
         if (ic.pos < w1) {
@@ -304,11 +283,8 @@ __global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ter
             cphase ^= 1u;
         }
     }
-    lc[3] = clock64();
     flush();
-    lc[4] = clock64();
     __syncthreads();
-    lc[5] = clock64();
     LB_TRACE(4);
 
     // ---- strip groups: finish what this CTA owns entirely, hand the rest to the fix-up ------------------
@@ -317,7 +293,6 @@ __global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ter
     const int per_group = p.group * M * 16;
     if (p.aligned) {  // every group is this CTA's own: no fix-up, no flags
         const int ngl_a = p.part_q + ((int)blockIdx.x < p.part_r ? 1 : 0);
-        lc[6] = clock64();
         for (int idx = tid; idx < ngl_a * per_group; idx += kThreads) {
             int gl, i;
             if (per_group == 16) {
@@ -329,12 +304,6 @@ __global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ter
             }
             const int e = i / (M * 16), rem = i - e * (M * 16);
             finish_row<EPI>(p, sm, (first_group + gl) * p.group, e, rem >> 4, rem & 15, sm.sacc + (size_t)gl * per_group);
-        }
-        if (p.trace_loop && blockIdx.x == 0 && tid == 0) {
-            lc[7] = clock64();
-#pragma unroll
-            for (int i = 0; i < 7; ++i) p.trace_loop[i] = (unsigned long long)(lc[i + 1] - lc[i]);
-            p.trace_loop[7] = (unsigned long long)(w1 - w0);
         }
         LB_TRACE(5);
         return;
@@ -383,7 +352,6 @@ __global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ter
         }
     }
     __syncthreads();
-    lc[6] = clock64();
     const bool do_first = sm.flag[0] != 0, do_last = sm.flag[1] != 0;
     for (int idx = tid; idx < ngl * per_group; idx += kThreads) {
         const int gl = idx / per_group, i = idx - gl * per_group;
@@ -392,24 +360,17 @@ __global__ void __launch_bounds__(NW * 32, NW == kWideWarps ? 1 : 2) lb_gemv_ter
         const int e = i / (M * 16), rem = i - e * (M * 16);
         finish_row<EPI>(p, sm, (first_group + gl) * p.group, e, rem >> 4, rem & 15, sm.sacc + (size_t)gl * per_group);
     }
-    if (p.trace_loop && blockIdx.x == 0 && tid == 0) {
-        // thread 0's clocks: first weights there, first chunk done, loop done, flushed, all warps done, fix-up decided, rows finished; tiles of warp 0
-        lc[7] = clock64();
-#pragma unroll
-        for (int i = 0; i < 7; ++i) p.trace_loop[i] = (unsigned long long)(lc[i + 1] - lc[i]);
-        p.trace_loop[7] = (unsigned long long)(w1 - w0);
-    }
     LB_TRACE(5);
 }
 
-size_t gemv_smem_bytes(const LbGemvParams& p, int max_local, int nw) {
+size_t gemv_smem_bytes(const LbGemvParams& p, int max_local) {
     int Kp = p.kblocks * kTileCols;
-    size_t b = (size_t)nw * p.stages * kStageBytes;
+    size_t b = (size_t)kWarps * p.stages * kStageBytes;
     b += (size_t)(p.M * ((Kp + 16) / 4) + 8) * 4;
     b = (b + 15) & ~(size_t)15;
     b += (size_t)max_local * p.M * 16 * 4;
     b += 32 + 32 + 256 + 3 * kMaxM * 8 + 16;
-    b += (size_t)nw * kStages * 8;
+    b += (size_t)kWarps * kStages * 8;
     b = (b + 15) & ~(size_t)15;
     b += (size_t)p.stage_bytes;
     b += (size_t)p.gain_bytes;
@@ -453,7 +414,7 @@ int lb_gemv_finalize_params(loom_b200_ctx* ctx, LbGemvParams& p) {
 }
 
 // Partition, ring depth and shared-memory footprint for a grid of SMs x cps CTAs.
-static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int nw, int* grid_out, size_t* smem_out) {
+static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int* grid_out, size_t* smem_out) {
     int vstrips = p.total_tiles / p.kblocks;
     int ngroups = (vstrips + p.group - 1) / p.group;
     int grid = ctx->sm_count * cps;
@@ -488,8 +449,8 @@ static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int nw
                 t1 = (long long)p.total_tiles * (b + 1) / grid;
             }
             const long long n = t1 - t0;
-            for (int w = 0; w < nw && most < kStages; ++w) {
-                long long w0 = t0 + n * w / nw, w1 = t0 + n * (w + 1) / nw;
+            for (int w = 0; w < kWarps && most < kStages; ++w) {
+                long long w0 = t0 + n * w / kWarps, w1 = t0 + n * (w + 1) / kWarps;
                 int chunks = 0;
                 while (w0 < w1) {
                     long long len = KB - w0 % KB;
@@ -506,19 +467,18 @@ static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int nw
     // prologue staging: the activation row in its input precision, when it fits beside the ring
     p.stage_bytes = 0;
     p.gain_bytes = 0;
-    const bool wide = nw == kWideWarps;  // the sixteen-warp variant keeps the row in registers: no staging buffer
-    if (!wide && p.pro != LB_PRO_Q8 && (p.K & 3) == 0) {
+    if (p.pro != LB_PRO_Q8 && (p.K & 3) == 0) {
         size_t want = (size_t)p.K * (p.pro == LB_PRO_INNERNORM64 ? 8 : 4);
-        if (gemv_smem_bytes(p, p.max_local_strips, nw) + want <= 227 * 1024) p.stage_bytes = (int)want;
+        if (gemv_smem_bytes(p, p.max_local_strips) + want <= 227 * 1024) p.stage_bytes = (int)want;
     }
-    if ((wide || p.stage_bytes > 0) && p.pro >= LB_PRO_BLOCKNORM && p.norm_w && p.norm_w_len > 0 && (((uintptr_t)p.norm_w) & 15) == 0) {
-        const size_t want = ((size_t)p.norm_w_len * (wide ? 8 : 4) + 15) & ~(size_t)15;
-        if (gemv_smem_bytes(p, p.max_local_strips, nw) + want <= 227 * 1024) p.gain_bytes = (int)want;
+    if (p.stage_bytes > 0 && p.pro >= LB_PRO_BLOCKNORM && p.norm_w && p.norm_w_len > 0 && (((uintptr_t)p.norm_w) & 15) == 0) {
+        const size_t want = ((size_t)p.norm_w_len * 4 + 15) & ~(size_t)15;
+        if (gemv_smem_bytes(p, p.max_local_strips) + want <= 227 * 1024) p.gain_bytes = (int)want;
     }
-    size_t smem = gemv_smem_bytes(p, p.max_local_strips, nw);
+    size_t smem = gemv_smem_bytes(p, p.max_local_strips);
     while (smem > 227 * 1024 && p.stages > 1) {  // wide inputs: a shallower ring before giving up
         --p.stages;
-        smem = gemv_smem_bytes(p, p.max_local_strips, nw);
+        smem = gemv_smem_bytes(p, p.max_local_strips);
     }
     *grid_out = grid;
     *smem_out = smem;
@@ -552,33 +512,18 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     size_t smem = 0;
     int cps = ctx->opt_gemv_ctas_per_sm;
     if (p.K >= 16384 && cps > 1) cps = 1;  // very wide rows: every CTA stages the whole int8 row, so fewer, longer CTAs win (measured)
-    // One or two tokens with the inner norm of a float64 row fused in (the attention output): the prologue, which every CTA
-    // repeats, is the critical path, and the launch before it (the attention clusters) leaves SMs free, so one sixteen-warp
-    // CTA per SM with the row in registers beats two eight-warp CTAs that both stage it (measured: 6.1 against 7.1 us).  After
-    // a launch that fills every SM the sixteen-warp CTA cannot become resident early and loses what its prologue gains, so
-    // the other prologues keep the eight-warp kernel (option "gemv_wide" = 2 uses the sixteen-warp one for all of them).
-    const bool aligned_ptrs = (((uintptr_t)p.x) & 15) == 0 && (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) &&
-                              (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) && (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0);
-    const bool wide = (ctx->opt_gemv_wide == 2 || (ctx->opt_gemv_wide == 1 && p.pro == LB_PRO_INNERNORM64)) &&
-                      p.pro != LB_PRO_Q8 && p.M <= 2 && (p.K & 3) == 0 && aligned_ptrs &&
-                      p.kblocks * kTileCols <= kRegUnits * 4 * kWideWarps * 32 &&
-                      (p.epi == LB_EPI_QKV || p.epi == LB_EPI_RESID || p.epi == LB_EPI_SWIGLU || (p.epi == LB_EPI_GENERIC && p.pro == LB_PRO_F32));
-    const int nw = wide ? kWideWarps : kWarps;
-    if (wide) cps = 1;
-    gemv_plan(ctx, p, cps, nw, &grid, &smem);
+    gemv_plan(ctx, p, cps, &grid, &smem);
     // A grid sized for more CTAs per SM than the shared memory lets be resident would run in waves, and every
     // wave repeats the prologue: fall back to what fits (228 KB per SM, 1 KB reserved per CTA).
     while (cps > 1 && (smem + 1024) * (size_t)cps > 228 * 1024) {
         --cps;
-        gemv_plan(ctx, p, cps, nw, &grid, &smem);
+        gemv_plan(ctx, p, cps, &grid, &smem);
     }
     if (int rc = lb_ensure_fixup(ctx, (size_t)ngroups * p.group * p.M * 16, (size_t)ngroups)) return rc;
     p.fix_acc = ctx->fix_acc;
     p.fix_cnt = ctx->fix_cnt;
     p.status = ctx->status_dev;
     p.trace = lb_trace_row(ctx, "gemv");
-    p.trace_pro = wide ? lb_trace_row(ctx, "gemv-pro") : nullptr;
-    p.trace_loop = ctx->trace_dev ? lb_trace_row(ctx, "gemv-loop") : nullptr;
     if (smem > 227 * 1024)
         return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: K=%d with %d tokens needs %zu B of shared memory", p.K, p.M, smem);
     // one instantiation per (inner loop, prologue, epilogue) combination that a caller can reach
@@ -587,13 +532,8 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     int kid = -1;
     const bool use_dp4a = ctx->opt_gemv_variant == 1 && p.M == 1 && p.pro == LB_PRO_Q8 && p.epi == LB_EPI_GENERIC;
 #define LB_PICK(id, mma, pro_, epi_)                                \
-    if (kid < 0 && !wide && p.pro == pro_ && p.epi == epi_ && (mma) == !use_dp4a) { \
+    if (kid < 0 && p.pro == pro_ && p.epi == epi_ && (mma) == !use_dp4a) { \
         kern = lb_gemv_ternary_kernel<mma, pro_, epi_>;             \
-        kid = id;                                                   \
-    }
-#define LB_PICK_WIDE(id, pro_, epi_)                                \
-    if (kid < 0 && wide && p.pro == pro_ && p.epi == epi_) {        \
-        kern = lb_gemv_ternary_kernel<true, pro_, epi_, kWideWarps>; \
         kid = id;                                                   \
     }
     LB_PICK(0, true, LB_PRO_Q8, LB_EPI_GENERIC)
@@ -610,15 +550,7 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     LB_PICK(11, true, LB_PRO_Q8, LB_EPI_SWIGLU)
     LB_PICK(12, true, LB_PRO_Q8, LB_EPI_QKV)
     LB_PICK(13, true, LB_PRO_Q8, LB_EPI_RESID)
-    LB_PICK_WIDE(14, LB_PRO_BLOCKNORM, LB_EPI_QKV)
-    LB_PICK_WIDE(15, LB_PRO_INNERNORM64, LB_EPI_RESID)
-    LB_PICK_WIDE(16, LB_PRO_BLOCKNORM, LB_EPI_SWIGLU)
-    LB_PICK_WIDE(17, LB_PRO_INNERNORM, LB_EPI_RESID)
-    LB_PICK_WIDE(18, LB_PRO_F32, LB_EPI_GENERIC)
-    LB_PICK_WIDE(19, LB_PRO_F32, LB_EPI_QKV)
-    LB_PICK_WIDE(20, LB_PRO_F32, LB_EPI_SWIGLU)
 #undef LB_PICK
-#undef LB_PICK_WIDE
     if (!kern) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: no kernel for prologue %d with epilogue %d", p.pro, p.epi);
     const unsigned attr_bit = 1u << kid;
     if (!(ctx->func_attr_mask & attr_bit)) {  // per device: the context pins the device
@@ -627,7 +559,7 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(nw * 32);
+    cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];

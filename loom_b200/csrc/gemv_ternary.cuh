@@ -85,8 +85,6 @@ struct LbGemvParams {
     unsigned int* fix_cnt;
     int* status;
     unsigned long long* trace;  // optional row of 8 phase timestamps (ns) written by CTA 0, or null
-    unsigned long long* trace_loop;  // optional third row: clock counts of warp 0's main loop and epilogue
-    unsigned long long* trace_pro;  // optional second row: clock counts of the prologue's parts (register-resident variant)
 };
 
 // Launches the GEMV on ctx->stream (programmatic dependent launch unless disabled).

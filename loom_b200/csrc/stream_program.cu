@@ -160,7 +160,6 @@ __global__ void __launch_bounds__(kThreads, 1) lb_stream_kernel(const __grid_con
         ptr += kWarps * kPStagesMax * 8;
         sm.stage = sp.stage_bytes > 0 ? (void*)ptr : nullptr;
         sm.gain = nullptr;  // the program reads norm gains from global memory
-        sm.gaind = nullptr;
         sm.pos0 = 0;
     }
     if (tid < kWarps * nstages) lb_mbar_init(&sm.bars[tid], 1);
