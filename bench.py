@@ -483,27 +483,18 @@ TP_SHAPES = {
 }
 
 
-def tp_mode(args):
-    """Tensor-parallel batch-1 decode of an 8B / 70B-shaped ternary decoder: one process per GPU (torchrun), column-
-    sharded Q/K/V/gate/up, row-sharded O/down with exact int32 all-reduces, vocabulary-sharded head.  Strong scaling:
-    the model is fixed and the group grows.  Each rank ternarises its own slices (synthetic weights, so the per-slice
-    absmean scale stands in for the whole-matrix one; timing does not depend on it)."""
-    import torch
-    import torch.distributed as dist
-
+def tp_decode_measure(args, torch, dist, rank, world, local, shape_name, layers, steps, warmup, exchange):
+    """Builds rank `rank`'s part of a `shape_name`-shaped ternary decoder (column-sharded Q/K/V/gate/up, row-sharded O/down,
+    vocabulary-sharded head) on a context of its own, times `steps` device-resident greedy decode steps (CUDA events,
+    barrier + synchronize on both sides, max over ranks) and returns the figures.  Each rank ternarises its own slices
+    (synthetic weights, so the per-slice absmean scale stands in for the whole-matrix one; timing does not depend on it)."""
     import loom_b200
     from loom_b200 import cabi
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    shape = dict(TP_SHAPES[args.shape])
-    if args.layers != SHAPE["layers"]:
-        shape["layers"] = args.layers
-    torch.cuda.set_device(local)
+    shape = dict(TP_SHAPES[shape_name])
+    if layers:
+        shape["layers"] = layers
     dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     ctx = loom_b200.Context(local, tstream.cuda_stream)
@@ -514,7 +505,7 @@ def tp_mode(args):
         dist.broadcast(idt, 0)
         torch.cuda.synchronize()
         ctx.tp_init(rank, world, bytes(idt.cpu().numpy().tobytes()))
-        if args.tp_exchange == "peer":  # row-parallel projections exchange through peer mailboxes (CUDA IPC over NVLink)
+        if exchange == "peer":  # row-parallel projections exchange through peer mailboxes (CUDA IPC over NVLink)
             mine = torch.frombuffer(bytearray(ctx.tp_peer_handle()), dtype=torch.uint8).to(dev)
             allh = [torch.zeros(64, dtype=torch.uint8, device=dev) for _ in range(world)]
             dist.all_gather(allh, mine)
@@ -541,24 +532,24 @@ def tp_mode(args):
     emb = torch.randn(shape["vocab"], H, device=dev, generator=ge, dtype=torch.float32) * 0.02
     dec.set_embeddings(emb)
     rng = np.random.default_rng(args.seed)
-    n_prompt = min(args.prompt, 64)
+    n_prompt = min(args.prompt, 64)  # under a tensor-parallel group prompts run eight tokens per pass: keep it short
     prompt = rng.integers(0, shape["vocab"], n_prompt).astype(np.int32)
-    args.warmup = max(args.warmup, 3)
-    assert n_prompt + args.warmup + args.steps + 2 <= shape["max_seq_len"]
+    warmup = max(warmup, 3)
+    assert n_prompt + warmup + steps + 40 <= shape["max_seq_len"]
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    toks, _ = dec.generate(prompt, args.warmup)
+    dec.generate(prompt, warmup)
     sampler = ClockSampler(local)
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    dec.continue_greedy(args.steps)
+    dec.continue_greedy(steps)
     e1.record()
     barrier()
     dev_s = e0.elapsed_time(e1) * 1e-3
@@ -566,7 +557,7 @@ def tp_mode(args):
     # end to end: token id in, logits out, host argmax
     logits = dec.forward(np.array([int(prompt[0])], np.int32))
     tok = int(np.argmax(logits))
-    e2e_steps = min(args.steps, 32)
+    e2e_steps = min(steps, 32)
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
@@ -578,35 +569,55 @@ def tp_mode(args):
         t = torch.tensor([dev_s, e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_s, e2e_s = float(t[0].item()), float(t[1].item())
-    tern_b, kv_b, head_b = algorithmic_bytes(shape, n_prompt + args.warmup + args.steps // 2)
+    tern_b, kv_b, head_b = algorithmic_bytes(shape, n_prompt + warmup + steps // 2)
+    res = {"shape": shape_name, "layers": shape["layers"], "world": world, "exchange": "none" if world == 1 else exchange,
+           "tok_per_s": steps / dev_s, "ms_per_step": 1e3 * dev_s / steps, "e2e_tok_per_s": e2e_steps / e2e_s, "e2e_steps": e2e_steps,
+           "launches_per_token": dec.launches_per_token(), "prompt": n_prompt, "clocks": clocks,
+           "bytes_per_gpu": (tern_b + kv_b + head_b) / world, "vocab": shape["vocab"]}
+    ctx.sync()
+    dec.close()
+    del keep, emb
+    barrier()
+    ctx.tp_finalize()
+    ctx.close()
+    return res
+
+
+def tp_mode(args):
+    """Tensor-parallel batch-1 decode of an 8B / 70B-shaped ternary decoder: one process per GPU (torchrun).  Strong
+    scaling: the model is fixed and the group grows."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    r = tp_decode_measure(args, torch, dist, rank, world, local, args.shape, args.layers if args.layers != SHAPE["layers"] else 0,
+                          args.steps, args.warmup, args.tp_exchange)
     peak, peak_kind = measured_peaks()
-    step_s = dev_s / args.steps
-    # kernels of this library per token (NCCL's collectives are not counted)
-    launches = shape["layers"] * (6 if world == 1 else (10 if args.tp_exchange == "peer" else 12)) + 4
+    step_s = r["ms_per_step"] * 1e-3
     line = {
-        "metric": "decode tok/s (%s-shape ternary decoder, bs=1, tensor parallel)" % args.shape.upper(), "value": args.steps / dev_s,
-        "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * step_s,
+        "metric": "decode tok/s (%s-shape ternary decoder, bs=1, tensor parallel)" % args.shape.upper(), "value": r["tok_per_s"],
+        "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": r["ms_per_step"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x ternary -> int32, fp64 rescale",
         "data": "synthetic",
         "config": {"workload": "Llama-3-%s-shape ternary decoder, batch-1 greedy decode" % args.shape.upper(),
-                   "layers": shape["layers"], "prompt": n_prompt, "parallelism": "tp%d" % world,
-                   "exchange": "none" if world == 1 else args.tp_exchange,
+                   "layers": r["layers"], "prompt": r["prompt"], "parallelism": "tp%d" % world, "exchange": r["exchange"],
                    "l2": "every step streams the rank's packed weights and head slice, far beyond the 126 MB L2"},
-        "e2e": {"value": e2e_steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": shape["vocab"] * 4,
-                "steps": e2e_steps},
-        "gpu_launches": args.steps * launches, "clocks": clocks,
-        "roofline": {"bound": "hbm", "achieved": (tern_b + kv_b + head_b) / world / step_s / 1e9, "peak": peak, "unit": "GB/s",
-                     "frac": (tern_b + kv_b + head_b) / world / step_s / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+        "e2e": {"value": r["e2e_tok_per_s"], "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": r["vocab"] * 4,
+                "steps": r["e2e_steps"]},
+        "gpu_launches": int(args.steps * r["launches_per_token"]), "clocks": r["clocks"],
+        "roofline": {"bound": "hbm", "achieved": r["bytes_per_gpu"] / step_s / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": r["bytes_per_gpu"] / step_s / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
                      "kernel": "whole decode step, per-GPU bytes (packed weights + KV + fp32 head slice) / step time"},
-        "collectives_per_token": 0 if world == 1 else (1 if args.tp_exchange == "peer" else shape["layers"] * 6 + 1),
     }
     if rank == 0:
         print(json.dumps(line))
-    ctx.sync()
-    dec.close()
-    barrier()
-    ctx.tp_finalize()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
     return 0
 
@@ -629,6 +640,7 @@ def main():
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
                     help="tp mode: how the row-parallel projections exchange their partial results")
     ap.add_argument("--tokens", type=int, default=512)
+    ap.add_argument("--no-tp-section", action="store_true", help="multi-GPU runs: skip the tensor-parallel decode after the replica measurement")
     args = ap.parse_args()
     if args.mode == "gemm":
         return gemm_mode(args)
@@ -794,6 +806,21 @@ def main():
     }
     if tp_check is not None:
         line["tp_check"] = tp_check
+    if world > 1 and world in (2, 4, 8) and not args.no_tp_section:
+        # Strong scaling beside the replica headline: the 8B shape (8 KV heads divide by 2, 4 and 8), batch-1 decode over a
+        # tensor-parallel group of all ranks with the peer-mailbox exchange.  The replica decoder is released first.
+        dec.close()
+        del dec, weights, emb
+        ctx.close()
+        torch.cuda.empty_cache()
+        try:
+            r = tp_decode_measure(args, torch, dist, rank, world, local, "8b", 0, min(args.steps, 32), args.warmup, "peer")
+            line["tp"] = {k: r[k] for k in ("shape", "layers", "world", "exchange", "tok_per_s", "ms_per_step", "e2e_tok_per_s",
+                                            "launches_per_token", "prompt")}
+            line["tp"]["note"] = ("strong scaling: compare tok_per_s across the N of a scaling run; the one-GPU figure of the same shape "
+                                  "comes from `bench.py --mode tp --shape 8b`")
+        except Exception as exc:
+            line["tp"] = {"error": "%s: %r" % (type(exc).__name__, exc)}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
             from oracle import oracle as orc
