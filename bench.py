@@ -622,6 +622,83 @@ def tp_mode(args):
     return 0
 
 
+def batch_mode(args):
+    """Decode with `--batch` independent sequences on one GPU (configs[3] at one GPU: 8B shape, batch 16, 2048-token prompts):
+    every sequence is prefilled with a prompt of its own, then all of them advance together, up to eight sequences per
+    pass over every packed matrix and several hidden rows per pass over the LM head.  value = sequences x steps / time."""
+    import torch
+
+    import loom_b200
+    from loom_b200 import cabi
+
+    shape = dict({"2b": SHAPE, **TP_SHAPES}[args.shape])
+    if args.layers != SHAPE["layers"]:
+        shape["layers"] = args.layers
+    B = args.batch
+    args.warmup = max(args.warmup, 3)
+    shape["max_seq_len"] = args.prompt + args.warmup + args.steps + 8
+    torch.cuda.set_device(0)
+    ts = torch.cuda.Stream()
+    torch.cuda.set_stream(ts)
+    ctx = loom_b200.Context(0, ts.cuda_stream)
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(args.seed)
+    H, I, hd = shape["hidden"], shape["inter"], shape["head_dim"]
+    qd, kvd = shape["heads"] * hd, shape["kv_heads"] * hd
+    dims = ((qd, H), (kvd, H), (kvd, H), (H, qd), (I, H), (I, H), (H, I))
+    dec = cabi.Decoder(ctx, shape["layers"], H, shape["heads"], shape["kv_heads"], hd, I, shape["vocab"], shape["eps"],
+                       shape["theta"], cabi.ACT_SILU, shape["max_seq_len"])
+    dec.set_batch(B)
+    keep = []
+    for b in range(shape["layers"]):
+        ws = []
+        for r, c in dims:
+            master = torch.randn(r * c, device=dev, generator=g, dtype=torch.float32) * 0.02
+            ws.append(ctx.pack_ternary_f32(master, r, c))
+            del master
+        dec.set_block(b, ws)
+        keep.append(ws)
+    emb = torch.randn(shape["vocab"], H, device=dev, generator=g, dtype=torch.float32) * 0.02
+    dec.set_embeddings(emb)
+    rng = np.random.default_rng(args.seed)
+    t0 = time.perf_counter()
+    for i in range(B):
+        dec.select(i)
+        dec.forward(rng.integers(0, shape["vocab"], args.prompt).astype(np.int32), want_logits=False)
+    ctx.sync()
+    prefill_s = time.perf_counter() - t0
+    dec.continue_batch(args.warmup)
+    ctx.sync()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    dec.continue_batch(args.steps)
+    e1.record()
+    torch.cuda.synchronize()
+    dev_s = e0.elapsed_time(e1) * 1e-3
+    clocks = sampler.stop()
+    peak, peak_kind = measured_peaks()
+    tern_b, kv_b, head_b = algorithmic_bytes(shape, args.prompt + args.warmup + args.steps // 2)
+    passes = (B + 7) // 8
+    step_s = dev_s / args.steps
+    moved = passes * tern_b + B * kv_b + ((B + 1) // 2) * head_b  # weights once per pass of eight, KV per sequence, head once per pass
+    print(json.dumps({
+        "metric": "decode tok/s (%s-shape ternary decoder, %d independent sequences, one GPU)" % (args.shape.upper(), B),
+        "value": B * args.steps / dev_s, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * step_s, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic",
+        "config": {"workload": "%s-shape ternary decoder, batch %d greedy decode, %d-token prompts" % (args.shape.upper(), B, args.prompt),
+                   "layers": shape["layers"], "batch": B, "prompt": args.prompt, "parallelism": "single GPU"},
+        "per_sequence_tok_per_s": args.steps / dev_s, "prefill_seconds_all_sequences": prefill_s, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": moved / step_s / 1e9, "peak": peak, "unit": "GB/s", "frac": moved / step_s / 1e9 / peak,
+                     "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "whole batch step: packed weights once per pass of eight sequences, KV of every sequence, fp32 head once per head pass"}}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -633,7 +710,8 @@ def main():
     ap.add_argument("--vocab", type=int, default=SHAPE["vocab"], help="smaller vocabularies are for profiling captures only")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--mode", default="decode", choices=["decode", "gemm", "tp", "sweep"],
+    ap.add_argument("--batch", type=int, default=16, help="batch mode: independent sequences")
+    ap.add_argument("--mode", default="decode", choices=["decode", "gemm", "tp", "sweep", "batch"],
                     help="gemm: the batched-prefill GEMM microbenchmark; tp: tensor-parallel decode of --shape under torchrun; "
                          "sweep: GEMV vs GEMM over batch sizes for the gate/down projections of --shape")
     ap.add_argument("--shape", default="8b", choices=sorted(TP_SHAPES) + ["2b"])
@@ -646,6 +724,8 @@ def main():
         return gemm_mode(args)
     if args.mode == "tp":
         return tp_mode(args)
+    if args.mode == "batch":
+        return batch_mode(args)
     if args.mode == "sweep":
         args.steps = min(args.steps, 20)
         return sweep_mode(args)

@@ -335,6 +335,26 @@ int loom_b200_decoder_last_hidden(loom_b200_decoder* dec, float* hidden_host);
  * device and without waiting for it (call loom_b200_sync to wait).  The body of Generate's loop,
  * poly/transformer.go:434-485. */
 int loom_b200_decoder_continue(loom_b200_decoder* dec, int steps);
+/* ---- independent sequences on one decoder ---------------------------------------------------------------
+ * The reference shares ONE KV ring across a batch: MHAForwardPackedTernaryCPU walks batch*seq rows as consecutive positions
+ * of one sequence (poly/mha.go:258-270, poly/mha_layout.go:62-70), so "batch 16" there means sixteen positions, not
+ * sixteen sequences.  Serving several sequences at once is therefore an extension, defined by its oracle: the result
+ * for every sequence is that of a decoder of its own fed the same tokens.  `batch` KV rings per block share the
+ * weights; a decode step carries up to eight sequences per pass over every packed matrix (the M dimension of the
+ * GEMV) and several hidden rows per pass over the LM head.  One GPU only.
+ *
+ * set_batch comes before the first set_block.  select(seq) picks the sequence the single-sequence calls act on
+ * (decoder_forward for its prompt, kv_offset, reset, upload/download_cache, last_hidden, read_tokens ...).  step_batch
+ * forwards one token per sequence (tokens [batch], or NULL to continue greedily from every sequence's last logits) and
+ * returns the logits [batch, vocab] (or NULL to skip the read-back); continue_batch runs `steps` greedy steps for all
+ * sequences on the device without waiting; read_tokens_batch returns the last n tokens every sequence fed to a forward,
+ * [batch, n].  Every sequence needs a prompt behind it before the first batch call. */
+int loom_b200_decoder_set_batch(loom_b200_decoder* dec, int batch);
+int loom_b200_decoder_batch(const loom_b200_decoder* dec);
+int loom_b200_decoder_select(loom_b200_decoder* dec, int seq);
+int loom_b200_decoder_step_batch(loom_b200_decoder* dec, const int32_t* tokens, float* logits_host);
+int loom_b200_decoder_continue_batch(loom_b200_decoder* dec, int steps);
+int loom_b200_decoder_read_tokens_batch(loom_b200_decoder* dec, int32_t* tokens_host, int n);
 /* Cuts the sequence back to its first kv_offset positions (0 < kv_offset <= the current offset), like assigning
  * layer.KVOffset on every MHA layer: the next one-token forward writes position kv_offset.  Ring rows beyond stay
  * until they are overwritten. */

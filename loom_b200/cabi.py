@@ -102,6 +102,12 @@ SIGNATURES = {
     "loom_b200_decoder_upload_cache": (_i, [_vp, _i, _i, _vp, _vp]),
     "loom_b200_decoder_read_tokens": (_i, [_vp, _vp, _i]),
     "loom_b200_decoder_set_kv_offset": (_i, [_vp, _i]),
+    "loom_b200_decoder_set_batch": (_i, [_vp, _i]),
+    "loom_b200_decoder_batch": (_i, [_vp]),
+    "loom_b200_decoder_select": (_i, [_vp, _i]),
+    "loom_b200_decoder_step_batch": (_i, [_vp, _vp, _vp]),
+    "loom_b200_decoder_continue_batch": (_i, [_vp, _i]),
+    "loom_b200_decoder_read_tokens_batch": (_i, [_vp, _vp, _i]),
     "loom_b200_decoder_step_launches": (_i, [_vp]),
     "loom_b200_decoder_linears_frame": (_i, [_vp]),
     "loom_b200_decoder_last_residual": (_i, [_vp, _vp, _i, C.POINTER(_i)]),
@@ -553,6 +559,34 @@ class Decoder:
         v = np.empty((self.dims.max_seq_len, kvd), np.float32)
         self.ctx._check(lib().loom_b200_decoder_download_cache(self.h, block, k.ctypes.data, v.ctypes.data))
         return k, v
+
+    # ---- independent sequences ----
+    def set_batch(self, batch: int):
+        """`batch` independent sequences (one KV ring each); before the first set_block."""
+        self.ctx._check(lib().loom_b200_decoder_set_batch(self.h, batch))
+
+    @property
+    def batch(self) -> int:
+        return lib().loom_b200_decoder_batch(self.h)
+
+    def select(self, seq: int):
+        """The sequence the single-sequence calls (forward, kv_offset, cache, ...) act on."""
+        self.ctx._check(lib().loom_b200_decoder_select(self.h, seq))
+
+    def step_batch(self, tokens=None, want_logits=True):
+        """One token per sequence (None = greedy continuation); logits [batch, vocab]."""
+        t = None if tokens is None else np.ascontiguousarray(tokens, np.int32).ravel()
+        logits = np.empty((self.batch, self.dims.vocab), np.float32) if want_logits else None
+        self.ctx._check(lib().loom_b200_decoder_step_batch(self.h, _hp(t), _hp(logits)))
+        return logits
+
+    def continue_batch(self, steps: int):
+        self.ctx._check(lib().loom_b200_decoder_continue_batch(self.h, steps))
+
+    def generated_tokens_batch(self, n: int) -> np.ndarray:
+        out = np.zeros((self.batch, n), np.int32)
+        self.ctx._check(lib().loom_b200_decoder_read_tokens_batch(self.h, out.ctypes.data, n))
+        return out
 
     def set_kv_offset(self, kv_offset: int):
         """Cuts the sequence back to its first kv_offset positions."""

@@ -93,6 +93,8 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
     __shared__ double s_gw[kAcMaxS * G];     // combine: weight of every (slice, head)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hd = p.hd, half = hd >> 1, kvh = blockIdx.y;
+    const int n = blockIdx.z;  // token of the pass; with seq_stride > 0 every token is a sequence of its own
+    const size_t seq_off = (size_t)n * (size_t)p.seq_stride;
     const uint32_t rank = cluster_ctarank(), S = cluster_nctarank();
     const int cmax = p.max_chunk;  // positions one CTA holds at most
     const int dps = hd / (int)S;   // output dimensions every CTA combines
@@ -113,15 +115,15 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
     lb_pdl_launch_dependents();
     lb_pdl_wait();
     lb_trace(p.trace, 2);
-    const int last = *p.pos_ptr;  // the new token's position; it attends to 0..last
+    const int last = p.seq_stride > 0 ? p.pos_ptr[n] : *p.pos_ptr;  // the new token's position; it attends to 0..last
     const int total = last + 1;
     const int per = (total + (int)S - 1) / (int)S;
     const int k0 = (int)rank * per;
     int k1 = k0 + per;
     if (k1 > total) k1 = total;
     const int cnt = k1 > k0 ? k1 - k0 : 0;
-    const float* kbase = p.cache_k + (size_t)kvh * p.msl * hd;
-    const float* vbase = p.cache_v + (size_t)kvh * p.msl * hd;
+    const float* kbase = p.cache_k + seq_off + (size_t)kvh * p.msl * hd;
+    const float* vbase = p.cache_v + seq_off + (size_t)kvh * p.msl * hd;
     if (cnt > 0 && lane == 0) {
         if (warp == 0) {
             lb_mbar_expect_tx(&bars[0], (uint32_t)cnt * hd * 4);
@@ -144,7 +146,7 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
             rsn = sn;
             rc = c;
         }
-        const double* qrow = p.q + (size_t)(kvh * G + g) * hd;
+        const double* qrow = p.q + (size_t)n * p.heads * hd + (size_t)(kvh * G + g) * hd;
         const double v0 = qrow[d], v1 = qrow[d + half];
         sq[g * hd + d] = __dsub_rn(__dmul_rn(v0, c), __dmul_rn(v1, sn));
         sq[g * hd + d + half] = __dadd_rn(__dmul_rn(v0, sn), __dmul_rn(v1, c));
@@ -155,13 +157,14 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
         // the newest position belongs to this slice: its ring row is not written yet; rotate the row the QKV projection
         // left in k_new into the tile and into the ring (threads 0..hd/2-1 hold the sine and cosine of their pair)
         if (tid < half) {
-            const double v0 = (double)p.k_new[(size_t)kvh * hd + tid], v1 = (double)p.k_new[(size_t)kvh * hd + tid + half];
+            const float* knew = p.k_new + (size_t)n * p.kv_heads * hd + (size_t)kvh * hd;
+            const double v0 = (double)knew[tid], v1 = (double)knew[tid + half];
             const float r0 = (float)__dsub_rn(__dmul_rn(v0, rc), __dmul_rn(v1, rsn));
             const float r1 = (float)__dadd_rn(__dmul_rn(v0, rsn), __dmul_rn(v1, rc));
             float* trow = kt + (size_t)(last - k0) * hd;
             trow[tid] = r0;
             trow[tid + half] = r1;
-            float* grow = p.cache_k_w + ((size_t)kvh * p.msl + (size_t)(last % p.msl)) * hd;
+            float* grow = p.cache_k_w + seq_off + ((size_t)kvh * p.msl + (size_t)(last % p.msl)) * hd;
             grow[tid] = r0;
             grow[tid + half] = r1;
         }
@@ -307,7 +310,7 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
                 dn = fma(slot[1], w, dn);
             }
         }
-        p.out[(size_t)(kvh * G + g) * hd + (int)rank * dps + dd] = __ddiv_rn(num, dn);
+        p.out[(size_t)n * p.heads * hd + (size_t)(kvh * G + g) * hd + (int)rank * dps + dd] = __ddiv_rn(num, dn);
     }
     lb_trace(p.trace, 5);
 }
@@ -339,7 +342,7 @@ int launch_cluster(loom_b200_ctx* ctx, LbAttnParams p, int S, bool probe_only, i
         ctx->func_attr_mask2 |= bit;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(S, p.kv_heads);
+    cfg.gridDim = dim3(S, p.kv_heads, p.M);
     cfg.blockDim = dim3(kAcThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
@@ -381,7 +384,7 @@ int dispatch_cluster(loom_b200_ctx* ctx, const LbAttnParams& p, int S, bool prob
 }  // namespace
 
 int lb_attention_cluster_size(loom_b200_ctx* ctx, const LbAttnParams& p) {
-    if (p.M != 1 || !p.rope_div || !p.k_new || !p.cache_k_w) return 0;
+    if ((p.M != 1 && p.seq_stride <= 0) || !p.rope_div || !p.k_new || !p.cache_k_w) return 0;
     if (p.kv_heads <= 0 || p.heads % p.kv_heads != 0) return 0;
     const int G = p.heads / p.kv_heads;
     if (G != 1 && G != 2 && G != 4 && G != 8) return 0;

@@ -57,6 +57,15 @@ struct loom_b200_decoder {
     // appends it to the output ring, advances the position and gathers the next embedding row, so a step is
     // {blocks, head} and needs no argmax, position or embedding launch
     bool fused_tail = false;
+    // independent sequences ("lanes"): `batch` KV rings per block and one position, current token, output ring and logits
+    // row per sequence.  The single-sequence calls act on the selected lane: pos, step, out_tokens, logits and cur_tok
+    // point into the arrays below at that lane.
+    int batch = 1, lane = 0;
+    int *pos_all = nullptr, *step_all = nullptr, *tok_all = nullptr, *out_tokens_all = nullptr;
+    float* logits_all = nullptr;
+    int* cur_tok = nullptr;             // the current token of the selected lane (tok when there is one sequence)
+    std::vector<int> kv_offsets;        // host mirror of every lane's position
+    int* h_tok_all = nullptr;           // pinned [batch]
 };
 
 namespace {
@@ -92,9 +101,34 @@ int dec_ensure_prefill(loom_b200_decoder* dec, int tokens) {
     return 0;
 }
 
+// Points the single-sequence state (position, output ring, logits row, current token, KV rings) at one lane.
+void dec_point_at_lane(loom_b200_decoder* dec, int lane) {
+    dec->lane = lane;
+    dec->pos = dec->pos_all + lane;
+    dec->step = dec->step_all + lane;
+    dec->out_tokens = dec->out_tokens_all + (size_t)lane * dec->out_cap;
+    dec->logits = dec->logits_all + (size_t)lane * dec->d.vocab;
+    dec->cur_tok = dec->batch > 1 ? dec->tok_all + lane : dec->tok;
+    dec->kv_offset = dec->kv_offsets.empty() ? 0 : dec->kv_offsets[lane];
+    for (size_t i = 0; i < dec->blocks.size(); ++i) {
+        LbDecBlock& b = dec->blocks[i];
+        if (!b.ready) continue;
+        loom_b200_mha& m = b.mha;
+        m.cache_k = m.cache_k_base + (size_t)lane * m.ring_elems;
+        m.cache_v = m.cache_v_base + (size_t)lane * m.ring_elems;
+        m.pos_dev = dec->pos;
+    }
+    for (size_t i = 0; i + 1 < dec->blocks.size(); ++i) {  // the attention of a block prefetches the KV rows of the block after it
+        if (dec->blocks[i].ready && dec->blocks[i + 1].ready) {
+            dec->blocks[i].mha.next_k = dec->blocks[i + 1].mha.cache_k;
+            dec->blocks[i].mha.next_v = dec->blocks[i + 1].mha.cache_v;
+        }
+    }
+}
+
 // The greedy tail of a head launch that ends a pass of M tokens.
 void dec_fill_tail(loom_b200_decoder* dec, LbLmHeadParams& h, int M) {
-    h.tok_out = dec->tok;
+    h.tok_out = dec->cur_tok;
     h.out_tokens = dec->out_tokens;
     h.out_cap = dec->out_cap;
     h.step = dec->step;
@@ -252,11 +286,13 @@ int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
 // linears_only: just the ternary projections of the step, on the step's own buffers (a measurement frame: the
 // attention, the embedding, the head and the position update are left out, so nothing of the sequence state moves)
 // embed: gather the rows of tok[0..M) first (false when the previous head's tail already left the row in x)
-int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int head_row, bool linears_only = false, bool embed = true) {
+// tok_src: where the M token ids are (null = the staging buffer the host paths fill)
+int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int head_row, bool linears_only = false, bool embed = true,
+                      const int* tok_src = nullptr) {
     loom_b200_ctx* ctx = dec->ctx;
     const loom_b200_decoder_dims& d = dec->d;
     if (!linears_only && embed)
-        if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, d.hidden, dec->tok, M, dec->x)) return rc;
+        if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, d.hidden, tok_src ? tok_src : dec->tok, M, dec->x)) return rc;
     for (auto& b : dec->blocks) {
         LbMhaStepArgs a = {};
         a.pro_mode = LB_PRO_BLOCKNORM;
@@ -323,6 +359,73 @@ int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int 
     return lb_launch_add_scalar(ctx, dec->pos, M);
 }
 
+// One token for each of the sequences lane0 .. lane0+M-1 (M <= 8), every sequence at its own position of its own KV
+// rings: the projections carry the M tokens in one pass over the weights (the same GEMV launches as an M-token chunk of
+// one sequence), RoPE and attention run per (sequence, head), and the head serves several hidden rows per pass over the
+// table.  Its tail publishes every sequence's next token and advances its position.
+int dec_forward_lanes(loom_b200_decoder* dec, int lane0, int M) {
+    loom_b200_ctx* ctx = dec->ctx;
+    const loom_b200_decoder_dims& d = dec->d;
+    const int H = d.hidden;
+    if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, H, dec->tok_all + lane0, M, dec->x)) return rc;
+    for (auto& b : dec->blocks) {
+        LbMhaStepArgs a = {};
+        a.pro_mode = LB_PRO_BLOCKNORM;
+        a.x = dec->x;
+        a.gain = b.g1;
+        a.block_eps = d.rms_eps > 0 ? d.rms_eps : 1e-6;
+        a.out = dec->x;
+        a.residual = dec->x;
+        a.M = M;
+        a.splits = 4;
+        a.fold_rope = true;
+        a.lanes_pos = dec->pos_all + lane0;
+        a.lane0 = lane0;
+        if (int rc = lb_mha_step_dev(&b.mha, a)) return rc;
+        LbSwigluArgs s = {};
+        s.gate = b.gate;
+        s.up = b.up;
+        s.down = b.down;
+        s.inner_w = b.ffn_inner;
+        s.inner_w_len = b.ffn_inner_len;
+        s.inner_eps = 0.0;
+        s.act = d.activation;
+        s.pro_mode = LB_PRO_BLOCKNORM;
+        s.x = dec->x;
+        s.gain = b.g2;
+        s.block_eps = d.rms_eps > 0 ? d.rms_eps : 1e-6;
+        s.prod = dec->prod;
+        s.out = dec->x;
+        s.residual = dec->x;
+        s.M = M;
+        if (int rc = lb_swiglu_dev(ctx, s)) return rc;
+    }
+    const int rpp = lb_lm_head_rows_per_pass(ctx, dec->emb, H);
+    LB_REQUIRE(ctx, rpp >= 1, "decoder: sequences in parallel need the streaming LM head");
+    for (int r0 = 0; r0 < M; r0 += rpp) {
+        LbLmHeadParams h = {};
+        h.nb = M - r0 < rpp ? M - r0 : rpp;
+        h.x = dec->x + (size_t)r0 * H;
+        h.x_stride = H;
+        h.gain = dec->final_gain;
+        h.eps = d.rms_eps > 0 ? d.rms_eps : 1e-6;
+        h.head = dec->emb;
+        h.vocab = d.vocab;
+        h.hidden = H;
+        h.logits = dec->logits_all + (size_t)(lane0 + r0) * d.vocab;
+        h.logits_stride = d.vocab;
+        h.tok_out = dec->tok_all + lane0 + r0;
+        h.out_tokens = dec->out_tokens_all + (size_t)(lane0 + r0) * dec->out_cap;
+        h.out_tokens_stride = dec->out_cap;
+        h.out_cap = dec->out_cap;
+        h.step = dec->step_all + lane0 + r0;
+        h.pos = dec->pos_all + lane0 + r0;
+        h.pos_delta = 1;
+        if (int rc = lb_launch_lm_head(ctx, h)) return rc;
+    }
+    return 0;
+}
+
 int dec_check_ready(loom_b200_decoder* dec) {
     loom_b200_ctx* ctx = dec->ctx;
     LB_REQUIRE(ctx, dec->emb != nullptr, "decoder: embeddings are not set");
@@ -346,14 +449,14 @@ int dec_step(loom_b200_decoder* dec, bool host_token) {
     const loom_b200_decoder_dims& d = dec->d;
     const bool in_frame = !dec->fused_tail;  // without the fused tail the gather is the first launch of the frame
     if (dec->fused_tail && host_token)
-        if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, d.hidden, dec->tok, 1, dec->x)) return rc;
+        if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, d.hidden, dec->cur_tok, 1, dec->x)) return rc;
     if (dec->step_graph) return loom_b200_graph_launch(ctx, dec->step_graph);
-    if (dec->tp_world > 1 && !ctx->opt_tp_graph) return dec_forward_chunk(dec, 1, dec->decode_splits, true, 0);
-    if (int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0, false, in_frame)) return rc;  // warm-up run, counts as the step
+    if (dec->tp_world > 1 && !ctx->opt_tp_graph) return dec_forward_chunk(dec, 1, dec->decode_splits, true, 0, false, true, dec->cur_tok);
+    if (int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0, false, in_frame, dec->cur_tok)) return rc;  // warm-up run, counts as the step
     // record the same step for all later tokens
     if (int rc = loom_b200_graph_begin(ctx)) return rc;
     const uint64_t l0 = ctx->launches;
-    int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0, false, in_frame);
+    int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0, false, in_frame, dec->cur_tok);
     dec->step_launches = (int)(ctx->launches - l0);
     loom_b200_graph* g = nullptr;
     int rc2 = loom_b200_graph_end(ctx, &g);
@@ -411,12 +514,15 @@ int loom_b200_decoder_create(loom_b200_ctx* ctx, const loom_b200_decoder_dims* d
     };
     A((void**)&dec->x, (size_t)kChunkTokens * d.hidden * 4);
     A((void**)&dec->prod, (size_t)kChunkTokens * dec->inter_l * 4);
-    A((void**)&dec->logits, (size_t)d.vocab * 4);
+    A((void**)&dec->logits_all, (size_t)d.vocab * 4);
     A((void**)&dec->hidden, (size_t)d.hidden * 4);
     A((void**)&dec->tok, kChunkTokens * sizeof(int));
-    A((void**)&dec->pos, sizeof(int));
-    A((void**)&dec->step, sizeof(int));
-    A((void**)&dec->out_tokens, (size_t)dec->out_cap * sizeof(int));
+    A((void**)&dec->pos_all, sizeof(int));
+    A((void**)&dec->step_all, sizeof(int));
+    A((void**)&dec->tok_all, sizeof(int));
+    A((void**)&dec->out_tokens_all, (size_t)dec->out_cap * sizeof(int));
+    dec->kv_offsets.assign(1, 0);
+    dec_point_at_lane(dec, 0);
     if (W > 1) {
         A((void**)&dec->tp_stats, 2 * kChunkTokens * sizeof(double));
         A((void**)&dec->tp_acc, (size_t)kChunkTokens * d.hidden * sizeof(int32_t));
@@ -449,11 +555,12 @@ void loom_b200_decoder_destroy(loom_b200_decoder* dec) {
         if (b.ffn_inner) cudaFree(b.ffn_inner);
     }
     dec_free_prefill(dec);
-    void* ptrs[] = {dec->final_gain, dec->x, dec->prod, dec->logits, dec->hidden, dec->tok, dec->pos, dec->step, dec->out_tokens,
-                    dec->tp_stats, dec->tp_acc};
+    void* ptrs[] = {dec->final_gain, dec->x, dec->prod, dec->logits_all, dec->hidden, dec->tok, dec->pos_all, dec->step_all,
+                    dec->tok_all, dec->out_tokens_all, dec->tp_stats, dec->tp_acc};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     if (dec->h_tok) cudaFreeHost(dec->h_tok);
+    if (dec->h_tok_all) cudaFreeHost(dec->h_tok_all);
     if (dec->h_logits) cudaFreeHost(dec->h_logits);
     delete dec;
 }
@@ -497,7 +604,7 @@ int loom_b200_decoder_set_block(loom_b200_decoder* dec, int block, const float* 
     m.wk = w7[1];
     m.wv = w7[2];
     m.wo = w7[3];
-    if (int rc = lb_mha_alloc(ctx, &m, 32)) return rc;
+    if (int rc = lb_mha_alloc(ctx, &m, 32, dec->batch)) return rc;
     cudaFree(m.pos_dev);
     m.pos_dev = dec->pos;
     b.gate = w7[4];
@@ -520,13 +627,7 @@ int loom_b200_decoder_set_block(loom_b200_decoder* dec, int block, const float* 
     }
     LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     b.ready = true;
-    // the attention of a block prefetches the KV rows of the block that runs after it
-    for (size_t i = 0; i + 1 < dec->blocks.size(); ++i) {
-        if (dec->blocks[i].ready && dec->blocks[i + 1].ready) {
-            dec->blocks[i].mha.next_k = dec->blocks[i + 1].mha.cache_k;
-            dec->blocks[i].mha.next_v = dec->blocks[i + 1].mha.cache_v;
-        }
-    }
+    dec_point_at_lane(dec, dec->lane);
     return 0;
 }
 
@@ -576,7 +677,7 @@ int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int
     LB_REQUIRE(ctx, dec->kv_offset + n <= dec->d.max_seq_len, "decoder_forward: %d positions exceed MaxSeqLen %d", dec->kv_offset + n, dec->d.max_seq_len);
     if (n == 1) {
         dec->h_tok[0] = tokens[0];
-        LB_CUDA(ctx, cudaMemcpyAsync(dec->tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+        LB_CUDA(ctx, cudaMemcpyAsync(dec->cur_tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
         if (int rc = dec_step(dec, true)) return rc;
     } else if (n >= kGemmMinTokens && dec->tp_world == 1 && ctx->opt_prefill_gemm) {
         const int cap = n < kPrefillBlock ? n : kPrefillBlock;
@@ -640,6 +741,130 @@ int loom_b200_decoder_download_cache(loom_b200_decoder* dec, int block, float* k
     loom_b200_ctx* ctx = dec->ctx;
     LB_REQUIRE(ctx, block >= 0 && block < (int)dec->blocks.size() && dec->blocks[block].ready, "decoder_download_cache: block %d is not set", block);
     return loom_b200_mha_download_cache(&dec->blocks[block].mha, k_host, v_host);
+}
+
+int loom_b200_decoder_set_batch(loom_b200_decoder* dec, int batch) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_set_batch: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, batch >= 1 && batch <= 256, "decoder_set_batch: %d sequences (1..256)", batch);
+    LB_REQUIRE(ctx, dec->tp_world == 1, "decoder_set_batch: sequences in parallel are not available under a tensor-parallel group");
+    for (auto& b : dec->blocks) LB_REQUIRE(ctx, !b.ready, "decoder_set_batch must be called before decoder_set_block");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_set_batch cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    void* old[] = {dec->logits_all, dec->pos_all, dec->step_all, dec->tok_all, dec->out_tokens_all};
+    for (void* p : old)
+        if (p) cudaFree(p);
+    dec->logits_all = nullptr;
+    dec->pos_all = dec->step_all = dec->tok_all = dec->out_tokens_all = nullptr;
+    if (dec->h_tok_all) cudaFreeHost(dec->h_tok_all);
+    dec->h_tok_all = nullptr;
+    const size_t B = (size_t)batch;
+    cudaError_t e = cudaSuccess;
+    auto A = [&](void** p, size_t bytes) {
+        if (e == cudaSuccess) e = cudaMalloc(p, bytes);
+        if (e == cudaSuccess) e = cudaMemsetAsync(*p, 0, bytes, ctx->stream);
+    };
+    A((void**)&dec->logits_all, B * dec->d.vocab * 4);
+    A((void**)&dec->pos_all, B * sizeof(int));
+    A((void**)&dec->step_all, B * sizeof(int));
+    A((void**)&dec->tok_all, B * sizeof(int));
+    A((void**)&dec->out_tokens_all, B * dec->out_cap * sizeof(int));
+    if (e == cudaSuccess) e = cudaMallocHost((void**)&dec->h_tok_all, B * sizeof(int));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return lb_fail(ctx, LOOM_B200_ERR_CUDA, "decoder_set_batch: %s", cudaGetErrorString(e));
+    dec->batch = batch;
+    dec->kv_offsets.assign(B, 0);
+    dec_drop_graph(dec);
+    dec_point_at_lane(dec, 0);
+    return 0;
+}
+
+int loom_b200_decoder_batch(const loom_b200_decoder* dec) { return dec ? dec->batch : -1; }
+
+int loom_b200_decoder_select(loom_b200_decoder* dec, int seq) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_select: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, seq >= 0 && seq < dec->batch, "decoder_select: sequence %d of %d", seq, dec->batch);
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_select cannot be recorded");
+    if (seq == dec->lane) return 0;
+    dec->kv_offsets[dec->lane] = dec->kv_offset;
+    dec_drop_graph(dec);  // the recorded step holds the previous sequence's ring pointers
+    dec_point_at_lane(dec, seq);
+    return 0;
+}
+
+// host bookkeeping shared by the two batch calls: every sequence must have a prompt behind it and room for `steps` more
+static int dec_batch_ready(loom_b200_decoder* dec, int steps, const char* who) {
+    loom_b200_ctx* ctx = dec->ctx;
+    if (int rc = dec_check_ready(dec)) return rc;
+    LB_REQUIRE(ctx, dec->fused_tail, "%s: sequences in parallel need the streaming LM head (one GPU, hidden size it has room for)", who);
+    dec->kv_offsets[dec->lane] = dec->kv_offset;
+    for (int i = 0; i < dec->batch; ++i) {
+        LB_REQUIRE(ctx, dec->kv_offsets[i] > 0, "%s: sequence %d has no prompt behind it (select it and run decoder_forward first)", who, i);
+        LB_REQUIRE(ctx, dec->kv_offsets[i] + steps <= dec->d.max_seq_len, "%s: sequence %d would exceed MaxSeqLen %d", who, i, dec->d.max_seq_len);
+    }
+    return 0;
+}
+
+int loom_b200_decoder_step_batch(loom_b200_decoder* dec, const int32_t* tokens, float* logits_host) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_step_batch: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_step_batch cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    if (int rc = dec_batch_ready(dec, 1, "decoder_step_batch")) return rc;
+    const int B = dec->batch;
+    if (tokens) {
+        LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the pinned staging buffer is reused
+        for (int i = 0; i < B; ++i) dec->h_tok_all[i] = tokens[i];
+        LB_CUDA(ctx, cudaMemcpyAsync(dec->tok_all, dec->h_tok_all, (size_t)B * sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+    }
+    for (int l0 = 0; l0 < B; l0 += kChunkTokens) {
+        const int M = B - l0 < kChunkTokens ? B - l0 : kChunkTokens;
+        if (int rc = dec_forward_lanes(dec, l0, M)) return rc;
+    }
+    for (int i = 0; i < B; ++i) dec->kv_offsets[i] += 1;
+    dec->kv_offset = dec->kv_offsets[dec->lane];
+    if (logits_host) {
+        LB_CUDA(ctx, cudaMemcpyAsync(logits_host, dec->logits_all, (size_t)B * dec->d.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        if (int rc = lb_sync_checked(ctx)) return rc;
+    }
+    return 0;
+}
+
+int loom_b200_decoder_continue_batch(loom_b200_decoder* dec, int steps) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_continue_batch: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, steps >= 0, "decoder_continue_batch: steps=%d", steps);
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_continue_batch cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    if (int rc = dec_batch_ready(dec, steps, "decoder_continue_batch")) return rc;
+    const int B = dec->batch;
+    for (int s = 0; s < steps; ++s)
+        for (int l0 = 0; l0 < B; l0 += kChunkTokens) {
+            const int M = B - l0 < kChunkTokens ? B - l0 : kChunkTokens;
+            if (int rc = dec_forward_lanes(dec, l0, M)) return rc;
+        }
+    for (int i = 0; i < B; ++i) dec->kv_offsets[i] += steps;
+    dec->kv_offset = dec->kv_offsets[dec->lane];
+    return 0;
+}
+
+int loom_b200_decoder_read_tokens_batch(loom_b200_decoder* dec, int32_t* tokens_host, int n) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_read_tokens_batch: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    LB_REQUIRE(ctx, tokens_host && n > 0, "decoder_read_tokens_batch: bad arguments");
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_read_tokens_batch takes host buffers and cannot be recorded");
+    if (int rc = lb_set_device(ctx)) return rc;
+    if (int rc = lb_sync_checked(ctx)) return rc;
+    std::vector<int> steps(dec->batch);
+    LB_CUDA(ctx, cudaMemcpy(steps.data(), dec->step_all, (size_t)dec->batch * sizeof(int), cudaMemcpyDeviceToHost));
+    for (int i = 0; i < dec->batch; ++i) {
+        const int consumed = steps[i] - 1;  // the newest entry is the token the next step will consume
+        LB_REQUIRE(ctx, n <= consumed && steps[i] <= dec->out_cap, "decoder_read_tokens_batch: sequence %d: %d tokens asked, %d consumed (ring of %d)", i, n, consumed, dec->out_cap);
+        LB_CUDA(ctx, cudaMemcpy(tokens_host + (size_t)i * n, dec->out_tokens_all + (size_t)i * dec->out_cap + (consumed - n), (size_t)n * sizeof(int), cudaMemcpyDeviceToHost));
+    }
+    return 0;
 }
 
 int loom_b200_decoder_set_kv_offset(loom_b200_decoder* dec, int kv_offset) {
@@ -736,7 +961,7 @@ int loom_b200_decoder_generate(loom_b200_decoder* dec, const int32_t* prompt, in
     if (n_prompt == 1) {
         if (int rc = loom_b200_decoder_reset(dec)) return rc;
         dec->h_tok[0] = prompt[0];
-        LB_CUDA(ctx, cudaMemcpyAsync(dec->tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
+        LB_CUDA(ctx, cudaMemcpyAsync(dec->cur_tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
         if (int rc = dec_step(dec, true)) return rc;
         dec->kv_offset = 1;
     } else {

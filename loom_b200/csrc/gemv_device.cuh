@@ -341,9 +341,16 @@ __device__ __noinline__ float activate_slow(float v, int act) { return lb_activa
 
 __device__ __forceinline__ size_t out_index(const LbGemvParams& p, const Smem& sm, const LbGemvSeg& sg, int n, int r) {
     if (sg.out_ring > 0) {
-        const int pos = (sm.pos0 + n) % sg.out_ring;
-        if (sg.ring_hd > 0) return ((size_t)(r / sg.ring_hd) * sg.out_ring + pos) * sg.ring_hd + r % sg.ring_hd;  // head-major KV ring
-        return (size_t)pos * sg.rows + r;
+        size_t base = 0;
+        int pos;
+        if (sg.seq_stride > 0) {  // one ring and one position per token
+            pos = p.pos_ptr[n] % sg.out_ring;
+            base = (size_t)n * (size_t)sg.seq_stride;
+        } else {
+            pos = (sm.pos0 + n) % sg.out_ring;
+        }
+        if (sg.ring_hd > 0) return base + ((size_t)(r / sg.ring_hd) * sg.out_ring + pos) * sg.ring_hd + r % sg.ring_hd;  // head-major KV ring
+        return base + (size_t)pos * sg.rows + r;
     }
     return (size_t)n * sg.rows + r;
 }

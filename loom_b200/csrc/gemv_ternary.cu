@@ -486,8 +486,10 @@ static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int* g
 
 int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     LbGemvParams p = pin;
-    // Wide inputs: normalise and quantize once in a launch of its own, then stream the weights against the int8 row.
-    if (p.pro != LB_PRO_Q8 && p.K >= kSplitQuantK && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
+    // Wide inputs, or three and more tokens: normalise and quantize once in a launch of its own (one CTA per token), then
+    // stream the weights against the int8 rows.  The fused prologue is repeated by every CTA and costs it 4-6 us per token:
+    // right for one or two tokens on the critical path of a decode step, wrong for a pass of eight.
+    if (p.pro != LB_PRO_Q8 && (p.K >= kSplitQuantK || p.M >= kSplitQuantTokens) && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
         (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) && (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) &&
         (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0)) {
         const size_t qbytes = ((size_t)p.M * p.K + 255) & ~(size_t)255;

@@ -40,6 +40,9 @@ struct LbGemvSeg {
     int kind;
     int ring_hd;            // with out_ring: the ring is head-major [rows/ring_hd][out_ring][ring_hd] (0 = position-major rows)
     int out_ring;  // > 0: token n goes to row (*pos_ptr + n) % out_ring of `out` (the KV ring), else row n
+    // > 0: the tokens are independent sequences: token n writes row pos_ptr[n] % out_ring of the ring that starts
+    // seq_stride elements after the ring of token n - 1
+    long long seq_stride;
 };
 
 // Tokens one pass can carry for K input columns: the int8 activations of all tokens sit in shared memory beside a
@@ -106,4 +109,5 @@ __device__ __forceinline__ double lb_pro_value(double x, double root, double rr,
 // Inputs at least this wide are normalised and quantized by one stand-alone launch (lb_launch_norm_quantize)
 // instead of inside every CTA of the GEMV.
 constexpr int kSplitQuantK = 8192;
+constexpr int kSplitQuantTokens = 3;  // ... and so are passes of at least this many tokens
 int lb_launch_norm_quantize(loom_b200_ctx* ctx, const LbGemvParams& p, int8_t* q, float* amax);

@@ -52,7 +52,7 @@ __global__ void lb_rope_kernel(const LbRopeParams p) {
     lb_pdl_wait();
     lb_trace(p.trace, 2);
     const int n = blockIdx.y, h = blockIdx.x, half = p.hd / 2, d = threadIdx.x;
-    const int pos = *p.pos_ptr + n;
+    const int pos = p.seq_stride > 0 ? p.pos_ptr[n] : *p.pos_ptr + n;
     const bool is_q = h < p.heads;
     double v0, v1;
     float* krow = nullptr;
@@ -63,7 +63,7 @@ __global__ void lb_rope_kernel(const LbRopeParams p) {
         v1 = qrow[d + half];
     } else {
         const int kh = h - p.heads;
-        krow = p.cache_k + ((size_t)kh * p.msl + (size_t)(pos % p.msl)) * p.hd;  // ring is head-major: [kv head][position][hd]
+        krow = p.cache_k + (size_t)n * (size_t)p.seq_stride + ((size_t)kh * p.msl + (size_t)(pos % p.msl)) * p.hd;  // ring is head-major: [kv head][position][hd]
         v0 = (double)krow[d];
         v1 = (double)krow[d + half];
     }
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     lb_pdl_launch_dependents();
     lb_pdl_wait();
     lb_trace(p.trace, 2);
-    const int last = *p.pos_ptr + n;  // attends to positions 0..last
+    const int last = p.seq_stride > 0 ? p.pos_ptr[n] : *p.pos_ptr + n;  // attends to positions 0..last
     const int total = last + 1;
     const int per = (total + p.splits - 1) / p.splits;
     const int k0 = sp * per;
@@ -162,8 +162,8 @@ __global__ void __launch_bounds__(kAttnThreads) lb_attention_kernel(const LbAttn
     if (k1 > total) k1 = total;
     const int cnt = k1 > k0 ? k1 - k0 : 0;
     const int kvh = h / (p.heads / p.kv_heads);
-    const float* kbase = p.cache_k + (size_t)kvh * p.msl * hd;
-    const float* vbase = p.cache_v + (size_t)kvh * p.msl * hd;
+    const float* kbase = p.cache_k + (size_t)n * (size_t)p.seq_stride + (size_t)kvh * p.msl * hd;
+    const float* vbase = p.cache_v + (size_t)n * (size_t)p.seq_stride + (size_t)kvh * p.msl * hd;
     const int ntiles = (cnt + tile - 1) / tile;
     bool failed = false;
     // first K and V tiles: every row of both is requested before anything else happens

@@ -18,6 +18,7 @@ struct LbRopeParams {
     int k_norm_len;
     double qk_eps;
     int M, heads, kv_heads, hd, msl;
+    long long seq_stride;  // > 0: the M tokens are independent sequences: token n is at position pos_ptr[n] of the ring n * seq_stride elements on
     unsigned long long* trace;
 };
 int lb_launch_rope(loom_b200_ctx* ctx, const LbRopeParams& p);
@@ -31,6 +32,7 @@ struct LbAttnParams {
     double* part;          // split scratch [M*heads*splits*(hd+2)]
     unsigned int* cnt;     // [M*heads], zero between launches
     int M, heads, kv_heads, hd, msl, splits;
+    long long seq_stride;  // > 0: the M tokens are independent sequences (see LbRopeParams)
     int max_chunk;         // positions one CTA may hold scores for (shared memory sizing)
     int tile;              // positions per shared-memory tile (set by the launcher)
     // One-token steps without q/k norm can fold RoPE in (one launch less per block): q arrives unrotated, the newest K
@@ -58,6 +60,10 @@ bool lb_attention_prefill_supported(const LbAttnParams& p);
 int lb_launch_attention_prefill(loom_b200_ctx* ctx, const LbAttnParams& p);
 
 struct LbLmHeadParams {
+    // nb hidden rows (independent sequences) share one pass over the table: row b is x + b * x_stride, its logits go to
+    // logits + b * logits_stride and its greedy tail to tok_out[b], out_tokens + b * out_tokens_stride, step[b], pos[b]
+    int nb;                // 0 or 1 = a single row
+    long long x_stride, logits_stride, out_tokens_stride;
     const float* x;        // [hidden] last hidden row (before the final norm)
     const float* gain;     // final RMSNorm gain [hidden] or null (= 1)
     double eps;
@@ -88,6 +94,8 @@ struct LbLmHeadParams {
 int lb_launch_lm_head(loom_b200_ctx* ctx, const LbLmHeadParams& p);
 // whether the streaming head (the one that can carry the greedy tail) takes this table
 bool lb_lm_head_streams(const loom_b200_ctx* ctx, const float* head, int hidden);
+// hidden rows the streaming head serves in one pass over the table (0 = the streaming head does not take this table)
+int lb_lm_head_rows_per_pass(const loom_b200_ctx* ctx, const float* head, int hidden);
 
 // Greedy step: first index of the maximum (poly/sampling.go:45-55) -> tok[0]; appends it to
 // out_tokens[*step]; then *step += 1 and *pos += 1 so that a recorded frame can be replayed as is.

@@ -67,19 +67,23 @@ int lb_swiglu_dev(loom_b200_ctx* ctx, const LbSwigluArgs& a) {
     return lb_launch_gemv(ctx, d);
 }
 
-int lb_mha_alloc(loom_b200_ctx* ctx, loom_b200_mha* m, int max_splits) {
+int lb_mha_alloc(loom_b200_ctx* ctx, loom_b200_mha* m, int max_splits, int lanes) {
     m->ctx = ctx;
-    const size_t cache = (size_t)m->msl * m->kv_dim * sizeof(float);
-    LB_CUDA(ctx, cudaMalloc(&m->cache_k, cache));
-    LB_CUDA(ctx, cudaMalloc(&m->cache_v, cache));
-    LB_CUDA(ctx, cudaMemsetAsync(m->cache_k, 0, cache, ctx->stream));
-    LB_CUDA(ctx, cudaMemsetAsync(m->cache_v, 0, cache, ctx->stream));
+    m->lanes = lanes < 1 ? 1 : lanes;
+    m->ring_elems = (size_t)m->msl * m->kv_dim;
+    const size_t cache = m->ring_elems * sizeof(float) * m->lanes;
+    LB_CUDA(ctx, cudaMalloc(&m->cache_k_base, cache));
+    LB_CUDA(ctx, cudaMalloc(&m->cache_v_base, cache));
+    LB_CUDA(ctx, cudaMemsetAsync(m->cache_k_base, 0, cache, ctx->stream));
+    LB_CUDA(ctx, cudaMemsetAsync(m->cache_v_base, 0, cache, ctx->stream));
+    m->cache_k = m->cache_k_base;
+    m->cache_v = m->cache_v_base;
     LB_CUDA(ctx, cudaMalloc(&m->q, (size_t)kChunkTokens * m->q_dim * sizeof(double)));
     LB_CUDA(ctx, cudaMalloc(&m->attn, (size_t)kChunkTokens * m->q_dim * sizeof(double)));
     LB_CUDA(ctx, cudaMalloc(&m->part, lb_attn_part_elems(kChunkTokens, m->heads, m->head_dim, max_splits) * sizeof(double)));
     LB_CUDA(ctx, cudaMalloc(&m->cnt, (size_t)kChunkTokens * m->heads * sizeof(unsigned int)));
     LB_CUDA(ctx, cudaMemsetAsync(m->cnt, 0, (size_t)kChunkTokens * m->heads * sizeof(unsigned int), ctx->stream));
-    LB_CUDA(ctx, cudaMalloc(&m->k_new, (size_t)m->kv_dim * sizeof(float)));
+    LB_CUDA(ctx, cudaMalloc(&m->k_new, (size_t)kChunkTokens * m->kv_dim * sizeof(float)));
     LB_CUDA(ctx, cudaMalloc(&m->pos_dev, sizeof(int)));
     LB_CUDA(ctx, cudaMemsetAsync(m->pos_dev, 0, sizeof(int), ctx->stream));
     // pow(theta, 2d/hd) in double on the host: the same libm call the CPU path makes once per use
@@ -94,14 +98,35 @@ int lb_mha_alloc(loom_b200_ctx* ctx, loom_b200_mha* m, int max_splits) {
 }
 
 void lb_mha_release(loom_b200_mha* m) {
-    void* ptrs[] = {m->bq, m->bk, m->bv, m->bo, m->q_norm, m->k_norm, m->inner, m->cache_k, m->cache_v,
+    void* ptrs[] = {m->bq, m->bk, m->bv, m->bo, m->q_norm, m->k_norm, m->inner, m->cache_k_base, m->cache_v_base,
                     m->rope_div, m->q, m->attn, m->part, m->cnt, m->pos_dev, m->k_new};
     for (void* p : ptrs)
         if (p) cudaFree(p);
 }
 
-static bool mha_folds_rope(const loom_b200_mha* m, const LbMhaStepArgs& a) {
-    return a.fold_rope && a.M == 1 && !m->q_norm && !m->k_norm && m->ctx->opt_fold_rope;
+// CTAs per KV head of the cluster attention for this layer's shape (0 = not usable); decided once
+static int mha_cluster_size(loom_b200_mha* m) {
+    if (m->attn_cluster < 0) {
+        LbAttnParams t = {};
+        t.M = 1;
+        t.heads = m->heads;
+        t.kv_heads = m->kv_heads;
+        t.hd = m->head_dim;
+        t.msl = m->msl;
+        t.rope_div = m->rope_div;
+        t.k_new = m->k_new;
+        t.cache_k_w = m->cache_k;
+        m->attn_cluster = m->ctx->opt_attn_cluster ? lb_attention_cluster_size(m->ctx, t) : 0;
+    }
+    return m->attn_cluster;
+}
+
+static bool mha_folds_rope(loom_b200_mha* m, const LbMhaStepArgs& a) {
+    // one token of one sequence: RoPE goes into the attention kernel; one token of each of several sequences: only the
+    // cluster kernel knows that layout, otherwise RoPE runs as a launch of its own
+    if (!a.fold_rope || m->q_norm || m->k_norm || !m->ctx->opt_fold_rope) return false;
+    if (a.lanes_pos) return mha_cluster_size(m) > 0;
+    return a.M == 1;
 }
 
 int lb_mha_qkv_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
@@ -117,9 +142,15 @@ int lb_mha_qkv_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     p.seg[2].out_ring = m->msl;
     p.seg[1].ring_hd = m->head_dim;
     p.seg[2].ring_hd = m->head_dim;
-    if (fold_rope) {  // the unrotated K row goes to a side buffer; the attention kernel rotates it into the ring
+    if (a.lanes_pos) {  // one ring and one position per token
+        p.seg[1].out = m->cache_k_base + (size_t)a.lane0 * m->ring_elems;
+        p.seg[2].out = m->cache_v_base + (size_t)a.lane0 * m->ring_elems;
+        p.seg[1].seq_stride = p.seg[2].seq_stride = (long long)m->ring_elems;
+    }
+    if (fold_rope) {  // the unrotated K row goes to a side buffer ([token][kv_dim]); the attention kernel rotates it into the ring
         p.seg[1].out = m->k_new;
         p.seg[1].out_ring = 0;
+        p.seg[1].seq_stride = 0;
     }
     p.K = m->d_model;
     p.M = a.M;
@@ -129,7 +160,7 @@ int lb_mha_qkv_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     p.norm_w_len = a.gain ? m->d_model : 0;
     p.eps = a.block_eps;
     p.epi = LB_EPI_QKV;
-    p.pos_ptr = m->pos_dev;
+    p.pos_ptr = a.lanes_pos ? a.lanes_pos : m->pos_dev;
     p.act = LOOM_B200_ACT_LINEAR;
     if (int rc = lb_gemv_finalize_params(ctx, p)) return rc;
     return lb_launch_gemv(ctx, p);
@@ -153,6 +184,11 @@ int lb_mha_attn_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     r.kv_heads = m->kv_heads;
     r.hd = m->head_dim;
     r.msl = m->msl;
+    if (a.lanes_pos) {
+        r.cache_k = m->cache_k_base + (size_t)a.lane0 * m->ring_elems;
+        r.pos_ptr = a.lanes_pos;
+        r.seq_stride = (long long)m->ring_elems;
+    }
     if (!fold_rope)
         if (int rc = lb_launch_rope(ctx, r)) return rc;
 
@@ -171,17 +207,20 @@ int lb_mha_attn_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
     t.msl = m->msl;
     t.splits = a.splits < 1 ? 1 : (a.splits > m->splits ? m->splits : a.splits);
     t.max_chunk = (m->msl + t.splits - 1) / t.splits;
+    if (a.lanes_pos) {
+        t.cache_k = m->cache_k_base + (size_t)a.lane0 * m->ring_elems;
+        t.cache_v = m->cache_v_base + (size_t)a.lane0 * m->ring_elems;
+        t.pos_ptr = a.lanes_pos;
+        t.seq_stride = (long long)m->ring_elems;
+    }
     if (fold_rope) {
         t.rope_div = m->rope_div;
         t.k_new = m->k_new;
-        t.cache_k_w = m->cache_k;
-        if (ctx->opt_attn_cluster) {
-            if (m->attn_cluster < 0) m->attn_cluster = lb_attention_cluster_size(ctx, t);
-            if (m->attn_cluster > 0) {
-                t.next_k = m->next_k;
-                t.next_v = m->next_v;
-                return lb_launch_attention_cluster(ctx, t, m->attn_cluster);
-            }
+        t.cache_k_w = a.lanes_pos ? m->cache_k_base + (size_t)a.lane0 * m->ring_elems : m->cache_k;
+        if (mha_cluster_size(m) > 0) {
+            t.next_k = a.lanes_pos ? nullptr : m->next_k;  // (the prefetch follows one sequence's rings)
+            t.next_v = a.lanes_pos ? nullptr : m->next_v;
+            return lb_launch_attention_cluster(ctx, t, m->attn_cluster);
         }
     }
     return lb_launch_attention(ctx, t);

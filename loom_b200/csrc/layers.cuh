@@ -41,7 +41,10 @@ struct loom_b200_mha {
     float *bq = nullptr, *bk = nullptr, *bv = nullptr, *bo = nullptr;                     // device, owned
     float *q_norm = nullptr, *k_norm = nullptr, *inner = nullptr;
     int q_norm_len = 0, k_norm_len = 0, inner_len = 0;
-    float *cache_k = nullptr, *cache_v = nullptr;  // [msl, kv_dim]
+    float *cache_k = nullptr, *cache_v = nullptr;  // ring of the selected sequence: [kv_heads, msl, head_dim]
+    float *cache_k_base = nullptr, *cache_v_base = nullptr;  // the allocation: `lanes` rings of ring_elems floats each
+    int lanes = 1;                                 // independent sequences (one ring each)
+    size_t ring_elems = 0;
     double* rope_div = nullptr;                    // [head_dim/2]
     int kv_offset = 0;                             // host mirror of KVOffset
     bool cache_live = false;
@@ -71,6 +74,10 @@ struct LbMhaStepArgs {
     int M;
     int splits;           // attention splits along positions
     bool fold_rope;       // one-token step: let the attention kernel rotate q and the newest K row (no q/k norm only)
+    // lanes_pos != null: the M tokens are independent sequences lane0 .. lane0+M-1, token n at position lanes_pos[n] of
+    // its own ring (RoPE as a launch of its own, attention per (sequence, head))
+    const int* lanes_pos = nullptr;
+    int lane0 = 0;
 };
 // One chunk (M <= 8 tokens at positions *pos_dev ...): QKV -> q/k norm + RoPE -> attention -> inner norm -> O.
 // Does not advance pos_dev.
@@ -79,7 +86,7 @@ int lb_mha_step_dev(loom_b200_mha* m, const LbMhaStepArgs& a);
 int lb_mha_qkv_dev(loom_b200_mha* m, const LbMhaStepArgs& a);
 int lb_mha_attn_dev(loom_b200_mha* m, const LbMhaStepArgs& a);
 int lb_mha_o_dev(loom_b200_mha* m, const LbMhaStepArgs& a);
-int lb_mha_alloc(loom_b200_ctx* ctx, loom_b200_mha* m, int max_splits);
+int lb_mha_alloc(loom_b200_ctx* ctx, loom_b200_mha* m, int max_splits, int lanes = 1);
 void lb_mha_release(loom_b200_mha* m);
 
 // ---- tensor parallelism (tp.cu) -------------------------------------------------------------------------
