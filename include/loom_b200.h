@@ -322,6 +322,11 @@ int loom_b200_decoder_set_block(loom_b200_decoder* dec, int block, const float* 
                                 const float* ffn_inner_norm, int ffn_inner_len);
 /* Tied fp32 embedding / LM head [vocab,hidden] in device memory (borrowed) and the final norm gain (host). */
 int loom_b200_decoder_set_embeddings(loom_b200_decoder* dec, const float* emb_dev, const float* final_gain);
+/* Untied LM head as a packed ternary matrix [vocab, hidden] (borrowed): with an untied head and exact dtypes the
+ * reference runs the head itself through the packed-ternary matvec (usePackedTernaryLMHead / applyPackedTernaryLMHead,
+ * poly/transformer.go:721-755): logits = float32(packed matvec of the quantized, final-normalised row).  Call it after
+ * set_embeddings (which still provides the embedding table); NULL goes back to the tied fp32 head. */
+int loom_b200_decoder_set_lm_head_ternary(loom_b200_decoder* dec, const loom_b200_weight* head);
 /* Transformer.Reset */
 int loom_b200_decoder_reset(loom_b200_decoder* dec);
 int loom_b200_decoder_kv_offset(const loom_b200_decoder* dec);

@@ -92,6 +92,7 @@ SIGNATURES = {
     "loom_b200_decoder_destroy": (None, [_vp]),
     "loom_b200_decoder_set_block": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i]),
     "loom_b200_decoder_set_embeddings": (_i, [_vp, _vp, _vp]),
+    "loom_b200_decoder_set_lm_head_ternary": (_i, [_vp, _vp]),
     "loom_b200_decoder_reset": (_i, [_vp]),
     "loom_b200_decoder_kv_offset": (_i, [_vp]),
     "loom_b200_decoder_forward": (_i, [_vp, _vp, _i, _vp]),
@@ -530,6 +531,11 @@ class Decoder:
         self._keep.append(emb_dev)
         fg = _f32(final_gain)
         self.ctx._check(lib().loom_b200_decoder_set_embeddings(self.h, _ptr(emb_dev), _hp(fg)))
+
+    def set_lm_head_ternary(self, head: "Weight"):
+        """Untied LM head as a packed ternary matrix [vocab, hidden] (None = back to the tied fp32 head)."""
+        self._keep.append(head)
+        self.ctx._check(lib().loom_b200_decoder_set_lm_head_ternary(self.h, head.h if head is not None else None))
 
     def reset(self):
         self.ctx._check(lib().loom_b200_decoder_reset(self.h))

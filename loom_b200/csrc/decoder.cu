@@ -28,6 +28,7 @@ struct loom_b200_decoder {
     loom_b200_decoder_dims d{};
     std::vector<LbDecBlock> blocks;
     const float* emb = nullptr;  // borrowed device pointer [vocab, hidden]
+    const loom_b200_weight* head_tern = nullptr;  // untied LM head as a packed ternary matrix [vocab, hidden] (borrowed), or null
     float* final_gain = nullptr;
     float *x = nullptr, *prod = nullptr, *logits = nullptr, *hidden = nullptr;
     int *tok = nullptr, *pos = nullptr, *step = nullptr, *out_tokens = nullptr;
@@ -124,6 +125,31 @@ void dec_point_at_lane(loom_b200_decoder* dec, int lane) {
             dec->blocks[i].mha.next_v = dec->blocks[i + 1].mha.cache_v;
         }
     }
+}
+
+// Untied ternarised LM head (applyPackedTernaryLMHead, poly/transformer.go:736-755): the final RMSNorm is the GEMV's
+// prologue, the logits are float32(packed matvec of the quantized normalised row).
+int dec_head_ternary(loom_b200_decoder* dec, const float* x_row) {
+    loom_b200_ctx* ctx = dec->ctx;
+    LbGemvParams p = {};
+    p.nseg = 1;
+    p.seg[0].tiles = dec->head_tern->tiles;
+    p.seg[0].rows = dec->head_tern->rows;
+    p.seg[0].scale = dec->head_tern->scale;
+    p.seg[0].out = dec->logits;
+    p.seg[0].kind = LB_OUT_F32;
+    p.K = dec->d.hidden;
+    p.M = 1;
+    p.pro = LB_PRO_BLOCKNORM;
+    p.x = x_row;
+    p.norm_w = dec->final_gain;
+    p.norm_w_len = dec->d.hidden;
+    p.eps = dec->d.rms_eps > 0 ? dec->d.rms_eps : 1e-6;
+    p.norm_out = dec->hidden;
+    p.epi = LB_EPI_GENERIC;
+    p.act = LOOM_B200_ACT_LINEAR;
+    if (int rc = lb_gemv_finalize_params(ctx, p)) return rc;
+    return lb_launch_gemv(ctx, p);
 }
 
 // The greedy tail of a head launch that ends a pass of M tokens.
@@ -264,7 +290,9 @@ int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
         o.residual = dec->pf_x;
         if (int rc = lb_gemm_run(ctx, b.down, M, o)) return rc;
     }
-    if (head) {
+    if (head && dec->head_tern) {
+        if (int rc = dec_head_ternary(dec, dec->pf_x + (size_t)(M - 1) * H)) return rc;
+    } else if (head) {
         LbLmHeadParams h = {};
         h.x = dec->pf_x + (size_t)(M - 1) * H;
         h.gain = dec->final_gain;
@@ -332,7 +360,9 @@ int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int 
         if (int rc = lb_swiglu_dev(ctx, s)) return rc;
     }
     if (linears_only) return 0;
-    if (head) {
+    if (head && dec->head_tern) {
+        if (int rc = dec_head_ternary(dec, dec->x + (size_t)head_row * d.hidden)) return rc;
+    } else if (head) {
         LbLmHeadParams h = {};
         h.x = dec->x + (size_t)head_row * d.hidden;
         h.gain = dec->final_gain;
@@ -481,7 +511,7 @@ int loom_b200_decoder_create(loom_b200_ctx* ctx, const loom_b200_decoder_dims* d
     LB_REQUIRE(ctx, d.num_layers > 0 && d.hidden > 0 && d.num_heads > 0 && d.head_dim > 0 && d.intermediate > 0 && d.vocab > 0,
                "decoder_create: bad dimensions");
     LB_REQUIRE(ctx, d.num_heads * d.head_dim == d.hidden, "decoder_create: heads*head_dim must equal hidden");
-    LB_REQUIRE(ctx, d.head_dim % 8 == 0, "decoder_create: head_dim %d must be a multiple of 8", d.head_dim);
+    LB_REQUIRE(ctx, d.head_dim % 2 == 0, "decoder_create: head_dim %d must be even (RoPE rotates pairs)", d.head_dim);
     if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_create cannot be recorded");
     if (int rc = lb_set_device(ctx)) return rc;
     const int W = ctx->tp_world, kvh = d.num_kv_heads == 0 ? d.num_heads : d.num_kv_heads;
@@ -645,6 +675,24 @@ int loom_b200_decoder_set_embeddings(loom_b200_decoder* dec, const float* emb_de
     if (!dec->final_gain) LB_CUDA(ctx, cudaMalloc(&dec->final_gain, (size_t)H * 4));
     LB_CUDA(ctx, cudaMemcpyAsync(dec->final_gain, final_gain ? final_gain : ones.data(), (size_t)H * 4, cudaMemcpyHostToDevice, ctx->stream));
     LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+int loom_b200_decoder_set_lm_head_ternary(loom_b200_decoder* dec, const loom_b200_weight* head) {
+    if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_set_lm_head_ternary: decoder is NULL");
+    loom_b200_ctx* ctx = dec->ctx;
+    if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_set_lm_head_ternary cannot be recorded");
+    LB_REQUIRE(ctx, dec->emb != nullptr, "decoder_set_lm_head_ternary: set the embeddings first");
+    LB_REQUIRE(ctx, dec->tp_world == 1 && dec->batch == 1, "decoder_set_lm_head_ternary: one GPU, one sequence");
+    if (head) {
+        LB_REQUIRE(ctx, head->rows == dec->d.vocab && head->cols == dec->d.hidden, "decoder_set_lm_head_ternary: head is %dx%d, expected %dx%d",
+                   head->rows, head->cols, dec->d.vocab, dec->d.hidden);
+        LB_REQUIRE(ctx, head->device == ctx->device, "decoder_set_lm_head_ternary: head lives on device %d", head->device);
+    }
+    dec_drop_graph(dec);
+    dec->head_tern = head;
+    // the greedy step folded into the fp32 head's tail does not exist for this head: argmax, position and embedding are launches again
+    dec->fused_tail = head == nullptr && dec->tp_world == 1 && lb_lm_head_streams(ctx, dec->emb, dec->d.hidden);
     return 0;
 }
 

@@ -552,6 +552,7 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     LB_PICK(11, true, LB_PRO_Q8, LB_EPI_SWIGLU)
     LB_PICK(12, true, LB_PRO_Q8, LB_EPI_QKV)
     LB_PICK(13, true, LB_PRO_Q8, LB_EPI_RESID)
+    LB_PICK(14, true, LB_PRO_BLOCKNORM, LB_EPI_GENERIC)
 #undef LB_PICK
     if (!kern) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: no kernel for prologue %d with epilogue %d", p.pro, p.epi);
     const unsigned attr_bit = 1u << kid;

@@ -492,6 +492,49 @@ __global__ void __launch_bounds__(256) lb_argmax_advance_kernel(const float* __r
     }
 }
 
+// Attention for head dimensions the tiled kernels do not take (not a multiple of 8, e.g. the reference's own smallest
+// fixture with head_dim 2, poly/tests/bitnet_cpu_test.go:364-386): one warp per (head, token), plain loads, the same
+// float64 arithmetic (poly/mha.go:316-354).  Scores of all positions sit in shared memory.
+__global__ void __launch_bounds__(32) lb_attention_small_kernel(const LbAttnParams p) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    double* sc = reinterpret_cast<double*>(smem_raw);  // [positions]
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    const int h = blockIdx.x, n = blockIdx.y, lane = threadIdx.x;
+    const int hd = p.hd, qd = p.heads * hd;
+    const int last = p.seq_stride > 0 ? p.pos_ptr[n] : *p.pos_ptr + n;
+    const int kvh = h / (p.heads / p.kv_heads);
+    const size_t seq_off = (size_t)n * (size_t)p.seq_stride;
+    const float* kbase = p.cache_k + seq_off + (size_t)kvh * p.msl * hd;
+    const float* vbase = p.cache_v + seq_off + (size_t)kvh * p.msl * hd;
+    const double* q = p.q + (size_t)n * qd + (size_t)h * hd;
+    const double scale = __ddiv_rn(1.0, sqrt((double)hd));
+    double mx = -1e300;
+    for (int j = lane; j <= last; j += 32) {
+        double dot = 0.0;
+        for (int d = 0; d < hd; ++d) dot = __dadd_rn(dot, __dmul_rn(q[d], (double)kbase[(size_t)j * hd + d]));
+        const double s = __dmul_rn(dot, scale);
+        sc[j] = s;
+        mx = fmax(mx, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    double den = 0.0;
+    for (int j = lane; j <= last; j += 32) {
+        const double e = exp(__dsub_rn(sc[j], mx));
+        sc[j] = e;
+        den = __dadd_rn(den, e);
+    }
+    den = lb_warp_sum(den);
+    __syncwarp();
+    for (int d = 0; d < hd; ++d) {
+        double acc = 0.0;
+        for (int j = lane; j <= last; j += 32) acc = __dadd_rn(acc, __dmul_rn(sc[j], (double)vbase[(size_t)j * hd + d]));
+        acc = lb_warp_sum(acc);
+        if (lane == 0) p.out[(size_t)n * qd + (size_t)h * hd + d] = __ddiv_rn(acc, den);
+    }
+}
+
 __global__ void lb_add_scalar_kernel(int* p, int delta) {
     lb_pdl_launch_dependents();
     lb_pdl_wait();
@@ -747,7 +790,20 @@ int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& pin) {
     LbAttnParams p = pin;
     p.trace = lb_trace_row(ctx, "attention");
     p.status = ctx->status_dev;
-    LB_REQUIRE(ctx, p.hd % 8 == 0, "attention: head_dim %d must be a multiple of 8", p.hd);
+    if (p.hd % 8 != 0) {  // small or odd head dimensions: the plain kernel
+        LB_REQUIRE(ctx, p.rope_div == nullptr, "attention: RoPE cannot be folded in for head_dim %d", p.hd);
+        LB_REQUIRE(ctx, p.heads % p.kv_heads == 0, "attention: %d heads over %d kv heads", p.heads, p.kv_heads);
+        const size_t smem = (size_t)p.msl * sizeof(double);
+        if (smem > 200 * 1024) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "attention: %d positions with head_dim %d", p.msl, p.hd);
+        if (smem > 48 * 1024 && !(ctx->func_attr_mask2 & (1u << 16))) {
+            LB_CUDA(ctx, cudaFuncSetAttribute(lb_attention_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            ctx->func_attr_mask2 |= 1u << 16;
+        }
+        p.trace = nullptr;
+        LB_CUDA(ctx, launch_pdl(ctx, lb_attention_small_kernel, dim3(p.heads, p.M), dim3(32), smem, p));
+        ctx->launches++;
+        return 0;
+    }
     LB_REQUIRE(ctx, p.heads % p.kv_heads == 0, "attention: %d heads over %d kv heads", p.heads, p.kv_heads);
     LB_REQUIRE(ctx, p.hd <= kAttnThreads, "attention: head_dim %d above %d is not supported", p.hd, kAttnThreads);
     LB_REQUIRE(ctx, p.splits >= 1 && p.splits <= 64, "attention: %d splits", p.splits);

@@ -124,7 +124,7 @@ static int mha_cluster_size(loom_b200_mha* m) {
 static bool mha_folds_rope(loom_b200_mha* m, const LbMhaStepArgs& a) {
     // one token of one sequence: RoPE goes into the attention kernel; one token of each of several sequences: only the
     // cluster kernel knows that layout, otherwise RoPE runs as a launch of its own
-    if (!a.fold_rope || m->q_norm || m->k_norm || !m->ctx->opt_fold_rope) return false;
+    if (!a.fold_rope || m->q_norm || m->k_norm || !m->ctx->opt_fold_rope || m->head_dim % 8 != 0) return false;
     if (a.lanes_pos) return mha_cluster_size(m) > 0;
     return a.M == 1;
 }
@@ -403,7 +403,7 @@ int loom_b200_mha_create(loom_b200_ctx* ctx, int d_model, int num_heads, int num
     LB_REQUIRE(ctx, out != nullptr, "mha_create: out is NULL");
     *out = nullptr;
     LB_REQUIRE(ctx, wq && wk && wv && wo, "mha_create: weight is NULL");
-    LB_REQUIRE(ctx, d_model > 0 && num_heads > 0 && head_dim > 0 && head_dim % 8 == 0, "mha_create: bad dimensions");
+    LB_REQUIRE(ctx, d_model > 0 && num_heads > 0 && head_dim > 0 && head_dim % 2 == 0, "mha_create: bad dimensions (head_dim must be even: RoPE rotates pairs)");
     if (num_kv_heads == 0) num_kv_heads = num_heads;
     LB_REQUIRE(ctx, num_heads % num_kv_heads == 0, "mha_create: %d heads over %d kv heads", num_heads, num_kv_heads);
     const int qd = num_heads * head_dim, kvd = num_kv_heads * head_dim;

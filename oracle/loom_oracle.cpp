@@ -786,6 +786,7 @@ struct orc_decoder {
     std::vector<orc_block> blocks;
     const float* emb = nullptr;
     std::vector<float> final_gain;
+    orc_matrix* head_tern = nullptr;  // untied LM head as a packed ternary matrix (borrowed), or null = tied fp32 head
 };
 
 namespace {
@@ -876,6 +877,12 @@ int orc_decoder_set_embeddings(orc_decoder* d, const float* emb, const float* fi
     return 0;
 }
 
+int orc_decoder_set_lm_head_ternary(orc_decoder* d, orc_matrix* head) {
+    if (!d || (head && (orc_matrix_rows(head) != d->vocab || orc_matrix_cols(head) != d->hidden))) return -1;
+    d->head_tern = head;
+    return 0;
+}
+
 int orc_decoder_set_kv(orc_decoder* d, int block, int kv_offset, const float* k, const float* v) {
     if (!d || block < 0 || block >= d->layers || !d->blocks[block].mha) return -1;
     return orc_mha_set_state(d->blocks[block].mha, kv_offset, k, v);
@@ -922,7 +929,18 @@ int orc_decoder_forward_taps(orc_decoder* d, const int32_t* tokens, int n, float
     }
     orc_block_rmsnorm(x.data(), n, H, d->final_gain.data(), d->eps, normed.data(), nullptr);
     if (hidden_out) std::memcpy(hidden_out, normed.data(), sizeof(float) * (size_t)n * H);
-    if (logits_out) orc_lm_head(&normed[(size_t)(n - 1) * H], d->emb, d->vocab, H, logits_out, threads);
+    if (logits_out) {
+        if (d->head_tern) {
+            // applyPackedTernaryLMHead, poly/transformer.go:736-755: quantize the normalised row, packed matvec, float32(logit)
+            std::vector<int8_t> xq((size_t)H);
+            const float amax = orc_quantize_f32(&normed[(size_t)(n - 1) * H], H, xq.data());
+            std::vector<double> l64((size_t)d->vocab);
+            if (orc_matrix_matvec(d->head_tern, xq.data(), amax, l64.data(), simd, threads)) return -3;
+            for (int v = 0; v < d->vocab; ++v) logits_out[v] = (float)l64[v];
+        } else {
+            orc_lm_head(&normed[(size_t)(n - 1) * H], d->emb, d->vocab, H, logits_out, threads);
+        }
+    }
     return 0;
 }
 

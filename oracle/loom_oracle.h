@@ -156,6 +156,10 @@ int orc_decoder_set_block_packed(orc_decoder* d, int block, const float* norm1_g
 /* tied fp32 embedding / LM head [vocab,hidden] (borrowed pointer: must outlive the decoder) and final gain */
 int orc_decoder_set_embeddings(orc_decoder* d, const float* emb, const float* final_gain);
 void orc_decoder_reset(orc_decoder* d);
+/* Untied LM head as a packed ternary matrix [vocab, hidden] (usePackedTernaryLMHead / applyPackedTernaryLMHead,
+ * poly/transformer.go:721-755): the logits are float32(packed matvec of the quantized normalised row).  Borrowed pointer;
+ * NULL goes back to the tied fp32 head. */
+int orc_decoder_set_lm_head_ternary(orc_decoder* d, orc_matrix* head);
 /* orc_mha_set_state on one block */
 int orc_decoder_set_kv(orc_decoder* d, int block, int kv_offset, const float* k, const float* v);
 /* forwardOnCPUNormal over n tokens (poly/transformer_forward.go:220-253) then ApplyLMHead on the last row

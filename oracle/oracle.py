@@ -137,6 +137,8 @@ def _declare(L):
     L.orc_decoder_set_block_packed.argtypes = [_vp, C.c_int, _f32p, _f32p, C.POINTER(_u32p), _f32p]
     L.orc_decoder_set_embeddings.restype = C.c_int
     L.orc_decoder_set_embeddings.argtypes = [_vp, _f32p, _f32p]
+    L.orc_decoder_set_lm_head_ternary.restype = C.c_int
+    L.orc_decoder_set_lm_head_ternary.argtypes = [_vp, _vp]
     L.orc_decoder_set_kv.restype = C.c_int
     L.orc_decoder_set_kv.argtypes = [_vp, C.c_int, C.c_int, _f32p, _f32p]
     L.orc_decoder_reset.restype = None
@@ -467,6 +469,11 @@ class Decoder:
         fg = _c(final_gain, np.float32)
         self._keep.append(emb)
         assert lib().orc_decoder_set_embeddings(self.h, _p(emb, _f32p), _p(fg, _f32p)) == 0
+
+    def set_lm_head_ternary(self, head: "Matrix"):
+        """Untied LM head as a packed ternary matrix [vocab, hidden] (poly/transformer.go:721-755)."""
+        self._keep.append(head)
+        assert lib().orc_decoder_set_lm_head_ternary(self.h, head.h) == 0
 
     def set_kv(self, block, kv_offset, k, v):
         k, v = _c(k, np.float32), _c(v, np.float32)

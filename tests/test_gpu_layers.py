@@ -120,16 +120,27 @@ def build_mha(ctx, rng, D, heads, kvh, hd, msl, theta, eps, biases=False, norms=
 
 
 def test_mha_reference_fixture(ctx):
-    # TestPackedTernaryMHAProducesFiniteOutput fixture, poly/tests/bitnet_cpu_test.go:364-386
+    # TestPackedTernaryMHAProducesFiniteOutput fixture, poly/tests/bitnet_cpu_test.go:364-386: d_model 4, two heads of
+    # dimension 2 (below the tiled kernels' vector width: the plain attention kernel computes it)
     s = split_mha_slab(deterministic_weights(80), 4, 2, 2, 2)
     om, gw = [], []
     for k in ("wq", "wk", "wv", "wo"):
         m, w = pair(ctx, s[k], 4, 4)
         om.append(m)
         gw.append(w)
-    # head_dim 2 is below the kernels' vector width: the GPU layer refuses it instead of falling back
-    with pytest.raises(loom_b200.LoomB200Error):
-        cabi.MHA(ctx, 4, 2, 2, 2, 8, 0.0, 0.0, *gw, bq=s["bq"], bk=s["bk"], bv=s["bv"], bo=s["bo"])
+    kw = dict(bq=s["bq"], bk=s["bk"], bv=s["bv"], bo=s["bo"])
+    o = orc.MHA(4, 2, 2, 2, 8, 0.0, 0.0, *om, **kw)
+    g = cabi.MHA(ctx, 4, 2, 2, 2, 8, 0.0, 0.0, *gw, **kw)
+    x = np.array([0.1, -0.2, 0.3, -0.4, 0.2, -0.1, 0.4, -0.3], np.float32).reshape(2, 4)
+    epre, epost = o.forward(x)
+    pre, post = g.forward(x)
+    assert np.isfinite(post).all()
+    assert rel_err(pre, epre) <= REL and rel_err(post, epost) <= REL
+    x1 = np.array([[0.05, 0.15, -0.25, 0.35]], np.float32)
+    _, ep = o.forward(x1)
+    _, gp = g.forward(x1)
+    assert g.kv_offset == 3 and rel_err(gp, ep) <= REL
+    g.close()
 
 
 @pytest.mark.parametrize("D,heads,kvh,hd,seq,biases,norms", [(64, 4, 2, 16, 5, True, True), (256, 2, 1, 128, 12, False, False),
@@ -265,5 +276,32 @@ def test_decoder_prompt_blocks_on_tensor_cores(ctx, n_prompt, H, heads, kvh, hd)
     assert np.allclose(v_gemm[:n_prompt], v_gemv[:n_prompt], rtol=1e-5, atol=1e-6)
     etok, _, _ = odec.generate(prompt, 12, threads=4, attn_threads=4)
     gtok, _ = gdec.generate(prompt, 12)
+    assert (gtok == etok).all()
+    gdec.close()
+
+
+def test_decoder_with_untied_ternary_lm_head(ctx):
+    # with an untied head and exact dtypes the reference runs the LM head through the packed-ternary matvec
+    # (poly/transformer.go:721-755): logits bit-exact up to the final norm's float64 reduction order, tokens identical
+    L, H, heads, kvh, hd, I, V = 2, 256, 4, 2, 64, 384, 1000
+    rng = np.random.default_rng(721)
+    odec, gdec = make_decoder(ctx, rng, L, H, heads, kvh, hd, I, V, 1e-5, 500000.0, cabi.ACT_SILU, 128)
+    head_master = (rng.standard_normal(V * H) * 0.02).astype(np.float32)
+    om = orc.Matrix.from_f32(head_master, V, H)
+    gw = ctx.upload_ternary(om.words, V, H, om.scale)
+    odec.set_lm_head_ternary(om)
+    gdec.set_lm_head_ternary(gw)
+    prompt = rng.integers(0, V, 11).astype(np.int32)
+    elog = odec.forward(prompt)
+    glog = gdec.forward(prompt)
+    assert np.max(np.abs(glog - elog)) <= 1e-5 * max(1.0, float(np.max(np.abs(elog))))
+    assert (glog == elog).mean() > 0.99
+    etok, _, _ = odec.generate(prompt, 12)
+    gtok, _ = gdec.generate(prompt, 12)
+    assert (gtok == etok).all()
+    # a 40-token prompt: the token-block path ends in the same head
+    prompt = rng.integers(0, V, 40).astype(np.int32)
+    etok, _, _ = odec.generate(prompt, 6, threads=4)
+    gtok, _ = gdec.generate(prompt, 6)
     assert (gtok == etok).all()
     gdec.close()
