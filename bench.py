@@ -309,17 +309,22 @@ def gemm_mode(args):
         ws = [ctx.pack_ternary_f32(torch.randn(rows * cols, device=dev, generator=g) * 0.02, rows, cols) for _ in range(8)]
         x = torch.randn(M, cols, device=dev, generator=g)
         out = torch.empty(M, rows, device=dev)
-        for i in range(max(args.warmup, 3)):
-            ctx.ternary_gemm(ws[i % 8], M, x, out=out)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(args.steps):
-            ctx.ternary_gemm(ws[i % 8], M, x, out=out)
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / args.steps
-        res[name] = {"us": us, "tops": 2.0 * M * rows * cols / us / 1e6}
+        # weights as pre-expanded int8 codes (the default; built untimed on each matrix's first GEMM), then as 2-bit tiles
+        # expanded inside the kernel
+        for cached in (1, 0):
+            ctx.set_option("gemm_cache", cached)
+            for i in range(max(args.warmup, 3, 8)):
+                ctx.ternary_gemm(ws[i % 8], M, x, out=out)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(args.steps):
+                ctx.ternary_gemm(ws[i % 8], M, x, out=out)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / args.steps
+            res[name if cached else name + "_expand_in_kernel"] = {"us": us, "tops": 2.0 * M * rows * cols / us / 1e6}
+        ctx.set_option("gemm_cache", 1)
     # config 0 beside it: the same two shapes at M = 1 through the decode GEMV (16 distinct matrices per replay)
     gemv = {}
     for name, rows, cols in (("gate", 6912, 2560), ("down", 2560, 6912)):

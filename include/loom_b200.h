@@ -101,7 +101,10 @@ void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
  * "fold_rope" 0/1 = one-token decoder steps apply RoPE inside the attention kernel (one launch less per block);
  * "decode_splits" 0..32 = position splits of the one-token attention, read by loom_b200_decoder_create (0 = choose); "tp_peer" 0/1 = use the peer mailboxes when attached;
  * "prefill_gemm" 0/1 = prompts of 32 or more tokens
- * run their projections as token-block GEMMs on the tensor cores (1) or eight tokens at a time through the GEMV (0).  "head_stream" 0/1 = the fp32 LM head streams
+ * run their projections as token-block GEMMs on the tensor cores (1) or eight tokens at a time through the GEMV (0).  "gemm_cache" 0/1 = the token-block GEMM reads pre-expanded int8 codes (one byte per weight, built per
+ * matrix the first time it meets the GEMM, four times its packed bytes; the device twin of ensureBitNetCodes,
+ * poly/bitnet_cpu.go:700-729) and fuses the SwiGLU gate product into the gate/up GEMM (1), or expands the 2-bit tiles
+ * inside the kernel (0); "head_stream" 0/1 = the fp32 LM head streams
  * its rows through shared memory with bulk copies and folds the greedy step (argmax, position, next embedding row) into
  * its tail (1), or runs as a warp-per-row kernel followed by separate launches (0; read when the embeddings are set);
  * "attn_cluster" 0/1 = one-token decoder steps run their attention

@@ -377,6 +377,12 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
     } else if (!strcmp(key, "gemm_tile")) {
         if (value != 0 && value != 128 && value != 256) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "ctx_set_option: gemm_tile is 0, 128 or 256");
         ctx->opt_gemm_tile = value;
+    } else if (!strcmp(key, "quant_regs")) {
+        ctx->opt_quant_regs = value != 0;
+    } else if (!strcmp(key, "gemm_stream")) {
+        ctx->opt_gemm_stream = value != 0;
+    } else if (!strcmp(key, "gemm_cache")) {
+        ctx->opt_gemm_cache = value != 0;
     } else if (!strcmp(key, "prefill_gemm")) {
         ctx->opt_prefill_gemm = value != 0;
     } else if (!strcmp(key, "tp_peer")) {
@@ -716,6 +722,7 @@ void loom_b200_weight_free(loom_b200_ctx* ctx, loom_b200_weight* w) {
         cudaStreamSynchronize(ctx->stream);
     }
     if (w->tiles) cudaFree(w->tiles);
+    if (w->codes8) cudaFree(w->codes8);
     delete w;
 }
 

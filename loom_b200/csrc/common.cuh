@@ -35,6 +35,10 @@ struct loom_b200_weight {
     int strips = 0, kblocks = 0;  // padded rows / 16, padded cols / 128
     float scale = 1.0f;
     uint32_t* tiles = nullptr;  // strips * kblocks * 128 u32
+    // Prefill cache, built the first time the matrix meets the token-block GEMM (context option "gemm_cache"): the codes
+    // as one byte per weight, already in the shared-memory image the tensor core reads, [row block of 128][k-slice of
+    // 128 columns][16 KB].  The device twin of ensureBitNetCodes (poly/bitnet_cpu.go:700-729): 4x the packed bytes.
+    uint8_t* codes8 = nullptr;
     int device = 0;
     size_t tile_bytes() const { return (size_t)strips * kblocks * kTileBytes; }
 };
@@ -83,6 +87,9 @@ struct loom_b200_ctx {
     int opt_gemm_splitk = 1;       // split the K range of the GEMM over several CTAs when there are few output tiles
     int opt_gemm_tile = 0;         // tokens per CTA of the GEMM: 0 = choose, 128 or 256 = force
     int opt_prefill_gemm = 1;      // prompts of 32+ tokens run their projections as token-block GEMMs
+    int opt_quant_regs = 1;        // the GEMM's quantizer keeps a token's row in registers (0: staged in shared memory)
+    int opt_gemm_stream = 1;       // over pre-expanded codes the GEMM runs as a persistent kernel with two accumulator buffers (0: the one-shot kernel)
+    int opt_gemm_cache = 1;        // the token-block GEMM reads pre-expanded int8 codes (built per matrix on first use) instead of expanding the 2-bit tiles in the kernel
     int opt_tp_graph = 1;          // record the sharded decode step (collectives included) as a graph
     void* nccl_comm = nullptr;
     // peer mailboxes (tp.cu): this rank's exchange buffer, the device table of every rank's buffer (own included) as

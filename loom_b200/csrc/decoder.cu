@@ -265,15 +265,22 @@ int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
         qa.norm_w_len = H;
         qa.eps = block_eps;
         if (int rc = lb_gemm_quantize(ctx, qa)) return rc;
-        o = LbGemmOut{};
-        o.act = LOOM_B200_ACT_LINEAR;
-        o.acc_out = dec->pf_accg;
-        if (int rc = lb_gemm_run(ctx, b.gate, M, o)) return rc;
-        o.acc_out = dec->pf_accu;
-        if (int rc = lb_gemm_run(ctx, b.up, M, o)) return rc;
-        if (int rc = lb_gemm_gate_product(ctx, dec->pf_accg, dec->pf_accu, M, I, H, b.gate->scale, b.up->scale, nullptr, nullptr,
-                                          d.activation, dec->pf_prod))
-            return rc;
+        // gate and up as one GEMM with two accumulators and the gate product in its epilogue; without the pre-expanded
+        // codes: two GEMMs that write raw accumulators, then the gate-product kernel
+        int frc = lb_gemm_run_swiglu(ctx, b.gate, b.up, M, nullptr, nullptr, d.activation, dec->pf_prod);
+        if (frc == LOOM_B200_ERR_UNSUPPORTED) {
+            o = LbGemmOut{};
+            o.act = LOOM_B200_ACT_LINEAR;
+            o.acc_out = dec->pf_accg;
+            if (int rc = lb_gemm_run(ctx, b.gate, M, o)) return rc;
+            o.acc_out = dec->pf_accu;
+            if (int rc = lb_gemm_run(ctx, b.up, M, o)) return rc;
+            if (int rc = lb_gemm_gate_product(ctx, dec->pf_accg, dec->pf_accu, M, I, H, b.gate->scale, b.up->scale, nullptr, nullptr,
+                                              d.activation, dec->pf_prod))
+                return rc;
+        } else if (frc) {
+            return frc;
+        }
 
         qa = LbGemmQuant{};
         qa.pro = LB_PRO_INNERNORM;

@@ -39,8 +39,18 @@ constexpr int kSliceBytesA = kRowsPerCta * kSliceK;  // 16 KB
 constexpr int kMaxStages = 6;
 constexpr uint32_t kWaitLimit = 20000000u;
 
+// How the A operand reaches shared memory
+enum GemmMode : int {
+    GEMM_EXPAND = 0,  // eight warps expand the 2-bit tiles to bytes inside the kernel
+    GEMM_CACHED = 1,  // one bulk copy per stage brings 16 KB of pre-expanded codes (loom_b200_weight::codes8)
+};
+
 struct GemmParams {
     const uint32_t* tiles;   // packed weights, tiled layout
+    const uint8_t* codes8;   // pre-expanded codes of the (gate) matrix, or null
+    const uint8_t* codes8_up;  // gate/up pair: pre-expanded codes of the up matrix
+    float scale_up;
+    const float* bias_up;
     int rows, strips, kblocks;
     float scale;
     const int8_t* q;         // int8 activations in core-matrix order (see lb_quantize_gemm_kernel), padded to whole CTA tiles
@@ -91,19 +101,85 @@ __device__ __forceinline__ bool wait_bounded(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
-// stages that fit beside 1 KB of alignment slack: 5 for 128 tokens per CTA, 4 for 256
-template <int NTOK>
+// Float epilogue of sixteen tokens (columns c0 .. c0+15 of the CTA's tile) of weight row r: raw[j] = sum(code * x).
+// int32 -> float64 by the exponent trick (2^52 + 2^31 + a as a bit pattern, minus the constant: exact, and a full-rate
+// addition where the conversion instruction runs at quarter rate).
+__device__ __forceinline__ double gemm_i2d(int a) {
+    return __dadd_rn(__hiloint2double(0x43300000, (int)((unsigned)a ^ 0x80000000u)), -4503601774854144.0);
+}
+
+__device__ __forceinline__ void gemm_emit16(const GemmParams& p, int r, bool row_ok, bool failed, int tok0, int c0, const int* raw,
+                                    const double* s_os, const int* s_xsum, double bias, bool has_bias) {
+    int acc[16];
+    double y[16];
+    float f[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        acc[j] = raw[j] - s_xsum[c0 + j];
+        const double t = __dmul_rn(gemm_i2d(acc[j]), s_os[c0 + j]);
+        y[j] = has_bias ? __dadd_rn(t, bias) : t;
+        f[j] = (float)y[j];
+    }
+    if (row_ok && !failed) {
+        const int ntok = p.tokens - (tok0 + c0);  // columns of this step that are real tokens
+        size_t o0 = (size_t)(tok0 + c0) * p.rows + r, ostride = (size_t)p.rows;
+        if (p.kv_hd > 0) {
+            o0 = ((size_t)(r / p.kv_hd) * p.kv_msl + p.kv_pos0 + tok0 + c0) * p.kv_hd + r % p.kv_hd;
+            ostride = (size_t)p.kv_hd;
+        }
+        if (p.acc_out) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (j < ntok) p.acc_out[o0 + j * ostride] = acc[j];
+        }
+        if (p.out_f64) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (j < ntok) p.out_f64[o0 + j * ostride] = y[j];
+        }
+        if (p.out) {
+            if (p.pre_out) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (j < ntok) p.pre_out[o0 + j * ostride] = f[j];
+            }
+            if (p.act != LOOM_B200_ACT_LINEAR) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (p.act == LOOM_B200_ACT_RELU) f[j] = f[j] < 0.f ? 0.f : f[j];
+                    else if (p.act == LOOM_B200_ACT_RELU2) f[j] = f[j] < 0.f ? 0.f : __fmul_rn(f[j], f[j]);
+                    else f[j] = lb_activate(f[j], p.act);
+                }
+            }
+            if (p.residual) {
+                float rs[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) rs[j] = j < ntok ? p.residual[o0 + j * ostride] : 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) f[j] = __fadd_rn(f[j], rs[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (j < ntok) p.out[o0 + j * ostride] = f[j];
+        }
+    }
+}
+
+// stages that fit beside 1 KB of alignment slack
+template <int NTOK, int MODE>
 struct GemmCfg {
     static constexpr int kSliceBytesB = NTOK * kSliceK;
-    static constexpr int kStageBytes = kSliceBytesA + kSliceBytesB;
-    static constexpr int kStages = NTOK == 128 ? 6 : 4;
+    static constexpr int kStageBytesA = kSliceBytesA;
+    static constexpr int kStageBytes = kStageBytesA + kSliceBytesB;
+    static constexpr int kStages = (200 * 1024) / kStageBytes > kMaxStages ? kMaxStages : (200 * 1024) / kStageBytes;
     static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024;
 };
 
-template <int NTOK>
+template <int NTOK, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(const GemmParams p) {
-    using Cfg = GemmCfg<NTOK>;
+    using Cfg = GemmCfg<NTOK, MODE>;
     constexpr int kStages = Cfg::kStages;
+    constexpr int kTmemCols = NTOK;
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t load_bar[kMaxStages], a_bar[kMaxStages], empty_bar[kMaxStages], done_bar;
     __shared__ uint32_t tmem_base_s;
@@ -113,7 +189,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row0 = blockIdx.x * kRowsPerCta, tok0 = blockIdx.y * NTOK;
     uint8_t* a_ring = smem;
-    uint8_t* b_ring = smem + kStages * kSliceBytesA;
+    uint8_t* b_ring = smem + kStages * Cfg::kStageBytesA;
     // one 128-column k-block per stage; with split-K (gridDim.z > 1) this CTA covers k-blocks [kbase, kbase + nslices)
     const int ktot = p.kblocks;
     const int kbase = (int)((long long)ktot * blockIdx.z / gridDim.z);
@@ -134,7 +210,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         s_failed = 0;
     }
     if (warp == kMmaWarp) {  // the MMA warp owns the tensor-memory allocation
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lb_smem_u32(&tmem_base_s)), "r"(NTOK) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lb_smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -152,8 +228,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
             if (ks >= kStages && !failed && !wait_bounded(&empty_bar[s], (uint32_t)((ks / kStages - 1) & 1))) failed = true;
             if (failed) break;
             if (lane == 0) {
-                lb_mbar_expect_tx(&load_bar[s], (uint32_t)Cfg::kSliceBytesB);
+                lb_mbar_expect_tx(&load_bar[s], (uint32_t)(Cfg::kSliceBytesB + (MODE != GEMM_EXPAND ? Cfg::kStageBytesA : 0)));
                 lb_bulk_g2s(b_ring + (size_t)s * Cfg::kSliceBytesB, qbase + (size_t)ks * 32768, (uint32_t)Cfg::kSliceBytesB, &load_bar[s]);
+                if (MODE != GEMM_EXPAND) {  // the weights of this (row block, k-slice): 16 KB per matrix, already in the tensor core's layout
+                    const size_t blk = ((size_t)blockIdx.x * ktot + kbase + ks) * kSliceBytesA;
+                    lb_bulk_g2s(a_ring + (size_t)s * Cfg::kStageBytesA, p.codes8 + blk, (uint32_t)kSliceBytesA, &load_bar[s]);
+                }
                 if (tr) tr[(1 + ks) * 8 + 0] = lb_gtime();
             }
             __syncwarp();
@@ -175,8 +255,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         const uint4 pad = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
         const uint4* tile0 = reinterpret_cast<const uint4*>(p.tiles + (size_t)(strip0 + (have_strip ? warp : 0)) * p.kblocks * kTileWords) + lane;
         auto fetch = [&](int ks) { return (have_strip && ks < nslices) ? __ldg(tile0 + (size_t)(kbase + ks) * (kTileWords / 4)) : pad; };
-        uint4 w0 = fetch(0), w1 = fetch(1);
-        for (int ks = 0; ks < nslices; ++ks) {
+        uint4 w0 = MODE == GEMM_EXPAND ? fetch(0) : pad, w1 = MODE == GEMM_EXPAND ? fetch(1) : pad;
+        for (int ks = 0; ks < (MODE == GEMM_EXPAND ? nslices : 0); ++ks) {
             const int s = ks % kStages;
             const uint4 w = w0;
             w0 = w1;
@@ -215,61 +295,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         // (sixteen independent int -> float64 -> float32 chains in flight: with two warps per scheduler the epilogue is
         // bound by instruction latency, not throughput), then stored under the per-output conditions.
         const bool has_bias = row_ok && p.bias != nullptr;
-        auto emit = [&](int c0, const int* raw) {  // raw[j] = sum(code * x) of column c0 + j
-            int acc[16];
-            double y[16];
-            float f[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                acc[j] = raw[j] - s_xsum[c0 + j];
-                const double t = __dmul_rn((double)acc[j], s_os[c0 + j]);
-                y[j] = has_bias ? __dadd_rn(t, bias) : t;
-                f[j] = (float)y[j];
-            }
-            if (row_ok && !failed) {
-                const int ntok = p.tokens - (tok0 + c0);  // columns of this step that are real tokens
-                size_t o0 = (size_t)(tok0 + c0) * p.rows + r, ostride = (size_t)p.rows;
-                if (p.kv_hd > 0) {
-                    o0 = ((size_t)(r / p.kv_hd) * p.kv_msl + p.kv_pos0 + tok0 + c0) * p.kv_hd + r % p.kv_hd;
-                    ostride = (size_t)p.kv_hd;
-                }
-                if (p.acc_out) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (j < ntok) p.acc_out[o0 + j * ostride] = acc[j];
-                }
-                if (p.out_f64) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (j < ntok) p.out_f64[o0 + j * ostride] = y[j];
-                }
-                if (p.out) {
-                    if (p.pre_out) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (j < ntok) p.pre_out[o0 + j * ostride] = f[j];
-                    }
-                    if (p.act != LOOM_B200_ACT_LINEAR) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (p.act == LOOM_B200_ACT_RELU) f[j] = f[j] < 0.f ? 0.f : f[j];
-                            else if (p.act == LOOM_B200_ACT_RELU2) f[j] = f[j] < 0.f ? 0.f : __fmul_rn(f[j], f[j]);
-                            else f[j] = lb_activate(f[j], p.act);
-                        }
-                    }
-                    if (p.residual) {
-                        float rs[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) rs[j] = j < ntok ? p.residual[o0 + j * ostride] : 0.f;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) f[j] = __fadd_rn(f[j], rs[j]);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (j < ntok) p.out[o0 + j * ostride] = f[j];
-                }
-            }
-        };
+        auto emit = [&](int c0, const int* raw) { gemm_emit16(p, r, row_ok, failed, tok0, c0, raw, s_os, s_xsum, bias, has_bias); };
         const bool split = gridDim.z > 1;
 #pragma unroll 1
         for (int c0 = chalf * (NTOK / 2); c0 < (chalf + 1) * (NTOK / 2); c0 += 16) {
@@ -332,12 +358,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
         bool failed = false;
         for (int ks = 0; ks < nslices; ++ks) {
             const int s = ks % kStages;
-            if (!failed && !wait_bounded(&a_bar[s], (uint32_t)((ks / kStages) & 1))) failed = true;
-            if (!failed && !wait_bounded(&load_bar[s], (uint32_t)((ks / kStages) & 1))) failed = true;  // the activations (long complete)
+            if (MODE == GEMM_EXPAND && !failed && !wait_bounded(&a_bar[s], (uint32_t)((ks / kStages) & 1))) failed = true;
+            if (!failed && !wait_bounded(&load_bar[s], (uint32_t)((ks / kStages) & 1))) failed = true;  // the activations (and the cached codes)
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (tr && lane == 0) tr[(1 + ks) * 8 + 4] = lb_gtime();
             if (lane == 0 && !failed) {
-                const uint32_t a_addr = lb_smem_u32(a_ring + (size_t)s * kSliceBytesA);
+                const uint32_t a_addr = lb_smem_u32(a_ring + (size_t)s * Cfg::kStageBytesA);
                 const uint32_t b_addr = lb_smem_u32(b_ring + (size_t)s * Cfg::kSliceBytesB);
 #pragma unroll
                 for (int k = 0; k < kSliceK / 32; ++k)  // K = 32 per instruction = two 16-byte chunks = 256 B further
@@ -357,10 +383,222 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_ternary_i8_kernel(con
     __syncthreads();
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(NTOK) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
     if (tid == 0 && s_failed) atomicExch(p.status, 3);
     if (tr && tid == 0) tr[4] = lb_gtime();
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Persistent variant over pre-expanded codes.  One CTA per SM walks output tiles (row tile fastest, so the CTAs that run
+// together share a token tile's activations in L2); the shared-memory ring runs on across tile boundaries, and tensor
+// memory holds TWO accumulator buffers, so the eight epilogue warps drain tile i (tcgen05.ld, float64 rescale, stores)
+// while the MMA warp already accumulates tile i+1.  In the one-shot kernel above the epilogue of a 128 x 256 tile costs
+// about as long as its twenty k-slices of MMAs, and two co-resident CTAs ran in lockstep instead of overlapping.
+// DUAL: a gate / up pair that shares the activations -- both code blocks ride in one stage, two accumulators per buffer
+// (gate at column 0, up at column NTOK), and the epilogue writes float32(gateProduct(yg + bg, yu + bu)) only
+// (poly/swiglu.go:299-310): the two int32 accumulator planes never travel through memory.
+template <int NTOK, bool DUAL>
+struct StreamCfg {
+    static constexpr int kMats = DUAL ? 2 : 1;
+    static constexpr int kBytesB = NTOK * kSliceK;
+    static constexpr int kBytesA = kSliceBytesA * kMats;
+    static constexpr int kStageBytes = kBytesA + kBytesB;
+    static constexpr int kStages = (200 * 1024) / kStageBytes > kMaxStages ? kMaxStages : (200 * 1024) / kStageBytes;
+    static constexpr int kAccCols = NTOK * kMats;  // TMEM columns of one accumulator buffer
+    static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024;
+    static_assert(2 * kAccCols <= 512, "two accumulator buffers must fit the 512 TMEM columns");
+};
+
+template <int NTOK, bool DUAL>
+__global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_stream_kernel(const GemmParams p, int row_tiles, int ntiles) {
+    using Cfg = StreamCfg<NTOK, DUAL>;
+    constexpr int kStages = Cfg::kStages;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t load_bar[kMaxStages], empty_bar[kMaxStages], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ double s_os[NTOK], s_os_up[DUAL ? NTOK : 1];
+    __shared__ int s_xsum[NTOK];
+    __shared__ int s_failed;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint8_t* a_ring = smem;
+    uint8_t* b_ring = smem + kStages * Cfg::kBytesA;
+    const int ktot = p.kblocks;
+    const int my_tiles = (int)blockIdx.x < ntiles ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            lb_mbar_init(&load_bar[s], 1);
+            lb_mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            lb_mbar_init(&acc_full[b], 1);
+            lb_mbar_init(&acc_empty[b], kExpandThreads / 32);  // one arrival per epilogue warp
+        }
+        lb_fence_mbar_init();
+        s_failed = 0;
+    }
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lb_smem_u32(&tmem_base_s)), "r"(2 * Cfg::kAccCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == kLoadWarp) {
+        // ---------------- loads: per stage the activations of the tile's tokens and the code block(s) of its rows ----------------
+        bool failed = false;
+        uint32_t it = 0;
+        for (int i = 0; i < my_tiles && !failed; ++i) {
+            const int t = (int)blockIdx.x + i * (int)gridDim.x;
+            const int rt = t % row_tiles, tok0 = (t / row_tiles) * NTOK;
+            const int8_t* qbase = p.q + (size_t)(tok0 >> 8) * ktot * 32768 + (size_t)((tok0 & 255) >> 3) * 1024;
+            const size_t blk0 = (size_t)rt * ktot * kSliceBytesA;
+            for (int ks = 0; ks < ktot; ++ks, ++it) {
+                const int s = (int)(it % kStages);
+                if (it >= (uint32_t)kStages && !wait_bounded(&empty_bar[s], (it / kStages - 1) & 1)) {
+                    failed = true;
+                    break;
+                }
+                if (lane == 0) {
+                    lb_mbar_expect_tx(&load_bar[s], (uint32_t)Cfg::kStageBytes);
+                    lb_bulk_g2s(b_ring + (size_t)s * Cfg::kBytesB, qbase + (size_t)ks * 32768, (uint32_t)Cfg::kBytesB, &load_bar[s]);
+                    lb_bulk_g2s(a_ring + (size_t)s * Cfg::kBytesA, p.codes8 + blk0 + (size_t)ks * kSliceBytesA, (uint32_t)kSliceBytesA, &load_bar[s]);
+                    if (DUAL)
+                        lb_bulk_g2s(a_ring + (size_t)s * Cfg::kBytesA + kSliceBytesA, p.codes8_up + blk0 + (size_t)ks * kSliceBytesA,
+                                    (uint32_t)kSliceBytesA, &load_bar[s]);
+                }
+                __syncwarp();
+            }
+        }
+        if (failed && lane == 0) atomicExch(&s_failed, 1);
+    } else if (warp == kMmaWarp) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(NTOK >> 3) << 17) | ((uint32_t)(kRowsPerCta >> 4) << 24);
+        bool failed = false;
+        uint32_t it = 0;
+        for (int i = 0; i < my_tiles && !failed; ++i) {
+            const int buf = i & 1;
+            // the epilogue must have drained this buffer's previous tile
+            if (i >= 2 && !wait_bounded(&acc_empty[buf], (uint32_t)(((i >> 1) - 1) & 1))) {
+                failed = true;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t d = tmem_base + (uint32_t)(buf * Cfg::kAccCols);
+            for (int ks = 0; ks < ktot; ++ks, ++it) {
+                const int s = (int)(it % kStages);
+                if (!wait_bounded(&load_bar[s], (it / kStages) & 1)) {
+                    failed = true;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (lane == 0) {
+                    const uint32_t a_addr = lb_smem_u32(a_ring + (size_t)s * Cfg::kBytesA);
+                    const uint32_t b_addr = lb_smem_u32(b_ring + (size_t)s * Cfg::kBytesB);
+#pragma unroll
+                    for (int k = 0; k < kSliceK / 32; ++k)
+                        mma_i8(d, smem_desc(a_addr + k * 256), smem_desc(b_addr + k * 256), idesc, (ks > 0 || k > 0) ? 1u : 0u);
+                    if (DUAL) {
+#pragma unroll
+                        for (int k = 0; k < kSliceK / 32; ++k)
+                            mma_i8(d + (uint32_t)NTOK, smem_desc(a_addr + kSliceBytesA + k * 256), smem_desc(b_addr + k * 256), idesc,
+                                   (ks > 0 || k > 0) ? 1u : 0u);
+                    }
+                    mma_commit(&empty_bar[s]);
+                }
+                __syncwarp();
+            }
+            if (!failed && lane == 0) mma_commit(&acc_full[buf]);  // arrives when every MMA of the tile is done
+            __syncwarp();
+        }
+        if (failed && lane == 0) atomicExch(&s_failed, 1);
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    } else {
+        // ---------------- epilogue warps: tile i while the MMA warp is on tile i + 1 ----------------
+        // a warp may only touch the 32 TMEM lanes of its quarter (warp % 4); the two warps of a quarter split the columns
+        const int quarter = warp & 3, chalf = warp >> 2;
+        bool failed = false;  // after a wait ran out the warp keeps walking the tiles (its named-barrier count must match) without touching TMEM or memory
+        for (int i = 0; i < my_tiles; ++i) {
+            const int t = (int)blockIdx.x + i * (int)gridDim.x;
+            const int rt = t % row_tiles, tok0 = (t / row_tiles) * NTOK, buf = i & 1;
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // the previous tile's scales are no longer read
+            for (int c = tid; c < NTOK; c += kExpandThreads) {
+                const int tok = tok0 + c;
+                s_os[c] = tok < p.tokens ? lb_output_scale(p.scale, p.amax[tok]) : 0.0;
+                if (DUAL) s_os_up[c] = tok < p.tokens ? lb_output_scale(p.scale_up, p.amax[tok]) : 0.0;
+                s_xsum[c] = tok < p.tokens ? p.xsum[tok] : 0;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (!failed && !wait_bounded(&acc_full[buf], (uint32_t)((i >> 1) & 1))) {
+                failed = true;
+                atomicExch(&s_failed, 1);
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int r = rt * kRowsPerCta + quarter * 32 + lane;
+            const bool row_ok = r < p.rows;
+            const bool has_bias = row_ok && p.bias != nullptr;
+            const double bias = has_bias ? (double)p.bias[r] : 0.0;
+            const uint32_t tacc = tmem_base + (uint32_t)(buf * Cfg::kAccCols) + ((uint32_t)(quarter * 32) << 16);
+            if (!failed) {
+#pragma unroll 1
+                for (int c0 = chalf * (NTOK / 2); c0 < (chalf + 1) * (NTOK / 2); c0 += 16) {
+                    uint32_t v[16];
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                                 : "r"(tacc + (uint32_t)c0)
+                                 : "memory");
+                    if (!DUAL) {
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        int raw[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) raw[j] = (int)v[j];
+                        gemm_emit16(p, r, row_ok, false, tok0, c0, raw, s_os, s_xsum, bias, has_bias);
+                    } else {
+                        uint32_t u[16];
+                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                     : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+                                       "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+                                     : "r"(tacc + (uint32_t)(NTOK + c0))
+                                     : "memory");
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        const bool has_bias_up = row_ok && p.bias_up != nullptr;
+                        const double bias_up = has_bias_up ? (double)p.bias_up[r] : 0.0;
+                        float f[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int xs = s_xsum[c0 + j];
+                            double yg = __dmul_rn(gemm_i2d((int)v[j] - xs), s_os[c0 + j]);
+                            double yu = __dmul_rn(gemm_i2d((int)u[j] - xs), s_os_up[c0 + j]);
+                            if (has_bias) yg = __dadd_rn(yg, bias);
+                            if (has_bias_up) yu = __dadd_rn(yu, bias_up);
+                            f[j] = (float)lb_gate_product(yg, yu, p.act);
+                        }
+                        if (row_ok) {
+                            const int ntok = p.tokens - (tok0 + c0);
+                            const size_t o0 = (size_t)(tok0 + c0) * p.rows + r;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (j < ntok) p.out[o0 + (size_t)j * p.rows] = f[j];
+                        }
+                    }
+                }
+            }
+            // this warp's reads of the buffer are complete (wait::ld above): hand it back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * Cfg::kAccCols) : "memory");
+    }
+    if (tid == 0 && s_failed) atomicExch(p.status, 3);
 }
 
 // Measures what the tensor pipe can do on this shape of instruction: one CTA per SM, operands resident in shared memory
@@ -493,6 +731,125 @@ __global__ void __launch_bounds__(256) lb_quantize_gemm_kernel(const LbGemmQuant
     }
 }
 
+// The same quantizer with the token's row held in registers: thread t owns the 16-column chunks t, t + T, ... (CPT of them),
+// loads each with four 16-byte loads (all in flight together), and never stages the row in shared memory; one block
+// reduction for the norm's sum of squares, one for the absmax.  The arithmetic per element is that of the kernel above;
+// only the order of the float64 additions inside the sum of squares differs (per-thread partial sums).
+template <int PRO, int CPT>
+__global__ void __launch_bounds__(256) lb_quantize_gemm_regs_kernel(const LbGemmQuant a, int Kp, int8_t* __restrict__ q,
+                                                                    float* __restrict__ amax_out, int* __restrict__ xsum_out) {
+    __shared__ float red[8];
+    __shared__ double redd[8];
+    __shared__ int redi[8];
+    constexpr bool f64 = PRO == LB_PRO_INNERNORM64;
+    using VT = typename std::conditional<f64, double, float>::type;
+    const int K = a.K, tid = threadIdx.x, T = blockDim.x, nwarps = T >> 5;
+    int8_t* qrow = q + (size_t)(blockIdx.x >> 8) * (Kp >> 7) * 32768 + (size_t)((blockIdx.x & 255) >> 3) * 1024 + (blockIdx.x & 7) * 16;
+    auto chunk_ptr = [&](int ch) { return reinterpret_cast<uint4*>(qrow + (size_t)(ch >> 3) * 32768 + (ch & 7) * 128); };
+    const int nchunks = Kp >> 4;
+    if ((int)blockIdx.x >= a.tokens) {  // padding token: zeros
+        for (int ch = tid; ch < nchunks; ch += T) *chunk_ptr(ch) = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    const VT* row = reinterpret_cast<const VT*>(a.x) + (size_t)blockIdx.x * K;
+    const bool vec = (K % (f64 ? 2 : 4)) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0;
+    VT v[CPT][16];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int base = (tid + c * T) << 4;
+        if (vec && base + 16 <= K) {
+            if (f64) {
+                const double2* src = reinterpret_cast<const double2*>(row + base);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const double2 d = src[k];
+                    v[c][2 * k] = (VT)d.x;
+                    v[c][2 * k + 1] = (VT)d.y;
+                }
+            } else {
+                const float4* src = reinterpret_cast<const float4*>(row + base);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float4 d = src[k];
+                    v[c][4 * k] = (VT)d.x;
+                    v[c][4 * k + 1] = (VT)d.y;
+                    v[c][4 * k + 2] = (VT)d.z;
+                    v[c][4 * k + 3] = (VT)d.w;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) v[c][k] = base + k < K ? row[base + k] : (VT)0;
+        }
+    }
+    float m = 0.0f;
+    if (PRO >= LB_PRO_BLOCKNORM) {
+        double ss = 0.0;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c)
+#pragma unroll
+            for (int k = 0; k < 16; ++k) ss = __dadd_rn(ss, __dmul_rn((double)v[c][k], (double)v[c][k]));  // columns past K hold zero
+        ss = lb_warp_sum(ss);
+        if ((tid & 31) == 0) redd[tid >> 5] = ss;
+        __syncthreads();
+        ss = 0.0;
+        for (int i = 0; i < nwarps; ++i) ss += redd[i];
+        const double root = sqrt(__dadd_rn(__ddiv_rn(ss, (double)K), a.eps));
+        const double rr = __ddiv_rn(1.0, root);
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            const int base = (tid + c * T) << 4;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const int col = base + k;
+                if (col < K) {
+                    const double w = (a.norm_w && col < a.norm_w_len) ? (double)__ldg(a.norm_w + col) : 1.0;
+                    const double y = lb_pro_value<PRO>((double)v[c][k], root, rr, w);
+                    v[c][k] = (VT)y;
+                    if (a.norm_out) a.norm_out[(size_t)blockIdx.x * K + col] = (float)y;
+                    m = fmaxf(m, (float)fabs(y));
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < CPT; ++c)
+#pragma unroll
+            for (int k = 0; k < 16; ++k) m = fmaxf(m, (float)fabs((double)v[c][k]));
+    }
+    m = lb_warp_max(m);
+    if ((tid & 31) == 0) red[tid >> 5] = m;
+    __syncthreads();
+    m = red[0];
+    for (int i = 1; i < nwarps; ++i) m = fmaxf(m, red[i]);
+    if (m < 1e-5f) m = 1e-5f;
+    const double s = __ddiv_rn(127.0, (double)m);
+    int sum = 0;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ch = tid + c * T;
+        if (ch < nchunks) {
+            uint32_t wds[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {  // k = 4b + j -> destination byte 4j + b
+                const int qv = lb_quant_i8((double)v[c][k], s);
+                sum += qv;
+                wds[k & 3] |= (uint32_t)(qv & 0xff) << (8 * (k >> 2));
+            }
+            *chunk_ptr(ch) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+        }
+    }
+    sum = lb_warp_sum_i(sum);
+    if ((tid & 31) == 0) redi[tid >> 5] = sum;
+    __syncthreads();
+    if (tid == 0) {
+        int tot = 0;
+        for (int i = 0; i < nwarps; ++i) tot += redi[i];
+        amax_out[blockIdx.x] = m;
+        xsum_out[blockIdx.x] = tot;
+    }
+}
+
 // gate product of a token block from the raw accumulators of the gate and up GEMMs (swigluGateProduct in float64,
 // poly/swiglu.go:37-46,299-306): prod = float32(f(acc_g * os_g + b_g) * (acc_u * os_u + b_u))
 __global__ void lb_gate_product_acc_kernel(const int32_t* __restrict__ acc_g, const int32_t* __restrict__ acc_u,
@@ -507,6 +864,28 @@ __global__ void lb_gate_product_acc_kernel(const int32_t* __restrict__ acc_g, co
     if (bias_g) yg = __dadd_rn(yg, (double)bias_g[r]);
     if (bias_u) yu = __dadd_rn(yu, (double)bias_u[r]);
     prod[i] = (float)lb_gate_product(yg, yu, act);
+}
+
+// Pre-expands a packed matrix into the GEMM's A image: per (row block of 128, k-slice of 128 columns) 16 KB in K-major
+// no-swizzle core-matrix order, [row / 8][16-byte K chunk][row % 8][16 B], byte 4j+b of a chunk = code of column 4b+j of
+// its 16-column group (the order the in-kernel expansion produces and the quantizer matches).  One thread per 16 bytes.
+__global__ void lb_expand_codes_kernel(const uint32_t* __restrict__ tiles, int strips, int kblocks, uint8_t* __restrict__ codes8) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row block, k-slice, row in block, chunk)
+    const int row_blocks = (strips + 7) / 8;
+    const size_t total = (size_t)row_blocks * kblocks * 128 * 8;
+    if (idx >= total) return;
+    const int kc = (int)(idx & 7), row = (int)((idx >> 3) & 127);
+    const size_t blk = idx >> 10;
+    const int ks = (int)(blk % kblocks), rb = (int)(blk / kblocks);
+    const int strip = rb * 8 + (row >> 4), r16 = row & 15;
+    uint32_t x = 0x55555555u;  // rows past the matrix: weight 0
+    if (strip < strips) {
+        // lane (g,t) of a tile holds [row g, word t] [row g+8, word t] [row g, word 4+t] [row g+8, word 4+t]
+        const int g = r16 & 7, t = kc & 3, slot = (r16 >> 3) | ((kc >> 2) << 1);
+        x = tiles[((size_t)strip * kblocks + ks) * kTileWords + (size_t)(g * 4 + t) * 4 + slot];
+    }
+    const uint4 e = make_uint4(x & 0x03030303u, (x >> 2) & 0x03030303u, (x >> 4) & 0x03030303u, (x >> 6) & 0x03030303u);
+    *reinterpret_cast<uint4*>(codes8 + blk * kSliceBytesA + (size_t)(row >> 3) * 1024 + kc * 128 + (row & 7) * 16) = e;
 }
 
 // layout of the GEMM scratch for `tokens` rows of Kp bytes: int8 rows, amax, sums
@@ -544,6 +923,39 @@ int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a) {
         ctx->gemm_scratch_bytes = need + need / 4;
     }
     GemmScratch g = gemm_scratch_at(ctx->gemm_scratch, a.tokens, Kp);
+    // rows of up to 256 * CPT chunks of 16 columns stay in registers (float rows: CPT up to 8, float64 rows: up to 4)
+    const int nchunks = Kp >> 4;
+    const int cpt_need = (nchunks + 255) / 256;
+    const int cpt = cpt_need <= 1 ? 1 : cpt_need <= 2 ? 2 : cpt_need <= 4 ? 4 : 8;
+    if (ctx->opt_quant_regs && cpt_need <= (a.pro == LB_PRO_INNERNORM64 ? 4 : 8)) {
+        const int T = ((nchunks + cpt - 1) / cpt + 31) / 32 * 32;
+#define LB_QREG(PRO, CPT) lb_quantize_gemm_regs_kernel<PRO, CPT><<<pt, T, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum)
+#define LB_QREG_PRO(PRO)            \
+    switch (cpt) {                  \
+        case 1: LB_QREG(PRO, 1); break; \
+        case 2: LB_QREG(PRO, 2); break; \
+        case 4: LB_QREG(PRO, 4); break; \
+        default: LB_QREG(PRO, 8); break; \
+    }
+        switch (a.pro) {
+            case LB_PRO_F32: LB_QREG_PRO(LB_PRO_F32) break;
+            case LB_PRO_BLOCKNORM: LB_QREG_PRO(LB_PRO_BLOCKNORM) break;
+            case LB_PRO_INNERNORM: LB_QREG_PRO(LB_PRO_INNERNORM) break;
+            case LB_PRO_INNERNORM64:
+                switch (cpt) {
+                    case 1: LB_QREG(LB_PRO_INNERNORM64, 1); break;
+                    case 2: LB_QREG(LB_PRO_INNERNORM64, 2); break;
+                    default: LB_QREG(LB_PRO_INNERNORM64, 4); break;
+                }
+                break;
+            default: return lb_fail(ctx, LOOM_B200_ERR_INVALID, "gemm_quantize: prologue %d", a.pro);
+        }
+#undef LB_QREG_PRO
+#undef LB_QREG
+        LB_CHECK_LAUNCH(ctx, "lb_quantize_gemm_regs_kernel");
+        ctx->launches++;
+        return 0;
+    }
     const size_t qsmem = (size_t)a.K * (a.pro == LB_PRO_INNERNORM64 ? 8 : 4);
     LB_REQUIRE(ctx, qsmem <= 200 * 1024, "gemm_quantize: rows of %d columns do not fit in shared memory", a.K);
     if (!(ctx->func_attr_mask & (1u << 25))) {
@@ -568,6 +980,66 @@ int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a) {
 const float* lb_gemm_last_amax(loom_b200_ctx* ctx, int tokens, int K) {
     const int Kp = (K + kTileCols - 1) / kTileCols * kTileCols;
     return gemm_scratch_at(ctx->gemm_scratch, tokens, Kp).amax;
+}
+
+// Builds the pre-expanded codes of a matrix on first use (4x its packed bytes).  Returns false when the cache is switched
+// off, cannot be built while a graph is being recorded, or does not fit: the caller then expands inside the kernel.
+static bool gemm_ensure_codes(loom_b200_ctx* ctx, const loom_b200_weight* wc) {
+    if (!ctx->opt_gemm_cache) return false;
+    if (wc->codes8) return true;
+    if (ctx->capturing) return false;
+    loom_b200_weight* w = const_cast<loom_b200_weight*>(wc);  // a cache: the matrix itself does not change
+    const int row_blocks = (w->strips + 7) / 8;
+    const size_t bytes = (size_t)row_blocks * w->kblocks * kSliceBytesA;
+    size_t free_b = 0, total_b = 0;
+    if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess || free_b < bytes + (total_b >> 3)) {  // keep an eighth of the device free
+        cudaGetLastError();
+        return false;
+    }
+    uint8_t* c = nullptr;
+    if (cudaMalloc(&c, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    const size_t threads = (size_t)row_blocks * w->kblocks * 128 * 8;
+    lb_expand_codes_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, ctx->stream>>>(w->tiles, w->strips, w->kblocks, c);
+    if (cudaGetLastError() != cudaSuccess) {
+        cudaFree(c);
+        return false;
+    }
+    ctx->launches++;
+    w->codes8 = c;
+    return true;
+}
+
+template <int NTOK, int MODE>
+static int gemm_launch(loom_b200_ctx* ctx, const GemmParams& p, dim3 grid, unsigned attr_bit) {
+    using Cfg = GemmCfg<NTOK, MODE>;
+    if (!(ctx->func_attr_mask2 & attr_bit)) {
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel<NTOK, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmem));
+        ctx->func_attr_mask2 |= attr_bit;
+    }
+    lb_gemm_ternary_i8_kernel<NTOK, MODE><<<grid, kGemmThreads, Cfg::kSmem, ctx->stream>>>(p);
+    LB_CHECK_LAUNCH(ctx, "lb_gemm_ternary_i8_kernel");
+    ctx->launches++;
+    return 0;
+}
+
+// the persistent kernel: one CTA per SM (or per tile, if there are fewer tiles)
+template <int NTOK, bool DUAL>
+static int gemm_launch_stream(loom_b200_ctx* ctx, const GemmParams& p, unsigned attr_bit) {
+    using Cfg = StreamCfg<NTOK, DUAL>;
+    if (!(ctx->func_attr_mask2 & attr_bit)) {
+        LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_stream_kernel<NTOK, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmem));
+        ctx->func_attr_mask2 |= attr_bit;
+    }
+    const int row_tiles = (p.rows + kRowsPerCta - 1) / kRowsPerCta;
+    const int ntiles = row_tiles * ((p.tokens + NTOK - 1) / NTOK);
+    const int grid = ntiles < ctx->sm_count ? ntiles : ctx->sm_count;
+    lb_gemm_stream_kernel<NTOK, DUAL><<<grid, kGemmThreads, Cfg::kSmem, ctx->stream>>>(p, row_tiles, ntiles);
+    LB_CHECK_LAUNCH(ctx, "lb_gemm_stream_kernel");
+    ctx->launches++;
+    return 0;
 }
 
 int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const LbGemmOut& o) {
@@ -613,11 +1085,8 @@ int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const
     bool wide = tokens > 128 && cost256 < cost128;
     if (ctx->opt_gemm_tile == 128) wide = false;
     if (ctx->opt_gemm_tile == 256) wide = true;
-    if (!(ctx->func_attr_mask & (1u << 27))) {
-        LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<128>::kSmem));
-        LB_CUDA(ctx, cudaFuncSetAttribute(lb_gemm_ternary_i8_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<256>::kSmem));
-        ctx->func_attr_mask |= 1u << 27;
-    }
+    const bool cached = gemm_ensure_codes(ctx, w);
+    p.codes8 = w->codes8;
     // Split-K when the output tiles alone would leave more than half of the SMs idle: up to eight CTAs share a tile,
     // each at least four k-slices deep; their int32 partial sums meet in a zero-initialised scratch (exact).
     const int tiles = wide ? ct256 : ct128;
@@ -636,16 +1105,54 @@ int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const
         p.part_acc = ctx->fix_acc;
         p.part_cnt = ctx->fix_cnt;
     }
+    if (cached && splits == 1 && !p.trace && ctx->opt_gemm_stream) {
+        // persistent kernel: a tile's time follows the bytes its stages load (32 KB per slice for 128 tokens, 48 KB for
+        // 256), the launch's time the tiles of the busiest CTA
+        bool wide_s = tokens > 128 && 48 * ((ct256 + sms - 1) / sms) <= 32 * ((ct128 + sms - 1) / sms);
+        if (ctx->opt_gemm_tile == 128) wide_s = false;
+        if (ctx->opt_gemm_tile == 256) wide_s = true;
+        return wide_s ? gemm_launch_stream<256, false>(ctx, p, 1u << 26) : gemm_launch_stream<128, false>(ctx, p, 1u << 27);
+    }
     if (wide) {
         dim3 grid(row_tiles, (tokens + 255) / 256, splits);
-        lb_gemm_ternary_i8_kernel<256><<<grid, kGemmThreads, GemmCfg<256>::kSmem, ctx->stream>>>(p);
-    } else {
-        dim3 grid(row_tiles, (tokens + 127) / 128, splits);
-        lb_gemm_ternary_i8_kernel<128><<<grid, kGemmThreads, GemmCfg<128>::kSmem, ctx->stream>>>(p);
+        return cached ? gemm_launch<256, GEMM_CACHED>(ctx, p, grid, 1u << 20) : gemm_launch<256, GEMM_EXPAND>(ctx, p, grid, 1u << 21);
     }
-    LB_CHECK_LAUNCH(ctx, "lb_gemm_ternary_i8_kernel");
-    ctx->launches++;
-    return 0;
+    dim3 grid(row_tiles, (tokens + 127) / 128, splits);
+    return cached ? gemm_launch<128, GEMM_CACHED>(ctx, p, grid, 1u << 22) : gemm_launch<128, GEMM_EXPAND>(ctx, p, grid, 1u << 23);
+}
+
+// gate and up projections of the block quantized last, fused with the gate product: prod [tokens, inter] float32.  Returns
+// LOOM_B200_ERR_UNSUPPORTED (without touching last_error's meaning for the caller) when the pre-expanded codes are not
+// available; the caller then runs the two projections and the gate-product kernel.
+int lb_gemm_run_swiglu(loom_b200_ctx* ctx, const loom_b200_weight* gate, const loom_b200_weight* up, int tokens, const float* bias_g,
+                       const float* bias_u, int act, float* prod) {
+    LB_REQUIRE(ctx, gate && up && tokens > 0 && prod, "gemm_run_swiglu: bad arguments");
+    LB_REQUIRE(ctx, gate->rows == up->rows && gate->cols == up->cols, "gemm_run_swiglu: gate %dx%d and up %dx%d differ", gate->rows, gate->cols, up->rows, up->cols);
+    if (!ctx->opt_gemm_stream || !gemm_ensure_codes(ctx, gate) || !gemm_ensure_codes(ctx, up)) return LOOM_B200_ERR_UNSUPPORTED;
+    const int Kp = gate->kblocks * kTileCols;
+    LB_REQUIRE(ctx, (size_t)padded_tokens(tokens) * Kp <= ctx->gemm_scratch_bytes, "gemm_run_swiglu: no quantized activations for %d tokens of %d columns", tokens, gate->cols);
+    GemmScratch g = gemm_scratch_at(ctx->gemm_scratch, tokens, Kp);
+    GemmParams p = {};
+    p.tiles = gate->tiles;
+    p.codes8 = gate->codes8;
+    p.codes8_up = up->codes8;
+    p.rows = gate->rows;
+    p.strips = gate->strips;
+    p.kblocks = gate->kblocks;
+    p.scale = gate->scale;
+    p.scale_up = up->scale;
+    p.q = g.q;
+    p.amax = g.amax;
+    p.xsum = g.xsum;
+    p.tokens = tokens;
+    p.Kp = Kp;
+    p.bias = bias_g;
+    p.bias_up = bias_u;
+    p.act = act;
+    p.out = prod;
+    p.status = ctx->status_dev;
+    // 128 tokens per tile: two accumulators of 128 columns in each of the two TMEM buffers
+    return gemm_launch_stream<128, true>(ctx, p, 1u << 25);
 }
 
 int lb_gemm_gate_product(loom_b200_ctx* ctx, const int32_t* acc_g, const int32_t* acc_u, int tokens, int inter, int K, float scale_g,

@@ -125,6 +125,9 @@ struct LbGemmOut {
 };
 int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a);
 int lb_gemm_run(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const LbGemmOut& o);
+// gate and up projections fused with the gate product (needs the pre-expanded codes; LOOM_B200_ERR_UNSUPPORTED otherwise)
+int lb_gemm_run_swiglu(loom_b200_ctx* ctx, const loom_b200_weight* gate, const loom_b200_weight* up, int tokens, const float* bias_g,
+                       const float* bias_u, int act, float* prod);
 // gate product from the raw accumulators of the gate and up projections of the block quantized last (K columns)
 int lb_gemm_gate_product(loom_b200_ctx* ctx, const int32_t* acc_g, const int32_t* acc_u, int tokens, int inter, int K, float scale_g,
                          float scale_u, const float* bias_g, const float* bias_u, int act, float* prod);

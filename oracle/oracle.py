@@ -450,6 +450,7 @@ class Decoder:
         self.h = lib().orc_decoder_create(layers, hidden, heads, kv_heads, head_dim, inter, vocab, eps, theta, act,
                                           max_seq_len)
         self._keep = []
+        self.max_seq_len = max_seq_len
 
     def set_block(self, b, wq, wk, wv, wo, wg, wu, wd, g1=None, g2=None):
         a = [_c(v, np.float32) for v in (g1, wq, wk, wv, wo, g2, wg, wu, wd)]
@@ -476,7 +477,17 @@ class Decoder:
         assert lib().orc_decoder_set_lm_head_ternary(self.h, head.h) == 0
 
     def set_kv(self, block, kv_offset, k, v):
-        k, v = _c(k, np.float32), _c(v, np.float32)
+        """Restores a block's KV rings: rows [0, kv_offset) of k and v ([rows, kv_heads * head_dim]); rows the caller
+        does not give are zero (the C side copies the whole ring of max_seq_len rows)."""
+        kvd = self.dims["kv_heads"] * self.dims["head_dim"]
+        full = []
+        for a in (k, v):
+            a = np.asarray(a, np.float32).reshape(-1, kvd)
+            assert kv_offset <= a.shape[0] <= self.max_seq_len
+            ring = np.zeros((self.max_seq_len, kvd), np.float32)
+            ring[:a.shape[0]] = a
+            full.append(ring)
+        k, v = full
         assert lib().orc_decoder_set_kv(self.h, block, kv_offset, _p(k, _f32p), _p(v, _f32p)) == 0
 
     def reset(self):

@@ -10,9 +10,13 @@ from oracle import oracle as orc
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def ctx():
+@pytest.fixture(scope="module", params=[(1, 1), (1, 0), (0, 0)], ids=["cached-codes-persistent", "cached-codes-one-shot", "expand-in-kernel"])
+def ctx(request):
+    # the ways the weights reach the tensor core: pre-expanded int8 codes (built on a matrix's first GEMM) read by the
+    # persistent kernel with two accumulator buffers or by the one-shot kernel, and 2-bit tiles expanded inside the kernel
     c = loom_b200.Context(0)
+    c.set_option("gemm_cache", request.param[0])
+    c.set_option("gemm_stream", request.param[1])
     yield c
     c.close()
 

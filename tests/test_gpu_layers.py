@@ -272,6 +272,14 @@ def test_decoder_prompt_blocks_on_tensor_cores(ctx, n_prompt, H, heads, kvh, hd)
     finally:
         ctx.set_option("prefill_gemm", 1)
     assert np.max(np.abs(glog - slog)) <= tol
+    # without the pre-expanded codes: tiles expanded in the kernel, gate and up as two GEMMs plus the gate-product kernel;
+    # the arithmetic is the same, so the logits are the same bits
+    ctx.set_option("gemm_cache", 0)
+    try:
+        xlog = gdec.forward(prompt)
+    finally:
+        ctx.set_option("gemm_cache", 1)
+    assert (xlog.view(np.uint32) == glog.view(np.uint32)).all()
     assert np.allclose(k_gemm[:n_prompt], k_gemv[:n_prompt], rtol=1e-5, atol=1e-6)
     assert np.allclose(v_gemm[:n_prompt], v_gemv[:n_prompt], rtol=1e-5, atol=1e-6)
     etok, _, _ = odec.generate(prompt, 12, threads=4, attn_threads=4)
