@@ -196,31 +196,6 @@ int loom_b200_ternary_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, int 
 int loom_b200_ternary_gemm(loom_b200_ctx* ctx, const loom_b200_weight* w, int tokens, const float* x, const float* bias,
                            const float* residual, int activation, float* out, int32_t* acc_out, float* amax_out);
 
-/* A frame of DispatchDenseBitNetTernaryQuantized calls (BeginFrame ... FlushFrame, poly/wgpu_context_native.go:263-276,
- * poly/wgpu_kernels.go:416-475) compiled into a program that ONE persistent launch executes: a CTA per SM walks
- * the jobs in order and streams every job's packed weights through shared memory several jobs ahead, so HBM
- * never waits for the start-up of a small matrix-vector product.  Each job is one loom_b200_ternary_linear
- * (batch 1..8).  depends_on_previous != 0 makes every CTA wait (bounded) until the previous job is complete
- * before this job reads its q / amax / residual; independent jobs flow into each other without a barrier.
- * Results are bit-identical to the individual calls. */
-typedef struct loom_b200_linear_job {
-    const loom_b200_weight* w;
-    int batch;
-    const int8_t* q;       /* [batch, cols] device */
-    const float* amax;     /* [batch] device */
-    const float* bias;     /* [rows] device or NULL */
-    const float* residual; /* [batch, rows] device or NULL */
-    int activation;
-    float* out;            /* [batch, rows] device */
-    int depends_on_previous;
-} loom_b200_linear_job;
-typedef struct loom_b200_program loom_b200_program;
-int loom_b200_linear_program_create(loom_b200_ctx* ctx, int n, const loom_b200_linear_job* jobs, loom_b200_program** out);
-int loom_b200_program_run(loom_b200_ctx* ctx, loom_b200_program* prog);
-/* packed weights + int8 activations + fp32 outputs one run of the program moves */
-uint64_t loom_b200_program_bytes(const loom_b200_program* prog);
-void loom_b200_program_free(loom_b200_ctx* ctx, loom_b200_program* prog);
-
 /* No counterpart in the reference.  The same computation as loom_b200_ternary_linear (without the raw
  * accumulator output) for hosts that must not allocate device memory while they run inference: an embedder
  * with a fixed, already-spent device-memory budget, a frame loop that promised "no allocation after load", or

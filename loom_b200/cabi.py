@@ -72,10 +72,6 @@ SIGNATURES = {
     "loom_b200_quantize_activation_f64": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "loom_b200_ternary_linear": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
     "loom_b200_ternary_gemm": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp]),
-    "loom_b200_linear_program_create": (_i, [_vp, _i, _vp, C.POINTER(_vp)]),
-    "loom_b200_program_run": (_i, [_vp, _vp]),
-    "loom_b200_program_bytes": (C.c_uint64, [_vp]),
-    "loom_b200_program_free": (None, [_vp, _vp]),
     "loom_b200_ternary_linear_no_alloc": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp]),
     "loom_b200_gate_product": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "loom_b200_inner_rmsnorm": (_i, [_vp, _i, _i, _vp, _vp, _i, _d]),
@@ -122,11 +118,6 @@ SIGNATURES = {
     "loom_b200_tp_allreduce_i32": (_i, [_vp, _vp, _sz]),
     "loom_b200_tp_rowsharded_linear": (_i, [_vp, _vp, _i, _vp, _i, _vp, _i, _d, _vp, _vp, _vp]),
 }
-
-
-class LinearJob(C.Structure):
-    _fields_ = [("w", _vp), ("batch", _i), ("q", _vp), ("amax", _vp), ("bias", _vp), ("residual", _vp),
-                ("activation", _i), ("out", _vp), ("depends_on_previous", _i)]
 
 
 class DecoderDims(C.Structure):
@@ -352,25 +343,6 @@ class Context:
     def ternary_gemm(self, w: Weight, tokens, x, out=None, bias=None, residual=None, act=ACT_LINEAR, acc_out=None, amax_out=None):
         self._check(lib().loom_b200_ternary_gemm(self.h, w.h, tokens, _ptr(x), _ptr(bias), _ptr(residual), act, _ptr(out),
                                                  _ptr(acc_out), _ptr(amax_out)))
-
-    def linear_program(self, jobs):
-        """jobs: list of dicts(w, batch, q, amax, out, bias=None, residual=None, act=ACT_LINEAR, depends=False)."""
-        arr = (LinearJob * len(jobs))()
-        for i, j in enumerate(jobs):
-            arr[i] = LinearJob(j["w"].h, j["batch"], _ptr(j["q"]), _ptr(j["amax"]), _ptr(j.get("bias")),
-                               _ptr(j.get("residual")), j.get("act", ACT_LINEAR), _ptr(j["out"]), 1 if j.get("depends") else 0)
-        h = _vp()
-        self._check(lib().loom_b200_linear_program_create(self.h, len(jobs), C.cast(arr, _vp), C.byref(h)))
-        return h
-
-    def program_run(self, prog):
-        self._check(lib().loom_b200_program_run(self.h, prog))
-
-    def program_bytes(self, prog) -> int:
-        return int(lib().loom_b200_program_bytes(prog))
-
-    def program_free(self, prog):
-        lib().loom_b200_program_free(self.h, prog)
 
     # ---- tensor parallelism: one process per GPU, one context per process ----
     @staticmethod

@@ -85,7 +85,7 @@ int lb_sync_checked(loom_b200_ctx* ctx) {
     if (code == 0) return 0;
     *ctx->status_host = 0;
     LB_CUDA(ctx, cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), ctx->stream));
-    static const char* what[] = {"", "a shared-memory tile copy did not complete", "the grid barrier of a program did not complete",
+    static const char* what[] = {"", "a shared-memory tile copy did not complete", "",
                                  "the tensor-core pipeline of the GEMM stalled", "", "a tensor-parallel peer did not answer",
                                  "self-test: a flag that nothing sets"};
     return lb_fail(ctx, LOOM_B200_ERR_TIMEOUT, "a bounded device-side wait ran out (%d: %s); results of the calls since the last sync are invalid",

@@ -1,6 +1,5 @@
-// gemv_device.cuh -- device-side pieces of the packed-ternary GEMV shared by the per-launch kernel
-// (gemv_ternary.cu) and the persistent streaming kernel (stream_program.cu): shared-memory layout, activation
-// staging with the fused normalise/quantize prologues, the per-tile integer MMA step and the epilogues.
+// gemv_device.cuh -- device-side pieces of the packed-ternary GEMV kernel (gemv_ternary.cu): shared-memory layout,
+// activation staging with the fused normalise/quantize prologues, the per-tile integer MMA step and the epilogues.
 #pragma once
 #include "gemv_ternary.cuh"
 

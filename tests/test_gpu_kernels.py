@@ -288,52 +288,6 @@ def test_error_reporting(ctx):
     assert n0 > 0
 
 
-def test_linear_program_matches_individual_calls(ctx):
-    # a frame of ternary linears run by one persistent launch: same bits as the individual dispatches,
-    # including a chain in which every job adds its result to the previous one (depends_on_previous)
-    rng = np.random.default_rng(11)
-    shapes = [(6912, 2560, 1), (2560, 6912, 1), (3840, 2560, 3), (2560, 2560, 8), (40, 70, 2), (6912, 2560, 1)]
-    jobs, expect, keep = [], [], []
-    for rows, cols, batch in shapes:
-        m = orc.Matrix.from_f32((rng.standard_normal(rows * cols) * 0.02).astype(np.float32), rows, cols)
-        w = ctx.upload_ternary(m.words, rows, cols, m.scale)
-        xq, amax = orc.quantize_rows_f32(rng.standard_normal((batch, cols)).astype(np.float32))
-        bias = (rng.standard_normal(rows) * 0.1).astype(np.float32)
-        dq, da, db, do = ctx.to_device(xq), ctx.to_device(amax), ctx.to_device(bias), ctx.alloc(batch * rows * 4)
-        jobs.append(dict(w=w, batch=batch, q=dq, amax=da, bias=db, out=do, act=cabi.ACT_RELU))
-        eo, _ = oracle_linear(m, xq, amax, bias=bias, act=orc.ACT_RELU)
-        expect.append(eo)
-        keep.append((m, w))
-    prog = ctx.linear_program(jobs)
-    assert ctx.program_bytes(prog) > 3 * 4423680
-    for _ in range(3):
-        for j in jobs:
-            ctx.zero(j["out"], j["batch"] * j["w"].rows * 4)
-        ctx.program_run(prog)
-        for j, eo in zip(jobs, expect):
-            got = ctx.download(j["out"], eo.shape, np.float32)
-            assert (got.view(np.uint32) == eo.view(np.uint32)).all()
-    ctx.program_free(prog)
-    # dependent chain: x_{k+1} = W x_q + x_k  (same q, residual = previous output)
-    rows, cols = 2560, 2560
-    m = orc.Matrix.from_f32((rng.standard_normal(rows * cols) * 0.02).astype(np.float32), rows, cols)
-    w = ctx.upload_ternary(m.words, rows, cols, m.scale)
-    xq, amax = orc.quantize_rows_f32(rng.standard_normal((1, cols)).astype(np.float32))
-    dq, da = ctx.to_device(xq), ctx.to_device(amax)
-    x0 = rng.standard_normal((1, rows)).astype(np.float32)
-    bufs = [ctx.to_device(x0)] + [ctx.alloc(rows * 4) for _ in range(6)]
-    chain = [dict(w=w, batch=1, q=dq, amax=da, residual=bufs[k], out=bufs[k + 1], depends=k > 0) for k in range(6)]
-    prog = ctx.linear_program(chain)
-    ctx.program_run(prog)
-    y = m.matvec(xq[0], amax[0]).astype(np.float32)
-    ref = x0[0].copy()
-    for k in range(6):
-        ref = (y + ref).astype(np.float32)
-    got = ctx.download(bufs[6], (rows,), np.float32)
-    assert (got.view(np.uint32) == ref.view(np.uint32)).all()
-    ctx.program_free(prog)
-
-
 def test_bounded_wait_reports_timeout_and_context_survives(ctx):
     # failure detection without a fault: a device-side wait on a flag nothing sets gives up after its poll limit, the
     # status word comes back through sync as LOOM_B200_ERR_TIMEOUT, and the context keeps working afterwards
