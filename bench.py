@@ -488,6 +488,13 @@ TP_SHAPES = {
 }
 
 
+def apply_opts(ctx, args):
+    """`--opt key=value` (repeatable): context options for A/B runs (`loom_b200_ctx_set_option`)."""
+    for kv in getattr(args, "opt", None) or []:
+        k, v = kv.split("=")
+        ctx.set_option(k, int(v))
+
+
 def tp_decode_measure(args, torch, dist, rank, world, local, shape_name, layers, steps, warmup, exchange):
     """Builds rank `rank`'s part of a `shape_name`-shaped ternary decoder (column-sharded Q/K/V/gate/up, row-sharded O/down,
     vocabulary-sharded head) on a context of its own, times `steps` device-resident greedy decode steps (CUDA events,
@@ -503,6 +510,7 @@ def tp_decode_measure(args, torch, dist, rank, world, local, shape_name, layers,
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     ctx = loom_b200.Context(local, tstream.cuda_stream)
+    apply_opts(ctx, args)
     if world > 1:
         idt = torch.zeros(128, dtype=torch.uint8, device=dev)
         if rank == 0:
@@ -628,30 +636,51 @@ def tp_mode(args):
 
 
 def batch_mode(args):
-    """Decode with `--batch` independent sequences on one GPU (configs[3] at one GPU: 8B shape, batch 16, 2048-token prompts):
-    every sequence is prefilled with a prompt of its own, then all of them advance together, up to eight sequences per
-    pass over every packed matrix and several hidden rows per pass over the LM head.  value = sequences x steps / time."""
+    """Decode with `--batch` independent sequences (configs[3]: 8B shape, batch 16, 2048-token prompts): every sequence is
+    prefilled with a prompt of its own, then all of them advance together, up to eight sequences per pass over every
+    packed matrix and several hidden rows per pass over the LM head.  value = sequences x steps / time.  Under torchrun
+    the decoder is tensor-parallel over the ranks (column-sharded Q/K/V/gate/up, row-sharded O/down, vocabulary-sharded
+    head whose tail exchanges (maximum, index) pairs; peer-memory exchange) and `scaling` is "strong"."""
     import torch
+    import torch.distributed as dist
 
     import loom_b200
     from loom_b200 import cabi
 
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
     shape = dict({"2b": SHAPE, **TP_SHAPES}[args.shape])
     if args.layers != SHAPE["layers"]:
         shape["layers"] = args.layers
     B = args.batch
     args.warmup = max(args.warmup, 3)
     shape["max_seq_len"] = args.prompt + args.warmup + args.steps + 8
-    torch.cuda.set_device(0)
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ts = torch.cuda.Stream()
     torch.cuda.set_stream(ts)
-    ctx = loom_b200.Context(0, ts.cuda_stream)
-    dev = torch.device("cuda", 0)
+    ctx = loom_b200.Context(local, ts.cuda_stream)
+    apply_opts(ctx, args)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        idt = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            idt.copy_(torch.frombuffer(bytearray(cabi.Context.tp_unique_id()), dtype=torch.uint8))
+        dist.broadcast(idt, 0)
+        torch.cuda.synchronize()
+        ctx.tp_init(rank, world, bytes(idt.cpu().numpy().tobytes()))
+        mine = torch.frombuffer(bytearray(ctx.tp_peer_handle()), dtype=torch.uint8).to(dev)
+        allh = [torch.zeros(64, dtype=torch.uint8, device=dev) for _ in range(world)]
+        dist.all_gather(allh, mine)
+        torch.cuda.synchronize()
+        ctx.tp_attach_peers(b"".join(bytes(t.cpu().numpy().tobytes()) for t in allh))
     g = torch.Generator(device=dev)
-    g.manual_seed(args.seed)
+    g.manual_seed(args.seed + rank)
     H, I, hd = shape["hidden"], shape["inter"], shape["head_dim"]
-    qd, kvd = shape["heads"] * hd, shape["kv_heads"] * hd
-    dims = ((qd, H), (kvd, H), (kvd, H), (H, qd), (I, H), (I, H), (H, I))
+    qd, kvd, Il = shape["heads"] // world * hd, shape["kv_heads"] // world * hd, I // world
+    dims = ((qd, H), (kvd, H), (kvd, H), (H, qd), (Il, H), (Il, H), (H, Il))
     dec = cabi.Decoder(ctx, shape["layers"], H, shape["heads"], shape["kv_heads"], hd, I, shape["vocab"], shape["eps"],
                        shape["theta"], cabi.ACT_SILU, shape["max_seq_len"])
     dec.set_batch(B)
@@ -664,9 +693,17 @@ def batch_mode(args):
             del master
         dec.set_block(b, ws)
         keep.append(ws)
-    emb = torch.randn(shape["vocab"], H, device=dev, generator=g, dtype=torch.float32) * 0.02
+    ge = torch.Generator(device=dev)
+    ge.manual_seed(args.seed)  # the embedding table is replicated: the same on every rank
+    emb = torch.randn(shape["vocab"], H, device=dev, generator=ge, dtype=torch.float32) * 0.02
     dec.set_embeddings(emb)
     rng = np.random.default_rng(args.seed)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     t0 = time.perf_counter()
     for i in range(B):
         dec.select(i)
@@ -675,32 +712,49 @@ def batch_mode(args):
     prefill_s = time.perf_counter() - t0
     dec.continue_batch(args.warmup)
     ctx.sync()
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(local)
+    barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
+    barrier()
     e0.record()
     dec.continue_batch(args.steps)
     e1.record()
-    torch.cuda.synchronize()
+    barrier()
     dev_s = e0.elapsed_time(e1) * 1e-3
     clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([dev_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_s = float(t[0].item())
     peak, peak_kind = measured_peaks()
     tern_b, kv_b, head_b = algorithmic_bytes(shape, args.prompt + args.warmup + args.steps // 2)
     passes = (B + 7) // 8
     step_s = dev_s / args.steps
-    moved = passes * tern_b + B * kv_b + ((B + 1) // 2) * head_b  # weights once per pass of eight, KV per sequence, head once per pass
-    print(json.dumps({
-        "metric": "decode tok/s (%s-shape ternary decoder, %d independent sequences, one GPU)" % (args.shape.upper(), B),
-        "value": B * args.steps / dev_s, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * step_s, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic",
-        "config": {"workload": "%s-shape ternary decoder, batch %d greedy decode, %d-token prompts" % (args.shape.upper(), B, args.prompt),
-                   "layers": shape["layers"], "batch": B, "prompt": args.prompt, "parallelism": "single GPU"},
-        "per_sequence_tok_per_s": args.steps / dev_s, "prefill_seconds_all_sequences": prefill_s, "clocks": clocks,
-        "roofline": {"bound": "hbm", "achieved": moved / step_s / 1e9, "peak": peak, "unit": "GB/s", "frac": moved / step_s / 1e9 / peak,
-                     "traffic": None, "peak_kind": peak_kind,
-                     "kernel": "whole batch step: packed weights once per pass of eight sequences, KV of every sequence, fp32 head once per head pass"}}))
+    # per GPU: weights once per pass of eight, KV of every sequence, head once per head pass of two rows
+    moved = (passes * tern_b + B * kv_b + ((B + 1) // 2) * head_b) / world
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode tok/s (%s-shape ternary decoder, %d independent sequences, %s)" % (
+                args.shape.upper(), B, "one GPU" if world == 1 else "tensor parallel over %d GPUs" % world),
+            "value": B * args.steps / dev_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * step_s, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
+            "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic",
+            "config": {"workload": "%s-shape ternary decoder, batch %d greedy decode, %d-token prompts" % (args.shape.upper(), B, args.prompt),
+                       "layers": shape["layers"], "batch": B, "prompt": args.prompt,
+                       "parallelism": "single GPU" if world == 1 else "tp%d, peer-memory exchange" % world},
+            "per_sequence_tok_per_s": args.steps / dev_s, "prefill_seconds_all_sequences": prefill_s, "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": moved / step_s / 1e9, "peak": peak, "unit": "GB/s", "frac": moved / step_s / 1e9 / peak,
+                         "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "whole batch step, per GPU: packed weights once per pass of eight sequences, KV of every sequence, fp32 head once per head pass"}}))
+    ctx.sync()
+    dec.close()
+    if world > 1:
+        barrier()
+        ctx.tp_finalize()
+        ctx.close()
+        dist.barrier()
+        dist.destroy_process_group()
     return 0
 
 
@@ -716,6 +770,7 @@ def main():
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=16, help="batch mode: independent sequences")
+    ap.add_argument("--opt", action="append", default=[], help="context option key=value (repeatable), e.g. --opt tp_fused=0")
     ap.add_argument("--mode", default="decode", choices=["decode", "gemm", "tp", "sweep", "batch"],
                     help="gemm: the batched-prefill GEMM microbenchmark; tp: tensor-parallel decode of --shape under torchrun; "
                          "sweep: GEMV vs GEMM over batch sizes for the gate/down projections of --shape")

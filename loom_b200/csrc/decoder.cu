@@ -165,6 +165,39 @@ void dec_fill_tail(loom_b200_decoder* dec, LbLmHeadParams& h, int M) {
     h.x_next = dec->x;
 }
 
+// Whether the fp32 head can carry the greedy step in its tail: the streaming kernel takes the table, and either one GPU
+// or a vocabulary-sharded head whose ranks can exchange their (maximum, index) pairs through the peer mailboxes.
+bool dec_tail_possible(const loom_b200_decoder* dec, const float* emb) {
+    const loom_b200_ctx* ctx = dec->ctx;
+    if (!lb_lm_head_streams(ctx, emb, dec->d.hidden)) return false;
+    if (dec->tp_world == 1) return true;
+    return dec->head_sharded && ctx->tp_peer && ctx->opt_tp_peer;
+}
+
+// this rank's vocabulary slice of the head and the mailbox exchange of its tail
+void dec_shard_head(loom_b200_decoder* dec, LbLmHeadParams& h, float* logits_row) {
+    loom_b200_ctx* ctx = dec->ctx;
+    const int vl = dec->d.vocab / dec->tp_world;
+    h.head = dec->emb + (size_t)dec->tp_rank * vl * dec->d.hidden;
+    h.vocab = vl;
+    h.logits = logits_row + (size_t)dec->tp_rank * vl;
+    if (dec->fused_tail) {
+        h.xchg_peers = (void* const*)ctx->peer_xbuf_dev;
+        h.xchg_rank = dec->tp_rank;
+        h.xchg_world = dec->tp_world;
+        h.vocab_offset = dec->tp_rank * vl;
+        h.xchg_ctr = ctx->x_ctr;
+    }
+}
+
+// with the greedy step in the tail of a sharded head nothing in the step needs the whole row of logits: gather it only
+// for a caller that reads it (every rank makes the same calls, so every rank gets here together)
+int dec_gather_logits(loom_b200_decoder* dec, float* logits_row) {
+    if (!(dec->head_sharded && dec->fused_tail)) return 0;
+    const int vl = dec->d.vocab / dec->tp_world;
+    return lb_tp_allgather_f32(dec->ctx, logits_row + (size_t)dec->tp_rank * vl, logits_row, (size_t)vl);
+}
+
 // A block of M prompt tokens (already in pf_tok) at positions pos0..pos0+M-1 through the whole stack, every
 // projection as a token-block GEMM on the tensor cores.  Same arithmetic as dec_forward_chunk: the quantizer applies
 // the same norms, the GEMM accumulates the same int32 sums, the epilogues rescale in float64.
@@ -379,15 +412,10 @@ int dec_forward_chunk(loom_b200_decoder* dec, int M, int splits, bool head, int 
         h.hidden = d.hidden;
         h.logits = dec->logits;
         h.hidden_out = dec->hidden;
-        if (dec->head_sharded) {
-            const int vl = d.vocab / dec->tp_world;
-            h.head = dec->emb + (size_t)dec->tp_rank * vl * d.hidden;
-            h.vocab = vl;
-            h.logits = dec->logits + (size_t)dec->tp_rank * vl;
-        }
+        if (dec->head_sharded) dec_shard_head(dec, h, dec->logits);
         if (dec->fused_tail) dec_fill_tail(dec, h, M);
         if (int rc = lb_launch_lm_head(ctx, h)) return rc;
-        if (dec->head_sharded)
+        if (dec->head_sharded && !dec->fused_tail)
             if (int rc = lb_tp_allgather_f32(ctx, h.logits, dec->logits, (size_t)h.vocab)) return rc;
     }
     dec->last_resid = dec->x;
@@ -435,6 +463,11 @@ int dec_forward_lanes(loom_b200_decoder* dec, int lane0, int M) {
         s.out = dec->x;
         s.residual = dec->x;
         s.M = M;
+        if (dec->tp_world > 1) {
+            s.inter_global = d.intermediate;
+            s.tp_stats = dec->tp_stats;
+            s.tp_acc = dec->tp_acc;
+        }
         if (int rc = lb_swiglu_dev(ctx, s)) return rc;
     }
     const int rpp = lb_lm_head_rows_per_pass(ctx, dec->emb, H);
@@ -450,6 +483,7 @@ int dec_forward_lanes(loom_b200_decoder* dec, int lane0, int M) {
         h.vocab = d.vocab;
         h.hidden = H;
         h.logits = dec->logits_all + (size_t)(lane0 + r0) * d.vocab;
+        if (dec->head_sharded) dec_shard_head(dec, h, dec->logits_all + (size_t)(lane0 + r0) * d.vocab);
         h.logits_stride = d.vocab;
         h.tok_out = dec->tok_all + lane0 + r0;
         h.out_tokens = dec->out_tokens_all + (size_t)(lane0 + r0) * dec->out_cap;
@@ -488,7 +522,7 @@ int dec_step(loom_b200_decoder* dec, bool host_token) {
     if (dec->fused_tail && host_token)
         if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, d.hidden, dec->cur_tok, 1, dec->x)) return rc;
     if (dec->step_graph) return loom_b200_graph_launch(ctx, dec->step_graph);
-    if (dec->tp_world > 1 && !ctx->opt_tp_graph) return dec_forward_chunk(dec, 1, dec->decode_splits, true, 0, false, true, dec->cur_tok);
+    if (dec->tp_world > 1 && !ctx->opt_tp_graph) return dec_forward_chunk(dec, 1, dec->decode_splits, true, 0, false, in_frame, dec->cur_tok);
     if (int rc = dec_forward_chunk(dec, 1, dec->decode_splits, true, 0, false, in_frame, dec->cur_tok)) return rc;  // warm-up run, counts as the step
     // record the same step for all later tokens
     if (int rc = loom_b200_graph_begin(ctx)) return rc;
@@ -676,7 +710,7 @@ int loom_b200_decoder_set_embeddings(loom_b200_decoder* dec, const float* emb_de
     if (int rc = lb_set_device(ctx)) return rc;
     dec_drop_graph(dec);
     dec->emb = emb_dev;
-    dec->fused_tail = dec->tp_world == 1 && lb_lm_head_streams(ctx, emb_dev, dec->d.hidden);
+    dec->fused_tail = dec_tail_possible(dec, emb_dev);
     const int H = dec->d.hidden;
     std::vector<float> ones(H, 1.0f);
     if (!dec->final_gain) LB_CUDA(ctx, cudaMalloc(&dec->final_gain, (size_t)H * 4));
@@ -699,7 +733,7 @@ int loom_b200_decoder_set_lm_head_ternary(loom_b200_decoder* dec, const loom_b20
     dec_drop_graph(dec);
     dec->head_tern = head;
     // the greedy step folded into the fp32 head's tail does not exist for this head: argmax, position and embedding are launches again
-    dec->fused_tail = head == nullptr && dec->tp_world == 1 && lb_lm_head_streams(ctx, dec->emb, dec->d.hidden);
+    dec->fused_tail = head == nullptr && dec_tail_possible(dec, dec->emb);
     return 0;
 }
 
@@ -757,6 +791,7 @@ int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int
     }
     dec->kv_offset += n;
     if (logits_host) {
+        if (int rc = dec_gather_logits(dec, dec->logits)) return rc;
         LB_CUDA(ctx, cudaMemcpyAsync(dec->h_logits, dec->logits, (size_t)dec->d.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
         if (int rc = lb_sync_checked(ctx)) return rc;
         memcpy(logits_host, dec->h_logits, (size_t)dec->d.vocab * 4);
@@ -802,7 +837,8 @@ int loom_b200_decoder_set_batch(loom_b200_decoder* dec, int batch) {
     if (!dec) return lb_fail(nullptr, LOOM_B200_ERR_INVALID, "decoder_set_batch: decoder is NULL");
     loom_b200_ctx* ctx = dec->ctx;
     LB_REQUIRE(ctx, batch >= 1 && batch <= 256, "decoder_set_batch: %d sequences (1..256)", batch);
-    LB_REQUIRE(ctx, dec->tp_world == 1, "decoder_set_batch: sequences in parallel are not available under a tensor-parallel group");
+    LB_REQUIRE(ctx, dec->tp_world == 1 || (ctx->tp_peer && ctx->opt_tp_peer && dec->head_sharded),
+               "decoder_set_batch: under a tensor-parallel group sequences in parallel need the peer-memory exchange (tp_attach_peers) and a vocabulary that divides by the group");
     for (auto& b : dec->blocks) LB_REQUIRE(ctx, !b.ready, "decoder_set_batch must be called before decoder_set_block");
     if (ctx->capturing) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "decoder_set_batch cannot be recorded");
     if (int rc = lb_set_device(ctx)) return rc;
@@ -853,7 +889,7 @@ int loom_b200_decoder_select(loom_b200_decoder* dec, int seq) {
 static int dec_batch_ready(loom_b200_decoder* dec, int steps, const char* who) {
     loom_b200_ctx* ctx = dec->ctx;
     if (int rc = dec_check_ready(dec)) return rc;
-    LB_REQUIRE(ctx, dec->fused_tail, "%s: sequences in parallel need the streaming LM head (one GPU, hidden size it has room for)", who);
+    LB_REQUIRE(ctx, dec->fused_tail, "%s: sequences in parallel need the streaming LM head (a hidden size it has room for; under a tensor-parallel group the peer-memory exchange)", who);
     dec->kv_offsets[dec->lane] = dec->kv_offset;
     for (int i = 0; i < dec->batch; ++i) {
         LB_REQUIRE(ctx, dec->kv_offsets[i] > 0, "%s: sequence %d has no prompt behind it (select it and run decoder_forward first)", who, i);
@@ -881,6 +917,8 @@ int loom_b200_decoder_step_batch(loom_b200_decoder* dec, const int32_t* tokens, 
     for (int i = 0; i < B; ++i) dec->kv_offsets[i] += 1;
     dec->kv_offset = dec->kv_offsets[dec->lane];
     if (logits_host) {
+        for (int i = 0; i < B; ++i)
+            if (int rc = dec_gather_logits(dec, dec->logits_all + (size_t)i * dec->d.vocab)) return rc;
         LB_CUDA(ctx, cudaMemcpyAsync(logits_host, dec->logits_all, (size_t)B * dec->d.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
         if (int rc = lb_sync_checked(ctx)) return rc;
     }

@@ -2,6 +2,7 @@
 // activation staging with the fused normalise/quantize prologues, the per-tile integer MMA step and the epilogues.
 #pragma once
 #include "gemv_ternary.cuh"
+#include "tp_xchg.cuh"
 
 #include <type_traits>
 
@@ -45,6 +46,7 @@ struct Smem {
     void* stage;      // K floats (doubles for fp64 input) of prologue staging, or null
     float* gain;      // norm_w copied before the dependency wait, or null
     int pos0;         // *pos_ptr, read once after the dependency wait (KV ring rows)
+    uint32_t xseq_a, xseq_c;  // tensor-parallel exchange: sequence numbers of this launch (statistics, accumulators)
 };
 
 __device__ __forceinline__ const uint32_t* tile_ptr(const LbGemvParams& p, int v, int kb) {
@@ -229,6 +231,38 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
     __syncthreads();  // the staging buffer is reused by the next token
 }
 
+// Tensor-parallel statistics of token n: every rank's partial value (a float64 as two words, or a float32) goes to every
+// rank's mailbox, and the partials come back in rank order.  Called by all threads of the CTA; every CTA of the launch
+// does the same with the same slots.  Returns false when a peer did not answer within the poll limit.
+// parts: the upper half of the reduction scratch (sm.red holds 32 doubles, the block reductions use the first eight):
+// [0, 2 * ranks) the gathered words, [16] the "every peer answered" flag.  No static shared memory: the kernel's dynamic
+// allocation goes up to the per-CTA limit.
+__device__ __forceinline__ uint32_t* xchg_parts(const Smem& sm) { return reinterpret_cast<uint32_t*>(sm.red) + 32; }
+
+__device__ __forceinline__ bool xchg_gather(const LbGemvParams& p, const Smem& sm, int n, bool f64, unsigned long long mine) {
+    uint32_t* parts = xchg_parts(sm);
+    const int tid = threadIdx.x, W = p.xchg_world;
+    const uint32_t seq = sm.xseq_a;
+    const size_t half = (size_t)(seq & 1);
+    const int words = f64 ? 2 : 1;
+    if (tid == 0) parts[16] = 1u;
+    __syncthreads();
+    if (tid < W * words) {
+        const int peer = tid / words, hw = tid - peer * words;
+        char* dst = f64 ? (char*)p.xchg_peers[peer] + kXRegionA + ((((half * kXMaxRanks + p.xchg_rank) * 8 + n) * 2 + hw) * 8)
+                        : (char*)p.xchg_peers[peer] + kXRegionB + (((half * kXMaxRanks + p.xchg_rank) * 8 + n) * 8);
+        ll_store(dst, (uint32_t)(mine >> (32 * hw)), seq);
+    }
+    if (tid < W * words) {
+        const int r = tid / words, hw = tid - r * words;
+        const char* src = f64 ? (const char*)p.xchg_peers[p.xchg_rank] + kXRegionA + ((((half * kXMaxRanks + r) * 8 + n) * 2 + hw) * 8)
+                              : (const char*)p.xchg_peers[p.xchg_rank] + kXRegionB + (((half * kXMaxRanks + r) * 8 + n) * 8);
+        if (!ll_wait(src, seq, &parts[tid])) parts[16] = 0u;
+    }
+    __syncthreads();
+    return parts[16] != 0u;
+}
+
 // Quantizes the M activation rows into shared memory in the k-slot order the MMA B-fragments use, and
 // leaves sum(q) and amax per token in shared memory.
 template <int PRO, int NW = kWarps>
@@ -248,7 +282,7 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
         if (!q8) {
             const bool aligned16 = (((uintptr_t)row) & 15) == 0 && (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) &&
                                    (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) && (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0);
-            if ((K & 3) == 0 && sm.stage && aligned16) {
+            if ((K & 3) == 0 && sm.stage && aligned16 && !p.xchg_peers) {
                 stage_row_fast<PRO == LB_PRO_Q8 ? LB_PRO_F32 : PRO, NW>(p, sm, n, row);
                 continue;
             }
@@ -273,6 +307,14 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
                 }
                 ss = block_sum<NW>(ss, sm.red);
                 if (p.given_ss) ss = p.given_ss[n];
+                if (p.xchg_peers) {  // the sum over the whole vector: partials of all ranks, added in rank order on every rank
+                    const uint32_t* s_parts = xchg_parts(sm);
+                    if (!xchg_gather(p, sm, n, true, (unsigned long long)__double_as_longlong(ss)) && tid == 0) atomicExch(p.status, 5);
+                    ss = 0.0;
+                    for (int r = 0; r < p.xchg_world; ++r)
+                        ss = __dadd_rn(ss, __longlong_as_double((long long)(((unsigned long long)s_parts[2 * r + 1] << 32) | s_parts[2 * r])));
+                    __syncthreads();
+                }
                 double mean = __dadd_rn(__ddiv_rn(ss, (double)(p.norm_count > 0 ? p.norm_count : K)), p.eps);
                 stat = PRO == LB_PRO_BLOCKNORM ? sqrt(mean) : __ddiv_rn(1.0, sqrt(mean));
                 if (PRO == LB_PRO_BLOCKNORM) rstat = __ddiv_rn(1.0, stat);
@@ -282,6 +324,13 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
                 m = fmaxf(m, (float)fabs(pro_value<PRO>(row, c, stat, rstat, p.norm_w, p.norm_w_len)));
             m = block_max<NW>(m, sm.red);
             if (p.given_amax) m = p.given_amax[n];
+            if (p.xchg_peers) {
+                const uint32_t* s_partm = xchg_parts(sm);
+                if (!xchg_gather(p, sm, n, false, (unsigned long long)__float_as_uint(m)) && tid == 0) atomicExch(p.status, 5);
+                m = 0.0f;
+                for (int r = 0; r < p.xchg_world; ++r) m = fmaxf(m, __uint_as_float(s_partm[r]));
+                __syncthreads();
+            }
             amax = m < 1e-5f ? 1e-5f : m;
         }
         const double s = __ddiv_rn(127.0, (double)amax);
@@ -397,7 +446,7 @@ __device__ __forceinline__ void finish_row(const LbGemvParams& p, const Smem& sm
         else ((float*)sg.out)[o] = (float)y;
         return;
     }
-    if (EPI == LB_EPI_RESID) {
+    if (EPI == LB_EPI_RESID || EPI == LB_EPI_TPSUM) {
         const size_t o = (size_t)n * sg.rows + r;
         float f = (float)y;
         if (p.residual) f = __fadd_rn(f, p.residual[o]);

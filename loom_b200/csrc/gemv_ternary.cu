@@ -148,6 +148,10 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     lb_pdl_wait();               // everything below may read what earlier launches wrote
     LB_TRACE(2);
     if (p.pos_ptr) sm.pos0 = *p.pos_ptr;
+    if (p.xchg_peers) {  // sequence numbers of this launch's exchanges (moved on by the last CTA of the previous one)
+        sm.xseq_a = p.xchg_ctr[0];
+        sm.xseq_c = p.xchg_ctr[2];
+    }
     if (EPI == LB_EPI_RESID && M == 1 && cta_tiles > 0) {
         // the epilogue's operands of this CTA's rows: requested now, so that they are in L1 when the sums are done
         const int row0 = (t0 / KB) * kTileRows, nrows = ((t1 - 1) / KB + 1) * kTileRows - row0;
@@ -291,6 +295,59 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     if (cta_tiles <= 0) return;
     const int group_tiles = p.group * KB;
     const int per_group = p.group * M * 16;
+    if (EPI == LB_EPI_TPSUM) {
+        // Row-parallel shard (always the aligned partition): this rank's corrected partial sums go to every other rank's
+        // mailbox, then every output adds up what the ranks sent, in rank order (integer: exact), and finishes like
+        // float(y + bias) + residual.  All stores first, then the polls, so that the NVLink latencies overlap.
+        const int ngl_a = p.part_q + ((int)blockIdx.x < p.part_r ? 1 : 0);
+        const LbGemvSeg& sg = p.seg[0];
+        const uint32_t seq = sm.xseq_c;
+        const size_t half = (size_t)(seq & 1);
+        const int W = p.xchg_world, me = p.xchg_rank;
+        for (int idx = tid; idx < ngl_a * per_group; idx += kThreads) {
+            const int gl = idx / per_group, i = idx - gl * per_group;
+            const int n = i >> 4, r = (first_group + gl) * kTileRows + (i & 15);
+            if (r >= sg.rows) continue;
+            const int mine = sm.sacc[idx] - sm.xsum[n];
+            const size_t o = (size_t)n * sg.rows + r;
+            for (int q = 0; q < W; ++q)
+                if (q != me) ll_store((char*)p.xchg_peers[q] + kXRegionC + ((half * kXMaxRanks + me) * kXMaxAcc + o) * 8, (uint32_t)mine, seq);
+        }
+        bool ok = true;
+        for (int idx = tid; idx < ngl_a * per_group; idx += kThreads) {
+            const int gl = idx / per_group, i = idx - gl * per_group;
+            const int n = i >> 4, r = (first_group + gl) * kTileRows + (i & 15);
+            if (r >= sg.rows) continue;
+            const size_t o = (size_t)n * sg.rows + r;
+            int sum = 0;
+            for (int q = 0; q < W; ++q) {
+                uint32_t d = (uint32_t)(sm.sacc[idx] - sm.xsum[n]);
+                if (q != me) ok = ll_wait((const char*)p.xchg_peers[me] + kXRegionC + ((half * kXMaxRanks + q) * kXMaxAcc + o) * 8, seq, &d) && ok;
+                sum += (int)d;
+            }
+            double y = __dmul_rn((double)sum, sm.os[n]);
+            if (sg.bias) y = __dadd_rn(y, (double)sg.bias[r]);
+            float f = (float)y;
+            if (p.residual) f = __fadd_rn(f, p.residual[o]);
+            ((float*)sg.out)[o] = f;
+        }
+        if (!ok) atomicExch(p.status, 5);
+        // the last CTA to get here moves the sequence numbers on (a CTA that starts late has read the old ones by now:
+        // it cannot start before the launch's dependency is resolved, and it reads them right after)
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            const unsigned int t = atomicAdd(&p.xchg_ctr[4], 1u);
+            if (t == gridDim.x - 1) {
+                p.xchg_ctr[4] = 0;
+                __threadfence();
+                if (PRO != LB_PRO_Q8) p.xchg_ctr[0] = sm.xseq_a + 1;
+                p.xchg_ctr[2] = seq + 1;
+            }
+        }
+        LB_TRACE(5);
+        return;
+    }
     if (p.aligned) {  // every group is this CTA's own: no fix-up, no flags
         const int ngl_a = p.part_q + ((int)blockIdx.x < p.part_r ? 1 : 0);
         for (int idx = tid; idx < ngl_a * per_group; idx += kThreads) {
@@ -420,6 +477,7 @@ static void gemv_plan(const loom_b200_ctx* ctx, LbGemvParams& p, int cps, int* g
     int grid = ctx->sm_count * cps;
     // Enough strip groups to occupy the SMs: give every CTA whole groups and skip the cross-CTA fix-up.
     p.aligned = ctx->opt_gemv_partition == 1 ? 0 : (ctx->opt_gemv_partition == 2 ? 1 : (ngroups * 2 >= ctx->sm_count ? 1 : 0));
+    if (p.epi == LB_EPI_TPSUM) p.aligned = 1;  // the exchange epilogue finishes whole rows inside one CTA
     if (p.aligned) {
         if (grid > ngroups) grid = ngroups;
         int gpc = (ngroups + grid - 1) / grid;
@@ -489,7 +547,7 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     // Wide inputs, or three and more tokens: normalise and quantize once in a launch of its own (one CTA per token), then
     // stream the weights against the int8 rows.  The fused prologue is repeated by every CTA and costs it 4-6 us per token:
     // right for one or two tokens on the critical path of a decode step, wrong for a pass of eight.
-    if (p.pro != LB_PRO_Q8 && (p.K >= kSplitQuantK || p.M >= kSplitQuantTokens) && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
+    if (p.pro != LB_PRO_Q8 && !p.xchg_peers && (p.K >= kSplitQuantK || p.M >= kSplitQuantTokens) && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
         (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) && (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) &&
         (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0)) {
         const size_t qbytes = ((size_t)p.M * p.K + 255) & ~(size_t)255;
@@ -553,6 +611,9 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     LB_PICK(12, true, LB_PRO_Q8, LB_EPI_QKV)
     LB_PICK(13, true, LB_PRO_Q8, LB_EPI_RESID)
     LB_PICK(14, true, LB_PRO_BLOCKNORM, LB_EPI_GENERIC)
+    LB_PICK(15, true, LB_PRO_INNERNORM64, LB_EPI_TPSUM)
+    LB_PICK(16, true, LB_PRO_INNERNORM, LB_EPI_TPSUM)
+    LB_PICK(17, true, LB_PRO_Q8, LB_EPI_TPSUM)
 #undef LB_PICK
     if (!kern) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: no kernel for prologue %d with epilogue %d", p.pro, p.epi);
     const unsigned attr_bit = 1u << kid;

@@ -25,6 +25,7 @@ enum LbEpi : int {
     LB_EPI_QKV = 1,      // segment 0 -> fp64 (query), segments 1,2 -> fp32 rows of the KV ring (poly/mha.go:274-283)
     LB_EPI_RESID = 2,    // float(y + bias) + residual (O and down projections; poly/mha.go:365, poly/swiglu.go:317)
     LB_EPI_SWIGLU = 3,   // gate/up pair -> float(gateProduct) (poly/swiglu.go:306-310)
+    LB_EPI_TPSUM = 4,    // row-parallel shard: the partial sums of every rank meet through the peer mailboxes, then float(y + bias) + residual
 };
 
 struct LbGemvSeg {
@@ -75,6 +76,13 @@ struct LbGemvParams {
     const double* given_ss;   // optional [M]: sum of squares over the full vector (tensor-parallel row shards)
     const float* given_amax;  // optional [M]: absmax of the normalised full vector
     int norm_count;           // elements the mean runs over (0 = K)
+    // Tensor-parallel row shard (x is this rank's slice of the input): with xchg_peers set, the prologue exchanges the
+    // partial sum of squares and the partial absmax of the normalised slice with the other ranks (every CTA sends and
+    // polls the same mailbox slots: the stores are idempotent), and LB_EPI_TPSUM exchanges the partial accumulators.
+    // xchg_ctr: {statistics sequence, accumulator sequence, arrivals}; the last CTA to finish moves both sequences on.
+    void* const* xchg_peers;
+    int xchg_rank, xchg_world;
+    unsigned int* xchg_ctr;
     int8_t* q_out;     // optional side outputs, written by CTA 0
     float* amax_out;
     float* norm_out;   // normalised row as float32 (what the layers report as preAct)

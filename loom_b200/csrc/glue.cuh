@@ -85,6 +85,12 @@ struct LbLmHeadParams {
     const float* emb;      // [emb_vocab, hidden] embedding table of the next token (the head itself when tied)
     int emb_vocab;
     float* x_next;
+    // Vocabulary-sharded head under a tensor-parallel group with peer mailboxes: `head` is this rank's slice (rows
+    // vocab_offset ...), and the tail exchanges every rank's (maximum, index) pair instead of gathering the logits: the
+    // first maximum over the slices in rank order is the first maximum of the whole row.  xchg_ctr[5] is the sequence number.
+    void* const* xchg_peers;
+    int xchg_rank, xchg_world, vocab_offset;
+    unsigned int* xchg_ctr;
     // scratch of the tail, set by the launcher: per-CTA (value, index) and the arrival counter (zero between launches)
     float* part_val;
     int* part_idx;

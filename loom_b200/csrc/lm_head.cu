@@ -9,6 +9,7 @@
 // The CTA that finishes last reduces the per-CTA maxima to the next token, appends it to the output ring, advances the
 // position and gathers the token's embedding row for the next step: no argmax, position or embedding launch.
 #include "glue.cuh"
+#include "tp_xchg.cuh"
 
 namespace {
 
@@ -182,6 +183,33 @@ __global__ void __launch_bounds__(NW * 32, 1) lb_lm_head_stream_kernel(const LbL
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             argmax_merge(bv, bi, ov, oi);
         }
+        if (lane == 0 && p.xchg_peers) {
+            // every rank's (maximum, index) of row b to every other rank, then the merge in rank order
+            const uint32_t seq = p.xchg_ctr[5];
+            const size_t half = (size_t)(seq & 1);
+            const int W = p.xchg_world, me = p.xchg_rank;
+            const float mv = bv;
+            const int mi = bi == 0x7fffffff ? bi : bi + p.vocab_offset;
+            for (int q = 0; q < W; ++q) {
+                if (q == me) continue;
+                char* dst = (char*)p.xchg_peers[q] + kXRegionD + (((half * kXMaxRanks + me) * 8 + b) * 2) * 8;
+                ll_store(dst, __float_as_uint(mv), seq);
+                ll_store(dst + 8, (uint32_t)mi, seq);
+            }
+            bv = -INFINITY;
+            bi = 0x7fffffff;
+            bool ok = true;
+            for (int q = 0; q < W; ++q) {
+                uint32_t dv = __float_as_uint(mv), di = (uint32_t)mi;
+                if (q != me) {
+                    const char* src = (const char*)p.xchg_peers[me] + kXRegionD + (((half * kXMaxRanks + q) * 8 + b) * 2) * 8;
+                    ok = ll_wait(src, seq, &dv) && ok;
+                    ok = ll_wait(src + 8, seq, &di) && ok;
+                }
+                argmax_merge(bv, bi, __uint_as_float(dv), (int)di);
+            }
+            if (!ok) atomicExch(p.status, 5);
+        }
         if (lane == 0) {
             if (bi == 0x7fffffff) bi = 0;  // only NaNs: the reference keeps index 0
             if (b == 0) s_tok = bi;
@@ -195,7 +223,10 @@ __global__ void __launch_bounds__(NW * 32, 1) lb_lm_head_stream_kernel(const LbL
         }
     }
     __syncthreads();
-    if (tid == 0) *p.cnt = 0;
+    if (tid == 0) {
+        *p.cnt = 0;
+        if (p.xchg_peers) p.xchg_ctr[5] += 1;  // every warp of this CTA has read the old value (barrier above)
+    }
     if (p.x_next && p.emb) {  // the embedding row of the new token, for the step that follows (poly/transformer.go:551-577)
         const int t = s_tok;
         const bool ok = t >= 0 && t < p.emb_vocab;

@@ -10,6 +10,7 @@
 // and only then applies the float64 rescale, bias and residual -- identically on every rank.
 // NCCL is loaded at run time (dlopen of libnccl.so.2): single-GPU users need no NCCL at all.
 #include "layers.cuh"
+#include "tp_xchg.cuh"
 
 #include <dlfcn.h>
 
@@ -119,37 +120,7 @@ __global__ void lb_tp_finalize_kernel(const int32_t* __restrict__ acc, int M, in
     out[i] = f;
 }
 
-// ---- exchange through peer memory ---------------------------------------------------------------------------
-// Every rank owns a mailbox in its own HBM and maps every other rank's mailbox (CUDA IPC).  A value travels as an
-// 8-byte {data, sequence} pair written with one store straight into the receiver's mailbox over NVLink; the receiver
-// polls its own memory until the sequence number of the current exchange shows up (the scheme NCCL calls LL).  No
-// kernel ever loads from a peer: only plain stores cross NVLink.  Two alternating halves per region let a rank run
-// one exchange ahead of a slow peer without overwriting what that peer has not read yet; it cannot run two ahead
-// because finishing an exchange needs every peer's contribution to it.  Every poll is bounded: on expiry the kernel
-// raises the context status word (5) and carries on with whatever it has, so a missing peer never hangs the GPU.
-constexpr int kXMaxRanks = 8;
-constexpr int kXMaxAcc = 8 * 8192;  // int32 accumulators one exchange can carry (tokens x rows)
-constexpr size_t kXRegionA = 0;                                                     // [2][ranks][8 tokens][lo, hi] sum of squares
-constexpr size_t kXRegionB = kXRegionA + 2 * kXMaxRanks * 8 * 2 * 8;                // [2][ranks][8 tokens] absmax
-constexpr size_t kXRegionC = kXRegionB + 2 * kXMaxRanks * 8 * 8;                    // [2][ranks][kXMaxAcc] accumulators
-constexpr size_t kXBytes = kXRegionC + 2 * (size_t)kXMaxRanks * kXMaxAcc * 8;
-constexpr unsigned int kXSpin = 40000000u;  // polls before giving up (of the order of a second)
-
-__device__ __forceinline__ void ll_store(void* p, uint32_t data, uint32_t seq) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(seq) : "memory");
-}
-__device__ __forceinline__ bool ll_wait(const void* p, uint32_t seq, uint32_t* data) {
-    for (unsigned int i = 0; i < kXSpin; ++i) {
-        uint32_t d, f;
-        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(d), "=r"(f) : "l"(p) : "memory");
-        if (f == seq) {
-            *data = d;
-            return true;
-        }
-    }
-    *data = 0;
-    return false;
-}
+// ---- exchange through peer memory (layout and store / poll pair: tp_xchg.cuh) -----------------------------------
 // the kernel's last block moves the exchange counter on: a block that starts late still reads the old value
 __device__ __forceinline__ void x_finish(unsigned int* ctr, unsigned int* done, uint32_t seq) {
     __syncthreads();
@@ -335,8 +306,13 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
     double* ss = stats;
     float* amax = reinterpret_cast<float*>(stats + M);
     const bool peer = ctx->tp_peer && ctx->opt_tp_peer && ctx->tp_world > 1 && (size_t)M * w->rows <= (size_t)kXMaxAcc && M <= 8;
+    // One launch: the GEMV exchanges the statistics in its prologue and the partial sums in its epilogue (one token), or
+    // takes the statistics kernel's int8 slice and exchanges only the sums (several tokens: one CTA per token is the
+    // better place for their statistics).  Option "tp_fused": 0 keeps the three-launch form, 1 fuses only the exchange of the sums, 2 both.
+    const bool fused = peer && ctx->opt_tp_fused && (Kl & 3) == 0 && out != nullptr;
+    const bool fused_pro = fused && ctx->opt_tp_fused >= 2 && M == 1 && Kl < kSplitQuantK;
     int8_t* q8 = nullptr;
-    if (peer) {
+    if (peer && !fused_pro) {
         LB_REQUIRE(ctx, (Kl & 3) == 0, "tensor-parallel shard width %d must be a multiple of 4", Kl);
         if (int rc = lb_ensure_quant_scratch(ctx, (size_t)kChunkTokens * Kl + 256)) return rc;
         q8 = reinterpret_cast<int8_t*>(ctx->quant_scratch);
@@ -372,7 +348,14 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
     p.seg[0].kind = LB_OUT_ACC;
     p.K = Kl;
     p.M = M;
-    if (peer) {  // the statistics kernel already quantized the slice
+    if (fused_pro) {
+        p.pro = x_is_f64 ? LB_PRO_INNERNORM64 : LB_PRO_INNERNORM;
+        p.x = x;
+        p.norm_w = inner_w;
+        p.norm_w_len = inner_w ? inner_w_len : 0;
+        p.eps = eps;
+        p.norm_count = K_global;
+    } else if (peer) {  // the statistics kernel already quantized the slice
         p.pro = LB_PRO_Q8;
         p.x = q8;
         p.amax_in = amax;
@@ -388,10 +371,23 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
     }
     p.epi = LB_EPI_GENERIC;
     p.act = LOOM_B200_ACT_LINEAR;
+    if (fused) {
+        p.epi = LB_EPI_TPSUM;
+        p.seg[0].acc_out = nullptr;
+        p.seg[0].kind = LB_OUT_F32;
+        p.seg[0].out = out;
+        p.seg[0].bias = bias;
+        p.residual = residual;
+        p.xchg_peers = (void* const*)ctx->peer_xbuf_dev;
+        p.xchg_rank = ctx->tp_rank;
+        p.xchg_world = ctx->tp_world;
+        p.xchg_ctr = ctx->x_ctr;
+    }
     LB_REQUIRE(ctx, (Kl & 3) == 0, "tensor-parallel shard width %d must be a multiple of 4", Kl);
     if (int rc = lb_gemv_finalize_params(ctx, p)) return rc;
     if (int rc = lb_launch_gemv(ctx, p)) return rc;
     const size_t n = (size_t)M * w->rows;
+    if (fused) return 0;
     if (peer) {
         lb_tp_finalize_peer_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(acc, M, w->rows, w->scale, amax, bias, residual, out,
                                                                                           (void* const*)ctx->peer_xbuf_dev, ctx->tp_rank,
@@ -450,8 +446,10 @@ int loom_b200_tp_peer_handle(loom_b200_ctx* ctx, uint8_t* handle64) {
     if (!ctx->xbuf) {
         LB_CUDA(ctx, cudaMalloc(&ctx->xbuf, kXBytes));
         LB_CUDA(ctx, cudaMemset(ctx->xbuf, 0, kXBytes));
-        LB_CUDA(ctx, cudaMalloc(&ctx->x_ctr, 4 * sizeof(unsigned int)));
-        const unsigned int init[4] = {1u, 0u, 1u, 0u};  // sequence numbers start at 1: a zeroed mailbox never matches
+        LB_CUDA(ctx, cudaMalloc(&ctx->x_ctr, 8 * sizeof(unsigned int)));
+        // {statistics sequence, arrivals, accumulator sequence, arrivals, arrivals of the GEMV that carries both exchanges};
+        // sequence numbers start at 1: a zeroed mailbox never matches
+        const unsigned int init[8] = {1u, 0u, 1u, 0u, 0u, 1u, 0u, 0u};  // [5]: sequence of the sharded head's (max, index) exchange
         LB_CUDA(ctx, cudaMemcpy(ctx->x_ctr, init, sizeof(init), cudaMemcpyHostToDevice));
     }
     cudaIpcMemHandle_t h;

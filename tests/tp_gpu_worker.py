@@ -34,7 +34,11 @@ def run_checks(mode: str, local: int, group=None):
     assert ctx.tp_rank == rank and ctx.tp_world == world
     if mode == "nograph":
         ctx.set_option("tp_graph", 0)
-    if mode == "peer":  # exchange through peer mailboxes instead of NCCL: gather every rank's IPC handle
+    if mode == "peer3":  # the three-launch form of a row-parallel projection (statistics kernel, GEMV, finalize kernel)
+        ctx.set_option("tp_fused", 0)
+    if mode == "peer2":  # the GEMV also exchanges the statistics itself (one launch; measured slower, kept as an option)
+        ctx.set_option("tp_fused", 2)
+    if mode in ("peer", "peer2", "peer3"):  # exchange through peer mailboxes instead of NCCL: gather every rank's IPC handle
         mine = torch.frombuffer(bytearray(ctx.tp_peer_handle()), dtype=torch.uint8).clone()
         allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
         dist.all_gather(allh, mine, group=group)
@@ -54,28 +58,30 @@ def run_checks(mode: str, local: int, group=None):
 
     # ---- a row-sharded linear with inner-norm weights, bias and residual ----
     rng = np.random.default_rng(77)
-    rows, K, batch = 96, 256 * world, 3
-    master = (rng.standard_normal(rows * K) * 0.05).astype(np.float32)
-    words, scale = orc.pack_f32(master, rows, K)
-    inner = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
-    bias = (0.01 * rng.standard_normal(rows)).astype(np.float32)
-    resid = rng.standard_normal((batch, rows)).astype(np.float32)
-    x = rng.standard_normal((batch, K)).astype(np.float32)
-    c0, c1 = rank * K // world, (rank + 1) * K // world
-    w_l = ctx.upload_ternary(slice_cols(words, rows, K, c0, c1), rows, c1 - c0, scale)
-    d_x = ctx.to_device(np.ascontiguousarray(x[:, c0:c1]))
-    d_in, d_b, d_r = ctx.to_device(np.ascontiguousarray(inner[c0:c1])), ctx.to_device(bias), ctx.to_device(resid)
-    d_out = ctx.alloc(batch * rows * 4)
-    ctx.tp_rowsharded_linear(w_l, batch, d_x, K, d_out, inner_w=d_in, inner_w_len=c1 - c0, eps=1e-5, bias=d_b, residual=d_r)
-    got = ctx.download(d_out, (batch, rows), np.float32)
-    for t in range(batch):
-        y = orc.inner_rmsnorm_f32(x[t], inner, 1e-5)
-        xq, amax = orc.quantize_f32(y)
-        acc = orc.matvec_i32(words, rows, K, xq).astype(np.float64)
-        os_ = float(np.float64(scale) * np.float64(amax) / 127.0)
-        want = (acc * os_ + bias.astype(np.float64)).astype(np.float32) + resid[t]
-        if not np.array_equal(got[t], want):
-            failures.append("row-sharded linear token %d differs in %d of %d" % (t, int((got[t] != want).sum()), rows))
+    # (three tokens: the statistics come from the one-CTA-per-token kernel; one token: the GEMV exchanges them itself)
+    for rows, K, batch in ((96, 256 * world, 3), (200, 512 * world, 1), (96, 256 * world, 8)):
+        master = (rng.standard_normal(rows * K) * 0.05).astype(np.float32)
+        words, scale = orc.pack_f32(master, rows, K)
+        inner = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+        bias = (0.01 * rng.standard_normal(rows)).astype(np.float32)
+        resid = rng.standard_normal((batch, rows)).astype(np.float32)
+        x = rng.standard_normal((batch, K)).astype(np.float32)
+        c0, c1 = rank * K // world, (rank + 1) * K // world
+        w_l = ctx.upload_ternary(slice_cols(words, rows, K, c0, c1), rows, c1 - c0, scale)
+        d_x = ctx.to_device(np.ascontiguousarray(x[:, c0:c1]))
+        d_in, d_b, d_r = ctx.to_device(np.ascontiguousarray(inner[c0:c1])), ctx.to_device(bias), ctx.to_device(resid)
+        d_out = ctx.alloc(batch * rows * 4)
+        for rep in range(3):  # repeated: the mailbox halves and sequence numbers must keep working
+            ctx.tp_rowsharded_linear(w_l, batch, d_x, K, d_out, inner_w=d_in, inner_w_len=c1 - c0, eps=1e-5, bias=d_b, residual=d_r)
+        got = ctx.download(d_out, (batch, rows), np.float32)
+        for t in range(batch):
+            y = orc.inner_rmsnorm_f32(x[t], inner, 1e-5)
+            xq, amax = orc.quantize_f32(y)
+            acc = orc.matvec_i32(words, rows, K, xq).astype(np.float64)
+            os_ = float(np.float64(scale) * np.float64(amax) / 127.0)
+            want = (acc * os_ + bias.astype(np.float64)).astype(np.float32) + resid[t]
+            if not np.array_equal(got[t], want):
+                failures.append("row-sharded linear %dx%d batch %d token %d differs in %d of %d" % (rows, K, batch, t, int((got[t] != want).sum()), rows))
 
     # ---- the decoder: logits and greedy tokens of the unsharded oracle ----
     L, H, heads, kvh, hd, I, V, msl = 2, 512, 8, 8, 64, 1024, 512, 96  # 8 heads / 8 KV heads: any group of up to 8 ranks divides them
@@ -84,6 +90,7 @@ def run_checks(mode: str, local: int, group=None):
     odec = orc.Decoder(L, H, heads, kvh, hd, I, V, eps, theta, act, msl)
     gdec = cabi.Decoder(ctx, L, H, heads, kvh, hd, I, V, eps, theta, act, msl)
     shapes = ((heads * hd, H), (kvh * hd, H), (kvh * hd, H), (H, heads * hd), (I, H), (I, H), (H, I))
+    blocks = []
     for b in range(L):
         masters = [(rng.standard_normal(r * c) * 0.02).astype(np.float32) for r, c in shapes]
         g1 = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
@@ -93,10 +100,12 @@ def run_checks(mode: str, local: int, group=None):
         slices, _, _ = plan.shard_block([p[0] for p in packed])
         ws = [ctx.upload_ternary(sw, sr, sc, packed[i][1]) for i, (sw, sr, sc) in enumerate(slices)]
         gdec.set_block(b, ws, g1=g1, g2=g2)
+        blocks.append((masters, ws, g1, g2))
     emb = (rng.standard_normal((V, H)) * 0.02).astype(np.float32)
     fg = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    emb_dev = ctx.to_device(emb)
     odec.set_embeddings(emb, fg)
-    gdec.set_embeddings(ctx.to_device(emb), fg)
+    gdec.set_embeddings(emb_dev, fg)
     prompt = rng.integers(0, V, 13).astype(np.int32)
     elog = odec.forward(prompt)
     glog = gdec.forward(prompt)
@@ -120,6 +129,47 @@ def run_checks(mode: str, local: int, group=None):
         failures.append("ranks disagree on the logits")
     ctx.sync()
     gdec.close()
+
+    # ---- independent sequences on the sharded decoder (peer exchange only: the sharded head's tail exchanges the
+    #      (maximum, index) pairs of the vocabulary slices): every sequence against an oracle decoder of its own ----
+    if mode in ("peer", "peer3"):
+        B = 3
+        bdec = cabi.Decoder(ctx, L, H, heads, kvh, hd, I, V, eps, theta, act, msl)
+        bdec.set_batch(B)
+        odecs = [orc.Decoder(L, H, heads, kvh, hd, I, V, eps, theta, act, msl) for _ in range(B)]
+        for b, (masters, ws, g1, g2) in enumerate(blocks):
+            bdec.set_block(b, ws, g1=g1, g2=g2)
+            for od in odecs:
+                od.set_block(b, *masters, g1=g1, g2=g2)
+        bdec.set_embeddings(emb_dev, fg)
+        elogs = []
+        for i, od in enumerate(odecs):
+            od.set_embeddings(emb, fg)
+            pr = rng.integers(0, V, 5 + 4 * i).astype(np.int32)
+            bdec.select(i)
+            gl = bdec.forward(pr)
+            el = od.forward(pr)
+            if not np.max(np.abs(gl - el)) <= tol:
+                failures.append("batch: prompt logits of sequence %d differ by %g" % (i, float(np.max(np.abs(gl - el)))))
+            elogs.append(el)
+        toks = rng.integers(0, V, B).astype(np.int32)
+        glogs = bdec.step_batch(toks)
+        for i, od in enumerate(odecs):
+            elogs[i] = od.forward(toks[i:i + 1])
+            if not np.max(np.abs(glogs[i] - elogs[i])) <= tol:
+                failures.append("batch: step logits of sequence %d differ by %g" % (i, float(np.max(np.abs(glogs[i] - elogs[i])))))
+        bdec.continue_batch(5)
+        got = bdec.generated_tokens_batch(5)
+        for i, od in enumerate(odecs):
+            want, lg = [], elogs[i]
+            for _ in range(5):
+                t = orc.argmax(lg)
+                want.append(t)
+                lg = od.forward(np.array([t], np.int32))
+            if got[i].tolist() != want:
+                failures.append("batch: greedy tokens of sequence %d: %s vs %s" % (i, got[i].tolist(), want))
+        ctx.sync()
+        bdec.close()
     dist.barrier(group=group)  # nobody leaves while a peer may still be inside a collective
     ctx.tp_finalize()
     ctx.close()
