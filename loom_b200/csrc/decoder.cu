@@ -51,6 +51,8 @@ struct loom_b200_decoder {
     float *pf_x = nullptr, *pf_prod = nullptr;
     double *pf_q = nullptr, *pf_attn = nullptr;
     int32_t *pf_accg = nullptr, *pf_accu = nullptr;
+    double* pf_ss = nullptr;  // tensor-parallel prompts: agreed per-token statistics
+    float* pf_amax = nullptr;
     const float* last_resid = nullptr;  // residual stream of the last pass (x or pf_x) and its rows
     int last_resid_rows = 0;
     int step_launches = 0;              // kernels of one recorded decode step (without the argmax)
@@ -74,13 +76,15 @@ namespace {
 constexpr int kPrefillBlock = 1024;  // prompt tokens per pass of the tensor-core path
 
 void dec_free_prefill(loom_b200_decoder* dec) {
-    void* ptrs[] = {dec->pf_tok, dec->pf_x, dec->pf_prod, dec->pf_q, dec->pf_attn, dec->pf_accg, dec->pf_accu};
+    void* ptrs[] = {dec->pf_tok, dec->pf_x, dec->pf_prod, dec->pf_q, dec->pf_attn, dec->pf_accg, dec->pf_accu, dec->pf_ss, dec->pf_amax};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     dec->pf_tok = nullptr;
     dec->pf_x = dec->pf_prod = nullptr;
     dec->pf_q = dec->pf_attn = nullptr;
     dec->pf_accg = dec->pf_accu = nullptr;
+    dec->pf_ss = nullptr;
+    dec->pf_amax = nullptr;
     dec->pf_cap = 0;
 }
 
@@ -90,7 +94,7 @@ int dec_ensure_prefill(loom_b200_decoder* dec, int tokens) {
     LB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     dec_free_prefill(dec);
     const loom_b200_decoder_dims& d = dec->d;
-    const size_t T = (size_t)tokens, qd = (size_t)d.num_heads * d.head_dim;
+    const size_t T = (size_t)tokens, qd = (size_t)d.num_heads * d.head_dim;  // (under a tensor-parallel group the slices need less)
     LB_CUDA(ctx, cudaMalloc(&dec->pf_tok, T * sizeof(int)));
     LB_CUDA(ctx, cudaMalloc(&dec->pf_x, T * d.hidden * sizeof(float)));
     LB_CUDA(ctx, cudaMalloc(&dec->pf_prod, T * d.intermediate * sizeof(float)));
@@ -98,6 +102,11 @@ int dec_ensure_prefill(loom_b200_decoder* dec, int tokens) {
     LB_CUDA(ctx, cudaMalloc(&dec->pf_attn, T * qd * sizeof(double)));
     LB_CUDA(ctx, cudaMalloc(&dec->pf_accg, T * d.intermediate * sizeof(int32_t)));
     LB_CUDA(ctx, cudaMalloc(&dec->pf_accu, T * d.intermediate * sizeof(int32_t)));
+    if (dec->tp_world > 1) {  // agreed per-token statistics of the row-parallel projections; pf_accg doubles as their accumulator plane
+        LB_REQUIRE(ctx, d.intermediate >= d.hidden, "decoder: prompts under a tensor-parallel group need intermediate >= hidden");
+        LB_CUDA(ctx, cudaMalloc(&dec->pf_ss, T * sizeof(double)));
+        LB_CUDA(ctx, cudaMalloc(&dec->pf_amax, T * sizeof(float)));
+    }
     dec->pf_cap = tokens;
     return 0;
 }
@@ -204,8 +213,33 @@ int dec_gather_logits(loom_b200_decoder* dec, float* logits_row) {
 int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
     loom_b200_ctx* ctx = dec->ctx;
     const loom_b200_decoder_dims& d = dec->d;
-    const int H = d.hidden, I = d.intermediate;
+    const int H = d.hidden, I = dec->tp_world > 1 ? dec->inter_l : d.intermediate;
+    const bool tp = dec->tp_world > 1;
     const double block_eps = d.rms_eps > 0 ? d.rms_eps : 1e-6;
+    // Row-parallel projection of the block under a tensor-parallel group: statistics of the whole row agreed by two small
+    // all-reduces, this rank's slice quantized with them, the GEMM writing raw int32 sums, one all-reduce of those, then
+    // the float epilogue (same arithmetic as one GPU: integer sums are exact in any order).
+    auto row_parallel = [&](const loom_b200_weight* w, bool f64, const void* x, int K_global, const float* inner_w, int inner_len,
+                            double eps, const float* bias) -> int {
+        if (int rc = lb_tp_block_stats(ctx, f64, x, M, w->cols, K_global, eps, inner_w, inner_len, dec->pf_ss, dec->pf_amax)) return rc;
+        LbGemmQuant q = {};
+        q.pro = f64 ? LB_PRO_INNERNORM64 : LB_PRO_INNERNORM;
+        q.x = x;
+        q.K = w->cols;
+        q.tokens = M;
+        q.norm_w = inner_w;
+        q.norm_w_len = inner_w ? inner_len : 0;
+        q.eps = eps;
+        q.given_ss = dec->pf_ss;
+        q.given_amax = dec->pf_amax;
+        q.norm_count = K_global;
+        if (int rc = lb_gemm_quantize(ctx, q)) return rc;
+        LbGemmOut go = {};
+        go.act = LOOM_B200_ACT_LINEAR;
+        go.acc_out = dec->pf_accg;
+        if (int rc = lb_gemm_run(ctx, w, M, go)) return rc;
+        return lb_tp_block_finalize(ctx, dec->pf_accg, M, H, w->scale, dec->pf_amax, bias, dec->pf_x, dec->pf_x);
+    };
     if (int rc = lb_launch_embed(ctx, dec->emb, d.vocab, H, dec->pf_tok, M, dec->pf_x)) return rc;
     for (auto& b : dec->blocks) {
         loom_b200_mha& m = b.mha;
@@ -273,21 +307,25 @@ int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
             return rc;
         }
 
-        qa = LbGemmQuant{};
-        qa.pro = LB_PRO_INNERNORM64;
-        qa.x = dec->pf_attn;
-        qa.K = m.q_dim;
-        qa.tokens = M;
-        qa.norm_w = m.inner;
-        qa.norm_w_len = m.inner ? m.inner_len : 0;
-        qa.eps = m.rms_eps > 0 ? m.rms_eps : 1e-5;
-        if (int rc = lb_gemm_quantize(ctx, qa)) return rc;
-        o = LbGemmOut{};
-        o.act = LOOM_B200_ACT_LINEAR;
-        o.bias = m.bo;
-        o.out = dec->pf_x;
-        o.residual = dec->pf_x;
-        if (int rc = lb_gemm_run(ctx, m.wo, M, o)) return rc;
+        if (tp) {
+            if (int rc = row_parallel(m.wo, true, dec->pf_attn, m.q_dim_global, m.inner, m.inner_len, m.rms_eps > 0 ? m.rms_eps : 1e-5, m.bo)) return rc;
+        } else {
+            qa = LbGemmQuant{};
+            qa.pro = LB_PRO_INNERNORM64;
+            qa.x = dec->pf_attn;
+            qa.K = m.q_dim;
+            qa.tokens = M;
+            qa.norm_w = m.inner;
+            qa.norm_w_len = m.inner ? m.inner_len : 0;
+            qa.eps = m.rms_eps > 0 ? m.rms_eps : 1e-5;
+            if (int rc = lb_gemm_quantize(ctx, qa)) return rc;
+            o = LbGemmOut{};
+            o.act = LOOM_B200_ACT_LINEAR;
+            o.bias = m.bo;
+            o.out = dec->pf_x;
+            o.residual = dec->pf_x;
+            if (int rc = lb_gemm_run(ctx, m.wo, M, o)) return rc;
+        }
 
         qa = LbGemmQuant{};
         qa.pro = LB_PRO_BLOCKNORM;
@@ -315,6 +353,10 @@ int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
             return frc;
         }
 
+        if (tp) {
+            if (int rc = row_parallel(b.down, false, dec->pf_prod, d.intermediate, b.ffn_inner, b.ffn_inner_len, 1e-5, nullptr)) return rc;
+            continue;
+        }
         qa = LbGemmQuant{};
         qa.pro = LB_PRO_INNERNORM;
         qa.x = dec->pf_prod;
@@ -342,8 +384,11 @@ int dec_prefill_block(loom_b200_decoder* dec, int M, int pos0, bool head) {
         h.hidden = H;
         h.logits = dec->logits;
         h.hidden_out = dec->hidden;
+        if (dec->head_sharded) dec_shard_head(dec, h, dec->logits);
         if (dec->fused_tail) dec_fill_tail(dec, h, M);
         if (int rc = lb_launch_lm_head(ctx, h)) return rc;
+        if (dec->head_sharded && !dec->fused_tail)
+            if (int rc = lb_tp_allgather_f32(ctx, h.logits, dec->logits, (size_t)h.vocab)) return rc;
     }
     dec->last_resid = dec->pf_x;
     dec->last_resid_rows = M;
@@ -768,7 +813,7 @@ int loom_b200_decoder_forward(loom_b200_decoder* dec, const int32_t* tokens, int
         dec->h_tok[0] = tokens[0];
         LB_CUDA(ctx, cudaMemcpyAsync(dec->cur_tok, dec->h_tok, sizeof(int), cudaMemcpyHostToDevice, ctx->stream));
         if (int rc = dec_step(dec, true)) return rc;
-    } else if (n >= kGemmMinTokens && dec->tp_world == 1 && ctx->opt_prefill_gemm) {
+    } else if (n >= kGemmMinTokens && ctx->opt_prefill_gemm) {
         const int cap = n < kPrefillBlock ? n : kPrefillBlock;
         if (int rc = dec_ensure_prefill(dec, cap)) return rc;
         for (int s0 = 0; s0 < n; s0 += cap) {

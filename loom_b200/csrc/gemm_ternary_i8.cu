@@ -794,7 +794,8 @@ __global__ void __launch_bounds__(256) lb_quantize_gemm_regs_kernel(const LbGemm
         __syncthreads();
         ss = 0.0;
         for (int i = 0; i < nwarps; ++i) ss += redd[i];
-        const double root = sqrt(__dadd_rn(__ddiv_rn(ss, (double)K), a.eps));
+        if (a.given_ss) ss = a.given_ss[blockIdx.x];
+        const double root = sqrt(__dadd_rn(__ddiv_rn(ss, (double)(a.norm_count > 0 ? a.norm_count : K)), a.eps));
         const double rr = __ddiv_rn(1.0, root);
 #pragma unroll
         for (int c = 0; c < CPT; ++c) {
@@ -822,6 +823,7 @@ __global__ void __launch_bounds__(256) lb_quantize_gemm_regs_kernel(const LbGemm
     __syncthreads();
     m = red[0];
     for (int i = 1; i < nwarps; ++i) m = fmaxf(m, red[i]);
+    if (a.given_amax) m = a.given_amax[blockIdx.x];
     if (m < 1e-5f) m = 1e-5f;
     const double s = __ddiv_rn(127.0, (double)m);
     int sum = 0;
@@ -927,7 +929,9 @@ int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a) {
     const int nchunks = Kp >> 4;
     const int cpt_need = (nchunks + 255) / 256;
     const int cpt = cpt_need <= 1 ? 1 : cpt_need <= 2 ? 2 : cpt_need <= 4 ? 4 : 8;
-    if (ctx->opt_quant_regs && cpt_need <= (a.pro == LB_PRO_INNERNORM64 ? 4 : 8)) {
+    const bool regs_ok = cpt_need <= (a.pro == LB_PRO_INNERNORM64 ? 4 : 8);
+    LB_REQUIRE(ctx, !(a.given_ss || a.given_amax) || regs_ok, "gemm_quantize: rows of %d columns with agreed statistics are not supported", a.K);
+    if ((ctx->opt_quant_regs || a.given_ss || a.given_amax) && regs_ok) {
         const int T = ((nchunks + cpt - 1) / cpt + 31) / 32 * 32;
 #define LB_QREG(PRO, CPT) lb_quantize_gemm_regs_kernel<PRO, CPT><<<pt, T, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum)
 #define LB_QREG_PRO(PRO)            \

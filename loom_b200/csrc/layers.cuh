@@ -94,6 +94,14 @@ void lb_mha_release(loom_b200_mha* m);
 constexpr int kTpInt32 = 2, kTpFloat32 = 7, kTpFloat64 = 8, kTpSum = 0, kTpMax = 2;
 int lb_tp_allreduce(loom_b200_ctx* ctx, void* buf, size_t count, int dtype, int op);
 int lb_tp_allgather_f32(loom_b200_ctx* ctx, const float* send, float* recv, size_t count_per_rank);
+// Row-parallel projection of a token block (prompts under a tensor-parallel group), the pieces around the GEMM:
+// per-token statistics of the whole row from this rank's slice x [M, Kl] (partial sum of squares -> all-reduce ->
+// partial absmax of the normalised slice -> all-reduce), and the float epilogue after the int32 all-reduce of the
+// accumulators: out = float(acc * os + bias) + residual.
+int lb_tp_block_stats(loom_b200_ctx* ctx, bool x_is_f64, const void* x, int M, int Kl, int K_global, double eps, const float* inner_w,
+                      int inner_w_len, double* ss, float* amax);
+int lb_tp_block_finalize(loom_b200_ctx* ctx, int32_t* acc, int M, int rows, float scale, const float* amax, const float* bias,
+                         const float* residual, float* out);
 // Row-sharded ternary linear whose inner RMSNorm spans the sharded dimension: x_local [M, w->cols] (float or double)
 // -> out [M, w->rows] (+ residual), identical on every rank.  stats: 2*M doubles of scratch; acc: M*w->rows int32.
 int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool x_is_f64, const void* x, int M, int K_global,
@@ -111,6 +119,10 @@ struct LbGemmQuant {
     int norm_w_len;
     double eps;
     float* norm_out;      // optional [tokens, K]: the normalised rows as float32
+    // tensor-parallel row shard (x is this rank's slice): statistics of the whole row, agreed between the ranks
+    const double* given_ss;   // [tokens] sum of squares over the whole row, or null
+    const float* given_amax;  // [tokens] absmax of the normalised whole row, or null
+    int norm_count;           // elements the mean runs over (0 = K)
 };
 struct LbGemmOut {
     const float* bias;      // [rows] or null

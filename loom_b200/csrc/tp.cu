@@ -402,6 +402,31 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
     return 0;
 }
 
+int lb_tp_block_stats(loom_b200_ctx* ctx, bool x_is_f64, const void* x, int M, int Kl, int K_global, double eps, const float* inner_w,
+                      int inner_w_len, double* ss, float* amax) {
+    if (x_is_f64) lb_sumsq_kernel<double><<<M, 256, 0, ctx->stream>>>((const double*)x, Kl, ss);
+    else lb_sumsq_kernel<float><<<M, 256, 0, ctx->stream>>>((const float*)x, Kl, ss);
+    LB_CHECK_LAUNCH(ctx, "lb_sumsq_kernel");
+    if (int rc = lb_tp_allreduce(ctx, ss, (size_t)M, kNcclFloat64, kNcclSum)) return rc;
+    if (x_is_f64)
+        lb_scaled_absmax_kernel<double><<<M, 256, 0, ctx->stream>>>((const double*)x, Kl, ss, K_global, eps, inner_w, inner_w ? inner_w_len : 0, amax);
+    else
+        lb_scaled_absmax_kernel<float><<<M, 256, 0, ctx->stream>>>((const float*)x, Kl, ss, K_global, eps, inner_w, inner_w ? inner_w_len : 0, amax);
+    LB_CHECK_LAUNCH(ctx, "lb_scaled_absmax_kernel");
+    ctx->launches += 2;
+    return lb_tp_allreduce(ctx, amax, (size_t)M, kNcclFloat32, kNcclMax);
+}
+
+int lb_tp_block_finalize(loom_b200_ctx* ctx, int32_t* acc, int M, int rows, float scale, const float* amax, const float* bias,
+                         const float* residual, float* out) {
+    if (int rc = lb_tp_allreduce(ctx, acc, (size_t)M * rows, kNcclInt32, kNcclSum)) return rc;
+    const size_t n = (size_t)M * rows;
+    lb_tp_finalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(acc, M, rows, scale, amax, bias, residual, out);
+    LB_CHECK_LAUNCH(ctx, "lb_tp_finalize_kernel");
+    ctx->launches++;
+    return 0;
+}
+
 extern "C" {
 
 int loom_b200_tp_unique_id(uint8_t* id128) {

@@ -120,6 +120,15 @@ def run_checks(mode: str, local: int, group=None):
     gtok, m = gdec.generate(prompt, 20)
     if not (gtok == etok).all():
         failures.append("greedy tokens differ: %s vs %s" % (gtok.tolist(), etok.tolist()))
+    # a prompt long enough for the token-block path (tcgen05 GEMMs; row-parallel projections all-reduce their int32 sums)
+    long_prompt = rng.integers(0, V, 45).astype(np.int32)
+    el, gl = odec.forward(long_prompt), gdec.forward(long_prompt)
+    if not np.max(np.abs(gl - el)) <= tol:
+        failures.append("token-block prompt logits differ by %g" % float(np.max(np.abs(gl - el))))
+    nxt = np.array([orc.argmax(el)], np.int32)
+    el, gl = odec.forward(nxt), gdec.forward(nxt)
+    if not np.max(np.abs(gl - el)) <= tol:
+        failures.append("step after the token-block prompt: logits differ by %g" % float(np.max(np.abs(gl - el))))
     # every rank must hold the same logits bit for bit
     mine = torch.from_numpy(gdec.forward(prompt).view(np.int32).astype(np.int64))
     lo, hi = mine.clone(), mine.clone()
