@@ -635,30 +635,19 @@ def tp_mode(args):
     return 0
 
 
-def batch_mode(args):
-    """Decode with `--batch` independent sequences (configs[3]: 8B shape, batch 16, 2048-token prompts): every sequence is
-    prefilled with a prompt of its own, then all of them advance together, up to eight sequences per pass over every
-    packed matrix and several hidden rows per pass over the LM head.  value = sequences x steps / time.  Under torchrun
-    the decoder is tensor-parallel over the ranks (column-sharded Q/K/V/gate/up, row-sharded O/down, vocabulary-sharded
-    head whose tail exchanges (maximum, index) pairs; peer-memory exchange) and `scaling` is "strong"."""
-    import torch
-    import torch.distributed as dist
-
+def batch_measure(args, torch, dist, rank, world, local, shape_name, B, n_prompt, steps, warmup, layers=0):
+    """`B` independent sequences on a `shape_name`-shaped decoder: one GPU, or tensor-parallel over the ranks of the (already
+    initialised) process group with the peer-memory exchange.  Every sequence is prefilled with a prompt of its own, then all
+    advance together.  Returns the figures (device time of `steps` batch steps: CUDA events, barrier + synchronize on both
+    sides, max over ranks)."""
     import loom_b200
     from loom_b200 import cabi
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    shape = dict({"2b": SHAPE, **TP_SHAPES}[args.shape])
-    if args.layers != SHAPE["layers"]:
-        shape["layers"] = args.layers
-    B = args.batch
-    args.warmup = max(args.warmup, 3)
-    shape["max_seq_len"] = args.prompt + args.warmup + args.steps + 8
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    shape = dict({"2b": SHAPE, **TP_SHAPES}[shape_name])
+    if layers:
+        shape["layers"] = layers
+    warmup = max(warmup, 3)
+    shape["max_seq_len"] = n_prompt + warmup + steps + 8
     ts = torch.cuda.Stream()
     torch.cuda.set_stream(ts)
     ctx = loom_b200.Context(local, ts.cuda_stream)
@@ -707,10 +696,10 @@ def batch_mode(args):
     t0 = time.perf_counter()
     for i in range(B):
         dec.select(i)
-        dec.forward(rng.integers(0, shape["vocab"], args.prompt).astype(np.int32), want_logits=False)
+        dec.forward(rng.integers(0, shape["vocab"], n_prompt).astype(np.int32), want_logits=False)
     ctx.sync()
     prefill_s = time.perf_counter() - t0
-    dec.continue_batch(args.warmup)
+    dec.continue_batch(warmup)
     ctx.sync()
     sampler = ClockSampler(local)
     barrier()
@@ -718,7 +707,7 @@ def batch_mode(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    dec.continue_batch(args.steps)
+    dec.continue_batch(steps)
     e1.record()
     barrier()
     dev_s = e0.elapsed_time(e1) * 1e-3
@@ -727,32 +716,60 @@ def batch_mode(args):
         t = torch.tensor([dev_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_s = float(t[0].item())
-    peak, peak_kind = measured_peaks()
-    tern_b, kv_b, head_b = algorithmic_bytes(shape, args.prompt + args.warmup + args.steps // 2)
+    tern_b, kv_b, head_b = algorithmic_bytes(shape, n_prompt + warmup + steps // 2)
     passes = (B + 7) // 8
-    step_s = dev_s / args.steps
     # per GPU: weights once per pass of eight, KV of every sequence, head once per head pass of two rows
     moved = (passes * tern_b + B * kv_b + ((B + 1) // 2) * head_b) / world
+    res = {"shape": shape_name, "layers": shape["layers"], "world": world, "batch": B, "prompt": n_prompt, "steps": steps,
+           "tok_per_s": B * steps / dev_s, "ms_per_step": 1e3 * dev_s / steps, "per_sequence_tok_per_s": steps / dev_s,
+           "prefill_seconds_all_sequences": prefill_s, "prefill_tok_per_s": B * n_prompt / prefill_s, "clocks": clocks,
+           "bytes_per_gpu_per_step": moved}
+    ctx.sync()
+    dec.close()
+    del keep, emb
+    barrier()
+    if world > 1:
+        ctx.tp_finalize()
+    ctx.close()
+    return res
+
+
+def batch_mode(args):
+    """Decode with `--batch` independent sequences (configs[3]: 8B shape, batch 16, 2048-token prompts): up to eight
+    sequences per pass over every packed matrix and several hidden rows per pass over the LM head.  value = sequences x
+    steps / time.  Under torchrun the decoder is tensor-parallel over the ranks (column-sharded Q/K/V/gate/up, row-sharded
+    O/down, vocabulary-sharded head whose tail exchanges (maximum, index) pairs; peer-memory exchange) and `scaling` is
+    "strong"."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    r = batch_measure(args, torch, dist, rank, world, local, args.shape, args.batch, args.prompt, args.steps, args.warmup,
+                      args.layers if args.layers != SHAPE["layers"] else 0)
+    peak, peak_kind = measured_peaks()
+    step_s = r["ms_per_step"] * 1e-3
+    B = r["batch"]
     if rank == 0:
         print(json.dumps({
             "metric": "decode tok/s (%s-shape ternary decoder, %d independent sequences, %s)" % (
                 args.shape.upper(), B, "one GPU" if world == 1 else "tensor parallel over %d GPUs" % world),
-            "value": B * args.steps / dev_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": 1e3 * step_s, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
+            "value": r["tok_per_s"], "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
             "dtype": "int8 x ternary -> int32, fp64 rescale", "data": "synthetic",
             "config": {"workload": "%s-shape ternary decoder, batch %d greedy decode, %d-token prompts" % (args.shape.upper(), B, args.prompt),
-                       "layers": shape["layers"], "batch": B, "prompt": args.prompt,
+                       "layers": r["layers"], "batch": B, "prompt": args.prompt,
                        "parallelism": "single GPU" if world == 1 else "tp%d, peer-memory exchange" % world},
-            "per_sequence_tok_per_s": args.steps / dev_s, "prefill_seconds_all_sequences": prefill_s, "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": moved / step_s / 1e9, "peak": peak, "unit": "GB/s", "frac": moved / step_s / 1e9 / peak,
-                         "traffic": None, "peak_kind": peak_kind,
+            "per_sequence_tok_per_s": r["per_sequence_tok_per_s"], "prefill_seconds_all_sequences": r["prefill_seconds_all_sequences"],
+            "prefill_tok_per_s": r["prefill_tok_per_s"], "clocks": r["clocks"],
+            "roofline": {"bound": "hbm", "achieved": r["bytes_per_gpu_per_step"] / step_s / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": r["bytes_per_gpu_per_step"] / step_s / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
                          "kernel": "whole batch step, per GPU: packed weights once per pass of eight sequences, KV of every sequence, fp32 head once per head pass"}}))
-    ctx.sync()
-    dec.close()
     if world > 1:
-        barrier()
-        ctx.tp_finalize()
-        ctx.close()
         dist.barrier()
         dist.destroy_process_group()
     return 0
@@ -961,6 +978,14 @@ def main():
                                   "comes from `bench.py --mode tp --shape 8b`")
         except Exception as exc:
             line["tp"] = {"error": "%s: %r" % (type(exc).__name__, exc)}
+        # configs[3] over the same ranks: 16 independent sequences on the 8B shape (512-token prompts keep the line quick;
+        # `bench.py --mode batch --prompt 2048` is the full configuration)
+        try:
+            rb = batch_measure(args, torch, dist, rank, world, local, "8b", 16, 512, 8, args.warmup)
+            line["tp_batch"] = {k: rb[k] for k in ("shape", "layers", "world", "batch", "prompt", "steps", "tok_per_s", "ms_per_step",
+                                                   "per_sequence_tok_per_s", "prefill_tok_per_s")}
+        except Exception as exc:
+            line["tp_batch"] = {"error": "%s: %r" % (type(exc).__name__, exc)}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
             from oracle import oracle as orc

@@ -100,6 +100,8 @@ void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
  * token-block GEMM (0 = choose); "gemm_splitk" 0/1 = let several CTAs share the K range of an output tile;
  * "fold_rope" 0/1 = one-token decoder steps apply RoPE inside the attention kernel (one launch less per block);
  * "decode_splits" 0..32 = position splits of the one-token attention, read by loom_b200_decoder_create (0 = choose); "tp_peer" 0/1 = use the peer mailboxes when attached;
+ * "tp_fused" 0/1/2 = row-parallel projections under the peer mailboxes as statistics kernel + GEMV + finalize kernel (0), with the
+ * exchange of the partial sums in the GEMV's epilogue (1, default), or with the statistics exchange in its prologue as well (2);
  * "prefill_gemm" 0/1 = prompts of 32 or more tokens
  * run their projections as token-block GEMMs on the tensor cores (1) or eight tokens at a time through the GEMV (0).  "gemm_cache" 0/1 = the token-block GEMM reads pre-expanded int8 codes (one byte per weight, built per
  * matrix the first time it meets the GEMM, four times its packed bytes; the device twin of ensureBitNetCodes,
@@ -324,7 +326,9 @@ int loom_b200_decoder_continue(loom_b200_decoder* dec, int steps);
  * sixteen sequences.  Serving several sequences at once is therefore an extension, defined by its oracle: the result
  * for every sequence is that of a decoder of its own fed the same tokens.  `batch` KV rings per block share the
  * weights; a decode step carries up to eight sequences per pass over every packed matrix (the M dimension of the
- * GEMV) and several hidden rows per pass over the LM head.  One GPU only.
+ * GEMV) and several hidden rows per pass over the LM head.  One GPU, or a tensor-parallel group with the peer
+ * mailboxes attached and a vocabulary that divides by the group (the sharded head's tail then exchanges the ranks'
+ * (maximum, index) pairs).
  *
  * set_batch comes before the first set_block.  select(seq) picks the sequence the single-sequence calls act on
  * (decoder_forward for its prompt, kv_offset, reset, upload/download_cache, last_hidden, read_tokens ...).  step_batch
@@ -392,7 +396,9 @@ int loom_b200_tp_init(loom_b200_ctx* ctx, int rank, int world, const uint8_t* id
  * three per-projection exchanges (sum of squares, absmax, int32 accumulators) then travel as 8-byte {value,
  * sequence} stores straight into the receivers' mailboxes over NVLink, inside the library's own kernels; polls are
  * bounded (status word 5, LOOM_B200_ERR_TIMEOUT semantics) so a missing rank cannot hang a GPU.  Option "tp_peer" 0
- * switches back to NCCL.  The LM-head gather stays on NCCL. */
+ * switches back to NCCL.  With the mailboxes the vocabulary-sharded LM head also keeps the greedy step in its tail: the
+ * ranks exchange the (maximum, index) pairs of their slices, and the full row of logits is gathered (NCCL) only by calls
+ * that return logits to the host -- which every rank must then make alike. */
 int loom_b200_tp_peer_handle(loom_b200_ctx* ctx, uint8_t* handle64);
 int loom_b200_tp_attach_peers(loom_b200_ctx* ctx, const uint8_t* handles);
 /* Leaves the group (also done by loom_b200_ctx_destroy). */
