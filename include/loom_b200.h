@@ -100,8 +100,10 @@ void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
  * token-block GEMM (0 = choose); "gemm_splitk" 0/1 = let several CTAs share the K range of an output tile;
  * "fold_rope" 0/1 = one-token decoder steps apply RoPE inside the attention kernel (one launch less per block);
  * "decode_splits" 0..32 = position splits of the one-token attention, read by loom_b200_decoder_create (0 = choose); "tp_peer" 0/1 = use the peer mailboxes when attached;
- * "tp_fused" 0/1/2 = row-parallel projections under the peer mailboxes as statistics kernel + GEMV + finalize kernel (0), with the
- * exchange of the partial sums in the GEMV's epilogue (1, default), or with the statistics exchange in its prologue as well (2);
+ * "gemv_lean" 0/1 = one-token launches with a fused prologue use GEMV instantiations compiled without the stream-K, general-prologue
+ * and phase-trace code (1, default: +7 % decode tok/s) or the full kernels (0);
+ * "tp_fused" 0/1 = row-parallel projections under the peer mailboxes as statistics kernel + GEMV + finalize kernel (0), or with the
+ * exchange of the partial sums in the GEMV's epilogue (1, default);
  * "prefill_gemm" 0/1 = prompts of 32 or more tokens
  * run their projections as token-block GEMMs on the tensor cores (1) or eight tokens at a time through the GEMV (0).  "gemm_cache" 0/1 = the token-block GEMM reads pre-expanded int8 codes (one byte per weight, built per
  * matrix the first time it meets the GEMM, four times its packed bytes; the device twin of ensureBitNetCodes,

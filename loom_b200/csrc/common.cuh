@@ -87,7 +87,8 @@ struct loom_b200_ctx {
     int opt_gemm_splitk = 1;       // split the K range of the GEMM over several CTAs when there are few output tiles
     int opt_gemm_tile = 0;         // tokens per CTA of the GEMM: 0 = choose, 128 or 256 = force
     int opt_prefill_gemm = 1;      // prompts of 32+ tokens run their projections as token-block GEMMs
-    int opt_tp_fused = 1;          // row-parallel projections under a peer-memory group: 0: statistics kernel, GEMV, finalize kernel; 1: the GEMV's epilogue exchanges the partial sums; 2: its prologue exchanges the statistics too (one launch; measured slower)
+    int opt_gemv_lean = 1;         // decode-step launches use the GEMV instantiations without the stream-K and general-prologue code
+    int opt_tp_fused = 1;          // row-parallel projections under a peer-memory group: the GEMV's epilogue exchanges the partial sums (0: a finalize kernel does)
     int opt_quant_regs = 1;        // the GEMM's quantizer keeps a token's row in registers (0: staged in shared memory)
     int opt_gemm_stream = 1;       // over pre-expanded codes the GEMM runs as a persistent kernel with two accumulator buffers (0: the one-shot kernel)
     int opt_gemm_cache = 1;        // the token-block GEMM reads pre-expanded int8 codes (built per matrix on first use) instead of expanding the 2-bit tiles in the kernel

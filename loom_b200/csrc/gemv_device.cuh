@@ -31,7 +31,10 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-#define LB_TRACE(k) lb_trace(p.trace, (k))
+#define LB_TRACE(k)                       \
+    do {                                  \
+        if (!LEAN) lb_trace(p.trace, (k)); \
+    } while (0)
 
 struct Smem {
     uint8_t* ring;
@@ -46,12 +49,16 @@ struct Smem {
     void* stage;      // K floats (doubles for fp64 input) of prologue staging, or null
     float* gain;      // norm_w copied before the dependency wait, or null
     int pos0;         // *pos_ptr, read once after the dependency wait (KV ring rows)
-    uint32_t xseq_a, xseq_c;  // tensor-parallel exchange: sequence numbers of this launch (statistics, accumulators)
+    uint32_t xseq_c;  // tensor-parallel exchange: sequence number of this launch's exchange of partial sums
 };
 
+template <int EPI = LB_EPI_GENERIC, bool LEAN = false>
 __device__ __forceinline__ const uint32_t* tile_ptr(const LbGemvParams& p, int v, int kb) {
     int s, local;
-    if (p.interleave2) {
+    if (LEAN && EPI == LB_EPI_RESID) {  // one matrix
+        s = 0;
+        local = v;
+    } else if (LEAN ? EPI == LB_EPI_SWIGLU : p.interleave2 != 0) {
         s = v & 1;
         local = v >> 1;
     } else {
@@ -231,155 +238,126 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
     __syncthreads();  // the staging buffer is reused by the next token
 }
 
-// Tensor-parallel statistics of token n: every rank's partial value (a float64 as two words, or a float32) goes to every
-// rank's mailbox, and the partials come back in rank order.  Called by all threads of the CTA; every CTA of the launch
-// does the same with the same slots.  Returns false when a peer did not answer within the poll limit.
-// parts: the upper half of the reduction scratch (sm.red holds 32 doubles, the block reductions use the first eight):
-// [0, 2 * ranks) the gathered words, [16] the "every peer answered" flag.  No static shared memory: the kernel's dynamic
-// allocation goes up to the per-CTA limit.
-__device__ __forceinline__ uint32_t* xchg_parts(const Smem& sm) { return reinterpret_cast<uint32_t*>(sm.red) + 32; }
-
-__device__ __forceinline__ bool xchg_gather(const LbGemvParams& p, const Smem& sm, int n, bool f64, unsigned long long mine) {
-    uint32_t* parts = xchg_parts(sm);
-    const int tid = threadIdx.x, W = p.xchg_world;
-    const uint32_t seq = sm.xseq_a;
-    const size_t half = (size_t)(seq & 1);
-    const int words = f64 ? 2 : 1;
-    if (tid == 0) parts[16] = 1u;
-    __syncthreads();
-    if (tid < W * words) {
-        const int peer = tid / words, hw = tid - peer * words;
-        char* dst = f64 ? (char*)p.xchg_peers[peer] + kXRegionA + ((((half * kXMaxRanks + p.xchg_rank) * 8 + n) * 2 + hw) * 8)
-                        : (char*)p.xchg_peers[peer] + kXRegionB + (((half * kXMaxRanks + p.xchg_rank) * 8 + n) * 8);
-        ll_store(dst, (uint32_t)(mine >> (32 * hw)), seq);
-    }
-    if (tid < W * words) {
-        const int r = tid / words, hw = tid - r * words;
-        const char* src = f64 ? (const char*)p.xchg_peers[p.xchg_rank] + kXRegionA + ((((half * kXMaxRanks + r) * 8 + n) * 2 + hw) * 8)
-                              : (const char*)p.xchg_peers[p.xchg_rank] + kXRegionB + (((half * kXMaxRanks + r) * 8 + n) * 8);
-        if (!ll_wait(src, seq, &parts[tid])) parts[16] = 0u;
-    }
-    __syncthreads();
-    return parts[16] != 0u;
-}
-
-// Quantizes the M activation rows into shared memory in the k-slot order the MMA B-fragments use, and
-// leaves sum(q) and amax per token in shared memory.
-template <int PRO, int NW = kWarps>
-__device__ __forceinline__ void stage_activations(const LbGemvParams& p, const Smem& sm) {
+// One token through the general prologue path: the row is read from global memory in every pass (no staging buffer, any
+// alignment, int8 rows).  For the float prologues this is the rare path (rows that are not 16-byte aligned or do not fit
+// the staging buffer).  (Keeping it out of line was tried: the call needs the shared-memory layout in local memory and
+// the decode step lost 2 %.)
+template <int PRO, int NW>
+__device__ __forceinline__ void stage_row_general(const LbGemvParams& p, const Smem& sm, int n, const void* row) {
     constexpr int kThreads = NW * 32;
+    constexpr bool q8 = PRO == LB_PRO_Q8;
     const int tid = threadIdx.x;
     const int K = p.K, Kp = p.kblocks * kTileCols;
     const int stride32 = (Kp + 16) / 4;
     const int chunks = Kp / 16;
+    double stat = 0.0, rstat = 0.0;  // rms (or 1/rms for the inner norms) and, for the block norm, RN(1/rms)
+    float amax;
+    if (q8) {
+        amax = p.amax_in[n];
+    } else {
+        if (PRO >= LB_PRO_BLOCKNORM) {
+            double ss = 0.0;
+            if (PRO == LB_PRO_INNERNORM64) {
+                for (int c = tid; c < K; c += kThreads) {
+                    double v = ((const double*)row)[c];
+                    ss = __dadd_rn(ss, __dmul_rn(v, v));
+                }
+            } else {
+                for (int c = tid; c < K; c += kThreads) {
+                    double v = (double)((const float*)row)[c];
+                    ss = __dadd_rn(ss, __dmul_rn(v, v));
+                }
+            }
+            ss = block_sum<NW>(ss, sm.red);
+            if (p.given_ss) ss = p.given_ss[n];
+            double mean = __dadd_rn(__ddiv_rn(ss, (double)(p.norm_count > 0 ? p.norm_count : K)), p.eps);
+            stat = PRO == LB_PRO_BLOCKNORM ? sqrt(mean) : __ddiv_rn(1.0, sqrt(mean));
+            if (PRO == LB_PRO_BLOCKNORM) rstat = __ddiv_rn(1.0, stat);
+        }
+        float m = 0.0f;
+        for (int c = tid; c < K; c += kThreads)
+            m = fmaxf(m, (float)fabs(pro_value<PRO>(row, c, stat, rstat, p.norm_w, p.norm_w_len)));
+        m = block_max<NW>(m, sm.red);
+        if (p.given_amax) m = p.given_amax[n];
+        amax = m < 1e-5f ? 1e-5f : m;
+    }
+    const double s = __ddiv_rn(127.0, (double)amax);
+    const bool side = blockIdx.x == 0;
+    int local_sum = 0;
+    const bool vec_ok = q8 && ((((uintptr_t)row) & 15) == 0);
+    for (int i = tid; i < chunks; i += kThreads) {
+        uint32_t r[4] = {0u, 0u, 0u, 0u};
+        const int c0 = i * 16;
+        if (q8) {
+            if (vec_ok && c0 + 16 <= K) {
+                uint4 v = *reinterpret_cast<const uint4*>((const int8_t*)row + c0);
+                r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+            } else {
+                for (int k = 0; k < 16; ++k)
+                    if (c0 + k < K) r[k >> 2] |= (uint32_t)(uint8_t)((const int8_t*)row)[c0 + k] << (8 * (k & 3));
+            }
+        } else {
+            for (int k = 0; k < 16; ++k) {
+                int c = c0 + k;
+                if (c < K) {
+                    double v = pro_value<PRO>(row, c, stat, rstat, p.norm_w, p.norm_w_len);
+                    int q = lb_quant_i8(v, s);
+                    r[k >> 2] |= (uint32_t)(q & 0xff) << (8 * (k & 3));
+                    if (side) {
+                        if (p.q_out) p.q_out[(size_t)n * K + c] = (int8_t)q;
+                        if (p.norm_out) p.norm_out[(size_t)n * K + c] = (float)v;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b) local_sum = __dp4a((int)r[b], 0x01010101, local_sum);
+        // 4x4 byte transpose: B_j = { byte j of r0, r1, r2, r3 }
+        uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[2], r[3], 0x5140);
+        uint32_t t2 = __byte_perm(r[0], r[1], 0x7362), t3 = __byte_perm(r[2], r[3], 0x7362);
+        uint32_t B0 = __byte_perm(t0, t1, 0x5410), B1 = __byte_perm(t0, t1, 0x7632);
+        uint32_t B2 = __byte_perm(t2, t3, 0x5410), B3 = __byte_perm(t2, t3, 0x7632);
+        const int kb = i >> 3, w8 = i & 7, h = w8 >> 2, t = w8 & 3;
+        uint32_t* dst = sm.acts + (size_t)n * stride32 + kb * 32 + t * 8 + h;
+        dst[0] = B0; dst[2] = B1; dst[4] = B2; dst[6] = B3;
+    }
+    local_sum = lb_warp_sum_i(local_sum);
+    if ((tid & 31) == 0 && local_sum != 0) atomicAdd(&sm.xsum[n], local_sum);
+    if (tid < 3) sm.os[tid * kMaxM + n] = tid < p.nseg ? lb_output_scale(p.seg[tid].scale, amax) : 1.0;
+    if (tid == 0) {
+        sm.amax[n] = amax;
+        if (side && p.amax_out) p.amax_out[n] = amax;
+    }
+}
+
+// Quantizes the M activation rows into shared memory in the k-slot order the MMA B-fragments use, and
+// leaves sum(q) and amax per token in shared memory.
+template <int PRO, int NW = kWarps, bool LEAN = false>
+__device__ __forceinline__ void stage_activations(const LbGemvParams& p, const Smem& sm) {
+    const int tid = threadIdx.x;
+    const int K = p.K, Kp = p.kblocks * kTileCols;
+    const int stride32 = (Kp + 16) / 4;
     if (tid < kMaxM) sm.xsum[tid] = 0;
-    if (tid < 8) sm.acts[p.M * stride32 + tid] = 0;  // zero block for the lanes of absent tokens
-    for (int n = 0; n < p.M; ++n) {
+    const int M = p.M;
+    if (tid < 8) sm.acts[M * stride32 + tid] = 0;  // zero block for the lanes of absent tokens
+    for (int n = 0; n < M; ++n) {
         constexpr bool q8 = PRO == LB_PRO_Q8;
         const void* row = q8 ? (const void*)((const int8_t*)p.x + (size_t)n * K)
                              : (PRO == LB_PRO_INNERNORM64 ? (const void*)((const double*)p.x + (size_t)n * K)
                                                             : (const void*)((const float*)p.x + (size_t)n * K));
+        if (LEAN && !q8) {  // the launcher checked the conditions of the staged path
+            stage_row_fast<PRO == LB_PRO_Q8 ? LB_PRO_F32 : PRO, NW>(p, sm, n, row);
+            continue;
+        }
         if (!q8) {
             const bool aligned16 = (((uintptr_t)row) & 15) == 0 && (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) &&
                                    (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) && (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0);
-            if ((K & 3) == 0 && sm.stage && aligned16 && !p.xchg_peers) {
+            if ((K & 3) == 0 && sm.stage && aligned16) {
                 stage_row_fast<PRO == LB_PRO_Q8 ? LB_PRO_F32 : PRO, NW>(p, sm, n, row);
                 continue;
             }
         }
-        double stat = 0.0, rstat = 0.0;  // rms (or 1/rms for the inner norms) and, for the block norm, RN(1/rms)
-        float amax;
-        if (q8) {
-            amax = p.amax_in[n];
-        } else {
-            if (PRO >= LB_PRO_BLOCKNORM) {
-                double ss = 0.0;
-                if (PRO == LB_PRO_INNERNORM64) {
-                    for (int c = tid; c < K; c += kThreads) {
-                        double v = ((const double*)row)[c];
-                        ss = __dadd_rn(ss, __dmul_rn(v, v));
-                    }
-                } else {
-                    for (int c = tid; c < K; c += kThreads) {
-                        double v = (double)((const float*)row)[c];
-                        ss = __dadd_rn(ss, __dmul_rn(v, v));
-                    }
-                }
-                ss = block_sum<NW>(ss, sm.red);
-                if (p.given_ss) ss = p.given_ss[n];
-                if (p.xchg_peers) {  // the sum over the whole vector: partials of all ranks, added in rank order on every rank
-                    const uint32_t* s_parts = xchg_parts(sm);
-                    if (!xchg_gather(p, sm, n, true, (unsigned long long)__double_as_longlong(ss)) && tid == 0) atomicExch(p.status, 5);
-                    ss = 0.0;
-                    for (int r = 0; r < p.xchg_world; ++r)
-                        ss = __dadd_rn(ss, __longlong_as_double((long long)(((unsigned long long)s_parts[2 * r + 1] << 32) | s_parts[2 * r])));
-                    __syncthreads();
-                }
-                double mean = __dadd_rn(__ddiv_rn(ss, (double)(p.norm_count > 0 ? p.norm_count : K)), p.eps);
-                stat = PRO == LB_PRO_BLOCKNORM ? sqrt(mean) : __ddiv_rn(1.0, sqrt(mean));
-                if (PRO == LB_PRO_BLOCKNORM) rstat = __ddiv_rn(1.0, stat);
-            }
-            float m = 0.0f;
-            for (int c = tid; c < K; c += kThreads)
-                m = fmaxf(m, (float)fabs(pro_value<PRO>(row, c, stat, rstat, p.norm_w, p.norm_w_len)));
-            m = block_max<NW>(m, sm.red);
-            if (p.given_amax) m = p.given_amax[n];
-            if (p.xchg_peers) {
-                const uint32_t* s_partm = xchg_parts(sm);
-                if (!xchg_gather(p, sm, n, false, (unsigned long long)__float_as_uint(m)) && tid == 0) atomicExch(p.status, 5);
-                m = 0.0f;
-                for (int r = 0; r < p.xchg_world; ++r) m = fmaxf(m, __uint_as_float(s_partm[r]));
-                __syncthreads();
-            }
-            amax = m < 1e-5f ? 1e-5f : m;
-        }
-        const double s = __ddiv_rn(127.0, (double)amax);
-        const bool side = blockIdx.x == 0;
-        int local_sum = 0;
-        const bool vec_ok = q8 && ((((uintptr_t)row) & 15) == 0);
-        for (int i = tid; i < chunks; i += kThreads) {
-            uint32_t r[4] = {0u, 0u, 0u, 0u};
-            const int c0 = i * 16;
-            if (q8) {
-                if (vec_ok && c0 + 16 <= K) {
-                    uint4 v = *reinterpret_cast<const uint4*>((const int8_t*)row + c0);
-                    r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
-                } else {
-                    for (int k = 0; k < 16; ++k)
-                        if (c0 + k < K) r[k >> 2] |= (uint32_t)(uint8_t)((const int8_t*)row)[c0 + k] << (8 * (k & 3));
-                }
-            } else {
-                for (int k = 0; k < 16; ++k) {
-                    int c = c0 + k;
-                    if (c < K) {
-                        double v = pro_value<PRO>(row, c, stat, rstat, p.norm_w, p.norm_w_len);
-                        int q = lb_quant_i8(v, s);
-                        r[k >> 2] |= (uint32_t)(q & 0xff) << (8 * (k & 3));
-                        if (side) {
-                            if (p.q_out) p.q_out[(size_t)n * K + c] = (int8_t)q;
-                            if (p.norm_out) p.norm_out[(size_t)n * K + c] = (float)v;
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int b = 0; b < 4; ++b) local_sum = __dp4a((int)r[b], 0x01010101, local_sum);
-            // 4x4 byte transpose: B_j = { byte j of r0, r1, r2, r3 }
-            uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[2], r[3], 0x5140);
-            uint32_t t2 = __byte_perm(r[0], r[1], 0x7362), t3 = __byte_perm(r[2], r[3], 0x7362);
-            uint32_t B0 = __byte_perm(t0, t1, 0x5410), B1 = __byte_perm(t0, t1, 0x7632);
-            uint32_t B2 = __byte_perm(t2, t3, 0x5410), B3 = __byte_perm(t2, t3, 0x7632);
-            const int kb = i >> 3, w8 = i & 7, h = w8 >> 2, t = w8 & 3;
-            uint32_t* dst = sm.acts + (size_t)n * stride32 + kb * 32 + t * 8 + h;
-            dst[0] = B0; dst[2] = B1; dst[4] = B2; dst[6] = B3;
-        }
-        local_sum = lb_warp_sum_i(local_sum);
-        if ((tid & 31) == 0 && local_sum != 0) atomicAdd(&sm.xsum[n], local_sum);
-        if (tid < 3) sm.os[tid * kMaxM + n] = tid < p.nseg ? lb_output_scale(p.seg[tid].scale, amax) : 1.0;
-        if (tid == 0) {
-            sm.amax[n] = amax;
-            if (side && p.amax_out) p.amax_out[n] = amax;
-        }
+        stage_row_general<PRO, NW>(p, sm, n, row);
     }
     __syncthreads();
 }
@@ -404,7 +382,7 @@ __device__ __forceinline__ size_t out_index(const LbGemvParams& p, const Smem& s
 }
 
 // Epilogue of one finished row (or gate/up row pair).  vals = [group][M][16] complete sums of sum(code*x).
-template <int EPI>
+template <int EPI, bool LEAN = false>
 __device__ __forceinline__ void finish_row(const LbGemvParams& p, const Smem& sm, int group_first_vstrip, int e, int n,
                                            int i, const int* vals) {
     const int M = p.M;

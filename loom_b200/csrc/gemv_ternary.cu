@@ -27,7 +27,10 @@
 namespace {
 
 
-template <bool MMA, int PRO, int EPI>
+// LEAN: the instantiation for the launches of a decode step -- one token, aligned partition, the staged prologue, no phase
+// trace.  The code of the other paths (stream-K ranges and their fix-up, the general prologue, the token loops) is left out: code a launch never runs still
+// costs it time (adding 200 instructions to an unused branch of the prologue slowed the decode step by 3 %).
+template <bool MMA, int PRO, int EPI, bool LEAN = false>
 __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __grid_constant__ LbGemvParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -66,7 +69,8 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     // ---- tile ranges --------------------------------------------------------------------------------
     // aligned: every CTA owns whole strip groups (no cross-CTA fix-up); otherwise stream-K over tiles.
     int t0, t1, first_group;
-    if (p.aligned) {
+    const bool aligned = LEAN || p.aligned;
+    if (aligned) {
         const int b = (int)blockIdx.x;
         const int g0 = b * p.part_q + (b < p.part_r ? b : p.part_r);
         const int g1 = g0 + p.part_q + (b < p.part_r ? 1 : 0);
@@ -115,14 +119,14 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     };
     auto issue = [&](int stage, const Cursor& c, int len) {  // lane 0 only
         lb_mbar_expect_tx(&my_bars[stage], (uint32_t)len * kTileBytes);
-        lb_bulk_g2s(my_ring + (size_t)stage * kStageBytes, tile_ptr(p, c.v, c.kb), (uint32_t)len * kTileBytes,
+        lb_bulk_g2s(my_ring + (size_t)stage * kStageBytes, tile_ptr<EPI, LEAN>(p, c.v, c.kb), (uint32_t)len * kTileBytes,
                     &my_bars[stage]);
     };
 
     // first ring fill: weights do not depend on the producer of the activations
     Cursor ic;
     ic.pos = w0;
-    if (p.aligned && KB > 1 && KB <= 256 && (unsigned)(w0 - t0) < 65536u) {  // t0 is a strip boundary: only the small offset needs dividing
+    if (aligned && KB > 1 && KB <= 256 && (unsigned)(w0 - t0) < 65536u) {  // t0 is a strip boundary: only the small offset needs dividing
         const int dv = (int)__umulhi((unsigned)(w0 - t0), p.kb_magic);
         ic.v = local_v0 + dv;
         ic.kb = (w0 - t0) - dv * KB;
@@ -148,10 +152,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     lb_pdl_wait();               // everything below may read what earlier launches wrote
     LB_TRACE(2);
     if (p.pos_ptr) sm.pos0 = *p.pos_ptr;
-    if (p.xchg_peers) {  // sequence numbers of this launch's exchanges (moved on by the last CTA of the previous one)
-        sm.xseq_a = p.xchg_ctr[0];
-        sm.xseq_c = p.xchg_ctr[2];
-    }
+    if (EPI == LB_EPI_TPSUM) sm.xseq_c = p.xchg_ctr[2];  // sequence number of this launch's exchange (moved on by the last CTA of the previous one)
     if (EPI == LB_EPI_RESID && M == 1 && cta_tiles > 0) {
         // the epilogue's operands of this CTA's rows: requested now, so that they are in L1 when the sums are done
         const int row0 = (t0 / KB) * kTileRows, nrows = ((t1 - 1) / KB + 1) * kTileRows - row0;
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
             if (p.seg[0].bias) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.seg[0].bias + row0 + tid));
         }
     }
-    stage_activations<PRO>(p, sm);
+    stage_activations<PRO, kWarps, LEAN>(p, sm);
     LB_TRACE(3);
 
     // ---- main loop ------------------------------------------------------------------------------------
@@ -341,14 +342,13 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
             if (t == gridDim.x - 1) {
                 p.xchg_ctr[4] = 0;
                 __threadfence();
-                if (PRO != LB_PRO_Q8) p.xchg_ctr[0] = sm.xseq_a + 1;
                 p.xchg_ctr[2] = seq + 1;
             }
         }
         LB_TRACE(5);
         return;
     }
-    if (p.aligned) {  // every group is this CTA's own: no fix-up, no flags
+    if (aligned) {  // every group is this CTA's own: no fix-up, no flags
         const int ngl_a = p.part_q + ((int)blockIdx.x < p.part_r ? 1 : 0);
         for (int idx = tid; idx < ngl_a * per_group; idx += kThreads) {
             int gl, i;
@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
                 i = idx - gl * per_group;
             }
             const int e = i / (M * 16), rem = i - e * (M * 16);
-            finish_row<EPI>(p, sm, (first_group + gl) * p.group, e, rem >> 4, rem & 15, sm.sacc + (size_t)gl * per_group);
+            finish_row<EPI, LEAN>(p, sm, (first_group + gl) * p.group, e, rem >> 4, rem & 15, sm.sacc + (size_t)gl * per_group);
         }
         LB_TRACE(5);
         return;
@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         if (gl == 0 && !do_first) continue;
         if (gl == ngl - 1 && ngl > 1 && !do_last) continue;
         const int e = i / (M * 16), rem = i - e * (M * 16);
-        finish_row<EPI>(p, sm, (first_group + gl) * p.group, e, rem >> 4, rem & 15, sm.sacc + (size_t)gl * per_group);
+        finish_row<EPI, LEAN>(p, sm, (first_group + gl) * p.group, e, rem >> 4, rem & 15, sm.sacc + (size_t)gl * per_group);
     }
     LB_TRACE(5);
 }
@@ -547,7 +547,7 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     // Wide inputs, or three and more tokens: normalise and quantize once in a launch of its own (one CTA per token), then
     // stream the weights against the int8 rows.  The fused prologue is repeated by every CTA and costs it 4-6 us per token:
     // right for one or two tokens on the critical path of a decode step, wrong for a pass of eight.
-    if (p.pro != LB_PRO_Q8 && !p.xchg_peers && (p.K >= kSplitQuantK || p.M >= kSplitQuantTokens) && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
+    if (p.pro != LB_PRO_Q8 && (p.K >= kSplitQuantK || p.M >= kSplitQuantTokens) && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
         (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) && (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) &&
         (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0)) {
         const size_t qbytes = ((size_t)p.M * p.K + 255) & ~(size_t)255;
@@ -611,10 +611,22 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     LB_PICK(12, true, LB_PRO_Q8, LB_EPI_QKV)
     LB_PICK(13, true, LB_PRO_Q8, LB_EPI_RESID)
     LB_PICK(14, true, LB_PRO_BLOCKNORM, LB_EPI_GENERIC)
-    LB_PICK(15, true, LB_PRO_INNERNORM64, LB_EPI_TPSUM)
-    LB_PICK(16, true, LB_PRO_INNERNORM, LB_EPI_TPSUM)
-    LB_PICK(17, true, LB_PRO_Q8, LB_EPI_TPSUM)
+    LB_PICK(15, true, LB_PRO_Q8, LB_EPI_TPSUM)
 #undef LB_PICK
+    // the lean instantiations of the decode step's four launches
+    const bool lean = ctx->opt_gemv_lean && p.M == 1 && !p.trace && p.aligned && p.stage_bytes > 0 && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
+                      (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) && (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) &&
+                      (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0);
+#define LB_PICK_LEAN(id, pro_, epi_)                              \
+    if (lean && p.pro == pro_ && p.epi == epi_) {                 \
+        kern = lb_gemv_ternary_kernel<true, pro_, epi_, true>;    \
+        kid = id;                                                 \
+    }
+    LB_PICK_LEAN(16, LB_PRO_BLOCKNORM, LB_EPI_QKV)
+    LB_PICK_LEAN(17, LB_PRO_INNERNORM64, LB_EPI_RESID)
+    LB_PICK_LEAN(18, LB_PRO_BLOCKNORM, LB_EPI_SWIGLU)
+    LB_PICK_LEAN(19, LB_PRO_INNERNORM, LB_EPI_RESID)
+#undef LB_PICK_LEAN
     if (!kern) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: no kernel for prologue %d with epilogue %d", p.pro, p.epi);
     const unsigned attr_bit = 1u << kid;
     if (!(ctx->func_attr_mask & attr_bit)) {  // per device: the context pins the device

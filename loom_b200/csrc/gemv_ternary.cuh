@@ -76,10 +76,9 @@ struct LbGemvParams {
     const double* given_ss;   // optional [M]: sum of squares over the full vector (tensor-parallel row shards)
     const float* given_amax;  // optional [M]: absmax of the normalised full vector
     int norm_count;           // elements the mean runs over (0 = K)
-    // Tensor-parallel row shard (x is this rank's slice of the input): with xchg_peers set, the prologue exchanges the
-    // partial sum of squares and the partial absmax of the normalised slice with the other ranks (every CTA sends and
-    // polls the same mailbox slots: the stores are idempotent), and LB_EPI_TPSUM exchanges the partial accumulators.
-    // xchg_ctr: {statistics sequence, accumulator sequence, arrivals}; the last CTA to finish moves both sequences on.
+    // Tensor-parallel row shard with LB_EPI_TPSUM: the epilogue exchanges the partial sums with the other ranks through
+    // the peer mailboxes.  xchg_ctr[2] is the exchange's sequence number, xchg_ctr[4] counts the CTAs that are done; the
+    // last one moves the sequence on.
     void* const* xchg_peers;
     int xchg_rank, xchg_world;
     unsigned int* xchg_ctr;

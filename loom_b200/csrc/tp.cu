@@ -306,13 +306,13 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
     double* ss = stats;
     float* amax = reinterpret_cast<float*>(stats + M);
     const bool peer = ctx->tp_peer && ctx->opt_tp_peer && ctx->tp_world > 1 && (size_t)M * w->rows <= (size_t)kXMaxAcc && M <= 8;
-    // One launch: the GEMV exchanges the statistics in its prologue and the partial sums in its epilogue (one token), or
-    // takes the statistics kernel's int8 slice and exchanges only the sums (several tokens: one CTA per token is the
-    // better place for their statistics).  Option "tp_fused": 0 keeps the three-launch form, 1 fuses only the exchange of the sums, 2 both.
+    // Two launches: the statistics kernel, then the GEMV that takes its int8 slice and exchanges the partial sums in its
+    // own epilogue.  Option "tp_fused" = 0 keeps the three-launch form (statistics, GEMV, finalize).  Moving the
+    // statistics exchange into the GEMV's prologue as well (one launch) was built and measured 2.3x slower -- every CTA
+    // repeats two NVLink round trips and the staged prologue cannot be used -- and is not kept.
     const bool fused = peer && ctx->opt_tp_fused && (Kl & 3) == 0 && out != nullptr;
-    const bool fused_pro = fused && ctx->opt_tp_fused >= 2 && M == 1 && Kl < kSplitQuantK;
     int8_t* q8 = nullptr;
-    if (peer && !fused_pro) {
+    if (peer) {
         LB_REQUIRE(ctx, (Kl & 3) == 0, "tensor-parallel shard width %d must be a multiple of 4", Kl);
         if (int rc = lb_ensure_quant_scratch(ctx, (size_t)kChunkTokens * Kl + 256)) return rc;
         q8 = reinterpret_cast<int8_t*>(ctx->quant_scratch);
@@ -348,14 +348,7 @@ int lb_tp_rowsharded_linear(loom_b200_ctx* ctx, const loom_b200_weight* w, bool 
     p.seg[0].kind = LB_OUT_ACC;
     p.K = Kl;
     p.M = M;
-    if (fused_pro) {
-        p.pro = x_is_f64 ? LB_PRO_INNERNORM64 : LB_PRO_INNERNORM;
-        p.x = x;
-        p.norm_w = inner_w;
-        p.norm_w_len = inner_w ? inner_w_len : 0;
-        p.eps = eps;
-        p.norm_count = K_global;
-    } else if (peer) {  // the statistics kernel already quantized the slice
+    if (peer) {  // the statistics kernel already quantized the slice
         p.pro = LB_PRO_Q8;
         p.x = q8;
         p.amax_in = amax;

@@ -36,9 +36,7 @@ def run_checks(mode: str, local: int, group=None):
         ctx.set_option("tp_graph", 0)
     if mode == "peer3":  # the three-launch form of a row-parallel projection (statistics kernel, GEMV, finalize kernel)
         ctx.set_option("tp_fused", 0)
-    if mode == "peer2":  # the GEMV also exchanges the statistics itself (one launch; measured slower, kept as an option)
-        ctx.set_option("tp_fused", 2)
-    if mode in ("peer", "peer2", "peer3"):  # exchange through peer mailboxes instead of NCCL: gather every rank's IPC handle
+    if mode in ("peer", "peer3"):  # exchange through peer mailboxes instead of NCCL: gather every rank's IPC handle
         mine = torch.frombuffer(bytearray(ctx.tp_peer_handle()), dtype=torch.uint8).clone()
         allh = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
         dist.all_gather(allh, mine, group=group)
@@ -58,7 +56,6 @@ def run_checks(mode: str, local: int, group=None):
 
     # ---- a row-sharded linear with inner-norm weights, bias and residual ----
     rng = np.random.default_rng(77)
-    # (three tokens: the statistics come from the one-CTA-per-token kernel; one token: the GEMV exchanges them itself)
     for rows, K, batch in ((96, 256 * world, 3), (200, 512 * world, 1), (96, 256 * world, 8)):
         master = (rng.standard_normal(rows * K) * 0.05).astype(np.float32)
         words, scale = orc.pack_f32(master, rows, K)
