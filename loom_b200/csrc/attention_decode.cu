@@ -127,10 +127,10 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
     if (cnt > 0 && lane == 0) {
         if (warp == 0) {
             lb_mbar_expect_tx(&bars[0], (uint32_t)cnt * hd * 4);
-            lb_bulk_g2s(kt, kbase + (size_t)k0 * hd, (uint32_t)cnt * hd * 4, &bars[0]);
+            lb_bulk_g2s_stream(kt, kbase + (size_t)k0 * hd, (uint32_t)cnt * hd * 4, &bars[0], lb_policy_evict_first());
         } else if (warp == 1) {
             lb_mbar_expect_tx(&bars[1], (uint32_t)cnt * hd * 4);
-            lb_bulk_g2s(vt, vbase + (size_t)k0 * hd, (uint32_t)cnt * hd * 4, &bars[1]);
+            lb_bulk_g2s_stream(vt, vbase + (size_t)k0 * hd, (uint32_t)cnt * hd * 4, &bars[1], lb_policy_evict_first());
         } else if (warp == 2 && p.next_k) {  // the next block's rows of the same positions, into L2
             l2_prefetch(p.next_k + ((size_t)kvh * p.msl + k0) * hd, (uint32_t)cnt * hd * 4);
             l2_prefetch(p.next_v + ((size_t)kvh * p.msl + k0) * hd, (uint32_t)cnt * hd * 4);

@@ -294,6 +294,20 @@ __device__ __forceinline__ void lb_bulk_g2s(void* dst_smem, const void* src_gmem
                  "l"(src_gmem), "r"(bytes), "r"(lb_smem_u32(bar))
                  : "memory");
 }
+// The same copy for data that is read once per step (packed weights, the fp32 head, KV rows): the lines are marked
+// evict-first in L2, so that a step's 2 GB of streams do not push out what IS reused from step to step -- the
+// activations, the norm gains and the kernels' own instructions.
+__device__ __forceinline__ uint64_t lb_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void lb_bulk_g2s_stream(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+                     lb_smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(lb_smem_u32(bar)), "l"(policy)
+                 : "memory");
+}
 // Programmatic dependent launch: wait for the kernels this one depends on / release dependents.
 __device__ __forceinline__ void lb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void lb_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

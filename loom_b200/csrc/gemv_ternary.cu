@@ -27,8 +27,8 @@
 namespace {
 
 
-// LEAN: the instantiation for the launches of a decode step -- one token, aligned partition, the staged prologue, no phase
-// trace.  The code of the other paths (stream-K ranges and their fix-up, the general prologue, the token loops) is left out: code a launch never runs still
+// LEAN: the instantiation for the launches of a decode step -- aligned partition, the staged prologue (or int8 rows), no
+// phase trace.  The code of the other paths (stream-K ranges and their fix-up, the general float prologue) is left out: code a launch never runs still
 // costs it time (adding 200 instructions to an unused branch of the prologue slowed the decode step by 3 %).
 template <bool MMA, int PRO, int EPI, bool LEAN = false>
 __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __grid_constant__ LbGemvParams p) {
@@ -117,10 +117,11 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
             c.v++;
         }
     };
+    const uint64_t stream_policy = lb_policy_evict_first();  // the weights are read once per step
     auto issue = [&](int stage, const Cursor& c, int len) {  // lane 0 only
         lb_mbar_expect_tx(&my_bars[stage], (uint32_t)len * kTileBytes);
-        lb_bulk_g2s(my_ring + (size_t)stage * kStageBytes, tile_ptr<EPI, LEAN>(p, c.v, c.kb), (uint32_t)len * kTileBytes,
-                    &my_bars[stage]);
+        lb_bulk_g2s_stream(my_ring + (size_t)stage * kStageBytes, tile_ptr<EPI, LEAN>(p, c.v, c.kb), (uint32_t)len * kTileBytes,
+                           &my_bars[stage], stream_policy);
     };
 
     // first ring fill: weights do not depend on the producer of the activations
@@ -613,10 +614,13 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     LB_PICK(14, true, LB_PRO_BLOCKNORM, LB_EPI_GENERIC)
     LB_PICK(15, true, LB_PRO_Q8, LB_EPI_TPSUM)
 #undef LB_PICK
-    // the lean instantiations of the decode step's four launches
-    const bool lean = ctx->opt_gemv_lean && p.M == 1 && !p.trace && p.aligned && p.stage_bytes > 0 && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
-                      (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) && (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) &&
-                      (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0);
+    // the lean instantiations: the launches of a decode step (fused prologues), and their int8-row forms (a pass of several
+    // sequences, tensor-parallel row shards, the plain ternary linear)
+    const bool lean_base = ctx->opt_gemv_lean && !p.trace && p.aligned && !use_dp4a;
+    const bool lean = lean_base && (p.pro == LB_PRO_Q8 ||
+                                    (p.stage_bytes > 0 && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
+                                     (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) && (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) &&
+                                     (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0)));
 #define LB_PICK_LEAN(id, pro_, epi_)                              \
     if (lean && p.pro == pro_ && p.epi == epi_) {                 \
         kern = lb_gemv_ternary_kernel<true, pro_, epi_, true>;    \
@@ -626,6 +630,11 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     LB_PICK_LEAN(17, LB_PRO_INNERNORM64, LB_EPI_RESID)
     LB_PICK_LEAN(18, LB_PRO_BLOCKNORM, LB_EPI_SWIGLU)
     LB_PICK_LEAN(19, LB_PRO_INNERNORM, LB_EPI_RESID)
+    LB_PICK_LEAN(20, LB_PRO_Q8, LB_EPI_GENERIC)
+    LB_PICK_LEAN(21, LB_PRO_Q8, LB_EPI_QKV)
+    LB_PICK_LEAN(22, LB_PRO_Q8, LB_EPI_SWIGLU)
+    LB_PICK_LEAN(23, LB_PRO_Q8, LB_EPI_RESID)
+    LB_PICK_LEAN(24, LB_PRO_Q8, LB_EPI_TPSUM)
 #undef LB_PICK_LEAN
     if (!kern) return lb_fail(ctx, LOOM_B200_ERR_UNSUPPORTED, "gemv: no kernel for prologue %d with epilogue %d", p.pro, p.epi);
     const unsigned attr_bit = 1u << kid;

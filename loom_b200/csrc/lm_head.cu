@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(NW * 32, 1) lb_lm_head_stream_kernel(const LbL
     const int r0 = (int)((long long)p.vocab * blockIdx.x / gridDim.x), r1 = (int)((long long)p.vocab * (blockIdx.x + 1) / gridDim.x);
     const int w0 = r0 + (r1 - r0) * warp / NW, w1 = r0 + (r1 - r0) * (warp + 1) / NW;
     const uint32_t row_bytes = (uint32_t)H * 4;
+    const uint64_t stream_policy = lb_policy_evict_first();  // 1.3 GB read once per token: do not let it own the L2
     if (lane == 0) {
         lb_mbar_init(&bars[0], 1);
         lb_mbar_init(&bars[1], 1);
@@ -54,7 +55,7 @@ __global__ void __launch_bounds__(NW * 32, 1) lb_lm_head_stream_kernel(const LbL
     if (lane == 0) {
         for (int s = 0; s < 2 && w0 + s < w1; ++s) {
             lb_mbar_expect_tx(&bars[s], row_bytes);
-            lb_bulk_g2s(ring + (size_t)s * H, p.head + (size_t)(w0 + s) * H, row_bytes, &bars[s]);
+            lb_bulk_g2s_stream(ring + (size_t)s * H, p.head + (size_t)(w0 + s) * H, row_bytes, &bars[s], stream_policy);
         }
     }
     lb_pdl_wait();
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(NW * 32, 1) lb_lm_head_stream_kernel(const LbL
         if (lane == 0 && r + 2 < w1) {  // the stage is free again: request the row after next
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             lb_mbar_expect_tx(&bars[st], row_bytes);
-            lb_bulk_g2s(ring + (size_t)st * H, p.head + (size_t)(r + 2) * H, row_bytes, &bars[st]);
+            lb_bulk_g2s_stream(ring + (size_t)st * H, p.head + (size_t)(r + 2) * H, row_bytes, &bars[st], stream_policy);
         }
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
