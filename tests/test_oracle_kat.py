@@ -238,3 +238,34 @@ def test_decoder_tiny_prefill_equals_incremental():
     a, _, _ = dec.generate(prompt, 6)
     b, _, _ = dec.generate(prompt, 6, simd=1, threads=2, attn_threads=2)
     assert (a == b).all()
+
+
+def test_summation_order_of_the_norm_statistics_is_bounded():
+    # The reference adds the squares of a row one after the other in float64 (poly/bitnet_cpu.go:893-913); the GPU
+    # kernels add them as trees of partial sums.  What that can change: the sum by some tens of units in its last place, the
+    # normalised float32 values in their last bit on a few elements, and an int8 code by one where a value sits on a
+    # rounding boundary.  The bound is shown here on the CPU: oracle (sequential) against a pairwise recomputation.
+    rng = np.random.default_rng(893)
+    flips = total = 0
+    for K in (2560, 6912):
+        for _ in range(8):
+            x = rng.standard_normal(K).astype(np.float32)
+            w = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+            y_seq = orc.inner_rmsnorm_f32(x, w, 1e-5)  # the oracle: sequential sum
+            xd = x.astype(np.float64)
+            sq = xd * xd
+            ss_seq = 0.0
+            for v in sq:
+                ss_seq += v
+            ss_tree = float(np.sum(sq.reshape(-1, 256).sum(axis=1)))  # partial sums of 256, then their sum
+            assert abs(ss_tree - ss_seq) <= 4 * np.sqrt(K) * np.spacing(ss_seq)  # random-walk growth of the sequential sum's rounding
+            sc = 1.0 / np.sqrt(ss_tree / K + 1e-5)
+            y_tree = ((xd * sc).astype(np.float64) * w.astype(np.float64)).astype(np.float32)
+            assert np.max(np.abs(y_tree.astype(np.float64) - y_seq.astype(np.float64))) <= 2 * np.max(np.spacing(np.abs(y_seq)))
+            q_seq, a_seq = orc.quantize_f32(y_seq)
+            q_tree, a_tree = orc.quantize_f32(y_tree)
+            d = np.abs(q_seq.astype(np.int32) - q_tree.astype(np.int32))
+            assert d.max() <= 1
+            flips += int((d != 0).sum())
+            total += K
+    assert flips <= total // 1000  # a code moves only where a value sits within an ulp of a rounding boundary
