@@ -122,7 +122,8 @@ __device__ __forceinline__ double pro_value(const void* row, int c, double stat,
 __device__ __forceinline__ double lb_wide(float v) { return (double)v; }
 __device__ __forceinline__ double lb_wide(double v) { return v; }
 
-template <int PRO, int NW = kWarps>
+// LEAN (the launcher checked): gains cover the whole row or are absent, no statistics supplied by the caller, no side outputs.
+template <int PRO, int NW = kWarps, bool LEAN = false>
 __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem& sm, int n, const void* row) {
     constexpr int kThreads = NW * 32;
     const int tid = threadIdx.x, K = p.K, units = K >> 2;
@@ -158,7 +159,7 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
     }
     if (PRO >= LB_PRO_BLOCKNORM) {
         // tensor-parallel row shards: the sum of squares over the whole (sharded) vector is supplied by the caller
-        if (p.given_ss) ss = p.given_ss[n];
+        if (!LEAN && p.given_ss) ss = p.given_ss[n];
         else ss = block_sum<NW>(ss, sm.red);
         const double mean = __dadd_rn(__ddiv_rn(ss, (double)(p.norm_count > 0 ? p.norm_count : K)), p.eps);
         const double root = sqrt(mean);
@@ -168,7 +169,7 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
         for (int idx = tid; idx < units; idx += kThreads) {
             double w[4] = {1.0, 1.0, 1.0, 1.0};
             if (have_w) {
-                if (4 * idx + 4 <= p.norm_w_len) {
+                if (LEAN || 4 * idx + 4 <= p.norm_w_len) {
                     const float4 g = reinterpret_cast<const float4*>(gw)[idx];
                     w[0] = (double)g.x; w[1] = (double)g.y; w[2] = (double)g.z; w[3] = (double)g.w;
                 } else {
@@ -190,11 +191,11 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
         }
     }
     if (f64) m = fmaxf(m, (float)__longlong_as_double((long long)mdb));
-    if (p.given_amax) m = p.given_amax[n];  // absmax over the whole sharded vector (already floored by the caller or below)
+    if (!LEAN && p.given_amax) m = p.given_amax[n];  // absmax over the whole sharded vector (already floored by the caller or below)
     else m = block_max<NW>(m, sm.red);
     const float amax = m < 1e-5f ? 1e-5f : m;
     const double s = __ddiv_rn(127.0, (double)amax);
-    const bool side = blockIdx.x == 0;
+    const bool side = !LEAN && blockIdx.x == 0;
     int local_sum = 0;
     uint8_t* abytes = reinterpret_cast<uint8_t*>(sm.acts + (size_t)n * stride32);
     // the output scales need a float64 division: the last threads (which own the fewest units) start it before their loop
@@ -346,7 +347,7 @@ __device__ __forceinline__ void stage_activations(const LbGemvParams& p, const S
                              : (PRO == LB_PRO_INNERNORM64 ? (const void*)((const double*)p.x + (size_t)n * K)
                                                             : (const void*)((const float*)p.x + (size_t)n * K));
         if (LEAN && !q8) {  // the launcher checked the conditions of the staged path
-            stage_row_fast<PRO == LB_PRO_Q8 ? LB_PRO_F32 : PRO, NW>(p, sm, n, row);
+            stage_row_fast<PRO == LB_PRO_Q8 ? LB_PRO_F32 : PRO, NW, true>(p, sm, n, row);
             continue;
         }
         if (!q8) {

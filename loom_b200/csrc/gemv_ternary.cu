@@ -619,8 +619,8 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
     const bool lean_base = ctx->opt_gemv_lean && !p.trace && p.aligned && !use_dp4a;
     const bool lean = lean_base && (p.pro == LB_PRO_Q8 ||
                                     (p.stage_bytes > 0 && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
-                                     (!p.norm_w || (((uintptr_t)p.norm_w) & 15) == 0) && (!p.norm_out || (((uintptr_t)p.norm_out) & 15) == 0) &&
-                                     (!p.q_out || (((uintptr_t)p.q_out) & 3) == 0)));
+                                     (!p.norm_w || ((((uintptr_t)p.norm_w) & 15) == 0 && p.norm_w_len == p.K)) && !p.norm_out && !p.q_out &&
+                                     !p.amax_out && !p.given_ss && !p.given_amax));
 #define LB_PICK_LEAN(id, pro_, epi_)                              \
     if (lean && p.pro == pro_ && p.epi == epi_) {                 \
         kern = lb_gemv_ternary_kernel<true, pro_, epi_, true>;    \
