@@ -84,7 +84,9 @@ __device__ __forceinline__ int halving_index(int lane) {
     return idx;
 }
 
-template <int G>
+// LEAN: one token of one sequence, no phase trace (what a decode step launches); the code of the other forms is left out.
+// (Fixing the head dimension at compile time as well measured no better.)
+template <int G, bool LEAN = false>
 __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(const LbAttnParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2];
@@ -93,8 +95,8 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
     __shared__ double s_gw[kAcMaxS * G];     // combine: weight of every (slice, head)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hd = p.hd, half = hd >> 1, kvh = blockIdx.y;
-    const int n = blockIdx.z;  // token of the pass; with seq_stride > 0 every token is a sequence of its own
-    const size_t seq_off = (size_t)n * (size_t)p.seq_stride;
+    const int n = LEAN ? 0 : blockIdx.z;  // token of the pass; with seq_stride > 0 every token is a sequence of its own
+    const size_t seq_off = LEAN ? 0 : (size_t)n * (size_t)p.seq_stride;
     const uint32_t rank = cluster_ctarank(), S = cluster_nctarank();
     const int cmax = p.max_chunk;  // positions one CTA holds at most
     const int dps = hd / (int)S;   // output dimensions every CTA combines
@@ -114,8 +116,8 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
     asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     lb_pdl_launch_dependents();
     lb_pdl_wait();
-    lb_trace(p.trace, 2);
-    const int last = p.seq_stride > 0 ? p.pos_ptr[n] : *p.pos_ptr;  // the new token's position; it attends to 0..last
+    if (!LEAN) lb_trace(p.trace, 2);
+    const int last = (!LEAN && p.seq_stride > 0) ? p.pos_ptr[n] : *p.pos_ptr;  // the new token's position; it attends to 0..last
     const int total = last + 1;
     const int per = (total + (int)S - 1) / (int)S;
     const int k0 = (int)rank * per;
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
         }
     }
     __syncthreads();
-    lb_trace(p.trace, 3);
+    if (!LEAN) lb_trace(p.trace, 3);
 
     // ---- softmax over this slice, per head: the warps w with w % G == g share head g ----
     {
@@ -267,7 +269,7 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
             *reinterpret_cast<double4*>(red + ((size_t)warp * G + g) * hd + 4 * lane) = make_double4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
     }
     __syncthreads();
-    lb_trace(p.trace, 4);
+    if (!LEAN) lb_trace(p.trace, 4);
 
     // ---- hand this slice's partials to the CTAs that own the output dimensions ----
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // completes the arrive at the top: every CTA has started
@@ -312,7 +314,7 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
         }
         p.out[(size_t)n * p.heads * hd + (size_t)(kvh * G + g) * hd + (int)rank * dps + dd] = __ddiv_rn(num, dn);
     }
-    lb_trace(p.trace, 5);
+    if (!LEAN) lb_trace(p.trace, 5);
 }
 
 template <int G>
@@ -334,8 +336,9 @@ int launch_cluster(loom_b200_ctx* ctx, LbAttnParams p, int S, bool probe_only, i
     if (smem > 200 * 1024) return LOOM_B200_ERR_UNSUPPORTED;
     p.tile = tile_bytes;
     p.max_chunk = (p.msl + S - 1) / S;
-    auto kern = lb_attention_cluster_kernel<G>;
-    const unsigned bit = 1u << (G == 1 ? 0 : G == 2 ? 1 : G == 4 ? 2 : 3);  // one bit per instantiation, per context (= per device)
+    const bool lean = !probe_only && !p.trace && p.M == 1 && p.seq_stride <= 0;
+    auto kern = lean ? lb_attention_cluster_kernel<G, true> : lb_attention_cluster_kernel<G, false>;
+    const unsigned bit = 1u << ((G == 1 ? 0 : G == 2 ? 1 : G == 4 ? 2 : 3) + (lean ? 4 : 0));  // one bit per instantiation, per context (= per device)
     if (!(ctx->func_attr_mask2 & bit)) {
         LB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         LB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));

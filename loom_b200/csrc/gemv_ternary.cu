@@ -267,7 +267,15 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
         const uint8_t* tile = my_ring + (size_t)cstage * kStageBytes + lane * 16;
         const uint32_t* ab = act_base + cc.kb * act_kb_mul;
         if (!failed) {
-            if (len == kStageTiles) {
+            if (LEAN) {  // one rolled loop, two tiles per trip: half the code of the unrolled chunk plus its remainder loop
+                int i = 0;
+#pragma unroll 1
+                for (; i + 2 <= len; i += 2) {
+                    tile_step(tile + i * kTileBytes, ab + i * act_kb_mul);
+                    tile_step(tile + (i + 1) * kTileBytes, ab + (i + 1) * act_kb_mul);
+                }
+                if (i < len) tile_step(tile + i * kTileBytes, ab + i * act_kb_mul);
+            } else if (len == kStageTiles) {
 #pragma unroll
                 for (int i = 0; i < kStageTiles; ++i) tile_step(tile + i * kTileBytes, ab + i * act_kb_mul);
             } else {
