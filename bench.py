@@ -855,6 +855,7 @@ def main():
     tstream = torch.cuda.Stream()
     torch.cuda.set_stream(tstream)
     ctx = loom_b200.Context(local, tstream.cuda_stream)
+    apply_opts(ctx, args)
 
     dec, weights, emb = build_model(ctx, torch, shape, args.seed)
     rng = np.random.default_rng(args.seed)

@@ -364,7 +364,7 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
     } else if (!strcmp(key, "head_stream")) {
         ctx->opt_head_stream = value != 0;
     } else if (!strcmp(key, "attn_cluster")) {
-        ctx->opt_attn_cluster = value != 0;
+        ctx->opt_attn_cluster = value < 0 ? 0 : value;
     } else if (!strcmp(key, "pdl")) {
         ctx->opt_pdl = value != 0;
     } else if (!strcmp(key, "fold_rope")) {

@@ -70,7 +70,7 @@ struct loom_b200_ctx {
     unsigned func_attr_mask = 0;  // kernels whose shared-memory limit was raised on this device
     unsigned func_attr_mask2 = 0; // the same for the cluster attention instantiations
     int opt_head_stream = 1;      // the LM head streams its rows through shared memory with bulk copies (0 = warp-per-row loads)
-    int opt_attn_cluster = 1;     // one-token decoder steps run the attention as a thread-block cluster per KV head
+    int opt_attn_cluster = 1;     // one-token decoder steps run the attention as a thread-block cluster per KV head (0: off, 1: the largest cluster that fits, 2..16: at most that many CTAs)
     // tuning knobs (loom_b200_ctx_set_option; initial values from LOOM_B200_* environment variables)
     int opt_gemv_variant = 0;      // 0 = integer-MMA inner loop, 1 = dp4a inner loop (batch 1 only)
     int opt_gemv_ctas_per_sm = 2;  // grid = SMs * this
