@@ -393,7 +393,9 @@ int lb_attention_cluster_size(loom_b200_ctx* ctx, const LbAttnParams& p) {
     if (G != 1 && G != 2 && G != 4 && G != 8) return 0;
     if (p.hd % 16 != 0 || p.hd > 128 || p.hd < 16) return 0;
     // the largest cluster that the device can keep resident for every KV head at once; smaller ones if not
+    const int smax = ctx->opt_attn_cluster >= 2 && ctx->opt_attn_cluster < kAcMaxS ? ctx->opt_attn_cluster : kAcMaxS;  // option: 1 = the largest that fits, 2..16 = at most that
     for (int S = kAcMaxS; S >= 2; S >>= 1) {
+        if (S > smax) continue;
         if (p.hd % S != 0) continue;
         int active = 0;
         if (dispatch_cluster(ctx, p, S, true, &active) != 0) continue;
