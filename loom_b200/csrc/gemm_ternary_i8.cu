@@ -446,11 +446,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_stream_kernel(const G
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    lb_pdl_launch_dependents();
 
     if (warp == kLoadWarp) {
         // ---------------- loads: per stage the activations of the tile's tokens and the code block(s) of its rows ----------------
         bool failed = false;
         uint32_t it = 0;
+        // The weights do not depend on the quantizer that runs before this kernel: the code blocks of the first stages
+        // are requested before the dependency wait, their activations after it (one barrier counts the bytes of both).
+        int pre = 0;
+        if (my_tiles > 0) {
+            const int rt0 = (int)blockIdx.x % row_tiles;
+            const size_t blk00 = (size_t)rt0 * ktot * kSliceBytesA;
+            pre = ktot < kStages ? ktot : kStages;
+            if (lane == 0) {
+                for (int ks = 0; ks < pre; ++ks) {
+                    lb_mbar_expect_tx(&load_bar[ks], (uint32_t)Cfg::kStageBytes);
+                    lb_bulk_g2s(a_ring + (size_t)ks * Cfg::kBytesA, p.codes8 + blk00 + (size_t)ks * kSliceBytesA, (uint32_t)kSliceBytesA, &load_bar[ks]);
+                    if (DUAL)
+                        lb_bulk_g2s(a_ring + (size_t)ks * Cfg::kBytesA + kSliceBytesA, p.codes8_up + blk00 + (size_t)ks * kSliceBytesA,
+                                    (uint32_t)kSliceBytesA, &load_bar[ks]);
+                }
+            }
+        }
+        lb_pdl_wait();
         for (int i = 0; i < my_tiles && !failed; ++i) {
             const int t = (int)blockIdx.x + i * (int)gridDim.x;
             const int rt = t % row_tiles, tok0 = (t / row_tiles) * NTOK;
@@ -463,12 +482,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_stream_kernel(const G
                     break;
                 }
                 if (lane == 0) {
-                    lb_mbar_expect_tx(&load_bar[s], (uint32_t)Cfg::kStageBytes);
+                    const bool a_done = i == 0 && ks < pre;  // requested before the dependency wait
+                    if (!a_done) lb_mbar_expect_tx(&load_bar[s], (uint32_t)Cfg::kStageBytes);
                     lb_bulk_g2s(b_ring + (size_t)s * Cfg::kBytesB, qbase + (size_t)ks * 32768, (uint32_t)Cfg::kBytesB, &load_bar[s]);
-                    lb_bulk_g2s(a_ring + (size_t)s * Cfg::kBytesA, p.codes8 + blk0 + (size_t)ks * kSliceBytesA, (uint32_t)kSliceBytesA, &load_bar[s]);
-                    if (DUAL)
-                        lb_bulk_g2s(a_ring + (size_t)s * Cfg::kBytesA + kSliceBytesA, p.codes8_up + blk0 + (size_t)ks * kSliceBytesA,
-                                    (uint32_t)kSliceBytesA, &load_bar[s]);
+                    if (!a_done) {
+                        lb_bulk_g2s(a_ring + (size_t)s * Cfg::kBytesA, p.codes8 + blk0 + (size_t)ks * kSliceBytesA, (uint32_t)kSliceBytesA, &load_bar[s]);
+                        if (DUAL)
+                            lb_bulk_g2s(a_ring + (size_t)s * Cfg::kBytesA + kSliceBytesA, p.codes8_up + blk0 + (size_t)ks * kSliceBytesA,
+                                        (uint32_t)kSliceBytesA, &load_bar[s]);
+                    }
                 }
                 __syncwarp();
             }
@@ -521,6 +543,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) lb_gemm_stream_kernel(const G
         // a warp may only touch the 32 TMEM lanes of its quarter (warp % 4); the two warps of a quarter split the columns
         const int quarter = warp & 3, chalf = warp >> 2;
         bool failed = false;  // after a wait ran out the warp keeps walking the tiles (its named-barrier count must match) without touching TMEM or memory
+        lb_pdl_wait();  // the per-token scales, the residual rows and the output buffer belong to earlier launches until here
         for (int i = 0; i < my_tiles; ++i) {
             const int t = (int)blockIdx.x + i * (int)gridDim.x;
             const int rt = t % row_tiles, tok0 = (t / row_tiles) * NTOK, buf = i & 1;
@@ -747,6 +770,11 @@ __global__ void __launch_bounds__(256) lb_quantize_gemm_regs_kernel(const LbGemm
     int8_t* qrow = q + (size_t)(blockIdx.x >> 8) * (Kp >> 7) * 32768 + (size_t)((blockIdx.x & 255) >> 3) * 1024 + (blockIdx.x & 7) * 16;
     auto chunk_ptr = [&](int ch) { return reinterpret_cast<uint4*>(qrow + (size_t)(ch >> 3) * 32768 + (ch & 7) * 128); };
     const int nchunks = Kp >> 4;
+    // programmatic dependent launch: the GEMM that follows may set itself up (barriers, tensor memory, first weight
+    // blocks) while this kernel runs; this kernel reads its rows, and overwrites the activation image the previous GEMM
+    // was reading, only after everything before it is complete
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
     if ((int)blockIdx.x >= a.tokens) {  // padding token: zeros
         for (int ch = tid; ch < nchunks; ch += T) *chunk_ptr(ch) = make_uint4(0u, 0u, 0u, 0u);
         return;
@@ -933,7 +961,17 @@ int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a) {
     LB_REQUIRE(ctx, !(a.given_ss || a.given_amax) || regs_ok, "gemm_quantize: rows of %d columns with agreed statistics are not supported", a.K);
     if ((ctx->opt_quant_regs || a.given_ss || a.given_amax) && regs_ok) {
         const int T = ((nchunks + cpt - 1) / cpt + 31) / 32 * 32;
-#define LB_QREG(PRO, CPT) lb_quantize_gemm_regs_kernel<PRO, CPT><<<pt, T, 0, ctx->stream>>>(a, Kp, g.q, g.amax, g.xsum)
+        cudaLaunchConfig_t qcfg = {};
+        qcfg.gridDim = dim3(pt);
+        qcfg.blockDim = dim3(T);
+        qcfg.stream = ctx->stream;
+        cudaLaunchAttribute qattr[1];
+        qattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        qattr[0].val.programmaticStreamSerializationAllowed = 1;
+        qcfg.attrs = qattr;
+        qcfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+        cudaError_t qerr = cudaSuccess;
+#define LB_QREG(PRO, CPT) qerr = cudaLaunchKernelEx(&qcfg, lb_quantize_gemm_regs_kernel<PRO, CPT>, a, Kp, g.q, g.amax, g.xsum)
 #define LB_QREG_PRO(PRO)            \
     switch (cpt) {                  \
         case 1: LB_QREG(PRO, 1); break; \
@@ -956,7 +994,7 @@ int lb_gemm_quantize(loom_b200_ctx* ctx, const LbGemmQuant& a) {
         }
 #undef LB_QREG_PRO
 #undef LB_QREG
-        LB_CHECK_LAUNCH(ctx, "lb_quantize_gemm_regs_kernel");
+        LB_CUDA(ctx, qerr);
         ctx->launches++;
         return 0;
     }
@@ -1013,6 +1051,7 @@ static bool gemm_ensure_codes(loom_b200_ctx* ctx, const loom_b200_weight* wc) {
     }
     ctx->launches++;
     w->codes8 = c;
+    ctx->gemm_codes_fresh = true;  // the next GEMM launch reads these before its dependency wait: it must not start early
     return true;
 }
 
@@ -1040,8 +1079,19 @@ static int gemm_launch_stream(loom_b200_ctx* ctx, const GemmParams& p, unsigned 
     const int row_tiles = (p.rows + kRowsPerCta - 1) / kRowsPerCta;
     const int ntiles = row_tiles * ((p.tokens + NTOK - 1) / NTOK);
     const int grid = ntiles < ctx->sm_count ? ntiles : ctx->sm_count;
-    lb_gemm_stream_kernel<NTOK, DUAL><<<grid, kGemmThreads, Cfg::kSmem, ctx->stream>>>(p, row_tiles, ntiles);
-    LB_CHECK_LAUNCH(ctx, "lb_gemm_stream_kernel");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    // (a launch that follows the build of its code cache starts only when that build is complete and visible)
+    cfg.numAttrs = ctx->opt_pdl && !ctx->gemm_codes_fresh ? 1 : 0;
+    ctx->gemm_codes_fresh = false;
+    LB_CUDA(ctx, cudaLaunchKernelEx(&cfg, lb_gemm_stream_kernel<NTOK, DUAL>, p, row_tiles, ntiles));
     ctx->launches++;
     return 0;
 }
