@@ -145,7 +145,7 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
             const float4 a = reinterpret_cast<const float4*>(row)[idx];
             a0 = (VT)a.x; a1 = (VT)a.y; a2 = (VT)a.z; a3 = (VT)a.w;
         }
-        if (have_w && !sm.gain && 4 * idx < p.norm_w_len) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.norm_w + 4 * idx));
+        if (!LEAN && have_w && !sm.gain && 4 * idx < p.norm_w_len) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.norm_w + 4 * idx));
         tmp[4 * idx] = a0; tmp[4 * idx + 1] = a1; tmp[4 * idx + 2] = a2; tmp[4 * idx + 3] = a3;
         if (PRO >= LB_PRO_BLOCKNORM) {
             const double d0 = lb_wide(a0), d1 = lb_wide(a1), d2 = lb_wide(a2), d3 = lb_wide(a3);
@@ -164,7 +164,7 @@ __device__ __forceinline__ void stage_row_fast(const LbGemvParams& p, const Smem
         const double mean = __dadd_rn(__ddiv_rn(ss, (double)(p.norm_count > 0 ? p.norm_count : K)), p.eps);
         const double root = sqrt(mean);
         const double rr = __ddiv_rn(1.0, root);  // RN(1/rms): the inner norms' scale, the block norm's reciprocal
-        const float* gw = sm.gain ? sm.gain : p.norm_w;  // the shared copy was made while waiting for the producer of the row
+        const float* gw = (LEAN || sm.gain) ? sm.gain : p.norm_w;  // the shared copy was made while waiting for the producer of the row (lean: always)
 #pragma unroll 2
         for (int idx = tid; idx < units; idx += kThreads) {
             double w[4] = {1.0, 1.0, 1.0, 1.0};

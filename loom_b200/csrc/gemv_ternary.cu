@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     // first ring fill: weights do not depend on the producer of the activations
     Cursor ic;
     ic.pos = w0;
-    if (aligned && KB > 1 && KB <= 256 && (unsigned)(w0 - t0) < 65536u) {  // t0 is a strip boundary: only the small offset needs dividing
+    if (LEAN || (aligned && KB > 1 && KB <= 256 && (unsigned)(w0 - t0) < 65536u)) {  // t0 is a strip boundary: only the small offset needs dividing (the lean launcher checked the ranges)
         const int dv = (int)__umulhi((unsigned)(w0 - t0), p.kb_magic);
         ic.v = local_v0 + dv;
         ic.kb = (w0 - t0) - dv * KB;
@@ -146,7 +146,8 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     if (sm.gain) {
         const int n4 = p.norm_w_len >> 2;
         for (int i = tid; i < n4; i += kThreads) reinterpret_cast<float4*>(sm.gain)[i] = __ldg(reinterpret_cast<const float4*>(p.norm_w) + i);
-        for (int i = (n4 << 2) + tid; i < p.norm_w_len; i += kThreads) sm.gain[i] = __ldg(p.norm_w + i);
+        if (!LEAN)  // (lean: the gains cover a row of K % 4 == 0 columns)
+            for (int i = (n4 << 2) + tid; i < p.norm_w_len; i += kThreads) sm.gain[i] = __ldg(p.norm_w + i);
     }
     lb_pdl_launch_dependents();  // the next launch may start prefetching its weights
     LB_TRACE(1);
@@ -254,15 +255,17 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
 
     int cstage = 0;
     uint32_t cphase = 0;
-    while (cc.pos < w1) {
+    for (;;) {  // (one copy of the flush in the code: the sums of a strip are handed over when the next strip, or the end, comes up)
+        const bool done = cc.pos >= w1;
+        if (done || cc.v != cur_v) {
+            flush();
+            cur_v = cc.v;
+        }
+        if (done) break;
         const int len = chunk_len(cc);
         if (!failed && !lb_mbar_wait_bounded(&my_bars[cstage], cphase)) {
             failed = true;
             if (lane == 0) atomicExch(p.status, 1);
-        }
-        if (cc.v != cur_v) {
-            flush();
-            cur_v = cc.v;
         }
         const uint8_t* tile = my_ring + (size_t)cstage * kStageBytes + lane * 16;
         const uint32_t* ab = act_base + cc.kb * act_kb_mul;
@@ -297,7 +300,6 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
             cphase ^= 1u;
         }
     }
-    flush();
     __syncthreads();
     LB_TRACE(4);
 
@@ -360,15 +362,24 @@ __global__ void __launch_bounds__(kThreads, 2) lb_gemv_ternary_kernel(const __gr
     if (aligned) {  // every group is this CTA's own: no fix-up, no flags
         const int ngl_a = p.part_q + ((int)blockIdx.x < p.part_r ? 1 : 0);
         for (int idx = tid; idx < ngl_a * per_group; idx += kThreads) {
-            int gl, i;
-            if (per_group == 16) {
-                gl = idx >> 4;
-                i = idx & 15;
+            int gl, i, e, rem;
+            if (LEAN) {  // a power-of-two token count (the launcher checked): shifts instead of divisions
+                const int msh = 31 - __clz(M * 16), gsh = msh + (p.group == 2 ? 1 : 0);
+                gl = idx >> gsh;
+                i = idx & ((1 << gsh) - 1);
+                e = i >> msh;
+                rem = i & ((1 << msh) - 1);
             } else {
-                gl = idx / per_group;
-                i = idx - gl * per_group;
+                if (per_group == 16) {
+                    gl = idx >> 4;
+                    i = idx & 15;
+                } else {
+                    gl = idx / per_group;
+                    i = idx - gl * per_group;
+                }
+                e = i / (M * 16);
+                rem = i - e * (M * 16);
             }
-            const int e = i / (M * 16), rem = i - e * (M * 16);
             finish_row<EPI, LEAN>(p, sm, (first_group + gl) * p.group, e, rem >> 4, rem & 15, sm.sacc + (size_t)gl * per_group);
         }
         LB_TRACE(5);
@@ -624,10 +635,13 @@ int lb_launch_gemv(loom_b200_ctx* ctx, const LbGemvParams& pin) {
 #undef LB_PICK
     // the lean instantiations: the launches of a decode step (fused prologues), and their int8-row forms (a pass of several
     // sequences, tensor-parallel row shards, the plain ternary linear)
-    const bool lean_base = ctx->opt_gemv_lean && !p.trace && p.aligned && !use_dp4a;
+    // (cursor start by multiplication: 1 < k-blocks <= 256 and fewer than 65536 tiles per CTA; epilogue indices by shifts:
+    //  a power-of-two token count)
+    const bool lean_base = ctx->opt_gemv_lean && !p.trace && p.aligned && !use_dp4a && p.kblocks > 1 && p.kblocks <= 256 &&
+                           (long long)(p.part_q + 1) * p.group * p.kblocks < 65536 && (p.M & (p.M - 1)) == 0;
     const bool lean = lean_base && (p.pro == LB_PRO_Q8 ||
                                     (p.stage_bytes > 0 && (p.K & 3) == 0 && (((uintptr_t)p.x) & 15) == 0 &&
-                                     (!p.norm_w || ((((uintptr_t)p.norm_w) & 15) == 0 && p.norm_w_len == p.K)) && !p.norm_out && !p.q_out &&
+                                     (!p.norm_w || ((((uintptr_t)p.norm_w) & 15) == 0 && p.norm_w_len == p.K && p.gain_bytes > 0)) && !p.norm_out && !p.q_out &&
                                      !p.amax_out && !p.given_ss && !p.given_amax));
 #define LB_PICK_LEAN(id, pro_, epi_)                              \
     if (lean && p.pro == pro_ && p.epi == epi_) {                 \
