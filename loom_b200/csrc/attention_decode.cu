@@ -90,7 +90,7 @@ template <int G, bool LEAN = false>
 __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(const LbAttnParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2];
-    __shared__ double s_red[kAcWarps];
+    __shared__ double s_red[kAcWarps], s_red2[kAcWarps];  // per-warp maxima, per-warp sums (separate: no barrier between the two reductions)
     __shared__ double s_m[G], s_l[G];        // this CTA's maximum and sum per head
     __shared__ double s_gw[kAcMaxS * G];     // combine: weight of every (slice, head)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -221,7 +221,6 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
         mx = s_red[g];
 #pragma unroll
         for (int w = 1; w < WPG; ++w) mx = fmax(mx, s_red[g + w * G]);
-        __syncthreads();
         double sum = 0.0;
         for (int j = wq * 32 + lane; j < cnt; j += WPG * 32) {
             const double e = exp(__dsub_rn(sc[g * cmax + j], mx));
@@ -229,11 +228,11 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
             sum = __dadd_rn(sum, e);
         }
         sum = lb_warp_sum(sum);
-        if (lane == 0) s_red[warp] = sum;
+        if (lane == 0) s_red2[warp] = sum;
         __syncthreads();
         if (tid < G) {
             double l = 0.0;
-            for (int w = 0; w < WPG; ++w) l += s_red[tid + w * G];
+            for (int w = 0; w < WPG; ++w) l += s_red2[tid + w * G];
             s_l[tid] = l;
         }
         if (wq == 0 && lane == 0) s_m[g] = mx;  // every warp of head g holds the same maximum
