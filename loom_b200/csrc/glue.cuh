@@ -50,7 +50,7 @@ struct LbAttnParams {
 int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p);
 // One-token steps with RoPE folded in: the cluster kernel (attention_decode.cu).  lb_attention_cluster_size returns the
 // cluster size to use (CTAs per KV head), or 0 when the shape or the device does not allow it; the launch takes that size.
-int lb_attention_cluster_size(loom_b200_ctx* ctx, const LbAttnParams& p);
+int lb_attention_cluster_size(loom_b200_ctx* ctx, const LbAttnParams& p, bool one_wave);
 int lb_launch_attention_cluster(loom_b200_ctx* ctx, const LbAttnParams& p, int cluster);
 size_t lb_attn_part_elems(int M, int heads, int hd, int splits);
 // The same attention for a block of M prompt tokens at once (splits, part and cnt are not used): K/V tiles are shared

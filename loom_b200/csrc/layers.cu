@@ -105,8 +105,9 @@ void lb_mha_release(loom_b200_mha* m) {
 }
 
 // CTAs per KV head of the cluster attention for this layer's shape (0 = not usable); decided once
-static int mha_cluster_size(loom_b200_mha* m) {
-    if (m->attn_cluster < 0) {
+static int mha_cluster_size(loom_b200_mha* m, bool lanes = false) {
+    int& slot = lanes ? m->attn_cluster_lanes : m->attn_cluster;
+    if (slot < 0) {
         LbAttnParams t = {};
         t.M = 1;
         t.heads = m->heads;
@@ -116,16 +117,16 @@ static int mha_cluster_size(loom_b200_mha* m) {
         t.rope_div = m->rope_div;
         t.k_new = m->k_new;
         t.cache_k_w = m->cache_k;
-        m->attn_cluster = m->ctx->opt_attn_cluster ? lb_attention_cluster_size(m->ctx, t) : 0;
+        slot = m->ctx->opt_attn_cluster ? lb_attention_cluster_size(m->ctx, t, !lanes) : 0;
     }
-    return m->attn_cluster;
+    return slot;
 }
 
 static bool mha_folds_rope(loom_b200_mha* m, const LbMhaStepArgs& a) {
     // one token of one sequence: RoPE goes into the attention kernel; one token of each of several sequences: only the
     // cluster kernel knows that layout, otherwise RoPE runs as a launch of its own
     if (!a.fold_rope || m->q_norm || m->k_norm || !m->ctx->opt_fold_rope || m->head_dim % 8 != 0) return false;
-    if (a.lanes_pos) return mha_cluster_size(m) > 0;
+    if (a.lanes_pos) return mha_cluster_size(m, true) > 0;
     return a.M == 1;
 }
 
@@ -217,10 +218,10 @@ int lb_mha_attn_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
         t.rope_div = m->rope_div;
         t.k_new = m->k_new;
         t.cache_k_w = a.lanes_pos ? m->cache_k_base + (size_t)a.lane0 * m->ring_elems : m->cache_k;
-        if (mha_cluster_size(m) > 0) {
+        if (mha_cluster_size(m, a.lanes_pos != nullptr) > 0) {
             t.next_k = a.lanes_pos ? nullptr : m->next_k;  // (the prefetch follows one sequence's rings)
             t.next_v = a.lanes_pos ? nullptr : m->next_v;
-            return lb_launch_attention_cluster(ctx, t, m->attn_cluster);
+            return lb_launch_attention_cluster(ctx, t, mha_cluster_size(m, a.lanes_pos != nullptr));
         }
     }
     return lb_launch_attention(ctx, t);

@@ -55,6 +55,7 @@ struct loom_b200_mha {
     int splits = 1, max_total = 0;
     float* k_new = nullptr;                        // [kv_dim] the newest K row before RoPE (one-token steps with RoPE folded into attention)
     int attn_cluster = -1;                         // CTAs per KV head of the cluster attention (0 = not usable, -1 = not decided yet)
+    int attn_cluster_lanes = -1;                   // the same for a pass of several sequences (clusters may run in waves)
     const float *next_k = nullptr, *next_v = nullptr;  // KV rings of the decoder block that follows (L2 prefetch), or null
     // tensor parallelism: > 0 when this object holds heads/world heads (wq/wk/wv row slices, wo a column slice);
     // the value is the unsharded heads*head_dim.  Scratch as for the SwiGLU arguments, borrowed from the decoder.
