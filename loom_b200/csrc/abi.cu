@@ -377,6 +377,8 @@ int loom_b200_ctx_set_option(loom_b200_ctx* ctx, const char* key, int value) {
     } else if (!strcmp(key, "gemm_tile")) {
         if (value != 0 && value != 128 && value != 256) return lb_fail(ctx, LOOM_B200_ERR_INVALID, "ctx_set_option: gemm_tile is 0, 128 or 256");
         ctx->opt_gemm_tile = value;
+    } else if (!strcmp(key, "attn_stream")) {
+        ctx->opt_attn_stream = value != 0;
     } else if (!strcmp(key, "gemv_lean")) {
         ctx->opt_gemv_lean = value != 0;
     } else if (!strcmp(key, "tp_fused")) {

@@ -316,6 +316,207 @@ __global__ void __launch_bounds__(kAcThreads, 1) lb_attention_cluster_kernel(con
     if (!LEAN) lb_trace(p.trace, 5);
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// The throughput form for a pass of several sequences (one new token each): ONE CTA per (sequence, KV head) streams the
+// sequence's whole context through double-buffered 64-position tiles (one bulk copy per K and per V tile) and keeps a
+// running softmax, all query heads of the GQA group served from the same tiles.  A pass of eight sequences launches
+// kv_heads x 8 such CTAs, which fit the device at once; the cluster kernel above would need sixteen CTAs for each of them
+// and run in waves.  q arrives rotated and the newest K row is already in the ring (lb_rope_kernel ran before).
+// Arithmetic as above; the running softmax rescales by exp(m_old - m_new) per tile (float64).
+constexpr int kAsThreads = 256;
+constexpr int kAsWarps = kAsThreads / 32;
+constexpr int kAsTile = 64;  // positions per tile
+
+template <int G>
+__global__ void __launch_bounds__(kAsThreads, 1) lb_attention_stream_kernel(const LbAttnParams p) {
+    static_assert(G == 4 || G == 8, "group sizes the score reduction is laid out for");
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[4];  // [stage][K, V]
+    __shared__ double s_red[kAsWarps], s_red2[kAsWarps];
+    __shared__ double s_m[G], s_l[G], s_alpha[2][G];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hd = p.hd, kvh = blockIdx.x, n = blockIdx.y;
+    const size_t seq_off = (size_t)n * (size_t)(p.seq_stride > 0 ? p.seq_stride : 0);
+    const size_t tile_elems = (size_t)kAsTile * hd;
+    float* kt = reinterpret_cast<float*>(smem_raw);                 // [2][64, hd]
+    float* vt = kt + 2 * tile_elems;                                // [2][64, hd]
+    double* sq = reinterpret_cast<double*>(vt + 2 * tile_elems);    // [G, hd] queries
+    double* sc = sq + G * hd;                                       // [2][G, 64] scores, then weights, per tile parity
+    double* red = reinterpret_cast<double*>(smem_raw);              // after the last tile: [warps, G, hd] over the tiles
+    if (tid == 0) {
+        for (int i = 0; i < 4; ++i) lb_mbar_init(&bars[i], 1);
+        lb_fence_mbar_init();
+    }
+    __syncthreads();
+    lb_pdl_launch_dependents();
+    lb_pdl_wait();
+    const int last = p.seq_stride > 0 ? p.pos_ptr[n] : *p.pos_ptr + n;  // the token's position; it attends to 0..last
+    const int total = last + 1;
+    const int ntiles = (total + kAsTile - 1) / kAsTile;
+    const float* kbase = p.cache_k + seq_off + (size_t)kvh * p.msl * hd;
+    const float* vbase = p.cache_v + seq_off + (size_t)kvh * p.msl * hd;
+    const uint64_t pol = lb_policy_evict_first();
+    auto rows_of = [&](int t) { return total - t * kAsTile < kAsTile ? total - t * kAsTile : kAsTile; };
+    auto issue = [&](int t) {  // one thread
+        const int st = t & 1, rows = rows_of(t);
+        lb_mbar_expect_tx(&bars[2 * st], (uint32_t)rows * hd * 4);
+        lb_bulk_g2s_stream(kt + st * tile_elems, kbase + (size_t)t * kAsTile * hd, (uint32_t)rows * hd * 4, &bars[2 * st], pol);
+        lb_mbar_expect_tx(&bars[2 * st + 1], (uint32_t)rows * hd * 4);
+        lb_bulk_g2s_stream(vt + st * tile_elems, vbase + (size_t)t * kAsTile * hd, (uint32_t)rows * hd * 4, &bars[2 * st + 1], pol);
+    };
+    if (tid == 0) {
+        issue(0);
+        if (ntiles > 1) issue(1);
+    }
+    for (int idx = tid; idx < G * hd; idx += kAsThreads) sq[idx] = p.q[(size_t)n * p.heads * hd + (size_t)kvh * G * hd + idx];
+    if (tid < G) {
+        s_m[tid] = -1e300;
+        s_l[tid] = 0.0;
+    }
+    __syncthreads();
+    const double scale = __ddiv_rn(1.0, sqrt((double)hd));
+    const bool lane_on = 4 * lane < hd;
+    constexpr int PP = 16 / G;           // positions whose G sums are reduced together
+    constexpr int WPG = kAsWarps / G < 1 ? 1 : kAsWarps / G;  // warps that share a head in the softmax (G = 8: one)
+    double qv[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) qv[g][c] = lane_on ? sq[g * hd + 4 * lane + c] : 0.0;
+    const int vi = halving_index<16>(lane);
+    double o[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[g][c] = 0.0;
+    bool failed = false;
+    for (int t = 0; t < ntiles; ++t) {
+        const int st = t & 1, rows = rows_of(t);
+        const uint32_t ph = (uint32_t)((t >> 1) & 1);
+        const float* ktile = kt + st * tile_elems;
+        const float* vtile = vt + st * tile_elems;
+        double* sct = sc + (size_t)st * G * kAsTile;
+        if (!failed && !lb_mbar_wait_bounded(&bars[2 * st], ph)) failed = true;
+        // ---- scores of the tile: warp = eight positions, lane = four dimensions ----
+        for (int j0 = warp * (kAsTile / kAsWarps); j0 < (warp + 1) * (kAsTile / kAsWarps); j0 += PP) {
+            double acc[16];
+#pragma unroll
+            for (int pp = 0; pp < PP; ++pp) {
+                float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (lane_on && j0 + pp < rows) kv = *reinterpret_cast<const float4*>(ktile + (size_t)(j0 + pp) * hd + 4 * lane);
+                const double k0d = (double)kv.x, k1d = (double)kv.y, k2d = (double)kv.z, k3d = (double)kv.w;
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    double a = __dmul_rn(qv[g][0], k0d);
+                    a = fma(qv[g][1], k1d, a);
+                    a = fma(qv[g][2], k2d, a);
+                    a = fma(qv[g][3], k3d, a);
+                    acc[pp * G + g] = a;
+                }
+            }
+            warp_reduce_halving<16>(acc, lane);
+            const int pp = vi / G, g = vi - pp * G;
+            if ((lane & 1) == 0) sct[g * kAsTile + j0 + pp] = j0 + pp < rows ? __dmul_rn(acc[0], scale) : -1e300;  // absent positions: weight 0
+        }
+        __syncthreads();  // scores complete; every warp is past the weighted sum of tile t - 1
+        if (tid == 0 && t >= 1 && t + 1 < ntiles) issue(t + 1);  // into the buffers tile t - 1 has just left
+        // ---- running softmax, per head ----
+        {
+            const int g = warp % G, wq = warp / G;
+            double mx = -1e300;
+            for (int j = wq * 32 + lane; j < kAsTile; j += WPG * 32) mx = fmax(mx, sct[g * kAsTile + j]);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            if (lane == 0) s_red[warp] = mx;
+            __syncthreads();
+            mx = s_red[g];
+#pragma unroll
+            for (int w = 1; w < WPG; ++w) mx = fmax(mx, s_red[g + w * G]);
+            const double m_old = s_m[g];
+            const double m_new = fmax(m_old, mx);
+            double sum = 0.0;
+            for (int j = wq * 32 + lane; j < kAsTile; j += WPG * 32) {
+                const double e = j < rows ? exp(__dsub_rn(sct[g * kAsTile + j], m_new)) : 0.0;
+                sct[g * kAsTile + j] = e;
+                sum = __dadd_rn(sum, e);
+            }
+            sum = lb_warp_sum(sum);
+            if (lane == 0) s_red2[warp] = sum;
+            __syncthreads();  // weights and per-warp sums visible; everyone has read the old maximum
+            if (wq == 0 && lane == 0) {
+                double l = 0.0;
+                for (int w = 0; w < WPG; ++w) l += s_red2[g + w * G];
+                const double alpha = exp(__dsub_rn(m_old, m_new));  // 0 for the first tile (m_old = -1e300)
+                s_alpha[st][g] = alpha;
+                s_l[g] = __dadd_rn(__dmul_rn(s_l[g], alpha), l);
+                s_m[g] = m_new;
+            }
+        }
+        if (!failed && !lb_mbar_wait_bounded(&bars[2 * st + 1], ph)) failed = true;
+        __syncthreads();  // rescale factors visible
+        // ---- weighted V: warp = every eighth position, lane = four dimensions ----
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const double al = s_alpha[st][g];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) o[g][c] = __dmul_rn(o[g][c], al);
+        }
+        if (lane_on) {
+            for (int j = warp; j < rows; j += kAsWarps) {
+                const float4 vv = *reinterpret_cast<const float4*>(vtile + (size_t)j * hd + 4 * lane);
+                const double v0 = (double)vv.x, v1 = (double)vv.y, v2 = (double)vv.z, v3 = (double)vv.w;
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const double w = sct[g * kAsTile + j];
+                    o[g][0] = fma(w, v0, o[g][0]);
+                    o[g][1] = fma(w, v1, o[g][1]);
+                    o[g][2] = fma(w, v2, o[g][2]);
+                    o[g][3] = fma(w, v3, o[g][3]);
+                }
+            }
+        }
+    }
+    if (failed && tid == 0) atomicExch(p.status, 1);
+    __syncthreads();  // every warp is done with the tiles: the reduction buffer takes their place
+    if (lane_on) {
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+            *reinterpret_cast<double4*>(red + ((size_t)warp * G + g) * hd + 4 * lane) = make_double4(o[g][0], o[g][1], o[g][2], o[g][3]);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * hd; idx += kAsThreads) {
+        const int g = idx / hd, d = idx - g * hd;
+        double v = 0.0;
+#pragma unroll
+        for (int w = 0; w < kAsWarps; ++w) v += red[((size_t)w * G + g) * hd + d];  // fixed order: the same bits on every replay
+        p.out[(size_t)n * p.heads * hd + (size_t)(kvh * G + g) * hd + d] = __ddiv_rn(v, s_l[g]);
+    }
+}
+
+template <int G>
+int launch_stream_attention(loom_b200_ctx* ctx, const LbAttnParams& p) {
+    const size_t smem = (size_t)4 * kAsTile * p.hd * sizeof(float) + (size_t)G * p.hd * 8 + (size_t)2 * G * kAsTile * 8;
+    auto kern = lb_attention_stream_kernel<G>;
+    const unsigned bit = 1u << (G == 4 ? 13 : 14);  // (bits 0-7: the cluster kernel, 8-12: the streaming head, 16, 20-27: others)
+    if (!(ctx->func_attr_mask2 & bit)) {
+        LB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        ctx->func_attr_mask2 |= bit;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.kv_heads, p.M);
+    cfg.blockDim = dim3(kAsThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+    LB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p));
+    ctx->launches++;
+    return 0;
+}
+
 template <int G>
 size_t cluster_smem(const LbAttnParams& p, int S, int* tile_bytes) {
     const int cmax = (p.msl + S - 1) / S;
@@ -413,4 +614,19 @@ int lb_launch_attention_cluster(loom_b200_ctx* ctx, const LbAttnParams& pin, int
     int rc = dispatch_cluster(ctx, p, S, false, nullptr);
     if (rc == LOOM_B200_ERR_UNSUPPORTED) return lb_fail(ctx, rc, "attention (cluster): shape not supported");
     return rc;
+}
+
+// A pass of several sequences through the streaming kernel: head dimension 128 (tiles of 64 x 512 B), four or eight query
+// heads per KV head, plain attention (q rotated, the newest K row already in the ring).
+bool lb_attention_stream_supported(const loom_b200_ctx* ctx, const LbAttnParams& p) {
+    if (!ctx->opt_attn_stream || p.hd != 128 || p.kv_heads <= 0 || p.heads % p.kv_heads != 0) return false;
+    const int G = p.heads / p.kv_heads;
+    return G == 4 || G == 8;
+}
+
+int lb_launch_attention_stream(loom_b200_ctx* ctx, const LbAttnParams& pin) {
+    LbAttnParams p = pin;
+    p.status = ctx->status_dev;
+    p.trace = nullptr;
+    return p.heads / p.kv_heads == 4 ? launch_stream_attention<4>(ctx, p) : launch_stream_attention<8>(ctx, p);
 }

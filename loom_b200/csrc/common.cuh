@@ -88,6 +88,7 @@ struct loom_b200_ctx {
     int opt_gemm_tile = 0;         // tokens per CTA of the GEMM: 0 = choose, 128 or 256 = force
     int opt_prefill_gemm = 1;      // prompts of 32+ tokens run their projections as token-block GEMMs
     bool gemm_codes_fresh = false;  // a matrix's pre-expanded codes were built since the last GEMM launch
+    int opt_attn_stream = 1;       // a pass of several sequences runs the attention as one streaming CTA per (sequence, KV head)
     int opt_gemv_lean = 1;         // decode-step launches use the GEMV instantiations without the stream-K and general-prologue code
     int opt_tp_fused = 1;          // row-parallel projections under a peer-memory group: the GEMV's epilogue exchanges the partial sums (0: a finalize kernel does)
     int opt_quant_regs = 1;        // the GEMM's quantizer keeps a token's row in registers (0: staged in shared memory)

@@ -52,6 +52,10 @@ int lb_launch_attention(loom_b200_ctx* ctx, const LbAttnParams& p);
 // cluster size to use (CTAs per KV head), or 0 when the shape or the device does not allow it; the launch takes that size.
 int lb_attention_cluster_size(loom_b200_ctx* ctx, const LbAttnParams& p, bool one_wave);
 int lb_launch_attention_cluster(loom_b200_ctx* ctx, const LbAttnParams& p, int cluster);
+// A pass of several sequences (seq_stride > 0), plain attention: one CTA per (sequence, KV head) streams the context through
+// tiles with a running softmax (attention_decode.cu).
+bool lb_attention_stream_supported(const loom_b200_ctx* ctx, const LbAttnParams& p);
+int lb_launch_attention_stream(loom_b200_ctx* ctx, const LbAttnParams& p);
 size_t lb_attn_part_elems(int M, int heads, int hd, int splits);
 // The same attention for a block of M prompt tokens at once (splits, part and cnt are not used): K/V tiles are shared
 // by the heads of a GQA group and by 64/group consecutive query tokens.  Needs head_dim % 16 == 0, head_dim <= 128

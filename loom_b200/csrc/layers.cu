@@ -126,7 +126,15 @@ static bool mha_folds_rope(loom_b200_mha* m, const LbMhaStepArgs& a) {
     // one token of one sequence: RoPE goes into the attention kernel; one token of each of several sequences: only the
     // cluster kernel knows that layout, otherwise RoPE runs as a launch of its own
     if (!a.fold_rope || m->q_norm || m->k_norm || !m->ctx->opt_fold_rope || m->head_dim % 8 != 0) return false;
-    if (a.lanes_pos) return mha_cluster_size(m, true) > 0;
+    if (a.lanes_pos) {
+        // several sequences: the streaming kernel takes rotated queries and a complete ring (RoPE as a launch of its own)
+        LbAttnParams t = {};
+        t.heads = m->heads;
+        t.kv_heads = m->kv_heads;
+        t.hd = m->head_dim;
+        if (lb_attention_stream_supported(m->ctx, t)) return false;
+        return mha_cluster_size(m, true) > 0;
+    }
     return a.M == 1;
 }
 
@@ -224,6 +232,7 @@ int lb_mha_attn_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
             return lb_launch_attention_cluster(ctx, t, mha_cluster_size(m, a.lanes_pos != nullptr));
         }
     }
+    if (a.lanes_pos && lb_attention_stream_supported(ctx, t)) return lb_launch_attention_stream(ctx, t);
     return lb_launch_attention(ctx, t);
 }
 
