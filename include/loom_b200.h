@@ -100,6 +100,8 @@ void* loom_b200_ctx_stream(loom_b200_ctx* ctx);
  * token-block GEMM (0 = choose); "gemm_splitk" 0/1 = let several CTAs share the K range of an output tile;
  * "fold_rope" 0/1 = one-token decoder steps apply RoPE inside the attention kernel (one launch less per block);
  * "decode_splits" 0..32 = position splits of the one-token attention, read by loom_b200_decoder_create (0 = choose); "tp_peer" 0/1 = use the peer mailboxes when attached;
+ * "attn_stream" 0/1 = a pass of several sequences runs its attention as one streaming CTA per (sequence, KV head) (1, default) or as
+ * clusters / the split kernel (0);
  * "gemv_lean" 0/1 = one-token launches with a fused prologue use GEMV instantiations compiled without the stream-K, general-prologue
  * and phase-trace code (1, default: +7 % decode tok/s) or the full kernels (0);
  * "tp_fused" 0/1 = row-parallel projections under the peer mailboxes as statistics kernel + GEMV + finalize kernel (0), or with the
