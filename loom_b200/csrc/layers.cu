@@ -122,17 +122,26 @@ static int mha_cluster_size(loom_b200_mha* m, bool lanes = false) {
     return slot;
 }
 
+// A pass of M sequences: the streaming kernel (one CTA per sequence and KV head) when that many CTAs fill a good part of
+// the device or nothing else takes the shape; with few of them (tensor-parallel slices, few sequences) the cluster kernel's
+// sixteen CTAs per (sequence, KV head) are faster (measured at the 8B shape: 64 CTAs 15.4 against 15.7 ms per step on one
+// GPU, 32 CTAs 14.4 against 11.6 ms on two).
+static bool mha_lanes_stream(loom_b200_mha* m, int M) {
+    LbAttnParams t = {};
+    t.heads = m->heads;
+    t.kv_heads = m->kv_heads;
+    t.hd = m->head_dim;
+    if (!lb_attention_stream_supported(m->ctx, t)) return false;
+    return m->kv_heads * M >= 48 || mha_cluster_size(m, true) == 0;
+}
+
 static bool mha_folds_rope(loom_b200_mha* m, const LbMhaStepArgs& a) {
     // one token of one sequence: RoPE goes into the attention kernel; one token of each of several sequences: only the
     // cluster kernel knows that layout, otherwise RoPE runs as a launch of its own
     if (!a.fold_rope || m->q_norm || m->k_norm || !m->ctx->opt_fold_rope || m->head_dim % 8 != 0) return false;
     if (a.lanes_pos) {
         // several sequences: the streaming kernel takes rotated queries and a complete ring (RoPE as a launch of its own)
-        LbAttnParams t = {};
-        t.heads = m->heads;
-        t.kv_heads = m->kv_heads;
-        t.hd = m->head_dim;
-        if (lb_attention_stream_supported(m->ctx, t)) return false;
+        if (mha_lanes_stream(m, a.M)) return false;
         return mha_cluster_size(m, true) > 0;
     }
     return a.M == 1;
@@ -232,7 +241,7 @@ int lb_mha_attn_dev(loom_b200_mha* m, const LbMhaStepArgs& a) {
             return lb_launch_attention_cluster(ctx, t, mha_cluster_size(m, a.lanes_pos != nullptr));
         }
     }
-    if (a.lanes_pos && lb_attention_stream_supported(ctx, t)) return lb_launch_attention_stream(ctx, t);
+    if (a.lanes_pos && !fold_rope && mha_lanes_stream(m, a.M)) return lb_launch_attention_stream(ctx, t);
     return lb_launch_attention(ctx, t);
 }
 
