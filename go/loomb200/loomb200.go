@@ -328,6 +328,72 @@ func (dec *Decoder) Generate(prompt []int32, maxNew int) ([]int32, error) {
 	return out[:maxNew], dec.ctx.check(rc)
 }
 
+// Continue runs `steps` greedy steps on the device without waiting (the body of Generate's loop); ReadTokens returns the
+// last n tokens the loop fed to a forward.
+func (dec *Decoder) Continue(steps int) error {
+	return dec.ctx.check(C.loom_b200_decoder_continue(dec.d, C.int(steps)))
+}
+
+func (dec *Decoder) ReadTokens(n int) ([]int32, error) {
+	out := make([]int32, n)
+	rc := C.loom_b200_decoder_read_tokens(dec.d, (*C.int32_t)(unsafe.Pointer(&out[0])), C.int(n))
+	return out, dec.ctx.check(rc)
+}
+
+// SetLMHeadTernary installs an untied LM head given as a packed ternary matrix [vocab, hidden]
+// (poly/transformer.go:721-755); nil returns to the tied fp32 head.
+func (dec *Decoder) SetLMHeadTernary(head *Weight) error {
+	var w *C.loom_b200_weight
+	if head != nil {
+		w = head.w
+	}
+	return dec.ctx.check(C.loom_b200_decoder_set_lm_head_ternary(dec.d, w))
+}
+
+// SetKVOffset cuts the selected sequence back to an earlier position (the rings are not cleared).
+func (dec *Decoder) SetKVOffset(kvOffset int) error {
+	return dec.ctx.check(C.loom_b200_decoder_set_kv_offset(dec.d, C.int(kvOffset)))
+}
+
+// UploadCache restores the first kvOffset rows of a block's KV rings from host memory (position-major, like the cache
+// the CPU path keeps, poly/mha.go:269-270).
+func (dec *Decoder) UploadCache(block, kvOffset int, k, v []float32) error {
+	return dec.ctx.check(C.loom_b200_decoder_upload_cache(dec.d, C.int(block), C.int(kvOffset), f32ptr(k), f32ptr(v)))
+}
+
+// ---- independent sequences on one decoder (the reference shares one KV ring across a batch, poly/mha.go:258-270) ----
+
+// SetBatch gives the decoder `batch` sequences with KV rings of their own; call it before the first SetBlock.
+func (dec *Decoder) SetBatch(batch int) error {
+	return dec.ctx.check(C.loom_b200_decoder_set_batch(dec.d, C.int(batch)))
+}
+
+// Select picks the sequence the single-sequence calls (Forward for its prompt, KVOffset, Reset ...) act on.
+func (dec *Decoder) Select(seq int) error {
+	return dec.ctx.check(C.loom_b200_decoder_select(dec.d, C.int(seq)))
+}
+
+// StepBatch forwards one token per sequence (nil: continue greedily) and returns the logits [batch*vocab] (nil to skip).
+func (dec *Decoder) StepBatch(tokens []int32, logits []float32) error {
+	var t *C.int32_t
+	if len(tokens) > 0 {
+		t = (*C.int32_t)(unsafe.Pointer(&tokens[0]))
+	}
+	return dec.ctx.check(C.loom_b200_decoder_step_batch(dec.d, t, f32ptr(logits)))
+}
+
+// ContinueBatch runs `steps` greedy steps for all sequences on the device without waiting.
+func (dec *Decoder) ContinueBatch(steps int) error {
+	return dec.ctx.check(C.loom_b200_decoder_continue_batch(dec.d, C.int(steps)))
+}
+
+// ReadTokensBatch returns the last n tokens every sequence fed to a forward, [batch][n] flattened.
+func (dec *Decoder) ReadTokensBatch(batch, n int) ([]int32, error) {
+	out := make([]int32, batch*n)
+	rc := C.loom_b200_decoder_read_tokens_batch(dec.d, (*C.int32_t)(unsafe.Pointer(&out[0])), C.int(n))
+	return out, dec.ctx.check(rc)
+}
+
 func (dec *Decoder) Reset() error  { return dec.ctx.check(C.loom_b200_decoder_reset(dec.d)) }
 func (dec *Decoder) KVOffset() int { return int(C.loom_b200_decoder_kv_offset(dec.d)) }
 func (dec *Decoder) Close() {
